@@ -1,0 +1,112 @@
+// Shared declarations of the library's CUDA translation units: status handling, the
+// tiled weight layout, PTX wrappers (mbarrier, bulk copy, mma) and launch entry points.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/bitttt.h"
+
+namespace bt {
+
+// ---------------------------------------------------------------------------------------
+// Errors
+// ---------------------------------------------------------------------------------------
+bt_status set_error(bt_status code, const char* fmt, ...);
+void clear_error();
+
+#define BT_CUDA_TRY(expr)                                                                   \
+    do {                                                                                    \
+        cudaError_t _e = (expr);                                                            \
+        if (_e != cudaSuccess)                                                              \
+            return bt::set_error(BT_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,               \
+                                 cudaGetErrorString(_e), __FILE__, __LINE__);               \
+    } while (0)
+
+// Sticky device-side error word (one per device, allocated on first use).  Kernels write
+// a non-zero code when a bounded wait runs out; bt_device_check reads and clears it.
+unsigned int* device_error_word(int device);
+int device_sm_count(int device);
+
+// RAII device switch.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// ---------------------------------------------------------------------------------------
+// Tiled weight layout ("streaming layout") held in device memory
+// ---------------------------------------------------------------------------------------
+// One tile = 16 output rows x 256 inputs of ONE basis = 4096 two-bit fields = 1024 bytes.
+// Inside a tile, lane L = 4*g + t of a warp (g = L/4, t = L%4) owns two 16-byte chunks:
+//   bytes [16*L, 16*L+16)        : row g      , inputs [64*t, 64*t+64) of the tile
+//   bytes [512+16*L, 512+16*L+16): row g + 8  , same inputs
+// so one warp-wide 16-byte load is 512 contiguous bytes and lands directly in the A
+// operand slots of mma.m16n8k32.  Each 2-bit field holds u = t + 1 (t the ternary value:
+// 0 -> -1, 1 -> 0, 2 -> +1) instead of the reference's code (00/01/10 = 0/+1/-1,
+// kernels/packing.rs:9-13), which lets a single AND isolate a field as an unsigned
+// multiple of 4^r; the kernels subtract sum_k q once per token to undo the +1.
+// Reference code 11 (decodes to 0, kernels/cpu.rs:59) becomes u = 1.
+// Tiles are ordered [basis][row_tile][k_tile]; rows >= n_out and inputs >= k_in are
+// padded with u = 1 (weight 0).
+constexpr int kTileRows = 16;
+constexpr int kTileK = 256;
+constexpr int kTileBytes = 1024;
+
+struct TiledWeights {
+    const uint8_t* tiles = nullptr;  // device
+    int64_t n_out = 0, k_in = 0;
+    int64_t row_tiles = 0, k_tiles = 0;
+    int n_bases = 1;
+    int64_t basis_stride() const { return row_tiles * k_tiles * kTileBytes; }
+    int64_t k_pad() const { return k_tiles * kTileK; }
+};
+
+// Epilogue selector of the ternary product kernels.
+enum Epilogue : int {
+    EPI_I32 = 0,        // raw accumulators, int32 [m, n]
+    EPI_F32 = 1,        // (acc * s_w) * s_x[m]           -> f32 [m, n]
+    EPI_F32_ACCUM = 2,  // out += (acc * s_w) * s_x[m]    (further bases)
+    EPI_BF16 = 3,       // bf16((acc * s_w) * s_x[m])
+};
+
+// ---------------------------------------------------------------------------------------
+// Kernel launchers (defined in the .cu files)
+// ---------------------------------------------------------------------------------------
+
+// Re-tiles packed bytes (layout [n_out, k_in/4, n_bases], n_bases = 1 is the in-memory
+// PackedTensor layout) that already sit in device memory into the streaming layout.
+cudaError_t launch_retile(const uint8_t* src_dev, int64_t n_out, int64_t k_in, int n_bases,
+                          uint8_t* tiles_dev, int64_t row_tiles, int64_t k_tiles,
+                          cudaStream_t stream);
+
+// Per-token absmax int8 quantiser.  q rows are written with stride q_stride (>= k, bytes
+// between k and q_stride are zeroed).  qsum may be null.
+cudaError_t launch_act_quant(const void* x, bt_dtype x_dtype, int64_t m, int64_t k, int8_t* q,
+                             int64_t q_stride, float* s, int32_t* qsum, cudaStream_t stream);
+
+// Ternary product for up to 8 tokens per launch.
+struct GemvArgs {
+    const uint8_t* tiles;   // one basis
+    int64_t row_tiles, k_tiles, n_out;
+    const int8_t* q;        // [m, q_stride] int8, zero beyond k_in
+    int64_t q_stride;
+    const int32_t* qsum;    // [m]
+    const float* sx;        // [m] (unused for EPI_I32)
+    float sw;
+    int m;                  // 1..8
+    void* out;              // [m, n_out]
+    int64_t out_stride;     // elements between tokens
+    int epilogue;
+    unsigned int* err;
+};
+cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream);
+
+}  // namespace bt

@@ -1,0 +1,411 @@
+// extern "C" entry points for BitLinear: handles, workspaces, forward calls.
+#include <stdarg.h>
+#include <string.h>
+
+#include <mutex>
+#include <new>
+
+#include "bt_common.cuh"
+
+namespace bt {
+
+// ---------------------------------------------------------------------------------------
+// errors / per-device state
+// ---------------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+bt_status set_error(bt_status code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+void clear_error() { g_err[0] = 0; }
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    std::mutex mu;
+    bool init = false;
+    int sm_count = 0;
+    unsigned int* err_word = nullptr;
+};
+static DeviceState g_dev[kMaxDevices];
+
+static DeviceState* device_state(int device) {
+    if (device < 0 || device >= kMaxDevices) return nullptr;
+    DeviceState* st = &g_dev[device];
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (!st->init) {
+        DeviceGuard guard(device);
+        if (!guard.ok) return nullptr;
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return nullptr;
+        st->sm_count = prop.multiProcessorCount;
+        if (cudaMalloc(&st->err_word, sizeof(unsigned int)) != cudaSuccess) return nullptr;
+        if (cudaMemset(st->err_word, 0, sizeof(unsigned int)) != cudaSuccess) return nullptr;
+        st->init = true;
+    }
+    return st;
+}
+
+unsigned int* device_error_word(int device) {
+    DeviceState* st = device_state(device);
+    return st ? st->err_word : nullptr;
+}
+
+int device_sm_count(int device) {
+    DeviceState* st = device_state(device);
+    return st ? st->sm_count : 0;
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                        int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16_rn(in[i]);
+}
+
+}  // namespace bt
+
+// ---------------------------------------------------------------------------------------
+// handle types
+// ---------------------------------------------------------------------------------------
+struct bt_workspace {
+    int device = 0;
+    uint8_t* base = nullptr;
+    size_t bytes = 0;
+};
+
+struct bt_linear {
+    int device = 0;
+    bt::TiledWeights w;
+    uint8_t* tiles = nullptr;
+    float scales[8] = {0};
+    bt_workspace* own_ws = nullptr;
+    std::mutex ws_mu;
+};
+
+using namespace bt;
+
+extern "C" const char* bt_last_error(void) { return bt::g_err; }
+extern "C" int bt_version(void) { return 100; }
+
+extern "C" int bt_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+extern "C" bt_status bt_device_check(int device) {
+    DeviceGuard guard(device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "bt_device_check: cannot select device %d", device);
+    unsigned int* w = device_error_word(device);
+    if (!w) return set_error(BT_ERR_DEVICE, "bt_device_check: device %d not usable", device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    unsigned int v = 0;
+    BT_CUDA_TRY(cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        BT_CUDA_TRY(cudaMemset(w, 0, sizeof(v)));
+        return set_error(BT_ERR_TIMEOUT, "a bounded device-side wait ran out (kernel tag 0x%08x)", v);
+    }
+    return BT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// workspace
+// ---------------------------------------------------------------------------------------
+extern "C" bt_status bt_workspace_create(bt_workspace** out, int device, size_t bytes) {
+    if (!out) return set_error(BT_ERR_ARG, "bt_workspace_create: null out pointer");
+    *out = nullptr;
+    if (bt_device_count() <= device || device < 0)
+        return set_error(BT_ERR_DEVICE, "bt_workspace_create: no CUDA device %d", device);
+    if (bytes == 0) bytes = (size_t)48 << 20;
+    DeviceGuard guard(device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", device);
+    bt_workspace* ws = new (std::nothrow) bt_workspace();
+    if (!ws) return set_error(BT_ERR_NOMEM, "host allocation failed");
+    ws->device = device;
+    ws->bytes = bytes;
+    cudaError_t e = cudaMalloc(&ws->base, bytes);
+    if (e != cudaSuccess) {
+        delete ws;
+        return set_error(BT_ERR_NOMEM, "cudaMalloc of %zu workspace bytes failed: %s", bytes,
+                         cudaGetErrorString(e));
+    }
+    *out = ws;
+    return BT_OK;
+}
+
+extern "C" bt_status bt_workspace_destroy(bt_workspace* ws) {
+    if (!ws) return BT_OK;
+    DeviceGuard guard(ws->device);
+    cudaFree(ws->base);
+    delete ws;
+    return BT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// BitLinear handle
+// ---------------------------------------------------------------------------------------
+extern "C" bt_status bt_linear_create(bt_linear** out, const uint8_t* packed_host, int64_t n_out,
+                                      int64_t k_in, int n_bases, const float* scales_host,
+                                      int device) {
+    if (!out) return set_error(BT_ERR_ARG, "bt_linear_create: null out pointer");
+    *out = nullptr;
+    if (!packed_host || !scales_host) return set_error(BT_ERR_ARG, "bt_linear_create: null pointer");
+    if (n_out <= 0 || k_in <= 0) return set_error(BT_ERR_SHAPE, "bt_linear_create: empty weight [%lld, %lld]", (long long)n_out, (long long)k_in);
+    if (k_in % 4 != 0)
+        return set_error(BT_ERR_ALIGN, "bt_linear_create: in_features %lld is not a multiple of 4", (long long)k_in);
+    if (n_bases < 1 || n_bases > 8) return set_error(BT_ERR_ARG, "bt_linear_create: n_bases %d outside 1..8", n_bases);
+    if (bt_device_count() <= device || device < 0)
+        return set_error(BT_ERR_DEVICE, "bt_linear_create: no CUDA device %d", device);
+    DeviceGuard guard(device);
+    if (!guard.ok || !device_error_word(device))
+        return set_error(BT_ERR_DEVICE, "bt_linear_create: cannot use device %d", device);
+
+    bt_linear* lin = new (std::nothrow) bt_linear();
+    if (!lin) return set_error(BT_ERR_NOMEM, "host allocation failed");
+    lin->device = device;
+    lin->w.n_out = n_out;
+    lin->w.k_in = k_in;
+    lin->w.n_bases = n_bases;
+    lin->w.row_tiles = (n_out + kTileRows - 1) / kTileRows;
+    lin->w.k_tiles = (k_in + kTileK - 1) / kTileK;
+    for (int b = 0; b < n_bases; ++b) lin->scales[b] = scales_host[b];
+
+    const size_t raw_bytes = (size_t)n_out * (size_t)(k_in / 4) * (size_t)n_bases;
+    const size_t tile_bytes = (size_t)lin->w.basis_stride() * (size_t)n_bases;
+    uint8_t* raw = nullptr;
+    cudaError_t e = cudaMalloc(&lin->tiles, tile_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&raw, raw_bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(raw, packed_host, raw_bytes, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess)
+        e = launch_retile(raw, n_out, k_in, n_bases, lin->tiles, lin->w.row_tiles, lin->w.k_tiles, 0);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaFree(raw);
+    if (e != cudaSuccess) {
+        cudaFree(lin->tiles);
+        delete lin;
+        return set_error(e == cudaErrorMemoryAllocation ? BT_ERR_NOMEM : BT_ERR_CUDA,
+                         "bt_linear_create: %s", cudaGetErrorString(e));
+    }
+    lin->w.tiles = lin->tiles;
+    *out = lin;
+    return BT_OK;
+}
+
+extern "C" bt_status bt_linear_destroy(bt_linear* lin) {
+    if (!lin) return BT_OK;
+    DeviceGuard guard(lin->device);
+    cudaFree(lin->tiles);
+    if (lin->own_ws) bt_workspace_destroy(lin->own_ws);
+    delete lin;
+    return BT_OK;
+}
+
+extern "C" bt_status bt_linear_dims(const bt_linear* lin, int64_t* n_out, int64_t* k_in, int* n_bases) {
+    if (!lin) return set_error(BT_ERR_ARG, "bt_linear_dims: null handle");
+    if (n_out) *n_out = lin->w.n_out;
+    if (k_in) *k_in = lin->w.k_in;
+    if (n_bases) *n_bases = lin->w.n_bases;
+    return BT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------
+namespace {
+
+struct WsPlan {
+    int8_t* q;       // [m, k_pad]
+    float* sx;       // [m]
+    int32_t* qsum;   // [m]
+    float* ytmp;     // [m, n] f32 (only when bf16 output needs several bases)
+};
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+bt_status plan_workspace(bt_workspace* ws, int64_t m, int64_t k_pad, int64_t n, bool need_tmp,
+                         WsPlan* p) {
+    size_t off = 0;
+    const size_t q_off = off;          off = align_up(off + (size_t)m * k_pad, 256);
+    const size_t sx_off = off;         off = align_up(off + (size_t)m * 4, 256);
+    const size_t qs_off = off;         off = align_up(off + (size_t)m * 4, 256);
+    const size_t tmp_off = off;        if (need_tmp) off = align_up(off + (size_t)m * n * 4, 256);
+    if (off > ws->bytes)
+        return set_error(BT_ERR_NOMEM, "workspace of %zu bytes is too small: %zu needed for m=%lld",
+                         ws->bytes, off, (long long)m);
+    p->q = reinterpret_cast<int8_t*>(ws->base + q_off);
+    p->sx = reinterpret_cast<float*>(ws->base + sx_off);
+    p->qsum = reinterpret_cast<int32_t*>(ws->base + qs_off);
+    p->ytmp = need_tmp ? reinterpret_cast<float*>(ws->base + tmp_off) : nullptr;
+    return BT_OK;
+}
+
+bt_status resolve_workspace(bt_linear* lin, bt_workspace** ws) {
+    if (*ws) {
+        if ((*ws)->device != lin->device)
+            return set_error(BT_ERR_DEVICE, "workspace is on device %d, layer on device %d",
+                             (*ws)->device, lin->device);
+        return BT_OK;
+    }
+    std::lock_guard<std::mutex> lock(lin->ws_mu);
+    if (!lin->own_ws) {
+        bt_status st = bt_workspace_create(&lin->own_ws, lin->device, 0);
+        if (st != BT_OK) return st;
+    }
+    *ws = lin->own_ws;
+    return BT_OK;
+}
+
+// Runs the product for all tokens (8 per launch) and all bases on quantised activations.
+bt_status run_product(bt_linear* lin, const WsPlan& p, int64_t m, void* out, bt_dtype out_dtype,
+                      bool raw_i32, cudaStream_t stream) {
+    const int sm = device_sm_count(lin->device);
+    unsigned int* err = device_error_word(lin->device);
+    const int64_t n = lin->w.n_out;
+    const bool multi = lin->w.n_bases > 1 && !raw_i32;
+    const bool via_tmp = multi && out_dtype == BT_BF16;
+    for (int64_t m0 = 0; m0 < m; m0 += 8) {
+        const int mc = (int)(m - m0 < 8 ? m - m0 : 8);
+        const int bases = raw_i32 ? 1 : lin->w.n_bases;
+        for (int b = 0; b < bases; ++b) {
+            GemvArgs a;
+            a.tiles = lin->tiles + (size_t)b * lin->w.basis_stride();
+            a.row_tiles = lin->w.row_tiles;
+            a.k_tiles = lin->w.k_tiles;
+            a.n_out = n;
+            a.q = p.q + m0 * lin->w.k_pad();
+            a.q_stride = lin->w.k_pad();
+            a.qsum = p.qsum + m0;
+            a.sx = p.sx + m0;
+            a.sw = lin->scales[b];
+            a.m = mc;
+            a.out_stride = n;
+            a.err = err;
+            if (raw_i32) {
+                a.out = reinterpret_cast<int32_t*>(out) + m0 * n;
+                a.epilogue = EPI_I32;
+            } else if (via_tmp) {
+                a.out = p.ytmp + m0 * n;
+                a.epilogue = b == 0 ? EPI_F32 : EPI_F32_ACCUM;
+            } else if (out_dtype == BT_BF16) {
+                a.out = reinterpret_cast<__nv_bfloat16*>(out) + m0 * n;
+                a.epilogue = EPI_BF16;
+            } else {
+                a.out = reinterpret_cast<float*>(out) + m0 * n;
+                a.epilogue = b == 0 ? EPI_F32 : EPI_F32_ACCUM;
+            }
+            BT_CUDA_TRY(launch_gemv(a, sm, stream));
+        }
+    }
+    if (via_tmp) {
+        const int64_t total = m * n;
+        int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+        cast_f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(p.ytmp, reinterpret_cast<__nv_bfloat16*>(out), total);
+        BT_CUDA_TRY(cudaGetLastError());
+    }
+    return BT_OK;
+}
+
+}  // namespace
+
+extern "C" bt_status bt_linear_forward(bt_linear* lin, bt_workspace* ws, const void* x_dev, int64_t m,
+                                       int64_t x_k, bt_dtype x_dtype, void* y_dev, bt_dtype y_dtype,
+                                       void* stream) {
+    if (!lin) return set_error(BT_ERR_ARG, "bt_linear_forward: null handle");
+    if (x_k != lin->w.k_in)  // wording of kernels/cpu.rs:22-30, kernels/cuda.rs:27-35
+        return set_error(BT_ERR_SHAPE, "Shape mismatch: Input [%lld, %lld] vs Weight [%lld, %lld]",
+                         (long long)m, (long long)x_k, (long long)lin->w.n_out, (long long)lin->w.k_in);
+    if (m < 0) return set_error(BT_ERR_SHAPE, "bt_linear_forward: negative token count");
+    if ((x_dtype != BT_F32 && x_dtype != BT_BF16) || (y_dtype != BT_F32 && y_dtype != BT_BF16))
+        return set_error(BT_ERR_ARG, "bt_linear_forward: dtype must be BT_F32 or BT_BF16");
+    if (m == 0) return BT_OK;
+    if (!x_dev || !y_dev) return set_error(BT_ERR_ARG, "bt_linear_forward: null pointer");
+    DeviceGuard guard(lin->device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", lin->device);
+    bt_status st = resolve_workspace(lin, &ws);
+    if (st != BT_OK) return st;
+    WsPlan p;
+    st = plan_workspace(ws, m, lin->w.k_pad(), lin->w.n_out, lin->w.n_bases > 1 && y_dtype == BT_BF16, &p);
+    if (st != BT_OK) return st;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    BT_CUDA_TRY(launch_act_quant(x_dev, x_dtype, m, lin->w.k_in, p.q, lin->w.k_pad(), p.sx, p.qsum, s));
+    return run_product(lin, p, m, y_dev, y_dtype, false, s);
+}
+
+__global__ void qsum_rows_kernel(const int8_t* __restrict__ q, int64_t stride, int64_t k,
+                                 int32_t* __restrict__ qsum) {
+    // one warp per token
+    const int8_t* row = q + (int64_t)blockIdx.x * stride;
+    int s = 0;
+    for (int64_t c = threadIdx.x; c < k; c += 32) s += row[c];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (threadIdx.x == 0) qsum[blockIdx.x] = s;
+}
+
+extern "C" bt_status bt_linear_forward_q(bt_linear* lin, bt_workspace* ws, const int8_t* q_dev,
+                                         const float* sx_dev, int64_t m, void* out_dev,
+                                         bt_dtype out_dtype, void* stream) {
+    if (!lin || !q_dev || !out_dev) return set_error(BT_ERR_ARG, "bt_linear_forward_q: null pointer");
+    if (out_dtype != BT_I32 && out_dtype != BT_F32)
+        return set_error(BT_ERR_ARG, "bt_linear_forward_q: out_dtype must be BT_I32 or BT_F32");
+    if (out_dtype == BT_F32 && !sx_dev) return set_error(BT_ERR_ARG, "bt_linear_forward_q: scales needed for BT_F32");
+    if (m < 0) return set_error(BT_ERR_SHAPE, "bt_linear_forward_q: negative token count");
+    if (m == 0) return BT_OK;
+    DeviceGuard guard(lin->device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", lin->device);
+    bt_status st = resolve_workspace(lin, &ws);
+    if (st != BT_OK) return st;
+    WsPlan p;
+    st = plan_workspace(ws, m, lin->w.k_pad(), lin->w.n_out, false, &p);
+    if (st != BT_OK) return st;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t k = lin->w.k_in, kp = lin->w.k_pad();
+    // stage into rows of k_pad bytes, zero beyond k
+    if (kp != k) BT_CUDA_TRY(cudaMemsetAsync(p.q, 0, (size_t)m * kp, s));
+    BT_CUDA_TRY(cudaMemcpy2DAsync(p.q, (size_t)kp, q_dev, (size_t)k, (size_t)k, (size_t)m,
+                                  cudaMemcpyDeviceToDevice, s));
+    qsum_rows_kernel<<<(unsigned)m, 32, 0, s>>>(p.q, kp, k, p.qsum);
+    BT_CUDA_TRY(cudaGetLastError());
+    if (sx_dev) BT_CUDA_TRY(cudaMemcpyAsync(p.sx, sx_dev, (size_t)m * 4, cudaMemcpyDeviceToDevice, s));
+    return run_product(lin, p, m, out_dev, out_dtype, out_dtype == BT_I32, s);
+}
+
+extern "C" bt_status bt_linear_forward_host(bt_linear* lin, const float* x_host, int64_t m, int64_t x_k,
+                                            float* y_host) {
+    if (!lin || !x_host || !y_host) return set_error(BT_ERR_ARG, "bt_linear_forward_host: null pointer");
+    if (x_k != lin->w.k_in)
+        return set_error(BT_ERR_SHAPE, "Shape mismatch: Input [%lld, %lld] vs Weight [%lld, %lld]",
+                         (long long)m, (long long)x_k, (long long)lin->w.n_out, (long long)lin->w.k_in);
+    if (m <= 0) return m == 0 ? BT_OK : set_error(BT_ERR_SHAPE, "negative token count");
+    DeviceGuard guard(lin->device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", lin->device);
+    float *xd = nullptr, *yd = nullptr;
+    const size_t xb = (size_t)m * x_k * 4, yb = (size_t)m * lin->w.n_out * 4;
+    cudaError_t e = cudaMalloc(&xd, xb);
+    if (e == cudaSuccess) e = cudaMalloc(&yd, yb);
+    bt_status st = BT_OK;
+    if (e == cudaSuccess) e = cudaMemcpy(xd, x_host, xb, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) st = bt_linear_forward(lin, nullptr, xd, m, x_k, BT_F32, yd, BT_F32, nullptr);
+    if (e == cudaSuccess && st == BT_OK) e = cudaMemcpy(y_host, yd, yb, cudaMemcpyDeviceToHost);
+    cudaFree(xd);
+    cudaFree(yd);
+    if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "bt_linear_forward_host: %s", cudaGetErrorString(e));
+    return st;
+}
+
+extern "C" bt_status bt_act_quant(const void* x_dev, bt_dtype x_dtype, int64_t m, int64_t k, int8_t* q_dev,
+                                  float* s_dev, int32_t* qsum_dev, int device, void* stream) {
+    if (!x_dev || !q_dev || !s_dev) return set_error(BT_ERR_ARG, "bt_act_quant: null pointer");
+    if (x_dtype != BT_F32 && x_dtype != BT_BF16) return set_error(BT_ERR_ARG, "bt_act_quant: dtype must be BT_F32 or BT_BF16");
+    if (m < 0 || k <= 0) return set_error(BT_ERR_SHAPE, "bt_act_quant: bad shape [%lld, %lld]", (long long)m, (long long)k);
+    DeviceGuard guard(device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", device);
+    BT_CUDA_TRY(launch_act_quant(x_dev, x_dtype, m, k, q_dev, k, s_dev, qsum_dev, reinterpret_cast<cudaStream_t>(stream)));
+    return BT_OK;
+}

@@ -1,0 +1,79 @@
+"""CPU-only checks of the C-ABI library: it loads, exports every symbol that
+include/bitttt.h declares, packs like the reference, and fails cleanly without a GPU."""
+import ctypes as C
+import importlib
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def bt():
+    mod = importlib.import_module("bit-ttt-engine_b200")
+    mod.build.build_library()
+    mod.lib()
+    return mod
+
+
+def declared_symbols():
+    names = set()
+    for fn in os.listdir(os.path.join(ROOT, "include")):
+        if fn.endswith(".h"):
+            text = open(os.path.join(ROOT, "include", fn)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names |= set(re.findall(r"\b(bt_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_exports_every_declared_symbol(bt):
+    L = bt.lib()
+    syms = declared_symbols()
+    assert len(syms) >= 12
+    for s in syms:
+        assert hasattr(L, s), f"{s} declared in include/*.h but not exported"
+
+
+def test_host_packing_known_answers(bt):
+    # kernels/packing.rs:205-232 and :236-261
+    assert bt.unpack_ternary(np.array([73], np.uint8), 4, 1.0).tolist() == [1, -1, 0, 1]
+    data, scale = bt.pack_ternary(np.array([1, 1, 1, 1, -1], np.float32))
+    assert data.tolist() == [85, 2] and abs(scale - 1.0) < 1e-3
+    # :176-202
+    p = bt.PackedTensor.pack(np.array([1, -1, 0, 0, 1, -1, 0, 0], np.float32))
+    assert abs(p.scale - 0.5) < 1e-3
+    assert np.allclose(p.unpack(), [0.5, -0.5, 0, 0, 0.5, -0.5, 0, 0], atol=1e-4)
+
+
+def test_host_packing_matches_oracle(bt, oracle):
+    rng = np.random.default_rng(11)
+    for n in (1, 5, 64, 1000):
+        w = rng.normal(0, 0.02, n).astype(np.float32)
+        d, s = bt.pack_ternary(w)
+        d0, s0 = oracle.pack_l1(w)
+        assert np.array_equal(d, d0) and s == s0
+
+
+def test_errors_without_device(bt):
+    L = bt.lib()
+    if L.bt_device_count() > 0:
+        pytest.skip("a GPU is present")
+    h = C.c_void_p()
+    packed = np.zeros(16, np.uint8)
+    sc = np.ones(1, np.float32)
+    st = L.bt_linear_create(C.byref(h), packed.ctypes.data, 4, 16, 1, sc.ctypes.data, 0)
+    assert st == bt.BT_ERR_DEVICE and b"device" in L.bt_last_error()
+    # argument checks come before the device check
+    st = L.bt_linear_create(C.byref(h), packed.ctypes.data, 4, 18, 1, sc.ctypes.data, 0)
+    assert st == bt.BT_ERR_ALIGN and b"multiple of 4" in L.bt_last_error()
+    with pytest.raises(bt.BitTTTError):
+        bt.BitLinear.from_packed(packed, [1.0], 4, 16)
+
+
+def test_forward_before_pack_raises(bt):
+    lin = bt.BitLinear.load(8, 4, np.zeros((4, 8), np.float32))
+    with pytest.raises(RuntimeError, match="not packed"):
+        lin.forward(None)
