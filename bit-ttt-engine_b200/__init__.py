@@ -75,7 +75,13 @@ from .layers import (  # noqa: E402
     BitLinear, PackedTensor, Workspace, act_quant, pack_ternary, unpack_ternary,
 )
 
+from .model import (  # noqa: E402
+    BitLlama, BitLlamaConfig, QuantizedKVCache, attn_decode, ttt_update,
+)
+from . import model  # noqa: E402,F401
+
 __all__ = [
+    "BitLlama", "BitLlamaConfig", "QuantizedKVCache", "attn_decode", "ttt_update",
     "lib", "lib_path", "check", "BitTTTError", "BitLinear", "PackedTensor", "Workspace",
     "act_quant", "pack_ternary", "unpack_ternary",
 ]

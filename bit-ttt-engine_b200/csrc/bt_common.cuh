@@ -100,7 +100,7 @@ struct GemvArgs {
     int64_t q_stride;
     const int32_t* qsum;    // [m]
     const float* sx;        // [m] (unused for EPI_I32)
-    float sw;
+    const float* sw_tiles;  // [row_tiles] weight scale of each row tile (unused for EPI_I32)
     int m;                  // 1..8
     void* out;              // [m, n_out]
     int64_t out_stride;     // elements between tokens
@@ -108,5 +108,21 @@ struct GemvArgs {
     unsigned int* err;
 };
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream);
+
+// A BitLinear as the kernels see it: tiles of every basis plus one weight scale per
+// (basis, row tile) - fused projections (q|k|v, gate|up) carry a different scale per
+// segment of rows.
+struct LinearDev {
+    TiledWeights w;
+    const float* scale_tiles = nullptr;  // device, [n_bases][row_tiles]
+};
+
+// Ternary product of `m` quantised tokens with every basis of `lin` (8 tokens per launch).
+// epilogue: EPI_I32 (basis 0 only), EPI_F32, EPI_F32_ACCUM (adds onto out) or EPI_BF16
+// (single basis only).
+cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stride,
+                           const int32_t* qsum, const float* sx, int64_t m, void* out,
+                           int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
+                           cudaStream_t stream);
 
 }  // namespace bt

@@ -1,0 +1,39 @@
+// Definitions of the opaque handle types shared between the C-ABI translation units.
+#pragma once
+
+#include <mutex>
+
+#include "bt_model.cuh"
+
+struct bt_workspace {
+    int device = 0;
+    uint8_t* base = nullptr;
+    size_t bytes = 0;
+};
+
+struct bt_linear {
+    int device = 0;
+    bt::TiledWeights w;
+    uint8_t* tiles = nullptr;
+    float* scale_tiles = nullptr;  // device [n_bases][row_tiles]
+    float scales[8] = {0};
+    bt_workspace* own_ws = nullptr;
+    std::mutex ws_mu;
+    bt::LinearDev dev() const {
+        bt::LinearDev d;
+        d.w = w;
+        d.scale_tiles = scale_tiles;
+        return d;
+    }
+};
+
+struct bt_kv_cache {
+    int device = 0;
+    int64_t batch = 0, n_kv = 0, head_dim = 0, max_seq = 0;
+    bt::KvCacheView view{};
+    float* inv_freq = nullptr;   // device [head_dim/2], built for inv_freq_theta
+    double inv_freq_theta = 0.0;
+    double* partial = nullptr;   // split-KV scratch
+    int64_t partial_floats = 0;
+    int max_heads = 0;
+};

@@ -1,0 +1,60 @@
+// Launchers of the kernels that make up one decode step besides the ternary products.
+#pragma once
+
+#include "bt_common.cuh"
+
+namespace bt {
+
+enum RowPre : int { PRE_NONE = 0, PRE_RMSNORM = 1, PRE_SWIGLU = 2 };
+
+cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int batch, int hidden,
+                         int vocab, float* h, cudaStream_t stream);
+
+// Row transform (none | RMSNorm | silu(gate)*up) + per-token absmax int8 quantisation.
+// x: [batch, x_stride] f32 (PRE_SWIGLU: gate at [0,k), up at [k,2k)); q rows of q_stride
+// bytes (multiple of 4, zero-filled beyond k); v_out optional [batch, k] transformed row.
+cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
+                             int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
+                             float* v_out, cudaStream_t stream);
+
+cudaError_t launch_lm_head(const __nv_bfloat16* w, const float* x, int batch, int hidden, int64_t vocab,
+                           float* logits, int sm_count, cudaStream_t stream);
+
+cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream);
+
+// Q8 KV cache of one layer: u8 data [batch, n_kv, max_seq, head_dim] and f32 scales
+// [batch, n_kv, max_seq] for K and V (layers/kv_cache.rs:14-24).
+struct KvCacheView {
+    uint8_t* k_q;
+    uint8_t* v_q;
+    float* k_s;
+    float* v_s;
+    int max_seq;
+};
+
+// Fused decode attention for one new token per sequence: RoPE on q and k at position
+// pos[b], Q8 append of k and v, attention of the n_heads queries over positions
+// 0..pos[b] of the quantised cache, output [batch, n_heads*head_dim] f32.
+// qkv: [batch, (n_heads + 2 n_kv) * head_dim] f32 laid out q | k | v.
+struct AttnArgs {
+    const float* qkv;
+    KvCacheView cache;
+    const int32_t* pos;      // [batch] position of the new token
+    const float* inv_freq;   // [head_dim/2]
+    float* out;              // [batch, n_heads*head_dim]
+    double* partial;         // scratch [batch, n_heads, splits, head_dim + 2] (max, sum, acc)
+    int batch, n_heads, n_kv, head_dim;
+    int splits;
+    float scaling;
+};
+cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
+
+// TTT fast-weight step (layers/ttt.rs:52-68) for `batch` independent states:
+// w: [batch, d, d] f32 updated in place, feat: [batch, d], z_out: [batch, d].
+cudaError_t launch_ttt_step(float* w, const float* feat, int batch, int d, float lr, float* z_out,
+                            cudaStream_t stream);
+// Chunked form (layers/ttt.rs:88-113): feats [batch, t_len, d], z_out [batch, t_len, d].
+cudaError_t launch_ttt_chunk(float* w, const float* feats, int batch, int t_len, int d, float lr,
+                             int chunk, float* z_out, cudaStream_t stream);
+
+}  // namespace bt

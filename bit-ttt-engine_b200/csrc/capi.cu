@@ -71,20 +71,7 @@ __global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloa
 // ---------------------------------------------------------------------------------------
 // handle types
 // ---------------------------------------------------------------------------------------
-struct bt_workspace {
-    int device = 0;
-    uint8_t* base = nullptr;
-    size_t bytes = 0;
-};
-
-struct bt_linear {
-    int device = 0;
-    bt::TiledWeights w;
-    uint8_t* tiles = nullptr;
-    float scales[8] = {0};
-    bt_workspace* own_ws = nullptr;
-    std::mutex ws_mu;
-};
+#include "bt_handles.cuh"
 
 using namespace bt;
 
@@ -194,6 +181,24 @@ extern "C" bt_status bt_linear_create(bt_linear** out, const uint8_t* packed_hos
                          "bt_linear_create: %s", cudaGetErrorString(e));
     }
     lin->w.tiles = lin->tiles;
+    {
+        // one weight scale per (basis, row tile); a plain BitLinear repeats scales[b]
+        const size_t cnt = (size_t)n_bases * (size_t)lin->w.row_tiles;
+        float* host = new (std::nothrow) float[cnt];
+        cudaError_t e2 = host ? cudaMalloc(&lin->scale_tiles, cnt * sizeof(float)) : cudaErrorMemoryAllocation;
+        if (e2 == cudaSuccess) {
+            for (int b = 0; b < n_bases; ++b)
+                for (int64_t r = 0; r < lin->w.row_tiles; ++r) host[(size_t)b * lin->w.row_tiles + r] = scales_host[b];
+            e2 = cudaMemcpy(lin->scale_tiles, host, cnt * sizeof(float), cudaMemcpyHostToDevice);
+        }
+        delete[] host;
+        if (e2 != cudaSuccess) {
+            cudaFree(lin->tiles);
+            cudaFree(lin->scale_tiles);
+            delete lin;
+            return set_error(BT_ERR_CUDA, "bt_linear_create: %s", cudaGetErrorString(e2));
+        }
+    }
     *out = lin;
     return BT_OK;
 }
@@ -202,6 +207,7 @@ extern "C" bt_status bt_linear_destroy(bt_linear* lin) {
     if (!lin) return BT_OK;
     DeviceGuard guard(lin->device);
     cudaFree(lin->tiles);
+    cudaFree(lin->scale_tiles);
     if (lin->own_ws) bt_workspace_destroy(lin->own_ws);
     delete lin;
     return BT_OK;
@@ -262,47 +268,16 @@ bt_status resolve_workspace(bt_linear* lin, bt_workspace** ws) {
     return BT_OK;
 }
 
-// Runs the product for all tokens (8 per launch) and all bases on quantised activations.
+// Runs the product for all tokens and all bases on quantised activations.
 bt_status run_product(bt_linear* lin, const WsPlan& p, int64_t m, void* out, bt_dtype out_dtype,
                       bool raw_i32, cudaStream_t stream) {
     const int sm = device_sm_count(lin->device);
     unsigned int* err = device_error_word(lin->device);
     const int64_t n = lin->w.n_out;
-    const bool multi = lin->w.n_bases > 1 && !raw_i32;
-    const bool via_tmp = multi && out_dtype == BT_BF16;
-    for (int64_t m0 = 0; m0 < m; m0 += 8) {
-        const int mc = (int)(m - m0 < 8 ? m - m0 : 8);
-        const int bases = raw_i32 ? 1 : lin->w.n_bases;
-        for (int b = 0; b < bases; ++b) {
-            GemvArgs a;
-            a.tiles = lin->tiles + (size_t)b * lin->w.basis_stride();
-            a.row_tiles = lin->w.row_tiles;
-            a.k_tiles = lin->w.k_tiles;
-            a.n_out = n;
-            a.q = p.q + m0 * lin->w.k_pad();
-            a.q_stride = lin->w.k_pad();
-            a.qsum = p.qsum + m0;
-            a.sx = p.sx + m0;
-            a.sw = lin->scales[b];
-            a.m = mc;
-            a.out_stride = n;
-            a.err = err;
-            if (raw_i32) {
-                a.out = reinterpret_cast<int32_t*>(out) + m0 * n;
-                a.epilogue = EPI_I32;
-            } else if (via_tmp) {
-                a.out = p.ytmp + m0 * n;
-                a.epilogue = b == 0 ? EPI_F32 : EPI_F32_ACCUM;
-            } else if (out_dtype == BT_BF16) {
-                a.out = reinterpret_cast<__nv_bfloat16*>(out) + m0 * n;
-                a.epilogue = EPI_BF16;
-            } else {
-                a.out = reinterpret_cast<float*>(out) + m0 * n;
-                a.epilogue = b == 0 ? EPI_F32 : EPI_F32_ACCUM;
-            }
-            BT_CUDA_TRY(launch_gemv(a, sm, stream));
-        }
-    }
+    const bool via_tmp = lin->w.n_bases > 1 && !raw_i32 && out_dtype == BT_BF16;
+    const int epi = raw_i32 ? EPI_I32 : ((out_dtype == BT_BF16 && !via_tmp) ? EPI_BF16 : EPI_F32);
+    BT_CUDA_TRY(linear_product(lin->dev(), p.q, lin->w.k_pad(), p.qsum, p.sx, m, via_tmp ? (void*)p.ytmp : out,
+                               n, epi, err, sm, stream));
     if (via_tmp) {
         const int64_t total = m * n;
         int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
@@ -407,5 +382,47 @@ extern "C" bt_status bt_act_quant(const void* x_dev, bt_dtype x_dtype, int64_t m
     DeviceGuard guard(device);
     if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", device);
     BT_CUDA_TRY(launch_act_quant(x_dev, x_dtype, m, k, q_dev, k, s_dev, qsum_dev, reinterpret_cast<cudaStream_t>(stream)));
+    return BT_OK;
+}
+
+extern "C" bt_status bt_linear_create_fused(bt_linear** out, const uint8_t* const* seg_packed_host,
+                                            const int64_t* seg_rows, const float* seg_scales, int n_seg,
+                                            int64_t k_in, int device) {
+    if (!out) return set_error(BT_ERR_ARG, "bt_linear_create_fused: null out pointer");
+    *out = nullptr;
+    if (!seg_packed_host || !seg_rows || !seg_scales || n_seg < 1)
+        return set_error(BT_ERR_ARG, "bt_linear_create_fused: null pointer or no segments");
+    if (k_in <= 0 || k_in % 4 != 0)
+        return set_error(BT_ERR_ALIGN, "bt_linear_create_fused: in_features %lld is not a multiple of 4", (long long)k_in);
+    int64_t n_total = 0;
+    for (int i = 0; i < n_seg; ++i) {
+        if (!seg_packed_host[i] || seg_rows[i] <= 0 || seg_rows[i] % kTileRows != 0)
+            return set_error(BT_ERR_ALIGN, "bt_linear_create_fused: segment %d has %lld rows (need a positive multiple of 16)",
+                             i, (long long)seg_rows[i]);
+        n_total += seg_rows[i];
+    }
+    const size_t row_bytes = (size_t)(k_in / 4);
+    uint8_t* cat = new (std::nothrow) uint8_t[(size_t)n_total * row_bytes];
+    if (!cat) return set_error(BT_ERR_NOMEM, "host allocation failed");
+    size_t off = 0;
+    for (int i = 0; i < n_seg; ++i) {
+        memcpy(cat + off, seg_packed_host[i], (size_t)seg_rows[i] * row_bytes);
+        off += (size_t)seg_rows[i] * row_bytes;
+    }
+    bt_linear* lin = nullptr;
+    bt_status st = bt_linear_create(&lin, cat, n_total, k_in, 1, seg_scales, device);
+    delete[] cat;
+    if (st != BT_OK) return st;
+    // overwrite the per-row-tile scales segment by segment
+    float* host = new (std::nothrow) float[(size_t)lin->w.row_tiles];
+    if (!host) { bt_linear_destroy(lin); return set_error(BT_ERR_NOMEM, "host allocation failed"); }
+    int64_t rt = 0;
+    for (int i = 0; i < n_seg; ++i)
+        for (int64_t r = 0; r < seg_rows[i] / kTileRows; ++r) host[rt++] = seg_scales[i];
+    DeviceGuard guard(device);
+    cudaError_t e = cudaMemcpy(lin->scale_tiles, host, (size_t)lin->w.row_tiles * sizeof(float), cudaMemcpyHostToDevice);
+    delete[] host;
+    if (e != cudaSuccess) { bt_linear_destroy(lin); return set_error(BT_ERR_CUDA, "bt_linear_create_fused: %s", cudaGetErrorString(e)); }
+    *out = lin;
     return BT_OK;
 }

@@ -1,0 +1,329 @@
+// Small memory-bound kernels around the ternary products of one decode step:
+// embedding gather, (RMSNorm | SwiGLU product | identity) + per-token int8 quantisation,
+// dense bf16 lm_head, arg-max.  All f32 arithmetic; reference operation order is kept
+// wherever a rounding could show (see each kernel).
+#include "bt_common.cuh"
+#include "bt_model.cuh"
+#include "bt_ptx.cuh"
+
+namespace bt {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Block-wide reductions over blockDim.x threads (multiple of 32, <= 1024).
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float r = l < nw ? red[l] : 0.0f;
+    r = warp_sum(r);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float r = l < nw ? red[l] : 0.0f;
+    r = warp_max(r);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ double block_sum_d(double v, double* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    double r = l < nw ? red[l] : 0.0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ int block_sum_i(int v, int* red) {
+    v = warp_sum_i(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    int r = l < nw ? red[l] : 0;
+    r = warp_sum_i(r);
+    __syncthreads();
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------
+// embedding gather: h[b, :] = table[token[b], :]   (Embedding::forward, model/llama.rs:208)
+// ---------------------------------------------------------------------------------------
+__global__ void embed_kernel(const int32_t* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                             int hidden, int vocab, float* __restrict__ h) {
+    const int b = blockIdx.x;
+    int tok = tokens[b];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const __nv_bfloat16* row = table + (int64_t)tok * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) h[(int64_t)b * hidden + c] = __bfloat162float(row[c]);
+}
+
+// ---------------------------------------------------------------------------------------
+// row transform + absmax int8 quantisation, one CTA per token, the row held in shared
+// memory so that global memory is read once.
+//   PRE_NONE   : v = x
+//   PRE_RMSNORM: v = (x / sqrt(mean(x^2) + eps)) * w        (layers/rms_norm.rs:40-55)
+//   PRE_SWIGLU : v = silu(gate) * up, x = [gate | up]        (layers/swiglu.rs:31-33)
+// then s = max|v|/127, q = clamp(round(v/s)), sum_k q.  `v_out` (optional) receives v.
+// ---------------------------------------------------------------------------------------
+template <int PRE>
+__global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict__ x, int64_t x_stride,
+                                                        const float* __restrict__ w, float eps, int k,
+                                                        int8_t* __restrict__ q, int64_t q_stride,
+                                                        float* __restrict__ s_out,
+                                                        int32_t* __restrict__ qsum_out,
+                                                        float* __restrict__ v_out) {
+    extern __shared__ float row[];
+    __shared__ float red_f[32];
+    __shared__ double red_d[32];
+    __shared__ int red_i[32];
+    ptx::pdl_wait();
+    const int b = blockIdx.x;
+    const float* xr = x + (int64_t)b * x_stride;
+    float amax = 0.0f;
+    if (PRE == PRE_RMSNORM) {
+        // sum of squares in f64, rounded once: reproducible against the CPU restatement
+        double ss = 0.0;
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            const float v = xr[c];
+            row[c] = v;
+            ss = fma((double)v, (double)v, ss);
+        }
+        ss = block_sum_d(ss, red_d);
+        const float denom = sqrtf(__fadd_rn((float)(ss / (double)k), eps));
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            const float v = __fmul_rn(__fdiv_rn(row[c], denom), w[c]);
+            row[c] = v;
+            amax = fmaxf(amax, fabsf(v));
+        }
+    } else if (PRE == PRE_SWIGLU) {
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            const float g = xr[c], u = xr[k + c];
+            const float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, (float)exp(-(double)g))), u);
+            row[c] = v;
+            amax = fmaxf(amax, fabsf(v));
+        }
+    } else {
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            const float v = xr[c];
+            row[c] = v;
+            amax = fmaxf(amax, fabsf(v));
+        }
+    }
+    amax = block_max(amax, red_f);  // also orders the row[] writes before the reads below
+    const float s = __fdiv_rn(amax, 127.0f);
+    int8_t* qr = q + (int64_t)b * q_stride;
+    int local = 0;
+    for (int c = threadIdx.x * 4; c < q_stride; c += blockDim.x * 4) {
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int v = 0;
+            if (c + j < k && s > 0.0f) {
+                float r = roundf(__fdiv_rn(row[c + j], s));
+                r = fminf(fmaxf(r, -127.0f), 127.0f);
+                v = (int)r;
+            }
+            local += v;
+            packed |= (uint32_t)(v & 0xff) << (8 * j);
+        }
+        *reinterpret_cast<uint32_t*>(qr + c) = packed;
+    }
+    if (v_out)
+        for (int c = threadIdx.x; c < k; c += blockDim.x) v_out[(int64_t)b * k + c] = row[c];
+    const int total = block_sum_i(local, red_i);
+    if (threadIdx.x == 0) {
+        s_out[b] = s;
+        qsum_out[b] = total;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// dense lm_head: logits[b, v] = sum_c W[v, c] * x[b, c], W bf16 row-major, x f32.
+// (candle_nn::Linear without bias, model/llama.rs:23,266; the converter keeps lm_head in
+// 16-bit, tools/conversion/convert_llama_v2.py:265-268.)  HBM-bound on W: one warp per
+// output row, 16-byte loads, x in shared memory, f32 accumulation.
+// ---------------------------------------------------------------------------------------
+template <int B>
+__global__ void __launch_bounds__(256) lm_head_kernel(const __nv_bfloat16* __restrict__ w,
+                                                      const float* __restrict__ x, int hidden,
+                                                      int64_t v_begin, int64_t v_end,
+                                                      float* __restrict__ logits, int64_t logits_stride) {
+    extern __shared__ float xs[];  // [B][hidden]
+    ptx::pdl_wait();
+    for (int i = threadIdx.x; i < B * hidden; i += blockDim.x) xs[i] = x[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_global = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t v = v_begin + warp_global; v < v_end; v += warps_total) {
+        const uint4* wr = reinterpret_cast<const uint4*>(w + v * hidden);
+        float acc[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) acc[b] = 0.0f;
+#pragma unroll 4
+        for (int c8 = lane; c8 < hidden / 8; c8 += 32) {
+            const uint4 pk = wr[c8];
+            const uint32_t u[4] = {pk.x, pk.y, pk.z, pk.w};
+            float wf[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                wf[2 * j] = __uint_as_float(u[j] << 16);
+                wf[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+            }
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                const float4 x0 = *reinterpret_cast<const float4*>(xs + b * hidden + c8 * 8);
+                const float4 x1 = *reinterpret_cast<const float4*>(xs + b * hidden + c8 * 8 + 4);
+                acc[b] = fmaf(wf[0], x0.x, acc[b]);
+                acc[b] = fmaf(wf[1], x0.y, acc[b]);
+                acc[b] = fmaf(wf[2], x0.z, acc[b]);
+                acc[b] = fmaf(wf[3], x0.w, acc[b]);
+                acc[b] = fmaf(wf[4], x1.x, acc[b]);
+                acc[b] = fmaf(wf[5], x1.y, acc[b]);
+                acc[b] = fmaf(wf[6], x1.z, acc[b]);
+                acc[b] = fmaf(wf[7], x1.w, acc[b]);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const float r = warp_sum(acc[b]);
+            if (lane == 0) logits[(int64_t)b * logits_stride + v] = r;
+        }
+    }
+}
+
+// Greedy pick: the LAST index among equal maxima, as Iterator::max_by does in the
+// reference's sampler (model/llama.rs:510-515).  One CTA per token.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t stride,
+                                                      int vocab, int32_t* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    ptx::pdl_wait();
+    const float* row = logits + (int64_t)blockIdx.x * stride;
+    float best = -INFINITY;
+    int idx = -1;
+    for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
+        const float v = row[c];
+        if (v >= best || idx < 0) { best = v; idx = c; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oi >= 0 && (idx < 0 || ov > best || (ov == best && oi > idx))) { best = ov; idx = oi; }
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) { sv[w] = best; si[w] = idx; }
+    __syncthreads();
+    if (w == 0) {
+        best = l < (blockDim.x >> 5) ? sv[l] : -INFINITY;
+        idx = l < (blockDim.x >> 5) ? si[l] : -1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (oi >= 0 && (idx < 0 || ov > best || (ov == best && oi > idx))) { best = ov; idx = oi; }
+        }
+        if (l == 0) out[blockIdx.x] = idx;
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------
+cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int batch, int hidden,
+                         int vocab, float* h, cudaStream_t stream) {
+    embed_kernel<<<batch, 256, 0, stream>>>(tokens, table, hidden, vocab, h);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
+                             int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
+                             float* v_out, cudaStream_t stream) {
+    const size_t smem = (size_t)k * sizeof(float);
+    const int threads = k >= 4096 ? 512 : 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(row_quant_kernel<PRE_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(row_quant_kernel<PRE_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(row_quant_kernel<PRE_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        configured = true;
+    }
+    if (smem > 160 * 1024) return cudaErrorInvalidConfiguration;
+    if (pre == PRE_RMSNORM)
+        row_quant_kernel<PRE_RMSNORM><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out);
+    else if (pre == PRE_SWIGLU)
+        row_quant_kernel<PRE_SWIGLU><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out);
+    else
+        row_quant_kernel<PRE_NONE><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out);
+    return cudaGetLastError();
+}
+
+template <int B>
+static cudaError_t launch_lm_head_b(const __nv_bfloat16* w, const float* x, int hidden, int64_t vocab,
+                                    float* logits, int64_t stride, int sm_count, cudaStream_t stream) {
+    const size_t smem = (size_t)B * hidden * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(lm_head_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        configured = true;
+    }
+    if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+    int per_sm = (int)((200 * 1024) / (smem + 1024));
+    per_sm = per_sm > 4 ? 4 : (per_sm < 1 ? 1 : per_sm);
+    lm_head_kernel<B><<<sm_count * per_sm, 256, smem, stream>>>(w, x, hidden, 0, vocab, logits, stride);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_lm_head(const __nv_bfloat16* w, const float* x, int batch, int hidden, int64_t vocab,
+                           float* logits, int sm_count, cudaStream_t stream) {
+    if (hidden % 8 != 0) return cudaErrorInvalidValue;
+    for (int b0 = 0; b0 < batch; b0 += 4) {
+        const int bc = batch - b0 < 4 ? batch - b0 : 4;
+        const float* xb = x + (int64_t)b0 * hidden;
+        float* lb = logits + (int64_t)b0 * vocab;
+        cudaError_t e;
+        switch (bc) {
+            case 1: e = launch_lm_head_b<1>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
+            case 2: e = launch_lm_head_b<2>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
+            case 3: e = launch_lm_head_b<3>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
+            default: e = launch_lm_head_b<4>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
+        }
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream) {
+    argmax_kernel<<<batch, 1024, 0, stream>>>(logits, vocab, vocab, out);
+    return cudaGetLastError();
+}
+
+}  // namespace bt

@@ -1,0 +1,431 @@
+// bt_model: one decode step of the reference's BitLlama (model/llama.rs:201-272,
+// model/block.rs:87-134) as a fixed sequence of this library's kernels on one stream,
+// replayed as a CUDA graph once captured.  Host code here only owns buffers and order;
+// all arithmetic is in the kernels.
+#include <string.h>
+
+#include <new>
+#include <vector>
+
+#include "bt_handles.cuh"
+
+using namespace bt;
+
+namespace bt {
+cudaError_t upload_inv_freq(float* dev, int head_dim, double theta);
+int attn_splits(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count);
+
+__global__ void advance_pos_kernel(int32_t* pos, int n) {
+    if (threadIdx.x < n) pos[threadIdx.x] += 1;
+}
+__global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16_rn(in[i]);
+}
+}  // namespace bt
+
+namespace {
+
+constexpr float kRmsEps = 1e-5f;  // model/block.rs:10, model/llama.rs:13
+
+struct HostLinear {
+    std::vector<uint8_t> packed;
+    int64_t n_out = 0, k_in = 0;
+    float scale = 0.f;
+    bool set = false;
+};
+
+struct Layer {
+    HostLinear host[9];
+    bt_linear* qkv = nullptr;
+    bt_linear* o = nullptr;
+    bt_linear* gate_up = nullptr;
+    bt_linear* down = nullptr;
+    bt_linear* ttt_down = nullptr;
+    bt_linear* ttt_up = nullptr;
+    float* norm1 = nullptr;
+    float* norm2 = nullptr;
+    bt_kv_cache* kv = nullptr;
+    float* w_state = nullptr;  // [max_batch, d, d]
+};
+
+}  // namespace
+
+struct bt_model {
+    bt_model_config cfg{};
+    int device = 0;
+    int sm_count = 0;
+    int head_dim = 0, d_small = 0, qkv_dim = 0;
+    bool finalized = false;
+    std::vector<Layer> layers;
+    __nv_bfloat16* embed = nullptr;
+    __nv_bfloat16* lm_head = nullptr;
+    float* norm_f = nullptr;
+    float* inv_freq = nullptr;
+    // activations
+    int32_t* tokens = nullptr;
+    int32_t* pos = nullptr;
+    float* h = nullptr;
+    int8_t* q = nullptr;
+    int64_t q_stride = 0;
+    float* sx = nullptr;
+    int32_t* qsum = nullptr;
+    float* qkv = nullptr;
+    float* att = nullptr;
+    float* gu = nullptr;
+    float* feat = nullptr;
+    float* z = nullptr;
+    float* xn = nullptr;
+    float* logits = nullptr;
+    int32_t* next = nullptr;
+    double* attn_partial = nullptr;
+    int32_t* tokens_pinned = nullptr;
+    int32_t* next_pinned = nullptr;
+    int host_pos = 0;
+    int64_t ternary_bytes = 0;
+    cudaStream_t stream = nullptr;
+    cudaGraphExec_t graphs[65] = {nullptr};
+};
+
+namespace {
+
+template <typename T>
+cudaError_t dev_alloc(T** p, size_t count) { return cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)); }
+
+bt_status make_linear(bt_model* m, HostLinear** parts, int n_parts, bt_linear** out) {
+    const uint8_t* ptrs[3];
+    int64_t rows[3];
+    float scales[3];
+    for (int i = 0; i < n_parts; ++i) {
+        if (!parts[i]->set) return set_error(BT_ERR_ARG, "bt_model_finalize: a projection weight was never set");
+        if (parts[i]->k_in != parts[0]->k_in) return set_error(BT_ERR_SHAPE, "bt_model_finalize: fused projections disagree on in_features");
+        ptrs[i] = parts[i]->packed.data();
+        rows[i] = parts[i]->n_out;
+        scales[i] = parts[i]->scale;
+    }
+    bt_status st;
+    if (n_parts == 1) st = bt_linear_create(out, ptrs[0], rows[0], parts[0]->k_in, 1, scales, m->device);
+    else st = bt_linear_create_fused(out, ptrs, rows, scales, n_parts, parts[0]->k_in, m->device);
+    if (st != BT_OK) return st;
+    m->ternary_bytes += (*out)->w.basis_stride();
+    for (int i = 0; i < n_parts; ++i) { parts[i]->packed.clear(); parts[i]->packed.shrink_to_fit(); }
+    return BT_OK;
+}
+
+// Enqueues one decode step for `batch` sequences on `s`.
+bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
+    const bt_model_config& c = m->cfg;
+    const int H = c.hidden_dim, I = c.intermediate_dim;
+    unsigned int* err = device_error_word(m->device);
+    const int sm = m->sm_count;
+    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s));
+    for (int li = 0; li < c.num_layers; ++li) {
+        Layer& L = m->layers[(size_t)li];
+        // x_norm = norm1(x)  (model/block.rs:98), quantised for the projections that follow
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm1, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
+        if (c.arch == 0) {
+            // TTTLayer::forward_update (layers/ttt.rs:48-74)
+            BT_CUDA_TRY(linear_product(L.ttt_down->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->feat, m->d_small, EPI_F32, err, sm, s));
+            BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s));
+            BT_CUDA_TRY(launch_row_quant(PRE_NONE, m->z, m->d_small, nullptr, 0.f, batch, m->d_small, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
+            BT_CUDA_TRY(linear_product(L.ttt_up->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
+        } else {
+            // BitAttention::forward (layers/attention.rs:149-225), seq_len 1
+            BT_CUDA_TRY(linear_product(L.qkv->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->qkv, m->qkv_dim, EPI_F32, err, sm, s));
+            AttnArgs a;
+            a.qkv = m->qkv;
+            a.cache = L.kv->view;
+            a.pos = m->pos;
+            a.inv_freq = m->inv_freq;
+            a.out = m->att;
+            a.partial = m->attn_partial;
+            a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
+            a.splits = attn_splits(batch, c.n_kv_heads, c.max_position_embeddings, sm);
+            a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
+            BT_CUDA_TRY(launch_attn_decode(a, s));
+            BT_CUDA_TRY(launch_row_quant(PRE_NONE, m->att, H, nullptr, 0.f, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
+            BT_CUDA_TRY(linear_product(L.o->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
+        }
+        // x = x + mlp(norm2(x))  (model/block.rs:119-131, layers/swiglu.rs:29-35)
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
+        BT_CUDA_TRY(linear_product(L.gate_up->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, 2 * I, EPI_F32, err, sm, s));
+        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
+        BT_CUDA_TRY(linear_product(L.down->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
+    }
+    // logits = lm_head(norm(h))  (model/llama.rs:256-266)
+    BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, m->norm_f, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, m->xn, s));
+    BT_CUDA_TRY(launch_lm_head(m->lm_head, m->xn, batch, H, c.vocab_size, m->logits, sm, s));
+    BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
+    advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, c.max_batch);
+    BT_CUDA_TRY(cudaGetLastError());
+    return BT_OK;
+}
+
+}  // namespace
+
+extern "C" bt_status bt_model_create(bt_model** out, const bt_model_config* cfg, int device) {
+    if (!out || !cfg) return set_error(BT_ERR_ARG, "bt_model_create: null pointer");
+    *out = nullptr;
+    const bt_model_config& c = *cfg;
+    if (c.arch != 0 && c.arch != 1) return set_error(BT_ERR_ARG, "bt_model_create: arch must be 0 (ttt) or 1 (llama)");
+    if (c.vocab_size < 1 || c.hidden_dim < 4 || c.num_layers < 1 || c.intermediate_dim < 4)
+        return set_error(BT_ERR_SHAPE, "bt_model_create: bad dimensions");
+    if (c.hidden_dim % 16 != 0 || c.intermediate_dim % 16 != 0)
+        return set_error(BT_ERR_ALIGN, "bt_model_create: hidden_dim and intermediate_dim must be multiples of 16");
+    if (c.max_batch < 1 || c.max_batch > 64) return set_error(BT_ERR_ARG, "bt_model_create: max_batch must be 1..64");
+    if (c.arch == 1) {
+        if (c.n_heads < 1 || c.n_kv_heads < 1 || c.hidden_dim % c.n_heads != 0 || c.n_heads % c.n_kv_heads != 0)
+            return set_error(BT_ERR_SHAPE, "bt_model_create: heads do not divide hidden_dim / each other");
+        const int hd = c.hidden_dim / c.n_heads;
+        if (hd % 32 != 0 || hd > 128) return set_error(BT_ERR_SHAPE, "bt_model_create: head_dim %d unsupported (32..128, multiple of 32)", hd);
+        { const int rep = c.n_heads / c.n_kv_heads; if (!(rep == 1 || rep == 2 || rep == 4 || rep == 8)) return set_error(BT_ERR_SHAPE, "bt_model_create: query heads per KV head must be 1, 2, 4 or 8"); }
+        if (c.max_position_embeddings < 1) return set_error(BT_ERR_ARG, "bt_model_create: max_position_embeddings < 1");
+    } else if ((c.hidden_dim / 4) % 16 != 0 || c.hidden_dim / 4 > 1024) {
+        return set_error(BT_ERR_SHAPE, "bt_model_create: d_small = hidden_dim/4 must be a multiple of 16 and <= 1024");
+    }
+    if (bt_device_count() <= device || device < 0) return set_error(BT_ERR_DEVICE, "bt_model_create: no CUDA device %d", device);
+    DeviceGuard guard(device);
+    if (!guard.ok || !device_error_word(device)) return set_error(BT_ERR_DEVICE, "bt_model_create: cannot use device %d", device);
+    bt_model* m = new (std::nothrow) bt_model();
+    if (!m) return set_error(BT_ERR_NOMEM, "host allocation failed");
+    m->cfg = c;
+    m->device = device;
+    m->sm_count = device_sm_count(device);
+    m->head_dim = c.arch == 1 ? c.hidden_dim / c.n_heads : 0;
+    m->d_small = c.hidden_dim / 4;  // layers/ttt.rs:29
+    m->qkv_dim = c.arch == 1 ? (c.n_heads + 2 * c.n_kv_heads) * m->head_dim : 0;
+    m->layers.resize((size_t)c.num_layers);
+    *out = m;
+    return BT_OK;
+}
+
+extern "C" bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
+                                         int64_t n_out, int64_t k_in, float scale) {
+    if (!m || !packed_host) return set_error(BT_ERR_ARG, "bt_model_set_linear: null pointer");
+    if (m->finalized) return set_error(BT_ERR_ARG, "bt_model_set_linear: model already finalized");
+    if (layer < 0 || layer >= m->cfg.num_layers || (int)kind < 0 || (int)kind > 8)
+        return set_error(BT_ERR_ARG, "bt_model_set_linear: layer %d / kind %d out of range", layer, (int)kind);
+    const bt_model_config& c = m->cfg;
+    const int64_t H = c.hidden_dim, I = c.intermediate_dim, hd = m->head_dim, d = m->d_small;
+    int64_t en = 0, ek = 0;
+    switch (kind) {
+        case BT_W_Q: en = c.n_heads * hd; ek = H; break;
+        case BT_W_K: case BT_W_V: en = c.n_kv_heads * hd; ek = H; break;
+        case BT_W_O: en = H; ek = c.n_heads * hd; break;
+        case BT_W_GATE: case BT_W_UP: en = I; ek = H; break;
+        case BT_W_DOWN: en = H; ek = I; break;
+        case BT_W_TTT_DOWN: en = d; ek = H; break;
+        case BT_W_TTT_UP: en = H; ek = d; break;
+    }
+    if (n_out != en || k_in != ek)
+        return set_error(BT_ERR_SHAPE, "bt_model_set_linear: weight [%lld, %lld] given, [%lld, %lld] expected",
+                         (long long)n_out, (long long)k_in, (long long)en, (long long)ek);
+    HostLinear& hl = m->layers[(size_t)layer].host[(int)kind];
+    hl.packed.assign(packed_host, packed_host + (size_t)n_out * (size_t)(k_in / 4));
+    hl.n_out = n_out; hl.k_in = k_in; hl.scale = scale; hl.set = true;
+    return BT_OK;
+}
+
+extern "C" bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int layer, const float* data, int64_t n_elem) {
+    if (!m || !data) return set_error(BT_ERR_ARG, "bt_model_set_tensor: null pointer");
+    const bt_model_config& c = m->cfg;
+    DeviceGuard guard(m->device);
+    const int64_t H = c.hidden_dim, VH = (int64_t)c.vocab_size * H;
+    if (kind == BT_T_EMBED || kind == BT_T_LM_HEAD) {
+        if (n_elem != VH) return set_error(BT_ERR_SHAPE, "bt_model_set_tensor: %lld elements given, %lld expected", (long long)n_elem, (long long)VH);
+        __nv_bfloat16** dst = kind == BT_T_EMBED ? &m->embed : &m->lm_head;
+        if (!*dst) BT_CUDA_TRY(dev_alloc(dst, (size_t)VH));
+        // staged through a bounded f32 buffer, converted on the device
+        const int64_t chunk = 16 << 20;
+        float* tmp = nullptr;
+        BT_CUDA_TRY(dev_alloc(&tmp, (size_t)(VH < chunk ? VH : chunk)));
+        for (int64_t off = 0; off < VH; off += chunk) {
+            const int64_t n = VH - off < chunk ? VH - off : chunk;
+            cudaError_t e = cudaMemcpy(tmp, data + off, (size_t)n * sizeof(float), cudaMemcpyHostToDevice);
+            if (e == cudaSuccess) {
+                f32_to_bf16_kernel<<<1184, 256>>>(tmp, *dst + off, n);
+                e = cudaDeviceSynchronize();
+            }
+            if (e != cudaSuccess) { cudaFree(tmp); return set_error(BT_ERR_CUDA, "bt_model_set_tensor: %s", cudaGetErrorString(e)); }
+        }
+        cudaFree(tmp);
+        return BT_OK;
+    }
+    if (n_elem != H) return set_error(BT_ERR_SHAPE, "bt_model_set_tensor: norm weight has %lld elements, %lld expected", (long long)n_elem, (long long)H);
+    float** dst = nullptr;
+    if (kind == BT_T_NORM_F) dst = &m->norm_f;
+    else {
+        if (layer < 0 || layer >= c.num_layers) return set_error(BT_ERR_ARG, "bt_model_set_tensor: layer %d out of range", layer);
+        dst = kind == BT_T_NORM1 ? &m->layers[(size_t)layer].norm1 : &m->layers[(size_t)layer].norm2;
+    }
+    if (!*dst) BT_CUDA_TRY(dev_alloc(dst, (size_t)H));
+    BT_CUDA_TRY(cudaMemcpy(*dst, data, (size_t)H * sizeof(float), cudaMemcpyHostToDevice));
+    return BT_OK;
+}
+
+extern "C" bt_status bt_model_finalize(bt_model* m) {
+    if (!m) return set_error(BT_ERR_ARG, "bt_model_finalize: null handle");
+    if (m->finalized) return BT_OK;
+    const bt_model_config& c = m->cfg;
+    DeviceGuard guard(m->device);
+    if (!m->embed || !m->lm_head || !m->norm_f) return set_error(BT_ERR_ARG, "bt_model_finalize: embedding, lm_head or final norm missing");
+    const int B = c.max_batch, H = c.hidden_dim, I = c.intermediate_dim;
+    for (auto& L : m->layers) {
+        if (!L.norm1 || !L.norm2) return set_error(BT_ERR_ARG, "bt_model_finalize: a layer norm weight is missing");
+        bt_status st;
+        if (c.arch == 1) {
+            HostLinear* qkv[3] = {&L.host[BT_W_Q], &L.host[BT_W_K], &L.host[BT_W_V]};
+            if ((st = make_linear(m, qkv, 3, &L.qkv)) != BT_OK) return st;
+            HostLinear* o[1] = {&L.host[BT_W_O]};
+            if ((st = make_linear(m, o, 1, &L.o)) != BT_OK) return st;
+            if ((st = bt_kv_create(&L.kv, B, c.n_kv_heads, m->head_dim, c.max_position_embeddings, m->device)) != BT_OK) return st;
+        } else {
+            HostLinear* dn[1] = {&L.host[BT_W_TTT_DOWN]};
+            if ((st = make_linear(m, dn, 1, &L.ttt_down)) != BT_OK) return st;
+            HostLinear* up[1] = {&L.host[BT_W_TTT_UP]};
+            if ((st = make_linear(m, up, 1, &L.ttt_up)) != BT_OK) return st;
+            BT_CUDA_TRY(dev_alloc(&L.w_state, (size_t)B * m->d_small * m->d_small));
+        }
+        HostLinear* gu[2] = {&L.host[BT_W_GATE], &L.host[BT_W_UP]};
+        if ((st = make_linear(m, gu, 2, &L.gate_up)) != BT_OK) return st;
+        HostLinear* dn[1] = {&L.host[BT_W_DOWN]};
+        if ((st = make_linear(m, dn, 1, &L.down)) != BT_OK) return st;
+    }
+    int64_t kmax = H > I ? H : I;
+    m->q_stride = (kmax + kTileK - 1) / kTileK * kTileK;
+    BT_CUDA_TRY(dev_alloc(&m->tokens, (size_t)B));
+    BT_CUDA_TRY(dev_alloc(&m->pos, (size_t)B));
+    BT_CUDA_TRY(dev_alloc(&m->h, (size_t)B * H));
+    BT_CUDA_TRY(dev_alloc(&m->q, (size_t)B * m->q_stride));
+    BT_CUDA_TRY(dev_alloc(&m->sx, (size_t)B));
+    BT_CUDA_TRY(dev_alloc(&m->qsum, (size_t)B));
+    BT_CUDA_TRY(dev_alloc(&m->gu, (size_t)B * 2 * I));
+    BT_CUDA_TRY(dev_alloc(&m->xn, (size_t)B * H));
+    BT_CUDA_TRY(dev_alloc(&m->logits, (size_t)B * c.vocab_size));
+    BT_CUDA_TRY(dev_alloc(&m->next, (size_t)B));
+    if (c.arch == 1) {
+        BT_CUDA_TRY(dev_alloc(&m->qkv, (size_t)B * m->qkv_dim));
+        BT_CUDA_TRY(dev_alloc(&m->att, (size_t)B * H));
+        BT_CUDA_TRY(dev_alloc(&m->inv_freq, (size_t)m->head_dim / 2));
+        BT_CUDA_TRY(upload_inv_freq(m->inv_freq, m->head_dim, c.rope_theta));
+        BT_CUDA_TRY(dev_alloc(&m->attn_partial, (size_t)B * c.n_heads * 32 * (m->head_dim + 2)));
+    } else {
+        BT_CUDA_TRY(dev_alloc(&m->feat, (size_t)B * m->d_small));
+        BT_CUDA_TRY(dev_alloc(&m->z, (size_t)B * m->d_small));
+    }
+    BT_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&m->tokens_pinned), (size_t)B * sizeof(int32_t)));
+    BT_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&m->next_pinned), (size_t)B * sizeof(int32_t)));
+    BT_CUDA_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    m->finalized = true;
+    return bt_model_reset(m);
+}
+
+extern "C" bt_status bt_model_destroy(bt_model* m) {
+    if (!m) return BT_OK;
+    DeviceGuard guard(m->device);
+    cudaDeviceSynchronize();
+    for (auto& g : m->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto& L : m->layers) {
+        bt_linear_destroy(L.qkv); bt_linear_destroy(L.o); bt_linear_destroy(L.gate_up); bt_linear_destroy(L.down);
+        bt_linear_destroy(L.ttt_down); bt_linear_destroy(L.ttt_up);
+        bt_kv_destroy(L.kv);
+        cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
+    }
+    void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial};
+    for (void* p : bufs) cudaFree(p);
+    if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
+    if (m->next_pinned) cudaFreeHost(m->next_pinned);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    delete m;
+    return BT_OK;
+}
+
+extern "C" bt_status bt_model_reset(bt_model* m) {
+    if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_reset: model not finalized");
+    DeviceGuard guard(m->device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    for (auto& L : m->layers) {
+        if (L.kv) { bt_status st = bt_kv_reset(L.kv); if (st != BT_OK) return st; }
+        if (L.w_state) BT_CUDA_TRY(cudaMemset(L.w_state, 0, (size_t)m->cfg.max_batch * m->d_small * m->d_small * sizeof(float)));
+    }
+    BT_CUDA_TRY(cudaMemset(m->pos, 0, (size_t)m->cfg.max_batch * sizeof(int32_t)));
+    m->host_pos = 0;
+    return BT_OK;
+}
+
+namespace {
+
+bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
+    if (m->cfg.arch == 1 && m->host_pos >= m->cfg.max_position_embeddings)
+        return set_error(BT_ERR_SHAPE, "position %d reaches max_position_embeddings %d", m->host_pos, m->cfg.max_position_embeddings);
+    // first call at a batch size runs eagerly (it also sets kernel attributes); the second
+    // is captured into a graph that later calls replay
+    static_assert(sizeof(m->graphs) / sizeof(m->graphs[0]) == 65, "graph table");
+    cudaGraphExec_t& exec = m->graphs[batch];
+    const uintptr_t marker = 1;  // "ran eagerly once" sentinel stored in the table
+    if (exec == nullptr) {
+        bt_status st = enqueue_step(m, batch, s);
+        if (st != BT_OK) return st;
+        exec = reinterpret_cast<cudaGraphExec_t>(marker);
+    } else if (exec == reinterpret_cast<cudaGraphExec_t>(marker)) {
+        cudaGraph_t graph = nullptr;
+        BT_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        bt_status st = enqueue_step(m, batch, s);
+        cudaError_t e = cudaStreamEndCapture(s, &graph);
+        if (st != BT_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        cudaGraphExec_t ge = nullptr;
+        e = cudaGraphInstantiate(&ge, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+        exec = ge;
+        BT_CUDA_TRY(cudaGraphLaunch(exec, s));
+    } else {
+        BT_CUDA_TRY(cudaGraphLaunch(exec, s));
+    }
+    m->host_pos += 1;
+    return BT_OK;
+}
+
+}  // namespace
+
+extern "C" bt_status bt_model_step_dev(bt_model* m, const int32_t* tokens_dev, int batch, void* stream) {
+    if (!m || !m->finalized || !tokens_dev) return set_error(BT_ERR_ARG, "bt_model_step_dev: null pointer or model not finalized");
+    if (batch < 1 || batch > m->cfg.max_batch) return set_error(BT_ERR_SHAPE, "bt_model_step_dev: batch %d outside 1..%d", batch, m->cfg.max_batch);
+    DeviceGuard guard(m->device);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    BT_CUDA_TRY(cudaMemcpyAsync(m->tokens, tokens_dev, (size_t)batch * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
+    return run_step(m, batch, s);
+}
+
+extern "C" bt_status bt_model_forward_one(bt_model* m, const int32_t* tokens_host, int batch, float* logits_host,
+                                          int32_t* next_host) {
+    if (!m || !m->finalized || !tokens_host) return set_error(BT_ERR_ARG, "bt_model_forward_one: null pointer or model not finalized");
+    if (batch < 1 || batch > m->cfg.max_batch) return set_error(BT_ERR_SHAPE, "bt_model_forward_one: batch %d outside 1..%d", batch, m->cfg.max_batch);
+    DeviceGuard guard(m->device);
+    cudaStream_t s = m->stream;
+    memcpy(m->tokens_pinned, tokens_host, (size_t)batch * sizeof(int32_t));
+    BT_CUDA_TRY(cudaMemcpyAsync(m->tokens, m->tokens_pinned, (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    bt_status st = run_step(m, batch, s);
+    if (st != BT_OK) return st;
+    if (logits_host)
+        BT_CUDA_TRY(cudaMemcpyAsync(logits_host, m->logits, (size_t)batch * m->cfg.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, s));
+    BT_CUDA_TRY(cudaMemcpyAsync(m->next_pinned, m->next, (size_t)batch * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    BT_CUDA_TRY(cudaStreamSynchronize(s));
+    if (next_host) memcpy(next_host, m->next_pinned, (size_t)batch * sizeof(int32_t));
+    return BT_OK;
+}
+
+extern "C" const float* bt_model_logits(bt_model* m) { return m ? m->logits : nullptr; }
+extern "C" const int32_t* bt_model_next(bt_model* m) { return m ? m->next : nullptr; }
+extern "C" int bt_model_pos(const bt_model* m) { return m ? m->host_pos : -1; }
+extern "C" float* bt_model_ttt_state(bt_model* m, int layer) {
+    if (!m || layer < 0 || layer >= (int)m->layers.size()) return nullptr;
+    return m->layers[(size_t)layer].w_state;
+}
+extern "C" bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer) {
+    if (!m || layer < 0 || layer >= (int)m->layers.size()) return nullptr;
+    return m->layers[(size_t)layer].kv;
+}
+extern "C" int64_t bt_model_ternary_bytes(const bt_model* m) { return m ? m->ternary_bytes : 0; }

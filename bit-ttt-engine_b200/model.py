@@ -1,0 +1,230 @@
+"""Model-level mirror of the reference engine (crates/rust_engine/src/model/llama.rs,
+layers/ttt.rs, layers/attention.rs, layers/kv_cache.rs) bound to the C ABI."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import check, lib
+from .layers import _ptr, _stream_ptr, _torch
+
+ARCH_TTT, ARCH_LLAMA = 0, 1
+(W_Q, W_K, W_V, W_O, W_GATE, W_UP, W_DOWN, W_TTT_DOWN, W_TTT_UP) = range(9)
+(T_EMBED, T_LM_HEAD, T_NORM_F, T_NORM1, T_NORM2) = range(5)
+
+
+class _CModelConfig(C.Structure):
+    _fields_ = [("arch", C.c_int), ("vocab_size", C.c_int), ("hidden_dim", C.c_int),
+                ("num_layers", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int),
+                ("intermediate_dim", C.c_int), ("inner_lr", C.c_float), ("rope_theta", C.c_double),
+                ("max_position_embeddings", C.c_int), ("max_batch", C.c_int)]
+
+
+def _bind():
+    L = lib()
+    if getattr(L, "_model_bound", False):
+        return L
+    vp, i64, i32 = C.c_void_p, C.c_int64, C.c_int
+    L.bt_ttt_update.argtypes = [vp, vp, i64, i64, i64, C.c_float, i64, vp, i32, vp]
+    L.bt_kv_create.argtypes = [C.POINTER(vp), i64, i64, i64, i64, i32]
+    L.bt_kv_reset.argtypes = [vp]
+    L.bt_kv_destroy.argtypes = [vp]
+    L.bt_kv_export.argtypes = [vp, i64, i64, vp, vp, vp, vp]
+    L.bt_attn_decode.argtypes = [vp, vp, vp, i64, i64, C.c_double, vp, vp]
+    L.bt_linear_create_fused.argtypes = [C.POINTER(vp), C.POINTER(vp), C.POINTER(i64), vp, i32, i64, i32]
+    L.bt_model_create.argtypes = [C.POINTER(vp), C.POINTER(_CModelConfig), i32]
+    L.bt_model_set_linear.argtypes = [vp, i32, i32, vp, i64, i64, C.c_float]
+    L.bt_model_set_tensor.argtypes = [vp, i32, i32, vp, i64]
+    L.bt_model_finalize.argtypes = [vp]
+    L.bt_model_destroy.argtypes = [vp]
+    L.bt_model_reset.argtypes = [vp]
+    L.bt_model_forward_one.argtypes = [vp, vp, i32, vp, vp]
+    L.bt_model_step_dev.argtypes = [vp, vp, i32, vp]
+    L.bt_model_logits.restype = vp
+    L.bt_model_logits.argtypes = [vp]
+    L.bt_model_next.restype = vp
+    L.bt_model_next.argtypes = [vp]
+    L.bt_model_pos.argtypes = [vp]
+    L.bt_model_ttt_state.restype = vp
+    L.bt_model_ttt_state.argtypes = [vp, i32]
+    L.bt_model_kv_cache.restype = vp
+    L.bt_model_kv_cache.argtypes = [vp, i32]
+    L.bt_model_ternary_bytes.restype = i64
+    L.bt_model_ternary_bytes.argtypes = [vp]
+    L._model_bound = True
+    return L
+
+
+def ttt_update(w_state, feats, inner_lr: float, chunk: int = 1):
+    """TTTLayer inner update (layers/ttt.rs:52-68 / :88-113).  w_state: CUDA f32
+    [batch, d, d], updated in place; feats: [batch, t_len, d] or [batch, d].  Returns z."""
+    torch = _torch()
+    L = _bind()
+    f3 = feats if feats.dim() == 3 else feats.unsqueeze(1)
+    f3 = f3.contiguous()
+    batch, t_len, d = f3.shape
+    z = torch.empty_like(f3)
+    check(L.bt_ttt_update(_ptr(w_state), _ptr(f3), batch, t_len, d, inner_lr, chunk, _ptr(z),
+                          w_state.device.index, _stream_ptr(w_state.device.index)))
+    return z if feats.dim() == 3 else z.squeeze(1)
+
+
+class QuantizedKVCache:
+    """layers/kv_cache.rs:14-44, preallocated for `batch` sequences on the device."""
+
+    def __init__(self, max_seq_len: int, batch: int, n_kv_heads: int, head_dim: int, device: int = 0,
+                 _borrowed=None):
+        self._L = _bind()
+        self.batch, self.n_kv, self.head_dim, self.max_seq_len = batch, n_kv_heads, head_dim, max_seq_len
+        self._owned = _borrowed is None
+        if _borrowed is None:
+            self._h = C.c_void_p()
+            check(self._L.bt_kv_create(C.byref(self._h), batch, n_kv_heads, head_dim, max_seq_len, device))
+        else:
+            self._h = C.c_void_p(_borrowed)
+
+    def reset(self):
+        check(self._L.bt_kv_reset(self._h))
+
+    def export(self, b: int, t_len: int):
+        kq = np.zeros((self.n_kv, t_len, self.head_dim), np.uint8)
+        vq = np.zeros_like(kq)
+        ks = np.zeros((self.n_kv, t_len), np.float32)
+        vs = np.zeros_like(ks)
+        check(self._L.bt_kv_export(self._h, b, t_len, kq.ctypes.data, ks.ctypes.data, vq.ctypes.data,
+                                   vs.ctypes.data))
+        return kq, ks, vq, vs
+
+    def __del__(self):
+        try:
+            if self._owned and getattr(self, "_h", None):
+                self._L.bt_kv_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+def attn_decode(cache: QuantizedKVCache, qkv, pos, n_heads: int, rope_theta: float = 10000.0):
+    """Attention core of BitAttention::forward for one new token per sequence
+    (layers/attention.rs:166-217): qkv CUDA f32 [batch, (n_heads+2 n_kv)*hd], pos CUDA int32
+    [batch] -> [batch, n_heads*hd]."""
+    torch = _torch()
+    qkv = qkv.contiguous()
+    batch = qkv.shape[0]
+    out = torch.empty((batch, n_heads * cache.head_dim), dtype=torch.float32, device=qkv.device)
+    check(cache._L.bt_attn_decode(cache._h, _ptr(qkv), _ptr(pos), batch, n_heads, rope_theta, _ptr(out),
+                                  _stream_ptr(qkv.device.index)))
+    return out
+
+
+@dataclass
+class BitLlamaConfig:
+    """model/config.rs:20-59 (the fields the decode path reads)."""
+    arch: str
+    vocab_size: int
+    hidden_dim: int
+    num_layers: int
+    n_heads: int
+    n_kv_heads: int
+    intermediate_dim: int
+    inner_lr: float = 0.0
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 2048
+
+
+class BitLlama:
+    """model/llama.rs:37-272: load weights, forward_one, reset_kv_cache."""
+
+    def __init__(self, cfg: BitLlamaConfig, max_batch: int = 1, device: int = 0):
+        self._L = _bind()
+        self.cfg, self.max_batch, self.device = cfg, max_batch, device
+        cc = _CModelConfig(ARCH_TTT if cfg.arch == "ttt" else ARCH_LLAMA, cfg.vocab_size, cfg.hidden_dim,
+                           cfg.num_layers, cfg.n_heads, cfg.n_kv_heads, cfg.intermediate_dim, cfg.inner_lr,
+                           cfg.rope_theta, cfg.max_position_embeddings, max_batch)
+        self._h = C.c_void_p()
+        check(self._L.bt_model_create(C.byref(self._h), C.byref(cc), device))
+
+    def set_linear(self, layer: int, kind: int, packed: np.ndarray, scale: float, n_out: int, k_in: int):
+        packed = np.ascontiguousarray(packed, np.uint8)
+        check(self._L.bt_model_set_linear(self._h, layer, kind, packed.ctypes.data, n_out, k_in, scale))
+
+    def set_tensor(self, kind: int, data: np.ndarray, layer: int = 0):
+        data = np.ascontiguousarray(data, np.float32)
+        check(self._L.bt_model_set_tensor(self._h, kind, layer, data.ctypes.data, data.size))
+
+    def finalize(self):
+        check(self._L.bt_model_finalize(self._h))
+
+    def reset_kv_cache(self):
+        check(self._L.bt_model_reset(self._h))
+
+    @property
+    def current_pos(self) -> int:
+        return self._L.bt_model_pos(self._h)
+
+    @property
+    def ternary_bytes(self) -> int:
+        return self._L.bt_model_ternary_bytes(self._h)
+
+    def forward_one(self, tokens, want_logits: bool = True):
+        """tokens: host ints [batch].  Returns (logits np [batch, vocab] or None, next ids)."""
+        tokens = np.ascontiguousarray(tokens, np.int32).reshape(-1)
+        b = tokens.size
+        logits = np.empty((b, self.cfg.vocab_size), np.float32) if want_logits else None
+        nxt = np.empty(b, np.int32)
+        check(self._L.bt_model_forward_one(self._h, tokens.ctypes.data, b,
+                                           logits.ctypes.data if want_logits else None, nxt.ctypes.data))
+        return logits, nxt
+
+    def step_dev(self, tokens_dev):
+        """Device-resident step on torch's current stream; results stay on the device."""
+        check(self._L.bt_model_step_dev(self._h, _ptr(tokens_dev), tokens_dev.numel(),
+                                        _stream_ptr(tokens_dev.device.index)))
+
+    def next_dev(self):
+        torch = _torch()
+        return _wrap_dev(self._L.bt_model_next(self._h), (self.max_batch,), torch.int32, self.device)
+
+    def logits_dev(self):
+        torch = _torch()
+        return _wrap_dev(self._L.bt_model_logits(self._h), (self.max_batch, self.cfg.vocab_size),
+                         torch.float32, self.device)
+
+    def ttt_state(self, layer: int):
+        torch = _torch()
+        d = self.cfg.hidden_dim // 4
+        p = self._L.bt_model_ttt_state(self._h, layer)
+        return None if not p else _wrap_dev(p, (self.max_batch, d, d), torch.float32, self.device)
+
+    def kv_cache(self, layer: int):
+        p = self._L.bt_model_kv_cache(self._h, layer)
+        if not p:
+            return None
+        c = self.cfg
+        return QuantizedKVCache(c.max_position_embeddings, self.max_batch, c.n_kv_heads,
+                                c.hidden_dim // c.n_heads, self.device, _borrowed=p)
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                self._L.bt_model_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+def _wrap_dev(ptr: int, shape, dtype, device: int):
+    """Zero-copy torch view of a device buffer owned by the library."""
+    torch = _torch()
+    n = int(np.prod(shape))
+    itemsize = torch.empty((), dtype=dtype).element_size()
+
+    class _Holder:
+        pass
+    h = _Holder()
+    h.__cuda_array_interface__ = {
+        "shape": (n * itemsize,), "typestr": "|u1", "data": (int(ptr), False), "version": 2,
+    }
+    return torch.as_tensor(h, device=f"cuda:{device}").view(dtype).reshape(shape)

@@ -1,0 +1,101 @@
+"""Seeded synthetic checkpoints with the shapes of the reference's model families.
+
+No model weights ship with the reference, so tests and the benchmark build random-init
+models of the right shape: ternary projections as packed 2-bit codes + one f32 scale,
+dense embedding / lm_head (values representable in bf16), unit RMSNorm weights.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .layers import pack_ternary
+from .model import (BitLlama, BitLlamaConfig, T_EMBED, T_LM_HEAD, T_NORM1, T_NORM2, T_NORM_F, W_DOWN,
+                    W_GATE, W_K, W_O, W_Q, W_TTT_DOWN, W_TTT_UP, W_UP, W_V)
+
+TINY_TTT = BitLlamaConfig("ttt", 32000, 256, 4, 4, 4, 688, inner_lr=0.01)
+TINY_LLAMA_TEST = BitLlamaConfig("llama", 1000, 256, 2, 8, 2, 512, max_position_embeddings=64)
+TINYLLAMA_1B = BitLlamaConfig("llama", 32000, 2048, 22, 32, 4, 5632, max_position_embeddings=2048)
+LLAMA3_8B = BitLlamaConfig("llama", 128256, 4096, 32, 32, 8, 14336, rope_theta=500000.0,
+                           max_position_embeddings=4096)
+
+
+@dataclass
+class SyntheticWeights:
+    cfg: BitLlamaConfig
+    embed: np.ndarray
+    lm_head: np.ndarray
+    norm_f: np.ndarray
+    layers: list = field(default_factory=list)  # dicts: norm1, norm2, kind -> (packed, scale, n, k)
+
+
+def _bf16_round(a: np.ndarray) -> np.ndarray:
+    """Round f32 to the nearest bf16-representable value (ties to even), still f32."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return r.view(np.float32)
+
+
+def _ternary_codes(rng, n, k):
+    codes = rng.integers(0, 3, size=(n, k // 4, 4), dtype=np.uint8)
+    return (codes[..., 0] | (codes[..., 1] << 2) | (codes[..., 2] << 4) | (codes[..., 3] << 6)).astype(np.uint8)
+
+
+def linear_shapes(cfg: BitLlamaConfig):
+    """kind -> (n_out, k_in) for one block (model/block.rs:43-64, layers/ttt.rs:29-34,
+    layers/attention.rs:121-129, layers/swiglu.rs:24-26)."""
+    H, I = cfg.hidden_dim, cfg.intermediate_dim
+    shapes = {W_GATE: (I, H), W_UP: (I, H), W_DOWN: (H, I)}
+    if cfg.arch == "ttt":
+        shapes.update({W_TTT_DOWN: (H // 4, H), W_TTT_UP: (H, H // 4)})
+    else:
+        hd = H // cfg.n_heads
+        shapes.update({W_Q: (cfg.n_heads * hd, H), W_K: (cfg.n_kv_heads * hd, H),
+                       W_V: (cfg.n_kv_heads * hd, H), W_O: (H, cfg.n_heads * hd)})
+    return shapes
+
+
+def make_weights(cfg: BitLlamaConfig, seed: int = 2000, from_latent: bool = True,
+                 share_layers: bool = False) -> SyntheticWeights:
+    """from_latent: draw N(0, 0.02) dense weights and run PackedTensor::pack on them (small
+    models); otherwise draw the ternary codes uniformly (p = 1/3) with scale 0.016.
+    share_layers: reuse layer 0's host arrays for every layer (the device copies stay
+    distinct) - keeps host-side generation of multi-GB models short."""
+    rng = np.random.default_rng(seed)
+    V, H = cfg.vocab_size, cfg.hidden_dim
+    w = SyntheticWeights(cfg,
+                         _bf16_round(rng.normal(0, 0.02, (V, H)).astype(np.float32)),
+                         _bf16_round(rng.normal(0, 0.02, (V, H)).astype(np.float32)),
+                         np.ones(H, np.float32))
+    for li in range(cfg.num_layers):
+        if share_layers and li > 0:
+            w.layers.append(w.layers[0])
+            continue
+        layer = {"norm1": np.ones(H, np.float32), "norm2": np.ones(H, np.float32)}
+        for kind, (n, k) in linear_shapes(cfg).items():
+            if from_latent:
+                dense = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+                packed, scale = pack_ternary(dense)
+                packed = packed.reshape(n, k // 4)
+            else:
+                packed, scale = _ternary_codes(rng, n, k), 0.016
+            layer[kind] = (packed, float(scale), n, k)
+        w.layers.append(layer)
+    return w
+
+
+def build_model(w: SyntheticWeights, max_batch: int = 1, device: int = 0) -> BitLlama:
+    m = BitLlama(w.cfg, max_batch=max_batch, device=device)
+    m.set_tensor(T_EMBED, w.embed)
+    m.set_tensor(T_LM_HEAD, w.lm_head)
+    m.set_tensor(T_NORM_F, w.norm_f)
+    for li, layer in enumerate(w.layers):
+        m.set_tensor(T_NORM1, layer["norm1"], li)
+        m.set_tensor(T_NORM2, layer["norm2"], li)
+        for kind, val in layer.items():
+            if isinstance(kind, int):
+                packed, scale, n, k = val
+                m.set_linear(li, kind, packed, scale, n, k)
+    m.finalize()
+    return m

@@ -116,6 +116,121 @@ bt_status bt_linear_forward_host(bt_linear* lin, const float* x_host, int64_t m,
 bt_status bt_act_quant(const void* x_dev, bt_dtype x_dtype, int64_t m, int64_t k, int8_t* q_dev,
                        float* s_dev, int32_t* qsum_dev, int device, void* stream);
 
+
+/* A BitLinear made of several projections that share their input, stacked along the
+ * output dimension (q|k|v, gate|up): one launch streams them all.  Each segment is given
+ * exactly like bt_linear_create's n_bases == 1 input; seg_rows[i] must be a multiple of
+ * 16.  No single call in the reference corresponds to it: it replaces the back-to-back
+ * forwards at RE/layers/attention.rs:159-161 and RE/layers/swiglu.rs:30-31. */
+bt_status bt_linear_create_fused(bt_linear** out, const uint8_t* const* seg_packed_host,
+                                 const int64_t* seg_rows, const float* seg_scales, int n_seg,
+                                 int64_t k_in, int device);
+
+/* ---- TTT fast-weight layer ------------------------------------------------------------ */
+
+/* Inner update of TTTLayer::forward_update (RE/layers/ttt.rs:52-68; t_len = 1, chunk = 1)
+ * and TTTLayer::forward_chunkwise (RE/layers/ttt.rs:88-113) between the down and up
+ * projections: features are L2-normalised (eps 1e-6 added after the sqrt), predicted
+ * with the state, and the state takes one gradient step per chunk.
+ * w_state_dev [batch, d, d] f32 in/out; feat_dev [batch, t_len, d]; z_dev [batch, t_len, d]
+ * receives the predictions made with the pre-update state.  d <= 1024, chunk <= 64. */
+bt_status bt_ttt_update(float* w_state_dev, const float* feat_dev, int64_t batch, int64_t t_len,
+                        int64_t d, float inner_lr, int64_t chunk, float* z_dev, int device,
+                        void* stream);
+
+/* ---- Q8 KV cache + decode attention --------------------------------------------------- */
+
+typedef struct bt_kv_cache bt_kv_cache;
+
+/* QuantizedKVCache::new (RE/layers/kv_cache.rs:26-35) for `batch` sequences: u8 data
+ * [batch, n_kv_heads, max_seq_len, head_dim] + f32 scale per (sequence, head, position)
+ * for K and V, preallocated (the reference grows it with `cat`, :61-76). */
+bt_status bt_kv_create(bt_kv_cache** out, int64_t batch, int64_t n_kv_heads, int64_t head_dim,
+                       int64_t max_seq_len, int device);
+/* QuantizedKVCache::reset (RE/layers/kv_cache.rs:38-44). */
+bt_status bt_kv_reset(bt_kv_cache* cache);
+bt_status bt_kv_destroy(bt_kv_cache* cache);
+/* Copies position range [0, t_len) of sequence b to host: k_q/v_q [n_kv, t_len, head_dim]
+ * u8, k_s/v_s [n_kv, t_len] f32 (any may be NULL).  Synchronous; for tests and state I/O. */
+bt_status bt_kv_export(bt_kv_cache* cache, int64_t b, int64_t t_len, uint8_t* k_q_host,
+                       float* k_s_host, uint8_t* v_q_host, float* v_s_host);
+
+/* The attention core of BitAttention::forward for one new token per sequence
+ * (RE/layers/attention.rs:166-217 with seq_len == 1): RoPE at pos[b] on q and k
+ * (:180-182), QuantizedKVCache::append of k and v (RE/layers/kv_cache.rs:50-92),
+ * softmax((q.K^T)/sqrt(head_dim)) . V over positions 0..pos[b] of the dequantised cache,
+ * grouped-query sharing of KV heads (:228-239).
+ * qkv_dev [batch, (n_heads + 2 n_kv) * head_dim] f32 = q | k | v projections;
+ * pos_dev [batch] int32; out_dev [batch, n_heads * head_dim] f32.
+ * pos[b] must be < max_seq_len (BT_ERR_SHAPE is not detectable on device: the caller
+ * guarantees it, as the reference's RoPE table narrows fail beyond max_position). */
+bt_status bt_attn_decode(bt_kv_cache* cache, const float* qkv_dev, const int32_t* pos_dev,
+                         int64_t batch, int64_t n_heads, double rope_theta, float* out_dev,
+                         void* stream);
+
+/* ---- whole model: one decode step ----------------------------------------------------- */
+
+typedef struct bt_model bt_model;
+
+typedef struct {
+    int arch;                     /* 0 = "ttt", 1 = "llama" (RE/model/config.rs:12-18) */
+    int vocab_size;
+    int hidden_dim;
+    int num_layers;
+    int n_heads;
+    int n_kv_heads;
+    int intermediate_dim;
+    float inner_lr;
+    double rope_theta;            /* default 10000 (RE/model/config.rs:61-63) */
+    int max_position_embeddings;  /* default 2048 (RE/model/config.rs:64-66) */
+    int max_batch;                /* sequences decoded together, >= 1 */
+} bt_model_config;
+
+typedef enum {
+    BT_W_Q = 0, BT_W_K, BT_W_V, BT_W_O, BT_W_GATE, BT_W_UP, BT_W_DOWN, BT_W_TTT_DOWN, BT_W_TTT_UP
+} bt_weight_kind;
+
+typedef enum {
+    BT_T_EMBED = 0,   /* [vocab, hidden] */
+    BT_T_LM_HEAD,     /* [vocab, hidden], dense (RE/model/llama.rs:23) */
+    BT_T_NORM_F,      /* [hidden] */
+    BT_T_NORM1,       /* per layer [hidden] */
+    BT_T_NORM2
+} bt_tensor_kind;
+
+/* BitLlama::load (RE/model/llama.rs:37-158) split into create / set_* / finalize so that
+ * the caller owns file parsing.  Weights are given the way a converted checkpoint stores
+ * them: ternary projections as packed bytes + scales (one basis here), embeddings, head
+ * and norms as f32 host arrays (the engine loads everything as F32, :414-415; embedding
+ * and head are kept in bf16 on the device). */
+bt_status bt_model_create(bt_model** out, const bt_model_config* cfg, int device);
+bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
+                              int64_t n_out, int64_t k_in, float scale);
+bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int layer, const float* data_host,
+                              int64_t n_elem);
+bt_status bt_model_finalize(bt_model* m);
+bt_status bt_model_destroy(bt_model* m);
+/* reset_kv_cache + fresh zero TTT states (RE/model/llama.rs:179-188,161-170). */
+bt_status bt_model_reset(bt_model* m);
+/* BitLlama::forward_one (RE/model/llama.rs:201-272) for `batch` sequences that are all at
+ * the same position: host token ids in, optional host logits [batch, vocab] f32 and/or
+ * greedy next ids out (last index among equal maxima, :510-515).  Synchronous. */
+bt_status bt_model_forward_one(bt_model* m, const int32_t* tokens_host, int batch,
+                               float* logits_host, int32_t* next_host);
+/* Same step with everything on the device and no synchronisation: the ids are read from
+ * tokens_dev, results stay in the model's buffers (bt_model_logits / bt_model_next). */
+bt_status bt_model_step_dev(bt_model* m, const int32_t* tokens_dev, int batch, void* stream);
+const float* bt_model_logits(bt_model* m);   /* device [max_batch, vocab] */
+const int32_t* bt_model_next(bt_model* m);   /* device [max_batch] */
+/* Current position (tokens consumed since the last reset). */
+int bt_model_pos(const bt_model* m);
+/* TTT state of one layer: device pointer [max_batch, d_small, d_small] f32 (NULL for
+ * arch llama); KV cache of one layer (NULL for arch ttt). */
+float* bt_model_ttt_state(bt_model* m, int layer);
+bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer);
+/* Ternary-weight bytes streamed by one decode step (sum over all BitLinear tiles). */
+int64_t bt_model_ternary_bytes(const bt_model* m);
+
 #ifdef __cplusplus
 }
 #endif

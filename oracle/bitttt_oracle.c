@@ -18,6 +18,14 @@
  *
  * Every function names the reference lines it follows (paths relative to the
  * reference project root).
+ *
+ * Reductions and transcendentals: the reference evaluates sums (RMSNorm mean, L2 norm,
+ * matmul rows, softmax) and exp/cos/sin in f32 through candle ops whose evaluation order
+ * and libm are not visible in its tree.  Here they are accumulated / evaluated in f64 and
+ * rounded to f32 once, which is within one f32 ulp of any f32 evaluation order and - more
+ * to the point - reproducible: the CUDA kernels do the same, so every value that feeds an
+ * int8 quantiser (a discontinuous step) is the same on both sides.  Pointwise f32
+ * operations keep the reference's order.  Built with -ffp-contract=off.
  */
 #include <math.h>
 #include <stdint.h>
@@ -305,9 +313,9 @@ EXPORT void oracle_rmsnorm(const float* x, int64_t m, int64_t h, const float* w,
                            float* y) {
     for (int64_t i = 0; i < m; ++i) {
         const float* xr = x + i * h;
-        float ss = 0.0f;
-        for (int64_t c = 0; c < h; ++c) ss += xr[c] * xr[c];
-        float denom = sqrtf(ss / (float)h + eps);
+        double ss = 0.0;
+        for (int64_t c = 0; c < h; ++c) ss += (double)xr[c] * (double)xr[c];
+        float denom = sqrtf((float)(ss / (double)h) + eps);
         for (int64_t c = 0; c < h; ++c) y[i * h + c] = (xr[c] / denom) * w[c];
     }
 }
@@ -315,7 +323,7 @@ EXPORT void oracle_rmsnorm(const float* x, int64_t m, int64_t h, const float* w,
 /* silu(g) * u -- crates/rust_engine/src/layers/swiglu.rs:31-33 (candle_nn::ops::silu =
  * x / (1 + exp(-x))). */
 EXPORT void oracle_silu_mul(const float* g, const float* u, int64_t n, float* out) {
-    for (int64_t i = 0; i < n; ++i) out[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
+    for (int64_t i = 0; i < n; ++i) out[i] = (g[i] / (1.0f + (float)exp(-(double)g[i]))) * u[i];
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -329,13 +337,14 @@ EXPORT void oracle_silu_mul(const float* g, const float* u, int64_t n, float* ou
 EXPORT void oracle_ttt_step(float* w, const float* feat, int64_t d, float lr, float* z_out) {
     float* fh = (float*)malloc(sizeof(float) * (size_t)d * 2);
     float* diff = fh + d;
-    float ss = 0.0f;
-    for (int64_t c = 0; c < d; ++c) ss += feat[c] * feat[c];
-    float nrm = sqrtf(ss) + 1e-6f;
+    double ss = 0.0;
+    for (int64_t c = 0; c < d; ++c) ss += (double)feat[c] * (double)feat[c];
+    float nrm = sqrtf((float)ss) + 1e-6f;
     for (int64_t c = 0; c < d; ++c) fh[c] = feat[c] / nrm;
     for (int64_t a = 0; a < d; ++a) {
-        float s = 0.0f;
-        for (int64_t c = 0; c < d; ++c) s += w[a * d + c] * fh[c];
+        double acc = 0.0;
+        for (int64_t c = 0; c < d; ++c) acc += (double)w[a * d + c] * (double)fh[c];
+        float s = (float)acc;
         z_out[a] = s;
         diff[a] = s - fh[a];
     }
@@ -353,25 +362,25 @@ EXPORT void oracle_ttt_chunk(float* w, const float* feats, int64_t t_len, int64_
     float* xh = (float*)malloc(sizeof(float) * (size_t)(t_len * d));
     float* g = (float*)malloc(sizeof(float) * (size_t)(d * d));
     for (int64_t t = 0; t < t_len; ++t) {
-        float ss = 0.0f;
-        for (int64_t c = 0; c < d; ++c) ss += feats[t * d + c] * feats[t * d + c];
-        float nrm = sqrtf(ss) + 1e-6f;
+        double ss = 0.0;
+        for (int64_t c = 0; c < d; ++c) ss += (double)feats[t * d + c] * (double)feats[t * d + c];
+        float nrm = sqrtf((float)ss) + 1e-6f;
         for (int64_t c = 0; c < d; ++c) xh[t * d + c] = feats[t * d + c] / nrm;
     }
     for (int64_t start = 0; start < t_len; start += chunk) {
         int64_t len = t_len - start < chunk ? t_len - start : chunk;
         for (int64_t t = start; t < start + len; ++t)
             for (int64_t a = 0; a < d; ++a) {
-                float s = 0.0f;
-                for (int64_t c = 0; c < d; ++c) s += w[a * d + c] * xh[t * d + c];
-                z_out[t * d + a] = s;
+                double acc = 0.0;
+                for (int64_t c = 0; c < d; ++c) acc += (double)w[a * d + c] * (double)xh[t * d + c];
+                z_out[t * d + a] = (float)acc;
             }
         for (int64_t a = 0; a < d; ++a)
             for (int64_t c = 0; c < d; ++c) {
-                float s = 0.0f;
+                double acc = 0.0;
                 for (int64_t t = start; t < start + len; ++t)
-                    s += (z_out[t * d + a] - xh[t * d + a]) * xh[t * d + c];
-                g[a * d + c] = s;
+                    acc += (double)(z_out[t * d + a] - xh[t * d + a]) * (double)xh[t * d + c];
+                g[a * d + c] = (float)acc;
             }
         for (int64_t i = 0; i < d * d; ++i) w[i] -= g[i] * lr;
     }
@@ -422,7 +431,7 @@ EXPORT void oracle_rope(float* x, int64_t rows, int64_t hd, int64_t pos, double 
     for (int64_t i = 0; i < half; ++i) {
         float inv = (float)(1.0 / pow(theta, (double)(2 * i) / (double)hd));
         float fr = (float)pos * inv;
-        float c = cosf(fr), s = sinf(fr);
+        float c = (float)cos((double)fr), s = (float)sin((double)fr);
         for (int64_t r = 0; r < rows; ++r) {
             float x1 = x[r * hd + i], x2 = x[r * hd + half + i];
             x[r * hd + i] = x1 * c - x2 * s;
@@ -442,29 +451,31 @@ EXPORT void oracle_attn_decode(const float* q, const float* k, const float* v, i
     int64_t rep = n_heads / n_kv;
     float scaling = (float)(1.0 / sqrt((double)hd));
     float* sc = (float*)malloc(sizeof(float) * (size_t)t_len);
+    double* pr = (double*)malloc(sizeof(double) * (size_t)t_len);
     for (int64_t h = 0; h < n_heads; ++h) {
         const float* kh = k + (h / rep) * t_len * hd;
         const float* vh = v + (h / rep) * t_len * hd;
         float mx = -INFINITY;
         for (int64_t t = 0; t < t_len; ++t) {
-            float s = 0.0f;
-            for (int64_t c = 0; c < hd; ++c) s += q[h * hd + c] * kh[t * hd + c];
-            s *= scaling;
+            double acc = 0.0;
+            for (int64_t c = 0; c < hd; ++c) acc += (double)q[h * hd + c] * (double)kh[t * hd + c];
+            float s = (float)acc * scaling;
             sc[t] = s;
             if (s > mx) mx = s;
         }
-        float den = 0.0f;
+        double den = 0.0;
         for (int64_t t = 0; t < t_len; ++t) {
-            sc[t] = expf(sc[t] - mx);
-            den += sc[t];
+            pr[t] = exp((double)sc[t] - (double)mx);
+            den += pr[t];
         }
         for (int64_t c = 0; c < hd; ++c) {
-            float s = 0.0f;
-            for (int64_t t = 0; t < t_len; ++t) s += (sc[t] / den) * vh[t * hd + c];
-            out[h * hd + c] = s;
+            double acc = 0.0;
+            for (int64_t t = 0; t < t_len; ++t) acc += pr[t] * (double)vh[t * hd + c];
+            out[h * hd + c] = (float)(acc / den);
         }
     }
     free(sc);
+    free(pr);
 }
 
 /* Dense f32 linear without bias: y[M,N] = x[M,K] . W[N,K]^T -- the lm_head

@@ -405,3 +405,26 @@ class Model:
         logits = dense_linear(hn, self.lm_head)[0]
         st.pos += 1
         return logits
+
+
+def model_from_weights(w) -> Model:
+    """Builds the oracle model from the synthetic checkpoint structure that the GPU model
+    is built from (fields: cfg, embed, lm_head, norm_f, layers[kind -> (packed, scale, n, k)]).
+    Weight-kind indices follow bt_weight_kind in include/bitttt.h."""
+    (W_Q, W_K, W_V, W_O, W_GATE, W_UP, W_DOWN, W_TTT_DOWN, W_TTT_UP) = range(9)
+    c = w.cfg
+    cfg = ModelConfig(c.arch, c.vocab_size, c.hidden_dim, c.num_layers, c.n_heads, c.n_kv_heads,
+                      c.intermediate_dim, c.inner_lr, c.rope_theta)
+
+    def lin(layer, kind):
+        if kind not in layer:
+            return None
+        packed, scale, n, k = layer[kind]
+        return Linear(np.ascontiguousarray(packed).reshape(n, k // 4), np.array([scale], np.float32), n, k)
+
+    layers = []
+    for layer in w.layers:
+        layers.append(Layer(layer["norm1"], layer["norm2"], lin(layer, W_GATE), lin(layer, W_UP),
+                            lin(layer, W_DOWN), lin(layer, W_TTT_DOWN), lin(layer, W_TTT_UP),
+                            lin(layer, W_Q), lin(layer, W_K), lin(layer, W_V), lin(layer, W_O)))
+    return Model(cfg, w.embed, layers, w.norm_f, w.lm_head)

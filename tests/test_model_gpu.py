@@ -1,0 +1,82 @@
+"""GPU parity of the whole decode step (BitLlama::forward_one) against the oracle:
+teacher-forced logits and final TTT states / KV caches within 1e-3."""
+import importlib
+
+import numpy as np
+import pytest
+
+from gpu_util import load_bt
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def bt():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    return load_bt()
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def run_teacher_forced(bt, oracle, cfg, n_tokens, seed, batch=1):
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    w = syn.make_weights(cfg, seed=seed)
+    gpu = syn.build_model(w, max_batch=batch)
+    ref = oracle.model_from_weights(w)
+    states = [ref.new_state() for _ in range(batch)]
+    rng = np.random.default_rng(7)
+    tokens = rng.integers(0, cfg.vocab_size, size=(n_tokens, batch))
+    worst = 0.0
+    for t in range(n_tokens):
+        logits, nxt = gpu.forward_one(tokens[t])
+        for b in range(batch):
+            ref_logits = ref.forward_one(int(tokens[t, b]), states[b])
+            worst = max(worst, rel_err(logits[b], ref_logits))
+            assert worst <= REL_TOL, (t, b, worst)
+            assert logits[b, nxt[b]] == logits[b].max()
+    assert gpu.current_pos == n_tokens
+    return gpu, ref, states, worst
+
+
+def test_tiny_ttt_model_teacher_forced(bt, oracle):
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    cfg = syn.TINY_TTT  # 4 layers, hidden 256, MLP 688, vocab 32000, TTT layers
+    gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 12, 2000)
+    for li in range(cfg.num_layers):
+        w_gpu = gpu.ttt_state(li)[0].cpu().numpy()
+        assert rel_err(w_gpu, states[0].w[li]) <= REL_TOL
+    # reset gives the same logits again
+    l0, _ = gpu.forward_one([5])
+    gpu.reset_kv_cache()
+    assert gpu.current_pos == 0
+    l1, _ = gpu.forward_one([5])
+    st = ref.new_state()
+    assert rel_err(l1[0], ref.forward_one(5, st)) <= REL_TOL
+    assert not np.array_equal(l0, l1)
+
+
+def test_tiny_llama_model_teacher_forced_batch2(bt, oracle):
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    cfg = syn.TINY_LLAMA_TEST  # 2 layers, hidden 256, 8 q heads / 2 kv heads, head_dim 32
+    gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 10, 3000, batch=2)
+    kq, ks, vq, vs = gpu.kv_cache(1).export(1, 10)
+    ref_k = np.stack(states[1].kq[1], 1)
+    assert np.abs(kq.astype(np.int32) - ref_k.astype(np.int32)).max() <= 1
+    assert bt.lib().bt_device_check(0) == 0
+
+
+def test_position_limit(bt):
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    cfg = syn.BitLlamaConfig("llama", 64, 64, 1, 2, 1, 64, max_position_embeddings=3)
+    gpu = syn.build_model(syn.make_weights(cfg, seed=1))
+    for _ in range(3):
+        gpu.forward_one([1])
+    with pytest.raises(bt.BitTTTError) as ei:
+        gpu.forward_one([1])
+    assert ei.value.status == bt.BT_ERR_SHAPE
