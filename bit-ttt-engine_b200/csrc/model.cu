@@ -370,9 +370,12 @@ bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
         exec = reinterpret_cast<cudaGraphExec_t>(marker);
     } else if (exec == reinterpret_cast<cudaGraphExec_t>(marker)) {
         cudaGraph_t graph = nullptr;
-        BT_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-        bt_status st = enqueue_step(m, batch, s);
-        cudaError_t e = cudaStreamEndCapture(s, &graph);
+        // captured on the model's own stream (the legacy default stream cannot capture),
+        // launched on the caller's
+        cudaStream_t cs = m->stream;
+        BT_CUDA_TRY(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+        bt_status st = enqueue_step(m, batch, cs);
+        cudaError_t e = cudaStreamEndCapture(cs, &graph);
         if (st != BT_OK) { if (graph) cudaGraphDestroy(graph); return st; }
         if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
         cudaGraphExec_t ge = nullptr;
@@ -429,3 +432,49 @@ extern "C" bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer) {
     return m->layers[(size_t)layer].kv;
 }
 extern "C" int64_t bt_model_ternary_bytes(const bt_model* m) { return m ? m->ternary_bytes : 0; }
+
+extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, void* stream, int* n_launches) {
+    if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_enqueue_products: model not finalized");
+    if (batch < 1 || batch > m->cfg.max_batch) return set_error(BT_ERR_SHAPE, "batch %d outside 1..%d", batch, m->cfg.max_batch);
+    DeviceGuard guard(m->device);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    unsigned int* err = device_error_word(m->device);
+    const int groups = (batch + 7) / 8;
+    int launches = 0;
+    // outputs go to the gate/up buffer (the largest activation buffer), never to h
+    for (auto& L : m->layers) {
+        bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up, L.gate_up, L.down};
+        for (bt_linear* lin : seq) {
+            BT_CUDA_TRY(linear_product(lin->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, lin->w.n_out,
+                                       EPI_F32, err, m->sm_count, s));
+            launches += groups;
+        }
+    }
+    if (n_launches) *n_launches = launches;
+    return BT_OK;
+}
+
+extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
+    if (!m) return 0;
+    const int groups = (batch + 7) / 8;
+    // per layer: 4 quantiser launches, 4 ternary products, attention (2) or TTT update (1)
+    const int per_layer = 4 + 4 * groups + (m->cfg.arch == 1 ? 2 : 1);
+    // embedding, final norm, lm_head (4 tokens per launch), arg-max, position advance
+    return m->cfg.num_layers * per_layer + 1 + 1 + (batch + 3) / 4 + 1 + 1;
+}
+
+__global__ void set_pos_kernel(int32_t* pos, int n, int value) {
+    if (threadIdx.x < n) pos[threadIdx.x] = value;
+}
+
+extern "C" bt_status bt_model_seek(bt_model* m, int pos) {
+    if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_seek: model not finalized");
+    if (pos < 0 || (m->cfg.arch == 1 && pos >= m->cfg.max_position_embeddings))
+        return set_error(BT_ERR_SHAPE, "bt_model_seek: position %d outside [0, %d)", pos, m->cfg.max_position_embeddings);
+    DeviceGuard guard(m->device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    set_pos_kernel<<<1, 64>>>(m->pos, m->cfg.max_batch, pos);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    m->host_pos = pos;
+    return BT_OK;
+}

@@ -53,6 +53,9 @@ def _bind():
     L.bt_model_kv_cache.argtypes = [vp, i32]
     L.bt_model_ternary_bytes.restype = i64
     L.bt_model_ternary_bytes.argtypes = [vp]
+    L.bt_model_seek.argtypes = [vp, i32]
+    L.bt_model_enqueue_products.argtypes = [vp, i32, vp, C.POINTER(i32)]
+    L.bt_model_launches_per_step.argtypes = [vp, i32]
     L._model_bound = True
     return L
 
@@ -160,6 +163,10 @@ class BitLlama:
     def reset_kv_cache(self):
         check(self._L.bt_model_reset(self._h))
 
+    def seek(self, pos: int):
+        """Continue from position `pos` with the caches as they are in device memory."""
+        check(self._L.bt_model_seek(self._h, pos))
+
     @property
     def current_pos(self) -> int:
         return self._L.bt_model_pos(self._h)
@@ -182,6 +189,15 @@ class BitLlama:
         """Device-resident step on torch's current stream; results stay on the device."""
         check(self._L.bt_model_step_dev(self._h, _ptr(tokens_dev), tokens_dev.numel(),
                                         _stream_ptr(tokens_dev.device.index)))
+
+    def enqueue_products(self, batch: int) -> int:
+        """Measurement aid: only the ternary-product launches of one step (state untouched)."""
+        n = C.c_int(0)
+        check(self._L.bt_model_enqueue_products(self._h, batch, _stream_ptr(self.device), C.byref(n)))
+        return n.value
+
+    def launches_per_step(self, batch: int) -> int:
+        return self._L.bt_model_launches_per_step(self._h, batch)
 
     def next_dev(self):
         torch = _torch()

@@ -224,12 +224,25 @@ const float* bt_model_logits(bt_model* m);   /* device [max_batch, vocab] */
 const int32_t* bt_model_next(bt_model* m);   /* device [max_batch] */
 /* Current position (tokens consumed since the last reset). */
 int bt_model_pos(const bt_model* m);
+/* State I/O aid: declares that the KV caches already hold `pos` positions (contents as
+ * they are in device memory: zero keys/values after a reset, or whatever the caller put
+ * there through bt_model_kv_cache) and continues decoding from there.  The reference's
+ * counterpart is assigning BitLlama::current_pos together with restored caches
+ * (RE/model/llama.rs:35,269). */
+bt_status bt_model_seek(bt_model* m, int pos);
 /* TTT state of one layer: device pointer [max_batch, d_small, d_small] f32 (NULL for
  * arch llama); KV cache of one layer (NULL for arch ttt). */
 float* bt_model_ttt_state(bt_model* m, int layer);
 bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer);
 /* Ternary-weight bytes streamed by one decode step (sum over all BitLinear tiles). */
 int64_t bt_model_ternary_bytes(const bt_model* m);
+/* Measurement aid (no counterpart in the reference): enqueues only the ternary-product
+ * launches of one decode step, in step order, on whatever the activation buffers hold,
+ * writing to scratch outputs; model state is not touched.  *n_launches receives the number
+ * of kernel launches enqueued. */
+bt_status bt_model_enqueue_products(bt_model* m, int batch, void* stream, int* n_launches);
+/* Kernel launches of one decode step at this batch size. */
+int bt_model_launches_per_step(const bt_model* m, int batch);
 
 #ifdef __cplusplus
 }

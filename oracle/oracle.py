@@ -285,12 +285,17 @@ class Linear:
     scales: np.ndarray
     n: int
     k: int
+    # False: the reference's own arithmetic, f32 activations straight into
+    # BitLinearCpu::forward (kernels/cpu.rs:17-127), no int8 stage (single basis only)
+    quantised: bool = True
 
     @property
     def n_bases(self):
         return 1 if self.packed.ndim == 2 else self.packed.shape[2]
 
     def __call__(self, x):
+        if not self.quantised:
+            return bitlinear_f32(x, self.packed, self.n, float(self.scales[0]))
         return bitlinear_q(x, self.packed, self.scales, self.n, self.n_bases)
 
 
@@ -407,7 +412,7 @@ class Model:
         return logits
 
 
-def model_from_weights(w) -> Model:
+def model_from_weights(w, quantised: bool = True) -> Model:
     """Builds the oracle model from the synthetic checkpoint structure that the GPU model
     is built from (fields: cfg, embed, lm_head, norm_f, layers[kind -> (packed, scale, n, k)]).
     Weight-kind indices follow bt_weight_kind in include/bitttt.h."""
@@ -420,7 +425,8 @@ def model_from_weights(w) -> Model:
         if kind not in layer:
             return None
         packed, scale, n, k = layer[kind]
-        return Linear(np.ascontiguousarray(packed).reshape(n, k // 4), np.array([scale], np.float32), n, k)
+        return Linear(np.ascontiguousarray(packed).reshape(n, k // 4), np.array([scale], np.float32), n, k,
+                      quantised)
 
     layers = []
     for layer in w.layers:
