@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
     L.bt_workspace_create.argtypes = [C.POINTER(vp), i32, C.c_size_t]
     L.bt_workspace_destroy.argtypes = [vp]
     L.bt_linear_forward.argtypes = [vp, vp, vp, i64, i64, i32, vp, i32, vp]
+    L.bt_linear_forward_noalloc.argtypes = [vp, vp, i64, i64, i32, vp, i32, vp]
     L.bt_linear_forward_q.argtypes = [vp, vp, vp, vp, i64, vp, i32, vp]
     L.bt_linear_forward_host.argtypes = [vp, vp, i64, i64, vp]
     L.bt_act_quant.argtypes = [vp, i32, i64, i64, vp, vp, vp, i32, vp]

@@ -426,3 +426,70 @@ extern "C" bt_status bt_linear_create_fused(bt_linear** out, const uint8_t* cons
     *out = lin;
     return BT_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// forward without any allocation: scratch in a static device array
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocActBytes = BT_NOALLOC_MAX_ACT_BYTES;
+constexpr size_t kNoAllocTailBytes = 1024;  // per-token scales and sums, 256-byte aligned slots
+
+// Scratch of bt_linear_forward_noalloc: [quantised activations | scales | sums].  In host
+// code this name is only a handle for cudaGetSymbolAddress; the kernels get the address
+// that call returns.
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocActBytes + kNoAllocTailBytes];
+
+std::mutex g_noalloc_mu;
+uint8_t* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Once per device, with that device current: the array's address in device memory.
+bt_status noalloc_scratch(int device, uint8_t** out) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return set_error(BT_ERR_CUDA, "bt_linear_forward_noalloc: cudaGetSymbolAddress failed: %s",
+                             cudaGetErrorString(e));
+        g_noalloc_ptr[device] = static_cast<uint8_t*>(p);
+    }
+    *out = g_noalloc_ptr[device];
+    return BT_OK;
+}
+
+}  // namespace
+
+extern "C" bt_status bt_linear_forward_noalloc(bt_linear* lin, const void* x_dev, int64_t m, int64_t x_k,
+                                               bt_dtype x_dtype, void* y_dev, bt_dtype y_dtype, void* stream) {
+    if (!lin) return set_error(BT_ERR_ARG, "bt_linear_forward_noalloc: null handle");
+    if (x_k != lin->w.k_in)
+        return set_error(BT_ERR_SHAPE, "Shape mismatch: Input [%lld, %lld] vs Weight [%lld, %lld]",
+                         (long long)m, (long long)x_k, (long long)lin->w.n_out, (long long)lin->w.k_in);
+    if (m < 0) return set_error(BT_ERR_SHAPE, "bt_linear_forward_noalloc: negative token count");
+    if ((x_dtype != BT_F32 && x_dtype != BT_BF16) || (y_dtype != BT_F32 && y_dtype != BT_BF16))
+        return set_error(BT_ERR_ARG, "bt_linear_forward_noalloc: dtype must be BT_F32 or BT_BF16");
+    if (m == 0) return BT_OK;
+    if (!x_dev || !y_dev) return set_error(BT_ERR_ARG, "bt_linear_forward_noalloc: null pointer");
+    const size_t act_bytes = (size_t)m * (size_t)lin->w.k_pad();
+    if (m > 8 || act_bytes > kNoAllocActBytes)
+        return set_error(BT_ERR_NOMEM,
+                         "bt_linear_forward_noalloc: %lld tokens x %lld padded inputs = %zu bytes exceed the static "
+                         "scratch (%zu bytes, at most 8 tokens); use bt_linear_forward with a workspace",
+                         (long long)m, (long long)lin->w.k_pad(), act_bytes, kNoAllocActBytes);
+    if (lin->w.n_bases > 1 && y_dtype == BT_BF16)
+        return set_error(BT_ERR_ARG, "bt_linear_forward_noalloc: several bases need a BT_F32 output");
+    DeviceGuard guard(lin->device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", lin->device);
+    uint8_t* base = nullptr;
+    bt_status st = noalloc_scratch(lin->device, &base);
+    if (st != BT_OK) return st;
+    WsPlan p;
+    p.q = reinterpret_cast<int8_t*>(base);
+    p.sx = reinterpret_cast<float*>(base + kNoAllocActBytes);
+    p.qsum = reinterpret_cast<int32_t*>(base + kNoAllocActBytes + 256);
+    p.ytmp = nullptr;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    BT_CUDA_TRY(launch_act_quant(x_dev, x_dtype, m, lin->w.k_in, p.q, lin->w.k_pad(), p.sx, p.qsum, s));
+    return run_product(lin, p, m, y_dev, y_dtype, false, s);
+}

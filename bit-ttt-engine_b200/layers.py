@@ -187,6 +187,20 @@ class BitLinear:
 
     __call__ = forward
 
+    def forward_noalloc(self, x, out):
+        """forward() for hosts that cannot let the library allocate device memory (an arena
+        that already owns the whole GPU, or a loop that cannot afford cudaMalloc's device-wide
+        synchronisation): the caller supplies `out`, and the quantised-activation scratch is
+        a fixed array inside the library.  At most 8 tokens and 128 KiB of padded int8
+        activations; calls that may overlap on the GPU race on that array."""
+        self._need_handle()
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous() or not out.is_contiguous():
+            raise ValueError("forward_noalloc needs contiguous tensors (it will not make copies)")
+        check(lib().bt_linear_forward_noalloc(self._h, _ptr(x2), x2.shape[0], x2.shape[1], _bt_dtype(x2),
+                                              _ptr(out), _bt_dtype(out), _stream_ptr(x.device.index)))
+        return out
+
     def forward_q(self, q, sx=None, workspace: Workspace | None = None):
         """q: CUDA int8 [m, in_features].  sx None -> raw int32 accumulators of basis 0;
         else f32 outputs scaled with sx [m]."""

@@ -117,6 +117,38 @@ bt_status bt_act_quant(const void* x_dev, bt_dtype x_dtype, int64_t m, int64_t k
                        float* s_dev, int32_t* qsum_dev, int device, void* stream);
 
 
+/* Largest activation block bt_linear_forward_noalloc accepts: m * k_pad bytes, where k_pad
+ * is k_in rounded up to a multiple of 256 (e.g. 8 tokens x 16384 inputs). */
+#define BT_NOALLOC_MAX_ACT_BYTES (128 * 1024)
+
+/* bt_linear_forward for callers that must not allocate device memory.  It has no
+ * counterpart in the reference.
+ *
+ * Some hosts cannot tolerate a cudaMalloc on their inference path: a serving runtime that
+ * has already handed every spare byte of the GPU to its own arena (KV cache sized to fit),
+ * or a latency-critical loop in which cudaMalloc's implicit device-wide synchronisation
+ * would stall other streams.  bt_linear_forward needs scratch for the quantised
+ * activations and normally takes it from a bt_workspace (a cudaMalloc at creation) or from
+ * a workspace it allocates on first use.  This variant instead keeps that scratch in a
+ * fixed array compiled into the library's device image, so the call performs no
+ * cudaMalloc / cudaFree and touches no allocator at all.
+ *
+ * Limits and rules:
+ *  - m * k_pad must not exceed BT_NOALLOC_MAX_ACT_BYTES and m must be <= 8; larger requests
+ *    fail with BT_ERR_NOMEM and a message, nothing is launched.  With several bases the
+ *    output must be BT_F32.
+ *  - The array lives once per GPU that loads the library (about 129 KiB of device memory,
+ *    held until the process exits) and is shared by every call on that GPU: two calls
+ *    whose kernels may overlap (different streams, different threads) race on it.  Issue
+ *    these calls on one stream, or order them yourself.
+ *  - Nothing in the array needs to start at zero: each call rewrites every byte it later
+ *    reads (the quantiser zero-fills the padding up to k_pad).
+ *  - The first call on a device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call outside of any stream capture.
+ * Same arithmetic, arguments and errors as bt_linear_forward otherwise. */
+bt_status bt_linear_forward_noalloc(bt_linear* lin, const void* x_dev, int64_t m, int64_t x_k,
+                                    bt_dtype x_dtype, void* y_dev, bt_dtype y_dtype, void* stream);
+
 /* A BitLinear made of several projections that share their input, stacked along the
  * output dimension (q|k|v, gate|up): one launch streams them all.  Each segment is given
  * exactly like bt_linear_create's n_bases == 1 input; seg_rows[i] must be a multiple of
