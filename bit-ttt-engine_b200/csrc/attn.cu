@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     __shared__ double red_m[kAttnWarps][NREP], red_l[kAttnWarps][NREP];
     __shared__ double red_acc[kAttnWarps][NREP][32 * PER_LANE];
     ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
 
     const int hd = a.head_dim, half = hd >> 1;
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 // Merge the per-split partials: out = sum_s e^{m_s - m} acc_s / sum_s e^{m_s - m} l_s.
 __global__ void attn_combine_kernel(AttnArgs a) {
     ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
     const int hd = a.head_dim;
     const int64_t bh = blockIdx.x;  // b * n_heads + head
     const double* base = a.partial + bh * a.splits * (hd + 2);
@@ -179,20 +181,24 @@ __global__ void attn_combine_kernel(AttnArgs a) {
             l = fma(base[s * (hd + 2) + 1], sc, l);
             v = fma(base[s * (hd + 2) + 2 + c], sc, v);
         }
-        a.out[bh * hd + c] = (float)(v / l);
+        const float o = (float)(v / l);
+        a.out[bh * hd + c] = o;
+        if (a.absmax_out) atomicMax(a.absmax_out + bh / a.n_heads, __float_as_uint(fabsf(o)));
     }
 }
 
 }  // namespace
 
 template <int PER_LANE>
-static void launch_rep(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+static cudaError_t launch_rep(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+    cudaError_t e = cudaSuccess;
     switch (a.n_heads / a.n_kv) {
-        case 1: attn_decode_kernel<PER_LANE, 1><<<grid, kAttnThreads, 0, stream>>>(a); break;
-        case 2: attn_decode_kernel<PER_LANE, 2><<<grid, kAttnThreads, 0, stream>>>(a); break;
-        case 4: attn_decode_kernel<PER_LANE, 4><<<grid, kAttnThreads, 0, stream>>>(a); break;
-        default: attn_decode_kernel<PER_LANE, 8><<<grid, kAttnThreads, 0, stream>>>(a); break;
+        case 1: e = launch_pdl(attn_decode_kernel<PER_LANE, 1>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
+        case 2: e = launch_pdl(attn_decode_kernel<PER_LANE, 2>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
+        case 4: e = launch_pdl(attn_decode_kernel<PER_LANE, 4>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
+        default: e = launch_pdl(attn_decode_kernel<PER_LANE, 8>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
     }
+    return e;
 }
 
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
@@ -201,16 +207,15 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
         !(rep == 1 || rep == 2 || rep == 4 || rep == 8))
         return cudaErrorInvalidValue;
     dim3 grid(a.batch * a.n_kv, a.splits);
+    cudaError_t e;
     switch (a.head_dim / 32) {
-        case 1: launch_rep<1>(a, grid, stream); break;
-        case 2: launch_rep<2>(a, grid, stream); break;
-        case 3: launch_rep<3>(a, grid, stream); break;
-        default: launch_rep<4>(a, grid, stream); break;
+        case 1: e = launch_rep<1>(a, grid, stream); break;
+        case 2: e = launch_rep<2>(a, grid, stream); break;
+        case 3: e = launch_rep<3>(a, grid, stream); break;
+        default: e = launch_rep<4>(a, grid, stream); break;
     }
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    attn_combine_kernel<<<a.batch * a.n_heads, a.head_dim, 0, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(attn_combine_kernel, dim3(a.batch * a.n_heads), dim3(a.head_dim), 0, stream, a.pdl, a);
 }
 
 }  // namespace bt

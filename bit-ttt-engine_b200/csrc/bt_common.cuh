@@ -75,6 +75,7 @@ enum Epilogue : int {
     EPI_F32 = 1,        // (acc * s_w) * s_x[m]           -> f32 [m, n]
     EPI_F32_ACCUM = 2,  // out += (acc * s_w) * s_x[m]    (further bases)
     EPI_BF16 = 3,       // bf16((acc * s_w) * s_x[m])
+    EPI_SWIGLU = 4,     // rows 0-7 of a tile = gate j, rows 8-15 = up j: out[m, j] = silu(gate)*up
 };
 
 // ---------------------------------------------------------------------------------------
@@ -92,20 +93,36 @@ cudaError_t launch_retile(const uint8_t* src_dev, int64_t n_out, int64_t k_in, i
 cudaError_t launch_act_quant(const void* x, bt_dtype x_dtype, int64_t m, int64_t k, int8_t* q,
                              int64_t q_stride, float* s, int32_t* qsum, cudaStream_t stream);
 
+// Where the int8 activations of a ternary product come from.
+enum Prologue : int {
+    PRO_Q8 = 0,       // already quantised in global memory (q, qsum, sx)
+    PRO_RMSNORM = 1,  // x f32 -> RMSNorm with norm_w -> per-token absmax quantisation, in the kernel
+    PRO_ABSMAX = 2,   // x f32 with its per-token max|x| already known (absmax_in) -> quantisation
+};
+
 // Ternary product for up to 8 tokens per launch.
 struct GemvArgs {
     const uint8_t* tiles;   // one basis
     int64_t row_tiles, k_tiles, n_out;
-    const int8_t* q;        // [m, q_stride] int8, zero beyond k_in
+    int64_t k_in;           // real number of inputs (<= k_tiles*256)
+    int prologue;
+    const int8_t* q;        // PRO_Q8: [m, q_stride] int8, zero beyond k_in
     int64_t q_stride;
-    const int32_t* qsum;    // [m]
-    const float* sx;        // [m] (unused for EPI_I32)
-    const float* sw_tiles;  // [row_tiles] weight scale of each row tile (unused for EPI_I32)
+    const int32_t* qsum;    // PRO_Q8: [m]
+    const float* sx;        // PRO_Q8: [m] (unused for EPI_I32)
+    const float* x;         // PRO_RMSNORM / PRO_ABSMAX: [m, x_stride] f32
+    int64_t x_stride;
+    const float* norm_w;    // PRO_RMSNORM: [k_in]
+    float eps;
+    const unsigned int* absmax_in;  // PRO_ABSMAX: [m] bit patterns of max|x| (non-negative floats)
+    unsigned int* absmax_out;       // EPI_SWIGLU: [m] running max of |out| via atomicMax on the bits
+    const float* sw_tiles;  // [row_tiles][2] weight scale of rows 0-7 / 8-15 of each row tile
     int m;                  // 1..8
-    void* out;              // [m, n_out]
+    void* out;              // [m, out_stride]
     int64_t out_stride;     // elements between tokens
     int epilogue;
     unsigned int* err;
+    bool pdl;               // launch with programmatic stream serialisation
 };
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream);
 
@@ -114,7 +131,7 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream);
 // segment of rows.
 struct LinearDev {
     TiledWeights w;
-    const float* scale_tiles = nullptr;  // device, [n_bases][row_tiles]
+    const float* scale_tiles = nullptr;  // device, [n_bases][row_tiles][2] (rows 0-7, rows 8-15)
 };
 
 // Ternary product of `m` quantised tokens with every basis of `lin` (8 tokens per launch).
@@ -124,5 +141,37 @@ cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stri
                            const int32_t* qsum, const float* sx, int64_t m, void* out,
                            int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
                            cudaStream_t stream);
+
+// Single-basis product for m <= 8 tokens whose quantisation happens inside the kernel.
+struct FusedIn {
+    int prologue;                   // PRO_RMSNORM or PRO_ABSMAX
+    const float* x;
+    int64_t x_stride;
+    const float* norm_w;
+    float eps;
+    const unsigned int* absmax_in;
+};
+cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m, void* out,
+                                 int64_t out_stride, int epilogue, unsigned int* absmax_out,
+                                 unsigned int* err, int sm_count, cudaStream_t stream);
+
+// Launch with the programmatic-stream-serialisation attribute: the kernel may start while
+// its predecessor in the stream is still running and must call griddepcontrol.wait before
+// touching anything the predecessor produces.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace bt

@@ -37,3 +37,11 @@ struct bt_kv_cache {
     int64_t partial_floats = 0;
     int max_heads = 0;
 };
+
+namespace bt {
+// Gate and up projections of a SwiGLU block as ONE BitLinear whose row tiles hold 8 gate
+// rows followed by the 8 matching up rows, so that the product's epilogue sees gate[j] and
+// up[j] in the same thread and can emit silu(gate)*up directly (EPI_SWIGLU).
+bt_status create_gate_up(bt_linear** out, const uint8_t* gate_packed_host, const uint8_t* up_packed_host,
+                         int64_t rows, int64_t k_in, float gate_scale, float up_scale, int device);
+}  // namespace bt

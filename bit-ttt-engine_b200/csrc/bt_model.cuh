@@ -7,8 +7,10 @@ namespace bt {
 
 enum RowPre : int { PRE_NONE = 0, PRE_RMSNORM = 1, PRE_SWIGLU = 2 };
 
+// Also clears `n_clear` words at `clear` (the per-step absmax cells).
 cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int batch, int hidden,
-                         int vocab, float* h, cudaStream_t stream);
+                         int vocab, float* h, cudaStream_t stream, unsigned int* clear = nullptr,
+                         int n_clear = 0, bool pdl = false);
 
 // Row transform (none | RMSNorm | silu(gate)*up) + per-token absmax int8 quantisation.
 // x: [batch, x_stride] f32 (PRE_SWIGLU: gate at [0,k), up at [k,2k)); q rows of q_stride
@@ -21,6 +23,16 @@ cudaError_t launch_lm_head(const __nv_bfloat16* w, const float* x, int batch, in
                            float* logits, int sm_count, cudaStream_t stream);
 
 cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream);
+
+// Final RMSNorm fused into the dense lm_head, plus per-CTA arg-max candidates:
+// logits[b, :] = lm_head . rmsnorm(h[b, :]); cand_val/cand_idx [batch, *n_cand].
+cudaError_t launch_lm_head_fused(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
+                                 int batch, int hidden, int64_t vocab, float* logits, float* cand_val,
+                                 int32_t* cand_idx, int* n_cand, int sm_count, cudaStream_t stream, bool pdl);
+// Reduces the candidates to the greedy pick per token and advances the positions.
+cudaError_t launch_pick(const float* cand_val, const int32_t* cand_idx, int n_cand, int batch, int32_t* out,
+                        int32_t* pos, int n_pos, cudaStream_t stream, bool pdl);
+int lm_head_max_candidates(int sm_count);
 
 // Q8 KV cache of one layer: u8 data [batch, n_kv, max_seq, head_dim] and f32 scales
 // [batch, n_kv, max_seq] for K and V (layers/kv_cache.rs:14-24).
@@ -46,15 +58,18 @@ struct AttnArgs {
     int batch, n_heads, n_kv, head_dim;
     int splits;
     float scaling;
+    unsigned int* absmax_out;  // optional [batch]: running max|out| (bits) via atomicMax
+    bool pdl;                  // launch with programmatic stream serialisation
 };
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
 
 // TTT fast-weight step (layers/ttt.rs:52-68) for `batch` independent states:
 // w: [batch, d, d] f32 updated in place, feat: [batch, d], z_out: [batch, d].
 cudaError_t launch_ttt_step(float* w, const float* feat, int batch, int d, float lr, float* z_out,
-                            cudaStream_t stream);
+                            cudaStream_t stream, unsigned int* absmax_out = nullptr, bool pdl = false);
 // Chunked form (layers/ttt.rs:88-113): feats [batch, t_len, d], z_out [batch, t_len, d].
 cudaError_t launch_ttt_chunk(float* w, const float* feats, int batch, int t_len, int d, float lr,
-                             int chunk, float* z_out, cudaStream_t stream);
+                             int chunk, float* z_out, cudaStream_t stream, unsigned int* absmax_out = nullptr,
+                             bool pdl = false);
 
 }  // namespace bt

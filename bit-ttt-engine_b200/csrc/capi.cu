@@ -182,13 +182,13 @@ extern "C" bt_status bt_linear_create(bt_linear** out, const uint8_t* packed_hos
     }
     lin->w.tiles = lin->tiles;
     {
-        // one weight scale per (basis, row tile); a plain BitLinear repeats scales[b]
-        const size_t cnt = (size_t)n_bases * (size_t)lin->w.row_tiles;
+        // one weight scale per (basis, half row tile); a plain BitLinear repeats scales[b]
+        const size_t cnt = (size_t)n_bases * (size_t)lin->w.row_tiles * 2;
         float* host = new (std::nothrow) float[cnt];
         cudaError_t e2 = host ? cudaMalloc(&lin->scale_tiles, cnt * sizeof(float)) : cudaErrorMemoryAllocation;
         if (e2 == cudaSuccess) {
             for (int b = 0; b < n_bases; ++b)
-                for (int64_t r = 0; r < lin->w.row_tiles; ++r) host[(size_t)b * lin->w.row_tiles + r] = scales_host[b];
+                for (int64_t r = 0; r < lin->w.row_tiles * 2; ++r) host[(size_t)b * lin->w.row_tiles * 2 + r] = scales_host[b];
             e2 = cudaMemcpy(lin->scale_tiles, host, cnt * sizeof(float), cudaMemcpyHostToDevice);
         }
         delete[] host;
@@ -413,14 +413,14 @@ extern "C" bt_status bt_linear_create_fused(bt_linear** out, const uint8_t* cons
     bt_status st = bt_linear_create(&lin, cat, n_total, k_in, 1, seg_scales, device);
     delete[] cat;
     if (st != BT_OK) return st;
-    // overwrite the per-row-tile scales segment by segment
-    float* host = new (std::nothrow) float[(size_t)lin->w.row_tiles];
+    // overwrite the per-half-tile scales segment by segment
+    float* host = new (std::nothrow) float[(size_t)lin->w.row_tiles * 2];
     if (!host) { bt_linear_destroy(lin); return set_error(BT_ERR_NOMEM, "host allocation failed"); }
     int64_t rt = 0;
     for (int i = 0; i < n_seg; ++i)
-        for (int64_t r = 0; r < seg_rows[i] / kTileRows; ++r) host[rt++] = seg_scales[i];
+        for (int64_t r = 0; r < seg_rows[i] / kTileRows * 2; ++r) host[rt++] = seg_scales[i];
     DeviceGuard guard(device);
-    cudaError_t e = cudaMemcpy(lin->scale_tiles, host, (size_t)lin->w.row_tiles * sizeof(float), cudaMemcpyHostToDevice);
+    cudaError_t e = cudaMemcpy(lin->scale_tiles, host, (size_t)lin->w.row_tiles * 2 * sizeof(float), cudaMemcpyHostToDevice);
     delete[] host;
     if (e != cudaSuccess) { bt_linear_destroy(lin); return set_error(BT_ERR_CUDA, "bt_linear_create_fused: %s", cudaGetErrorString(e)); }
     *out = lin;
@@ -493,3 +493,36 @@ extern "C" bt_status bt_linear_forward_noalloc(bt_linear* lin, const void* x_dev
     BT_CUDA_TRY(launch_act_quant(x_dev, x_dtype, m, lin->w.k_in, p.q, lin->w.k_pad(), p.sx, p.qsum, s));
     return run_product(lin, p, m, y_dev, y_dtype, false, s);
 }
+
+namespace bt {
+
+bt_status create_gate_up(bt_linear** out, const uint8_t* gate, const uint8_t* up, int64_t rows, int64_t k_in,
+                         float gate_scale, float up_scale, int device) {
+    if (!out || !gate || !up) return set_error(BT_ERR_ARG, "create_gate_up: null pointer");
+    if (rows <= 0 || rows % 8 != 0 || k_in <= 0 || k_in % 4 != 0)
+        return set_error(BT_ERR_ALIGN, "create_gate_up: rows must be a multiple of 8 and in_features of 4");
+    const size_t row_bytes = (size_t)(k_in / 4);
+    uint8_t* cat = new (std::nothrow) uint8_t[(size_t)rows * 2 * row_bytes];
+    if (!cat) return set_error(BT_ERR_NOMEM, "host allocation failed");
+    for (int64_t t = 0; t < rows / 8; ++t) {
+        memcpy(cat + (size_t)(16 * t) * row_bytes, gate + (size_t)(8 * t) * row_bytes, 8 * row_bytes);
+        memcpy(cat + (size_t)(16 * t + 8) * row_bytes, up + (size_t)(8 * t) * row_bytes, 8 * row_bytes);
+    }
+    bt_linear* lin = nullptr;
+    const float one_scale[1] = {gate_scale};
+    bt_status st = bt_linear_create(&lin, cat, rows * 2, k_in, 1, one_scale, device);
+    delete[] cat;
+    if (st != BT_OK) return st;
+    const size_t cnt = (size_t)lin->w.row_tiles * 2;
+    float* host = new (std::nothrow) float[cnt];
+    if (!host) { bt_linear_destroy(lin); return set_error(BT_ERR_NOMEM, "host allocation failed"); }
+    for (size_t i = 0; i < cnt; ++i) host[i] = (i & 1) ? up_scale : gate_scale;
+    DeviceGuard guard(device);
+    cudaError_t e = cudaMemcpy(lin->scale_tiles, host, cnt * sizeof(float), cudaMemcpyHostToDevice);
+    delete[] host;
+    if (e != cudaSuccess) { bt_linear_destroy(lin); return set_error(BT_ERR_CUDA, "create_gate_up: %s", cudaGetErrorString(e)); }
+    *out = lin;
+    return BT_OK;
+}
+
+}  // namespace bt

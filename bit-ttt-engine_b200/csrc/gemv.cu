@@ -20,7 +20,12 @@
 //     a shared-memory buffer and signals an mbarrier; a separate epilogue warp adds the 8
 //     partials, subtracts sum_k q (undoing the +1 weight offset), scales and stores, so
 //     the math warps never stop at a CTA barrier.  Integer accumulation makes the result
-//     independent of how K was split.
+//     independent of how K was split;
+//   * the quantisation of the activations can run inside the kernel (RMSNorm + absmax
+//     quantise, or quantise with a known absmax): every CTA does it redundantly while its
+//     first weight stages are already in flight, which removes a kernel boundary per
+//     projection from the decode step; with programmatic dependent launch the weight
+//     prefetch even starts before the previous kernel has finished.
 #include "bt_common.cuh"
 #include "bt_ptx.cuh"
 
@@ -40,6 +45,8 @@ constexpr int kRedBufInts = kMathWarps * 128;
 constexpr int kRedBytes = kRedBufs * kRedBufInts * 4;
 constexpr int kMaxStages = 12;
 constexpr int kBarBytes = (2 * kMaxStages + 2 * kRedBufs) * 8;
+constexpr int kTokBytes = 128;  // per-token scale and sum, shared with the epilogue warp
+constexpr int kScratchBytes = 512;  // block-reduction scratch of the prologue
 constexpr unsigned kErrGemvTimeout = 0x47454d56u;  // 'GEMV'
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
@@ -59,6 +66,161 @@ __device__ __forceinline__ void tile_mma(int (&acc)[4][4], const uint8_t* tile, 
     }
 }
 
+
+// ---- reductions over the 256 math threads (named barrier 1) ----------------------------
+__device__ __forceinline__ double math_sum_d(double v, double* slot, int warp, int lane) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) slot[warp] = v;
+    ptx::named_bar_sync(1, kMathThreads);
+    double r = 0.0;
+#pragma unroll
+    for (int w = 0; w < kMathWarps; ++w) r += slot[w];
+    return r;
+}
+__device__ __forceinline__ float math_max_f(float v, float* slot, int warp, int lane) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (lane == 0) slot[warp] = v;
+    ptx::named_bar_sync(1, kMathThreads);
+    float r = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kMathWarps; ++w) r = fmaxf(r, slot[w]);
+    return r;
+}
+__device__ __forceinline__ int math_sum_i(int v, int* slot, int warp, int lane) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) slot[warp] = v;
+    ptx::named_bar_sync(1, kMathThreads);
+    int r = 0;
+#pragma unroll
+    for (int w = 0; w < kMathWarps; ++w) r += slot[w];
+    return r;
+}
+
+// Quantise 16 consecutive values (group j of a token) with scale s, store them
+// byte-transposed at their place in the activation image, return their sum.
+__device__ __forceinline__ int quant_store_group(const float (&v)[16], float s, uint8_t* dst_token, int j) {
+    uint32_t in[4], out[4];
+    int sum = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int qv = 0;
+            if (s > 0.0f) {
+                float rr = roundf(__fdiv_rn(v[4 * b + r], s));
+                rr = fminf(fmaxf(rr, -127.0f), 127.0f);
+                qv = (int)rr;
+            }
+            sum += qv;
+            word |= (uint32_t)(qv & 0xff) << (8 * r);
+        }
+        in[b] = word;
+    }
+    ptx::transpose4x4(in, out);
+    const int kt = j >> 4, tt = (j >> 2) & 3, i = j & 3;
+    uint8_t* p = dst_token + kt * kTileK + tt * 16 + i * 4;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) *reinterpret_cast<uint32_t*>(p + r * 64) = out[r];
+    return sum;
+}
+
+__device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float4 f = *reinterpret_cast<const float4*>(p + 4 * b);
+        v[4 * b] = f.x; v[4 * b + 1] = f.y; v[4 * b + 2] = f.z; v[4 * b + 3] = f.w;
+    }
+}
+
+// Builds the int8 activation image of all tokens in shared memory (math warps only) and
+// leaves the per-token scale and sum in tok_sx / tok_qsum.
+template <int PRO>
+__device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* acts, int act_stride, float* tok_sx,
+                                                  int* tok_qsum, uint8_t* scratch, int tid, int warp, int lane,
+                                                  int k_tiles) {
+    const int groups_pad = k_tiles * (kTileK / 16);
+    const int groups = (int)(a.k_in >> 4);  // k_in is a multiple of 16 on the fused paths
+    double* sl_d = reinterpret_cast<double*>(scratch);            // 8 doubles
+    float* sl_f = reinterpret_cast<float*>(scratch + 64);          // 8 floats
+    int* sl_i = reinterpret_cast<int*>(scratch + 128);             // 2 x 8 ints (alternating)
+    if (PRO == PRO_Q8) {
+        for (int n = 0; n < a.m; ++n) {
+            const uint4* src = reinterpret_cast<const uint4*>(a.q + (int64_t)n * a.q_stride);
+            uint8_t* dst = acts + (size_t)n * act_stride;
+            for (int j = tid; j < groups_pad; j += kMathThreads) {
+                const uint4 v = src[j];
+                const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+                uint32_t out[4];
+                ptx::transpose4x4(in, out);
+                const int kt = j >> 4, tt = (j >> 2) & 3, i = j & 3;
+                uint8_t* p = dst + kt * kTileK + tt * 16 + i * 4;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) *reinterpret_cast<uint32_t*>(p + r * 64) = out[r];
+            }
+        }
+        if (tid < a.m) {
+            tok_qsum[tid] = a.qsum[tid];
+            tok_sx[tid] = a.sx ? a.sx[tid] : 0.0f;
+        }
+        return;
+    }
+    for (int n = 0; n < a.m; ++n) {
+        const float* xr = a.x + (int64_t)n * a.x_stride;
+        uint8_t* dst = acts + (size_t)n * act_stride;
+        int local = 0;
+        float s;
+        if (PRO == PRO_RMSNORM) {
+            // up to two 16-groups per thread held in registers (k_in <= 8192)
+            float v0[16], v1[16];
+            const int j0 = tid, j1 = tid + kMathThreads;
+            const bool h0 = j0 < groups, h1 = j1 < groups;
+            double ss = 0.0;
+            if (h0) { load16(xr + 16 * j0, v0);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) ss = fma((double)v0[e], (double)v0[e], ss); }
+            if (h1) { load16(xr + 16 * j1, v1);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) ss = fma((double)v1[e], (double)v1[e], ss); }
+            ss = math_sum_d(ss, sl_d, warp, lane);
+            // x / sqrt(mean(x^2) + eps) * w  (layers/rms_norm.rs:40-55)
+            const float denom = sqrtf(__fadd_rn((float)(ss / (double)a.k_in), a.eps));
+            float amax = 0.0f;
+            if (h0) { float w[16]; load16(a.norm_w + 16 * j0, w);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) { v0[e] = __fmul_rn(__fdiv_rn(v0[e], denom), w[e]); amax = fmaxf(amax, fabsf(v0[e])); } }
+            if (h1) { float w[16]; load16(a.norm_w + 16 * j1, w);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) { v1[e] = __fmul_rn(__fdiv_rn(v1[e], denom), w[e]); amax = fmaxf(amax, fabsf(v1[e])); } }
+            amax = math_max_f(amax, sl_f, warp, lane);
+            s = __fdiv_rn(amax, 127.0f);
+            if (h0) local += quant_store_group(v0, s, dst, j0);
+            if (h1) local += quant_store_group(v1, s, dst, j1);
+            for (int j = groups + tid; j < groups_pad; j += kMathThreads) {
+                const float z[16] = {0};
+                quant_store_group(z, 0.0f, dst, j);
+            }
+        } else {  // PRO_ABSMAX
+            s = __fdiv_rn(__uint_as_float(a.absmax_in[n]), 127.0f);
+            for (int j = tid; j < groups_pad; j += kMathThreads) {
+                float v[16];
+                if (j < groups) load16(xr + 16 * j, v);
+                else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) v[e] = 0.0f;
+                }
+                local += quant_store_group(v, s, dst, j);
+            }
+        }
+        const int total = math_sum_i(local, sl_i + 8 * (n & 1), warp, lane);
+        if (tid == 0) { tok_qsum[n] = total; tok_sx[n] = s; }
+    }
+}
+
+template <int PRO>
 __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstages, int act_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
@@ -67,7 +229,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
     uint64_t* empty = full + kMaxStages;
     uint64_t* red_full = empty + kMaxStages;
     uint64_t* red_empty = red_full + kRedBufs;
-    uint8_t* acts = reinterpret_cast<uint8_t*>(red_empty + kRedBufs);
+    float* tok_sx = reinterpret_cast<float*>(red_empty + kRedBufs);
+    int* tok_qsum = reinterpret_cast<int*>(tok_sx + 8);
+    uint8_t* scratch = reinterpret_cast<uint8_t*>(tok_sx) + kTokBytes;
+    uint8_t* acts = scratch + kScratchBytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = (int)a.k_tiles;
@@ -106,8 +271,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
                               a.tiles + (rt * k_tiles + kt0) * kTileBytes, bytes, &full[slot]);
                 if (++slot == nstages) { slot = 0; first_round = false; wait_parity ^= 1; }
                 if (++sk == stages_per_rt) { sk = 0; rt += gridDim.x; }
+                // once the ring is primed, let the next kernel of the stream start its own prefetch
                 if (it + 1 == nstages || it + 1 == total_iters) ptx::pdl_launch_dependents();
             }
+            if (total_iters == 0) ptx::pdl_launch_dependents();
             if (!ok) atomicExch(a.err, kErrGemvTimeout);
         }
         return;
@@ -117,22 +284,22 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
 
     if (warp == kEpilogueWarp) {
         // ---------------- epilogue warp ----------------
+        ptx::named_bar_sync(2, kMathThreads + 32);  // tok_sx / tok_qsum are ready
         const int t = lane & 3, g = lane >> 2;
         int qs[2] = {0, 0};
         float sx[2] = {0.f, 0.f};
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             const int token = 2 * t + e;
-            if (token < a.m) {
-                qs[e] = a.qsum[token];
-                if (a.epilogue != EPI_I32) sx[e] = a.sx[token];
-            }
+            if (token < a.m) { qs[e] = tok_qsum[token]; sx[e] = tok_sx[token]; }
         }
         bool ok = true;
         int rb = 0;
         uint32_t parity = 0;
         int64_t rt = blockIdx.x;
         for (int lt = 0; lt < my_rts; ++lt) {
+            float sw[2] = {0.f, 0.f};
+            if (a.epilogue != EPI_I32) { sw[0] = a.sw_tiles[2 * rt]; sw[1] = a.sw_tiles[2 * rt + 1]; }
             ok &= ptx::mbar_wait_bounded(&red_full[rb], parity);
             const int* buf = red + rb * kRedBufInts;
             int sum[4] = {0, 0, 0, 0};
@@ -142,22 +309,38 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
                 for (int j = 0; j < 4; ++j) sum[j] += buf[w * 128 + j * 32 + lane];
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&red_empty[rb]);
+            if (a.epilogue == EPI_SWIGLU) {
+                // rows 0-7 of the tile are gate rows, rows 8-15 the matching up rows
+                const int64_t col = rt * 8 + g;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int64_t row = rt * kTileRows + g + ((j & 2) ? 8 : 0);
-                const int e = j & 1, token = 2 * t + e;
-                if (token < a.m && row < a.n_out) {
-                    const int accv = sum[j] - qs[e];
-                    const float sw = a.epilogue != EPI_I32 ? a.sw_tiles[rt] : 0.0f;
-                    const int64_t o = (int64_t)token * a.out_stride + row;
-                    if (a.epilogue == EPI_I32) {
-                        reinterpret_cast<int32_t*>(a.out)[o] = accv;
-                    } else {
-                        const float y = __fmul_rn(__fmul_rn((float)accv, sw), sx[e]);
-                        if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
-                        else if (a.epilogue == EPI_F32_ACCUM)
-                            reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
-                        else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
+                for (int e = 0; e < 2; ++e) {
+                    const int token = 2 * t + e;
+                    if (token < a.m && col < a.n_out / 2) {
+                        const float gv = __fmul_rn(__fmul_rn((float)(sum[e] - qs[e]), sw[0]), sx[e]);
+                        const float uv = __fmul_rn(__fmul_rn((float)(sum[2 + e] - qs[e]), sw[1]), sx[e]);
+                        // silu(g) * u, exp in f64 rounded once (layers/swiglu.rs:31-33)
+                        const float act = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, (float)exp(-(double)gv))), uv);
+                        reinterpret_cast<float*>(a.out)[(int64_t)token * a.out_stride + col] = act;
+                        atomicMax(a.absmax_out + token, __float_as_uint(fabsf(act)));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t row = rt * kTileRows + g + ((j & 2) ? 8 : 0);
+                    const int e = j & 1, token = 2 * t + e;
+                    if (token < a.m && row < a.n_out) {
+                        const int accv = sum[j] - qs[e];
+                        const int64_t o = (int64_t)token * a.out_stride + row;
+                        if (a.epilogue == EPI_I32) {
+                            reinterpret_cast<int32_t*>(a.out)[o] = accv;
+                        } else {
+                            const float y = __fmul_rn(__fmul_rn((float)accv, sw[j >> 1]), sx[e]);
+                            if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
+                            else if (a.epilogue == EPI_F32_ACCUM)
+                                reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
+                            else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
+                        }
                     }
                 }
             }
@@ -171,28 +354,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
     // ---------------- math warps ----------------
     const int tid = threadIdx.x;
     const int g = lane >> 2, t = lane & 3;
-
-    // Stage the int8 activations: for every group of 16 consecutive inputs, byte r of word
-    // b (input 4b + r) moves to byte b of word r, and word r of the four 16-groups of a
-    // lane's 64-input chunk are stored side by side: offset = kt*256 + r*64 + t*16 + i*4.
-    {
-        const int groups = k_tiles * (kTileK / 16);
-        for (int n = 0; n < a.m; ++n) {
-            const uint4* src = reinterpret_cast<const uint4*>(a.q + (int64_t)n * a.q_stride);
-            uint8_t* dst = acts + (size_t)n * act_stride;
-            for (int j = tid; j < groups; j += kMathThreads) {
-                const uint4 v = src[j];
-                const uint32_t in[4] = {v.x, v.y, v.z, v.w};
-                uint32_t out[4];
-                ptx::transpose4x4(in, out);
-                const int kt = j >> 4, tt = (j >> 2) & 3, i = j & 3;
-                uint8_t* p = dst + kt * kTileK + tt * 16 + i * 4;
-#pragma unroll
-                for (int r = 0; r < 4; ++r) *reinterpret_cast<uint32_t*>(p + r * 64) = out[r];
-            }
-        }
-    }
-    ptx::named_bar_sync(1, kMathThreads);
+    stage_activations<PRO>(a, acts, act_stride, tok_sx, tok_qsum, scratch, tid, warp, lane, k_tiles);
+    ptx::named_bar_sync(2, kMathThreads + 32);  // activation image complete, epilogue warp may read the scales
 
     int acc[4][4];
 #pragma unroll
@@ -249,8 +412,11 @@ int g_configured[64] = {0};
 
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     if (a.m < 1 || a.m > 8) return cudaErrorInvalidValue;
+    if (a.prologue != PRO_Q8 && (a.k_in % 16 != 0)) return cudaErrorInvalidValue;
+    if (a.prologue == PRO_RMSNORM && a.k_in > 16 * 2 * kMathThreads) return cudaErrorInvalidValue;
+    if (a.epilogue == EPI_SWIGLU && (!a.absmax_out || a.n_out % 16 != 0)) return cudaErrorInvalidValue;
     const int act_stride = (int)(a.k_tiles * kTileK + 64);
-    const size_t fixed = (size_t)a.m * act_stride + kRedBytes + kBarBytes;
+    const size_t fixed = (size_t)a.m * act_stride + kRedBytes + kBarBytes + kTokBytes + kScratchBytes;
     const int stages_per_rt = (int)((a.k_tiles + kStageTiles - 1) / kStageTiles);
     // two CTAs per SM when each still gets at least 3 stages in ~110 KB
     const size_t half_budget = 110 * 1024, full_budget = 220 * 1024;
@@ -269,13 +435,17 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !g_configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)full_budget);
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_budget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_budget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_budget);
         if (e != cudaSuccess) return e;
         g_configured[dev] = 1;
     }
-    gemv_kernel<<<grid, kThreads, smem, stream>>>(a, nstages, act_stride);
-    return cudaGetLastError();
+    switch (a.prologue) {
+        case PRO_RMSNORM: return launch_pdl(gemv_kernel<PRO_RMSNORM>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
+        case PRO_ABSMAX: return launch_pdl(gemv_kernel<PRO_ABSMAX>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
+        default: return launch_pdl(gemv_kernel<PRO_Q8>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
+    }
 }
 
 cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stride,
@@ -287,26 +457,56 @@ cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stri
     const size_t elem = epilogue == EPI_BF16 ? 2 : 4;
     for (int64_t m0 = 0; m0 < m; m0 += 8) {
         for (int b = 0; b < bases; ++b) {
-            GemvArgs a;
+            GemvArgs a = {};
             a.tiles = lin.w.tiles + (size_t)b * lin.w.basis_stride();
             a.row_tiles = lin.w.row_tiles;
             a.k_tiles = lin.w.k_tiles;
             a.n_out = lin.w.n_out;
+            a.k_in = lin.w.k_in;
+            a.prologue = PRO_Q8;
             a.q = q + m0 * q_stride;
             a.q_stride = q_stride;
             a.qsum = qsum + m0;
             a.sx = sx ? sx + m0 : nullptr;
-            a.sw_tiles = lin.scale_tiles ? lin.scale_tiles + (size_t)b * lin.w.row_tiles : nullptr;
+            a.sw_tiles = lin.scale_tiles ? lin.scale_tiles + (size_t)b * lin.w.row_tiles * 2 : nullptr;
             a.m = (int)(m - m0 < 8 ? m - m0 : 8);
             a.out = reinterpret_cast<uint8_t*>(out) + (size_t)m0 * out_stride * elem;
             a.out_stride = out_stride;
             a.epilogue = (b > 0 && epilogue == EPI_F32) ? EPI_F32_ACCUM : epilogue;
             a.err = err;
+            a.pdl = false;
             cudaError_t e = launch_gemv(a, sm_count, stream);
             if (e != cudaSuccess) return e;
         }
     }
     return cudaSuccess;
+}
+
+cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m, void* out,
+                                 int64_t out_stride, int epilogue, unsigned int* absmax_out,
+                                 unsigned int* err, int sm_count, cudaStream_t stream) {
+    if (lin.w.n_bases != 1 || m < 1 || m > 8) return cudaErrorInvalidValue;
+    GemvArgs a = {};
+    a.tiles = lin.w.tiles;
+    a.row_tiles = lin.w.row_tiles;
+    a.k_tiles = lin.w.k_tiles;
+    a.n_out = lin.w.n_out;
+    a.k_in = lin.w.k_in;
+    a.prologue = in.prologue;
+    a.x = in.x;
+    a.x_stride = in.x_stride;
+    a.norm_w = in.norm_w;
+    a.eps = in.eps;
+    a.absmax_in = in.absmax_in;
+    a.absmax_out = absmax_out;
+    a.sw_tiles = lin.scale_tiles;
+    a.m = m;
+    a.out = out;
+    a.out_stride = out_stride;
+    a.epilogue = epilogue;
+    a.err = err;
+    a.pdl = true;
+    return launch_gemv(a, sm_count, stream);
 }
 
 }  // namespace bt

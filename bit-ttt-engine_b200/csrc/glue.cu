@@ -74,8 +74,13 @@ __device__ __forceinline__ int block_sum_i(int v, int* red) {
 // embedding gather: h[b, :] = table[token[b], :]   (Embedding::forward, model/llama.rs:208)
 // ---------------------------------------------------------------------------------------
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
-                             int hidden, int vocab, float* __restrict__ h) {
+                             int hidden, int vocab, float* __restrict__ h, unsigned int* __restrict__ clear,
+                             int n_clear) {
+    ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
     const int b = blockIdx.x;
+    if (b == 0)
+        for (int i = threadIdx.x; i < n_clear; i += blockDim.x) clear[i] = 0u;
     int tok = tokens[b];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
     const __nv_bfloat16* row = table + (int64_t)tok * hidden;
@@ -253,15 +258,142 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
 }
 
+
+// lm_head with the final RMSNorm folded in (every CTA normalises the hidden vector itself,
+// sum of squares in f64) and a running arg-max per CTA, so that the greedy pick does not
+// need a pass over all logits.  Ties keep the larger index (model/llama.rs:510-515).
+template <int B>
+__global__ void __launch_bounds__(256) lm_head_fused_kernel(const __nv_bfloat16* __restrict__ w,
+                                                            const float* __restrict__ h,
+                                                            const float* __restrict__ norm_w, float eps,
+                                                            int hidden, int64_t vocab, float* __restrict__ logits,
+                                                            float* __restrict__ cand_val,
+                                                            int32_t* __restrict__ cand_idx) {
+    extern __shared__ float xs[];  // [B][hidden]
+    __shared__ double red_d[32];
+    __shared__ float best_v[8][B];
+    __shared__ int best_i[8][B];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t warp_global = (int64_t)blockIdx.x * 8 + warp;
+    const int64_t warps_total = (int64_t)gridDim.x * 8;
+    // warm the first rows of this warp into L2/L1 while the previous kernel drains
+    ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
+    for (int b = 0; b < B; ++b) {
+        double ss = 0.0;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float v = h[(int64_t)b * hidden + c];
+            xs[b * hidden + c] = v;
+            ss = fma((double)v, (double)v, ss);
+        }
+        ss = block_sum_d(ss, red_d);
+        const float denom = sqrtf(__fadd_rn((float)(ss / (double)hidden), eps));
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+            xs[b * hidden + c] = __fmul_rn(__fdiv_rn(xs[b * hidden + c], denom), norm_w[c]);
+    }
+    __syncthreads();
+    float bv[B];
+    int bi[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) { bv[b] = -INFINITY; bi[b] = -1; }
+    for (int64_t v = warp_global; v < vocab; v += warps_total) {
+        const uint4* wr = reinterpret_cast<const uint4*>(w + v * hidden);
+        float acc[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) acc[b] = 0.0f;
+#pragma unroll 4
+        for (int c8 = lane; c8 < hidden / 8; c8 += 32) {
+            const uint4 pk = wr[c8];
+            const uint32_t u[4] = {pk.x, pk.y, pk.z, pk.w};
+            float wf[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                wf[2 * j] = __uint_as_float(u[j] << 16);
+                wf[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+            }
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                const float4 x0 = *reinterpret_cast<const float4*>(xs + b * hidden + c8 * 8);
+                const float4 x1 = *reinterpret_cast<const float4*>(xs + b * hidden + c8 * 8 + 4);
+                acc[b] = fmaf(wf[0], x0.x, acc[b]);
+                acc[b] = fmaf(wf[1], x0.y, acc[b]);
+                acc[b] = fmaf(wf[2], x0.z, acc[b]);
+                acc[b] = fmaf(wf[3], x0.w, acc[b]);
+                acc[b] = fmaf(wf[4], x1.x, acc[b]);
+                acc[b] = fmaf(wf[5], x1.y, acc[b]);
+                acc[b] = fmaf(wf[6], x1.z, acc[b]);
+                acc[b] = fmaf(wf[7], x1.w, acc[b]);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const float r = warp_sum(acc[b]);
+            if (lane == 0) logits[(int64_t)b * vocab + v] = r;
+            if (r >= bv[b]) { bv[b] = r; bi[b] = (int)v; }  // v increases: ties keep the later index
+        }
+    }
+    if (lane == 0)
+#pragma unroll
+        for (int b = 0; b < B; ++b) { best_v[warp][b] = bv[b]; best_i[warp][b] = bi[b]; }
+    __syncthreads();
+    if (threadIdx.x < B) {
+        const int b = threadIdx.x;
+        float v = -INFINITY;
+        int i = -1;
+        for (int wv = 0; wv < 8; ++wv) {
+            const float ov = best_v[wv][b];
+            const int oi = best_i[wv][b];
+            if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi > i))) { v = ov; i = oi; }
+        }
+        cand_val[(int64_t)b * gridDim.x + blockIdx.x] = v;
+        cand_idx[(int64_t)b * gridDim.x + blockIdx.x] = i;
+    }
+}
+
+__global__ void __launch_bounds__(256) pick_kernel(const float* __restrict__ cand_val,
+                                                   const int32_t* __restrict__ cand_idx, int n_cand,
+                                                   int32_t* __restrict__ out, int32_t* __restrict__ pos, int n_pos) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
+    const int b = blockIdx.x;
+    float v = -INFINITY;
+    int i = -1;
+    for (int c = threadIdx.x; c < n_cand; c += blockDim.x) {
+        const float ov = cand_val[(int64_t)b * n_cand + c];
+        const int oi = cand_idx[(int64_t)b * n_cand + c];
+        if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi > i))) { v = ov; i = oi; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi > i))) { v = ov; i = oi; }
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) { sv[w] = v; si[w] = i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 1; k < 8; ++k) {
+            const float ov = sv[k];
+            const int oi = si[k];
+            if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi > i))) { v = ov; i = oi; }
+        }
+        out[b] = i;
+    }
+    if (b == 0 && threadIdx.x < n_pos) pos[threadIdx.x] += 1;  // BitLlama::current_pos += 1, model/llama.rs:269
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------------------
 cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int batch, int hidden,
-                         int vocab, float* h, cudaStream_t stream) {
-    embed_kernel<<<batch, 256, 0, stream>>>(tokens, table, hidden, vocab, h);
-    return cudaGetLastError();
+                         int vocab, float* h, cudaStream_t stream, unsigned int* clear, int n_clear, bool pdl) {
+    return launch_pdl(embed_kernel, dim3(batch), dim3(256), 0, stream, pdl, tokens, table, hidden, vocab, h, clear,
+                      n_clear);
 }
 
 cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
@@ -324,6 +456,56 @@ cudaError_t launch_lm_head(const __nv_bfloat16* w, const float* x, int batch, in
 cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream) {
     argmax_kernel<<<batch, 1024, 0, stream>>>(logits, vocab, vocab, out);
     return cudaGetLastError();
+}
+
+int lm_head_max_candidates(int sm_count) { return sm_count * 4; }
+
+template <int B>
+static cudaError_t launch_lm_head_fused_b(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
+                                          int hidden, int64_t vocab, float* logits, float* cand_val,
+                                          int32_t* cand_idx, int grid, cudaStream_t stream, bool pdl) {
+    const size_t smem = (size_t)B * hidden * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(lm_head_fused_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        configured = true;
+    }
+    if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+    return launch_pdl(lm_head_fused_kernel<B>, dim3(grid), dim3(256), smem, stream, pdl, w, h, norm_w, eps, hidden,
+                      vocab, logits, cand_val, cand_idx);
+}
+
+cudaError_t launch_lm_head_fused(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
+                                 int batch, int hidden, int64_t vocab, float* logits, float* cand_val,
+                                 int32_t* cand_idx, int* n_cand, int sm_count, cudaStream_t stream, bool pdl) {
+    if (hidden % 8 != 0 || batch < 1) return cudaErrorInvalidValue;
+    // one grid size for every group of 4 tokens, so that the candidate rows share a stride
+    const size_t smem_max = (size_t)(batch < 4 ? batch : 4) * hidden * sizeof(float);
+    int per_sm = (int)((200 * 1024) / (smem_max + 2048));
+    per_sm = per_sm > 4 ? 4 : (per_sm < 1 ? 1 : per_sm);
+    const int grid = sm_count * per_sm;
+    *n_cand = grid;
+    for (int b0 = 0; b0 < batch; b0 += 4) {
+        const int bc = batch - b0 < 4 ? batch - b0 : 4;
+        const float* hb = h + (size_t)b0 * hidden;
+        float* lb = logits + (size_t)b0 * vocab;
+        float* cv = cand_val + (size_t)b0 * grid;
+        int32_t* ci = cand_idx + (size_t)b0 * grid;
+        cudaError_t e;
+        switch (bc) {
+            case 1: e = launch_lm_head_fused_b<1>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            case 2: e = launch_lm_head_fused_b<2>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            case 3: e = launch_lm_head_fused_b<3>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            default: e = launch_lm_head_fused_b<4>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+        }
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_pick(const float* cand_val, const int32_t* cand_idx, int n_cand, int batch, int32_t* out,
+                        int32_t* pos, int n_pos, cudaStream_t stream, bool pdl) {
+    return launch_pdl(pick_kernel, dim3(batch), dim3(256), 0, stream, pdl, cand_val, cand_idx, n_cand, out, pos, n_pos);
 }
 
 }  // namespace bt

@@ -39,7 +39,8 @@ struct Layer {
     HostLinear host[9];
     bt_linear* qkv = nullptr;
     bt_linear* o = nullptr;
-    bt_linear* gate_up = nullptr;
+    bt_linear* gate_up = nullptr;      // [gate; up] stacked (batches above 8)
+    bt_linear* gate_up_il = nullptr;   // gate/up interleaved by 8 rows (fused SwiGLU epilogue)
     bt_linear* down = nullptr;
     bt_linear* ttt_down = nullptr;
     bt_linear* ttt_up = nullptr;
@@ -79,6 +80,10 @@ struct bt_model {
     float* logits = nullptr;
     int32_t* next = nullptr;
     double* attn_partial = nullptr;
+    float* act = nullptr;            // [max_batch, intermediate] silu(gate)*up
+    unsigned int* absmax = nullptr;  // [num_layers][2][max_batch] max|x| cells of the fused path
+    float* cand_val = nullptr;
+    int32_t* cand_idx = nullptr;
     int32_t* tokens_pinned = nullptr;
     int32_t* next_pinned = nullptr;
     int host_pos = 0;
@@ -112,7 +117,57 @@ bt_status make_linear(bt_model* m, HostLinear** parts, int n_parts, bt_linear** 
     return BT_OK;
 }
 
-// Enqueues one decode step for `batch` sequences on `s`.
+// One decode step for up to 8 sequences with the quantisers folded into the product
+// kernels and every launch allowed to start early (programmatic dependent launch):
+// per block  [norm1+quant+q|k|v]  [attention]  [combine]  [quant+o_proj+residual]
+//            [norm2+quant+gate|up+SiLU*up]  [quant+down+residual].
+bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
+    const bt_model_config& c = m->cfg;
+    const int H = c.hidden_dim, I = c.intermediate_dim, B = c.max_batch;
+    unsigned int* err = device_error_word(m->device);
+    const int sm = m->sm_count;
+    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, true));
+    for (int li = 0; li < c.num_layers; ++li) {
+        Layer& L = m->layers[(size_t)li];
+        unsigned int* amax_core = m->absmax + ((size_t)li * 2 + 0) * B;
+        unsigned int* amax_mlp = m->absmax + ((size_t)li * 2 + 1) * B;
+        FusedIn norm1{PRO_RMSNORM, m->h, H, L.norm1, kRmsEps, nullptr};
+        if (c.arch == 0) {
+            BT_CUDA_TRY(linear_product_fused(L.ttt_down->dev(), norm1, batch, m->feat, m->d_small, EPI_F32, nullptr, err, sm, s));
+            BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s, amax_core, true));
+            FusedIn zin{PRO_ABSMAX, m->z, m->d_small, nullptr, 0.f, amax_core};
+            BT_CUDA_TRY(linear_product_fused(L.ttt_up->dev(), zin, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
+        } else {
+            BT_CUDA_TRY(linear_product_fused(L.qkv->dev(), norm1, batch, m->qkv, m->qkv_dim, EPI_F32, nullptr, err, sm, s));
+            AttnArgs a;
+            a.qkv = m->qkv;
+            a.cache = L.kv->view;
+            a.pos = m->pos;
+            a.inv_freq = m->inv_freq;
+            a.out = m->att;
+            a.partial = m->attn_partial;
+            a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
+            a.splits = attn_splits(batch, c.n_kv_heads, c.max_position_embeddings, sm);
+            a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
+            a.absmax_out = amax_core;
+            a.pdl = true;
+            BT_CUDA_TRY(launch_attn_decode(a, s));
+            FusedIn ain{PRO_ABSMAX, m->att, H, nullptr, 0.f, amax_core};
+            BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
+        }
+        FusedIn norm2{PRO_RMSNORM, m->h, H, L.norm2, kRmsEps, nullptr};
+        BT_CUDA_TRY(linear_product_fused(L.gate_up_il->dev(), norm2, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, sm, s));
+        FusedIn din{PRO_ABSMAX, m->act, I, nullptr, 0.f, amax_mlp};
+        BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
+    }
+    int n_cand = 0;
+    BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
+                                     m->cand_val, m->cand_idx, &n_cand, sm, s, true));
+    BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, true));
+    return BT_OK;
+}
+
+// Enqueues one decode step for `batch` sequences on `s` (separate quantiser kernels; any batch).
 bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     const bt_model_config& c = m->cfg;
     const int H = c.hidden_dim, I = c.intermediate_dim;
@@ -142,6 +197,8 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
             a.splits = attn_splits(batch, c.n_kv_heads, c.max_position_embeddings, sm);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
+            a.absmax_out = nullptr;
+            a.pdl = false;
             BT_CUDA_TRY(launch_attn_decode(a, s));
             BT_CUDA_TRY(launch_row_quant(PRE_NONE, m->att, H, nullptr, 0.f, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
             BT_CUDA_TRY(linear_product(L.o->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
@@ -287,7 +344,16 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
             BT_CUDA_TRY(dev_alloc(&L.w_state, (size_t)B * m->d_small * m->d_small));
         }
         HostLinear* gu[2] = {&L.host[BT_W_GATE], &L.host[BT_W_UP]};
-        if ((st = make_linear(m, gu, 2, &L.gate_up)) != BT_OK) return st;
+        if (!gu[0]->set || !gu[1]->set) return set_error(BT_ERR_ARG, "bt_model_finalize: a projection weight was never set");
+        if ((st = create_gate_up(&L.gate_up_il, gu[0]->packed.data(), gu[1]->packed.data(), gu[0]->n_out, gu[0]->k_in,
+                                 gu[0]->scale, gu[1]->scale, m->device)) != BT_OK) return st;
+        m->ternary_bytes += L.gate_up_il->w.basis_stride();
+        if (B > 8) {
+            if ((st = make_linear(m, gu, 2, &L.gate_up)) != BT_OK) return st;
+            m->ternary_bytes -= L.gate_up->w.basis_stride();  // alternative copy, not streamed in the same step
+        } else {
+            for (HostLinear* hl : gu) { hl->packed.clear(); hl->packed.shrink_to_fit(); }
+        }
         HostLinear* dn[1] = {&L.host[BT_W_DOWN]};
         if ((st = make_linear(m, dn, 1, &L.down)) != BT_OK) return st;
     }
@@ -301,6 +367,11 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
     BT_CUDA_TRY(dev_alloc(&m->qsum, (size_t)B));
     BT_CUDA_TRY(dev_alloc(&m->gu, (size_t)B * 2 * I));
     BT_CUDA_TRY(dev_alloc(&m->xn, (size_t)B * H));
+    BT_CUDA_TRY(dev_alloc(&m->act, (size_t)B * I));
+    BT_CUDA_TRY(dev_alloc(&m->absmax, (size_t)c.num_layers * 2 * B));
+    BT_CUDA_TRY(cudaMemset(m->absmax, 0, (size_t)c.num_layers * 2 * B * sizeof(unsigned int)));
+    BT_CUDA_TRY(dev_alloc(&m->cand_val, (size_t)B * lm_head_max_candidates(m->sm_count)));
+    BT_CUDA_TRY(dev_alloc(&m->cand_idx, (size_t)B * lm_head_max_candidates(m->sm_count)));
     BT_CUDA_TRY(dev_alloc(&m->logits, (size_t)B * c.vocab_size));
     BT_CUDA_TRY(dev_alloc(&m->next, (size_t)B));
     if (c.arch == 1) {
@@ -326,13 +397,13 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
     cudaDeviceSynchronize();
     for (auto& g : m->graphs) if (g) cudaGraphExecDestroy(g);
     for (auto& L : m->layers) {
-        bt_linear_destroy(L.qkv); bt_linear_destroy(L.o); bt_linear_destroy(L.gate_up); bt_linear_destroy(L.down);
+        bt_linear_destroy(L.qkv); bt_linear_destroy(L.o); bt_linear_destroy(L.gate_up); bt_linear_destroy(L.gate_up_il); bt_linear_destroy(L.down);
         bt_linear_destroy(L.ttt_down); bt_linear_destroy(L.ttt_up);
         bt_kv_destroy(L.kv);
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx};
     for (void* p : bufs) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
@@ -365,7 +436,7 @@ bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
     cudaGraphExec_t& exec = m->graphs[batch];
     const uintptr_t marker = 1;  // "ran eagerly once" sentinel stored in the table
     if (exec == nullptr) {
-        bt_status st = enqueue_step(m, batch, s);
+        bt_status st = batch <= 8 ? enqueue_step_fused(m, batch, s) : enqueue_step(m, batch, s);
         if (st != BT_OK) return st;
         exec = reinterpret_cast<cudaGraphExec_t>(marker);
     } else if (exec == reinterpret_cast<cudaGraphExec_t>(marker)) {
@@ -374,7 +445,7 @@ bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
         // launched on the caller's
         cudaStream_t cs = m->stream;
         BT_CUDA_TRY(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
-        bt_status st = enqueue_step(m, batch, cs);
+        bt_status st = batch <= 8 ? enqueue_step_fused(m, batch, cs) : enqueue_step(m, batch, cs);
         cudaError_t e = cudaStreamEndCapture(cs, &graph);
         if (st != BT_OK) { if (graph) cudaGraphDestroy(graph); return st; }
         if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
@@ -443,7 +514,8 @@ extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, void* str
     int launches = 0;
     // outputs go to the gate/up buffer (the largest activation buffer), never to h
     for (auto& L : m->layers) {
-        bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up, L.gate_up, L.down};
+        bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up,
+                             (batch <= 8 || !L.gate_up) ? L.gate_up_il : L.gate_up, L.down};
         for (bt_linear* lin : seq) {
             BT_CUDA_TRY(linear_product(lin->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, lin->w.n_out,
                                        EPI_F32, err, m->sm_count, s));
@@ -456,8 +528,13 @@ extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, void* str
 
 extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
     if (!m) return 0;
+    if (batch <= 8) {
+        // fused path: per layer 4 products + attention pair or TTT update; embedding, lm_head per 4 tokens, pick
+        const int per_layer = 4 + (m->cfg.arch == 1 ? 2 : 1);
+        return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
+    }
     const int groups = (batch + 7) / 8;
-    // per layer: 4 quantiser launches, 4 ternary products, attention (2) or TTT update (1)
+    // per layer: 4 quantiser launches, 4 ternary products per 8 tokens, attention (2) or TTT update (1)
     const int per_layer = 4 + 4 * groups + (m->cfg.arch == 1 ? 2 : 1);
     // embedding, final norm, lm_head (4 tokens per launch), arg-max, position advance
     return m->cfg.num_layers * per_layer + 1 + 1 + (batch + 3) / 4 + 1 + 1;

@@ -146,6 +146,8 @@ extern "C" bt_status bt_attn_decode(bt_kv_cache* c, const float* qkv_dev, const 
     a.batch = (int)batch; a.n_heads = (int)n_heads; a.n_kv = (int)c->n_kv; a.head_dim = (int)c->head_dim;
     a.splits = attn_splits(batch, c->n_kv, c->max_seq, device_sm_count(c->device));
     a.scaling = (float)(1.0 / sqrt((double)c->head_dim));  // layers/attention.rs:114
+    a.absmax_out = nullptr;
+    a.pdl = false;
     BT_CUDA_TRY(launch_attn_decode(a, reinterpret_cast<cudaStream_t>(stream)));
     return BT_OK;
 }

@@ -28,10 +28,12 @@ template <int PL>
 __global__ void __launch_bounds__(kTttWarps * 32) ttt_chunk_kernel(float* __restrict__ w,
                                                                   const float* __restrict__ feats,
                                                                   int t_len, int d, float lr, int chunk,
-                                                                  float* __restrict__ z_out) {
+                                                                  float* __restrict__ z_out,
+                                                                  unsigned int* __restrict__ absmax_out) {
     extern __shared__ float xh[];  // [chunk][d] normalised features of the current chunk
     __shared__ float inv_norm[kMaxChunk];
     ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
     const int b = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a = blockIdx.y * kTttWarps + warp;  // row of W owned by this warp
@@ -77,7 +79,10 @@ __global__ void __launch_bounds__(kTttWarps * 32) ttt_chunk_kernel(float* __rest
                     if (c < d) sd = fma((double)wr[j], (double)xt[c], sd);
                 }
                 const float s = (float)warp_sum(sd);
-                if (lane == 0) zb[(int64_t)(start + t) * d + a] = s;
+                if (lane == 0) {
+                    zb[(int64_t)(start + t) * d + a] = s;
+                    if (absmax_out) atomicMax(absmax_out + b, __float_as_uint(fabsf(s)));
+                }
                 const float diff = __fsub_rn(s, xt[a]);
 #pragma unroll
                 for (int j = 0; j < PL; ++j) {
@@ -100,36 +105,35 @@ __global__ void __launch_bounds__(kTttWarps * 32) ttt_chunk_kernel(float* __rest
 
 template <int PL>
 cudaError_t launch_pl(float* w, const float* feats, int batch, int t_len, int d, float lr, int chunk,
-                      float* z_out, cudaStream_t stream) {
+                      float* z_out, cudaStream_t stream, unsigned int* absmax_out, bool pdl) {
     const size_t smem = (size_t)chunk * d * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(ttt_chunk_kernel<PL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
     dim3 grid(batch, (d + kTttWarps - 1) / kTttWarps);
-    ttt_chunk_kernel<PL><<<grid, kTttWarps * 32, smem, stream>>>(w, feats, t_len, d, lr, chunk, z_out);
-    return cudaGetLastError();
+    return launch_pdl(ttt_chunk_kernel<PL>, grid, dim3(kTttWarps * 32), smem, stream, pdl, w, feats, t_len, d, lr, chunk, z_out, absmax_out);
 }
 
 }  // namespace
 
 cudaError_t launch_ttt_chunk(float* w, const float* feats, int batch, int t_len, int d, float lr, int chunk,
-                             float* z_out, cudaStream_t stream) {
+                             float* z_out, cudaStream_t stream, unsigned int* absmax_out, bool pdl) {
     if (d < 1 || d > 1024 || chunk < 1 || chunk > kMaxChunk || (size_t)chunk * d * 4 > 200 * 1024)
         return cudaErrorInvalidValue;
     if (batch <= 0 || t_len <= 0) return cudaSuccess;
     const int pl = (d + 31) / 32;
-    if (pl <= 1) return launch_pl<1>(w, feats, batch, t_len, d, lr, chunk, z_out, stream);
-    if (pl <= 2) return launch_pl<2>(w, feats, batch, t_len, d, lr, chunk, z_out, stream);
-    if (pl <= 4) return launch_pl<4>(w, feats, batch, t_len, d, lr, chunk, z_out, stream);
-    if (pl <= 8) return launch_pl<8>(w, feats, batch, t_len, d, lr, chunk, z_out, stream);
-    if (pl <= 16) return launch_pl<16>(w, feats, batch, t_len, d, lr, chunk, z_out, stream);
-    return launch_pl<32>(w, feats, batch, t_len, d, lr, chunk, z_out, stream);
+    if (pl <= 1) return launch_pl<1>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
+    if (pl <= 2) return launch_pl<2>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
+    if (pl <= 4) return launch_pl<4>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
+    if (pl <= 8) return launch_pl<8>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
+    if (pl <= 16) return launch_pl<16>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
+    return launch_pl<32>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
 }
 
 cudaError_t launch_ttt_step(float* w, const float* feat, int batch, int d, float lr, float* z_out,
-                            cudaStream_t stream) {
-    return launch_ttt_chunk(w, feat, batch, 1, d, lr, 1, z_out, stream);
+                            cudaStream_t stream, unsigned int* absmax_out, bool pdl) {
+    return launch_ttt_chunk(w, feat, batch, 1, d, lr, 1, z_out, stream, absmax_out, pdl);
 }
 
 }  // namespace bt
