@@ -1,4 +1,4 @@
-// Per-token absmax int8 activation quantiser: s = max|x|/127, q = clamp(round(x/s)),
+// Per-token absmax int8 activation quantiser: s = max|x|/127, q = clamp(round(x*(127/max|x|))),
 // round half away from zero, s == 0 -> q = 0.  The reference has no such kernel; the
 // definition follows its Q8 KV-cache quantiser (layers/kv_cache.rs:95-119) without the
 // zero point.  One CTA per token; x is read twice (the second pass hits L2).
@@ -39,9 +39,9 @@ __device__ __forceinline__ int block_sum_i32(int v, int* red) {
     return r;
 }
 
-__device__ __forceinline__ int quant_one(float x, float s) {
-    // true IEEE division and round-half-away, so the CPU restatement reproduces every q
-    float r = roundf(__fdiv_rn(x, s));
+__device__ __forceinline__ int quant_one(float x, float inv) {
+    // one f32 multiply by 127/amax and round-half-away, so the CPU restatement reproduces every q
+    float r = roundf(__fmul_rn(x, inv));
     r = fminf(fmaxf(r, -127.0f), 127.0f);
     return (int)r;
 }
@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
     for (int64_t c = threadIdx.x; c < k; c += blockDim.x) amax = fmaxf(amax, fabsf(to_f32(xr[c])));
     amax = block_max(amax, red_f);
     const float s = __fdiv_rn(amax, 127.0f);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
 
     int local = 0;
     // four outputs per thread per step so that the int8 stores are 32-bit
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int64_t cc = c + j;
-            v[j] = (cc < k && s > 0.0f) ? quant_one(to_f32(xr[cc]), s) : 0;
+            v[j] = (cc < k && amax > 0.0f) ? quant_one(to_f32(xr[cc]), inv) : 0;
             local += v[j];
         }
         if (c + 3 < q_stride && ((q_stride & 3) == 0)) {

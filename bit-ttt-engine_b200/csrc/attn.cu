@@ -40,12 +40,19 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
     if (lane == 0) *s_out = s;
 }
 
+// One CTA = one (sequence, KV head, span of positions).  Each warp takes chunks of 32
+// positions: (A) lane j dots key row j with the NREP query heads (no cross-lane traffic),
+// (B) the chunk's softmax weights are formed with one exp per lane and head, (C) the lanes
+// switch to owning head dimensions and accumulate P.V with the weights broadcast by
+// shuffle.  Everything between the u8 loads and the final rounding is f64, so the result
+// does not depend on how positions are split over lanes, warps and CTAs.
 template <int PER_LANE, int NREP>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
-    __shared__ float qs[NREP * 128];
+    constexpr int HD = 32 * PER_LANE;
+    __shared__ double qs[NREP][HD];
     __shared__ float knew[128], vnew[128];
     __shared__ double red_m[kAttnWarps][NREP], red_l[kAttnWarps][NREP];
-    __shared__ double red_acc[kAttnWarps][NREP][32 * PER_LANE];
+    __shared__ double red_acc[kAttnWarps][NREP][HD];
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
 
@@ -55,11 +62,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p = a.pos[b];
     const int t_len = p + 1;
-    const int chunk = (t_len + a.splits - 1) / a.splits;
-    const int t0 = split * chunk;
-    const int t1 = min(t_len, t0 + chunk);
+    const int t0 = split * a.span;
+    const int t1 = min(t_len, t0 + a.span);
     const int64_t qkv_stride = (int64_t)(a.n_heads + 2 * a.n_kv) * hd;
     const float* qkv = a.qkv + b * qkv_stride;
+    double* part_base = a.partial + (((int64_t)b * a.n_heads + kvh * NREP) * a.splits + split) * (hd + 2);
+    if (t0 >= t_len) {
+        // nothing in this span yet: leave an empty partial (max = -inf, sum = 0)
+        for (int h = threadIdx.x; h < NREP; h += blockDim.x) {
+            double* dst = part_base + (int64_t)h * a.splits * (hd + 2);
+            dst[0] = -INFINITY;
+            dst[1] = 0.0;
+        }
+        return;
+    }
     const float fp = (float)p;
 
     // rotate the NREP query heads of this KV group (cos/sin evaluated in f64, rounded once)
@@ -69,11 +85,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         const float cs = (float)cos((double)fr), sn = (float)sin((double)fr);
         const float* qh = qkv + (int64_t)(kvh * NREP + h) * hd;
         const float x1 = qh[c], x2 = qh[half + c];
-        qs[h * hd + c] = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
-        qs[h * hd + half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
+        qs[h][c] = (double)__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+        qs[h][half + c] = (double)__fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
     }
     const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
-    // the CTA whose range holds position p appends the new key / value first
+    // the CTA whose span holds position p appends the new key / value first
     const bool owner = (p >= t0 && p < t1);
     if (owner) {
         const float* kh = qkv + (int64_t)(a.n_heads + kvh) * hd;
@@ -94,47 +110,81 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     }
     __syncthreads();  // the block's own global writes are visible to it after the barrier
 
-    // Scores, softmax weights and the weighted sum are carried in f64 and rounded to f32
-    // once at the end, so that the result does not depend on how positions are split over
-    // warps and CTAs.
     double m_run[NREP], l_run[NREP], acc[NREP][PER_LANE];
-    float qreg[NREP][PER_LANE];
 #pragma unroll
     for (int h = 0; h < NREP; ++h) {
         m_run[h] = -INFINITY;
         l_run[h] = 0.0;
 #pragma unroll
-        for (int j = 0; j < PER_LANE; ++j) {
-            acc[h][j] = 0.0;
-            qreg[h][j] = (lane * PER_LANE + j < hd) ? qs[h * hd + lane * PER_LANE + j] : 0.0f;
-        }
+        for (int j = 0; j < PER_LANE; ++j) acc[h][j] = 0.0;
     }
 
-    for (int t = t0 + warp; t < t1; t += kAttnWarps) {
-        const uint8_t* kr = a.cache.k_q + (row_base + t) * hd + lane * PER_LANE;
-        const uint8_t* vr = a.cache.v_q + (row_base + t) * hd + lane * PER_LANE;
-        float kf[PER_LANE], vf[PER_LANE];
-        const float ks = a.cache.k_s[row_base + t], vs = a.cache.v_s[row_base + t];
+    for (int tb = t0 + warp * 32; tb < t1; tb += kAttnWarps * 32) {
+        // (A) scores of position tb + lane against the NREP heads
+        const int t = tb + lane;
+        const bool valid = t < t1;
+        double sc[NREP];
 #pragma unroll
-        for (int j = 0; j < PER_LANE; ++j) {
-            kf[j] = __fmul_rn((float)kr[j] - 128.0f, ks);   // dequantize_q8, kv_cache.rs:122-128
-            vf[j] = __fmul_rn((float)vr[j] - 128.0f, vs);
+        for (int h = 0; h < NREP; ++h) sc[h] = 0.0;
+        if (valid) {
+            const uint4* kr = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + t) * hd);
+            const float ks = a.cache.k_s[row_base + t];
+#pragma unroll
+            for (int c16 = 0; c16 < HD / 16; ++c16) {
+                const uint4 pk = kr[c16];
+                const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+                    for (int bi = 0; bi < 4; ++bi) {
+                        const int c = c16 * 16 + wi * 4 + bi;
+                        // dequantize_q8, kv_cache.rs:122-128: (f32(q) - 128) * s
+                        const double kf = (double)__fmul_rn((float)((wds[wi] >> (8 * bi)) & 0xffu) - 128.0f, ks);
+#pragma unroll
+                        for (int h = 0; h < NREP; ++h) sc[h] = fma(qs[h][c], kf, sc[h]);
+                    }
+                }
+            }
         }
+        // (B) softmax weights of the chunk: (q.k) * 1/sqrt(hd) in f32 (attention.rs:202), then f64
+        double pw[NREP];
 #pragma unroll
         for (int h = 0; h < NREP; ++h) {
-            double d = 0.0;
+            const double s_h = valid ? (double)__fmul_rn((float)sc[h], a.scaling) : -INFINITY;
+            double cmax = s_h;
 #pragma unroll
-            for (int j = 0; j < PER_LANE; ++j) d = fma((double)qreg[h][j], (double)kf[j], d);
+            for (int o = 16; o > 0; o >>= 1) cmax = fmax(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
+            const double m_new = fmax(m_run[h], cmax);
+            const double corr = exp(m_run[h] - m_new);  // exp(-inf) = 0 on the first chunk
+            pw[h] = valid ? exp(s_h - m_new) : 0.0;
+            double psum = pw[h];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-            const double sc = (double)__fmul_rn((float)d, a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
-            const double m_new = fmax(m_run[h], sc);
-            const double corr = exp(m_run[h] - m_new);  // exp(-inf) = 0 on the first key
-            const double pe = exp(sc - m_new);
-            l_run[h] = fma(l_run[h], corr, pe);
+            for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+            l_run[h] = fma(l_run[h], corr, psum);
 #pragma unroll
-            for (int j = 0; j < PER_LANE; ++j) acc[h][j] = fma(acc[h][j], corr, pe * (double)vf[j]);
+            for (int j = 0; j < PER_LANE; ++j) acc[h][j] *= corr;
             m_run[h] = m_new;
+        }
+        // (C) acc[h][dims of this lane] += sum_j p_j[h] * v_j[dims]
+        const int n_here = min(32, t1 - tb);
+        for (int j = 0; j < n_here; ++j) {
+            const uint8_t* vr = a.cache.v_q + (row_base + tb + j) * hd + lane * PER_LANE;
+            const float vs = a.cache.v_s[row_base + tb + j];
+            double vf[PER_LANE];
+            if (PER_LANE == 4) {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(vr);
+#pragma unroll
+                for (int d = 0; d < PER_LANE; ++d) vf[d] = (double)__fmul_rn((float)((w >> (8 * d)) & 0xffu) - 128.0f, vs);
+            } else {
+#pragma unroll
+                for (int d = 0; d < PER_LANE; ++d) vf[d] = (double)__fmul_rn((float)vr[d] - 128.0f, vs);
+            }
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) {
+                const double pj = __shfl_sync(0xffffffffu, pw[h], j);
+#pragma unroll
+                for (int d = 0; d < PER_LANE; ++d) acc[h][d] = fma(pj, vf[d], acc[h][d]);
+            }
         }
     }
     // combine the warps of this CTA
@@ -153,12 +203,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         double l = 0.0, v = 0.0;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
-            const double sc = red_m[w][h] == -INFINITY ? 0.0 : exp(red_m[w][h] - m);
-            l = fma(red_l[w][h], sc, l);
-            v = fma(red_acc[w][h][c], sc, v);
+            const double scw = red_m[w][h] == -INFINITY ? 0.0 : exp(red_m[w][h] - m);
+            l = fma(red_l[w][h], scw, l);
+            v = fma(red_acc[w][h][c], scw, v);
         }
-        const int head = kvh * NREP + h;
-        double* dst = a.partial + (((int64_t)b * a.n_heads + head) * a.splits + split) * (hd + 2);
+        double* dst = part_base + (int64_t)h * a.splits * (hd + 2);
         dst[2 + c] = v;
         if (c == 0) { dst[0] = m; dst[1] = l; }
     }
@@ -177,7 +226,8 @@ __global__ void attn_combine_kernel(AttnArgs a) {
         double l = 0.0, v = 0.0;
         for (int s = 0; s < a.splits; ++s) {
             const double ms = base[s * (hd + 2)];
-            const double sc = ms == -INFINITY ? 0.0 : exp(ms - m);
+            if (ms == -INFINITY) continue;  // span without positions yet
+            const double sc = exp(ms - m);
             l = fma(base[s * (hd + 2) + 1], sc, l);
             v = fma(base[s * (hd + 2) + 2 + c], sc, v);
         }

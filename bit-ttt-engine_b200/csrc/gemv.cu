@@ -99,9 +99,9 @@ __device__ __forceinline__ int math_sum_i(int v, int* slot, int warp, int lane) 
     return r;
 }
 
-// Quantise 16 consecutive values (group j of a token) with scale s, store them
+// Quantise 16 consecutive values (group j of a token) with multiplier inv = 127/max|x|, store them
 // byte-transposed at their place in the activation image, return their sum.
-__device__ __forceinline__ int quant_store_group(const float (&v)[16], float s, uint8_t* dst_token, int j) {
+__device__ __forceinline__ int quant_store_group(const float (&v)[16], float inv, uint8_t* dst_token, int j) {
     uint32_t in[4], out[4];
     int sum = 0;
 #pragma unroll
@@ -109,12 +109,9 @@ __device__ __forceinline__ int quant_store_group(const float (&v)[16], float s, 
         uint32_t word = 0;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            int qv = 0;
-            if (s > 0.0f) {
-                float rr = roundf(__fdiv_rn(v[4 * b + r], s));
-                rr = fminf(fmaxf(rr, -127.0f), 127.0f);
-                qv = (int)rr;
-            }
+            float rr = roundf(__fmul_rn(v[4 * b + r], inv));
+            rr = fminf(fmaxf(rr, -127.0f), 127.0f);
+            const int qv = (int)rr;
             sum += qv;
             word |= (uint32_t)(qv & 0xff) << (8 * r);
         }
@@ -197,14 +194,17 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
                 for (int e = 0; e < 16; ++e) { v1[e] = __fmul_rn(__fdiv_rn(v1[e], denom), w[e]); amax = fmaxf(amax, fabsf(v1[e])); } }
             amax = math_max_f(amax, sl_f, warp, lane);
             s = __fdiv_rn(amax, 127.0f);
-            if (h0) local += quant_store_group(v0, s, dst, j0);
-            if (h1) local += quant_store_group(v1, s, dst, j1);
+            const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+            if (h0) local += quant_store_group(v0, inv, dst, j0);
+            if (h1) local += quant_store_group(v1, inv, dst, j1);
             for (int j = groups + tid; j < groups_pad; j += kMathThreads) {
                 const float z[16] = {0};
                 quant_store_group(z, 0.0f, dst, j);
             }
         } else {  // PRO_ABSMAX
-            s = __fdiv_rn(__uint_as_float(a.absmax_in[n]), 127.0f);
+            const float amax = __uint_as_float(a.absmax_in[n]);
+            s = __fdiv_rn(amax, 127.0f);
+            const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
             for (int j = tid; j < groups_pad; j += kMathThreads) {
                 float v[16];
                 if (j < groups) load16(xr + 16 * j, v);
@@ -212,7 +212,7 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
 #pragma unroll
                     for (int e = 0; e < 16; ++e) v[e] = 0.0f;
                 }
-                local += quant_store_group(v, s, dst, j);
+                local += quant_store_group(v, inv, dst, j);
             }
         }
         const int total = math_sum_i(local, sl_i + 8 * (n & 1), warp, lane);

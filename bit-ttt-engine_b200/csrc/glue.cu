@@ -93,7 +93,7 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const __nv_bflo
 //   PRE_NONE   : v = x
 //   PRE_RMSNORM: v = (x / sqrt(mean(x^2) + eps)) * w        (layers/rms_norm.rs:40-55)
 //   PRE_SWIGLU : v = silu(gate) * up, x = [gate | up]        (layers/swiglu.rs:31-33)
-// then s = max|v|/127, q = clamp(round(v/s)), sum_k q.  `v_out` (optional) receives v.
+// then s = max|v|/127, q = clamp(round(v * (127/max|v|))), sum_k q.  `v_out` (optional) receives v.
 // ---------------------------------------------------------------------------------------
 template <int PRE>
 __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict__ x, int64_t x_stride,
@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
     }
     amax = block_max(amax, red_f);  // also orders the row[] writes before the reads below
     const float s = __fdiv_rn(amax, 127.0f);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     int8_t* qr = q + (int64_t)b * q_stride;
     int local = 0;
     for (int c = threadIdx.x * 4; c < q_stride; c += blockDim.x * 4) {
@@ -148,8 +149,8 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             int v = 0;
-            if (c + j < k && s > 0.0f) {
-                float r = roundf(__fdiv_rn(row[c + j], s));
+            if (c + j < k && amax > 0.0f) {
+                float r = roundf(__fmul_rn(row[c + j], inv));
                 r = fminf(fmaxf(r, -127.0f), 127.0f);
                 v = (int)r;
             }

@@ -13,7 +13,7 @@ using namespace bt;
 
 namespace bt {
 cudaError_t upload_inv_freq(float* dev, int head_dim, double theta);
-int attn_splits(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count);
+void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* splits, int* span);
 
 __global__ void advance_pos_kernel(int32_t* pos, int n) {
     if (threadIdx.x < n) pos[threadIdx.x] += 1;
@@ -147,7 +147,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.out = m->att;
             a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
-            a.splits = attn_splits(batch, c.n_kv_heads, c.max_position_embeddings, sm);
+            attn_plan(batch, c.n_kv_heads, c.max_position_embeddings, sm, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = amax_core;
             a.pdl = true;
@@ -195,7 +195,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.out = m->att;
             a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
-            a.splits = attn_splits(batch, c.n_kv_heads, c.max_position_embeddings, sm);
+            attn_plan(batch, c.n_kv_heads, c.max_position_embeddings, sm, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = nullptr;
             a.pdl = false;
@@ -379,7 +379,7 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
         BT_CUDA_TRY(dev_alloc(&m->att, (size_t)B * H));
         BT_CUDA_TRY(dev_alloc(&m->inv_freq, (size_t)m->head_dim / 2));
         BT_CUDA_TRY(upload_inv_freq(m->inv_freq, m->head_dim, c.rope_theta));
-        BT_CUDA_TRY(dev_alloc(&m->attn_partial, (size_t)B * c.n_heads * 32 * (m->head_dim + 2)));
+        BT_CUDA_TRY(dev_alloc(&m->attn_partial, (size_t)B * c.n_heads * 64 * (m->head_dim + 2)));
     } else {
         BT_CUDA_TRY(dev_alloc(&m->feat, (size_t)B * m->d_small));
         BT_CUDA_TRY(dev_alloc(&m->z, (size_t)B * m->d_small));
@@ -395,7 +395,8 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
     if (!m) return BT_OK;
     DeviceGuard guard(m->device);
     cudaDeviceSynchronize();
-    for (auto& g : m->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto& g : m->graphs)
+        if (g && g != reinterpret_cast<cudaGraphExec_t>(uintptr_t(1))) cudaGraphExecDestroy(g);  // 1 = "ran eagerly once" sentinel
     for (auto& L : m->layers) {
         bt_linear_destroy(L.qkv); bt_linear_destroy(L.o); bt_linear_destroy(L.gate_up); bt_linear_destroy(L.gate_up_il); bt_linear_destroy(L.down);
         bt_linear_destroy(L.ttt_down); bt_linear_destroy(L.ttt_up);

@@ -20,13 +20,16 @@ cudaError_t upload_inv_freq(float* dev, int head_dim, double theta) {
     return cudaMemcpy(dev, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice);
 }
 
-// Number of KV splits so that batch * n_kv * splits CTAs roughly fill the GPU.
-int attn_splits(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count) {
-    int64_t s = (2 * (int64_t)sm_count + batch * n_kv - 1) / (batch * n_kv);
-    if (s > 32) s = 32;
-    if (s > (max_seq + 63) / 64) s = (max_seq + 63) / 64;  // at least 64 positions per split
-    if (s < 1) s = 1;
-    return (int)s;
+// Cuts the positions of a sequence into fixed spans so that batch * n_kv * splits CTAs
+// roughly fill the GPU: span is a multiple of 128 (4 warps x 32 positions), at most 64 spans.
+void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* splits, int* span) {
+    int64_t want = (2 * (int64_t)sm_count + batch * n_kv - 1) / (batch * n_kv);
+    if (want > 64) want = 64;
+    if (want < 1) want = 1;
+    int64_t sp = (max_seq + want - 1) / want;
+    sp = (sp + 127) / 128 * 128;
+    *span = (int)sp;
+    *splits = (int)((max_seq + sp - 1) / sp);
 }
 
 }  // namespace bt
@@ -67,8 +70,8 @@ extern "C" bt_status bt_kv_create(bt_kv_cache** out, int64_t batch, int64_t n_kv
     const size_t rows = (size_t)batch * n_kv_heads * max_seq_len;
     const int sm = device_sm_count(device);
     c->max_heads = (int)n_kv_heads * 8;
-    const int splits = attn_splits(1, n_kv_heads, max_seq_len, sm);  // worst case: batch 1
-    c->partial_floats = (int64_t)batch * c->max_heads * (splits > 32 ? splits : 32) * (head_dim + 2);
+    (void)sm;
+    c->partial_floats = (int64_t)batch * c->max_heads * 64 * (head_dim + 2);  // at most 64 spans
     cudaError_t e = cudaMalloc(&c->view.k_q, rows * head_dim);
     if (e == cudaSuccess) e = cudaMalloc(&c->view.v_q, rows * head_dim);
     if (e == cudaSuccess) e = cudaMalloc(&c->view.k_s, rows * sizeof(float));
@@ -144,7 +147,7 @@ extern "C" bt_status bt_attn_decode(bt_kv_cache* c, const float* qkv_dev, const 
     a.out = out_dev;
     a.partial = c->partial;
     a.batch = (int)batch; a.n_heads = (int)n_heads; a.n_kv = (int)c->n_kv; a.head_dim = (int)c->head_dim;
-    a.splits = attn_splits(batch, c->n_kv, c->max_seq, device_sm_count(c->device));
+    attn_plan(batch, c->n_kv, c->max_seq, device_sm_count(c->device), &a.splits, &a.span);
     a.scaling = (float)(1.0 / sqrt((double)c->head_dim));  // layers/attention.rs:114
     a.absmax_out = nullptr;
     a.pdl = false;

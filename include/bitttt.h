@@ -111,7 +111,8 @@ bt_status bt_linear_forward_host(bt_linear* lin, const float* x_host, int64_t m,
 
 /* Per-token absmax int8 quantiser (no counterpart kernel in the reference; defined
  * after QuantizedKVCache::quantize_q8, RE/layers/kv_cache.rs:95-119, without the +128
- * zero point): s = max|x|/127, q = clamp(round(x/s), -127, 127), s == 0 -> q = 0.
+ * zero point; the BitNet b1.58 form): amax = max|x|, q = clamp(round(x * (127/amax)), -127, 127)
+ * with round half away from zero, dequantisation scale s = amax/127, amax == 0 -> q = 0.
  * q_dev [m,k] int8, s_dev [m] f32, qsum_dev [m] int32 (sum_k q, may be NULL). */
 bt_status bt_act_quant(const void* x_dev, bt_dtype x_dtype, int64_t m, int64_t k, int8_t* q_dev,
                        float* s_dev, int32_t* qsum_dev, int device, void* stream);

@@ -237,10 +237,12 @@ EXPORT void oracle_bitlinear_i32(const int8_t* q, int64_t m, int64_t k, const ui
 }
 
 /* Per-token absmax int8 quantiser placed in front of the ternary product.  The
- * reference has no such stage on this path; the definition follows its only absmax
- * quantiser, crates/rust_engine/src/layers/kv_cache.rs:95-119, without the +128
- * zero-point: s = max|x|/127, q = round(x/s) (half away from zero), clamped to
- * [-127,127]; an all-zero row gives s = 0, q = 0 (the reference would give NaN).
+ * reference has no such stage on this path; the definition is the BitNet b1.58 one, in the
+ * spirit of the reference's only absmax quantiser (crates/rust_engine/src/layers/
+ * kv_cache.rs:95-119) without the +128 zero-point:
+ *   amax = max|x|;  q = clamp(round(x * (127/amax)), -127, 127)  (round half away from zero,
+ *   the multiplier 127/amax computed once per token in f32);  dequantisation scale
+ *   s = amax/127;  an all-zero row gives s = 0, q = 0 (the reference would give NaN).
  * Also returns sum_k q per token, which the CUDA kernels use internally. */
 EXPORT void oracle_act_quant(const float* x, int64_t m, int64_t k, int8_t* q, float* s_out,
                              int32_t* qsum_out) {
@@ -252,11 +254,12 @@ EXPORT void oracle_act_quant(const float* x, int64_t m, int64_t k, int8_t* q, fl
             if (a > amax) amax = a;
         }
         float s = amax / 127.0f;
+        float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
         int32_t sum = 0;
         for (int64_t l = 0; l < k; ++l) {
             float r = 0.0f;
-            if (s > 0.0f) {
-                r = roundf(xr[l] / s);
+            if (amax > 0.0f) {
+                r = roundf(xr[l] * inv);
                 if (r > 127.0f) r = 127.0f;
                 if (r < -127.0f) r = -127.0f;
             }

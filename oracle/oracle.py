@@ -261,11 +261,12 @@ def np_pack_l1(w):
 
 def np_act_quant(x):
     x = np.asarray(x, np.float32)
-    s = (np.abs(x).max(axis=1) / np.float32(127.0)).astype(np.float32)
-    safe = np.where(s > 0, s, np.float32(1.0)).astype(np.float32)
-    ratio = (x / safe[:, None]).astype(np.float32)
+    amax = np.abs(x).max(axis=1).astype(np.float32)
+    s = (amax / np.float32(127.0)).astype(np.float32)
+    inv = np.where(amax > 0, np.float32(127.0) / np.where(amax > 0, amax, np.float32(1.0)), 0).astype(np.float32)
+    ratio = (x * inv[:, None]).astype(np.float32)
     q = np.sign(ratio) * np.floor(np.abs(ratio) + np.float32(0.5))
-    q = np.where(s[:, None] > 0, np.clip(q, -127, 127), 0).astype(np.int8)
+    q = np.where(amax[:, None] > 0, np.clip(q, -127, 127), 0).astype(np.int8)
     return q, s
 
 
