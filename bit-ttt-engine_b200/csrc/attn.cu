@@ -12,7 +12,7 @@ namespace bt {
 
 namespace {
 
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 16;
 constexpr int kAttnThreads = kAttnWarps * 32;
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -40,232 +40,275 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
     if (lane == 0) *s_out = s;
 }
 
-// One CTA = one (sequence, KV head, span of positions).  Each warp takes chunks of 32
-// positions: (A) lane j dots key row j with the NREP query heads (no cross-lane traffic),
-// (B) the chunk's softmax weights are formed with one exp per lane and head, (C) the lanes
-// switch to owning head dimensions and accumulate P.V with the weights broadcast by
-// shuffle.  Everything between the u8 loads and the final rounding is f64, so the result
-// does not depend on how positions are split over lanes, warps and CTAs.
-template <int PER_LANE, int NREP>
+// One CTA = one (sequence, KV head, span of positions), 512 threads.  The span is walked
+// in tiles of 128 positions; per tile: (1) the K and V rows are staged in shared memory,
+// (2) thread (position, head) forms one score with a 128-long f64 dot product, (3) one warp
+// per head turns the tile's scores into softmax weights (running max / sum across tiles),
+// (4) thread (head, dim) accumulates P.V over the tile.  No cross-thread reduction of the
+// accumulators is needed, and everything between the u8 loads and the final rounding is
+// f64, so the result does not depend on how positions are cut into tiles and spans.
+constexpr int kTilePos = 128;
+constexpr int kRowPad = 144;  // bytes per staged row: 128 + 16, conflict-free 16-byte reads
+constexpr int kMaxRep = 8;
+
+struct AttnSmem {
+    double qs[kMaxRep][128];
+    double pw[kMaxRep][kTilePos];
+    float sc[kMaxRep][kTilePos];
+    double m_run[kMaxRep], l_run[kMaxRep], corr[kMaxRep];
+    float k_s[kTilePos], v_s[kTilePos];
+    float knew[128], vnew[128];
+    alignas(16) uint8_t k_rows[kTilePos * kRowPad];
+    alignas(16) uint8_t v_rows[kTilePos * kRowPad];
+};
+
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
-    constexpr int HD = 32 * PER_LANE;
-    __shared__ double qs[NREP][HD];
-    __shared__ float knew[128], vnew[128];
-    __shared__ double red_m[kAttnWarps][NREP], red_l[kAttnWarps][NREP];
-    __shared__ double red_acc[kAttnWarps][NREP][HD];
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
+#define STAMP(i) do { if (a.dbg && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) a.dbg[i] = ptx::globaltimer(); } while (0)
+    STAMP(0);
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
+    STAMP(1);
 
     const int hd = a.head_dim, half = hd >> 1;
+    const int nrep = a.n_heads / a.n_kv;
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int split = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int p = a.pos[b];
     const int t_len = p + 1;
     const int t0 = split * a.span;
     const int t1 = min(t_len, t0 + a.span);
     const int64_t qkv_stride = (int64_t)(a.n_heads + 2 * a.n_kv) * hd;
     const float* qkv = a.qkv + b * qkv_stride;
-    double* part_base = a.partial + (((int64_t)b * a.n_heads + kvh * NREP) * a.splits + split) * (hd + 2);
-    if (t0 >= t_len) {
+    double* part_base = a.partial + (((int64_t)b * a.n_heads + kvh * nrep) * a.splits + split) * (hd + 2);
+    const bool empty = t0 >= t_len;
+    if (empty) {
         // nothing in this span yet: leave an empty partial (max = -inf, sum = 0)
-        for (int h = threadIdx.x; h < NREP; h += blockDim.x) {
+        for (int h = tid; h < nrep; h += blockDim.x) {
             double* dst = part_base + (int64_t)h * a.splits * (hd + 2);
             dst[0] = -INFINITY;
             dst[1] = 0.0;
         }
-        return;
     }
-    const float fp = (float)p;
+    if (!empty) {
+    const float* cos_p = a.rope_cos + (int64_t)p * half;
+    const float* sin_p = a.rope_sin + (int64_t)p * half;
 
-    // rotate the NREP query heads of this KV group (cos/sin evaluated in f64, rounded once)
-    for (int i = threadIdx.x; i < NREP * half; i += blockDim.x) {
+    // rotate the query heads of this KV group: [x1*cos - x2*sin, x1*sin + x2*cos] (attention.rs:79-83)
+    for (int i = tid; i < nrep * half; i += blockDim.x) {
         const int h = i / half, c = i % half;
-        const float fr = __fmul_rn(fp, a.inv_freq[c]);
-        const float cs = (float)cos((double)fr), sn = (float)sin((double)fr);
-        const float* qh = qkv + (int64_t)(kvh * NREP + h) * hd;
+        const float cs = cos_p[c], sn = sin_p[c];
+        const float* qh = qkv + (int64_t)(kvh * nrep + h) * hd;
         const float x1 = qh[c], x2 = qh[half + c];
-        qs[h][c] = (double)__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
-        qs[h][half + c] = (double)__fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
+        sm.qs[h][c] = (double)__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+        sm.qs[h][half + c] = (double)__fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
     }
+    if (tid < nrep) { sm.m_run[tid] = -INFINITY; sm.l_run[tid] = 0.0; }
     const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
     // the CTA whose span holds position p appends the new key / value first
     const bool owner = (p >= t0 && p < t1);
     if (owner) {
         const float* kh = qkv + (int64_t)(a.n_heads + kvh) * hd;
         const float* vh = qkv + (int64_t)(a.n_heads + a.n_kv + kvh) * hd;
-        for (int c = threadIdx.x; c < half; c += blockDim.x) {
-            const float fr = __fmul_rn(fp, a.inv_freq[c]);
-            const float cs = (float)cos((double)fr), sn = (float)sin((double)fr);
+        for (int c = tid; c < half; c += blockDim.x) {
+            const float cs = cos_p[c], sn = sin_p[c];
             const float x1 = kh[c], x2 = kh[half + c];
-            knew[c] = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
-            knew[half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
+            sm.knew[c] = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+            sm.knew[half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
         }
-        for (int c = threadIdx.x; c < hd; c += blockDim.x) vnew[c] = vh[c];
+        for (int c = tid; c < hd; c += blockDim.x) sm.vnew[c] = vh[c];
     }
     __syncthreads();
     if (owner) {
-        if (warp == 0) quant_row_warp(knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p, lane);
-        if (warp == 1) quant_row_warp(vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p, lane);
+        if (warp == 0) quant_row_warp(sm.knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p, lane);
+        if (warp == 1) quant_row_warp(sm.vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p, lane);
     }
     __syncthreads();  // the block's own global writes are visible to it after the barrier
+    STAMP(2);
 
-    double m_run[NREP], l_run[NREP], acc[NREP][PER_LANE];
-#pragma unroll
-    for (int h = 0; h < NREP; ++h) {
-        m_run[h] = -INFINITY;
-        l_run[h] = 0.0;
-#pragma unroll
-        for (int j = 0; j < PER_LANE; ++j) acc[h][j] = 0.0;
-    }
+    // thread-owned output elements (head, dim): items tid, tid + 512
+    double acc[2] = {0.0, 0.0};
+    const int n_out = nrep * hd;
+    const int row16 = hd / 16;  // 16-byte pieces per row
 
-    for (int tb = t0 + warp * 32; tb < t1; tb += kAttnWarps * 32) {
-        // (A) scores of position tb + lane against the NREP heads
-        const int t = tb + lane;
-        const bool valid = t < t1;
-        double sc[NREP];
+    for (int tb = t0; tb < t1; tb += kTilePos) {
+        const int n_here = min(kTilePos, t1 - tb);
+        // (1) stage the tile's K and V rows and scales
+        for (int i = tid; i < n_here * row16; i += blockDim.x) {
+            const int r = i / row16, c16 = i % row16;
+            const uint4 kv = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + tb + r) * hd)[c16];
+            const uint4 vv = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + tb + r) * hd)[c16];
+            *reinterpret_cast<uint4*>(sm.k_rows + r * kRowPad + c16 * 16) = kv;
+            *reinterpret_cast<uint4*>(sm.v_rows + r * kRowPad + c16 * 16) = vv;
+        }
+        for (int r = tid; r < n_here; r += blockDim.x) {
+            sm.k_s[r] = a.cache.k_s[row_base + tb + r];
+            sm.v_s[r] = a.cache.v_s[row_base + tb + r];
+        }
+        __syncthreads();
+        STAMP(3);
+        // (2) scores: item = (head, position); position runs over lanes, so q is a broadcast
+        for (int it = tid; it < nrep * kTilePos; it += blockDim.x) {
+            const int h = it / kTilePos, r = it % kTilePos;
+            if (r < n_here) {
+                const uint8_t* row = sm.k_rows + r * kRowPad;
+                const float ks = sm.k_s[r];
+                double d4[4] = {0.0, 0.0, 0.0, 0.0};  // four independent chains, one per byte lane
+                for (int c16 = 0; c16 < row16; ++c16) {
+                    const uint4 pk = *reinterpret_cast<const uint4*>(row + c16 * 16);
+                    const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-        for (int h = 0; h < NREP; ++h) sc[h] = 0.0;
-        if (valid) {
-            const uint4* kr = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + t) * hd);
-            const float ks = a.cache.k_s[row_base + t];
+                    for (int wi = 0; wi < 4; ++wi)
 #pragma unroll
-            for (int c16 = 0; c16 < HD / 16; ++c16) {
-                const uint4 pk = kr[c16];
-                const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-#pragma unroll
-                    for (int bi = 0; bi < 4; ++bi) {
-                        const int c = c16 * 16 + wi * 4 + bi;
-                        // dequantize_q8, kv_cache.rs:122-128: (f32(q) - 128) * s
-                        const double kf = (double)__fmul_rn((float)((wds[wi] >> (8 * bi)) & 0xffu) - 128.0f, ks);
-#pragma unroll
-                        for (int h = 0; h < NREP; ++h) sc[h] = fma(qs[h][c], kf, sc[h]);
-                    }
+                        for (int bi = 0; bi < 4; ++bi) {
+                            // dequantize_q8, kv_cache.rs:122-128: (f32(q) - 128) * s
+                            const float kf = __fmul_rn((float)((wds[wi] >> (8 * bi)) & 0xffu) - 128.0f, ks);
+                            d4[bi] = fma(sm.qs[h][c16 * 16 + wi * 4 + bi], (double)kf, d4[bi]);
+                        }
                 }
+                const double d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+                sm.sc[h][r] = __fmul_rn((float)d, a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
             }
         }
-        // (B) softmax weights of the chunk: (q.k) * 1/sqrt(hd) in f32 (attention.rs:202), then f64
-        double pw[NREP];
+        __syncthreads();
+        STAMP(4);
+        // (3) softmax weights of the tile, one warp per head
+        if (warp < nrep) {
+            const int h = warp;
+            double sv[kTilePos / 32];
+            double tmax = -INFINITY;
 #pragma unroll
-        for (int h = 0; h < NREP; ++h) {
-            const double s_h = valid ? (double)__fmul_rn((float)sc[h], a.scaling) : -INFINITY;
-            double cmax = s_h;
+            for (int i = 0; i < kTilePos / 32; ++i) {
+                const int r = lane + 32 * i;
+                sv[i] = r < n_here ? (double)sm.sc[h][r] : -INFINITY;
+                tmax = fmax(tmax, sv[i]);
+            }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) cmax = fmax(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
-            const double m_new = fmax(m_run[h], cmax);
-            const double corr = exp(m_run[h] - m_new);  // exp(-inf) = 0 on the first chunk
-            pw[h] = valid ? exp(s_h - m_new) : 0.0;
-            double psum = pw[h];
+            for (int o = 16; o > 0; o >>= 1) tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+            const double m_old = sm.m_run[h];
+            const double m_new = fmax(m_old, tmax);
+            double psum = 0.0;
+#pragma unroll
+            for (int i = 0; i < kTilePos / 32; ++i) {
+                const int r = lane + 32 * i;
+                const double pe = r < n_here ? exp(sv[i] - m_new) : 0.0;
+                sm.pw[h][r] = pe;
+                psum += pe;
+            }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
-            l_run[h] = fma(l_run[h], corr, psum);
-#pragma unroll
-            for (int j = 0; j < PER_LANE; ++j) acc[h][j] *= corr;
-            m_run[h] = m_new;
-        }
-        // (C) acc[h][dims of this lane] += sum_j p_j[h] * v_j[dims]
-        const int n_here = min(32, t1 - tb);
-        for (int j = 0; j < n_here; ++j) {
-            const uint8_t* vr = a.cache.v_q + (row_base + tb + j) * hd + lane * PER_LANE;
-            const float vs = a.cache.v_s[row_base + tb + j];
-            double vf[PER_LANE];
-            if (PER_LANE == 4) {
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(vr);
-#pragma unroll
-                for (int d = 0; d < PER_LANE; ++d) vf[d] = (double)__fmul_rn((float)((w >> (8 * d)) & 0xffu) - 128.0f, vs);
-            } else {
-#pragma unroll
-                for (int d = 0; d < PER_LANE; ++d) vf[d] = (double)__fmul_rn((float)vr[d] - 128.0f, vs);
-            }
-#pragma unroll
-            for (int h = 0; h < NREP; ++h) {
-                const double pj = __shfl_sync(0xffffffffu, pw[h], j);
-#pragma unroll
-                for (int d = 0; d < PER_LANE; ++d) acc[h][d] = fma(pj, vf[d], acc[h][d]);
+            if (lane == 0) {
+                const double corr = exp(m_old - m_new);  // exp(-inf) = 0 on the first tile
+                sm.corr[h] = corr;
+                sm.l_run[h] = fma(sm.l_run[h], corr, psum);
+                sm.m_run[h] = m_new;
             }
         }
-    }
-    // combine the warps of this CTA
+        __syncthreads();
+        STAMP(5);
+        // (4) acc[head, dim] = acc * corr + sum_r p[head, r] * v[r, dim]
 #pragma unroll
-    for (int h = 0; h < NREP; ++h) {
-        if (lane == 0) { red_m[warp][h] = m_run[h]; red_l[warp][h] = l_run[h]; }
-#pragma unroll
-        for (int j = 0; j < PER_LANE; ++j) red_acc[warp][h][lane * PER_LANE + j] = acc[h][j];
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < NREP * hd; i += blockDim.x) {
-        const int h = i / hd, c = i % hd;
-        double m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) m = fmax(m, red_m[w][h]);
-        double l = 0.0, v = 0.0;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) {
-            const double scw = red_m[w][h] == -INFINITY ? 0.0 : exp(red_m[w][h] - m);
-            l = fma(red_l[w][h], scw, l);
-            v = fma(red_acc[w][h][c], scw, v);
+        for (int e = 0; e < 2; ++e) {
+            const int it = tid + e * kAttnThreads;
+            if (it < n_out) {
+                const int h = it / hd, dcol = it % hd;
+                double v = acc[e] * sm.corr[h];
+                for (int r = 0; r < n_here; ++r) {
+                    const float vf = __fmul_rn((float)sm.v_rows[r * kRowPad + dcol] - 128.0f, sm.v_s[r]);
+                    v = fma(sm.pw[h][r], (double)vf, v);
+                }
+                acc[e] = v;
+            }
         }
-        double* dst = part_base + (int64_t)h * a.splits * (hd + 2);
-        dst[2 + c] = v;
-        if (c == 0) { dst[0] = m; dst[1] = l; }
+        __syncthreads();
     }
-}
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int it = tid + e * kAttnThreads;
+        if (it < n_out) {
+            const int h = it / hd, dcol = it % hd;
+            double* dst = part_base + (int64_t)h * a.splits * (hd + 2);
+            dst[2 + dcol] = acc[e];
+            if (dcol == 0) { dst[0] = sm.m_run[h]; dst[1] = sm.l_run[h]; }
+        }
+    }
+    }  // !empty
+    STAMP(6);
 
-// Merge the per-split partials: out = sum_s e^{m_s - m} acc_s / sum_s e^{m_s - m} l_s.
-__global__ void attn_combine_kernel(AttnArgs a) {
-    ptx::pdl_wait();
-    ptx::pdl_launch_dependents();
-    const int hd = a.head_dim;
-    const int64_t bh = blockIdx.x;  // b * n_heads + head
-    const double* base = a.partial + bh * a.splits * (hd + 2);
-    double m = -INFINITY;
-    for (int s = 0; s < a.splits; ++s) m = fmax(m, base[s * (hd + 2)]);
-    for (int c = threadIdx.x; c < hd; c += blockDim.x) {
-        double l = 0.0, v = 0.0;
-        for (int s = 0; s < a.splits; ++s) {
-            const double ms = base[s * (hd + 2)];
+    // The last CTA of this (sequence, KV head) to get here merges the spans:
+    // out = sum_s e^{m_s - m} acc_s / sum_s e^{m_s - m} l_s, rounded to f32 once.
+    __threadfence();
+    __syncthreads();
+    __shared__ unsigned int arrived;
+    if (tid == 0) arrived = atomicAdd(a.counters + blockIdx.x, 1u);
+    __syncthreads();
+    STAMP(7);
+    if (arrived != (unsigned int)a.splits - 1) return;
+    __threadfence();
+    if (tid == 0) a.counters[blockIdx.x] = 0;  // ready for the next launch
+    const double* group = a.partial + ((int64_t)b * a.n_heads + kvh * nrep) * a.splits * (hd + 2);
+    for (int it = tid; it < nrep * hd; it += blockDim.x) {
+        const int h = it / hd, c = it % hd;
+        const double* base = group + (int64_t)h * a.splits * (hd + 2);
+        double m = -INFINITY, l = 0.0, v = 0.0;
+        for (int s2 = 0; s2 < a.splits; ++s2) {
+            const double ms = __ldcg(base + s2 * (hd + 2));
+            const double ls = __ldcg(base + s2 * (hd + 2) + 1);
+            const double vs2 = __ldcg(base + s2 * (hd + 2) + 2 + c);
             if (ms == -INFINITY) continue;  // span without positions yet
-            const double sc = exp(ms - m);
-            l = fma(base[s * (hd + 2) + 1], sc, l);
-            v = fma(base[s * (hd + 2) + 2 + c], sc, v);
+            const double m_new = fmax(m, ms);
+            const double c_old = exp(m - m_new), c_new = exp(ms - m_new);  // exp(-inf) = 0 at first
+            l = fma(l, c_old, ls * c_new);
+            v = fma(v, c_old, vs2 * c_new);
+            m = m_new;
         }
         const float o = (float)(v / l);
-        a.out[bh * hd + c] = o;
-        if (a.absmax_out) atomicMax(a.absmax_out + bh / a.n_heads, __float_as_uint(fabsf(o)));
+        a.out[((int64_t)b * a.n_heads + kvh * nrep + h) * hd + c] = o;
+        if (a.absmax_out) {
+            float mx = fabsf(o);
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
+            if (lane == 0) atomicMax(a.absmax_out + b, __float_as_uint(mx));
+        }
+    }
+    STAMP(8);
+}
+
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, int max_seq, int half,
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t) {
+    const int64_t n = (int64_t)max_seq * half;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int pos = (int)(i / half), c = (int)(i % half);
+        const float fr = __fmul_rn((float)pos, inv_freq[c]);  // f32 product, attention.rs:30
+        cos_t[i] = (float)cos((double)fr);
+        sin_t[i] = (float)sin((double)fr);
     }
 }
 
 }  // namespace
 
-template <int PER_LANE>
-static cudaError_t launch_rep(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
-    cudaError_t e = cudaSuccess;
-    switch (a.n_heads / a.n_kv) {
-        case 1: e = launch_pdl(attn_decode_kernel<PER_LANE, 1>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
-        case 2: e = launch_pdl(attn_decode_kernel<PER_LANE, 2>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
-        case 4: e = launch_pdl(attn_decode_kernel<PER_LANE, 4>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
-        default: e = launch_pdl(attn_decode_kernel<PER_LANE, 8>, grid, dim3(kAttnThreads), 0, stream, a.pdl, a); break;
-    }
-    return e;
-}
-
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     const int rep = a.n_kv > 0 ? a.n_heads / a.n_kv : 0;
-    if (a.head_dim % 32 != 0 || a.head_dim > 128 || a.n_heads % a.n_kv != 0 ||
-        !(rep == 1 || rep == 2 || rep == 4 || rep == 8))
+    if (a.head_dim % 32 != 0 || a.head_dim > 128 || a.n_heads % a.n_kv != 0 || rep < 1 || rep > kMaxRep ||
+        a.span % 32 != 0)
         return cudaErrorInvalidValue;
-    dim3 grid(a.batch * a.n_kv, a.splits);
-    cudaError_t e;
-    switch (a.head_dim / 32) {
-        case 1: e = launch_rep<1>(a, grid, stream); break;
-        case 2: e = launch_rep<2>(a, grid, stream); break;
-        case 3: e = launch_rep<3>(a, grid, stream); break;
-        default: e = launch_rep<4>(a, grid, stream); break;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e0 = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)sizeof(AttnSmem));
+        if (e0 != cudaSuccess) return e0;
+        configured = true;
     }
-    if (e != cudaSuccess) return e;
-    return launch_pdl(attn_combine_kernel, dim3(a.batch * a.n_heads), dim3(a.head_dim), 0, stream, a.pdl, a);
+    dim3 grid(a.batch * a.n_kv, a.splits);
+    return launch_pdl(attn_decode_kernel, grid, dim3(kAttnThreads), sizeof(AttnSmem), stream, a.pdl, a);
+}
+
+cudaError_t launch_rope_tables(const float* inv_freq, int max_seq, int half, float* cos_t, float* sin_t,
+                               cudaStream_t stream) {
+    rope_table_kernel<<<148, 256, 0, stream>>>(inv_freq, max_seq, half, cos_t, sin_t);
+    return cudaGetLastError();
 }
 
 }  // namespace bt

@@ -123,6 +123,7 @@ struct GemvArgs {
     int epilogue;
     unsigned int* err;
     bool pdl;               // launch with programmatic stream serialisation
+    unsigned long long* dbg; // optional timeline slot: [grid][4] globaltimer stamps (development aid)
 };
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream);
 

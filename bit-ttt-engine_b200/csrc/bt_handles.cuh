@@ -33,6 +33,9 @@ struct bt_kv_cache {
     bt::KvCacheView view{};
     float* inv_freq = nullptr;   // device [head_dim/2], built for inv_freq_theta
     double inv_freq_theta = 0.0;
+    float* rope_cos = nullptr;   // device [max_seq, head_dim/2] for inv_freq_theta
+    float* rope_sin = nullptr;
+    unsigned int* counters = nullptr;  // device [batch * n_kv] arrival counters of the attention kernel
     double* partial = nullptr;   // split-KV scratch
     int64_t partial_floats = 0;
     int max_heads = 0;

@@ -52,7 +52,9 @@ struct AttnArgs {
     const float* qkv;
     KvCacheView cache;
     const int32_t* pos;      // [batch] position of the new token
-    const float* inv_freq;   // [head_dim/2]
+    const float* rope_cos;   // [max_seq, head_dim/2] f32 tables (RotaryEmbedding::new, attention.rs:15-41)
+    const float* rope_sin;
+    unsigned int* counters;  // [batch * n_kv] zero-initialised arrival counters (self-resetting)
     float* out;              // [batch, n_heads*head_dim]
     double* partial;         // scratch [batch, n_heads, splits, head_dim + 2] (max, sum, acc)
     int batch, n_heads, n_kv, head_dim;
@@ -61,8 +63,13 @@ struct AttnArgs {
     float scaling;
     unsigned int* absmax_out;  // optional [batch]: running max|out| (bits) via atomicMax
     bool pdl;                  // launch with programmatic stream serialisation
+    unsigned long long* dbg;   // optional: 16 globaltimer stamps of CTA (0,0) (development aid)
 };
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
+// cos/sin tables for positions 0..max_seq-1: freq = f32(pos) * inv_freq (f32 product), cos/sin
+// evaluated in f64 and rounded to f32.
+cudaError_t launch_rope_tables(const float* inv_freq, int max_seq, int half, float* cos_t, float* sin_t,
+                               cudaStream_t stream);
 
 // TTT fast-weight step (layers/ttt.rs:52-68) for `batch` independent states:
 // w: [batch, d, d] f32 updated in place, feat: [batch, d], z_out: [batch, d].

@@ -71,11 +71,26 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // D(16x8,s32) += A(16x32,u8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// round(v) with halves away from zero as an int, for |v| < 2^22: equal to (int)roundf(v).
+// trunc(v + copysign(0.5, v)) is exact except when |v| < 0.5 (the sum can round up to 1),
+// which is answered directly.
+__device__ __forceinline__ int round_half_away(float v) {
+    const float h = __uint_as_float((__float_as_uint(v) & 0x80000000u) | 0x3f000000u);  // copysign(0.5, v)
+    const int r = __float2int_rz(__fadd_rn(v, h));
+    return fabsf(v) < 0.5f ? 0 : r;
+}
+
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {

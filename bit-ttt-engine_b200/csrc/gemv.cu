@@ -26,6 +26,8 @@
 //     first weight stages are already in flight, which removes a kernel boundary per
 //     projection from the decode step; with programmatic dependent launch the weight
 //     prefetch even starts before the previous kernel has finished.
+#include <stdlib.h>
+
 #include "bt_common.cuh"
 #include "bt_ptx.cuh"
 
@@ -33,14 +35,16 @@ namespace bt {
 
 namespace {
 
+constexpr int kEpiWarps_ = 4;
 constexpr int kMathWarps = 8;
 constexpr int kMathThreads = kMathWarps * 32;
 constexpr int kProducerWarp = kMathWarps;
-constexpr int kEpilogueWarp = kMathWarps + 1;
-constexpr int kThreads = (kMathWarps + 2) * 32;
+constexpr int kEpilogueWarp0 = kMathWarps + 1;  // first of kRedBufs epilogue warps
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = (kMathWarps + 1 + kEpiWarps) * 32;
 constexpr int kStageTiles = 16;
 constexpr int kStageBytes = kStageTiles * kTileBytes;
-constexpr int kRedBufs = 4;
+constexpr int kRedBufs = kEpiWarps_;
 constexpr int kRedBufInts = kMathWarps * 128;
 constexpr int kRedBytes = kRedBufs * kRedBufInts * 4;
 constexpr int kMaxStages = 12;
@@ -51,21 +55,29 @@ constexpr unsigned kErrGemvTimeout = 0x47454d56u;  // 'GEMV'
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
-// One 1 KB tile: 2 A loads, 4 B loads, 32 ANDs, 8 MMAs.
+// One 1 KB tile: 2 A loads, 4 B loads, 32 ANDs, 8 MMAs.  The four field positions are four
+// independent accumulator chains: their first MMAs are issued back to back, then the second.
 __device__ __forceinline__ void tile_mma(int (&acc)[4][4], const uint8_t* tile, int lane,
                                          const uint8_t* acts_kt, bool has_token) {
     const uint4 w4 = lds128(tile + lane * 16);
     const uint4 v4 = lds128(tile + 512 + lane * 16);
+    uint4 b4[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-        uint4 b4 = make_uint4(0u, 0u, 0u, 0u);
-        if (has_token) b4 = lds128(acts_kt + r * 64);
+        b4[r] = make_uint4(0u, 0u, 0u, 0u);
+        if (has_token) b4[r] = lds128(acts_kt + r * 64);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
         const uint32_t mask = 0x03030303u << (2 * r);
-        ptx::mma_u8s8(acc[r], w4.x & mask, v4.x & mask, w4.z & mask, v4.z & mask, b4.x, b4.z);
-        ptx::mma_u8s8(acc[r], w4.y & mask, v4.y & mask, w4.w & mask, v4.w & mask, b4.y, b4.w);
+        ptx::mma_u8s8(acc[r], w4.x & mask, v4.x & mask, w4.z & mask, v4.z & mask, b4[r].x, b4[r].z);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t mask = 0x03030303u << (2 * r);
+        ptx::mma_u8s8(acc[r], w4.y & mask, v4.y & mask, w4.w & mask, v4.w & mask, b4[r].y, b4[r].w);
     }
 }
-
 
 // ---- reductions over the 256 math threads (named barrier 1) ----------------------------
 __device__ __forceinline__ double math_sum_d(double v, double* slot, int warp, int lane) {
@@ -109,9 +121,7 @@ __device__ __forceinline__ int quant_store_group(const float (&v)[16], float inv
         uint32_t word = 0;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            float rr = roundf(__fmul_rn(v[4 * b + r], inv));
-            rr = fminf(fmaxf(rr, -127.0f), 127.0f);
-            const int qv = (int)rr;
+            const int qv = max(-127, min(127, ptx::round_half_away(__fmul_rn(v[4 * b + r], inv))));
             sum += qv;
             word |= (uint32_t)(qv & 0xff) << (8 * r);
         }
@@ -143,7 +153,6 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
     const int groups = (int)(a.k_in >> 4);  // k_in is a multiple of 16 on the fused paths
     double* sl_d = reinterpret_cast<double*>(scratch);            // 8 doubles
     float* sl_f = reinterpret_cast<float*>(scratch + 64);          // 8 floats
-    int* sl_i = reinterpret_cast<int*>(scratch + 128);             // 2 x 8 ints (alternating)
     if (PRO == PRO_Q8) {
         for (int n = 0; n < a.m; ++n) {
             const uint4* src = reinterpret_cast<const uint4*>(a.q + (int64_t)n * a.q_stride);
@@ -172,23 +181,25 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
         float s;
         if (PRO == PRO_RMSNORM) {
             // up to two 16-groups per thread held in registers (k_in <= 8192)
-            float v0[16], v1[16];
+            float v0[16], v1[16], w0[16];
             const int j0 = tid, j1 = tid + kMathThreads;
             const bool h0 = j0 < groups, h1 = j1 < groups;
             double ss = 0.0;
-            if (h0) { load16(xr + 16 * j0, v0);
+            if (h0) { load16(xr + 16 * j0, v0); load16(a.norm_w + 16 * j0, w0); }
+            if (h1) load16(xr + 16 * j1, v1);
+            if (h0) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e) ss = fma((double)v0[e], (double)v0[e], ss); }
-            if (h1) { load16(xr + 16 * j1, v1);
+            if (h1) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e) ss = fma((double)v1[e], (double)v1[e], ss); }
             ss = math_sum_d(ss, sl_d, warp, lane);
             // x / sqrt(mean(x^2) + eps) * w  (layers/rms_norm.rs:40-55)
             const float denom = sqrtf(__fadd_rn((float)(ss / (double)a.k_in), a.eps));
             float amax = 0.0f;
-            if (h0) { float w[16]; load16(a.norm_w + 16 * j0, w);
+            if (h0) {
 #pragma unroll
-                for (int e = 0; e < 16; ++e) { v0[e] = __fmul_rn(__fdiv_rn(v0[e], denom), w[e]); amax = fmaxf(amax, fabsf(v0[e])); } }
+                for (int e = 0; e < 16; ++e) { v0[e] = __fmul_rn(__fdiv_rn(v0[e], denom), w0[e]); amax = fmaxf(amax, fabsf(v0[e])); } }
             if (h1) { float w[16]; load16(a.norm_w + 16 * j1, w);
 #pragma unroll
                 for (int e = 0; e < 16; ++e) { v1[e] = __fmul_rn(__fdiv_rn(v1[e], denom), w[e]); amax = fmaxf(amax, fabsf(v1[e])); } }
@@ -205,23 +216,35 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
             const float amax = __uint_as_float(a.absmax_in[n]);
             s = __fdiv_rn(amax, 127.0f);
             const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-            for (int j = tid; j < groups_pad; j += kMathThreads) {
-                float v[16];
-                if (j < groups) load16(xr + 16 * j, v);
-                else {
+            // four groups per thread per round, all loads of a round issued before any use
+            for (int jb = tid; jb < groups_pad; jb += 4 * kMathThreads) {
+                float v[4][16];
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) v[e] = 0.0f;
+                for (int u = 0; u < 4; ++u) {
+                    const int j = jb + u * kMathThreads;
+                    if (j < groups) load16(xr + 16 * j, v[u]);
+                    else {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) v[u][e] = 0.0f;
+                    }
                 }
-                local += quant_store_group(v, inv, dst, j);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = jb + u * kMathThreads;
+                    if (j < groups_pad) local += quant_store_group(v[u], inv, dst, j);
+                }
             }
         }
-        const int total = math_sum_i(local, sl_i + 8 * (n & 1), warp, lane);
-        if (tid == 0) { tok_qsum[n] = total; tok_sx[n] = s; }
+        // the sum is only read by the epilogue warps, after the barrier that ends the prologue
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if (lane == 0) atomicAdd(&tok_qsum[n], local);
+        if (tid == 0) tok_sx[n] = s;
     }
 }
 
 template <int PRO>
-__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstages, int act_stride) {
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstages, int act_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     int* red = reinterpret_cast<int*>(ring + (size_t)nstages * kStageBytes);
@@ -240,6 +263,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
     const int my_rts = (int)((a.row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
     const int total_iters = my_rts * stages_per_rt;
 
+    if (a.dbg && threadIdx.x == 0) a.dbg[blockIdx.x * 4 + 0] = ptx::globaltimer();
+    if (threadIdx.x < 8) tok_qsum[threadIdx.x] = 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
             ptx::mbar_init(&full[s], 1);
@@ -282,9 +307,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
 
     ptx::pdl_wait();  // activations and the output buffer belong to earlier kernels until here
 
-    if (warp == kEpilogueWarp) {
-        // ---------------- epilogue warp ----------------
-        ptx::named_bar_sync(2, kMathThreads + 32);  // tok_sx / tok_qsum are ready
+    if (warp >= kEpilogueWarp0) {
+        // ---------------- epilogue warps: warp e serves reduction buffer e, i.e. the CTA's row
+        // tiles e, e + kEpiWarps, ... ----------------
+        const int epi = warp - kEpilogueWarp0;
+        ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // tok_sx / tok_qsum are ready
         const int t = lane & 3, g = lane >> 2;
         int qs[2] = {0, 0};
         float sx[2] = {0.f, 0.f};
@@ -294,10 +321,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
             if (token < a.m) { qs[e] = tok_qsum[token]; sx[e] = tok_sx[token]; }
         }
         bool ok = true;
-        int rb = 0;
+        const int rb = epi;
         uint32_t parity = 0;
-        int64_t rt = blockIdx.x;
-        for (int lt = 0; lt < my_rts; ++lt) {
+        float run_max[2] = {0.f, 0.f};  // EPI_SWIGLU: running max|out| of this lane's two tokens
+        int64_t rt = blockIdx.x + (int64_t)epi * gridDim.x;
+        for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
             float sw[2] = {0.f, 0.f};
             if (a.epilogue != EPI_I32) { sw[0] = a.sw_tiles[2 * rt]; sw[1] = a.sw_tiles[2 * rt + 1]; }
             ok &= ptx::mbar_wait_bounded(&red_full[rb], parity);
@@ -321,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
                         // silu(g) * u, exp in f64 rounded once (layers/swiglu.rs:31-33)
                         const float act = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, (float)exp(-(double)gv))), uv);
                         reinterpret_cast<float*>(a.out)[(int64_t)token * a.out_stride + col] = act;
-                        atomicMax(a.absmax_out + token, __float_as_uint(fabsf(act)));
+                        run_max[e] = fmaxf(run_max[e], fabsf(act));
                     }
                 }
             } else {
@@ -344,18 +372,31 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(GemvArgs a, int nstag
                     }
                 }
             }
-            if (++rb == kRedBufs) { rb = 0; parity ^= 1; }
-            rt += gridDim.x;
+            parity ^= 1;
+            rt += (int64_t)kEpiWarps * gridDim.x;
+        }
+        if (a.epilogue == EPI_SWIGLU) {
+            // one atomic per token and warp: fold the lanes that share a token pair (same t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) run_max[e] = fmaxf(run_max[e], __shfl_xor_sync(0xffffffffu, run_max[e], o));
+                const int token = 2 * t + e;
+                if (g == 0 && token < a.m) atomicMax(a.absmax_out + token, __float_as_uint(run_max[e]));
+            }
         }
         if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
+        if (a.dbg && lane == 0 && epi == 0) a.dbg[blockIdx.x * 4 + 3] = ptx::globaltimer();
         return;
     }
 
     // ---------------- math warps ----------------
     const int tid = threadIdx.x;
     const int g = lane >> 2, t = lane & 3;
+    if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 1] = ptx::globaltimer();
     stage_activations<PRO>(a, acts, act_stride, tok_sx, tok_qsum, scratch, tid, warp, lane, k_tiles);
-    ptx::named_bar_sync(2, kMathThreads + 32);  // activation image complete, epilogue warp may read the scales
+    ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // activation image complete, epilogue warps may read the scales
+    if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 2] = ptx::globaltimer();
 
     int acc[4][4];
 #pragma unroll
@@ -418,10 +459,16 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     const int act_stride = (int)(a.k_tiles * kTileK + 64);
     const size_t fixed = (size_t)a.m * act_stride + kRedBytes + kBarBytes + kTokBytes + kScratchBytes;
     const int stages_per_rt = (int)((a.k_tiles + kStageTiles - 1) / kStageTiles);
-    // two CTAs per SM when each still gets at least 3 stages in ~110 KB
-    const size_t half_budget = 110 * 1024, full_budget = 220 * 1024;
-    int ctas_per_sm = (fixed + 3 * kStageBytes <= half_budget) ? 2 : 1;
-    const size_t budget = ctas_per_sm == 2 ? half_budget : full_budget;
+    // One CTA per SM.  The ring takes what shared memory allows, but never more stages than
+    // the CTA has iterations: small projections (q|k|v, o) then leave room for the next
+    // product kernel of the stream (programmatic dependent launch) to become resident
+    // beside this one and stream its first stages early, while large ones (gate|up, down)
+    // get the deepest ring - HBM needs well over 100 KB in flight per SM to stay busy.
+    const size_t full_budget = 220 * 1024;
+    int ctas_per_sm = 1;
+    static const char* env_ctas = getenv("BT_GEMV_CTAS");
+    if (env_ctas && env_ctas[0] == '2') ctas_per_sm = 2;
+    const size_t budget = ctas_per_sm == 2 ? full_budget / 2 : full_budget;
     if (fixed + 2 * kStageBytes > budget) return cudaErrorInvalidConfiguration;
     int nstages = (int)((budget - fixed) / kStageBytes);
     if (nstages > kMaxStages) nstages = kMaxStages;
@@ -482,6 +529,9 @@ cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stri
     return cudaSuccess;
 }
 
+unsigned long long* g_dbg_base = nullptr;
+int g_dbg_slot = 0;
+
 cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m, void* out,
                                  int64_t out_stride, int epilogue, unsigned int* absmax_out,
                                  unsigned int* err, int sm_count, cudaStream_t stream) {
@@ -505,7 +555,9 @@ cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m,
     a.out_stride = out_stride;
     a.epilogue = epilogue;
     a.err = err;
-    a.pdl = true;
+    a.dbg = g_dbg_base ? g_dbg_base + (size_t)(g_dbg_slot++) * 4 * 512 : nullptr;
+    static const char* env_pdl = getenv("BT_PDL");
+    a.pdl = !(env_pdl && env_pdl[0] == '0');
     return launch_gemv(a, sm_count, stream);
 }
 

@@ -12,6 +12,8 @@
 using namespace bt;
 
 namespace bt {
+extern unsigned long long* g_dbg_base;
+extern int g_dbg_slot;
 cudaError_t upload_inv_freq(float* dev, int head_dim, double theta);
 void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* splits, int* span);
 
@@ -63,6 +65,8 @@ struct bt_model {
     __nv_bfloat16* lm_head = nullptr;
     float* norm_f = nullptr;
     float* inv_freq = nullptr;
+    float* rope_cos = nullptr;   // [max_pos, head_dim/2]
+    float* rope_sin = nullptr;
     // activations
     int32_t* tokens = nullptr;
     int32_t* pos = nullptr;
@@ -143,7 +147,9 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.qkv = m->qkv;
             a.cache = L.kv->view;
             a.pos = m->pos;
-            a.inv_freq = m->inv_freq;
+            a.rope_cos = m->rope_cos;
+            a.rope_sin = m->rope_sin;
+            a.counters = L.kv->counters;
             a.out = m->att;
             a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
@@ -151,6 +157,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = amax_core;
             a.pdl = true;
+            a.dbg = g_dbg_base ? g_dbg_base + (size_t)(g_dbg_slot++) * 4 * 512 : nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
             FusedIn ain{PRO_ABSMAX, m->att, H, nullptr, 0.f, amax_core};
             BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
@@ -191,7 +198,9 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.qkv = m->qkv;
             a.cache = L.kv->view;
             a.pos = m->pos;
-            a.inv_freq = m->inv_freq;
+            a.rope_cos = m->rope_cos;
+            a.rope_sin = m->rope_sin;
+            a.counters = L.kv->counters;
             a.out = m->att;
             a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
@@ -199,6 +208,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = nullptr;
             a.pdl = false;
+            a.dbg = nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
             BT_CUDA_TRY(launch_row_quant(PRE_NONE, m->att, H, nullptr, 0.f, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
             BT_CUDA_TRY(linear_product(L.o->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
@@ -379,6 +389,10 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
         BT_CUDA_TRY(dev_alloc(&m->att, (size_t)B * H));
         BT_CUDA_TRY(dev_alloc(&m->inv_freq, (size_t)m->head_dim / 2));
         BT_CUDA_TRY(upload_inv_freq(m->inv_freq, m->head_dim, c.rope_theta));
+        BT_CUDA_TRY(dev_alloc(&m->rope_cos, (size_t)c.max_position_embeddings * (m->head_dim / 2)));
+        BT_CUDA_TRY(dev_alloc(&m->rope_sin, (size_t)c.max_position_embeddings * (m->head_dim / 2)));
+        BT_CUDA_TRY(launch_rope_tables(m->inv_freq, c.max_position_embeddings, m->head_dim / 2, m->rope_cos, m->rope_sin, 0));
+        BT_CUDA_TRY(cudaDeviceSynchronize());
         BT_CUDA_TRY(dev_alloc(&m->attn_partial, (size_t)B * c.n_heads * 64 * (m->head_dim + 2)));
     } else {
         BT_CUDA_TRY(dev_alloc(&m->feat, (size_t)B * m->d_small));
@@ -404,7 +418,7 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin};
     for (void* p : bufs) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
@@ -531,12 +545,12 @@ extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
     if (!m) return 0;
     if (batch <= 8) {
         // fused path: per layer 4 products + attention pair or TTT update; embedding, lm_head per 4 tokens, pick
-        const int per_layer = 4 + (m->cfg.arch == 1 ? 2 : 1);
+        const int per_layer = 4 + 1;  // 4 products + attention or TTT update
         return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
     }
     const int groups = (batch + 7) / 8;
-    // per layer: 4 quantiser launches, 4 ternary products per 8 tokens, attention (2) or TTT update (1)
-    const int per_layer = 4 + 4 * groups + (m->cfg.arch == 1 ? 2 : 1);
+    // per layer: 4 quantiser launches, 4 ternary products per 8 tokens, attention or TTT update
+    const int per_layer = 4 + 4 * groups + 1;
     // embedding, final norm, lm_head (4 tokens per launch), arg-max, position advance
     return m->cfg.num_layers * per_layer + 1 + 1 + (batch + 3) / 4 + 1 + 1;
 }
@@ -556,3 +570,7 @@ extern "C" bt_status bt_model_seek(bt_model* m, int pos) {
     m->host_pos = pos;
     return BT_OK;
 }
+
+// Development aid: fused product launches enqueued after this call stamp their timeline
+// (entry / after dependency wait / after activation staging / end) into buf[slot][cta][4].
+extern "C" void bt_debug_timeline(unsigned long long* buf) { bt::g_dbg_base = buf; bt::g_dbg_slot = 0; }

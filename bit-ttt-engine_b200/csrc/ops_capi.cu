@@ -78,6 +78,10 @@ extern "C" bt_status bt_kv_create(bt_kv_cache** out, int64_t batch, int64_t n_kv
     if (e == cudaSuccess) e = cudaMalloc(&c->view.v_s, rows * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&c->inv_freq, (size_t)head_dim / 2 * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&c->partial, (size_t)c->partial_floats * sizeof(double));
+    if (e == cudaSuccess) e = cudaMalloc(&c->rope_cos, (size_t)max_seq_len * (head_dim / 2) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&c->rope_sin, (size_t)max_seq_len * (head_dim / 2) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&c->counters, (size_t)batch * n_kv_heads * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(c->counters, 0, (size_t)batch * n_kv_heads * sizeof(unsigned int));
     c->view.max_seq = (int)max_seq_len;
     if (e != cudaSuccess) {
         bt_kv_destroy(c);
@@ -95,6 +99,7 @@ extern "C" bt_status bt_kv_reset(bt_kv_cache* c) {
     BT_CUDA_TRY(cudaMemset(c->view.v_q, 128, rows * c->head_dim));
     BT_CUDA_TRY(cudaMemset(c->view.k_s, 0, rows * sizeof(float)));
     BT_CUDA_TRY(cudaMemset(c->view.v_s, 0, rows * sizeof(float)));
+    BT_CUDA_TRY(cudaMemset(c->counters, 0, (size_t)c->batch * c->n_kv * sizeof(unsigned int)));
     return BT_OK;
 }
 
@@ -102,7 +107,7 @@ extern "C" bt_status bt_kv_destroy(bt_kv_cache* c) {
     if (!c) return BT_OK;
     DeviceGuard guard(c->device);
     cudaFree(c->view.k_q); cudaFree(c->view.v_q); cudaFree(c->view.k_s); cudaFree(c->view.v_s);
-    cudaFree(c->inv_freq); cudaFree(c->partial);
+    cudaFree(c->inv_freq); cudaFree(c->partial); cudaFree(c->rope_cos); cudaFree(c->rope_sin); cudaFree(c->counters);
     delete c;
     return BT_OK;
 }
@@ -137,13 +142,17 @@ extern "C" bt_status bt_attn_decode(bt_kv_cache* c, const float* qkv_dev, const 
     if (c->inv_freq_theta != rope_theta) {
         BT_CUDA_TRY(cudaDeviceSynchronize());
         BT_CUDA_TRY(upload_inv_freq(c->inv_freq, (int)c->head_dim, rope_theta));
+        BT_CUDA_TRY(launch_rope_tables(c->inv_freq, (int)c->max_seq, (int)c->head_dim / 2, c->rope_cos, c->rope_sin, 0));
+        BT_CUDA_TRY(cudaDeviceSynchronize());
         c->inv_freq_theta = rope_theta;
     }
     AttnArgs a;
     a.qkv = qkv_dev;
     a.cache = c->view;
     a.pos = pos_dev;
-    a.inv_freq = c->inv_freq;
+    a.rope_cos = c->rope_cos;
+    a.rope_sin = c->rope_sin;
+    a.counters = c->counters;
     a.out = out_dev;
     a.partial = c->partial;
     a.batch = (int)batch; a.n_heads = (int)n_heads; a.n_kv = (int)c->n_kv; a.head_dim = (int)c->head_dim;
@@ -151,6 +160,7 @@ extern "C" bt_status bt_attn_decode(bt_kv_cache* c, const float* qkv_dev, const 
     a.scaling = (float)(1.0 / sqrt((double)c->head_dim));  // layers/attention.rs:114
     a.absmax_out = nullptr;
     a.pdl = false;
+    a.dbg = nullptr;
     BT_CUDA_TRY(launch_attn_decode(a, reinterpret_cast<cudaStream_t>(stream)));
     return BT_OK;
 }
