@@ -41,34 +41,34 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
 }
 
 // One CTA = one (sequence, KV head, span of positions), 512 threads.  The span is walked
-// in tiles of 128 positions; per tile: (1) the K and V rows are staged in shared memory,
-// (2) thread (position, head) forms one score with a 128-long f64 dot product, (3) one warp
+// in tiles of 64 positions; per tile: (1) the K and V rows are dequantised into shared memory,
+// (2) thread (head, position, half) forms half of a score with a 64-long f64 dot product, (3) one warp
 // per head turns the tile's scores into softmax weights (running max / sum across tiles),
 // (4) thread (head, dim) accumulates P.V over the tile.  No cross-thread reduction of the
 // accumulators is needed, and everything between the u8 loads and the final rounding is
 // f64, so the result does not depend on how positions are cut into tiles and spans.
-constexpr int kTilePos = 128;
-constexpr int kRowPad = 144;  // bytes per staged row: 128 + 16, conflict-free 16-byte reads
+constexpr int kTilePos = 64;
+constexpr int kHalfPad = 68;   // floats per staged half row: 64 + 4, conflict-free 16-byte reads
 constexpr int kMaxRep = 8;
 
 struct AttnSmem {
-    double qs[kMaxRep][128];
+    alignas(16) float qs[kMaxRep][128];  // rotated queries (exact f32 values)
     double pw[kMaxRep][kTilePos];
     float sc[kMaxRep][kTilePos];
     double m_run[kMaxRep], l_run[kMaxRep], corr[kMaxRep];
-    float k_s[kTilePos], v_s[kTilePos];
     float knew[128], vnew[128];
-    alignas(16) uint8_t k_rows[kTilePos * kRowPad];
-    alignas(16) uint8_t v_rows[kTilePos * kRowPad];
+    alignas(16) float kf[kTilePos][2][kHalfPad];  // dequantised keys of the tile, two halves of 64 dims
+    alignas(16) float vf[kTilePos][128];          // dequantised values of the tile
 };
 
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
-#define STAMP(i) do { if (a.dbg && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) a.dbg[i] = ptx::globaltimer(); } while (0)
+#define STAMP(i) do { if (a.dbg && (i) < 2 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 4 + (i)] = ptx::globaltimer(); \
+                      if (a.dbg && (i) == 6 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 4 + 2] = ptx::globaltimer(); \
+                      if (a.dbg && (i) == 7 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 4 + 3] = ptx::globaltimer(); } while (0)
     STAMP(0);
     ptx::pdl_wait();
-    ptx::pdl_launch_dependents();
     STAMP(1);
 
     const int hd = a.head_dim, half = hd >> 1;
@@ -102,8 +102,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         const float cs = cos_p[c], sn = sin_p[c];
         const float* qh = qkv + (int64_t)(kvh * nrep + h) * hd;
         const float x1 = qh[c], x2 = qh[half + c];
-        sm.qs[h][c] = (double)__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
-        sm.qs[h][half + c] = (double)__fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
+        sm.qs[h][c] = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+        sm.qs[h][half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
     }
     if (tid < nrep) { sm.m_run[tid] = -INFINITY; sm.l_run[tid] = 0.0; }
     const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
@@ -135,42 +135,55 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 
     for (int tb = t0; tb < t1; tb += kTilePos) {
         const int n_here = min(kTilePos, t1 - tb);
-        // (1) stage the tile's K and V rows and scales
+        // (1) stage the tile: every byte is dequantised once, (f32(q) - 128) * s
+        //     (dequantize_q8, kv_cache.rs:122-128), into f32 rows
         for (int i = tid; i < n_here * row16; i += blockDim.x) {
             const int r = i / row16, c16 = i % row16;
             const uint4 kv = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + tb + r) * hd)[c16];
             const uint4 vv = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + tb + r) * hd)[c16];
-            *reinterpret_cast<uint4*>(sm.k_rows + r * kRowPad + c16 * 16) = kv;
-            *reinterpret_cast<uint4*>(sm.v_rows + r * kRowPad + c16 * 16) = vv;
-        }
-        for (int r = tid; r < n_here; r += blockDim.x) {
-            sm.k_s[r] = a.cache.k_s[row_base + tb + r];
-            sm.v_s[r] = a.cache.v_s[row_base + tb + r];
+            const float ks = a.cache.k_s[row_base + tb + r], vs = a.cache.v_s[row_base + tb + r];
+            const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
+            float* kdst = &sm.kf[r][(c16 * 16) >> 6][(c16 * 16) & 63];
+            float* vdst = &sm.vf[r][c16 * 16];
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                float4 ko, vo;
+                ko.x = __fmul_rn((float)(kw[wi] & 0xffu) - 128.0f, ks);
+                ko.y = __fmul_rn((float)((kw[wi] >> 8) & 0xffu) - 128.0f, ks);
+                ko.z = __fmul_rn((float)((kw[wi] >> 16) & 0xffu) - 128.0f, ks);
+                ko.w = __fmul_rn((float)(kw[wi] >> 24) - 128.0f, ks);
+                vo.x = __fmul_rn((float)(vw[wi] & 0xffu) - 128.0f, vs);
+                vo.y = __fmul_rn((float)((vw[wi] >> 8) & 0xffu) - 128.0f, vs);
+                vo.z = __fmul_rn((float)((vw[wi] >> 16) & 0xffu) - 128.0f, vs);
+                vo.w = __fmul_rn((float)(vw[wi] >> 24) - 128.0f, vs);
+                *reinterpret_cast<float4*>(kdst + 4 * wi) = ko;
+                *reinterpret_cast<float4*>(vdst + 4 * wi) = vo;
+            }
         }
         __syncthreads();
         STAMP(3);
-        // (2) scores: item = (head, position); position runs over lanes, so q is a broadcast
-        for (int it = tid; it < nrep * kTilePos; it += blockDim.x) {
-            const int h = it / kTilePos, r = it % kTilePos;
-            if (r < n_here) {
-                const uint8_t* row = sm.k_rows + r * kRowPad;
-                const float ks = sm.k_s[r];
-                double d4[4] = {0.0, 0.0, 0.0, 0.0};  // four independent chains, one per byte lane
-                for (int c16 = 0; c16 < row16; ++c16) {
-                    const uint4 pk = *reinterpret_cast<const uint4*>(row + c16 * 16);
-                    const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
-#pragma unroll
-                    for (int wi = 0; wi < 4; ++wi)
-#pragma unroll
-                        for (int bi = 0; bi < 4; ++bi) {
-                            // dequantize_q8, kv_cache.rs:122-128: (f32(q) - 128) * s
-                            const float kf = __fmul_rn((float)((wds[wi] >> (8 * bi)) & 0xffu) - 128.0f, ks);
-                            d4[bi] = fma(sm.qs[h][c16 * 16 + wi * 4 + bi], (double)kf, d4[bi]);
-                        }
+        // (2) scores: item = (head, position, half of the head dims); the two halves sit in
+        //     neighbouring lanes and are added with one shuffle
+        for (int it = tid; it < nrep * kTilePos * 2; it += blockDim.x) {
+            const int hf = it & 1, r = (it >> 1) % kTilePos, h = it / (2 * kTilePos);
+            const int c0 = hf * 64, cn = min(64, hd - c0);
+            double d0 = 0.0, d1 = 0.0;
+            if (r < n_here && cn > 0) {
+                const float* row = sm.kf[r][hf];
+                const float* qh = sm.qs[h] + c0;
+#pragma unroll 4
+                for (int c = 0; c < cn; c += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(row + c);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qh + c);
+                    d0 = fma((double)q4.x, (double)k4.x, d0);
+                    d1 = fma((double)q4.y, (double)k4.y, d1);
+                    d0 = fma((double)q4.z, (double)k4.z, d0);
+                    d1 = fma((double)q4.w, (double)k4.w, d1);
                 }
-                const double d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-                sm.sc[h][r] = __fmul_rn((float)d, a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
             }
+            double d = d0 + d1;
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            if (hf == 0 && r < n_here) sm.sc[h][r] = __fmul_rn((float)d, a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
         }
         __syncthreads();
         STAMP(4);
@@ -208,18 +221,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         }
         __syncthreads();
         STAMP(5);
-        // (4) acc[head, dim] = acc * corr + sum_r p[head, r] * v[r, dim]
+        // (4) acc[head, dim] = acc * corr + sum_r p[head, r] * v[r, dim], two chains per thread
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             const int it = tid + e * kAttnThreads;
             if (it < n_out) {
                 const int h = it / hd, dcol = it % hd;
-                double v = acc[e] * sm.corr[h];
-                for (int r = 0; r < n_here; ++r) {
-                    const float vf = __fmul_rn((float)sm.v_rows[r * kRowPad + dcol] - 128.0f, sm.v_s[r]);
-                    v = fma(sm.pw[h][r], (double)vf, v);
+                double v0 = acc[e] * sm.corr[h], v1 = 0.0;
+                int r = 0;
+                for (; r + 1 < n_here; r += 2) {
+                    v0 = fma(sm.pw[h][r], (double)sm.vf[r][dcol], v0);
+                    v1 = fma(sm.pw[h][r + 1], (double)sm.vf[r + 1][dcol], v1);
                 }
-                acc[e] = v;
+                if (r < n_here) v0 = fma(sm.pw[h][r], (double)sm.vf[r][dcol], v0);
+                acc[e] = v0 + v1;
             }
         }
         __syncthreads();
@@ -236,6 +251,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     }
     }  // !empty
     STAMP(6);
+    // only now may the next kernel's CTAs move in: earlier they would take the registers and
+    // shared memory that this kernel's later CTAs are waiting for
+    ptx::pdl_launch_dependents();
 
     // The last CTA of this (sequence, KV head) to get here merges the spans:
     // out = sum_s e^{m_s - m} acc_s / sum_s e^{m_s - m} l_s, rounded to f32 once.
@@ -249,22 +267,45 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     __threadfence();
     if (tid == 0) a.counters[blockIdx.x] = 0;  // ready for the next launch
     const double* group = a.partial + ((int64_t)b * a.n_heads + kvh * nrep) * a.splits * (hd + 2);
+    // per-span maxima and sums first (one batch of independent loads), weights w_s = e^{m_s - m}
+    double* mw = reinterpret_cast<double*>(sm.vf);          // [nrep][splits] weights (the tile buffers are free now)
+    double* lsum = mw + kMaxRep * 64;                        // [nrep] merged denominators
+    for (int i = tid; i < nrep * a.splits; i += blockDim.x) {
+        const int h = i / a.splits, s2 = i % a.splits;
+        mw[h * 64 + s2] = __ldcg(group + ((int64_t)h * a.splits + s2) * (hd + 2));
+    }
+    __syncthreads();
+    if (warp < nrep) {
+        const int h = warp;
+        double m = -INFINITY;
+        for (int s2 = lane; s2 < a.splits; s2 += 32) m = fmax(m, mw[h * 64 + s2]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmax(m, __shfl_xor_sync(0xffffffffu, m, o));
+        double l = 0.0;
+        for (int s2 = lane; s2 < a.splits; s2 += 32) {
+            const double ms = mw[h * 64 + s2];
+            const double w = ms == -INFINITY ? 0.0 : exp(ms - m);  // spans without positions weigh nothing
+            const double ls = __ldcg(group + ((int64_t)h * a.splits + s2) * (hd + 2) + 1);
+            l = fma(ls, w, l);
+            mw[h * 64 + s2] = w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) lsum[h] = l;
+    }
+    __syncthreads();
     for (int it = tid; it < nrep * hd; it += blockDim.x) {
         const int h = it / hd, c = it % hd;
-        const double* base = group + (int64_t)h * a.splits * (hd + 2);
-        double m = -INFINITY, l = 0.0, v = 0.0;
-        for (int s2 = 0; s2 < a.splits; ++s2) {
-            const double ms = __ldcg(base + s2 * (hd + 2));
-            const double ls = __ldcg(base + s2 * (hd + 2) + 1);
-            const double vs2 = __ldcg(base + s2 * (hd + 2) + 2 + c);
-            if (ms == -INFINITY) continue;  // span without positions yet
-            const double m_new = fmax(m, ms);
-            const double c_old = exp(m - m_new), c_new = exp(ms - m_new);  // exp(-inf) = 0 at first
-            l = fma(l, c_old, ls * c_new);
-            v = fma(v, c_old, vs2 * c_new);
-            m = m_new;
+        const double* base = group + (int64_t)h * a.splits * (hd + 2) + 2 + c;
+        double v0 = 0.0, v1 = 0.0;
+        int s2 = 0;
+#pragma unroll 4
+        for (; s2 + 1 < a.splits; s2 += 2) {
+            v0 = fma(__ldcg(base + (int64_t)s2 * (hd + 2)), mw[h * 64 + s2], v0);
+            v1 = fma(__ldcg(base + (int64_t)(s2 + 1) * (hd + 2)), mw[h * 64 + s2 + 1], v1);
         }
-        const float o = (float)(v / l);
+        if (s2 < a.splits) v0 = fma(__ldcg(base + (int64_t)s2 * (hd + 2)), mw[h * 64 + s2], v0);
+        const float o = (float)((v0 + v1) / lsum[h]);
         a.out[((int64_t)b * a.n_heads + kvh * nrep + h) * hd + c] = o;
         if (a.absmax_out) {
             float mx = fabsf(o);
@@ -297,12 +338,17 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e0 = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)sizeof(AttnSmem));
+                                              (int)(sizeof(AttnSmem) > 116 * 1024 ? sizeof(AttnSmem) : 116 * 1024));
         if (e0 != cudaSuccess) return e0;
         configured = true;
     }
     dim3 grid(a.batch * a.n_kv, a.splits);
-    return launch_pdl(attn_decode_kernel, grid, dim3(kAttnThreads), sizeof(AttnSmem), stream, a.pdl, a);
+    // When the whole grid fits one CTA per SM, ask for more than half of an SM's shared
+    // memory: the block scheduler then cannot pair two CTAs on one SM while others idle
+    // (measured: paired CTAs take 22 us instead of 16).
+    size_t smem = sizeof(AttnSmem);
+    if ((int64_t)grid.x * grid.y <= a.sm_count && smem < 116 * 1024) smem = 116 * 1024;
+    return launch_pdl(attn_decode_kernel, grid, dim3(kAttnThreads), smem, stream, a.pdl, a);
 }
 
 cudaError_t launch_rope_tables(const float* inv_freq, int max_seq, int half, float* cos_t, float* sin_t,

@@ -58,6 +58,7 @@ struct AttnArgs {
     float* out;              // [batch, n_heads*head_dim]
     double* partial;         // scratch [batch, n_heads, splits, head_dim + 2] (max, sum, acc)
     int batch, n_heads, n_kv, head_dim;
+    int sm_count;            // SMs of the device
     int splits;              // spans per sequence (grid.y)
     int span;                // positions per span, multiple of 32
     float scaling;

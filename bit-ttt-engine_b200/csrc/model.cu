@@ -153,6 +153,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.out = m->att;
             a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
+            a.sm_count = sm;
             attn_plan(batch, c.n_kv_heads, c.max_position_embeddings, sm, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = amax_core;
@@ -204,6 +205,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.out = m->att;
             a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
+            a.sm_count = sm;
             attn_plan(batch, c.n_kv_heads, c.max_position_embeddings, sm, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = nullptr;

@@ -21,13 +21,13 @@ cudaError_t upload_inv_freq(float* dev, int head_dim, double theta) {
 }
 
 // Cuts the positions of a sequence into fixed spans so that batch * n_kv * splits CTAs
-// roughly fill the GPU: span is a multiple of 128 (4 warps x 32 positions), at most 64 spans.
+// roughly fill the GPU: span is a multiple of 64 (one tile), at most 64 spans.
 void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* splits, int* span) {
-    int64_t want = (2 * (int64_t)sm_count + batch * n_kv - 1) / (batch * n_kv);
+    int64_t want = ((int64_t)sm_count + batch * n_kv - 1) / (batch * n_kv);
     if (want > 64) want = 64;
     if (want < 1) want = 1;
     int64_t sp = (max_seq + want - 1) / want;
-    sp = (sp + 127) / 128 * 128;
+    sp = (sp + 63) / 64 * 64;
     *span = (int)sp;
     *splits = (int)((max_seq + sp - 1) / sp);
 }
@@ -156,7 +156,8 @@ extern "C" bt_status bt_attn_decode(bt_kv_cache* c, const float* qkv_dev, const 
     a.out = out_dev;
     a.partial = c->partial;
     a.batch = (int)batch; a.n_heads = (int)n_heads; a.n_kv = (int)c->n_kv; a.head_dim = (int)c->head_dim;
-    attn_plan(batch, c->n_kv, c->max_seq, device_sm_count(c->device), &a.splits, &a.span);
+    a.sm_count = device_sm_count(c->device);
+    attn_plan(batch, c->n_kv, c->max_seq, a.sm_count, &a.splits, &a.span);
     a.scaling = (float)(1.0 / sqrt((double)c->head_dim));  // layers/attention.rs:114
     a.absmax_out = nullptr;
     a.pdl = false;
