@@ -15,9 +15,11 @@ and host next-token ids out every step; `roofline` is the ternary GEMV alone (al
 bytes per launch / average launch time, measured in this run); `cpu_baseline` is the CPU
 oracle timed on this host on a bounded sample.
 
-With --gpus N > 1 (torchrun, one rank per GPU) every rank decodes its own sequences with
-its own replica of the model: the path has no tensor-parallel sharding yet, so this is
-"replicas only" and no collective is on the data path.
+With --gpus N > 1 (torchrun, one rank per GPU) the model is tensor-parallel over the N GPUs:
+q|k|v and gate|up split by rows, o_proj and down_proj by input columns with an
+all-reduce(max) of the activation absmax and an all-reduce(sum) of the int32 accumulators
+(NCCL over NVLink), lm_head replicated.  All ranks decode the SAME B sequences, so the total
+work is fixed and the scaling is strong.
 """
 from __future__ import annotations
 
@@ -97,7 +99,7 @@ class ClockSampler:
 # workload
 # ---------------------------------------------------------------------------------------
 
-def build_8b(bt, syn, batch, max_pos, seed=4000):
+def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0):
     """Random-init Llama-3-8B-shaped ternary model.  Layer 0's host arrays are reused for
     every layer (each layer still owns its own device copy, so HBM traffic is real); the
     embedding and lm_head are one N(0, 0.02) block tiled over the vocabulary."""
@@ -111,7 +113,7 @@ def build_8b(bt, syn, batch, max_pos, seed=4000):
     for kind, (n, k) in syn.linear_shapes(cfg).items():
         layer[kind] = (syn._ternary_codes(rng, n, k), 0.016, n, k)
     w.layers = [layer] * cfg.num_layers
-    return cfg, w, syn.build_model(w, max_batch=batch)
+    return cfg, w, syn.build_model(w, max_batch=batch, device=device, tp_rank=tp_rank, tp_size=tp_size)
 
 
 def cpu_decode_baseline(cfg, syn, budget_s=20.0):
@@ -215,10 +217,14 @@ def main():
 
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     max_pos = args.context + W + 2 * K + 16
-    cfg, weights, model = build_8b(bt, syn, B, max_pos)
+    cfg, weights, model = build_8b(bt, syn, B, max_pos, tp_rank=rank, tp_size=world, device=local_rank)
     del weights
+    if world > 1:
+        uid = [bt.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        model.tp_init(uid[0])
     dev = torch.device(f"cuda:{local_rank}")
-    rng = np.random.default_rng(11 + rank)
+    rng = np.random.default_rng(11)  # every rank feeds the same ids
 
     def barrier():
         if world > 1:
@@ -255,7 +261,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
-    value = world * B * K / (ms_max * 1e-3)
+    value = B * K / (ms_max * 1e-3)
 
     # ---- end to end: host ids in, host ids out, every step ---------------------------------
     ids = rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)
@@ -270,7 +276,7 @@ def main():
     t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * B * K / float(t.item())
+    e2e_value = B * K / float(t.item())
 
     # ---- roofline of the dominant kernel: the ternary GEMV launches of a step, alone -------
     peak, peak_kind = measured_peaks()
@@ -310,10 +316,11 @@ def main():
         cpu = None if args.no_cpu_baseline else cpu_decode_baseline(cfg, syn)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None,
             "dtype": "int8 x ternary -> int32 (f32 epilogue, bf16 lm_head)", "data": "synthetic",
-            "config": {"workload": f"Llama-3-8B-shaped ternary decode, batch {B} per GPU, context {args.context}+",
-                       "batch": B, "context": args.context, "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+            "config": {"workload": f"Llama-3-8B-shaped ternary decode, batch {B}, context {args.context}+",
+                       "batch": B, "context": args.context, "parallelism": f"tp{world}" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: 1.74 GB of ternary tiles + 1.05 GB lm_head per step"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": model.launches_per_step(B) * K,

@@ -77,7 +77,7 @@ from .layers import (  # noqa: E402
 )
 
 from .model import (  # noqa: E402
-    BitLlama, BitLlamaConfig, QuantizedKVCache, attn_decode, ttt_update,
+    BitLlama, BitLlamaConfig, QuantizedKVCache, attn_decode, tp_unique_id, ttt_update,
 )
 from . import model  # noqa: E402,F401
 

@@ -49,7 +49,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", LIB_PATH, *sources()]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", LIB_PATH, *sources(), "-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     proc = subprocess.run(cmd, capture_output=True, text=True)

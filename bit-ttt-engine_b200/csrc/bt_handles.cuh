@@ -48,3 +48,14 @@ namespace bt {
 bt_status create_gate_up(bt_linear** out, const uint8_t* gate_packed_host, const uint8_t* up_packed_host,
                          int64_t rows, int64_t k_in, float gate_scale, float up_scale, int device);
 }  // namespace bt
+
+namespace bt {
+// tensor-parallel plumbing (tp.cu)
+bt_status tp_unique_id(void* out128);
+bt_status tp_comm_init(void** comm, const void* id128, int rank, int size);
+void tp_comm_destroy(void* comm);
+bt_status tp_allreduce_max_f32(void* comm, float* buf, size_t count, cudaStream_t s);
+bt_status tp_allreduce_sum_i32(void* comm, int32_t* buf, size_t count, cudaStream_t s);
+cudaError_t launch_tp_residual(const int32_t* acc, const unsigned int* absmax, float sw, int m, int n, float* h,
+                               cudaStream_t s, bool pdl);
+}  // namespace bt

@@ -59,6 +59,10 @@ struct bt_model {
     int device = 0;
     int sm_count = 0;
     int head_dim = 0, d_small = 0, qkv_dim = 0;
+    int tp = 1;                      // tensor-parallel degree
+    int nh_l = 0, nkv_l = 0, i_l = 0;  // this rank's query heads, KV heads, MLP columns
+    void* comm = nullptr;            // NCCL communicator when tp > 1
+    int32_t* acc_i32 = nullptr;      // [max_batch, hidden] accumulators of a row-parallel projection
     bool finalized = false;
     std::vector<Layer> layers;
     __nv_bfloat16* embed = nullptr;
@@ -127,7 +131,8 @@ bt_status make_linear(bt_model* m, HostLinear** parts, int n_parts, bt_linear** 
 //            [norm2+quant+gate|up+SiLU*up]  [quant+down+residual].
 bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
     const bt_model_config& c = m->cfg;
-    const int H = c.hidden_dim, I = c.intermediate_dim, B = c.max_batch;
+    const int H = c.hidden_dim, I = m->i_l, B = c.max_batch;
+    const int att_dim = m->nh_l * m->head_dim;  // this rank's attention output width
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
     BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, true));
@@ -152,21 +157,38 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.counters = L.kv->counters;
             a.out = m->att;
             a.partial = m->attn_partial;
-            a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
+            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim;
             a.sm_count = sm;
-            attn_plan(batch, c.n_kv_heads, c.max_position_embeddings, sm, &a.splits, &a.span);
+            attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = amax_core;
             a.pdl = true;
             a.dbg = g_dbg_base ? g_dbg_base + (size_t)(g_dbg_slot++) * 4 * 512 : nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
-            FusedIn ain{PRO_ABSMAX, m->att, H, nullptr, 0.f, amax_core};
-            BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
+            FusedIn ain{PRO_ABSMAX, m->att, att_dim, nullptr, 0.f, amax_core};
+            if (m->tp > 1) {
+                // row-parallel: same quantisation scale on every rank, integer sum over the ranks
+                bt_status st = tp_allreduce_max_f32(m->comm, reinterpret_cast<float*>(amax_core), (size_t)batch, s);
+                if (st != BT_OK) return st;
+                BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
+                if ((st = tp_allreduce_sum_i32(m->comm, m->acc_i32, (size_t)batch * H, s)) != BT_OK) return st;
+                BT_CUDA_TRY(launch_tp_residual(m->acc_i32, amax_core, L.o->scales[0], batch, H, m->h, s, true));
+            } else {
+                BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
+            }
         }
         FusedIn norm2{PRO_RMSNORM, m->h, H, L.norm2, kRmsEps, nullptr};
         BT_CUDA_TRY(linear_product_fused(L.gate_up_il->dev(), norm2, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, sm, s));
         FusedIn din{PRO_ABSMAX, m->act, I, nullptr, 0.f, amax_mlp};
-        BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
+        if (m->tp > 1) {
+            bt_status st = tp_allreduce_max_f32(m->comm, reinterpret_cast<float*>(amax_mlp), (size_t)batch, s);
+            if (st != BT_OK) return st;
+            BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
+            if ((st = tp_allreduce_sum_i32(m->comm, m->acc_i32, (size_t)batch * H, s)) != BT_OK) return st;
+            BT_CUDA_TRY(launch_tp_residual(m->acc_i32, amax_mlp, L.down->scales[0], batch, H, m->h, s, true));
+        } else {
+            BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
+        }
     }
     int n_cand = 0;
     BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
@@ -178,7 +200,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
 // Enqueues one decode step for `batch` sequences on `s` (separate quantiser kernels; any batch).
 bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     const bt_model_config& c = m->cfg;
-    const int H = c.hidden_dim, I = c.intermediate_dim;
+    const int H = c.hidden_dim, I = m->i_l;
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
     BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s));
@@ -257,12 +279,26 @@ extern "C" bt_status bt_model_create(bt_model** out, const bt_model_config* cfg,
     if (!guard.ok || !device_error_word(device)) return set_error(BT_ERR_DEVICE, "bt_model_create: cannot use device %d", device);
     bt_model* m = new (std::nothrow) bt_model();
     if (!m) return set_error(BT_ERR_NOMEM, "host allocation failed");
+    const int tp = c.tp_size > 1 ? c.tp_size : 1;
+    if (tp > 1) {
+        if (c.arch != 1) { delete m; return set_error(BT_ERR_ARG, "bt_model_create: tensor parallelism needs arch llama"); }
+        if (c.tp_rank < 0 || c.tp_rank >= tp || c.n_kv_heads % tp != 0 || c.n_heads % tp != 0 ||
+            c.intermediate_dim % (16 * tp) != 0 || c.max_batch > 8) {
+            delete m;
+            return set_error(BT_ERR_SHAPE, "bt_model_create: tp_size %d must divide n_kv_heads, n_heads and intermediate_dim/16 "
+                                           "(rank in range, max_batch <= 8)", tp);
+        }
+    }
     m->cfg = c;
+    m->tp = tp;
     m->device = device;
     m->sm_count = device_sm_count(device);
     m->head_dim = c.arch == 1 ? c.hidden_dim / c.n_heads : 0;
     m->d_small = c.hidden_dim / 4;  // layers/ttt.rs:29
-    m->qkv_dim = c.arch == 1 ? (c.n_heads + 2 * c.n_kv_heads) * m->head_dim : 0;
+    m->nh_l = c.arch == 1 ? c.n_heads / tp : 0;
+    m->nkv_l = c.arch == 1 ? c.n_kv_heads / tp : 0;
+    m->i_l = c.intermediate_dim / tp;
+    m->qkv_dim = c.arch == 1 ? (m->nh_l + 2 * m->nkv_l) * m->head_dim : 0;
     m->layers.resize((size_t)c.num_layers);
     *out = m;
     return BT_OK;
@@ -275,12 +311,12 @@ extern "C" bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind 
     if (layer < 0 || layer >= m->cfg.num_layers || (int)kind < 0 || (int)kind > 8)
         return set_error(BT_ERR_ARG, "bt_model_set_linear: layer %d / kind %d out of range", layer, (int)kind);
     const bt_model_config& c = m->cfg;
-    const int64_t H = c.hidden_dim, I = c.intermediate_dim, hd = m->head_dim, d = m->d_small;
+    const int64_t H = c.hidden_dim, I = m->i_l, hd = m->head_dim, d = m->d_small;
     int64_t en = 0, ek = 0;
     switch (kind) {
-        case BT_W_Q: en = c.n_heads * hd; ek = H; break;
-        case BT_W_K: case BT_W_V: en = c.n_kv_heads * hd; ek = H; break;
-        case BT_W_O: en = H; ek = c.n_heads * hd; break;
+        case BT_W_Q: en = m->nh_l * hd; ek = H; break;
+        case BT_W_K: case BT_W_V: en = m->nkv_l * hd; ek = H; break;
+        case BT_W_O: en = H; ek = m->nh_l * hd; break;
         case BT_W_GATE: case BT_W_UP: en = I; ek = H; break;
         case BT_W_DOWN: en = H; ek = I; break;
         case BT_W_TTT_DOWN: en = d; ek = H; break;
@@ -338,7 +374,7 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
     const bt_model_config& c = m->cfg;
     DeviceGuard guard(m->device);
     if (!m->embed || !m->lm_head || !m->norm_f) return set_error(BT_ERR_ARG, "bt_model_finalize: embedding, lm_head or final norm missing");
-    const int B = c.max_batch, H = c.hidden_dim, I = c.intermediate_dim;
+    const int B = c.max_batch, H = c.hidden_dim, I = m->i_l;
     for (auto& L : m->layers) {
         if (!L.norm1 || !L.norm2) return set_error(BT_ERR_ARG, "bt_model_finalize: a layer norm weight is missing");
         bt_status st;
@@ -347,7 +383,7 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
             if ((st = make_linear(m, qkv, 3, &L.qkv)) != BT_OK) return st;
             HostLinear* o[1] = {&L.host[BT_W_O]};
             if ((st = make_linear(m, o, 1, &L.o)) != BT_OK) return st;
-            if ((st = bt_kv_create(&L.kv, B, c.n_kv_heads, m->head_dim, c.max_position_embeddings, m->device)) != BT_OK) return st;
+            if ((st = bt_kv_create(&L.kv, B, m->nkv_l, m->head_dim, c.max_position_embeddings, m->device)) != BT_OK) return st;
         } else {
             HostLinear* dn[1] = {&L.host[BT_W_TTT_DOWN]};
             if ((st = make_linear(m, dn, 1, &L.ttt_down)) != BT_OK) return st;
@@ -396,6 +432,7 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
         BT_CUDA_TRY(launch_rope_tables(m->inv_freq, c.max_position_embeddings, m->head_dim / 2, m->rope_cos, m->rope_sin, 0));
         BT_CUDA_TRY(cudaDeviceSynchronize());
         BT_CUDA_TRY(dev_alloc(&m->attn_partial, (size_t)B * c.n_heads * 64 * (m->head_dim + 2)));
+        if (m->tp > 1) BT_CUDA_TRY(dev_alloc(&m->acc_i32, (size_t)B * H));
     } else {
         BT_CUDA_TRY(dev_alloc(&m->feat, (size_t)B * m->d_small));
         BT_CUDA_TRY(dev_alloc(&m->z, (size_t)B * m->d_small));
@@ -420,11 +457,12 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32};
     for (void* p : bufs) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
     if (m->stream) cudaStreamDestroy(m->stream);
+    if (m->comm) tp_comm_destroy(m->comm);
     delete m;
     return BT_OK;
 }
@@ -445,6 +483,7 @@ extern "C" bt_status bt_model_reset(bt_model* m) {
 namespace {
 
 bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
+    if (m->tp > 1 && !m->comm) return set_error(BT_ERR_NCCL, "tensor-parallel model used before bt_model_tp_init");
     if (m->cfg.arch == 1 && m->host_pos >= m->cfg.max_position_embeddings)
         return set_error(BT_ERR_SHAPE, "position %d reaches max_position_embeddings %d", m->host_pos, m->cfg.max_position_embeddings);
     // first call at a batch size runs eagerly (it also sets kernel attributes); the second
@@ -547,7 +586,7 @@ extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
     if (!m) return 0;
     if (batch <= 8) {
         // fused path: per layer 4 products + attention pair or TTT update; embedding, lm_head per 4 tokens, pick
-        const int per_layer = 4 + 1;  // 4 products + attention or TTT update
+        const int per_layer = 4 + 1 + (m->tp > 1 ? 2 : 0);  // 4 products + attention or TTT update (+ 2 scale epilogues after the all-reduces)
         return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
     }
     const int groups = (batch + 7) / 8;
@@ -576,3 +615,16 @@ extern "C" bt_status bt_model_seek(bt_model* m, int pos) {
 // Development aid: fused product launches enqueued after this call stamp their timeline
 // (entry / after dependency wait / after activation staging / end) into buf[slot][cta][4].
 extern "C" void bt_debug_timeline(unsigned long long* buf) { bt::g_dbg_base = buf; bt::g_dbg_slot = 0; }
+
+extern "C" bt_status bt_tp_unique_id(uint8_t* id128_out) {
+    if (!id128_out) return set_error(BT_ERR_ARG, "bt_tp_unique_id: null pointer");
+    return tp_unique_id(id128_out);
+}
+
+extern "C" bt_status bt_model_tp_init(bt_model* m, const uint8_t* id128) {
+    if (!m || !m->finalized || !id128) return set_error(BT_ERR_ARG, "bt_model_tp_init: null pointer or model not finalized");
+    if (m->tp <= 1) return BT_OK;
+    if (m->comm) return BT_OK;
+    DeviceGuard guard(m->device);
+    return tp_comm_init(&m->comm, id128, m->cfg.tp_rank, m->tp);
+}

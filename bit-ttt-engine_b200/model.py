@@ -19,7 +19,8 @@ class _CModelConfig(C.Structure):
     _fields_ = [("arch", C.c_int), ("vocab_size", C.c_int), ("hidden_dim", C.c_int),
                 ("num_layers", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int),
                 ("intermediate_dim", C.c_int), ("inner_lr", C.c_float), ("rope_theta", C.c_double),
-                ("max_position_embeddings", C.c_int), ("max_batch", C.c_int)]
+                ("max_position_embeddings", C.c_int), ("max_batch", C.c_int),
+                ("tp_rank", C.c_int), ("tp_size", C.c_int)]
 
 
 def _bind():
@@ -53,6 +54,8 @@ def _bind():
     L.bt_model_kv_cache.argtypes = [vp, i32]
     L.bt_model_ternary_bytes.restype = i64
     L.bt_model_ternary_bytes.argtypes = [vp]
+    L.bt_tp_unique_id.argtypes = [vp]
+    L.bt_model_tp_init.argtypes = [vp, vp]
     L.bt_model_seek.argtypes = [vp, i32]
     L.bt_model_enqueue_products.argtypes = [vp, i32, vp, C.POINTER(i32)]
     L.bt_model_launches_per_step.argtypes = [vp, i32]
@@ -140,12 +143,14 @@ class BitLlamaConfig:
 class BitLlama:
     """model/llama.rs:37-272: load weights, forward_one, reset_kv_cache."""
 
-    def __init__(self, cfg: BitLlamaConfig, max_batch: int = 1, device: int = 0):
+    def __init__(self, cfg: BitLlamaConfig, max_batch: int = 1, device: int = 0, tp_rank: int = 0,
+                 tp_size: int = 1):
         self._L = _bind()
         self.cfg, self.max_batch, self.device = cfg, max_batch, device
+        self.tp_rank, self.tp_size = tp_rank, tp_size
         cc = _CModelConfig(ARCH_TTT if cfg.arch == "ttt" else ARCH_LLAMA, cfg.vocab_size, cfg.hidden_dim,
                            cfg.num_layers, cfg.n_heads, cfg.n_kv_heads, cfg.intermediate_dim, cfg.inner_lr,
-                           cfg.rope_theta, cfg.max_position_embeddings, max_batch)
+                           cfg.rope_theta, cfg.max_position_embeddings, max_batch, tp_rank, tp_size)
         self._h = C.c_void_p()
         check(self._L.bt_model_create(C.byref(self._h), C.byref(cc), device))
 
@@ -159,6 +164,11 @@ class BitLlama:
 
     def finalize(self):
         check(self._L.bt_model_finalize(self._h))
+
+    def tp_init(self, unique_id: bytes):
+        """Joins the tensor-parallel communicator (collective); unique_id from tp_unique_id() of rank 0."""
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        check(self._L.bt_model_tp_init(self._h, buf))
 
     def reset_kv_cache(self):
         check(self._L.bt_model_reset(self._h))
@@ -219,7 +229,7 @@ class BitLlama:
         if not p:
             return None
         c = self.cfg
-        return QuantizedKVCache(c.max_position_embeddings, self.max_batch, c.n_kv_heads,
+        return QuantizedKVCache(c.max_position_embeddings, self.max_batch, c.n_kv_heads // max(self.tp_size, 1),
                                 c.hidden_dim // c.n_heads, self.device, _borrowed=p)
 
     def __del__(self):
@@ -229,6 +239,13 @@ class BitLlama:
                 self._h = None
         except Exception:
             pass
+
+
+def tp_unique_id() -> bytes:
+    """128-byte communicator id; create on rank 0 and send to the other ranks by any means."""
+    buf = (C.c_uint8 * 128)()
+    check(_bind().bt_tp_unique_id(buf))
+    return bytes(buf)
 
 
 def _wrap_dev(ptr: int, shape, dtype, device: int):

@@ -85,8 +85,44 @@ def make_weights(cfg: BitLlamaConfig, seed: int = 2000, from_latent: bool = True
     return w
 
 
-def build_model(w: SyntheticWeights, max_batch: int = 1, device: int = 0) -> BitLlama:
-    m = BitLlama(w.cfg, max_batch=max_batch, device=device)
+def shard_weights(w: SyntheticWeights, rank: int, size: int) -> SyntheticWeights:
+    """This rank's tensor-parallel shard: q/k/v by heads and gate/up by rows (column-parallel),
+    o_proj and down_proj by packed input columns (row-parallel); everything else replicated."""
+    if size <= 1:
+        return w
+    cfg = w.cfg
+    hd = cfg.hidden_dim // cfg.n_heads
+    out = SyntheticWeights(cfg, w.embed, w.lm_head, w.norm_f)
+    cache = {}
+    for layer in w.layers:
+        if id(layer) in cache:
+            out.layers.append(cache[id(layer)])
+            continue
+        new = {"norm1": layer["norm1"], "norm2": layer["norm2"]}
+        for kind, val in layer.items():
+            if not isinstance(kind, int):
+                continue
+            packed, scale, n, k = val
+            packed = np.ascontiguousarray(packed).reshape(n, k // 4)
+            if kind in (W_Q, W_K, W_V, W_GATE, W_UP):      # split output rows
+                rows = n // size
+                new[kind] = (np.ascontiguousarray(packed[rank * rows:(rank + 1) * rows]), scale, rows, k)
+            elif kind in (W_O, W_DOWN):                     # split input columns (4 per byte)
+                cols = k // size
+                assert cols % 4 == 0
+                new[kind] = (np.ascontiguousarray(packed[:, rank * cols // 4:(rank + 1) * cols // 4]), scale, n, cols)
+            else:
+                raise ValueError("tensor parallelism covers arch llama only")
+        cache[id(layer)] = new
+        out.layers.append(new)
+    del hd
+    return out
+
+
+def build_model(w: SyntheticWeights, max_batch: int = 1, device: int = 0, tp_rank: int = 0,
+                tp_size: int = 1) -> BitLlama:
+    w = shard_weights(w, tp_rank, tp_size)
+    m = BitLlama(w.cfg, max_batch=max_batch, device=device, tp_rank=tp_rank, tp_size=tp_size)
     m.set_tensor(T_EMBED, w.embed)
     m.set_tensor(T_LM_HEAD, w.lm_head)
     m.set_tensor(T_NORM_F, w.norm_f)

@@ -217,6 +217,8 @@ typedef struct {
     double rope_theta;            /* default 10000 (RE/model/config.rs:61-63) */
     int max_position_embeddings;  /* default 2048 (RE/model/config.rs:64-66) */
     int max_batch;                /* sequences decoded together, >= 1 */
+    int tp_rank;                  /* tensor-parallel rank of this process (0 when tp_size <= 1) */
+    int tp_size;                  /* tensor-parallel degree: 0 or 1 = none; else it divides n_kv_heads */
 } bt_model_config;
 
 typedef enum {
@@ -237,6 +239,19 @@ typedef enum {
  * and norms as f32 host arrays (the engine loads everything as F32, :414-415; embedding
  * and head are kept in bf16 on the device). */
 bt_status bt_model_create(bt_model** out, const bt_model_config* cfg, int device);
+
+/* Tensor parallelism (an addition: the reference is single-GPU, RE/model/llama.rs:43,404).
+ * One process per GPU.  With tp_size = R > 1 (arch llama only) bt_model_set_linear takes this
+ * rank's shard: q/k/v rows of its n_heads/R query and n_kv_heads/R KV heads, gate/up rows
+ * [rank*I/R, (rank+1)*I/R), and for o_proj / down_proj the matching input COLUMNS (a
+ * [hidden, n_heads/R*head_dim] resp. [hidden, I/R] matrix).  Embedding, norms and lm_head are
+ * replicated.  Every rank computes the same hidden state bit for bit, identical to R = 1: the
+ * row-parallel projections quantise with the all-reduced max|x| and all-reduce their int32
+ * accumulators before scaling.  bt_tp_unique_id gives the 128-byte NCCL id that rank 0
+ * creates and hands to the others (any transport); bt_model_tp_init joins the communicator
+ * (collective call, after bt_model_finalize, before the first step). */
+bt_status bt_tp_unique_id(uint8_t* id128_out);
+bt_status bt_model_tp_init(bt_model* m, const uint8_t* id128);
 bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
                               int64_t n_out, int64_t k_in, float scale);
 bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int layer, const float* data_host,

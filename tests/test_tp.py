@@ -1,0 +1,42 @@
+"""Tensor parallelism: host-side arithmetic on 2 gloo ranks (CPU), and the sharded model on
+2 GPUs against the oracle."""
+import os
+import socket
+import tempfile
+
+import pytest
+
+torch = pytest.importorskip("torch")
+import torch.multiprocessing as mp  # noqa: E402
+
+import tp_common  # noqa: E402
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _results(d, world):
+    return [open(os.path.join(d, f"rank{r}.txt")).read() for r in range(world)]
+
+
+def test_row_parallel_exact_on_two_gloo_ranks(oracle):
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(tp_common.cpu_row_parallel_worker, args=(2, _free_port(), d), nprocs=2, join=True)
+        assert _results(d, 2) == ["ok", "ok"]
+
+
+@pytest.mark.gpu
+def test_tp2_model_matches_oracle_and_ranks_agree():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(tp_common.gpu_model_worker, args=(2, _free_port(), d, 8), nprocs=2, join=True)
+        res = _results(d, 2)
+        worst, same0 = res[0].split()
+        assert float(worst) <= 1e-3 and same0 == "1"
+        assert res[1].split()[1] == "1"

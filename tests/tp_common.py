@@ -1,0 +1,90 @@
+"""Worker functions of the tensor-parallel tests (importable by spawned processes)."""
+import importlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def _init(rank, world, port, backend):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group(backend, rank=rank, world_size=world)
+    return dist
+
+
+def cpu_row_parallel_worker(rank, world, port, result_dir):
+    """Host-side logic of a row-parallel BitLinear on `world` gloo ranks: shard the packed
+    columns, all-reduce(max) the per-token absmax, quantise, integer product on the shard,
+    all-reduce(sum) the int32 accumulators, scale.  Must equal the unsharded oracle bit for bit."""
+    import torch
+    from oracle import oracle as orc
+    dist = _init(rank, world, port, "gloo")
+    rng = np.random.default_rng(5)  # same data on every rank
+    m, n, k = 3, 48, 512
+    w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    packed, sw = orc.pack_l1(w)
+    packed = packed.reshape(n, k // 4)
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    cols = k // world
+    x_loc = x[:, rank * cols:(rank + 1) * cols]
+    p_loc = np.ascontiguousarray(packed[:, rank * cols // 4:(rank + 1) * cols // 4])
+    amax = torch.from_numpy(np.abs(x_loc).max(axis=1).astype(np.float32))
+    dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+    amax = amax.numpy()
+    inv = np.where(amax > 0, np.float32(127.0) / amax, 0).astype(np.float32)
+    ratio = (x_loc * inv[:, None]).astype(np.float32)
+    q = np.clip(np.sign(ratio) * np.floor(np.abs(ratio) + np.float32(0.5)), -127, 127).astype(np.int8)
+    acc = torch.from_numpy(orc.bitlinear_i32(q, p_loc, n))
+    dist.all_reduce(acc, op=dist.ReduceOp.SUM)
+    sx = (amax / np.float32(127.0)).astype(np.float32)
+    y = (acc.numpy().astype(np.float32) * np.float32(sw)) * sx[:, None]
+    ref = orc.bitlinear_q(x, packed, [sw], n)
+    ok = bool(np.array_equal(y, ref))
+    # column-parallel: rows of the output are simply split
+    rows = n // world
+    y_col = orc.bitlinear_q(x, np.ascontiguousarray(packed[rank * rows:(rank + 1) * rows]), [sw], rows)
+    ok = ok and bool(np.array_equal(y_col, ref[:, rank * rows:(rank + 1) * rows]))
+    open(os.path.join(result_dir, f"rank{rank}.txt"), "w").write("ok" if ok else "mismatch")
+    dist.destroy_process_group()
+
+
+def gpu_model_worker(rank, world, port, result_dir, n_tokens):
+    """Tensor-parallel decode of a small llama-shaped model on `world` GPUs; rank 0 checks the
+    logits against the single-process oracle, every rank checks them against rank 0's."""
+    import torch
+    dist = _init(rank, world, port, "gloo")
+    torch.cuda.set_device(rank)
+    bt = importlib.import_module("bit-ttt-engine_b200")
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    from oracle import oracle as orc
+    cfg = syn.BitLlamaConfig("llama", 1000, 256, 2, 8, 4, 512, max_position_embeddings=64)
+    w = syn.make_weights(cfg, seed=3000)
+    model = syn.build_model(w, max_batch=2, device=rank, tp_rank=rank, tp_size=world)
+    uid = [bt.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    model.tp_init(uid[0])
+    ref = orc.model_from_weights(w)
+    states = [ref.new_state(), ref.new_state()]
+    tokens = np.random.default_rng(7).integers(0, cfg.vocab_size, size=(n_tokens, 2))
+    worst, same = 0.0, True
+    for t in range(n_tokens):
+        logits, nxt = model.forward_one(tokens[t])
+        mine = torch.from_numpy(logits.copy())
+        theirs = mine.clone()
+        dist.broadcast(theirs, src=0)
+        same = same and bool(torch.equal(mine, theirs))
+        if rank == 0:
+            for b in range(2):
+                r = ref.forward_one(int(tokens[t, b]), states[b])
+                worst = max(worst, float(np.abs(logits[b] - r).max() / np.abs(r).max()))
+    bt.check(bt.lib().bt_device_check(rank))
+    open(os.path.join(result_dir, f"rank{rank}.txt"), "w").write(f"{worst} {int(same)}")
+    del model
+    dist.destroy_process_group()
