@@ -156,6 +156,14 @@ cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m,
                                  int64_t out_stride, int epilogue, unsigned int* absmax_out,
                                  unsigned int* err, int sm_count, cudaStream_t stream);
 
+// Tensor-core (tcgen05) product for more than 8 tokens: quantises x [m, k_in] f32 into the
+// residue-split layout `qtc` (gemm_tc_act_bytes(m, k_tiles) bytes), then runs the product of
+// every basis.  sx / qsum: [m] scratch for the per-token scale and sum.
+size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles);
+cudaError_t launch_gemm_tc(const LinearDev& lin, const float* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
+                           int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
+                           cudaStream_t stream);
+
 // Launch with the programmatic-stream-serialisation attribute: the kernel may start while
 // its predecessor in the stream is still running and must call griddepcontrol.wait before
 // touching anything the predecessor produces.

@@ -309,6 +309,21 @@ extern "C" bt_status bt_linear_forward(bt_linear* lin, bt_workspace* ws, const v
     st = plan_workspace(ws, m, lin->w.k_pad(), lin->w.n_out, lin->w.n_bases > 1 && y_dtype == BT_BF16, &p);
     if (st != BT_OK) return st;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (m > 8 && x_dtype == BT_F32 && !(lin->w.n_bases > 1 && y_dtype == BT_BF16) &&
+        gemm_tc_act_bytes(m, lin->w.k_tiles) <= (size_t)m * lin->w.k_pad() + 256 * 1024 &&
+        gemm_tc_act_bytes(m, lin->w.k_tiles) + 4096 <= ws->bytes) {
+        // more than 8 tokens: tensor-core path (tcgen05), activations re-laid residue-split
+        int8_t* qtc = reinterpret_cast<int8_t*>(ws->base);
+        const size_t off = align_up(gemm_tc_act_bytes(m, lin->w.k_tiles), 256);
+        if (off + (size_t)m * 8 + 512 <= ws->bytes) {
+            float* sx = reinterpret_cast<float*>(ws->base + off);
+            int32_t* qs = reinterpret_cast<int32_t*>(ws->base + off + align_up((size_t)m * 4, 256));
+            BT_CUDA_TRY(launch_gemm_tc(lin->dev(), reinterpret_cast<const float*>(x_dev), lin->w.k_in, m, qtc, sx, qs, y_dev,
+                                       lin->w.n_out, y_dtype == BT_BF16 ? EPI_BF16 : EPI_F32,
+                                       device_error_word(lin->device), device_sm_count(lin->device), s));
+            return BT_OK;
+        }
+    }
     BT_CUDA_TRY(launch_act_quant(x_dev, x_dtype, m, lin->w.k_in, p.q, lin->w.k_pad(), p.sx, p.qsum, s));
     return run_product(lin, p, m, y_dev, y_dtype, false, s);
 }

@@ -1,0 +1,390 @@
+// Batched / prefill ternary product on the 5th-generation tensor cores (tcgen05, TMEM):
+//   acc[n, m] = sum_k t[n, k] * q[m, k]   for M > 8 tokens.
+// Stands in for BitLinearCpu::forward / BitLinearCuda::forward (kernels/cpu.rs:17-127,
+// kernels/cuda.rs:21-47) at batch and prefill sizes, where the reference runs a dense f32 GEMM
+// on a host-unpacked weight.
+//
+// Roles inside one CTA (1 per SM, persistent over output tiles of 128 weight rows x NT tokens):
+//   warp 0     producer: 1-D bulk copies of the packed weight tiles (8 x 1 KB per 256-input
+//              chunk) and of the chunk's int8 activation block into a shared-memory ring;
+//   warp 1     MMA issuer (one thread): tcgen05.mma.kind::i8, A = weights (u8), B = activations
+//              (s8), both K-major without swizzle, accumulators in TMEM;
+//   warps 2-5  unpack: one AND per 16-byte register isolates field r of every byte as an
+//              unsigned multiple of 4^r and one 16-byte store puts it into the A tile of
+//              residue r, so the four field positions become four independent products
+//              with four TMEM accumulators (shifted back in the epilogue); the same warps
+//              read TMEM (tcgen05.ld) and store the outputs at the end of a tile.
+// A 2-bit field at position r of a byte multiplies the activations k = r (mod 4), hence the
+// activations are stored residue-split: B_r[m, k'] = q[m, 4k' + r].
+#include "bt_common.cuh"
+#include "bt_ptx.cuh"
+
+namespace bt {
+
+namespace {
+
+constexpr int kRows = 128;               // weight rows per tile = UMMA M
+constexpr int kChunkK = 256;             // inputs per k-chunk (one weight tile column)
+constexpr int kRawBytes = 8 * kTileBytes;  // packed weights of a chunk: 8 row tiles x 1 KB
+constexpr int kATileBytes = kRows * 64;  // unpacked A of one residue: 128 rows x 64 k'
+constexpr int kStages = 3;
+constexpr int kUnpBufs = 2;
+constexpr int kTcThreads = 6 * 32;
+constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(dst_smem)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ptx::smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrices are 8 rows x 16 bytes
+// (128 contiguous bytes); lbo = byte distance between core matrices adjacent along K,
+// sbo = byte distance between core matrices adjacent along rows.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+    return d;                // base offset 0, layout type 0 = no swizzle
+}
+
+// Instruction descriptor for kind::i8: D = s32, A = u8, B = s8, both K-major, M x N tile.
+__device__ __forceinline__ uint32_t instr_desc_i8(int m, int n) {
+    uint32_t d = 0;
+    d |= 2u << 4;                    // accumulator format: s32
+    d |= 0u << 7;                    // A format: unsigned 8-bit
+    d |= 1u << 10;                   // B format: signed 8-bit
+    d |= (uint32_t)(n >> 3) << 17;   // N / 8
+    d |= (uint32_t)(m >> 4) << 24;   // M / 16
+    return d;
+}
+
+struct TcArgs {
+    const uint8_t* tiles;      // one basis, tiled layout [row_tile][k_tile][1024]
+    int64_t row_tiles, k_tiles, n_out;
+    const int8_t* qtc;         // activations: [token_block][k_tile][4 residues][NT/8][4][8][16]
+    const int32_t* qsum;       // [m]
+    const float* sx;           // [m]
+    const float* sw_tiles;     // [row_tiles][2]
+    int m;                     // tokens
+    void* out;                 // [m, out_stride]
+    int64_t out_stride;
+    int epilogue;              // EPI_I32 / EPI_F32 / EPI_F32_ACCUM / EPI_BF16
+    unsigned int* err;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
+    constexpr int kBBytes = 4 * NT * 64;                 // activation block of a chunk (4 residues)
+    constexpr int kStageBytes = kRawBytes + kBBytes;
+    constexpr uint32_t kTmemCols = 4 * NT;               // four accumulators of NT columns
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stage_base = smem;                                           // kStages x (raw | B)
+    uint8_t* unp_base = stage_base + (size_t)kStages * kStageBytes;       // kUnpBufs x 4 x A tile
+    uint64_t* full = reinterpret_cast<uint64_t*>(unp_base + (size_t)kUnpBufs * 4 * kATileBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* unp_full = empty + kStages;
+    uint64_t* unp_empty = unp_full + kUnpBufs;
+    uint64_t* acc_full = unp_empty + kUnpBufs;
+    uint64_t* acc_empty = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_tiles = (int)a.k_tiles;
+    const int row_sets = (int)((a.row_tiles + 7) / 8);
+    const int tok_blocks = (a.m + NT - 1) / NT;
+    const int n_tiles = row_sets * tok_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1); }
+        for (int u = 0; u < kUnpBufs; ++u) { ptx::mbar_init(&unp_full[u], 128); ptx::mbar_init(&unp_empty[u], 1); }
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, 128);
+        ptx::mbar_fence_init();
+    }
+    if (warp == 1) {  // one warp allocates (and later frees) the tensor memory
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t par = 1;
+            bool first = true;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int rs = tile % row_sets, tb = tile / row_sets;
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    if (!first) ok &= ptx::mbar_wait_bounded(&empty[slot], par);
+                    uint8_t* st = stage_base + (size_t)slot * kStageBytes;
+                    const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
+                    ptx::mbar_arrive_expect_tx(&full[slot], (uint32_t)(rts * kTileBytes + kBBytes));
+                    for (int r8 = 0; r8 < rts; ++r8)
+                        ptx::bulk_g2s(st + r8 * kTileBytes,
+                                      a.tiles + (((int64_t)rs * 8 + r8) * k_tiles + kt) * kTileBytes, kTileBytes,
+                                      &full[slot]);
+                    ptx::bulk_g2s(st + kRawBytes, a.qtc + ((int64_t)tb * k_tiles + kt) * kBBytes, kBBytes, &full[slot]);
+                    if (++slot == kStages) { slot = 0; first = false; par ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc_i8(kRows, NT);
+            int slot = 0, u = 0;
+            uint32_t par = 0, upar = 0, acc_par = 0;
+            bool first_tile = true;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                if (!first_tile) { ok &= ptx::mbar_wait_bounded(acc_empty, acc_par); acc_par ^= 1; }
+                first_tile = false;
+                tc_fence_after();
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    ok &= ptx::mbar_wait_bounded(&full[slot], par);        // activation block landed
+                    ok &= ptx::mbar_wait_bounded(&unp_full[u], upar);      // weights unpacked
+                    tc_fence_after();
+                    const uint32_t b_addr = ptx::smem_u32(stage_base + (size_t)slot * kStageBytes + kRawBytes);
+                    const uint32_t a_addr = ptx::smem_u32(unp_base + (size_t)u * 4 * kATileBytes);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks) {  // 64 k' per residue = 2 x K32
+                            const uint64_t ad = smem_desc(a_addr + r * kATileBytes + ks * 256, 128, 512);
+                            const uint64_t bd = smem_desc(b_addr + r * (NT * 64) + ks * 256, 128, 512);
+                            umma_i8(tmem_base + r * NT, ad, bd, idesc, (kt > 0 || ks > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(&unp_empty[u]);  // unpacked buffer reusable once these MMAs are done
+                    umma_commit(&empty[slot]);   // and the stage (its activation block)
+                    if (++slot == kStages) { slot = 0; par ^= 1; }
+                    if (++u == kUnpBufs) { u = 0; upar ^= 1; }
+                }
+                umma_commit(acc_full);
+            }
+        }
+    } else {
+        // ---------------- unpack + epilogue warps (4 warps = 128 threads, one weight row each) ----
+        const int tid = threadIdx.x - 64;              // 0..127 = row inside the tile
+        const int sub = warp & 3;                      // TMEM sub-partition this warp may read
+        int slot = 0, u = 0;
+        uint32_t par = 0, upar = 1, acc_par = 0;
+        bool first_unp = true;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const int rs = tile % row_sets, tb = tile / row_sets;
+            const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                ok &= ptx::mbar_wait_bounded(&full[slot], par);
+                if (!first_unp) ok &= ptx::mbar_wait_bounded(&unp_empty[u], upar);
+                // this thread's row: row tile r8 = tid/16, half = (tid%16)/8, g = tid%8; its 64 packed
+                // bytes are the four 16-byte chunks t = 0..3 at ((half*32 + g*4 + t) * 16)
+                const int r8 = tid >> 4, half = (tid >> 3) & 1, g = tid & 7;
+                const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g * 64;
+                uint8_t* dst = unp_base + (size_t)u * 4 * kATileBytes + (tid >> 3) * 512 + (tid & 7) * 16;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    uint4 w = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // weight 0
+                    if (r8 < rts) w = *reinterpret_cast<const uint4*>(raw + t * 16);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const uint32_t mask = 0x03030303u << (2 * r);
+                        *reinterpret_cast<uint4*>(dst + r * kATileBytes + t * 128) =
+                            make_uint4(w.x & mask, w.y & mask, w.z & mask, w.w & mask);
+                    }
+                }
+                fence_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+                ptx::mbar_arrive(&unp_full[u]);
+                if (++slot == kStages) { slot = 0; par ^= 1; }
+                if (++u == kUnpBufs) { u = 0; first_unp = false; upar ^= 1; }
+            }
+            // ---- epilogue of this tile ----
+            ok &= ptx::mbar_wait_bounded(acc_full, acc_par);
+            acc_par ^= 1;
+            tc_fence_after();
+            const int64_t row = (int64_t)rs * kRows + sub * 32 + lane;
+            const int64_t rt = row >> 4;
+            float sw = 0.f;
+            if (a.epilogue != EPI_I32 && rt < a.row_tiles) sw = a.sw_tiles[2 * rt + ((row >> 3) & 1)];
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                uint32_t d0[32], d1[32], d2[32], d3[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + c0;
+                tmem_ld32(taddr + 0 * NT, d0);
+                tmem_ld32(taddr + 1 * NT, d1);
+                tmem_ld32(taddr + 2 * NT, d2);
+                tmem_ld32(taddr + 3 * NT, d3);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int token = tb * NT + c0 + j;
+                    if (token < a.m && row < a.n_out) {
+                        const int accv = (int)d0[j] + ((int)d1[j] >> 2) + ((int)d2[j] >> 4) + ((int)d3[j] >> 6) - a.qsum[token];
+                        const int64_t o = (int64_t)token * a.out_stride + row;
+                        if (a.epilogue == EPI_I32) {
+                            reinterpret_cast<int32_t*>(a.out)[o] = accv;
+                        } else {
+                            const float y = __fmul_rn(__fmul_rn((float)accv, sw), a.sx[token]);
+                            if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
+                            else if (a.epilogue == EPI_F32_ACCUM)
+                                reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
+                            else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            ptx::mbar_arrive(acc_empty);
+        }
+    }
+    if (!ok) atomicExch(a.err, kErrTcTimeout);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// Per-token absmax int8 quantiser writing the residue-split, core-matrix-ordered layout that
+// gemm_tc_kernel copies in bulk: [token_block][k_tile][residue][token_group][kc][token%8][16].
+template <int NT>
+__global__ void __launch_bounds__(256) act_quant_tc_kernel(const float* __restrict__ x, int64_t x_stride, int k,
+                                                           int k_tiles, int m, int8_t* __restrict__ qtc,
+                                                           float* __restrict__ s_out, int32_t* __restrict__ qsum_out) {
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+    const int token = blockIdx.x;  // grid covers the padded token count
+    const int tb = token / NT, tin = token % NT;
+    int8_t* blk = qtc + (int64_t)tb * k_tiles * (4 * NT * 64);
+    const bool real = token < m;
+    const float* xr = x + (int64_t)(real ? token : 0) * x_stride;
+    float amax = 0.0f;
+    if (real)
+        for (int c = threadIdx.x; c < k; c += blockDim.x) amax = fmaxf(amax, fabsf(xr[c]));
+    // block max
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red_f[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = 0.0f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) amax = fmaxf(amax, red_f[w]);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    int local = 0;
+    const int k_pad = k_tiles * kChunkK;
+    for (int c = threadIdx.x; c < k_pad; c += blockDim.x) {
+        int qv = 0;
+        if (real && c < k) qv = max(-127, min(127, ptx::round_half_away(__fmul_rn(xr[c], inv))));
+        local += qv;
+        const int kt = c >> 8, r = c & 3, kp = (c & 255) >> 2;  // k' inside the chunk
+        const int64_t off = (int64_t)kt * (4 * NT * 64) + (int64_t)r * (NT * 64) + (tin >> 3) * 512 + (kp >> 4) * 128 +
+                            (tin & 7) * 16 + (kp & 15);
+        blk[off] = (int8_t)qv;
+    }
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if ((threadIdx.x & 31) == 0) red_i[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0 && real) {
+        int tot = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red_i[w];
+        s_out[token] = __fdiv_rn(amax, 127.0f);
+        qsum_out[token] = tot;
+    }
+}
+
+template <int NT>
+cudaError_t launch_nt(const TcArgs& a, int sm_count, cudaStream_t stream) {
+    constexpr int kBBytes = 4 * NT * 64;
+    const size_t smem = (size_t)kStages * (kRawBytes + kBBytes) + (size_t)kUnpBufs * 4 * kATileBytes + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const int row_sets = (int)((a.row_tiles + 7) / 8);
+    const int n_tiles = row_sets * ((a.m + NT - 1) / NT);
+    const int grid = n_tiles < sm_count ? n_tiles : sm_count;
+    gemm_tc_kernel<NT><<<grid, kTcThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles) {
+    const int64_t nt = m <= 64 ? 64 : 128;
+    return (size_t)((m + nt - 1) / nt * k_tiles * 4 * nt * 64);
+}
+
+cudaError_t launch_gemm_tc(const LinearDev& lin, const float* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
+                           int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
+                           cudaStream_t stream) {
+    if (lin.w.n_bases != 1 && epilogue == EPI_BF16) return cudaErrorInvalidValue;
+    const int nt = m <= 64 ? 64 : 128;
+    const int padded = (int)((m + nt - 1) / nt * nt);
+    if (nt == 64)
+        act_quant_tc_kernel<64><<<padded, 256, 0, stream>>>(x, x_stride, (int)lin.w.k_in, (int)lin.w.k_tiles, (int)m, qtc, sx, qsum);
+    else
+        act_quant_tc_kernel<128><<<padded, 256, 0, stream>>>(x, x_stride, (int)lin.w.k_in, (int)lin.w.k_tiles, (int)m, qtc, sx, qsum);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    for (int b = 0; b < lin.w.n_bases; ++b) {
+        TcArgs a;
+        a.tiles = lin.w.tiles + (size_t)b * lin.w.basis_stride();
+        a.row_tiles = lin.w.row_tiles;
+        a.k_tiles = lin.w.k_tiles;
+        a.n_out = lin.w.n_out;
+        a.qtc = qtc;
+        a.qsum = qsum;
+        a.sx = sx;
+        a.sw_tiles = lin.scale_tiles + (size_t)b * lin.w.row_tiles * 2;
+        a.m = (int)m;
+        a.out = out;
+        a.out_stride = out_stride;
+        a.epilogue = (b > 0 && epilogue == EPI_F32) ? EPI_F32_ACCUM : epilogue;
+        a.err = err;
+        e = nt == 64 ? launch_nt<64>(a, sm_count, stream) : launch_nt<128>(a, sm_count, stream);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace bt

@@ -144,3 +144,18 @@ def test_shape_error_wording(bt):
     assert ei.value.status == bt.BT_ERR_ALIGN
     assert lin.forward(torch.zeros(0, 64, device="cuda")).shape == (0, 16)  # empty input
     assert bt.lib().bt_device_check(0) == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(9, 128, 256), (64, 256, 1024), (100, 1000, 688), (300, 2048, 2048), (130, 48, 4096)])
+def test_tensor_core_path_many_tokens(bt, oracle, m, n, k):
+    # more than 8 tokens go through the tcgen05 kernel; same bits as the oracle pipeline
+    rng = np.random.default_rng(m * 7 + n)
+    packed = ternary_packed(rng, n, k, p_code3=0.01)
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    x[m // 2] = 0  # an all-zero token
+    lin = bt.BitLinear.from_packed(packed, [0.016], n, k)
+    y = lin.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = oracle.bitlinear_q(x, packed, [0.016], n)
+    assert np.abs(y - ref).max() <= REL_TOL * np.abs(ref).max()
+    assert np.array_equal(y, ref)
+    assert bt.lib().bt_device_check(0) == 0
