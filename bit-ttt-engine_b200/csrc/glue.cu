@@ -480,14 +480,15 @@ cudaError_t launch_lm_head_fused(const __nv_bfloat16* w, const float* h, const f
                                  int batch, int hidden, int64_t vocab, float* logits, float* cand_val,
                                  int32_t* cand_idx, int* n_cand, int sm_count, cudaStream_t stream, bool pdl) {
     if (hidden % 8 != 0 || batch < 1) return cudaErrorInvalidValue;
-    // one grid size for every group of 4 tokens, so that the candidate rows share a stride
-    const size_t smem_max = (size_t)(batch < 4 ? batch : 4) * hidden * sizeof(float);
+    // one grid size for every group of tokens, so that the candidate rows share a stride
+    const int per_pass = batch > 4 ? 8 : 4;  // tokens per pass over the weights
+    const size_t smem_max = (size_t)(batch < per_pass ? batch : per_pass) * hidden * sizeof(float);
     int per_sm = (int)((200 * 1024) / (smem_max + 2048));
     per_sm = per_sm > 4 ? 4 : (per_sm < 1 ? 1 : per_sm);
     const int grid = sm_count * per_sm;
     *n_cand = grid;
-    for (int b0 = 0; b0 < batch; b0 += 4) {
-        const int bc = batch - b0 < 4 ? batch - b0 : 4;
+    for (int b0 = 0; b0 < batch; b0 += per_pass) {
+        const int bc = batch - b0 < per_pass ? batch - b0 : per_pass;
         const float* hb = h + (size_t)b0 * hidden;
         float* lb = logits + (size_t)b0 * vocab;
         float* cv = cand_val + (size_t)b0 * grid;
@@ -497,7 +498,11 @@ cudaError_t launch_lm_head_fused(const __nv_bfloat16* w, const float* h, const f
             case 1: e = launch_lm_head_fused_b<1>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
             case 2: e = launch_lm_head_fused_b<2>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
             case 3: e = launch_lm_head_fused_b<3>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            default: e = launch_lm_head_fused_b<4>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            case 4: e = launch_lm_head_fused_b<4>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            case 5: e = launch_lm_head_fused_b<5>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            case 6: e = launch_lm_head_fused_b<6>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            case 7: e = launch_lm_head_fused_b<7>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            default: e = launch_lm_head_fused_b<8>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
         }
         if (e != cudaSuccess) return e;
     }

@@ -89,6 +89,8 @@ struct bt_model {
     int32_t* next = nullptr;
     double* attn_partial = nullptr;
     float* act = nullptr;            // [max_batch, intermediate] silu(gate)*up
+    float* xt = nullptr;             // [max_batch, max(hidden, intermediate)] transformed rows (batches above 8)
+    int8_t* qtc = nullptr;           // activations in the tensor-core product's layout (batches above 8)
     unsigned int* absmax = nullptr;  // [num_layers][2][max_batch] max|x| cells of the fused path
     float* cand_val = nullptr;
     int32_t* cand_idx = nullptr;
@@ -197,26 +199,26 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
     return BT_OK;
 }
 
-// Enqueues one decode step for `batch` sequences on `s` (separate quantiser kernels; any batch).
+// One decode step for more than 8 sequences: row transforms (RMSNorm, SiLU*up) as separate
+// kernels, every projection on the tensor-core product (tcgen05), which quantises its input.
 bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     const bt_model_config& c = m->cfg;
-    const int H = c.hidden_dim, I = m->i_l;
+    const int H = c.hidden_dim, I = m->i_l, B = c.max_batch;
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
-    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s));
+    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, false));
     for (int li = 0; li < c.num_layers; ++li) {
         Layer& L = m->layers[(size_t)li];
-        // x_norm = norm1(x)  (model/block.rs:98), quantised for the projections that follow
-        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm1, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
+        // x_norm = norm1(x)  (model/block.rs:98)
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm1, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, m->xt, s));
         if (c.arch == 0) {
             // TTTLayer::forward_update (layers/ttt.rs:48-74)
-            BT_CUDA_TRY(linear_product(L.ttt_down->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->feat, m->d_small, EPI_F32, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), m->xt, H, batch, m->qtc, m->sx, m->qsum, m->feat, m->d_small, EPI_F32, err, sm, s));
             BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s));
-            BT_CUDA_TRY(launch_row_quant(PRE_NONE, m->z, m->d_small, nullptr, 0.f, batch, m->d_small, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
-            BT_CUDA_TRY(linear_product(L.ttt_up->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), m->z, m->d_small, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
         } else {
             // BitAttention::forward (layers/attention.rs:149-225), seq_len 1
-            BT_CUDA_TRY(linear_product(L.qkv->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->qkv, m->qkv_dim, EPI_F32, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), m->xt, H, batch, m->qtc, m->sx, m->qsum, m->qkv, m->qkv_dim, EPI_F32, err, sm, s));
             AttnArgs a;
             a.qkv = m->qkv;
             a.cache = L.kv->view;
@@ -226,29 +228,27 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.counters = L.kv->counters;
             a.out = m->att;
             a.partial = m->attn_partial;
-            a.batch = batch; a.n_heads = c.n_heads; a.n_kv = c.n_kv_heads; a.head_dim = m->head_dim;
+            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim;
             a.sm_count = sm;
-            attn_plan(batch, c.n_kv_heads, c.max_position_embeddings, sm, &a.splits, &a.span);
+            attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = nullptr;
             a.pdl = false;
             a.dbg = nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
-            BT_CUDA_TRY(launch_row_quant(PRE_NONE, m->att, H, nullptr, 0.f, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
-            BT_CUDA_TRY(linear_product(L.o->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
         }
         // x = x + mlp(norm2(x))  (model/block.rs:119-131, layers/swiglu.rs:29-35)
-        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
-        BT_CUDA_TRY(linear_product(L.gate_up->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, 2 * I, EPI_F32, err, sm, s));
-        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, m->q, m->q_stride, m->sx, m->qsum, nullptr, s));
-        BT_CUDA_TRY(linear_product(L.down->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->h, H, EPI_F32_ACCUM, err, sm, s));
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, m->xt, s));
+        BT_CUDA_TRY(launch_gemm_tc(L.gate_up->dev(), m->xt, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s));
+        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, m->q, m->q_stride, m->sx, m->qsum, m->xt, s));
+        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), m->xt, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
     }
-    // logits = lm_head(norm(h))  (model/llama.rs:256-266)
-    BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, m->norm_f, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, m->xn, s));
-    BT_CUDA_TRY(launch_lm_head(m->lm_head, m->xn, batch, H, c.vocab_size, m->logits, sm, s));
-    BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
-    advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, c.max_batch);
-    BT_CUDA_TRY(cudaGetLastError());
+    // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
+    int n_cand = 0;
+    BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
+                                     m->cand_val, m->cand_idx, &n_cand, sm, s, false));
+    BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, false));
     return BT_OK;
 }
 
@@ -416,6 +416,10 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
     BT_CUDA_TRY(dev_alloc(&m->gu, (size_t)B * 2 * I));
     BT_CUDA_TRY(dev_alloc(&m->xn, (size_t)B * H));
     BT_CUDA_TRY(dev_alloc(&m->act, (size_t)B * I));
+    if (B > 8) {
+        BT_CUDA_TRY(dev_alloc(&m->xt, (size_t)B * (H > I ? H : I)));
+        BT_CUDA_TRY(dev_alloc(&m->qtc, gemm_tc_act_bytes(B, (kmax + kTileK - 1) / kTileK)));
+    }
     BT_CUDA_TRY(dev_alloc(&m->absmax, (size_t)c.num_layers * 2 * B));
     BT_CUDA_TRY(cudaMemset(m->absmax, 0, (size_t)c.num_layers * 2 * B * sizeof(unsigned int)));
     BT_CUDA_TRY(dev_alloc(&m->cand_val, (size_t)B * lm_head_max_candidates(m->sm_count)));
@@ -457,7 +461,7 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc};
     for (void* p : bufs) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
@@ -573,9 +577,16 @@ extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, void* str
         bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up,
                              (batch <= 8 || !L.gate_up) ? L.gate_up_il : L.gate_up, L.down};
         for (bt_linear* lin : seq) {
-            BT_CUDA_TRY(linear_product(lin->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, lin->w.n_out,
-                                       EPI_F32, err, m->sm_count, s));
-            launches += groups;
+            if (batch > 8) {
+                // tensor-core product on whatever the transformed-row buffer holds (quantiser included)
+                BT_CUDA_TRY(launch_gemm_tc(lin->dev(), m->xt, lin->w.k_in, batch, m->qtc, m->sx, m->qsum, m->gu,
+                                           lin->w.n_out, EPI_F32, err, m->sm_count, s));
+                launches += 2;
+            } else {
+                BT_CUDA_TRY(linear_product(lin->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, lin->w.n_out,
+                                           EPI_F32, err, m->sm_count, s));
+                launches += groups;
+            }
         }
     }
     if (n_launches) *n_launches = launches;
@@ -589,11 +600,10 @@ extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
         const int per_layer = 4 + 1 + (m->tp > 1 ? 2 : 0);  // 4 products + attention or TTT update (+ 2 scale epilogues after the all-reduces)
         return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
     }
-    const int groups = (batch + 7) / 8;
-    // per layer: 4 quantiser launches, 4 ternary products per 8 tokens, attention or TTT update
-    const int per_layer = 4 + 4 * groups + 1;
-    // embedding, final norm, lm_head (4 tokens per launch), arg-max, position advance
-    return m->cfg.num_layers * per_layer + 1 + 1 + (batch + 3) / 4 + 1 + 1;
+    // batches above 8: per layer 3 row kernels, 4 x (quantiser + tensor-core product), attention or
+    // TTT update; embedding, lm_head per 8 tokens, pick
+    const int per_layer = 3 + 8 + 1;
+    return m->cfg.num_layers * per_layer + 1 + (batch + 7) / 8 + 1;
 }
 
 __global__ void set_pos_kernel(int32_t* pos, int n, int value) {

@@ -80,3 +80,12 @@ def test_position_limit(bt):
     with pytest.raises(bt.BitTTTError) as ei:
         gpu.forward_one([1])
     assert ei.value.status == bt.BT_ERR_SHAPE
+
+
+def test_models_batch_12_use_tensor_core_product(bt, oracle):
+    # more than 8 sequences: projections run on the tcgen05 kernel, row transforms separately
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    for cfg, seed in ((syn.TINY_LLAMA_TEST, 3100), (syn.BitLlamaConfig("ttt", 500, 256, 2, 4, 4, 688, inner_lr=0.01), 3200)):
+        gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 4, seed, batch=12)
+        assert worst <= REL_TOL
+    assert bt.lib().bt_device_check(0) == 0
