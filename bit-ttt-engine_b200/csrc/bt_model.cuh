@@ -34,6 +34,14 @@ cudaError_t launch_pick(const float* cand_val, const int32_t* cand_idx, int n_ca
                         int32_t* pos, int n_pos, cudaStream_t stream, bool pdl);
 int lm_head_max_candidates(int sm_count);
 
+// Tensor-core lm_head for batches above 8 (tcgen05, bf16 x (bf16 hi + bf16 lo), f32 accumulate).
+size_t lm_head_tc_weight_bytes(int64_t vocab, int hidden);
+size_t lm_head_tc_act_bytes(int hidden);
+cudaError_t launch_lm_retile(const __nv_bfloat16* w, int64_t vocab, int hidden, void* tiles, cudaStream_t stream);
+cudaError_t launch_lm_head_tc(const void* wtiles, const float* h, const float* norm_w, float eps, int batch, int hidden,
+                              int64_t vocab, void* btiles, float* logits, unsigned int* err, int sm_count,
+                              cudaStream_t stream);
+
 // Q8 KV cache of one layer: u8 data [batch, n_kv, max_seq, head_dim] and f32 scales
 // [batch, n_kv, max_seq] for K and V (layers/kv_cache.rs:14-24).
 struct KvCacheView {

@@ -91,6 +91,8 @@ struct bt_model {
     float* act = nullptr;            // [max_batch, intermediate] silu(gate)*up
     float* xt = nullptr;             // [max_batch, max(hidden, intermediate)] transformed rows (batches above 8)
     int8_t* qtc = nullptr;           // activations in the tensor-core product's layout (batches above 8)
+    void* lm_tiles = nullptr;        // lm_head in tensor-core tile order (batches above 8, hidden % 64 == 0)
+    void* lm_btiles = nullptr;       // normalised hidden states as bf16 hi|lo tiles
     unsigned int* absmax = nullptr;  // [num_layers][2][max_batch] max|x| cells of the fused path
     float* cand_val = nullptr;
     int32_t* cand_idx = nullptr;
@@ -245,6 +247,14 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
         BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), m->xt, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
     }
     // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
+    if (m->lm_tiles) {
+        BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
+                                      err, sm, s));
+        BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
+        advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, B);
+        BT_CUDA_TRY(cudaGetLastError());
+        return BT_OK;
+    }
     int n_cand = 0;
     BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
                                      m->cand_val, m->cand_idx, &n_cand, sm, s, false));
@@ -419,6 +429,12 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
     if (B > 8) {
         BT_CUDA_TRY(dev_alloc(&m->xt, (size_t)B * (H > I ? H : I)));
         BT_CUDA_TRY(dev_alloc(&m->qtc, gemm_tc_act_bytes(B, (kmax + kTileK - 1) / kTileK)));
+        if (H % 64 == 0) {
+            BT_CUDA_TRY(cudaMalloc(&m->lm_tiles, lm_head_tc_weight_bytes(c.vocab_size, H)));
+            BT_CUDA_TRY(cudaMalloc(&m->lm_btiles, lm_head_tc_act_bytes(H)));
+            BT_CUDA_TRY(launch_lm_retile(m->lm_head, c.vocab_size, H, m->lm_tiles, 0));
+            BT_CUDA_TRY(cudaDeviceSynchronize());
+        }
     }
     BT_CUDA_TRY(dev_alloc(&m->absmax, (size_t)c.num_layers * 2 * B));
     BT_CUDA_TRY(cudaMemset(m->absmax, 0, (size_t)c.num_layers * 2 * B * sizeof(unsigned int)));
@@ -461,7 +477,7 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles};
     for (void* p : bufs) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
