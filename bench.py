@@ -99,15 +99,15 @@ class ClockSampler:
 # workload
 # ---------------------------------------------------------------------------------------
 
-def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0):
+def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0, layers=32, vocab=128256):
     """Random-init Llama-3-8B-shaped ternary model.  Layer 0's host arrays are reused for
     every layer (each layer still owns its own device copy, so HBM traffic is real); the
     embedding and lm_head are one N(0, 0.02) block tiled over the vocabulary."""
-    cfg = syn.BitLlamaConfig("llama", 128256, 4096, 32, 32, 8, 14336, rope_theta=500000.0,
+    cfg = syn.BitLlamaConfig("llama", vocab, 4096, layers, 32, 8, 14336, rope_theta=500000.0,
                              max_position_embeddings=max_pos)
     rng = np.random.default_rng(seed)
-    block = rng.normal(0, 0.02, (8016, cfg.hidden_dim)).astype(np.float32)
-    table = np.tile(block, (16, 1))
+    block = rng.normal(0, 0.02, (min(8016, vocab), cfg.hidden_dim)).astype(np.float32)
+    table = np.tile(block, ((vocab + block.shape[0] - 1) // block.shape[0], 1))[:vocab]
     w = syn.SyntheticWeights(cfg, table, table, np.ones(cfg.hidden_dim, np.float32))
     layer = {"norm1": np.ones(cfg.hidden_dim, np.float32), "norm2": np.ones(cfg.hidden_dim, np.float32)}
     for kind, (n, k) in syn.linear_shapes(cfg).items():
@@ -157,6 +157,80 @@ def cpu_decode_baseline(cfg, syn, budget_s=20.0):
     }
 
 
+def run_linear_probe(bt, n, k, m):
+    """Three forwards of one BitLinear (profiling aid for the product kernels)."""
+    import torch
+    rng = np.random.default_rng(0)
+    lin = bt.BitLinear.from_packed(rng.integers(0, 256, size=(n, k // 4), dtype=np.uint8), [0.016], n, k)
+    x = torch.randn(m, k, device="cuda")
+    ws = bt.Workspace(0, 768 << 20)
+    for _ in range(3):
+        y = lin.forward(x, workspace=ws)
+    torch.cuda.synchronize()
+    print("linear probe done", float(y.abs().sum()), file=sys.stderr)
+
+
+def run_sweep(bt, device):
+    """BASELINE config 5: per point GB/s of packed weights (HBM-bound points) and int8 TOP/s."""
+    import ctypes as C
+    import torch
+    peak, peak_kind = measured_peaks()
+    L = bt.lib()
+    rng = np.random.default_rng(0)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for (k, n) in [(4096, 4096), (4096, 14336), (14336, 4096), (4096, 128256)]:
+        # distinct weight copies so that consecutive launches do not hit L2 (126 MB)
+        copies = max(2, int(400e6 // (n * k / 4))) if n * k / 4 < 200e6 else 2
+        packed = rng.integers(0, 256, size=(n, k // 4), dtype=np.uint8)
+        lins = [bt.BitLinear.from_packed(packed, [0.016], n, k, device=device) for _ in range(copies)]
+        ws = bt.Workspace(device, 768 << 20)
+        for m in (1, 8, 64, 512, 4096):
+            if m * n * 4 > 3 << 30:
+                continue
+            x = torch.randn(m, k, device="cuda")
+            y = torch.empty(m, n, device="cuda")
+
+            def run():
+                for lin in lins:
+                    bt.check(L.bt_linear_forward(lin._h, ws._h, C.c_void_p(x.data_ptr()), m, k, 0,
+                                                 C.c_void_p(y.data_ptr()), 0, stream))
+            run()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 5 if m <= 64 else 2
+            e0.record()
+            for _ in range(reps):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+            byts = n * k / 4 + 2 * m * k + 2 * m * n
+            print(json.dumps({"sweep": "bitlinear", "K": k, "N": n, "M": m, "us": us,
+                              "kernel": "gemv (mma.sync)" if m <= 8 else "gemm_tc (tcgen05)",
+                              "GBps": byts / us / 1e3, "hbm_frac": byts / us / 1e3 / peak, "peak_kind": peak_kind,
+                              "int8_TOPs": 2.0 * m * n * k / us / 1e6,
+                              "note": "quantiser kernel included; weights rotate through copies larger than L2"}),
+                  flush=True)
+        del lins
+    # TTT fast-weight update: S independent 64x64 states, mini-batch 16
+    for s_cnt in (4, 64, 1024, 8192):
+        w = torch.zeros(s_cnt, 64, 64, device="cuda")
+        f = torch.randn(s_cnt, 16, 64, device="cuda")
+        bt.ttt_update(w, f, 0.01, 16)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            bt.ttt_update(w, f, 0.01, 16)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 10
+        byts = s_cnt * (2 * 64 * 64 * 4 + 2 * 16 * 64 * 4)
+        print(json.dumps({"sweep": "ttt_update", "states": s_cnt, "d": 64, "chunk": 16, "us": us,
+                          "updates_per_s": s_cnt / us * 1e6, "GBps": byts / us / 1e3, "hbm_frac": byts / us / 1e3 / peak}),
+              flush=True)
+
+
 def run_reference_arm(args, rank):
     """--impl reference: the reference's CPU implementation of the path.  The reference is a
     Rust workspace with no Rust toolchain available here, so the timed code is the CPU port
@@ -192,6 +266,16 @@ def main():
     ap.add_argument("--context", type=int, default=2048, help="tokens in the KV cache before the timed steps")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=32, help="profiling aid: fewer layers of the same shape")
+    ap.add_argument("--vocab", type=int, default=128256, help="profiling aid: smaller vocabulary")
+    ap.add_argument("--one-step", action="store_true",
+                    help="profiling aid: build the model, --seek to the context, run ONE eager decode step "
+                         "(every kernel launched outside a graph) and exit without a JSON line")
+    ap.add_argument("--linear", type=int, nargs=3, metavar=("N", "K", "M"),
+                    help="profiling aid: three bt_linear_forward calls on a random [N, K] weight with M tokens, then exit")
+    ap.add_argument("--sweep", action="store_true",
+                    help="BitLinear shape sweep (K,N in {4096x4096, 4096x14336, 14336x4096, 4096x128256}, "
+                         "M in {1, 8, 64, 512, 4096}) plus the TTT update: one JSON line per point")
     ap.add_argument("--seek", action="store_true",
                     help="profiling aid: skip the token-by-token prefill and declare the (zero-filled) "
                          "cache to hold --context positions")
@@ -217,7 +301,14 @@ def main():
 
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     max_pos = args.context + W + 2 * K + 16
-    cfg, weights, model = build_8b(bt, syn, B, max_pos, tp_rank=rank, tp_size=world, device=local_rank)
+    if args.linear:
+        run_linear_probe(bt, *args.linear)
+        return
+    if args.sweep:
+        run_sweep(bt, local_rank)
+        return
+    cfg, weights, model = build_8b(bt, syn, B, max_pos, tp_rank=rank, tp_size=world, device=local_rank,
+                                   layers=args.layers, vocab=args.vocab)
     del weights
     if world > 1:
         uid = [bt.tp_unique_id() if rank == 0 else None]
@@ -230,6 +321,14 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.one_step:
+        model.seek(args.context)
+        _, ids = model.forward_one(np.arange(B, dtype=np.int32) + 5, want_logits=False)
+        torch.cuda.synchronize()
+        print("one eager step done, next ids", ids[:4].tolist(), file=sys.stderr)
+        del model
+        return
 
     # prefill token by token, tokens fed from the host like the reference CLI
     tok = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(dev)
