@@ -26,8 +26,6 @@
 //     first weight stages are already in flight, which removes a kernel boundary per
 //     projection from the decode step; with programmatic dependent launch the weight
 //     prefetch even starts before the previous kernel has finished.
-#include <stdlib.h>
-
 #include "bt_common.cuh"
 #include "bt_ptx.cuh"
 
@@ -35,16 +33,15 @@ namespace bt {
 
 namespace {
 
-constexpr int kEpiWarps_ = 4;
+constexpr int kEpiWarps = 4;  // epilogue warps = reduction buffers
 constexpr int kMathWarps = 8;
 constexpr int kMathThreads = kMathWarps * 32;
 constexpr int kProducerWarp = kMathWarps;
-constexpr int kEpilogueWarp0 = kMathWarps + 1;  // first of kRedBufs epilogue warps
-constexpr int kEpiWarps = 4;
+constexpr int kEpilogueWarp0 = kMathWarps + 1;  // first epilogue warp
 constexpr int kThreads = (kMathWarps + 1 + kEpiWarps) * 32;
 constexpr int kStageTiles = 16;
 constexpr int kStageBytes = kStageTiles * kTileBytes;
-constexpr int kRedBufs = kEpiWarps_;
+constexpr int kRedBufs = kEpiWarps;
 constexpr int kRedBufInts = kMathWarps * 128;
 constexpr int kRedBytes = kRedBufs * kRedBufInts * 4;
 constexpr int kMaxStages = 12;
@@ -148,7 +145,7 @@ __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
 template <int PRO>
 __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* acts, int act_stride, float* tok_sx,
                                                   int* tok_qsum, uint8_t* scratch, int tid, int warp, int lane,
-                                                  int k_tiles) {
+                                                  int k_tiles, const float (&w0)[16]) {
     const int groups_pad = k_tiles * (kTileK / 16);
     const int groups = (int)(a.k_in >> 4);  // k_in is a multiple of 16 on the fused paths
     double* sl_d = reinterpret_cast<double*>(scratch);            // 8 doubles
@@ -181,11 +178,11 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
         float s;
         if (PRO == PRO_RMSNORM) {
             // up to two 16-groups per thread held in registers (k_in <= 8192)
-            float v0[16], v1[16], w0[16];
+            float v0[16], v1[16];
             const int j0 = tid, j1 = tid + kMathThreads;
             const bool h0 = j0 < groups, h1 = j1 < groups;
             double ss = 0.0;
-            if (h0) { load16(xr + 16 * j0, v0); load16(a.norm_w + 16 * j0, w0); }
+            if (h0) load16(xr + 16 * j0, v0);
             if (h1) load16(xr + 16 * j1, v1);
             if (h0) {
 #pragma unroll
@@ -305,9 +302,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
         return;
     }
 
-    ptx::pdl_wait();  // activations and the output buffer belong to earlier kernels until here
-
     if (warp >= kEpilogueWarp0) {
+        ptx::pdl_wait();  // the output buffer belongs to earlier kernels until here
         // ---------------- epilogue warps: warp e serves reduction buffer e, i.e. the CTA's row
         // tiles e, e + kEpiWarps, ... ----------------
         const int epi = warp - kEpilogueWarp0;
@@ -393,8 +389,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     // ---------------- math warps ----------------
     const int tid = threadIdx.x;
     const int g = lane >> 2, t = lane & 3;
+    // The norm weights do not depend on earlier kernels and usually come from DRAM (nothing
+    // else touches them during a step): fetch them before waiting on the dependency.
+    float w0[16];
+    if (PRO == PRO_RMSNORM && tid < (int)(a.k_in >> 4)) load16(a.norm_w + 16 * tid, w0);
+    ptx::pdl_wait();  // activations belong to earlier kernels until here
     if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 1] = ptx::globaltimer();
-    stage_activations<PRO>(a, acts, act_stride, tok_sx, tok_qsum, scratch, tid, warp, lane, k_tiles);
+    stage_activations<PRO>(a, acts, act_stride, tok_sx, tok_qsum, scratch, tid, warp, lane, k_tiles, w0);
     ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // activation image complete, epilogue warps may read the scales
     if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 2] = ptx::globaltimer();
 
@@ -465,10 +466,8 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     // beside this one and stream its first stages early, while large ones (gate|up, down)
     // get the deepest ring - HBM needs well over 100 KB in flight per SM to stay busy.
     const size_t full_budget = 220 * 1024;
-    int ctas_per_sm = 1;
-    static const char* env_ctas = getenv("BT_GEMV_CTAS");
-    if (env_ctas && env_ctas[0] == '2') ctas_per_sm = 2;
-    const size_t budget = ctas_per_sm == 2 ? full_budget / 2 : full_budget;
+    const int ctas_per_sm = 1;
+    const size_t budget = full_budget;
     if (fixed + 2 * kStageBytes > budget) return cudaErrorInvalidConfiguration;
     int nstages = (int)((budget - fixed) / kStageBytes);
     if (nstages > kMaxStages) nstages = kMaxStages;
@@ -521,7 +520,7 @@ cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stri
             a.out_stride = out_stride;
             a.epilogue = (b > 0 && epilogue == EPI_F32) ? EPI_F32_ACCUM : epilogue;
             a.err = err;
-            a.pdl = false;
+            a.pdl = true;  // weight prefetch may overlap the tail of whatever precedes it in the stream
             cudaError_t e = launch_gemv(a, sm_count, stream);
             if (e != cudaSuccess) return e;
         }
@@ -556,8 +555,7 @@ cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m,
     a.epilogue = epilogue;
     a.err = err;
     a.dbg = g_dbg_base ? g_dbg_base + (size_t)(g_dbg_slot++) * 4 * 512 : nullptr;
-    static const char* env_pdl = getenv("BT_PDL");
-    a.pdl = !(env_pdl && env_pdl[0] == '0');
+    a.pdl = true;
     return launch_gemv(a, sm_count, stream);
 }
 
