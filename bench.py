@@ -408,7 +408,10 @@ def main():
     achieved = bytes_per_launch / us_per_launch / 1e3  # GB/s
     roofline = {"bound": "hbm", "kernel": "gemv_kernel (ternary BitLinear product)", "achieved": achieved,
                 "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                "traffic": None, "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
+                # dram__bytes_read+write per launch, average over the four projections of a block, from the
+                # ncu capture summarised in profiles/gemv_kernel_decode_layer_8b.md (batch 1, one GPU)
+                "traffic": 13.73e6 if (B == 1 and world == 1) else None,
+                "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
                 "launches_per_step": n_launch}
 
     if rank == 0:
