@@ -9,7 +9,7 @@
 //   * a producer thread streams the tiles of a row tile (contiguous in the tiled layout)
 //     into a shared-memory ring with 1-D bulk async copies that complete on mbarriers -
 //     16 KB per stage, so tens of KB per SM are in flight whatever the math warps do;
-//   * 8 math warps split each stage along K (two 1 KB tiles each).  A lane's two 16-byte
+//   * 16 math warps split each stage along K (one 1 KB tile each).  A lane's two 16-byte
 //     chunks are already the A-operand slots of mma.m16n8k32 (u8 x s8 -> s32): one AND
 //     per register isolates field r of every byte as an unsigned multiple of 4^r, so the
 //     unpack costs one integer instruction per four weights; the four field positions
@@ -34,7 +34,7 @@ namespace bt {
 namespace {
 
 constexpr int kEpiWarps = 4;  // epilogue warps = reduction buffers
-constexpr int kMathWarps = 8;
+constexpr int kMathWarps = 16;
 constexpr int kMathThreads = kMathWarps * 32;
 constexpr int kProducerWarp = kMathWarps;
 constexpr int kEpilogueWarp0 = kMathWarps + 1;  // first epilogue warp
@@ -148,8 +148,8 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
                                                   int k_tiles, const float (&w0)[16]) {
     const int groups_pad = k_tiles * (kTileK / 16);
     const int groups = (int)(a.k_in >> 4);  // k_in is a multiple of 16 on the fused paths
-    double* sl_d = reinterpret_cast<double*>(scratch);            // 8 doubles
-    float* sl_f = reinterpret_cast<float*>(scratch + 64);          // 8 floats
+    double* sl_d = reinterpret_cast<double*>(scratch);            // kMathWarps doubles
+    float* sl_f = reinterpret_cast<float*>(scratch + 256);         // kMathWarps floats
     if (PRO == PRO_Q8) {
         for (int n = 0; n < a.m; ++n) {
             const uint4* src = reinterpret_cast<const uint4*>(a.q + (int64_t)n * a.q_stride);
@@ -415,10 +415,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     for (int it = 0; it < total_iters; ++it) {
         ok &= ptx::mbar_wait_bounded(&full[slot], parity);
         const uint8_t* stage = ring + (size_t)slot * kStageBytes;
-        const int kt_a = sk * kStageTiles + warp, kt_b = kt_a + kMathWarps;
-        if (kt_a < k_tiles) tile_mma(acc, stage + warp * kTileBytes, lane, my_acts + kt_a * kTileK, has_token);
-        if (kt_b < k_tiles)
-            tile_mma(acc, stage + (warp + kMathWarps) * kTileBytes, lane, my_acts + kt_b * kTileK, has_token);
+        const int kt = sk * kStageTiles + warp;  // one 1 KB tile per math warp and stage
+        if (kt < k_tiles) tile_mma(acc, stage + warp * kTileBytes, lane, my_acts + kt * kTileK, has_token);
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&empty[slot]);
         if (++slot == nstages) { slot = 0; parity ^= 1; }
@@ -456,6 +454,7 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     if (a.m < 1 || a.m > 8) return cudaErrorInvalidValue;
     if (a.prologue != PRO_Q8 && (a.k_in % 16 != 0)) return cudaErrorInvalidValue;
     if (a.prologue == PRO_RMSNORM && a.k_in > 16 * 2 * kMathThreads) return cudaErrorInvalidValue;
+    static_assert(kStageTiles == kMathWarps, "one tile per math warp");
     if (a.epilogue == EPI_SWIGLU && (!a.absmax_out || a.n_out % 16 != 0)) return cudaErrorInvalidValue;
     const int act_stride = (int)(a.k_tiles * kTileK + 64);
     const size_t fixed = (size_t)a.m * act_stride + kRedBytes + kBarBytes + kTokBytes + kScratchBytes;
