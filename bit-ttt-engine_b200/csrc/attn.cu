@@ -27,7 +27,9 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Quantise one head vector held in shared memory (hd values) by one warp.
-__device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* q_out, float* s_out, int lane) {
+// q_copy / s_copy: optional second destination (the CTA's prefetched copy of the cache rows).
+__device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* q_out, float* s_out, uint8_t* q_copy,
+                                               float* s_copy, int lane) {
     float amax = 0.0f;
     for (int c = lane; c < hd; c += 32) amax = fmaxf(amax, fabsf(v[c]));
     amax = warp_max(amax);
@@ -36,8 +38,12 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
         float r = s > 0.0f ? roundf(__fdiv_rn(v[c], s)) : 0.0f;
         r = fminf(fmaxf(r + 128.0f, 0.0f), 255.0f);
         q_out[c] = (uint8_t)r;
+        if (q_copy) q_copy[c] = (uint8_t)r;
     }
-    if (lane == 0) *s_out = s;
+    if (lane == 0) {
+        *s_out = s;
+        if (s_copy) *s_copy = s;
+    }
 }
 
 // One CTA = one (sequence, KV head, span of positions), 512 threads.  The span is walked
@@ -50,6 +56,7 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
 constexpr int kTilePos = 64;
 constexpr int kHalfPad = 68;   // floats per staged half row: 64 + 4, conflict-free 16-byte reads
 constexpr int kMaxRep = 8;
+constexpr int kRawPos = 128;   // cache rows prefetched per CTA
 
 struct AttnSmem {
     alignas(16) float qs[kMaxRep][128];  // rotated queries (exact f32 values)
@@ -59,26 +66,53 @@ struct AttnSmem {
     float knew[128], vnew[128];
     alignas(16) float kf[kTilePos][2][kHalfPad];  // dequantised keys of the tile, two halves of 64 dims
     alignas(16) float vf[kTilePos][128];          // dequantised values of the tile
+    // the span's first kRawPos cache rows as stored (u8 + scale), fetched before the kernel
+    // waits for its predecessor
+    alignas(16) uint8_t kraw[kRawPos * 128];
+    alignas(16) uint8_t vraw[kRawPos * 128];
+    float ksr[kRawPos], vsr[kRawPos];
 };
 
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
-#define STAMP(i) do { if (a.dbg && (i) < 2 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 4 + (i)] = ptx::globaltimer(); \
-                      if (a.dbg && (i) == 6 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 4 + 2] = ptx::globaltimer(); \
-                      if (a.dbg && (i) == 7 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 4 + 3] = ptx::globaltimer(); } while (0)
+#define STAMP(i) do { if (a.dbg && (i) < 8 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = ptx::globaltimer(); } while (0)
     STAMP(0);
-    ptx::pdl_wait();
-    STAMP(1);
-
     const int hd = a.head_dim, half = hd >> 1;
     const int nrep = a.n_heads / a.n_kv;
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int split = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = split * a.span;
+    const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
+    const int row16 = hd / 16;  // 16-byte pieces per row
+    // The cache rows of earlier positions were written by earlier steps, so they can be fetched
+    // before the dependency wait (whatever sits in rows at or beyond the current position is
+    // fetched too and never used; the owner of the new position overwrites its copy below).
+    const int raw_rows = max(0, min(min(kRawPos, a.span), a.cache.max_seq - t0));
+    {
+        const uint4* ksrc = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + t0) * hd);
+        const uint4* vsrc = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + t0) * hd);
+        uint4* kdst = reinterpret_cast<uint4*>(sm.kraw);
+        uint4* vdst = reinterpret_cast<uint4*>(sm.vraw);
+        const int n16 = raw_rows * row16;
+        for (int i0 = tid; i0 < n16; i0 += 2 * kAttnThreads) {
+            const int i1 = i0 + kAttnThreads;
+            const bool h1 = i1 < n16;
+            const uint4 k0 = ksrc[i0], v0 = vsrc[i0];
+            uint4 k1 = make_uint4(0u, 0u, 0u, 0u), v1 = k1;
+            if (h1) { k1 = ksrc[i1]; v1 = vsrc[i1]; }
+            kdst[i0] = k0; vdst[i0] = v0;
+            if (h1) { kdst[i1] = k1; vdst[i1] = v1; }
+        }
+        if (tid < raw_rows) sm.ksr[tid] = a.cache.k_s[row_base + t0 + tid];
+        else if (tid >= 256 && tid - 256 < raw_rows) sm.vsr[tid - 256] = a.cache.v_s[row_base + t0 + tid - 256];
+    }
+    ptx::pdl_wait();
+    STAMP(1);
+
     const int p = a.pos[b];
     const int t_len = p + 1;
-    const int t0 = split * a.span;
     const int t1 = min(t_len, t0 + a.span);
     const int64_t qkv_stride = (int64_t)(a.n_heads + 2 * a.n_kv) * hd;
     const float* qkv = a.qkv + b * qkv_stride;
@@ -106,7 +140,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         sm.qs[h][half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
     }
     if (tid < nrep) { sm.m_run[tid] = -INFINITY; sm.l_run[tid] = 0.0; }
-    const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
     // the CTA whose span holds position p appends the new key / value first
     const bool owner = (p >= t0 && p < t1);
     if (owner) {
@@ -122,8 +155,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     }
     __syncthreads();
     if (owner) {
-        if (warp == 0) quant_row_warp(sm.knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p, lane);
-        if (warp == 1) quant_row_warp(sm.vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p, lane);
+        const bool in_raw = p - t0 < raw_rows;
+        if (warp == 0) quant_row_warp(sm.knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p,
+                                      in_raw ? sm.kraw + (p - t0) * hd : nullptr, in_raw ? sm.ksr + (p - t0) : nullptr, lane);
+        if (warp == 1) quant_row_warp(sm.vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p,
+                                      in_raw ? sm.vraw + (p - t0) * hd : nullptr, in_raw ? sm.vsr + (p - t0) : nullptr, lane);
     }
     __syncthreads();  // the block's own global writes are visible to it after the barrier
     STAMP(2);
@@ -131,7 +167,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     // thread-owned output elements (head, dim): items tid, tid + 512
     double acc[2] = {0.0, 0.0};
     const int n_out = nrep * hd;
-    const int row16 = hd / 16;  // 16-byte pieces per row
 
     for (int tb = t0; tb < t1; tb += kTilePos) {
         const int n_here = min(kTilePos, t1 - tb);
@@ -139,9 +174,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         //     (dequantize_q8, kv_cache.rs:122-128), into f32 rows
         for (int i = tid; i < n_here * row16; i += blockDim.x) {
             const int r = i / row16, c16 = i % row16;
-            const uint4 kv = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + tb + r) * hd)[c16];
-            const uint4 vv = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + tb + r) * hd)[c16];
-            const float ks = a.cache.k_s[row_base + tb + r], vs = a.cache.v_s[row_base + tb + r];
+            const int rr = tb - t0 + r;  // row within the span
+            uint4 kv, vv;
+            float ks, vs;
+            if (rr < raw_rows) {
+                kv = reinterpret_cast<const uint4*>(sm.kraw + rr * hd)[c16];
+                vv = reinterpret_cast<const uint4*>(sm.vraw + rr * hd)[c16];
+                ks = sm.ksr[rr];
+                vs = sm.vsr[rr];
+            } else {
+                kv = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + tb + r) * hd)[c16];
+                vv = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + tb + r) * hd)[c16];
+                ks = a.cache.k_s[row_base + tb + r];
+                vs = a.cache.v_s[row_base + tb + r];
+            }
             const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
             float* kdst = &sm.kf[r][(c16 * 16) >> 6][(c16 * 16) & 63];
             float* vdst = &sm.vf[r][c16 * 16];
@@ -267,12 +313,31 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     __threadfence();
     if (tid == 0) a.counters[blockIdx.x] = 0;  // ready for the next launch
     const double* group = a.partial + ((int64_t)b * a.n_heads + kvh * nrep) * a.splits * (hd + 2);
-    // per-span maxima and sums first (one batch of independent loads), weights w_s = e^{m_s - m}
-    double* mw = reinterpret_cast<double*>(sm.vf);          // [nrep][splits] weights (the tile buffers are free now)
-    double* lsum = mw + kMaxRep * 64;                        // [nrep] merged denominators
+    // One batch of independent loads: every span's maximum and sum into shared memory and, at
+    // the same time, this thread's output column of the first spans into registers; the weights
+    // w_s = e^{m_s - m} are formed while those are in flight.
+    constexpr int kMergeBatch = 16;
+    double* mw = reinterpret_cast<double*>(sm.vf);          // [nrep][64] maxima, then weights (the tile buffers are free now)
+    double* ls = mw + kMaxRep * 64;                          // [nrep][64] sums
+    double* lsum = ls + kMaxRep * 64;                        // [nrep] merged denominators
     for (int i = tid; i < nrep * a.splits; i += blockDim.x) {
         const int h = i / a.splits, s2 = i % a.splits;
-        mw[h * 64 + s2] = __ldcg(group + ((int64_t)h * a.splits + s2) * (hd + 2));
+        const double* src = group + ((int64_t)h * a.splits + s2) * (hd + 2);
+        mw[h * 64 + s2] = __ldcg(src);
+        ls[h * 64 + s2] = __ldcg(src + 1);
+    }
+    // (head, column) items: item tid and, for nrep * hd > 512, item tid + 512
+    double pre[2][kMergeBatch];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int it = tid + e * kAttnThreads;
+        if (it < nrep * hd) {
+            const int h = it / hd, c = it % hd;
+            const double* base = group + (int64_t)h * a.splits * (hd + 2) + 2 + c;
+#pragma unroll
+            for (int s2 = 0; s2 < kMergeBatch; ++s2)
+                pre[e][s2] = s2 < a.splits ? __ldcg(base + (int64_t)s2 * (hd + 2)) : 0.0;
+        }
     }
     __syncthreads();
     if (warp < nrep) {
@@ -285,8 +350,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         for (int s2 = lane; s2 < a.splits; s2 += 32) {
             const double ms = mw[h * 64 + s2];
             const double w = ms == -INFINITY ? 0.0 : exp(ms - m);  // spans without positions weigh nothing
-            const double ls = __ldcg(group + ((int64_t)h * a.splits + s2) * (hd + 2) + 1);
-            l = fma(ls, w, l);
+            l = fma(ls[h * 64 + s2], w, l);
             mw[h * 64 + s2] = w;
         }
 #pragma unroll
@@ -294,24 +358,32 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         if (lane == 0) lsum[h] = l;
     }
     __syncthreads();
-    for (int it = tid; it < nrep * hd; it += blockDim.x) {
-        const int h = it / hd, c = it % hd;
-        const double* base = group + (int64_t)h * a.splits * (hd + 2) + 2 + c;
-        double v0 = 0.0, v1 = 0.0;
-        int s2 = 0;
-#pragma unroll 4
-        for (; s2 + 1 < a.splits; s2 += 2) {
-            v0 = fma(__ldcg(base + (int64_t)s2 * (hd + 2)), mw[h * 64 + s2], v0);
-            v1 = fma(__ldcg(base + (int64_t)(s2 + 1) * (hd + 2)), mw[h * 64 + s2 + 1], v1);
-        }
-        if (s2 < a.splits) v0 = fma(__ldcg(base + (int64_t)s2 * (hd + 2)), mw[h * 64 + s2], v0);
-        const float o = (float)((v0 + v1) / lsum[h]);
-        a.out[((int64_t)b * a.n_heads + kvh * nrep + h) * hd + c] = o;
-        if (a.absmax_out) {
-            float mx = fabsf(o);
 #pragma unroll
-            for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
-            if (lane == 0) atomicMax(a.absmax_out + b, __float_as_uint(mx));
+    for (int e = 0; e < 2; ++e) {
+        const int it = tid + e * kAttnThreads;
+        if (it < nrep * hd) {
+            const int h = it / hd, c = it % hd;
+            const double* base = group + (int64_t)h * a.splits * (hd + 2) + 2 + c;
+            double v0 = 0.0, v1 = 0.0;
+#pragma unroll
+            for (int s2 = 0; s2 < kMergeBatch; s2 += 2) {
+                // (spans without positions have weight 0 but may hold anything: skip them)
+                if (s2 < a.splits && mw[h * 64 + s2] != 0.0) v0 = fma(pre[e][s2], mw[h * 64 + s2], v0);
+                if (s2 + 1 < a.splits && mw[h * 64 + s2 + 1] != 0.0) v1 = fma(pre[e][s2 + 1], mw[h * 64 + s2 + 1], v1);
+            }
+            for (int s2 = kMergeBatch; s2 < a.splits; s2 += 2) {
+                if (mw[h * 64 + s2] != 0.0) v0 = fma(__ldcg(base + (int64_t)s2 * (hd + 2)), mw[h * 64 + s2], v0);
+                if (s2 + 1 < a.splits && mw[h * 64 + s2 + 1] != 0.0)
+                    v1 = fma(__ldcg(base + (int64_t)(s2 + 1) * (hd + 2)), mw[h * 64 + s2 + 1], v1);
+            }
+            const float o = (float)((v0 + v1) / lsum[h]);
+            a.out[((int64_t)b * a.n_heads + kvh * nrep + h) * hd + c] = o;
+            if (a.absmax_out) {
+                float mx = fabsf(o);
+#pragma unroll
+                for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
+                if (lane == 0) atomicMax(a.absmax_out + b, __float_as_uint(mx));
+            }
         }
     }
     STAMP(8);

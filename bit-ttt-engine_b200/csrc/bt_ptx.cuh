@@ -52,6 +52,45 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Bounded wait for warps that are off the critical path (a producer waiting for a free slot,
+// an epilogue warp waiting for partial sums): a non-blocking test and a short sleep between
+// tests, so that the waiting warp leaves the shared-memory pipeline to the warps doing work.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Two non-blocking tests issued back to back, so that their shared-memory round trips overlap
+// (a test's result is consumed inside its own asm block, which stalls the warp until it is back).
+__device__ __forceinline__ void mbar_test_wait2(uint64_t* bar_a, uint32_t parity_a, uint64_t* bar_b, uint32_t parity_b,
+                                                bool& done_a, bool& done_b) {
+    uint32_t ra, rb;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%2], %3;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%4], %5;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "selp.u32 %1, 1, 0, q;\n\t}"
+        : "=r"(ra), "=r"(rb)
+        : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b)
+        : "memory");
+    done_a = ra != 0;
+    done_b = rb != 0;
+}
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        __nanosleep(32);
+    }
+    return false;
+}
+
 // 1-D bulk copy global -> shared of this CTA; bytes and both addresses multiples of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
                                          uint64_t* bar) {
@@ -76,6 +115,13 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// c + sum of the four byte products a_i (unsigned) * b_i (signed)
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
 
 // round(v) with halves away from zero as an int, for |v| < 2^22: equal to (int)roundf(v).
