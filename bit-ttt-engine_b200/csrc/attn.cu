@@ -5,6 +5,8 @@
 // layers/attention.rs:228-239).  The cache is read in place as u8; nothing is
 // re-materialised in f32 (the reference dequantises the whole cache every step,
 // layers/kv_cache.rs:84-92).  HBM-bound on the cache bytes: 2*n_kv*T*(hd+4) per sequence.
+#include <stddef.h>
+
 #include "bt_model.cuh"
 #include "bt_ptx.cuh"
 
@@ -46,40 +48,50 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
     }
 }
 
-// One CTA = one (sequence, KV head, span of positions), 512 threads.  The span is walked
-// in tiles of 64 positions; per tile: (1) the K and V rows are dequantised into shared memory,
-// (2) thread (head, position, half) forms half of a score with a 64-long f64 dot product, (3) one warp
-// per head turns the tile's scores into softmax weights (running max / sum across tiles),
-// (4) thread (head, dim) accumulates P.V over the tile.  No cross-thread reduction of the
-// accumulators is needed, and everything between the u8 loads and the final rounding is
-// f64, so the result does not depend on how positions are cut into tiles and spans.
-constexpr int kTilePos = 64;
-constexpr int kHalfPad = 68;   // floats per staged half row: 64 + 4, conflict-free 16-byte reads
+// One CTA = one (sequence, KV head, span of positions), 512 threads.  The span is walked in
+// tiles of 128 positions that sit in shared memory exactly as the cache stores them (u8 rows +
+// one f32 scale per row); the first tile is fetched before the kernel waits for its
+// predecessor.  Converting to f64 is the expensive instruction here (a fraction of the rate of
+// an f64 FMA), so the work is cut such that every cache element is dequantised and widened by
+// exactly one thread, in registers, and used there for all NREP query heads of the KV group:
+//   (1) scores: warp w owns rows 4w .. 4w + 3 (+64), lane e the dims {2e, 2e + 1} + 64 j; the
+//       lane's partial sums for 4 rows x NREP heads are added across the warp by a butterfly;
+//   (2) softmax weights of the tile, one warp per head (running max / sum across tiles);
+//   (3) P.V: thread (pair of dims, group of rows) accumulates its rows for all NREP heads; the
+//       row groups are added once, after the last tile.
+// Everything between the u8 loads and the final rounding is f64 on exact f32 values
+// ((f32(q) - 128) * s, dequantize_q8, kv_cache.rs:122-128), so the result does not depend
+// (beyond f64 rounding) on how positions are cut into tiles, groups and spans.
+constexpr int kTilePos = 128;  // = cache rows prefetched per CTA
 constexpr int kMaxRep = 8;
-constexpr int kRawPos = 128;   // cache rows prefetched per CTA
 
 struct AttnSmem {
-    alignas(16) float qs[kMaxRep][128];  // rotated queries (exact f32 values)
+    alignas(16) double qd[kMaxRep][128];  // rotated queries (exact f32 values, widened)
     double pw[kMaxRep][kTilePos];
     float sc[kMaxRep][kTilePos];
     double m_run[kMaxRep], l_run[kMaxRep], corr[kMaxRep];
     float knew[128], vnew[128];
-    alignas(16) float kf[kTilePos][2][kHalfPad];  // dequantised keys of the tile, two halves of 64 dims
-    alignas(16) float vf[kTilePos][128];          // dequantised values of the tile
-    // the span's first kRawPos cache rows as stored (u8 + scale), fetched before the kernel
-    // waits for its predecessor
-    alignas(16) uint8_t kraw[kRawPos * 128];
-    alignas(16) uint8_t vraw[kRawPos * 128];
-    float ksr[kRawPos], vsr[kRawPos];
+    alignas(16) uint8_t kraw[kTilePos * 128];  // the tile's cache rows as stored
+    alignas(16) uint8_t vraw[kTilePos * 128];
+    float ksr[kTilePos], vsr[kTilePos];
+    alignas(16) double red[512 * 2 * kMaxRep];  // [row group][head][dim] partial outputs; scratch of the merge
 };
 
+// (f32(byte) - 128) * s without an integer-to-float conversion: 0x4B0000bb is the float
+// 2^23 + b, and subtracting 2^23 + 128 is exact.
+__device__ __forceinline__ double dequant_wide(uint32_t bytes, int which, float s) {
+    const uint32_t bits = which == 0 ? __byte_perm(bytes, 0x4B000000u, 0x7540) : __byte_perm(bytes, 0x4B000000u, 0x7541);
+    return (double)__fmul_rn(__fsub_rn(__uint_as_float(bits), 8388736.0f), s);
+}
+
+template <int NREP>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
 #define STAMP(i) do { if (a.dbg && (i) < 8 && threadIdx.x == 0) a.dbg[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = ptx::globaltimer(); } while (0)
     STAMP(0);
     const int hd = a.head_dim, half = hd >> 1;
-    const int nrep = a.n_heads / a.n_kv;
+    constexpr int nrep = NREP;
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int split = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -89,7 +101,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     // The cache rows of earlier positions were written by earlier steps, so they can be fetched
     // before the dependency wait (whatever sits in rows at or beyond the current position is
     // fetched too and never used; the owner of the new position overwrites its copy below).
-    const int raw_rows = max(0, min(min(kRawPos, a.span), a.cache.max_seq - t0));
+    const int raw_rows = max(0, min(min(kTilePos, a.span), a.cache.max_seq - t0));
     {
         const uint4* ksrc = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + t0) * hd);
         const uint4* vsrc = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + t0) * hd);
@@ -136,8 +148,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         const float cs = cos_p[c], sn = sin_p[c];
         const float* qh = qkv + (int64_t)(kvh * nrep + h) * hd;
         const float x1 = qh[c], x2 = qh[half + c];
-        sm.qs[h][c] = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
-        sm.qs[h][half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
+        sm.qd[h][c] = (double)__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+        sm.qd[h][half + c] = (double)__fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
     }
     if (tid < nrep) { sm.m_run[tid] = -INFINITY; sm.l_run[tid] = 0.0; }
     // the CTA whose span holds position p appends the new key / value first
@@ -164,76 +176,87 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     __syncthreads();  // the block's own global writes are visible to it after the barrier
     STAMP(2);
 
-    // thread-owned output elements (head, dim): items tid, tid + 512
-    double acc[2] = {0.0, 0.0};
-    const int n_out = nrep * hd;
+    // P.V ownership: thread = (pair of dims dp, row group rg); rows rg, rg + n_rg, ... of each tile
+    const int n_dp = hd >> 1;
+    const int n_rg = kAttnThreads / n_dp < kTilePos ? kAttnThreads / n_dp : kTilePos;
+    const int dp = tid % n_dp, rg = tid / n_dp;
+    const bool pv_active = rg < n_rg;
+    double acc[NREP][2];
+#pragma unroll
+    for (int h = 0; h < NREP; ++h) acc[h][0] = acc[h][1] = 0.0;
 
     for (int tb = t0; tb < t1; tb += kTilePos) {
         const int n_here = min(kTilePos, t1 - tb);
-        // (1) stage the tile: every byte is dequantised once, (f32(q) - 128) * s
-        //     (dequantize_q8, kv_cache.rs:122-128), into f32 rows
-        for (int i = tid; i < n_here * row16; i += blockDim.x) {
-            const int r = i / row16, c16 = i % row16;
-            const int rr = tb - t0 + r;  // row within the span
-            uint4 kv, vv;
-            float ks, vs;
-            if (rr < raw_rows) {
-                kv = reinterpret_cast<const uint4*>(sm.kraw + rr * hd)[c16];
-                vv = reinterpret_cast<const uint4*>(sm.vraw + rr * hd)[c16];
-                ks = sm.ksr[rr];
-                vs = sm.vsr[rr];
-            } else {
-                kv = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + tb + r) * hd)[c16];
-                vv = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + tb + r) * hd)[c16];
-                ks = a.cache.k_s[row_base + tb + r];
-                vs = a.cache.v_s[row_base + tb + r];
+        if (tb > t0) {
+            // later tiles of a long span: copy the rows as stored (the first tile is already there)
+            __syncthreads();
+            const uint4* ksrc = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + tb) * hd);
+            const uint4* vsrc = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + tb) * hd);
+            for (int i = tid; i < n_here * row16; i += blockDim.x) {
+                reinterpret_cast<uint4*>(sm.kraw)[i] = ksrc[i];
+                reinterpret_cast<uint4*>(sm.vraw)[i] = vsrc[i];
             }
-            const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
-            float* kdst = &sm.kf[r][(c16 * 16) >> 6][(c16 * 16) & 63];
-            float* vdst = &sm.vf[r][c16 * 16];
-#pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-                float4 ko, vo;
-                ko.x = __fmul_rn((float)(kw[wi] & 0xffu) - 128.0f, ks);
-                ko.y = __fmul_rn((float)((kw[wi] >> 8) & 0xffu) - 128.0f, ks);
-                ko.z = __fmul_rn((float)((kw[wi] >> 16) & 0xffu) - 128.0f, ks);
-                ko.w = __fmul_rn((float)(kw[wi] >> 24) - 128.0f, ks);
-                vo.x = __fmul_rn((float)(vw[wi] & 0xffu) - 128.0f, vs);
-                vo.y = __fmul_rn((float)((vw[wi] >> 8) & 0xffu) - 128.0f, vs);
-                vo.z = __fmul_rn((float)((vw[wi] >> 16) & 0xffu) - 128.0f, vs);
-                vo.w = __fmul_rn((float)(vw[wi] >> 24) - 128.0f, vs);
-                *reinterpret_cast<float4*>(kdst + 4 * wi) = ko;
-                *reinterpret_cast<float4*>(vdst + 4 * wi) = vo;
+            for (int i = tid; i < n_here; i += blockDim.x) {
+                sm.ksr[i] = a.cache.k_s[row_base + tb + i];
+                sm.vsr[i] = a.cache.v_s[row_base + tb + i];
             }
+            __syncthreads();
         }
-        __syncthreads();
         STAMP(3);
-        // (2) scores: item = (head, position, half of the head dims); the two halves sit in
-        //     neighbouring lanes and are added with one shuffle
-        for (int it = tid; it < nrep * kTilePos * 2; it += blockDim.x) {
-            const int hf = it & 1, r = (it >> 1) % kTilePos, h = it / (2 * kTilePos);
-            const int c0 = hf * 64, cn = min(64, hd - c0);
-            double d0 = 0.0, d1 = 0.0;
-            if (r < n_here && cn > 0) {
-                const float* row = sm.kf[r][hf];
-                const float* qh = sm.qs[h] + c0;
-#pragma unroll 4
-                for (int c = 0; c < cn; c += 4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(row + c);
-                    const float4 q4 = *reinterpret_cast<const float4*>(qh + c);
-                    d0 = fma((double)q4.x, (double)k4.x, d0);
-                    d1 = fma((double)q4.y, (double)k4.y, d1);
-                    d0 = fma((double)q4.z, (double)k4.z, d0);
-                    d1 = fma((double)q4.w, (double)k4.w, d1);
+        // (1) scores.  One read of q serves four rows, one dequantised K element all heads; the
+        //     lane's 4 * NREP partial sums are then added across the warp with a halving
+        //     butterfly (each step sends half of the values and keeps the other half), which
+        //     leaves the sum of value number lane >> kScoreShift in every lane.
+        for (int row0 = 4 * warp; row0 < n_here; row0 += 4 * kAttnWarps) {
+            constexpr int kVals = 4 * NREP;
+            double d[kVals];
+#pragma unroll
+            for (int i = 0; i < kVals; ++i) d[i] = 0.0;
+            for (int c = 2 * lane; c < hd; c += 64) {
+                double2 q2[NREP];
+#pragma unroll
+                for (int h = 0; h < NREP; ++h) q2[h] = *reinterpret_cast<const double2*>(&sm.qd[h][c]);
+#pragma unroll
+                for (int rl = 0; rl < 4; ++rl) {
+                    if (row0 + rl < n_here) {  // rows beyond the current length hold anything
+                        const uint32_t kb = *reinterpret_cast<const uint16_t*>(sm.kraw + (row0 + rl) * hd + c);
+                        const float ks = sm.ksr[row0 + rl];
+                        const double k0 = dequant_wide(kb, 0, ks), k1 = dequant_wide(kb, 1, ks);
+#pragma unroll
+                        for (int h = 0; h < NREP; ++h) {
+                            d[rl * NREP + h] = fma(q2[h].x, k0, d[rl * NREP + h]);
+                            d[rl * NREP + h] = fma(q2[h].y, k1, d[rl * NREP + h]);
+                        }
+                    }
                 }
             }
-            double d = d0 + d1;
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            if (hf == 0 && r < n_here) sm.sc[h][r] = __fmul_rn((float)d, a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
+            int n = kVals;
+#pragma unroll
+            for (int msk = 16; msk >= 1; msk >>= 1) {
+                if (n > 1) {
+                    n >>= 1;
+                    const bool upper = (lane & msk) != 0;
+#pragma unroll
+                    for (int i = 0; i < kVals / 2; ++i) {
+                        if (i < n) {
+                            const double keep = upper ? d[n + i] : d[i];
+                            const double send = upper ? d[i] : d[n + i];
+                            d[i] = keep + __shfl_xor_sync(0xffffffffu, send, msk);
+                        }
+                    }
+                } else {
+                    d[0] += __shfl_xor_sync(0xffffffffu, d[0], msk);
+                }
+            }
+            constexpr int kScoreShift = NREP == 8 ? 0 : NREP == 4 ? 1 : NREP == 2 ? 2 : 3;
+            const int idx = lane >> kScoreShift;
+            const int rl = idx / NREP, h = idx % NREP;
+            if ((lane & ((1 << kScoreShift) - 1)) == 0 && row0 + rl < n_here)
+                sm.sc[h][row0 + rl] = __fmul_rn((float)d[0], a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
         }
         __syncthreads();
         STAMP(4);
-        // (3) softmax weights of the tile, one warp per head
+        // (2) softmax weights of the tile, one warp per head
         if (warp < nrep) {
             const int h = warp;
             double sv[kTilePos / 32];
@@ -267,31 +290,38 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         }
         __syncthreads();
         STAMP(5);
-        // (4) acc[head, dim] = acc * corr + sum_r p[head, r] * v[r, dim], two chains per thread
+        // (3) acc[head][dim pair] = acc * corr + sum over this thread's rows of p[head, r] * v[r, dims]
+        if (pv_active) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int it = tid + e * kAttnThreads;
-            if (it < n_out) {
-                const int h = it / hd, dcol = it % hd;
-                double v0 = acc[e] * sm.corr[h], v1 = 0.0;
-                int r = 0;
-                for (; r + 1 < n_here; r += 2) {
-                    v0 = fma(sm.pw[h][r], (double)sm.vf[r][dcol], v0);
-                    v1 = fma(sm.pw[h][r + 1], (double)sm.vf[r + 1][dcol], v1);
+            for (int h = 0; h < NREP; ++h) { const double cr = sm.corr[h]; acc[h][0] *= cr; acc[h][1] *= cr; }
+            for (int r = rg; r < n_here; r += n_rg) {
+                const uint32_t vb = *reinterpret_cast<const uint16_t*>(sm.vraw + r * hd + 2 * dp);
+                const float vs = sm.vsr[r];
+                const double v0 = dequant_wide(vb, 0, vs), v1 = dequant_wide(vb, 1, vs);
+#pragma unroll
+                for (int h = 0; h < NREP; ++h) {
+                    const double pr = sm.pw[h][r];
+                    acc[h][0] = fma(pr, v0, acc[h][0]);
+                    acc[h][1] = fma(pr, v1, acc[h][1]);
                 }
-                if (r < n_here) v0 = fma(sm.pw[h][r], (double)sm.vf[r][dcol], v0);
-                acc[e] = v0 + v1;
             }
         }
-        __syncthreads();
     }
+    // add the row groups (fixed order) through shared memory, one (head, dim) per thread
+    {
+        double* red = sm.red;  // [n_rg][NREP][hd]
+        if (pv_active) {
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        const int it = tid + e * kAttnThreads;
-        if (it < n_out) {
+            for (int h = 0; h < NREP; ++h)
+                *reinterpret_cast<double2*>(red + ((int64_t)rg * NREP + h) * hd + 2 * dp) = make_double2(acc[h][0], acc[h][1]);
+        }
+        __syncthreads();
+        for (int it = tid; it < NREP * hd; it += blockDim.x) {
             const int h = it / hd, dcol = it % hd;
+            double v = 0.0;
+            for (int g2 = 0; g2 < n_rg; ++g2) v += red[((int64_t)g2 * NREP + h) * hd + dcol];
             double* dst = part_base + (int64_t)h * a.splits * (hd + 2);
-            dst[2 + dcol] = acc[e];
+            dst[2 + dcol] = v;
             if (dcol == 0) { dst[0] = sm.m_run[h]; dst[1] = sm.l_run[h]; }
         }
     }
@@ -317,7 +347,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     // the same time, this thread's output column of the first spans into registers; the weights
     // w_s = e^{m_s - m} are formed while those are in flight.
     constexpr int kMergeBatch = 16;
-    double* mw = reinterpret_cast<double*>(sm.vf);          // [nrep][64] maxima, then weights (the tile buffers are free now)
+    double* mw = sm.red;          // [nrep][64] maxima, then weights (the tile buffers are free now)
     double* ls = mw + kMaxRep * 64;                          // [nrep][64] sums
     double* lsum = ls + kMaxRep * 64;                        // [nrep] merged denominators
     for (int i = tid; i < nrep * a.splits; i += blockDim.x) {
@@ -402,25 +432,41 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, int max_se
 
 }  // namespace
 
-cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
-    const int rep = a.n_kv > 0 ? a.n_heads / a.n_kv : 0;
-    if (a.head_dim % 32 != 0 || a.head_dim > 128 || a.n_heads % a.n_kv != 0 || rep < 1 || rep > kMaxRep ||
-        a.span % 32 != 0)
-        return cudaErrorInvalidValue;
+namespace {
+template <int NREP>
+cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
+    // the row-group buffer at the end of the shared-memory block scales with the heads per group
+    constexpr size_t kRedDoubles = 512 * 2 * NREP > 2 * kMaxRep * 64 + kMaxRep ? 512 * 2 * NREP : 2 * kMaxRep * 64 + kMaxRep;
+    constexpr size_t kSmem = offsetof(AttnSmem, red) + kRedDoubles * sizeof(double);
+    constexpr size_t kHalfSm = 116 * 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e0 = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)(sizeof(AttnSmem) > 116 * 1024 ? sizeof(AttnSmem) : 116 * 1024));
+        cudaError_t e0 = cudaFuncSetAttribute(attn_decode_kernel<NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)(kSmem > kHalfSm ? kSmem : kHalfSm));
         if (e0 != cudaSuccess) return e0;
         configured = true;
     }
     dim3 grid(a.batch * a.n_kv, a.splits);
     // When the whole grid fits one CTA per SM, ask for more than half of an SM's shared
-    // memory: the block scheduler then cannot pair two CTAs on one SM while others idle
-    // (measured: paired CTAs take 22 us instead of 16).
-    size_t smem = sizeof(AttnSmem);
-    if ((int64_t)grid.x * grid.y <= a.sm_count && smem < 116 * 1024) smem = 116 * 1024;
-    return launch_pdl(attn_decode_kernel, grid, dim3(kAttnThreads), smem, stream, a.pdl, a);
+    // memory: the block scheduler then cannot pair two CTAs on one SM while others idle.
+    size_t smem = kSmem;
+    if ((int64_t)grid.x * grid.y <= a.sm_count && smem < kHalfSm) smem = kHalfSm;
+    return launch_pdl(attn_decode_kernel<NREP>, grid, dim3(kAttnThreads), smem, stream, a.pdl, a);
+}
+}  // namespace
+
+cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
+    const int rep = a.n_kv > 0 ? a.n_heads / a.n_kv : 0;
+    if (a.head_dim % 32 != 0 || a.head_dim > 128 || a.n_heads % a.n_kv != 0 || rep < 1 || rep > kMaxRep ||
+        a.span % 32 != 0)
+        return cudaErrorInvalidValue;
+    switch (rep) {
+        case 1: return launch_attn_rep<1>(a, stream);
+        case 2: return launch_attn_rep<2>(a, stream);
+        case 4: return launch_attn_rep<4>(a, stream);
+        case 8: return launch_attn_rep<8>(a, stream);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t launch_rope_tables(const float* inv_freq, int max_seq, int half, float* cos_t, float* sin_t,
