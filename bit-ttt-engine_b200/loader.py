@@ -251,3 +251,10 @@ def save_checkpoint(directory: str, w: SyntheticWeights, hf_names: bool = True, 
                  n_kv_heads=cfg.n_kv_heads, intermediate_dim=cfg.intermediate_dim)
     with open(os.path.join(directory, "config.json"), "w", encoding="utf-8") as f:
         json.dump(d, f, indent=1)
+
+
+def load_model(path: str, max_batch: int = 1, device: int = 0):
+    """`Llama::load_auto` for the decode path: read the checkpoint and build the device model."""
+    from .synthetic import build_model
+    cfg, w = load_checkpoint(path)
+    return build_model(w, max_batch=max_batch, device=device)
