@@ -69,7 +69,8 @@ struct AttnSmem {
     alignas(16) double qd[kMaxRep][128];  // rotated queries (exact f32 values, widened)
     double pw[kMaxRep][kTilePos];
     float sc[kMaxRep][kTilePos];
-    double m_run[kMaxRep], l_run[kMaxRep], corr[kMaxRep];
+    double m_run[kMaxRep], l_run[kMaxRep], corr[kMaxRep], m_next[kMaxRep];
+    double wmax[kMaxRep][4], wsum[kMaxRep][4];  // per warp (32 rows) maxima and sums of the tile
     float knew[128], vnew[128];
     alignas(16) uint8_t kraw[kTilePos * 128];  // the tile's cache rows as stored
     alignas(16) uint8_t vraw[kTilePos * 128];
@@ -256,40 +257,48 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         }
         __syncthreads();
         STAMP(4);
-        // (2) softmax weights of the tile, one warp per head
-        if (warp < nrep) {
-            const int h = warp;
-            double sv[kTilePos / 32];
-            double tmax = -INFINITY;
+        // (2) softmax weights of the tile: one (head, row) per thread, so that the f64 exponentials
+        //     run on every warp; a warp covers 32 rows of one head, four warps a head.  Tile
+        //     maxima and sums go through shared memory in a fixed order.
+        constexpr int kSoftItems = (NREP * kTilePos + kAttnThreads - 1) / kAttnThreads;
+        double sv[kSoftItems];
 #pragma unroll
-            for (int i = 0; i < kTilePos / 32; ++i) {
-                const int r = lane + 32 * i;
-                sv[i] = r < n_here ? (double)sm.sc[h][r] : -INFINITY;
-                tmax = fmax(tmax, sv[i]);
-            }
+        for (int e = 0; e < kSoftItems; ++e) {
+            const int it = tid + e * kAttnThreads;
+            const int h = it / kTilePos, r = it % kTilePos;
+            sv[e] = (h < NREP && r < n_here) ? (double)sm.sc[h][r] : -INFINITY;
+            double wm = sv[e];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
-            const double m_old = sm.m_run[h];
-            const double m_new = fmax(m_old, tmax);
-            double psum = 0.0;
+            for (int o = 16; o > 0; o >>= 1) wm = fmax(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+            if (lane == 0 && h < NREP) sm.wmax[h][(it >> 5) & 3] = wm;
+        }
+        __syncthreads();
 #pragma unroll
-            for (int i = 0; i < kTilePos / 32; ++i) {
-                const int r = lane + 32 * i;
-                const double pe = r < n_here ? exp(sv[i] - m_new) : 0.0;
+        for (int e = 0; e < kSoftItems; ++e) {
+            const int it = tid + e * kAttnThreads;
+            const int h = it / kTilePos, r = it % kTilePos;
+            if (h < NREP) {  // warp-uniform
+                const double m_old = sm.m_run[h];
+                const double m_new = fmax(fmax(m_old, fmax(sm.wmax[h][0], sm.wmax[h][1])), fmax(sm.wmax[h][2], sm.wmax[h][3]));
+                const double pe = r < n_here ? exp(sv[e] - m_new) : 0.0;
                 sm.pw[h][r] = pe;
-                psum += pe;
-            }
+                double ws = pe;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
-            if (lane == 0) {
-                const double corr = exp(m_old - m_new);  // exp(-inf) = 0 on the first tile
-                sm.corr[h] = corr;
-                sm.l_run[h] = fma(sm.l_run[h], corr, psum);
-                sm.m_run[h] = m_new;
+                for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+                if (lane == 0) sm.wsum[h][(it >> 5) & 3] = ws;
+                if (r == 0) {
+                    sm.corr[h] = exp(m_old - m_new);  // exp(-inf) = 0 on the first tile
+                    sm.m_next[h] = m_new;
+                }
             }
         }
         __syncthreads();
         STAMP(5);
+        if (tid < NREP) {  // running sum and maximum (nobody reads them before the next barrier)
+            const double psum = ((sm.wsum[tid][0] + sm.wsum[tid][1]) + sm.wsum[tid][2]) + sm.wsum[tid][3];
+            sm.l_run[tid] = fma(sm.l_run[tid], sm.corr[tid], psum);
+            sm.m_run[tid] = sm.m_next[tid];
+        }
         // (3) acc[head][dim pair] = acc * corr + sum over this thread's rows of p[head, r] * v[r, dims]
         if (pv_active) {
 #pragma unroll
@@ -346,7 +355,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     // One batch of independent loads: every span's maximum and sum into shared memory and, at
     // the same time, this thread's output column of the first spans into registers; the weights
     // w_s = e^{m_s - m} are formed while those are in flight.
-    constexpr int kMergeBatch = 16;
+    constexpr int kItems = NREP * 128 > kAttnThreads ? 2 : 1;  // (head, column) outputs per thread
+    constexpr int kMergeBatch = kItems == 1 ? 32 : 16;          // spans whose values are fetched up front
     double* mw = sm.red;          // [nrep][64] maxima, then weights (the tile buffers are free now)
     double* ls = mw + kMaxRep * 64;                          // [nrep][64] sums
     double* lsum = ls + kMaxRep * 64;                        // [nrep] merged denominators
@@ -357,9 +367,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         ls[h * 64 + s2] = __ldcg(src + 1);
     }
     // (head, column) items: item tid and, for nrep * hd > 512, item tid + 512
-    double pre[2][kMergeBatch];
+    double pre[kItems][kMergeBatch];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < kItems; ++e) {
         const int it = tid + e * kAttnThreads;
         if (it < nrep * hd) {
             const int h = it / hd, c = it % hd;
@@ -389,7 +399,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     }
     __syncthreads();
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < kItems; ++e) {
         const int it = tid + e * kAttnThreads;
         if (it < nrep * hd) {
             const int h = it / hd, c = it % hd;
