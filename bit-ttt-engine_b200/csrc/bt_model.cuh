@@ -14,10 +14,12 @@ cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int 
 
 // Row transform (none | RMSNorm | silu(gate)*up) + per-token absmax int8 quantisation.
 // x: [batch, x_stride] f32 (PRE_SWIGLU: gate at [0,k), up at [k,2k)); q rows of q_stride
-// bytes (multiple of 4, zero-filled beyond k); v_out optional [batch, k] transformed row.
+// bytes (multiple of 4, zero-filled beyond k; q may be null); v_out optional [batch, k]
+// transformed row; qtc optional: the same int8 values in the tensor-core product's activation
+// layout (k_tiles = padded k / 256), so that launch_gemm_tc can skip its own quantiser.
 cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
                              int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
-                             float* v_out, cudaStream_t stream);
+                             float* v_out, cudaStream_t stream, int8_t* qtc = nullptr, int k_tiles = 0);
 
 cudaError_t launch_lm_head(const __nv_bfloat16* w, const float* x, int batch, int hidden, int64_t vocab,
                            float* logits, int sm_count, cudaStream_t stream);

@@ -109,6 +109,11 @@ struct TcArgs {
     int64_t out_stride;
     int epilogue;              // EPI_I32 / EPI_F32 / EPI_F32_ACCUM / EPI_BF16
     unsigned int* err;
+    // With few output tiles (small N and M) the k range of a tile is cut into k_splits pieces
+    // that different CTAs work on; each piece leaves its raw int32 sums in part[split][token][row]
+    // and tc_finish_kernel adds them (integers: the result does not depend on the cut).
+    int k_splits;
+    int32_t* part;
 };
 
 template <int NT>
@@ -131,7 +136,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
     const int k_tiles = (int)a.k_tiles;
     const int row_sets = (int)((a.row_tiles + 7) / 8);
     const int tok_blocks = (a.m + NT - 1) / NT;
-    const int n_tiles = row_sets * tok_blocks;
+    const int k_splits = a.k_splits;
+    const int cps = (k_tiles + k_splits - 1) / k_splits;  // chunks per split (the host makes every split non-empty)
+    const int n_tiles = row_sets * tok_blocks * k_splits;  // work units: (row set, token block, k split)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1); }
@@ -156,9 +163,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
             int slot = 0;
             uint32_t par = 1;
             bool first = true;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < n_tiles; unit += gridDim.x) {
+                const int split = unit % k_splits, tile = unit / k_splits;
                 const int rs = tile % row_sets, tb = tile / row_sets;
-                for (int kt = 0; kt < k_tiles; ++kt) {
+                const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
+                for (int kt = kt0; kt < kt1; ++kt) {
                     if (!first) ok &= ptx::mbar_wait_bounded(&empty[slot], par);
                     uint8_t* st = stage_base + (size_t)slot * kStageBytes;
                     const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
@@ -179,11 +188,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
             int slot = 0, u = 0;
             uint32_t par = 0, upar = 0, acc_par = 0;
             bool first_tile = true;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < n_tiles; unit += gridDim.x) {
+                const int split = unit % k_splits;
+                const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
                 if (!first_tile) { ok &= ptx::mbar_wait_bounded(acc_empty, acc_par); acc_par ^= 1; }
                 first_tile = false;
                 tc_fence_after();
-                for (int kt = 0; kt < k_tiles; ++kt) {
+                for (int kt = kt0; kt < kt1; ++kt) {
                     ok &= ptx::mbar_wait_bounded(&full[slot], par);        // activation block landed
                     ok &= ptx::mbar_wait_bounded(&unp_full[u], upar);      // weights unpacked
                     tc_fence_after();
@@ -195,7 +206,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                         for (int ks = 0; ks < 2; ++ks) {  // 64 k' per residue = 2 x K32
                             const uint64_t ad = smem_desc(a_addr + r * kATileBytes + ks * 256, 128, 512);
                             const uint64_t bd = smem_desc(b_addr + r * (NT * 64) + ks * 256, 128, 512);
-                            umma_i8(tmem_base + r * NT, ad, bd, idesc, (kt > 0 || ks > 0) ? 1u : 0u);
+                            umma_i8(tmem_base + r * NT, ad, bd, idesc, (kt > kt0 || ks > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&unp_empty[u]);  // unpacked buffer reusable once these MMAs are done
@@ -213,10 +224,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
         int slot = 0, u = 0;
         uint32_t par = 0, upar = 1, acc_par = 0;
         bool first_unp = true;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        for (int unit = blockIdx.x; unit < n_tiles; unit += gridDim.x) {
+            const int split = unit % k_splits, tile = unit / k_splits;
             const int rs = tile % row_sets, tb = tile / row_sets;
             const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
-            for (int kt = 0; kt < k_tiles; ++kt) {
+            const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
+            for (int kt = kt0; kt < kt1; ++kt) {
                 ok &= ptx::mbar_wait_bounded(&full[slot], par);
                 if (!first_unp) ok &= ptx::mbar_wait_bounded(&unp_empty[u], upar);
                 // this thread's row: row tile r8 = tid/16, half = (tid%16)/8, g = tid%8; its 64 packed
@@ -261,7 +274,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                 for (int j = 0; j < 32; ++j) {
                     const int token = tb * NT + c0 + j;
                     if (token < a.m && row < a.n_out) {
-                        const int accv = (int)d0[j] + ((int)d1[j] >> 2) + ((int)d2[j] >> 4) + ((int)d3[j] >> 6) - a.qsum[token];
+                        const int folded = (int)d0[j] + ((int)d1[j] >> 2) + ((int)d2[j] >> 4) + ((int)d3[j] >> 6);
+                        if (k_splits > 1) {
+                            a.part[((int64_t)split * a.m + token) * a.n_out + row] = folded;
+                            continue;
+                        }
+                        const int accv = folded - a.qsum[token];
                         const int64_t o = (int64_t)token * a.out_stride + row;
                         if (a.epilogue == EPI_I32) {
                             reinterpret_cast<int32_t*>(a.out)[o] = accv;
@@ -314,10 +332,7 @@ __global__ void __launch_bounds__(256) act_quant_tc_kernel(const float* __restri
         int qv = 0;
         if (real && c < k) qv = max(-127, min(127, ptx::round_half_away(__fmul_rn(xr[c], inv))));
         local += qv;
-        const int kt = c >> 8, r = c & 3, kp = (c & 255) >> 2;  // k' inside the chunk
-        const int64_t off = (int64_t)kt * (4 * NT * 64) + (int64_t)r * (NT * 64) + (tin >> 3) * 512 + (kp >> 4) * 128 +
-                            (tin & 7) * 16 + (kp & 15);
-        blk[off] = (int8_t)qv;
+        blk[gemm_tc_act_offset(c, tin, NT)] = (int8_t)qv;
     }
     for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
     if ((threadIdx.x & 31) == 0) red_i[threadIdx.x >> 5] = local;
@@ -330,8 +345,37 @@ __global__ void __launch_bounds__(256) act_quant_tc_kernel(const float* __restri
     }
 }
 
+// Fewer tiles than half the SMs: cut k so that one wave of CTAs covers the product.
+int tc_k_splits(int n_tiles, int64_t k_tiles, int sm_count) {
+    if (n_tiles * 2 > sm_count || k_tiles < 4) return 1;
+    int want = sm_count / n_tiles;
+    if (want > k_tiles / 2) want = (int)(k_tiles / 2);
+    const int cps = (int)((k_tiles + want - 1) / want);
+    return (int)((k_tiles + cps - 1) / cps);
+}
+
+// Adds the k-split pieces of a product and applies the epilogue: one thread per (token, row).
+__global__ void __launch_bounds__(256) tc_finish_kernel(TcArgs a) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)a.m * a.n_out) return;
+    const int token = (int)(idx / a.n_out);
+    const int64_t row = idx % a.n_out;
+    int accv = -a.qsum[token];
+    for (int s2 = 0; s2 < a.k_splits; ++s2) accv += a.part[((int64_t)s2 * a.m + token) * a.n_out + row];
+    const int64_t o = (int64_t)token * a.out_stride + row;
+    if (a.epilogue == EPI_I32) {
+        reinterpret_cast<int32_t*>(a.out)[o] = accv;
+        return;
+    }
+    const float sw = a.sw_tiles[2 * (row >> 4) + ((row >> 3) & 1)];
+    const float y = __fmul_rn(__fmul_rn((float)accv, sw), a.sx[token]);
+    if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
+    else if (a.epilogue == EPI_F32_ACCUM) reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
+    else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
+}
+
 template <int NT>
-cudaError_t launch_nt(const TcArgs& a, int sm_count, cudaStream_t stream) {
+cudaError_t launch_nt(TcArgs a, int sm_count, int32_t* part, size_t part_bytes, cudaStream_t stream) {
     constexpr int kBBytes = 4 * NT * 64;
     const size_t smem = (size_t)kStages * (kRawBytes + kBBytes) + (size_t)kUnpBufs * 4 * kATileBytes + 256;
     static bool configured = false;
@@ -342,12 +386,32 @@ cudaError_t launch_nt(const TcArgs& a, int sm_count, cudaStream_t stream) {
     }
     const int row_sets = (int)((a.row_tiles + 7) / 8);
     const int n_tiles = row_sets * ((a.m + NT - 1) / NT);
-    const int grid = n_tiles < sm_count ? n_tiles : sm_count;
+    int splits = part ? tc_k_splits(n_tiles, a.k_tiles, sm_count) : 1;
+    if ((size_t)splits * a.m * a.n_out * sizeof(int32_t) > part_bytes) splits = 1;
+    a.k_splits = splits;
+    a.part = splits > 1 ? part : nullptr;
+    const int units = n_tiles * splits;
+    const int grid = units < sm_count ? units : sm_count;
     gemm_tc_kernel<NT><<<grid, kTcThreads, smem, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || splits == 1) return e;
+    const int64_t total = (int64_t)a.m * a.n_out;
+    tc_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 
 }  // namespace
+
+size_t gemm_tc_part_bytes(int sm_count) {
+    // pieces <= SMs / tiles and tokens x rows <= tiles x 128 x 128, hence pieces x tokens x rows <= SMs x 128 x 128
+    return (size_t)sm_count * kRows * 128 * sizeof(int32_t);
+}
+
+int gemm_tc_kernels(const LinearDev& lin, int64_t m, int sm_count) {
+    const int nt = m <= 64 ? 64 : 128;
+    const int n_tiles = (int)((lin.w.row_tiles + 7) / 8) * (int)((m + nt - 1) / nt);
+    return lin.w.n_bases * (tc_k_splits(n_tiles, lin.w.k_tiles, sm_count) > 1 ? 2 : 1);
+}
 
 size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles) {
     const int64_t nt = m <= 64 ? 64 : 128;
@@ -356,18 +420,19 @@ size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles) {
 
 cudaError_t launch_gemm_tc(const LinearDev& lin, const float* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
                            int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, int32_t* part, size_t part_bytes, bool prequantised) {
     if (lin.w.n_bases != 1 && epilogue == EPI_BF16) return cudaErrorInvalidValue;
     const int nt = m <= 64 ? 64 : 128;
     const int padded = (int)((m + nt - 1) / nt * nt);
-    if (nt == 64)
+    if (prequantised) {
+    } else if (nt == 64)
         act_quant_tc_kernel<64><<<padded, 256, 0, stream>>>(x, x_stride, (int)lin.w.k_in, (int)lin.w.k_tiles, (int)m, qtc, sx, qsum);
     else
         act_quant_tc_kernel<128><<<padded, 256, 0, stream>>>(x, x_stride, (int)lin.w.k_in, (int)lin.w.k_tiles, (int)m, qtc, sx, qsum);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     for (int b = 0; b < lin.w.n_bases; ++b) {
-        TcArgs a;
+        TcArgs a = {};
         a.tiles = lin.w.tiles + (size_t)b * lin.w.basis_stride();
         a.row_tiles = lin.w.row_tiles;
         a.k_tiles = lin.w.k_tiles;
@@ -381,7 +446,7 @@ cudaError_t launch_gemm_tc(const LinearDev& lin, const float* x, int64_t x_strid
         a.out_stride = out_stride;
         a.epilogue = (b > 0 && epilogue == EPI_F32) ? EPI_F32_ACCUM : epilogue;
         a.err = err;
-        e = nt == 64 ? launch_nt<64>(a, sm_count, stream) : launch_nt<128>(a, sm_count, stream);
+        e = nt == 64 ? launch_nt<64>(a, sm_count, part, part_bytes, stream) : launch_nt<128>(a, sm_count, part, part_bytes, stream);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;

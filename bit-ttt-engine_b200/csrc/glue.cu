@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
                                                         int8_t* __restrict__ q, int64_t q_stride,
                                                         float* __restrict__ s_out,
                                                         int32_t* __restrict__ qsum_out,
-                                                        float* __restrict__ v_out) {
+                                                        float* __restrict__ v_out, int8_t* __restrict__ qtc,
+                                                        int tc_nt, int k_tiles) {
     extern __shared__ float row[];
     __shared__ float red_f[32];
     __shared__ double red_d[32];
@@ -142,9 +143,20 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
     amax = block_max(amax, red_f);  // also orders the row[] writes before the reads below
     const float s = __fdiv_rn(amax, 127.0f);
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    int8_t* qr = q + (int64_t)b * q_stride;
     int local = 0;
-    for (int c = threadIdx.x * 4; c < q_stride; c += blockDim.x * 4) {
+    if (qtc) {
+        // straight into the tensor-core product's activation layout (gemm_tc_act_offset)
+        const int tb = b / tc_nt, tin = b % tc_nt;
+        int8_t* blk = qtc + (int64_t)tb * k_tiles * (4 * tc_nt * 64);
+        for (int c = threadIdx.x; c < k_tiles * kTileK; c += blockDim.x) {
+            int v = 0;
+            if (c < k && amax > 0.0f) v = max(-127, min(127, ptx::round_half_away(__fmul_rn(row[c], inv))));
+            local += v;
+            blk[gemm_tc_act_offset(c, tin, tc_nt)] = (int8_t)v;
+        }
+    }
+    int8_t* qr = q + (int64_t)b * q_stride;
+    for (int c = threadIdx.x * 4; q && c < q_stride; c += blockDim.x * 4) {
         uint32_t packed = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -399,7 +411,8 @@ cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int 
 
 cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
                              int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
-                             float* v_out, cudaStream_t stream) {
+                             float* v_out, cudaStream_t stream, int8_t* qtc, int k_tiles) {
+    const int tc_nt = batch <= 64 ? 64 : 128;
     const size_t smem = (size_t)k * sizeof(float);
     const int threads = k >= 4096 ? 512 : 256;
     static bool configured = false;
@@ -411,11 +424,11 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
     }
     if (smem > 160 * 1024) return cudaErrorInvalidConfiguration;
     if (pre == PRE_RMSNORM)
-        row_quant_kernel<PRE_RMSNORM><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out);
+        row_quant_kernel<PRE_RMSNORM><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
     else if (pre == PRE_SWIGLU)
-        row_quant_kernel<PRE_SWIGLU><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out);
+        row_quant_kernel<PRE_SWIGLU><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
     else
-        row_quant_kernel<PRE_NONE><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out);
+        row_quant_kernel<PRE_NONE><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
     return cudaGetLastError();
 }
 

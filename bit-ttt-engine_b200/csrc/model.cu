@@ -91,6 +91,8 @@ struct bt_model {
     float* act = nullptr;            // [max_batch, intermediate] silu(gate)*up
     float* xt = nullptr;             // [max_batch, max(hidden, intermediate)] transformed rows (batches above 8)
     int8_t* qtc = nullptr;           // activations in the tensor-core product's layout (batches above 8)
+    int32_t* tc_part = nullptr;      // k-split pieces of the tensor-core product
+    size_t tc_part_bytes = 0;
     void* lm_tiles = nullptr;        // lm_head in tensor-core tile order (batches above 8, hidden % 64 == 0)
     void* lm_btiles = nullptr;       // normalised hidden states as bf16 hi|lo tiles
     unsigned int* absmax = nullptr;  // [num_layers][2][max_batch] max|x| cells of the fused path
@@ -208,19 +210,21 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     const int H = c.hidden_dim, I = m->i_l, B = c.max_batch;
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
+    const int kt_h = (H + kTileK - 1) / kTileK, kt_i = (I + kTileK - 1) / kTileK;
     BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, false));
     for (int li = 0; li < c.num_layers; ++li) {
         Layer& L = m->layers[(size_t)li];
         // x_norm = norm1(x)  (model/block.rs:98)
-        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm1, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, m->xt, s));
+        //   (the row kernels write the int8 activations straight in the tensor-core product's layout)
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm1, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
         if (c.arch == 0) {
             // TTTLayer::forward_update (layers/ttt.rs:48-74)
-            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), m->xt, H, batch, m->qtc, m->sx, m->qsum, m->feat, m->d_small, EPI_F32, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->feat, m->d_small, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
             BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s));
-            BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), m->z, m->d_small, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), m->z, m->d_small, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes));
         } else {
             // BitAttention::forward (layers/attention.rs:149-225), seq_len 1
-            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), m->xt, H, batch, m->qtc, m->sx, m->qsum, m->qkv, m->qkv_dim, EPI_F32, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->qkv, m->qkv_dim, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
             AttnArgs a;
             a.qkv = m->qkv;
             a.cache = L.kv->view;
@@ -238,13 +242,13 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.pdl = false;
             a.dbg = nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
-            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes));
         }
         // x = x + mlp(norm2(x))  (model/block.rs:119-131, layers/swiglu.rs:29-35)
-        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, m->q, m->q_stride, m->sx, m->qsum, m->xt, s));
-        BT_CUDA_TRY(launch_gemm_tc(L.gate_up->dev(), m->xt, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s));
-        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, m->q, m->q_stride, m->sx, m->qsum, m->xt, s));
-        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), m->xt, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
+        BT_CUDA_TRY(launch_gemm_tc(L.gate_up->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_i));
+        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes, true));
     }
     // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
     if (m->lm_tiles) {
@@ -429,6 +433,8 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
     if (B > 8) {
         BT_CUDA_TRY(dev_alloc(&m->xt, (size_t)B * (H > I ? H : I)));
         BT_CUDA_TRY(dev_alloc(&m->qtc, gemm_tc_act_bytes(B, (kmax + kTileK - 1) / kTileK)));
+        m->tc_part_bytes = gemm_tc_part_bytes(m->sm_count);
+        BT_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&m->tc_part), m->tc_part_bytes));
         if (H % 64 == 0) {
             BT_CUDA_TRY(cudaMalloc(&m->lm_tiles, lm_head_tc_weight_bytes(c.vocab_size, H)));
             BT_CUDA_TRY(cudaMalloc(&m->lm_btiles, lm_head_tc_act_bytes(H)));
@@ -477,7 +483,7 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles, m->tc_part};
     for (void* p : bufs) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
@@ -596,7 +602,7 @@ extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, void* str
             if (batch > 8) {
                 // tensor-core product on whatever the transformed-row buffer holds (quantiser included)
                 BT_CUDA_TRY(launch_gemm_tc(lin->dev(), m->xt, lin->w.k_in, batch, m->qtc, m->sx, m->qsum, m->gu,
-                                           lin->w.n_out, EPI_F32, err, m->sm_count, s));
+                                           lin->w.n_out, EPI_F32, err, m->sm_count, s, m->tc_part, m->tc_part_bytes));
                 launches += 2;
             } else {
                 BT_CUDA_TRY(linear_product(lin->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, lin->w.n_out,
@@ -616,10 +622,14 @@ extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
         const int per_layer = 4 + 1 + (m->tp > 1 ? 2 : 0);  // 4 products + attention or TTT update (+ 2 scale epilogues after the all-reduces)
         return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
     }
-    // batches above 8: per layer 3 row kernels, 4 x (quantiser + tensor-core product), attention or
-    // TTT update; embedding, lm_head per 8 tokens, pick
-    const int per_layer = 3 + 8 + 1;
-    return m->cfg.num_layers * per_layer + 1 + (batch + 7) / 8 + 1;
+    // batches above 8: per layer 3 row kernels (norm1, norm2, SiLU*up, quantiser included), the quantiser of the
+    // attention / TTT output, 4 tensor-core products (+ a finishing kernel each where k is split), attention
+    // or TTT update; embedding, lm_head (tensor-core: prepare + product; else per 8 tokens), pick
+    const Layer& L = m->layers[0];
+    const bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up, L.gate_up, L.down};
+    int per_layer = 3 + 1 + 1;
+    for (const bt_linear* lin : seq) per_layer += gemm_tc_kernels(lin->dev(), batch, m->sm_count);
+    return m->cfg.num_layers * per_layer + 1 + (m->lm_tiles ? 2 + 2 : (batch + 7) / 8 + 1);
 }
 
 __global__ void set_pos_kernel(int32_t* pos, int n, int value) {

@@ -224,6 +224,43 @@ class BitLlama:
         p = self._L.bt_model_ttt_state(self._h, layer)
         return None if not p else _wrap_dev(p, (self.max_batch, d, d), torch.float32, self.device)
 
+    def save_memory(self, path: str) -> None:
+        """TTT fast-weight states to a safetensors file, tensors `layer_{i}` (Llama::save_memory,
+        model/llama.rs:575-591): `[d, d]` for a single-sequence model, `[batch, d, d]` otherwise."""
+        from .loader import write_safetensors
+        torch = _torch()
+        torch.cuda.synchronize(self.device)
+        tensors = {}
+        for li in range(self.cfg.num_layers):
+            st = self.ttt_state(li)
+            if st is None:
+                continue
+            a = st.cpu().numpy()
+            tensors[f"layer_{li}"] = a[0] if self.max_batch == 1 else a
+        write_safetensors(path, tensors)
+
+    def load_memory(self, path: str) -> None:
+        """Restores the states written by `save_memory`; layers missing from the file keep their
+        state (Llama::load_memory, model/llama.rs:593-611).  A `[d, d]` tensor goes to every
+        sequence of the batch."""
+        from .loader import CheckpointError, read_safetensors
+        torch = _torch()
+        tensors = read_safetensors(path)
+        d = self.cfg.hidden_dim // 4
+        torch.cuda.synchronize(self.device)
+        for li in range(self.cfg.num_layers):
+            st = self.ttt_state(li)
+            a = tensors.get(f"layer_{li}")
+            if st is None or a is None:
+                continue
+            a = np.ascontiguousarray(a, np.float32)
+            if a.shape == (d, d):
+                a = np.broadcast_to(a, (self.max_batch, d, d))
+            if a.shape != (self.max_batch, d, d):
+                raise CheckpointError(f"{path}: layer_{li} has shape {a.shape}, expected {(d, d)} or {(self.max_batch, d, d)}")
+            st.copy_(torch.from_numpy(np.ascontiguousarray(a)).to(st.device))
+        torch.cuda.synchronize(self.device)
+
     def kv_cache(self, layer: int):
         p = self._L.bt_model_kv_cache(self._h, layer)
         if not p:

@@ -136,3 +136,29 @@ def test_loaded_checkpoint_runs_like_direct_weights(mods, tmp_path):
         la, na = a.forward_one(np.array([tok], np.int32))
         lb, nb = b.forward_one(np.array([tok], np.int32))
         assert np.array_equal(la, lb) and np.array_equal(na, nb)
+
+
+@pytest.mark.gpu
+def test_ttt_memory_file_round_trip(mods, tmp_path):
+    """Llama::save_memory / load_memory (model/llama.rs:575-611): the TTT states survive a
+    trip through the file, and a model that loads them continues exactly like the original."""
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    loader, syn, _ = mods
+    cfg = syn.BitLlamaConfig("ttt", 500, 64, 2, 4, 4, 176, inner_lr=0.05)
+    w = syn.make_weights(cfg, seed=9)
+    a, b = syn.build_model(w), syn.build_model(w)
+    for tok in (1, 2, 3, 4, 5):
+        a.forward_one(np.array([tok], np.int32))
+    path = str(tmp_path / "memory.soul")
+    a.save_memory(path)
+    saved = loader.read_safetensors(path)
+    assert set(saved) == {"layer_0", "layer_1"} and saved["layer_0"].shape == (16, 16)
+    assert np.abs(saved["layer_0"]).max() > 0
+    b.load_memory(path)
+    for li in range(2):
+        assert np.array_equal(a.ttt_state(li).cpu().numpy(), b.ttt_state(li).cpu().numpy())
+    la, _ = a.forward_one(np.array([7], np.int32))
+    lb, _ = b.forward_one(np.array([7], np.int32))
+    assert np.array_equal(la, lb)
