@@ -72,11 +72,20 @@ struct AttnSmem {
     double m_run[kMaxRep], l_run[kMaxRep], corr[kMaxRep], m_next[kMaxRep];
     double wmax[kMaxRep][4], wsum[kMaxRep][4];  // per warp (32 rows) maxima and sums of the tile
     float knew[128], vnew[128];
-    alignas(16) uint8_t kraw[kTilePos * 128];  // the tile's cache rows as stored
-    alignas(16) uint8_t vraw[kTilePos * 128];
-    float ksr[kTilePos], vsr[kTilePos];
+    // cache rows as stored, two tiles: while one is worked on, the next arrives (cp.async)
+    alignas(16) uint8_t kraw[2][kTilePos * 128];
+    alignas(16) uint8_t vraw[2][kTilePos * 128];
+    alignas(16) float ksr[2][kTilePos], vsr[2][kTilePos];
     alignas(16) double red[512 * 2 * kMaxRep];  // [row group][head][dim] partial outputs; scratch of the merge
 };
+
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // (f32(byte) - 128) * s without an integer-to-float conversion: 0x4B0000bb is the float
 // 2^23 + b, and subtracting 2^23 + 128 is exact.
@@ -106,8 +115,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     {
         const uint4* ksrc = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + t0) * hd);
         const uint4* vsrc = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + t0) * hd);
-        uint4* kdst = reinterpret_cast<uint4*>(sm.kraw);
-        uint4* vdst = reinterpret_cast<uint4*>(sm.vraw);
+        uint4* kdst = reinterpret_cast<uint4*>(sm.kraw[0]);
+        uint4* vdst = reinterpret_cast<uint4*>(sm.vraw[0]);
         const int n16 = raw_rows * row16;
         for (int i0 = tid; i0 < n16; i0 += 2 * kAttnThreads) {
             const int i1 = i0 + kAttnThreads;
@@ -118,8 +127,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
             kdst[i0] = k0; vdst[i0] = v0;
             if (h1) { kdst[i1] = k1; vdst[i1] = v1; }
         }
-        if (tid < raw_rows) sm.ksr[tid] = a.cache.k_s[row_base + t0 + tid];
-        else if (tid >= 256 && tid - 256 < raw_rows) sm.vsr[tid - 256] = a.cache.v_s[row_base + t0 + tid - 256];
+        if (tid < raw_rows) sm.ksr[0][tid] = a.cache.k_s[row_base + t0 + tid];
+        else if (tid >= 256 && tid - 256 < raw_rows) sm.vsr[0][tid - 256] = a.cache.v_s[row_base + t0 + tid - 256];
     }
     ptx::pdl_wait();
     STAMP(1);
@@ -170,9 +179,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     if (owner) {
         const bool in_raw = p - t0 < raw_rows;
         if (warp == 0) quant_row_warp(sm.knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p,
-                                      in_raw ? sm.kraw + (p - t0) * hd : nullptr, in_raw ? sm.ksr + (p - t0) : nullptr, lane);
+                                      in_raw ? sm.kraw[0] + (p - t0) * hd : nullptr, in_raw ? sm.ksr[0] + (p - t0) : nullptr, lane);
         if (warp == 1) quant_row_warp(sm.vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p,
-                                      in_raw ? sm.vraw + (p - t0) * hd : nullptr, in_raw ? sm.vsr + (p - t0) : nullptr, lane);
+                                      in_raw ? sm.vraw[0] + (p - t0) * hd : nullptr, in_raw ? sm.vsr[0] + (p - t0) : nullptr, lane);
     }
     __syncthreads();  // the block's own global writes are visible to it after the barrier
     STAMP(2);
@@ -186,23 +195,28 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
     for (int h = 0; h < NREP; ++h) acc[h][0] = acc[h][1] = 0.0;
 
+    int cur = 0;  // buffer holding the current tile
     for (int tb = t0; tb < t1; tb += kTilePos) {
         const int n_here = min(kTilePos, t1 - tb);
-        if (tb > t0) {
-            // later tiles of a long span: copy the rows as stored (the first tile is already there)
-            __syncthreads();
-            const uint4* ksrc = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + tb) * hd);
-            const uint4* vsrc = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + tb) * hd);
-            for (int i = tid; i < n_here * row16; i += blockDim.x) {
-                reinterpret_cast<uint4*>(sm.kraw)[i] = ksrc[i];
-                reinterpret_cast<uint4*>(sm.vraw)[i] = vsrc[i];
+        if (tb + kTilePos < t1) {
+            // long span: start fetching the next tile's rows into the other buffer (its previous
+            // contents were last read before the barrier that ended the previous tile)
+            const int nb = tb + kTilePos, n_next = min(kTilePos, t1 - nb);
+            const uint8_t* ksrc = a.cache.k_q + (row_base + nb) * hd;
+            const uint8_t* vsrc = a.cache.v_q + (row_base + nb) * hd;
+            for (int i = tid; i < n_next * row16; i += blockDim.x) {
+                cp_async16(sm.kraw[cur ^ 1] + 16 * i, ksrc + 16 * i);
+                cp_async16(sm.vraw[cur ^ 1] + 16 * i, vsrc + 16 * i);
             }
-            for (int i = tid; i < n_here; i += blockDim.x) {
-                sm.ksr[i] = a.cache.k_s[row_base + tb + i];
-                sm.vsr[i] = a.cache.v_s[row_base + tb + i];
+            for (int i = tid; i < n_next; i += blockDim.x) {
+                cp_async4(&sm.ksr[cur ^ 1][i], a.cache.k_s + row_base + nb + i);
+                cp_async4(&sm.vsr[cur ^ 1][i], a.cache.v_s + row_base + nb + i);
             }
-            __syncthreads();
         }
+        const uint8_t* kraw = sm.kraw[cur];
+        const uint8_t* vraw = sm.vraw[cur];
+        const float* ksr = sm.ksr[cur];
+        const float* vsr = sm.vsr[cur];
         STAMP(3);
         // (1) scores.  One read of q serves four rows, one dequantised K element all heads; the
         //     lane's 4 * NREP partial sums are then added across the warp with a halving
@@ -220,8 +234,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
                 for (int rl = 0; rl < 4; ++rl) {
                     if (row0 + rl < n_here) {  // rows beyond the current length hold anything
-                        const uint32_t kb = *reinterpret_cast<const uint16_t*>(sm.kraw + (row0 + rl) * hd + c);
-                        const float ks = sm.ksr[row0 + rl];
+                        const uint32_t kb = *reinterpret_cast<const uint16_t*>(kraw + (row0 + rl) * hd + c);
+                        const float ks = ksr[row0 + rl];
                         const double k0 = dequant_wide(kb, 0, ks), k1 = dequant_wide(kb, 1, ks);
 #pragma unroll
                         for (int h = 0; h < NREP; ++h) {
@@ -304,8 +318,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
             for (int h = 0; h < NREP; ++h) { const double cr = sm.corr[h]; acc[h][0] *= cr; acc[h][1] *= cr; }
             for (int r = rg; r < n_here; r += n_rg) {
-                const uint32_t vb = *reinterpret_cast<const uint16_t*>(sm.vraw + r * hd + 2 * dp);
-                const float vs = sm.vsr[r];
+                const uint32_t vb = *reinterpret_cast<const uint16_t*>(vraw + r * hd + 2 * dp);
+                const float vs = vsr[r];
                 const double v0 = dequant_wide(vb, 0, vs), v1 = dequant_wide(vb, 1, vs);
 #pragma unroll
                 for (int h = 0; h < NREP; ++h) {
@@ -314,6 +328,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
                     acc[h][1] = fma(pr, v1, acc[h][1]);
                 }
             }
+        }
+        if (tb + kTilePos < t1) {
+            cp_async_wait_all();
+            __syncthreads();  // next tile complete and visible; this tile's buffers free again
+            cur ^= 1;
         }
     }
     // add the row groups (fixed order) through shared memory, one (head, dim) per thread

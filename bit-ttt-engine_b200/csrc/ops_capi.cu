@@ -23,9 +23,23 @@ cudaError_t upload_inv_freq(float* dev, int head_dim, double theta) {
 // Cuts the positions of a sequence into fixed spans so that batch * n_kv * splits CTAs
 // roughly fill the GPU: span is a multiple of 64 (one tile), at most 64 spans.
 void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* splits, int* span) {
-    int64_t want = ((int64_t)sm_count + batch * n_kv - 1) / (batch * n_kv);
+    // One CTA per (sequence, KV head, span).  Fewer pairs than SMs: cut the positions so that
+    // every SM gets a span.  More pairs than SMs: the CTAs run in waves of sm_count, and cutting
+    // the positions in 2..4 can fill the last wave better; cost model = waves x (tiles of 128
+    // positions per CTA + 1 for the fixed work of a CTA).
+    const int64_t pairs = batch * n_kv;
+    int64_t want = ((int64_t)sm_count + pairs - 1) / pairs;
     if (want > 64) want = 64;
     if (want < 1) want = 1;
+    if (pairs >= sm_count) {
+        int64_t best_cost = -1;
+        for (int64_t s = 1; s <= 4; ++s) {
+            const int64_t sp = ((max_seq + s - 1) / s + 63) / 64 * 64;
+            const int64_t waves = (pairs * s + sm_count - 1) / sm_count;
+            const int64_t cost = waves * ((sp + 127) / 128 + 1);
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; want = s; }
+        }
+    }
     int64_t sp = (max_seq + want - 1) / want;
     sp = (sp + 63) / 64 * 64;
     *span = (int)sp;
