@@ -253,12 +253,12 @@ class BitLlama:
             a = tensors.get(f"layer_{li}")
             if st is None or a is None:
                 continue
-            a = np.ascontiguousarray(a, np.float32)
+            a = np.array(a, dtype=np.float32)  # a writable copy (the file is memory-mapped read-only)
             if a.shape == (d, d):
                 a = np.broadcast_to(a, (self.max_batch, d, d))
             if a.shape != (self.max_batch, d, d):
                 raise CheckpointError(f"{path}: layer_{li} has shape {a.shape}, expected {(d, d)} or {(self.max_batch, d, d)}")
-            st.copy_(torch.from_numpy(np.ascontiguousarray(a)).to(st.device))
+            st.copy_(torch.from_numpy(np.array(a, dtype=np.float32)).to(st.device))
         torch.cuda.synchronize(self.device)
 
     def kv_cache(self, layer: int):
