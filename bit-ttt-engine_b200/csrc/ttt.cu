@@ -103,6 +103,138 @@ __global__ void __launch_bounds__(kTttWarps * 32) ttt_chunk_kernel(float* __rest
     }
 }
 
+// Small states (d = 32, 64 or 128): LPR = d / 16 lanes share a row of W, each holding 16
+// consecutive columns widened to f64 once per launch, so that the inner loops are plain f64
+// FMAs on registers (a float-to-double conversion costs several FMAs on this part, and the
+// per-row kernel above converts both operands of every product).  A row's dot product is
+// finished with log2(LPR) shuffles, which also leave z - x in every lane of the row for the
+// gradient.  A warp covers 32 / LPR rows; with d <= 64 a CTA of 8 warps covers a whole state,
+// so the chunk is normalised once per state.
+template <int LPR>
+__global__ void __launch_bounds__(kTttWarps * 32, 2) ttt_rows_kernel(float* __restrict__ w,
+                                                                    const float* __restrict__ feats,
+                                                                    int t_len, int d, float lr, int chunk,
+                                                                    float* __restrict__ z_out,
+                                                                    unsigned int* __restrict__ absmax_out) {
+    constexpr int kCols = 16;                 // columns per lane
+    constexpr int kRowsPerWarp = 32 / LPR;
+    // [chunk][d + 2 * LPR] normalised features of the current chunk, widened; every block of 16
+    // columns is shifted by 2 more doubles, so that the LPR lanes of a row, which read different
+    // blocks in the same instruction, hit different banks
+    extern __shared__ __align__(16) double xd[];
+    const int pitch = d + 2 * LPR;
+    ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
+    const int b = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a = (blockIdx.y * kTttWarps + warp) * kRowsPerWarp + lane / LPR;  // this lane's row of W
+    const int c0 = (lane % LPR) * kCols;                                        // and its first column
+    const bool active = a < d;
+    float* wrow = w + ((int64_t)b * d + (active ? a : 0)) * d + c0;
+    // the row is requested first and widened only after the first chunk has been staged, so that
+    // its DRAM latency overlaps the feature loads
+    float4 wf[kCols / 4];
+#pragma unroll
+    for (int i = 0; i < kCols / 4; ++i) wf[i] = active ? reinterpret_cast<const float4*>(wrow)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    double wr[kCols];
+    const float* fb = feats + (int64_t)b * t_len * d;
+    float* zb = z_out + (int64_t)b * t_len * d;
+    float run_max = 0.0f;
+    constexpr int kPerTok = 16;               // threads that share a token while staging
+    constexpr int kElems = LPR;               // d / 16 elements per such thread
+
+    for (int start = 0; start < t_len; start += chunk) {
+        const int len = min(chunk, t_len - start);
+        __syncthreads();  // previous chunk fully consumed
+        // stage the chunk: x / (sqrt(sum x^2) + 1e-6) (layers/ttt.rs:53-55), 16 threads per token,
+        // every feature read once
+        for (int tb = 0; tb < len; tb += (kTttWarps * 32) / kPerTok) {
+            const int t = tb + (int)(threadIdx.x / kPerTok), sub = threadIdx.x % kPerTok;
+            float f[kElems];
+            double ss = 0.0;
+#pragma unroll
+            for (int e = 0; e < kElems; ++e) f[e] = t < len ? fb[(int64_t)(start + t) * d + sub + kPerTok * e] : 0.0f;
+#pragma unroll
+            for (int e = 0; e < kElems; ++e) ss = fma((double)f[e], (double)f[e], ss);
+#pragma unroll
+            for (int o = kPerTok / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float nrm = __fadd_rn(sqrtf((float)ss), 1e-6f);
+#pragma unroll
+            for (int e = 0; e < kElems; ++e)
+                if (t < len) xd[t * pitch + sub + (kPerTok + 2) * e] = (double)__fdiv_rn(f[e], nrm);
+        }
+        if (start == 0) {
+#pragma unroll
+            for (int i = 0; i < kCols / 4; ++i) {
+                wr[4 * i] = (double)wf[i].x; wr[4 * i + 1] = (double)wf[i].y;
+                wr[4 * i + 2] = (double)wf[i].z; wr[4 * i + 3] = (double)wf[i].w;
+            }
+        }
+        __syncthreads();
+        double g[kCols];
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) g[i] = 0.0;
+        for (int t = 0; t < len; ++t) {
+            const double* xt = xd + t * pitch;
+            double x[kCols];
+#pragma unroll
+            for (int i = 0; i < kCols; i += 2) {
+                const double2 v = *reinterpret_cast<const double2*>(xt + c0 + 2 * (lane % LPR) + i);
+                x[i] = v.x;
+                x[i + 1] = v.y;
+            }
+            // prediction with the pre-update row: four partial sums, then the lanes of the row
+            double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+#pragma unroll
+            for (int i = 0; i < kCols; i += 4) {
+                s0 = fma(wr[i], x[i], s0);
+                s1 = fma(wr[i + 1], x[i + 1], s1);
+                s2 = fma(wr[i + 2], x[i + 2], s2);
+                s3 = fma(wr[i + 3], x[i + 3], s3);
+            }
+            double sd = (s0 + s1) + (s2 + s3);
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1) sd += __shfl_xor_sync(0xffffffffu, sd, o);
+            const float s = (float)sd;
+            const float xa = active ? (float)xt[a + 2 * (a / kCols)] : 0.0f;
+            if (active && (lane % LPR) == 0) {
+                zb[(int64_t)(start + t) * d + a] = s;
+                run_max = fmaxf(run_max, fabsf(s));
+            }
+            // rank-1 piece of the chunk gradient
+            const double df = (double)__fsub_rn(s, xa);
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) g[i] = fma(df, x[i], g[i]);
+        }
+        // W <- W - lr * G in f32 (layers/ttt.rs:68,111), widened again for the next chunk
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) wr[i] = (double)__fsub_rn((float)wr[i], __fmul_rn((float)g[i], lr));
+    }
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < kCols / 4; ++i)
+            reinterpret_cast<float4*>(wrow)[i] = make_float4((float)wr[4 * i], (float)wr[4 * i + 1], (float)wr[4 * i + 2], (float)wr[4 * i + 3]);
+    }
+    if (absmax_out) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) run_max = fmaxf(run_max, __shfl_xor_sync(0xffffffffu, run_max, o));
+        if (lane == 0 && run_max > 0.0f) atomicMax(absmax_out + b, __float_as_uint(run_max));
+    }
+}
+
+template <int LPR>
+cudaError_t launch_rows(float* w, const float* feats, int batch, int t_len, int d, float lr, int chunk,
+                        float* z_out, cudaStream_t stream, unsigned int* absmax_out, bool pdl) {
+    const size_t smem = (size_t)chunk * (d + 2 * LPR) * sizeof(double);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(ttt_rows_kernel<LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    const int rows_per_cta = kTttWarps * (32 / LPR);
+    dim3 grid(batch, (d + rows_per_cta - 1) / rows_per_cta);
+    return launch_pdl(ttt_rows_kernel<LPR>, grid, dim3(kTttWarps * 32), smem, stream, pdl, w, feats, t_len, d, lr, chunk, z_out, absmax_out);
+}
+
 template <int PL>
 cudaError_t launch_pl(float* w, const float* feats, int batch, int t_len, int d, float lr, int chunk,
                       float* z_out, cudaStream_t stream, unsigned int* absmax_out, bool pdl) {
@@ -123,6 +255,10 @@ cudaError_t launch_ttt_chunk(float* w, const float* feats, int batch, int t_len,
         return cudaErrorInvalidValue;
     if (batch <= 0 || t_len <= 0) return cudaSuccess;
     const int pl = (d + 31) / 32;
+    const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;  // the row kernels load 16 bytes at a time
+    if (aligned && d == 32) return launch_rows<2>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
+    if (aligned && d == 64) return launch_rows<4>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
+    if (aligned && d == 128) return launch_rows<8>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
     if (pl <= 1) return launch_pl<1>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
     if (pl <= 2) return launch_pl<2>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
     if (pl <= 4) return launch_pl<4>(w, feats, batch, t_len, d, lr, chunk, z_out, stream, absmax_out, pdl);
