@@ -177,7 +177,6 @@ def run_sweep(bt, device):
     peak, peak_kind = measured_peaks()
     L = bt.lib()
     rng = np.random.default_rng(0)
-    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     for (k, n) in [(4096, 4096), (4096, 14336), (14336, 4096), (4096, 128256)]:
         # distinct weight copies so that consecutive launches do not hit L2 (126 MB)
         copies = max(2, int(400e6 // (n * k / 4))) if n * k / 4 < 200e6 else 2
@@ -191,16 +190,24 @@ def run_sweep(bt, device):
             y = torch.empty(m, n, device="cuda")
 
             def run():
+                st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
                 for lin in lins:
                     bt.check(L.bt_linear_forward(lin._h, ws._h, C.c_void_p(x.data_ptr()), m, k, 0,
-                                                 C.c_void_p(y.data_ptr()), 0, stream))
-            run()
+                                                 C.c_void_p(y.data_ptr()), 0, st))
+            run()  # eager once: kernel attributes are set outside the capture
+            torch.cuda.synchronize()
+            # one pass over all copies as a CUDA graph, so that small points measure the device and
+            # not the host's launch rate
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run()
+            graph.replay()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             reps = 5 if m <= 64 else 2
             e0.record()
             for _ in range(reps):
-                run()
+                graph.replay()
             e1.record()
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
@@ -209,7 +216,7 @@ def run_sweep(bt, device):
                               "kernel": "gemv (mma.sync)" if m <= 8 else "gemm_tc (tcgen05)",
                               "GBps": byts / us / 1e3, "hbm_frac": byts / us / 1e3 / peak, "peak_kind": peak_kind,
                               "int8_TOPs": 2.0 * m * n * k / us / 1e6,
-                              "note": "quantiser kernel included; weights rotate through copies larger than L2"}),
+                              "note": "quantiser kernel included; graph-replayed; weights rotate through copies larger than L2"}),
                   flush=True)
         del lins
     # TTT fast-weight update: S independent 64x64 states, mini-batch 16
@@ -218,10 +225,15 @@ def run_sweep(bt, device):
         f = torch.randn(s_cnt, 16, 64, device="cuda")
         bt.ttt_update(w, f, 0.01, 16)
         torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            bt.ttt_update(w, f, 0.01, 16)
+        graph.replay()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(10):
-            bt.ttt_update(w, f, 0.01, 16)
+            graph.replay()
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / 10

@@ -52,31 +52,29 @@ constexpr unsigned kErrGemvTimeout = 0x47454d56u;  // 'GEMV'
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
-// One 1 KB tile: 2 A loads, 4 B loads, 32 ANDs, 8 MMAs.  Loads and arithmetic are separate
-// calls so that the caller can put a barrier probe between them; the four field positions are
-// four independent accumulator chains: their first MMAs are issued back to back, then the second.
-struct TileRegs {
-    uint4 w4, v4, b4[4];
-};
-__device__ __forceinline__ void tile_load(TileRegs& r, const uint8_t* tile, int lane, const uint8_t* acts_kt, bool has_token) {
-    r.w4 = lds128(tile + lane * 16);
-    r.v4 = lds128(tile + 512 + lane * 16);
+// One 1 KB tile: 2 A loads, 4 B loads, 32 ANDs, 8 MMAs.  The four field positions are four
+// independent accumulator chains: their first MMAs are issued back to back, then the second.
+// FIRST: the tile opens a row tile, its first MMAs start from the zero register (the
+// accumulators need no clearing between row tiles).  The loop is bound by instruction issue
+// (about one instruction per cycle and scheduler in steady state), so every instruction that
+// is not a load, an AND or an MMA is worth removing.
+template <bool FIRST>
+__device__ __forceinline__ void tile_mma(int (&acc)[4][4], const uint8_t* tile, int lane, const uint8_t* acts_kt) {
+    const uint4 w4 = lds128(tile + lane * 16);
+    const uint4 v4 = lds128(tile + 512 + lane * 16);
+    uint4 b4[4];
 #pragma unroll
-    for (int f = 0; f < 4; ++f) {
-        r.b4[f] = make_uint4(0u, 0u, 0u, 0u);
-        if (has_token) r.b4[f] = lds128(acts_kt + f * 64);
-    }
-}
-__device__ __forceinline__ void tile_compute(int (&acc)[4][4], const TileRegs& r) {
+    for (int f = 0; f < 4; ++f) b4[f] = lds128(acts_kt + f * 64);
 #pragma unroll
     for (int f = 0; f < 4; ++f) {
         const uint32_t mask = 0x03030303u << (2 * f);
-        ptx::mma_u8s8(acc[f], r.w4.x & mask, r.v4.x & mask, r.w4.z & mask, r.v4.z & mask, r.b4[f].x, r.b4[f].z);
+        if (FIRST) ptx::mma_u8s8_zero(acc[f], w4.x & mask, v4.x & mask, w4.z & mask, v4.z & mask, b4[f].x, b4[f].z);
+        else ptx::mma_u8s8(acc[f], w4.x & mask, v4.x & mask, w4.z & mask, v4.z & mask, b4[f].x, b4[f].z);
     }
 #pragma unroll
     for (int f = 0; f < 4; ++f) {
         const uint32_t mask = 0x03030303u << (2 * f);
-        ptx::mma_u8s8(acc[f], r.w4.y & mask, r.v4.y & mask, r.w4.w & mask, r.v4.w & mask, r.b4[f].y, r.b4[f].w);
+        ptx::mma_u8s8(acc[f], w4.y & mask, v4.y & mask, w4.w & mask, v4.w & mask, b4[f].y, b4[f].w);
     }
 }
 
@@ -288,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             bool first_round = true;
             int64_t rt = blockIdx.x;
             for (int it = 0; it < total_iters; ++it) {
-                if (!first_round && ok) ok = ptx::mbar_wait_bounded(&empty[slot], wait_parity);
+                if (!first_round && ok) ok = ptx::mbar_wait_relaxed(&empty[slot], wait_parity);
                 const int kt0 = sk * kStageTiles;
                 const int nt = k_tiles - kt0 < kStageTiles ? k_tiles - kt0 : kStageTiles;
                 const uint32_t bytes = (uint32_t)nt * kTileBytes;
@@ -328,7 +326,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
         for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
             float sw[2] = {0.f, 0.f};
             if (a.epilogue != EPI_I32) { sw[0] = a.sw_tiles[2 * rt]; sw[1] = a.sw_tiles[2 * rt + 1]; }
-            if (ok) ok = ptx::mbar_wait_bounded(&red_full[rb], parity);
+            if (ok) ok = ptx::mbar_wait_relaxed(&red_full[rb], parity);
             const int* buf = red + rb * kRedBufInts;
             int sum[4] = {0, 0, 0, 0};
 #pragma unroll
@@ -403,57 +401,43 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // activation image complete, epilogue warps may read the scales
     if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 2] = ptx::globaltimer();
 
-    int acc[4][4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[r][j] = 0;
-
-    const uint8_t* my_acts = acts + (size_t)g * act_stride + t * 16;
-    const bool has_token = g < a.m;
+    int acc[4][4];  // written by the first tile of every row tile
+    // lanes whose MMA column has no token read the last token's row instead: their columns are
+    // never stored, and the loads need no predicate
+    const uint8_t* my_acts = acts + (size_t)(g < a.m ? g : a.m - 1) * act_stride + t * 16;
     bool ok = true;
     int slot = 0, sk = 0, rb = 0;
     uint32_t parity = 0, red_parity = 1;
     bool red_first = true;
 
-    // Shared-memory round trips (barrier tests included) cost on the order of a hundred cycles
-    // each, so the loop keeps them off the critical path: while a tile's loads are in flight it
-    // already probes, without blocking, the barriers the warp will need next (the next stage's
-    // "full", the reduction buffer's "empty"), and only falls back to a blocking wait when a
-    // probe came back negative.
-    bool stage_ready = false;  // a probe has already seen full[slot] complete
     for (int it = 0; it < total_iters; ++it) {
-        if (!stage_ready && ok) ok = ptx::mbar_wait_bounded(&full[slot], parity);
-        const uint8_t* stage = ring + (size_t)slot * kStageBytes;
+        if (ok) ok = ptx::mbar_wait_bounded(&full[slot], parity);
+        const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes;
         const int kt = sk * kStageTiles + warp;  // one 1 KB tile per math warp and stage
-        const bool last_of_rt = sk + 1 == stages_per_rt;
-        TileRegs regs;
-        if (kt < k_tiles) tile_load(regs, stage + warp * kTileBytes, lane, my_acts + kt * kTileK, has_token);
-        const int cur_slot = slot;
-        if (++slot == nstages) { slot = 0; parity ^= 1; }
-        bool red_free;
-        ptx::mbar_test_wait2(&full[slot], parity, &red_empty[rb], red_parity, stage_ready, red_free);
-        stage_ready = stage_ready && it + 1 < total_iters;  // (the parity test is meaningless past the last use)
-        red_free = red_free || red_first;
-        if (kt < k_tiles) tile_compute(acc, regs);
+        if (kt < k_tiles) {
+            if (sk == 0) tile_mma<true>(acc, tile, lane, my_acts + kt * kTileK);
+            else tile_mma<false>(acc, tile, lane, my_acts + kt * kTileK);
+        } else if (sk == 0) {  // fewer tiles than math warps: this warp contributes zeros
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[r][j] = 0;
+        }
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&empty[cur_slot]);
+        if (lane == 0) ptx::mbar_arrive(&empty[slot]);
+        if (++slot == nstages) { slot = 0; parity ^= 1; }
 
-        if (last_of_rt) {
+        if (++sk == stages_per_rt) {
             sk = 0;
             // row tile complete: fold the four field positions and hand the partials over
-            if (!red_free && ok) ok = ptx::mbar_wait_bounded(&red_empty[rb], red_parity);
+            if (!red_first && ok) ok = ptx::mbar_wait_bounded(&red_empty[rb], red_parity);
             int* my_red = red + rb * kRedBufInts + warp * 128;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 4; ++j)
                 my_red[j * 32 + lane] = acc[0][j] + (acc[1][j] >> 2) + (acc[2][j] >> 4) + (acc[3][j] >> 6);
-                acc[0][j] = acc[1][j] = acc[2][j] = acc[3][j] = 0;
-            }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&red_full[rb]);
             if (++rb == kRedBufs) { rb = 0; red_first = false; red_parity ^= 1; }
-        } else {
-            ++sk;
         }
     }
     if (!ok) {
