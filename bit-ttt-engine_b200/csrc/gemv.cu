@@ -323,6 +323,59 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
         uint32_t parity = 0;
         float run_max[2] = {0.f, 0.f};  // EPI_SWIGLU: running max|out| of this lane's two tokens
         int64_t rt = blockIdx.x + (int64_t)epi * gridDim.x;
+        if (a.m == 1) {
+            // Single token: the math warps leave 16 sums each (one per row of the tile), the lane
+            // pair (r, r + 16) adds 8 warps each.  Lane r < 16 then owns row r of the tile.
+            const int r = lane & 15, half_w = lane >> 4;
+            const int qs0 = tok_qsum[0];
+            const float sx0 = tok_sx[0];
+            float amax1 = 0.f;
+            for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
+                float sw = 0.f;
+                if (a.epilogue != EPI_I32) sw = a.sw_tiles[2 * rt + (r >> 3)];
+                if (ok) ok = ptx::mbar_wait_relaxed(&red_full[rb], parity);
+                const int* buf = red + rb * kRedBufInts + half_w * (kMathWarps / 2) * 16 + r;
+                int sum = 0;
+#pragma unroll
+                for (int w = 0; w < kMathWarps / 2; ++w) sum += buf[w * 16];
+                sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&red_empty[rb]);
+                const int accv = sum - qs0;
+                const int64_t row = rt * kTileRows + r;
+                if (a.epilogue == EPI_I32) {
+                    if (lane < 16 && row < a.n_out) reinterpret_cast<int32_t*>(a.out)[row] = accv;
+                } else {
+                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), sx0);
+                    if (a.epilogue == EPI_SWIGLU) {
+                        // rows 0-7 of the tile are gate rows, rows 8-15 the matching up rows
+                        const float uv = __shfl_down_sync(0xffffffffu, y, 8);
+                        const int64_t col = rt * 8 + r;
+                        if (lane < 8 && col < a.n_out / 2) {
+                            // silu(g) * u, exp in f64 rounded once (layers/swiglu.rs:31-33)
+                            const float act = __fmul_rn(__fdiv_rn(y, __fadd_rn(1.0f, (float)exp(-(double)y))), uv);
+                            reinterpret_cast<float*>(a.out)[col] = act;
+                            amax1 = fmaxf(amax1, fabsf(act));
+                        }
+                    } else if (lane < 16 && row < a.n_out) {
+                        if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[row] = y;
+                        else if (a.epilogue == EPI_F32_ACCUM)
+                            reinterpret_cast<float*>(a.out)[row] = __fadd_rn(reinterpret_cast<float*>(a.out)[row], y);
+                        else reinterpret_cast<__nv_bfloat16*>(a.out)[row] = __float2bfloat16_rn(y);
+                    }
+                }
+                parity ^= 1;
+                rt += (int64_t)kEpiWarps * gridDim.x;
+            }
+            if (a.epilogue == EPI_SWIGLU) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax1 = fmaxf(amax1, __shfl_xor_sync(0xffffffffu, amax1, o));
+                if (lane == 0) atomicMax(a.absmax_out, __float_as_uint(amax1));
+            }
+            if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
+            if (a.dbg && lane == 0 && epi == 0) a.dbg[blockIdx.x * 4 + 3] = ptx::globaltimer();
+            return;
+        }
         for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
             float sw[2] = {0.f, 0.f};
             if (a.epilogue != EPI_I32) { sw[0] = a.sw_tiles[2 * rt]; sw[1] = a.sw_tiles[2 * rt + 1]; }
@@ -405,6 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     // lanes whose MMA column has no token read the last token's row instead: their columns are
     // never stored, and the loads need no predicate
     const uint8_t* my_acts = acts + (size_t)(g < a.m ? g : a.m - 1) * act_stride + t * 16;
+    const bool single = a.m == 1;
     bool ok = true;
     int slot = 0, sk = 0, rb = 0;
     uint32_t parity = 0, red_parity = 1;
@@ -431,10 +485,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             sk = 0;
             // row tile complete: fold the four field positions and hand the partials over
             if (!red_first && ok) ok = ptx::mbar_wait_bounded(&red_empty[rb], red_parity);
-            int* my_red = red + rb * kRedBufInts + warp * 128;
+            if (single) {
+                // one token: only column 0 of the MMA tile is live (lanes with t = 0: rows g and g + 8)
+                int* my_red = red + rb * kRedBufInts + warp * 16;
+                const int lo = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
+                const int hi = acc[0][2] + (acc[1][2] >> 2) + (acc[2][2] >> 4) + (acc[3][2] >> 6);
+                if (t == 0) { my_red[g] = lo; my_red[g + 8] = hi; }
+            } else {
+                int* my_red = red + rb * kRedBufInts + warp * 128;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                my_red[j * 32 + lane] = acc[0][j] + (acc[1][j] >> 2) + (acc[2][j] >> 4) + (acc[3][j] >> 6);
+                for (int j = 0; j < 4; ++j)
+                    my_red[j * 32 + lane] = acc[0][j] + (acc[1][j] >> 2) + (acc[2][j] >> 4) + (acc[3][j] >> 6);
+            }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&red_full[rb]);
             if (++rb == kRedBufs) { rb = 0; red_first = false; red_parity ^= 1; }
