@@ -59,12 +59,9 @@ __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cas
 // (about one instruction per cycle and scheduler in steady state), so every instruction that
 // is not a load, an AND or an MMA is worth removing.
 template <bool FIRST>
-__device__ __forceinline__ void tile_mma(int (&acc)[4][4], const uint8_t* tile, int lane, const uint8_t* acts_kt) {
+__device__ __forceinline__ void tile_mma_b(int (&acc)[4][4], const uint8_t* tile, int lane, const uint4 (&b4)[4]) {
     const uint4 w4 = lds128(tile + lane * 16);
     const uint4 v4 = lds128(tile + 512 + lane * 16);
-    uint4 b4[4];
-#pragma unroll
-    for (int f = 0; f < 4; ++f) b4[f] = lds128(acts_kt + f * 64);
 #pragma unroll
     for (int f = 0; f < 4; ++f) {
         const uint32_t mask = 0x03030303u << (2 * f);
@@ -76,6 +73,13 @@ __device__ __forceinline__ void tile_mma(int (&acc)[4][4], const uint8_t* tile, 
         const uint32_t mask = 0x03030303u << (2 * f);
         ptx::mma_u8s8(acc[f], w4.y & mask, v4.y & mask, w4.w & mask, v4.w & mask, b4[f].y, b4[f].w);
     }
+}
+template <bool FIRST>
+__device__ __forceinline__ void tile_mma(int (&acc)[4][4], const uint8_t* tile, int lane, const uint8_t* acts_kt) {
+    uint4 b4[4];
+#pragma unroll
+    for (int f = 0; f < 4; ++f) b4[f] = lds128(acts_kt + f * 64);
+    tile_mma_b<FIRST>(acc, tile, lane, b4);
 }
 
 // ---- reductions over the 256 math threads (named barrier 1) ----------------------------
@@ -464,42 +468,71 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     uint32_t parity = 0, red_parity = 1;
     bool red_first = true;
 
-    for (int it = 0; it < total_iters; ++it) {
-        if (ok) ok = ptx::mbar_wait_bounded(&full[slot], parity);
-        const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes;
-        const int kt = sk * kStageTiles + warp;  // one 1 KB tile per math warp and stage
-        if (kt < k_tiles) {
-            if (sk == 0) tile_mma<true>(acc, tile, lane, my_acts + kt * kTileK);
-            else tile_mma<false>(acc, tile, lane, my_acts + kt * kTileK);
-        } else if (sk == 0) {  // fewer tiles than math warps: this warp contributes zeros
+    // row tile complete: fold the four field positions and hand the partial sums to an epilogue warp
+    auto hand_over = [&]() {
+        if (!red_first && ok) ok = ptx::mbar_wait_bounded(&red_empty[rb], red_parity);
+        if (single) {
+            // one token: only column 0 of the MMA tile is live (lanes with t = 0: rows g and g + 8)
+            int* my_red = red + rb * kRedBufInts + warp * 16;
+            const int lo = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
+            const int hi = acc[0][2] + (acc[1][2] >> 2) + (acc[2][2] >> 4) + (acc[3][2] >> 6);
+            if (t == 0) { my_red[g] = lo; my_red[g + 8] = hi; }
+        } else {
+            int* my_red = red + rb * kRedBufInts + warp * 128;
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[r][j] = 0;
+            for (int j = 0; j < 4; ++j)
+                my_red[j * 32 + lane] = acc[0][j] + (acc[1][j] >> 2) + (acc[2][j] >> 4) + (acc[3][j] >> 6);
         }
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&empty[slot]);
-        if (++slot == nstages) { slot = 0; parity ^= 1; }
+        if (lane == 0) ptx::mbar_arrive(&red_full[rb]);
+        if (++rb == kRedBufs) { rb = 0; red_first = false; red_parity ^= 1; }
+    };
 
-        if (++sk == stages_per_rt) {
-            sk = 0;
-            // row tile complete: fold the four field positions and hand the partials over
-            if (!red_first && ok) ok = ptx::mbar_wait_bounded(&red_empty[rb], red_parity);
-            if (single) {
-                // one token: only column 0 of the MMA tile is live (lanes with t = 0: rows g and g + 8)
-                int* my_red = red + rb * kRedBufInts + warp * 16;
-                const int lo = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
-                const int hi = acc[0][2] + (acc[1][2] >> 2) + (acc[2][2] >> 4) + (acc[3][2] >> 6);
-                if (t == 0) { my_red[g] = lo; my_red[g + 8] = hi; }
-            } else {
-                int* my_red = red + rb * kRedBufInts + warp * 128;
+    if (stages_per_rt == 1) {
+        // K <= 4096: this warp multiplies the same 256 inputs in every row tile, so its
+        // activation registers are loaded once (the activation loads are two thirds of the
+        // loop's shared-memory traffic otherwise) and every tile is a whole row tile
+        const bool have = warp < k_tiles;
+        uint4 b4[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    my_red[j * 32 + lane] = acc[0][j] + (acc[1][j] >> 2) + (acc[2][j] >> 4) + (acc[3][j] >> 6);
+        for (int f = 0; f < 4; ++f) b4[f] = have ? lds128(my_acts + warp * kTileK + f * 64) : make_uint4(0u, 0u, 0u, 0u);
+        for (int it = 0; it < total_iters; ++it) {
+            if (ok) ok = ptx::mbar_wait_bounded(&full[slot], parity);
+            const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes;
+            if (have) {
+                tile_mma_b<true>(acc, tile, lane, b4);
+            } else {
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[r][j] = 0;
             }
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&red_full[rb]);
-            if (++rb == kRedBufs) { rb = 0; red_first = false; red_parity ^= 1; }
+            if (lane == 0) ptx::mbar_arrive(&empty[slot]);
+            if (++slot == nstages) { slot = 0; parity ^= 1; }
+            hand_over();
+        }
+    } else {
+        for (int it = 0; it < total_iters; ++it) {
+            if (ok) ok = ptx::mbar_wait_bounded(&full[slot], parity);
+            const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes;
+            const int kt = sk * kStageTiles + warp;  // one 1 KB tile per math warp and stage
+            if (kt < k_tiles) {
+                if (sk == 0) tile_mma<true>(acc, tile, lane, my_acts + kt * kTileK);
+                else tile_mma<false>(acc, tile, lane, my_acts + kt * kTileK);
+            } else if (sk == 0) {  // fewer tiles than math warps: this warp contributes zeros
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[r][j] = 0;
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty[slot]);
+            if (++slot == nstages) { slot = 0; parity ^= 1; }
+            if (++sk == stages_per_rt) {
+                sk = 0;
+                hand_over();
+            }
         }
     }
     if (!ok) {
