@@ -288,6 +288,9 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="BitLinear shape sweep (K,N in {4096x4096, 4096x14336, 14336x4096, 4096x128256}, "
                          "M in {1, 8, 64, 512, 4096}) plus the TTT update: one JSON line per point")
+    ap.add_argument("--tp-nccl", action="store_true",
+                    help="with --gpus N > 1: keep the tensor-parallel exchanges on NCCL instead of the "
+                         "library's peer-memory kernels")
     ap.add_argument("--seek", action="store_true",
                     help="profiling aid: skip the token-by-token prefill and declare the (zero-filled) "
                          "cache to hold --context positions")
@@ -326,6 +329,25 @@ def main():
         uid = [bt.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         model.tp_init(uid[0])
+        if not args.tp_nccl:
+            # the row-parallel exchanges as kernels over NVLink peer memory instead of NCCL calls
+            # (every rank has to succeed, otherwise all of them stay on NCCL)
+            ok = 1
+            try:
+                handles = [None] * world
+                dist.all_gather_object(handles, model.tp_peer_handle())
+                model.tp_peer_init(handles)
+            except Exception as exc:  # noqa: BLE001
+                print(f"rank {rank}: peer-memory exchange unavailable ({exc}); using NCCL", file=sys.stderr)
+                ok = 0
+            flag = torch.tensor([ok], device=f"cuda:{local_rank}")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                args.tp_nccl = True
+                try:
+                    model.tp_peer_disable()
+                except Exception:  # noqa: BLE001
+                    pass
     dev = torch.device(f"cuda:{local_rank}")
     rng = np.random.default_rng(11)  # every rank feeds the same ids
 
@@ -434,7 +456,7 @@ def main():
             "vs_baseline": None,
             "dtype": "int8 x ternary -> int32 (f32 epilogue, bf16 lm_head)", "data": "synthetic",
             "config": {"workload": f"Llama-3-8B-shaped ternary decode, batch {B}, context {args.context}+",
-                       "batch": B, "context": args.context, "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                       "batch": B, "context": args.context, "parallelism": (f"tp{world} ({'NCCL' if args.tp_nccl else 'peer-memory'} exchange)") if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: 1.74 GB of ternary tiles + 1.05 GB lm_head per step"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
             "gpu_launches": model.launches_per_step(B) * K,

@@ -58,4 +58,13 @@ bt_status tp_allreduce_max_f32(void* comm, float* buf, size_t count, cudaStream_
 bt_status tp_allreduce_sum_i32(void* comm, int32_t* buf, size_t count, cudaStream_t s);
 cudaError_t launch_tp_residual(const int32_t* acc, const unsigned int* absmax, float sw, int m, int n, float* h,
                                cudaStream_t s, bool pdl);
+// exchange over NVLink peer memory (CUDA IPC between the ranks' processes) instead of NCCL
+bt_status tp_peer_create(void** out, int rank, int size, int max_batch, int hidden, unsigned int* err);
+bt_status tp_peer_export(void* peer, void* handle64_out);
+bt_status tp_peer_import(void* peer, const void* handles /* [size][64] */);
+bool tp_peer_ready(const void* peer);
+void tp_peer_destroy(void* peer);
+cudaError_t launch_tp_peer_max(void* peer, int slot, unsigned int* amax_cell, int batch, cudaStream_t s);
+cudaError_t launch_tp_peer_sum_residual(void* peer, int slot, const int32_t* acc, const unsigned int* amax_cell, float sw,
+                                        int batch, int n, float* h, cudaStream_t s);
 }  // namespace bt

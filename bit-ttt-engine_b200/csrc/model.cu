@@ -62,6 +62,7 @@ struct bt_model {
     int tp = 1;                      // tensor-parallel degree
     int nh_l = 0, nkv_l = 0, i_l = 0;  // this rank's query heads, KV heads, MLP columns
     void* comm = nullptr;            // NCCL communicator when tp > 1
+    void* peer = nullptr;            // peer-memory exchange (CUDA IPC inboxes) when the ranks have set it up
     int32_t* acc_i32 = nullptr;      // [max_batch, hidden] accumulators of a row-parallel projection
     bool finalized = false;
     std::vector<Layer> layers;
@@ -172,7 +173,13 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.dbg = g_dbg_base ? g_dbg_base + (size_t)(g_dbg_slot++) * 4 * 512 : nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
             FusedIn ain{PRO_ABSMAX, m->att, att_dim, nullptr, 0.f, amax_core};
-            if (m->tp > 1) {
+            if (m->tp > 1 && tp_peer_ready(m->peer)) {
+                // row-parallel over NVLink peer memory: max of the quantisation scale, then the integer
+                // sum fused with the scale epilogue and the residual
+                BT_CUDA_TRY(launch_tp_peer_max(m->peer, 0, amax_core, batch, s));
+                BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
+                BT_CUDA_TRY(launch_tp_peer_sum_residual(m->peer, 0, m->acc_i32, amax_core, L.o->scales[0], batch, H, m->h, s));
+            } else if (m->tp > 1) {
                 // row-parallel: same quantisation scale on every rank, integer sum over the ranks
                 bt_status st = tp_allreduce_max_f32(m->comm, reinterpret_cast<float*>(amax_core), (size_t)batch, s);
                 if (st != BT_OK) return st;
@@ -186,7 +193,11 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
         FusedIn norm2{PRO_RMSNORM, m->h, H, L.norm2, kRmsEps, nullptr};
         BT_CUDA_TRY(linear_product_fused(L.gate_up_il->dev(), norm2, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, sm, s));
         FusedIn din{PRO_ABSMAX, m->act, I, nullptr, 0.f, amax_mlp};
-        if (m->tp > 1) {
+        if (m->tp > 1 && tp_peer_ready(m->peer)) {
+            BT_CUDA_TRY(launch_tp_peer_max(m->peer, 1, amax_mlp, batch, s));
+            BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
+            BT_CUDA_TRY(launch_tp_peer_sum_residual(m->peer, 1, m->acc_i32, amax_mlp, L.down->scales[0], batch, H, m->h, s));
+        } else if (m->tp > 1) {
             bt_status st = tp_allreduce_max_f32(m->comm, reinterpret_cast<float*>(amax_mlp), (size_t)batch, s);
             if (st != BT_OK) return st;
             BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
@@ -489,6 +500,7 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
     if (m->stream) cudaStreamDestroy(m->stream);
     if (m->comm) tp_comm_destroy(m->comm);
+    if (m->peer) tp_peer_destroy(m->peer);
     delete m;
     return BT_OK;
 }
@@ -509,7 +521,8 @@ extern "C" bt_status bt_model_reset(bt_model* m) {
 namespace {
 
 bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
-    if (m->tp > 1 && !m->comm) return set_error(BT_ERR_NCCL, "tensor-parallel model used before bt_model_tp_init");
+    if (m->tp > 1 && !m->comm && !tp_peer_ready(m->peer))
+        return set_error(BT_ERR_NCCL, "tensor-parallel model used before bt_model_tp_init / bt_model_tp_peer_import");
     if (m->cfg.arch == 1 && m->host_pos >= m->cfg.max_position_embeddings)
         return set_error(BT_ERR_SHAPE, "position %d reaches max_position_embeddings %d", m->host_pos, m->cfg.max_position_embeddings);
     // first call at a batch size runs eagerly (it also sets kernel attributes); the second
@@ -655,6 +668,40 @@ extern "C" void bt_debug_timeline(unsigned long long* buf) { bt::g_dbg_base = bu
 extern "C" bt_status bt_tp_unique_id(uint8_t* id128_out) {
     if (!id128_out) return set_error(BT_ERR_ARG, "bt_tp_unique_id: null pointer");
     return tp_unique_id(id128_out);
+}
+
+extern "C" bt_status bt_model_tp_peer_export(bt_model* m, uint8_t* handle64_out) {
+    if (!m || !m->finalized || !handle64_out) return set_error(BT_ERR_ARG, "bt_model_tp_peer_export: null pointer or model not finalized");
+    if (m->tp <= 1) return set_error(BT_ERR_ARG, "bt_model_tp_peer_export: the model is not tensor-parallel");
+    DeviceGuard guard(m->device);
+    if (!m->peer) {
+        bt_status st = tp_peer_create(&m->peer, m->cfg.tp_rank, m->tp, m->cfg.max_batch, m->cfg.hidden_dim, device_error_word(m->device));
+        if (st != BT_OK) return st;
+    }
+    return tp_peer_export(m->peer, handle64_out);
+}
+
+extern "C" bt_status bt_model_tp_peer_import(bt_model* m, const uint8_t* handles) {
+    if (!m || !m->finalized || !m->peer)
+        return set_error(BT_ERR_ARG, "bt_model_tp_peer_import: null pointer, model not finalized or bt_model_tp_peer_export not called");
+    DeviceGuard guard(m->device);
+    if (!handles) {  // back to NCCL (e.g. another rank could not map the inboxes)
+        BT_CUDA_TRY(cudaDeviceSynchronize());
+        for (auto& g : m->graphs) {
+            if (g && g != reinterpret_cast<cudaGraphExec_t>(uintptr_t(1))) cudaGraphExecDestroy(g);
+            g = nullptr;
+        }
+        tp_peer_destroy(m->peer);
+        m->peer = nullptr;
+        return BT_OK;
+    }
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    // graphs captured with the NCCL path must not be replayed after the switch
+    for (auto& g : m->graphs) {
+        if (g && g != reinterpret_cast<cudaGraphExec_t>(uintptr_t(1))) cudaGraphExecDestroy(g);
+        g = nullptr;
+    }
+    return tp_peer_import(m->peer, handles);
 }
 
 extern "C" bt_status bt_model_tp_init(bt_model* m, const uint8_t* id128) {

@@ -9,9 +9,21 @@
 // The collectives go through NCCL, looked up at run time in the process (the library has no
 // link-time dependency on it): ncclAllReduce is stream-ordered and can be captured into
 // the decode step's CUDA graph.
+//
+// Decode moves a few KB per exchange, so two NCCL calls per projection cost far more than the
+// data: when the ranks have exchanged CUDA IPC handles of their inboxes (tp_peer_*), the two
+// all-reduces run as two small kernels of this library over NVLink peer memory instead.  Every
+// rank PUSHES its values into each peer's inbox (plain stores to peer memory), publishes a
+// per-source epoch flag with release semantics at system scope, waits - with a bound - for the
+// flags of all sources in its own inbox, and reduces locally; the integer sum is fused with
+// the scale epilogue and the residual add.  Two inbox slots alternate (o_proj / down_proj), so
+// a rank that runs ahead never overwrites values a slower rank has not read yet: it cannot
+// reach the same slot again without the slower rank's contribution to the exchanges between.
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>
+
+#include <new>
 
 #include "bt_handles.cuh"
 #include "bt_ptx.cuh"
@@ -62,6 +74,129 @@ __global__ void tp_residual_kernel(const int32_t* __restrict__ acc, const unsign
     }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// peer-memory exchange
+// ---------------------------------------------------------------------------------------
+constexpr int kTpMaxRanks = 8;
+constexpr unsigned kErrTpTimeout = 0x54505754u;  // 'TPWT'
+
+// Inbox layout (identical on every rank): for slot s in {0, 1} and source rank r
+//   acc  [s][r][max_batch * hidden] int32
+//   amax [s][r][max_batch] u32 (rows padded to 16 entries)
+//   flag [s][kind][r] u64 epochs (kind 0: amax published, kind 1: acc published)
+struct TpLayout {
+    int size, max_batch, hidden;
+    __host__ __device__ size_t acc_elems() const { return (size_t)max_batch * hidden; }
+    __host__ __device__ size_t acc_off(int s, int r) const { return ((size_t)(s * size + r) * acc_elems()) * 4; }
+    __host__ __device__ size_t amax_base() const { return (size_t)2 * size * acc_elems() * 4; }
+    __host__ __device__ size_t amax_off(int s, int r) const { return amax_base() + (size_t)(s * size + r) * 16 * 4; }
+    __host__ __device__ size_t flag_base() const { return amax_base() + (size_t)2 * size * 16 * 4; }
+    __host__ __device__ size_t flag_off(int s, int kind, int r) const { return flag_base() + (size_t)((s * 2 + kind) * size + r) * 8; }
+    __host__ __device__ size_t bytes() const { return flag_base() + (size_t)2 * 2 * size * 8; }
+};
+
+struct TpView {
+    TpLayout lay;
+    int rank;
+    uint8_t* inbox[kTpMaxRanks];       // every rank's inbox as mapped into this process (own included)
+    unsigned long long* epoch;         // local, [2 slots]: exchanges done on the slot
+    unsigned int* done;                // local, [2 slots]: CTAs of the running sum kernel that have pushed
+    unsigned int* err;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// waits until every source rank has published epoch e on (slot, kind) of this rank's inbox
+__device__ __forceinline__ bool wait_sources(const TpView& v, int slot, int kind, unsigned long long e, int src) {
+    const unsigned long long* f = reinterpret_cast<const unsigned long long*>(v.inbox[v.rank] + v.lay.flag_off(slot, kind, src));
+    for (unsigned i = 0; i < (1u << 21); ++i)
+        if (ld_acquire_sys(f) >= e) return true;
+    return false;
+}
+
+// all-reduce(max) of the per-token max|x| cells: one CTA
+__global__ void __launch_bounds__(256) tp_max_exchange_kernel(TpView v, int slot, unsigned int* amax_cell, int batch) {
+    __shared__ int ok_s;
+    const int tid = threadIdx.x, R = v.lay.size;
+    const unsigned long long e = v.epoch[slot] + 1;
+    if (tid == 0) ok_s = 1;
+    for (int i = tid; i < batch * R; i += blockDim.x) {
+        const int p = i / batch, tok = i % batch;
+        reinterpret_cast<unsigned int*>(v.inbox[p] + v.lay.amax_off(slot, v.rank))[tok] = amax_cell[tok];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < R) {
+        st_release_sys(reinterpret_cast<unsigned long long*>(v.inbox[tid] + v.lay.flag_off(slot, 0, v.rank)), e);
+        if (!wait_sources(v, slot, 0, e, tid)) ok_s = 0;
+    }
+    __syncthreads();
+    if (tid < batch) {
+        unsigned int mx = 0;  // bit patterns of non-negative floats order like the floats
+        for (int r = 0; r < R; ++r)
+            mx = max(mx, __ldcg(reinterpret_cast<const unsigned int*>(v.inbox[v.rank] + v.lay.amax_off(slot, r)) + tid));
+        amax_cell[tid] = mx;
+    }
+    if (tid == 0) {
+        v.epoch[slot] = e;  // the sum kernel that follows on this slot uses the same epoch
+        if (!ok_s) atomicExch(v.err, kErrTpTimeout);
+    }
+}
+
+// all-reduce(sum) of the int32 accumulators fused with the scale epilogue and the residual:
+// h[m, n] += ((float)sum_r acc_r[m, n] * sw) * (absmax[m] / 127)
+__global__ void __launch_bounds__(256) tp_sum_residual_kernel(TpView v, int slot, const int32_t* __restrict__ acc,
+                                                              const unsigned int* __restrict__ amax_cell, float sw,
+                                                              int batch, int n, float* __restrict__ h) {
+    __shared__ int ok_s;
+    __shared__ unsigned int last_s;
+    const int tid = threadIdx.x, R = v.lay.size;
+    const unsigned long long e = v.epoch[slot];  // set by the max exchange just before
+    const int total4 = batch * n / 4;            // n is a multiple of 16
+    const int per_cta = (total4 + gridDim.x - 1) / gridDim.x;
+    const int i0 = blockIdx.x * per_cta, i1 = min(total4, i0 + per_cta);
+    if (tid == 0) ok_s = 1;
+    for (int i = i0 + tid; i < i1; i += blockDim.x) {
+        const int4 val = reinterpret_cast<const int4*>(acc)[i];
+        for (int p = 0; p < R; ++p) reinterpret_cast<int4*>(v.inbox[p] + v.lay.acc_off(slot, v.rank))[i] = val;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) last_s = atomicAdd(v.done + slot, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (last_s) {
+        // every CTA of this rank has pushed (and fenced): publish the epoch to all ranks
+        if (tid == 0) v.done[slot] = 0;
+        __threadfence_system();
+        if (tid < R) st_release_sys(reinterpret_cast<unsigned long long*>(v.inbox[tid] + v.lay.flag_off(slot, 1, v.rank)), e);
+    }
+    if (tid < R && !wait_sources(v, slot, 1, e, tid)) ok_s = 0;
+    __syncthreads();
+    for (int i = i0 + tid; i < i1; i += blockDim.x) {
+        int4 sum = make_int4(0, 0, 0, 0);
+        for (int r = 0; r < R; ++r) {
+            const int4 a4 = __ldcg(reinterpret_cast<const int4*>(v.inbox[v.rank] + v.lay.acc_off(slot, r)) + i);
+            sum.x += a4.x; sum.y += a4.y; sum.z += a4.z; sum.w += a4.w;
+        }
+        const int m = (4 * i) / n;
+        const float sx = __fdiv_rn(__uint_as_float(amax_cell[m]), 127.0f);
+        float4 hv = reinterpret_cast<float4*>(h)[i];
+        hv.x = __fadd_rn(hv.x, __fmul_rn(__fmul_rn((float)sum.x, sw), sx));
+        hv.y = __fadd_rn(hv.y, __fmul_rn(__fmul_rn((float)sum.y, sw), sx));
+        hv.z = __fadd_rn(hv.z, __fmul_rn(__fmul_rn((float)sum.z, sw), sx));
+        hv.w = __fadd_rn(hv.w, __fmul_rn(__fmul_rn((float)sum.w, sw), sx));
+        reinterpret_cast<float4*>(h)[i] = hv;
+    }
+    if (tid == 0 && !ok_s) atomicExch(v.err, kErrTpTimeout);
+}
+
 }  // namespace
 
 bt_status tp_unique_id(void* out128) {
@@ -104,6 +239,99 @@ bt_status tp_allreduce_sum_i32(void* comm, int32_t* buf, size_t count, cudaStrea
     ncclResult_t r = api->AllReduce(buf, buf, count, ncclInt32, ncclSum, reinterpret_cast<ncclComm_t>(comm), s);
     if (r != ncclSuccess) return set_error(BT_ERR_NCCL, "ncclAllReduce(sum): %s", api->GetErrorString(r));
     return BT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// peer-memory exchange: host side
+// ---------------------------------------------------------------------------------------
+struct TpPeer {
+    TpView view{};
+    uint8_t* local = nullptr;
+    bool opened[kTpMaxRanks] = {false};
+    bool ready = false;
+};
+
+bt_status tp_peer_create(void** out, int rank, int size, int max_batch, int hidden, unsigned int* err) {
+    if (size < 2 || size > kTpMaxRanks || rank < 0 || rank >= size || max_batch < 1 || max_batch > 16 || hidden % 16 != 0)
+        return set_error(BT_ERR_ARG, "tp_peer_create: size %d (2..8), rank %d, max_batch %d (1..16) or hidden %d unsupported",
+                         size, rank, max_batch, hidden);
+    TpPeer* p = new (std::nothrow) TpPeer();
+    if (!p) return set_error(BT_ERR_NOMEM, "host allocation failed");
+    p->view.lay = TpLayout{size, max_batch, hidden};
+    p->view.rank = rank;
+    p->view.err = err;
+    // plain cudaMalloc memory: IPC handles cannot be taken from pool allocations
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->local), p->view.lay.bytes());
+    if (e == cudaSuccess) e = cudaMemset(p->local, 0, p->view.lay.bytes());
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->view.epoch), 2 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(p->view.epoch, 0, 2 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&p->view.done), 2 * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(p->view.done, 0, 2 * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(p->local); cudaFree(p->view.epoch); cudaFree(p->view.done);
+        delete p;
+        return set_error(BT_ERR_CUDA, "tp_peer_create: %s", cudaGetErrorString(e));
+    }
+    p->view.inbox[rank] = p->local;
+    *out = p;
+    return BT_OK;
+}
+
+bt_status tp_peer_export(void* peer, void* handle64_out) {
+    TpPeer* p = reinterpret_cast<TpPeer*>(peer);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p->local);
+    if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    memcpy(handle64_out, &h, 64);
+    return BT_OK;
+}
+
+bt_status tp_peer_import(void* peer, const void* handles) {
+    TpPeer* p = reinterpret_cast<TpPeer*>(peer);
+    if (p->ready) return BT_OK;
+    for (int r = 0; r < p->view.lay.size; ++r) {
+        if (r == p->view.rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, reinterpret_cast<const uint8_t*>(handles) + 64 * r, 64);
+        void* mapped = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", r, cudaGetErrorString(e));
+        p->view.inbox[r] = reinterpret_cast<uint8_t*>(mapped);
+        p->opened[r] = true;
+    }
+    p->ready = true;
+    return BT_OK;
+}
+
+bool tp_peer_ready(const void* peer) { return peer && reinterpret_cast<const TpPeer*>(peer)->ready; }
+
+void tp_peer_destroy(void* peer) {
+    TpPeer* p = reinterpret_cast<TpPeer*>(peer);
+    if (!p) return;
+    for (int r = 0; r < kTpMaxRanks; ++r)
+        if (p->opened[r]) cudaIpcCloseMemHandle(p->view.inbox[r]);
+    cudaFree(p->local);
+    cudaFree(p->view.epoch);
+    cudaFree(p->view.done);
+    delete p;
+}
+
+cudaError_t launch_tp_peer_max(void* peer, int slot, unsigned int* amax_cell, int batch, cudaStream_t s) {
+    TpPeer* p = reinterpret_cast<TpPeer*>(peer);
+    tp_max_exchange_kernel<<<1, 256, 0, s>>>(p->view, slot, amax_cell, batch);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_tp_peer_sum_residual(void* peer, int slot, const int32_t* acc, const unsigned int* amax_cell, float sw,
+                                        int batch, int n, float* h, cudaStream_t s) {
+    TpPeer* p = reinterpret_cast<TpPeer*>(peer);
+    const int total4 = batch * n / 4;
+    int grid = (total4 + 1023) / 1024;
+    grid = grid < 1 ? 1 : (grid > 16 ? 16 : grid);
+    tp_sum_residual_kernel<<<grid, 256, 0, s>>>(p->view, slot, acc, amax_cell, sw, batch, n, h);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_tp_residual(const int32_t* acc, const unsigned int* absmax, float sw, int m, int n, float* h,

@@ -57,6 +57,8 @@ def _bind():
     L.bt_tp_unique_id.argtypes = [vp]
     L.bt_model_tp_init.argtypes = [vp, vp]
     L.bt_model_seek.argtypes = [vp, i32]
+    L.bt_model_tp_peer_export.argtypes = [vp, C.c_char_p]
+    L.bt_model_tp_peer_import.argtypes = [vp, C.c_char_p]
     L.bt_model_enqueue_products.argtypes = [vp, i32, vp, C.POINTER(i32)]
     L.bt_model_launches_per_step.argtypes = [vp, i32]
     L._model_bound = True
@@ -169,6 +171,24 @@ class BitLlama:
         """Joins the tensor-parallel communicator (collective); unique_id from tp_unique_id() of rank 0."""
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
         check(self._L.bt_model_tp_init(self._h, buf))
+
+    def tp_peer_handle(self) -> bytes:
+        """This rank's 64-byte CUDA IPC handle for the peer-memory exchange."""
+        buf = C.create_string_buffer(64)
+        check(self._L.bt_model_tp_peer_export(self._h, buf))
+        return buf.raw
+
+    def tp_peer_init(self, handles) -> None:
+        """handles: the 64-byte handles of all ranks in rank order; switches the row-parallel
+        projections from NCCL calls to this library's NVLink peer-memory kernels."""
+        blob = b"".join(handles)
+        if len(blob) != 64 * self.tp_size:
+            raise ValueError("tp_peer_init expects one 64-byte handle per rank")
+        check(self._L.bt_model_tp_peer_import(self._h, blob))
+
+    def tp_peer_disable(self) -> None:
+        """Back to the NCCL exchange (every rank must call it)."""
+        check(self._L.bt_model_tp_peer_import(self._h, None))
 
     def reset_kv_cache(self):
         check(self._L.bt_model_reset(self._h))

@@ -252,6 +252,17 @@ bt_status bt_model_create(bt_model** out, const bt_model_config* cfg, int device
  * (collective call, after bt_model_finalize, before the first step). */
 bt_status bt_tp_unique_id(uint8_t* id128_out);
 bt_status bt_model_tp_init(bt_model* m, const uint8_t* id128);
+/* Optional, faster exchange for the row-parallel projections (no reference counterpart): the
+ * two all-reduces run as kernels of this library over NVLink peer memory instead of NCCL calls.
+ * Each rank calls bt_model_tp_peer_export (64-byte CUDA IPC handle of its inbox), the ranks
+ * exchange the handles by any transport, and each calls bt_model_tp_peer_import with all
+ * tp_size handles in rank order (64 bytes each; its own entry is ignored).  One process per
+ * GPU, all on one node with peer access.  Results are bit-identical to the NCCL path and to
+ * tp_size = 1.  A rank that never arrives makes the others' bounded waits run out: the step
+ * completes with garbage and bt_device_check reports BT_ERR_TIMEOUT.  bt_model_tp_peer_import with
+ * handles = NULL drops the inbox and returns the model to the NCCL path (all ranks must do the same). */
+bt_status bt_model_tp_peer_export(bt_model* m, uint8_t* handle64_out);
+bt_status bt_model_tp_peer_import(bt_model* m, const uint8_t* handles);
 bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
                               int64_t n_out, int64_t k_in, float scale);
 bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int layer, const float* data_host,

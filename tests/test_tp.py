@@ -29,13 +29,14 @@ def test_row_parallel_exact_on_two_gloo_ranks(oracle):
 
 
 @pytest.mark.gpu
-def test_tp2_model_matches_oracle_and_ranks_agree():
+@pytest.mark.parametrize("use_peer", [False, True], ids=["nccl", "peer_memory"])
+def test_tp2_model_matches_oracle_and_ranks_agree(use_peer):
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(tp_common.gpu_model_worker, args=(2, _free_port(), d, 8), nprocs=2, join=True)
+        mp.spawn(tp_common.gpu_model_worker, args=(2, _free_port(), d, 8, use_peer), nprocs=2, join=True)
         res = _results(d, 2)
         worst, same0 = res[0].split()
         assert float(worst) <= 1e-3 and same0 == "1"

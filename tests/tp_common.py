@@ -55,9 +55,10 @@ def cpu_row_parallel_worker(rank, world, port, result_dir):
     dist.destroy_process_group()
 
 
-def gpu_model_worker(rank, world, port, result_dir, n_tokens):
+def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
     """Tensor-parallel decode of a small llama-shaped model on `world` GPUs; rank 0 checks the
-    logits against the single-process oracle, every rank checks them against rank 0's."""
+    logits against the single-process oracle, every rank checks them against rank 0's.
+    use_peer: exchange over NVLink peer memory (CUDA IPC inboxes) instead of NCCL."""
     import torch
     dist = _init(rank, world, port, "gloo")
     torch.cuda.set_device(rank)
@@ -67,9 +68,14 @@ def gpu_model_worker(rank, world, port, result_dir, n_tokens):
     cfg = syn.BitLlamaConfig("llama", 1000, 256, 2, 8, 4, 512, max_position_embeddings=64)
     w = syn.make_weights(cfg, seed=3000)
     model = syn.build_model(w, max_batch=2, device=rank, tp_rank=rank, tp_size=world)
-    uid = [bt.tp_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(uid, src=0)
-    model.tp_init(uid[0])
+    if use_peer:
+        handles = [None] * world
+        dist.all_gather_object(handles, model.tp_peer_handle())
+        model.tp_peer_init(handles)
+    else:
+        uid = [bt.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        model.tp_init(uid[0])
     ref = orc.model_from_weights(w)
     states = [ref.new_state(), ref.new_state()]
     tokens = np.random.default_rng(7).integers(0, cfg.vocab_size, size=(n_tokens, 2))
