@@ -134,6 +134,21 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     return d;
 }
 
+// c + sum of the four byte products a_i * b_i, both signed
+__device__ __forceinline__ int dp4a_s8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// four ints saturated to signed bytes, q0 in the lowest byte
+__device__ __forceinline__ uint32_t pack4_sat_s8(int q0, int q1, int q2, int q3) {
+    uint32_t hi, d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(q3), "r"(q2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(q1), "r"(q0), "r"(hi));
+    return d;
+}
+
 // round(v) with halves away from zero as an int, for |v| < 2^22: equal to (int)roundf(v).
 // trunc(v + copysign(0.5, v)) is exact except when |v| < 0.5 (the sum can round up to 1),
 // which is answered directly.

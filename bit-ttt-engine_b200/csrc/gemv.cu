@@ -33,35 +33,36 @@ namespace bt {
 
 namespace {
 
-constexpr int kEpiWarps = 4;  // epilogue warps = reduction buffers
+constexpr int kEpiWarps = 4;
 constexpr int kMathWarps = 16;
 constexpr int kMathThreads = kMathWarps * 32;
 constexpr int kProducerWarp = kMathWarps;
 constexpr int kEpilogueWarp0 = kMathWarps + 1;  // first epilogue warp
 constexpr int kThreads = (kMathWarps + 1 + kEpiWarps) * 32;
-constexpr int kStageTiles = 16;
-constexpr int kStageBytes = kStageTiles * kTileBytes;
-constexpr int kRedBufs = kEpiWarps;
-constexpr int kRedBufInts = kMathWarps * 128;
-constexpr int kRedBytes = kRedBufs * kRedBufInts * 4;
+constexpr int kHalfTiles = kMathWarps;               // tiles of one pass over the math warps
+constexpr int kHalfBytes = kHalfTiles * kTileBytes;  // 16 KB
+constexpr int kAccBufs = 16;                          // accumulate buffers, one per row tile in flight
+constexpr int kAccBufInts = 128;                      // [4 accumulator registers][32 lanes]
+constexpr int kAccBytes = kAccBufs * kAccBufInts * 4;
 constexpr int kMaxStages = 12;
-constexpr int kBarBytes = (2 * kMaxStages + 2 * kRedBufs) * 8;
+constexpr int kBarBytes = (2 * kMaxStages + kAccBufs + 1) * 8 + kAccBufs * 4 + 8;
+constexpr int kEarlyBytes = 64 * 1024;  // weight bytes a CTA requests before its activation loads are issued
 constexpr int kTokBytes = 128;  // per-token scale and sum, shared with the epilogue warp
 constexpr int kScratchBytes = 512;  // block-reduction scratch of the prologue
 constexpr unsigned kErrGemvTimeout = 0x47454d56u;  // 'GEMV'
+
+__device__ __forceinline__ void red_add_s32(int* p, int v) {
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(ptx::smem_u32(p)), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // One 1 KB tile: 2 A loads, 4 B loads, 32 ANDs, 8 MMAs.  The four field positions are four
 // independent accumulator chains: their first MMAs are issued back to back, then the second.
 // FIRST: the tile opens a row tile, its first MMAs start from the zero register (the
-// accumulators need no clearing between row tiles).  The loop is bound by instruction issue
-// (about one instruction per cycle and scheduler in steady state), so every instruction that
-// is not a load, an AND or an MMA is worth removing.
+// accumulators need no clearing between row tiles).
 template <bool FIRST>
-__device__ __forceinline__ void tile_mma_b(int (&acc)[4][4], const uint8_t* tile, int lane, const uint4 (&b4)[4]) {
-    const uint4 w4 = lds128(tile + lane * 16);
-    const uint4 v4 = lds128(tile + 512 + lane * 16);
+__device__ __forceinline__ void tile_mma_r(int (&acc)[4][4], const uint4& w4, const uint4& v4, const uint4 (&b4)[4]) {
 #pragma unroll
     for (int f = 0; f < 4; ++f) {
         const uint32_t mask = 0x03030303u << (2 * f);
@@ -73,13 +74,6 @@ __device__ __forceinline__ void tile_mma_b(int (&acc)[4][4], const uint8_t* tile
         const uint32_t mask = 0x03030303u << (2 * f);
         ptx::mma_u8s8(acc[f], w4.y & mask, v4.y & mask, w4.w & mask, v4.w & mask, b4[f].y, b4[f].w);
     }
-}
-template <bool FIRST>
-__device__ __forceinline__ void tile_mma(int (&acc)[4][4], const uint8_t* tile, int lane, const uint8_t* acts_kt) {
-    uint4 b4[4];
-#pragma unroll
-    for (int f = 0; f < 4; ++f) b4[f] = lds128(acts_kt + f * 64);
-    tile_mma_b<FIRST>(acc, tile, lane, b4);
 }
 
 // ---- reductions over the 256 math threads (named barrier 1) ----------------------------
@@ -121,13 +115,13 @@ __device__ __forceinline__ int quant_store_group(const float (&v)[16], float inv
     int sum = 0;
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-        uint32_t word = 0;
+        // |x| <= max|x| makes |x * inv| <= 127 up to two roundings, so the rounded values lie in
+        // [-127, 127] and the saturating pack to signed bytes never changes one
+        int qv[4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int qv = max(-127, min(127, ptx::round_half_away(__fmul_rn(v[4 * b + r], inv))));
-            sum += qv;
-            word |= (uint32_t)(qv & 0xff) << (8 * r);
-        }
+        for (int r = 0; r < 4; ++r) qv[r] = ptx::round_half_away(__fmul_rn(v[4 * b + r], inv));
+        const uint32_t word = ptx::pack4_sat_s8(qv[0], qv[1], qv[2], qv[3]);
+        sum = ptx::dp4a_s8s8(word, 0x01010101u, sum);
         in[b] = word;
     }
     ptx::transpose4x4(in, out);
@@ -135,6 +129,22 @@ __device__ __forceinline__ int quant_store_group(const float (&v)[16], float inv
     uint8_t* p = dst_token + kt * kTileK + tt * 16 + i * 4;
 #pragma unroll
     for (int r = 0; r < 4; ++r) *reinterpret_cast<uint32_t*>(p + r * 64) = out[r];
+    return sum;
+}
+
+// The same for half a group: values 8*hf .. 8*hf+7 of group j (two of the four bytes of each word).
+__device__ __forceinline__ int quant_store_half(const float (&v)[8], float inv, uint8_t* dst_token, int j, int hf) {
+    int qv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qv[e] = ptx::round_half_away(__fmul_rn(v[e], inv));
+    const uint32_t in0 = ptx::pack4_sat_s8(qv[0], qv[1], qv[2], qv[3]);
+    const uint32_t in1 = ptx::pack4_sat_s8(qv[4], qv[5], qv[6], qv[7]);
+    const int sum = ptx::dp4a_s8s8(in1, 0x01010101u, ptx::dp4a_s8s8(in0, 0x01010101u, 0));
+    const int kt = j >> 4, tt = (j >> 2) & 3, i = j & 3;
+    uint8_t* p = dst_token + kt * kTileK + tt * 16 + i * 4 + 2 * hf;
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<uint16_t*>(p + r * 64) = (uint16_t)ptx::prmt(in0, in1, (uint32_t)(r | ((4 + r) << 4)));
     return sum;
 }
 
@@ -151,7 +161,12 @@ __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
 template <int PRO>
 __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* acts, int act_stride, float* tok_sx,
                                                   int* tok_qsum, uint8_t* scratch, int tid, int warp, int lane,
-                                                  int k_tiles, const float (&w0)[16]) {
+                                                  int k_tiles, const float (&w0)[16], uint64_t* x_issued) {
+    // tells the producer that this warp's first activation loads are on their way
+    auto loads_issued = [&]() {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(x_issued);
+    };
     const int groups_pad = k_tiles * (kTileK / 16);
     const int groups = (int)(a.k_in >> 4);  // k_in is a multiple of 16 on the fused paths
     double* sl_d = reinterpret_cast<double*>(scratch);            // kMathWarps doubles
@@ -170,6 +185,7 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
 #pragma unroll
                 for (int r = 0; r < 4; ++r) *reinterpret_cast<uint32_t*>(p + r * 64) = out[r];
             }
+            if (n == 0) loads_issued();
         }
         if (tid < a.m) {
             tok_qsum[tid] = a.qsum[tid];
@@ -182,7 +198,41 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
         uint8_t* dst = acts + (size_t)n * act_stride;
         int local = 0;
         float s;
-        if (PRO == PRO_RMSNORM) {
+        if (PRO == PRO_RMSNORM && 2 * groups <= kMathThreads) {
+            // k_in <= 4096: half a group (8 values) per thread, so that all math threads share the work
+            const int j = tid >> 1, hf = tid & 1;
+            const bool h = j < groups;
+            float v[8];
+            double ss0 = 0.0, ss1 = 0.0;
+            if (h) {
+                const float4 f0 = *reinterpret_cast<const float4*>(xr + 16 * j + 8 * hf);
+                const float4 f1 = *reinterpret_cast<const float4*>(xr + 16 * j + 8 * hf + 4);
+                v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w; v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+            }
+            if (n == 0) loads_issued();
+            if (h) {
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    ss0 = fma((double)v[e], (double)v[e], ss0);
+                    ss1 = fma((double)v[e + 1], (double)v[e + 1], ss1);
+                }
+            }
+            const double ss = math_sum_d(ss0 + ss1, sl_d, warp, lane);
+            const float denom = sqrtf(__fadd_rn((float)(ss / (double)a.k_in), a.eps));
+            float amax = 0.0f;
+            if (h) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { v[e] = __fmul_rn(__fdiv_rn(v[e], denom), w0[e]); amax = fmaxf(amax, fabsf(v[e])); }
+            }
+            amax = math_max_f(amax, sl_f, warp, lane);
+            s = __fdiv_rn(amax, 127.0f);
+            const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+            if (h) local += quant_store_half(v, inv, dst, j, hf);
+            for (int jp = groups + tid; jp < groups_pad; jp += kMathThreads) {
+                const float z[16] = {0};
+                quant_store_group(z, 0.0f, dst, jp);
+            }
+        } else if (PRO == PRO_RMSNORM) {
             // up to two 16-groups per thread held in registers (k_in <= 8192)
             float v0[16], v1[16];
             const int j0 = tid, j1 = tid + kMathThreads;
@@ -190,6 +240,7 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
             double ss = 0.0;
             if (h0) load16(xr + 16 * j0, v0);
             if (h1) load16(xr + 16 * j1, v1);
+            if (n == 0) loads_issued();
             if (h0) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e) ss = fma((double)v0[e], (double)v0[e], ss); }
@@ -220,7 +271,8 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
             s = __fdiv_rn(amax, 127.0f);
             const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
             // four groups per thread per round, all loads of a round issued before any use
-            for (int jb = tid; jb < groups_pad; jb += 4 * kMathThreads) {
+            for (int jb0 = 0; jb0 < groups_pad; jb0 += 4 * kMathThreads) {  // same trip count in every thread
+                const int jb = jb0 + tid;
                 float v[4][16];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -231,6 +283,7 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
                         for (int e = 0; e < 16; ++e) v[u][e] = 0.0f;
                     }
                 }
+                if (n == 0 && jb0 == 0) loads_issued();
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int j = jb + u * kMathThreads;
@@ -246,37 +299,48 @@ __device__ __forceinline__ void stage_activations(const GemvArgs& a, uint8_t* ac
     }
 }
 
-template <int PRO>
+// TPW: tiles per math warp and ring stage (a stage is TPW passes of 16 KB).  With K <= 4096 a
+// row tile is one pass, so a stage holds TPW row tiles of the CTA (one bulk copy each); with a
+// longer K a stage holds up to 16*TPW consecutive tiles of one row tile.  Two tiles per warp
+// halve the barrier round trips per byte and put both tiles' shared-memory loads in flight
+// before the first MMA.
+template <int PRO, int TPW>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstages, int act_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kStageBytes = TPW * kHalfBytes;
+    constexpr int kStageTiles = TPW * kHalfTiles;
     uint8_t* ring = smem;
-    int* red = reinterpret_cast<int*>(ring + (size_t)nstages * kStageBytes);
-    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(red) + kRedBytes);
+    int* accbuf = reinterpret_cast<int*>(ring + (size_t)nstages * kStageBytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(accbuf) + kAccBytes);
     uint64_t* empty = full + kMaxStages;
-    uint64_t* red_full = empty + kMaxStages;
-    uint64_t* red_empty = red_full + kRedBufs;
-    float* tok_sx = reinterpret_cast<float*>(red_empty + kRedBufs);
+    uint64_t* acc_full = empty + kMaxStages;
+    uint64_t* x_issued = acc_full + kAccBufs;  // every math warp has issued its activation loads
+    volatile unsigned* acc_gen = reinterpret_cast<volatile unsigned*>(x_issued + 1);
+    float* tok_sx = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full) + kBarBytes);
     int* tok_qsum = reinterpret_cast<int*>(tok_sx + 8);
     uint8_t* scratch = reinterpret_cast<uint8_t*>(tok_sx) + kTokBytes;
     uint8_t* acts = scratch + kScratchBytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = (int)a.k_tiles;
-    const int stages_per_rt = (k_tiles + kStageTiles - 1) / kStageTiles;
+    const bool short_k = k_tiles <= kHalfTiles;  // a row tile is one pass
+    const int stages_per_rt = (k_tiles + kStageTiles - 1) / kStageTiles;  // long K only
     const int my_rts = (int)((a.row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
-    const int total_iters = my_rts * stages_per_rt;
+    const int total_iters = short_k ? (my_rts + TPW - 1) / TPW : my_rts * stages_per_rt;
 
     if (a.dbg && threadIdx.x == 0) a.dbg[blockIdx.x * 4 + 0] = ptx::globaltimer();
     if (threadIdx.x < 8) tok_qsum[threadIdx.x] = 0;
+    for (int i = threadIdx.x; i < kAccBufs * kAccBufInts; i += kThreads) accbuf[i] = 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
             ptx::mbar_init(&full[s], 1);
             ptx::mbar_init(&empty[s], kMathWarps);
         }
-        for (int b = 0; b < kRedBufs; ++b) {
-            ptx::mbar_init(&red_full[b], kMathWarps);
-            ptx::mbar_init(&red_empty[b], 1);
+        for (int b = 0; b < kAccBufs; ++b) {
+            ptx::mbar_init(&acc_full[b], kMathWarps);
+            acc_gen[b] = 0;
         }
+        ptx::mbar_init(x_issued, kMathWarps);
         ptx::mbar_fence_init();
     }
     __syncthreads();
@@ -288,17 +352,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             int slot = 0, sk = 0;
             uint32_t wait_parity = 1;  // flips to 0 for the second use of each slot
             bool first_round = true;
-            int64_t rt = blockIdx.x;
+            int lt = 0;  // CTA-local row tile: global row tile blockIdx.x + lt * gridDim.x
+            // The activation loads of the math warps queue behind whatever this SM has already
+            // requested, and the math cannot start before they are back.  So only kEarlyBytes of
+            // weights are requested up front (enough to keep HBM busy across the dependency
+            // wait); the rest follows once the activation loads have been issued.
+            const int early_iters = kEarlyBytes / kStageBytes;
             for (int it = 0; it < total_iters; ++it) {
+                if (it == early_iters && ok) ok = ptx::mbar_wait_relaxed(x_issued, 0);
                 if (!first_round && ok) ok = ptx::mbar_wait_relaxed(&empty[slot], wait_parity);
-                const int kt0 = sk * kStageTiles;
-                const int nt = k_tiles - kt0 < kStageTiles ? k_tiles - kt0 : kStageTiles;
-                const uint32_t bytes = (uint32_t)nt * kTileBytes;
-                ptx::mbar_arrive_expect_tx(&full[slot], bytes);
-                ptx::bulk_g2s(ring + (size_t)slot * kStageBytes,
-                              a.tiles + (rt * k_tiles + kt0) * kTileBytes, bytes, &full[slot]);
+                uint8_t* dst = ring + (size_t)slot * kStageBytes;
+                if (short_k) {
+                    const int n_rt = my_rts - lt < TPW ? my_rts - lt : TPW;
+                    const uint32_t bytes = (uint32_t)k_tiles * kTileBytes;
+                    ptx::mbar_arrive_expect_tx(&full[slot], bytes * n_rt);
+                    for (int u = 0; u < n_rt; ++u) {
+                        const int64_t rt = blockIdx.x + (int64_t)(lt + u) * gridDim.x;
+                        ptx::bulk_g2s(dst + u * kHalfBytes, a.tiles + rt * k_tiles * kTileBytes, bytes, &full[slot]);
+                    }
+                    lt += n_rt;
+                } else {
+                    const int kt0 = sk * kStageTiles;
+                    const int nt = k_tiles - kt0 < kStageTiles ? k_tiles - kt0 : kStageTiles;
+                    const uint32_t bytes = (uint32_t)nt * kTileBytes;
+                    const int64_t rt = blockIdx.x + (int64_t)lt * gridDim.x;
+                    ptx::mbar_arrive_expect_tx(&full[slot], bytes);
+                    ptx::bulk_g2s(dst, a.tiles + (rt * k_tiles + kt0) * kTileBytes, bytes, &full[slot]);
+                    if (++sk == stages_per_rt) { sk = 0; ++lt; }
+                }
                 if (++slot == nstages) { slot = 0; first_round = false; wait_parity ^= 1; }
-                if (++sk == stages_per_rt) { sk = 0; rt += gridDim.x; }
                 // once the ring is primed, let the next kernel of the stream start its own prefetch
                 if (it + 1 == nstages || it + 1 == total_iters) ptx::pdl_launch_dependents();
             }
@@ -310,8 +392,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
 
     if (warp >= kEpilogueWarp0) {
         ptx::pdl_wait();  // the output buffer belongs to earlier kernels until here
-        // ---------------- epilogue warps: warp e serves reduction buffer e, i.e. the CTA's row
-        // tiles e, e + kEpiWarps, ... ----------------
+        // ---------------- epilogue warps: warp e serves the CTA's row tiles e, e + kEpiWarps, ...
+        // Row tile lt is summed by the math warps (shared-memory atomics) into accumulate buffer
+        // lt % kAccBufs; the epilogue warp reads the finished sums, clears the buffer and
+        // publishes the buffer's generation so that the math warps may use it again. ----------
         const int epi = warp - kEpilogueWarp0;
         ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // tok_sx / tok_qsum are ready
         const int t = lane & 3, g = lane >> 2;
@@ -323,28 +407,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             if (token < a.m) { qs[e] = tok_qsum[token]; sx[e] = tok_sx[token]; }
         }
         bool ok = true;
-        const int rb = epi;
-        uint32_t parity = 0;
         float run_max[2] = {0.f, 0.f};  // EPI_SWIGLU: running max|out| of this lane's two tokens
         int64_t rt = blockIdx.x + (int64_t)epi * gridDim.x;
         if (a.m == 1) {
-            // Single token: the math warps leave 16 sums each (one per row of the tile), the lane
-            // pair (r, r + 16) adds 8 warps each.  Lane r < 16 then owns row r of the tile.
-            const int r = lane & 15, half_w = lane >> 4;
+            // Single token: lane r < 16 owns row r of the tile (lanes 16-31 mirror them).
+            const int r = lane & 15;
             const int qs0 = tok_qsum[0];
             const float sx0 = tok_sx[0];
             float amax1 = 0.f;
+            float sw = 0.f;
+            if (a.epilogue != EPI_I32 && epi < my_rts) sw = a.sw_tiles[2 * rt + (r >> 3)];
             for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
-                float sw = 0.f;
-                if (a.epilogue != EPI_I32) sw = a.sw_tiles[2 * rt + (r >> 3)];
-                if (ok) ok = ptx::mbar_wait_relaxed(&red_full[rb], parity);
-                const int* buf = red + rb * kRedBufInts + half_w * (kMathWarps / 2) * 16 + r;
-                int sum = 0;
-#pragma unroll
-                for (int w = 0; w < kMathWarps / 2; ++w) sum += buf[w * 16];
-                sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+                // the next row tile's scale comes from global memory: fetch it a round early
+                float sw_next = 0.f;
+                if (a.epilogue != EPI_I32 && lt + kEpiWarps < my_rts)
+                    sw_next = a.sw_tiles[2 * (rt + (int64_t)kEpiWarps * gridDim.x) + (r >> 3)];
+                const int b = lt % kAccBufs;
+                const unsigned use = (unsigned)(lt / kAccBufs);
+                if (ok) ok = ptx::mbar_wait_relaxed(&acc_full[b], use & 1);
+                int* buf = accbuf + b * kAccBufInts;
+                const int sum = buf[r];
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&red_empty[rb]);
+                if (lane < 16) buf[lane] = 0;
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) acc_gen[b] = use + 1;
                 const int accv = sum - qs0;
                 const int64_t row = rt * kTileRows + r;
                 if (a.epilogue == EPI_I32) {
@@ -368,7 +455,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                         else reinterpret_cast<__nv_bfloat16*>(a.out)[row] = __float2bfloat16_rn(y);
                     }
                 }
-                parity ^= 1;
+                sw = sw_next;
                 rt += (int64_t)kEpiWarps * gridDim.x;
             }
             if (a.epilogue == EPI_SWIGLU) {
@@ -383,15 +470,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
         for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
             float sw[2] = {0.f, 0.f};
             if (a.epilogue != EPI_I32) { sw[0] = a.sw_tiles[2 * rt]; sw[1] = a.sw_tiles[2 * rt + 1]; }
-            if (ok) ok = ptx::mbar_wait_relaxed(&red_full[rb], parity);
-            const int* buf = red + rb * kRedBufInts;
-            int sum[4] = {0, 0, 0, 0};
+            const int b = lt % kAccBufs;
+            const unsigned use = (unsigned)(lt / kAccBufs);
+            if (ok) ok = ptx::mbar_wait_relaxed(&acc_full[b], use & 1);
+            int* buf = accbuf + b * kAccBufInts;
+            int sum[4];
 #pragma unroll
-            for (int w = 0; w < kMathWarps; ++w)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sum[j] += buf[w * 128 + j * 32 + lane];
+            for (int j = 0; j < 4; ++j) { sum[j] = buf[j * 32 + lane]; buf[j * 32 + lane] = 0; }
+            __threadfence_block();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&red_empty[rb]);
+            if (lane == 0) acc_gen[b] = use + 1;
             if (a.epilogue == EPI_SWIGLU) {
                 // rows 0-7 of the tile are gate rows, rows 8-15 the matching up rows
                 const int64_t col = rt * 8 + g;
@@ -427,7 +515,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                     }
                 }
             }
-            parity ^= 1;
             rt += (int64_t)kEpiWarps * gridDim.x;
         }
         if (a.epilogue == EPI_SWIGLU) {
@@ -451,10 +538,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     // The norm weights do not depend on earlier kernels and usually come from DRAM (nothing
     // else touches them during a step): fetch them before waiting on the dependency.
     float w0[16];
-    if (PRO == PRO_RMSNORM && tid < (int)(a.k_in >> 4)) load16(a.norm_w + 16 * tid, w0);
+    if (PRO == PRO_RMSNORM) {
+        const int groups = (int)(a.k_in >> 4);
+        if (2 * groups <= kMathThreads) {  // half a group per thread (see stage_activations)
+            if ((tid >> 1) < groups) {
+                const float4 f0 = *reinterpret_cast<const float4*>(a.norm_w + 8 * tid);
+                const float4 f1 = *reinterpret_cast<const float4*>(a.norm_w + 8 * tid + 4);
+                w0[0] = f0.x; w0[1] = f0.y; w0[2] = f0.z; w0[3] = f0.w; w0[4] = f1.x; w0[5] = f1.y; w0[6] = f1.z; w0[7] = f1.w;
+            }
+        } else if (tid < groups) {
+            load16(a.norm_w + 16 * tid, w0);
+        }
+    }
     ptx::pdl_wait();  // activations belong to earlier kernels until here
     if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 1] = ptx::globaltimer();
-    stage_activations<PRO>(a, acts, act_stride, tok_sx, tok_qsum, scratch, tid, warp, lane, k_tiles, w0);
+    stage_activations<PRO>(a, acts, act_stride, tok_sx, tok_qsum, scratch, tid, warp, lane, k_tiles, w0, x_issued);
     ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // activation image complete, epilogue warps may read the scales
     if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 2] = ptx::globaltimer();
 
@@ -464,31 +562,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     const uint8_t* my_acts = acts + (size_t)(g < a.m ? g : a.m - 1) * act_stride + t * 16;
     const bool single = a.m == 1;
     bool ok = true;
-    int slot = 0, sk = 0, rb = 0;
-    uint32_t parity = 0, red_parity = 1;
-    bool red_first = true;
+    int slot = 0;
+    uint32_t parity = 0;
 
-    // row tile complete: fold the four field positions and hand the partial sums to an epilogue warp
-    auto hand_over = [&]() {
-        if (!red_first && ok) ok = ptx::mbar_wait_bounded(&red_empty[rb], red_parity);
-        if (single) {
-            // one token: only column 0 of the MMA tile is live (lanes with t = 0: rows g and g + 8)
-            int* my_red = red + rb * kRedBufInts + warp * 16;
-            const int lo = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
-            const int hi = acc[0][2] + (acc[1][2] >> 2) + (acc[2][2] >> 4) + (acc[3][2] >> 6);
-            if (t == 0) { my_red[g] = lo; my_red[g + 8] = hi; }
-        } else {
-            int* my_red = red + rb * kRedBufInts + warp * 128;
+    // Row tile lt complete in this warp: fold the four field positions and add the warp's partial
+    // sums into the row tile's accumulate buffer (integer atomics: the order of the 16 warps does
+    // not matter).  gen_seen is the buffer's generation as read before the tile's math, so the
+    // check normally costs nothing; it only spins when the epilogue warps are a whole round of
+    // buffers behind.
+    auto hand_over = [&](int lt, unsigned gen_seen, bool contributes) {
+        const int b = lt % kAccBufs;
+        const unsigned use = (unsigned)(lt / kAccBufs);
+        if (gen_seen < use && ok) {
+            bool got = false;
+            for (unsigned i = 0; i < (1u << 22) && !got; ++i) got = acc_gen[b] >= use;
+            ok = got;
+        }
+        int* buf = accbuf + b * kAccBufInts;
+        if (contributes) {
+            if (single) {
+                // one token: only column 0 of the MMA tile is live (lanes with t = 0: rows g and g + 8)
+                const int lo = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
+                const int hi = acc[0][2] + (acc[1][2] >> 2) + (acc[2][2] >> 4) + (acc[3][2] >> 6);
+                if (t == 0) { red_add_s32(buf + g, lo); red_add_s32(buf + g + 8, hi); }
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                my_red[j * 32 + lane] = acc[0][j] + (acc[1][j] >> 2) + (acc[2][j] >> 4) + (acc[3][j] >> 6);
+                for (int j = 0; j < 4; ++j)
+                    red_add_s32(buf + j * 32 + lane, acc[0][j] + (acc[1][j] >> 2) + (acc[2][j] >> 4) + (acc[3][j] >> 6));
+            }
         }
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&red_full[rb]);
-        if (++rb == kRedBufs) { rb = 0; red_first = false; red_parity ^= 1; }
+        if (lane == 0) ptx::mbar_arrive(&acc_full[b]);
     };
 
-    if (stages_per_rt == 1) {
+    if (short_k) {
         // K <= 4096: this warp multiplies the same 256 inputs in every row tile, so its
         // activation registers are loaded once (the activation loads are two thirds of the
         // loop's shared-memory traffic otherwise) and every tile is a whole row tile
@@ -496,42 +603,64 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
         uint4 b4[4];
 #pragma unroll
         for (int f = 0; f < 4; ++f) b4[f] = have ? lds128(my_acts + warp * kTileK + f * 64) : make_uint4(0u, 0u, 0u, 0u);
+        int lt = 0;
         for (int it = 0; it < total_iters; ++it) {
+            unsigned gen[TPW];
+#pragma unroll
+            for (int u = 0; u < TPW; ++u) gen[u] = acc_gen[(lt + u) % kAccBufs];
             if (ok) ok = ptx::mbar_wait_bounded(&full[slot], parity);
-            const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes;
-            if (have) {
-                tile_mma_b<true>(acc, tile, lane, b4);
-            } else {
+            const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes + lane * 16;
+            uint4 w4[TPW], v4[TPW];
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[r][j] = 0;
+            for (int u = 0; u < TPW; ++u) {
+                if (have && lt + u < my_rts) { w4[u] = lds128(tile + u * kHalfBytes); v4[u] = lds128(tile + u * kHalfBytes + 512); }
             }
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&empty[slot]);
+#pragma unroll
+            for (int u = 0; u < TPW; ++u) {
+                if (lt + u < my_rts) {
+                    if (have) tile_mma_r<true>(acc, w4[u], v4[u], b4);
+                    if (u == TPW - 1 || lt + u + 1 == my_rts) {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&empty[slot]);
+                    }
+                    hand_over(lt + u, gen[u], have);
+                }
+            }
+            lt += TPW;
             if (++slot == nstages) { slot = 0; parity ^= 1; }
-            hand_over();
         }
     } else {
+        int lt = 0, sk = 0;
+        unsigned gen = 0;
         for (int it = 0; it < total_iters; ++it) {
+            if (sk == 0) gen = acc_gen[lt % kAccBufs];
             if (ok) ok = ptx::mbar_wait_bounded(&full[slot], parity);
-            const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes;
-            const int kt = sk * kStageTiles + warp;  // one 1 KB tile per math warp and stage
-            if (kt < k_tiles) {
-                if (sk == 0) tile_mma<true>(acc, tile, lane, my_acts + kt * kTileK);
-                else tile_mma<false>(acc, tile, lane, my_acts + kt * kTileK);
-            } else if (sk == 0) {  // fewer tiles than math warps: this warp contributes zeros
+            const uint8_t* tile = ring + (size_t)slot * kStageBytes + warp * kTileBytes + lane * 16;
+            const int kt0 = sk * kStageTiles + warp;  // this warp's tiles of the stage: kt0, kt0 + 16, ...
+            uint4 w4[TPW], v4[TPW];
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
+            for (int u = 0; u < TPW; ++u) {
+                if (kt0 + u * kHalfTiles < k_tiles) { w4[u] = lds128(tile + u * kHalfBytes); v4[u] = lds128(tile + u * kHalfBytes + 512); }
+            }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[r][j] = 0;
+            for (int u = 0; u < TPW; ++u) {
+                const int kt = kt0 + u * kHalfTiles;
+                if (kt < k_tiles) {
+                    uint4 b4[4];
+#pragma unroll
+                    for (int f = 0; f < 4; ++f) b4[f] = lds128(my_acts + kt * kTileK + f * 64);
+                    // tile `warp` of a row tile always exists here (more than 16 tiles): it opens the accumulators
+                    if (u == 0 && sk == 0) tile_mma_r<true>(acc, w4[u], v4[u], b4);
+                    else tile_mma_r<false>(acc, w4[u], v4[u], b4);
+                }
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty[slot]);
             if (++slot == nstages) { slot = 0; parity ^= 1; }
             if (++sk == stages_per_rt) {
                 sk = 0;
-                hand_over();
+                hand_over(lt, gen, true);
+                ++lt;
             }
         }
     }
@@ -549,47 +678,56 @@ int g_configured[64] = {0};
 
 }  // namespace
 
+template <int TPW>
+static cudaError_t launch_gemv_t(const GemvArgs& a, int grid, size_t smem, int nstages, int act_stride, cudaStream_t stream) {
+    switch (a.prologue) {
+        case PRO_RMSNORM: return launch_pdl(gemv_kernel<PRO_RMSNORM, TPW>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
+        case PRO_ABSMAX: return launch_pdl(gemv_kernel<PRO_ABSMAX, TPW>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
+        default: return launch_pdl(gemv_kernel<PRO_Q8, TPW>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
+    }
+}
+
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     if (a.m < 1 || a.m > 8) return cudaErrorInvalidValue;
     if (a.prologue != PRO_Q8 && (a.k_in % 16 != 0)) return cudaErrorInvalidValue;
     if (a.prologue == PRO_RMSNORM && a.k_in > 16 * 2 * kMathThreads) return cudaErrorInvalidValue;
-    static_assert(kStageTiles == kMathWarps, "one tile per math warp");
     if (a.epilogue == EPI_SWIGLU && (!a.absmax_out || a.n_out % 16 != 0)) return cudaErrorInvalidValue;
     const int act_stride = (int)(a.k_tiles * kTileK + 64);
-    const size_t fixed = (size_t)a.m * act_stride + kRedBytes + kBarBytes + kTokBytes + kScratchBytes;
-    const int stages_per_rt = (int)((a.k_tiles + kStageTiles - 1) / kStageTiles);
+    const size_t fixed = (size_t)a.m * act_stride + kAccBytes + kBarBytes + kTokBytes + kScratchBytes;
     // One CTA per SM.  The ring takes what shared memory allows, but never more stages than
-    // the CTA has iterations: small projections (q|k|v, o) then leave room for the next
-    // product kernel of the stream (programmatic dependent launch) to become resident
-    // beside this one and stream its first stages early, while large ones (gate|up, down)
-    // get the deepest ring - HBM needs well over 100 KB in flight per SM to stay busy.
-    const size_t full_budget = 220 * 1024;
-    const int ctas_per_sm = 1;
-    const size_t budget = full_budget;
-    if (fixed + 2 * kStageBytes > budget) return cudaErrorInvalidConfiguration;
-    int nstages = (int)((budget - fixed) / kStageBytes);
-    if (nstages > kMaxStages) nstages = kMaxStages;
-    int64_t grid64 = (int64_t)ctas_per_sm * sm_count;
+    // the CTA has iterations.  Stages of two passes (32 KB) are used whenever at least three of
+    // them fit beside the activation image; HBM needs well over 100 KB in flight per SM.
+    const size_t budget = 220 * 1024;
+    if (fixed + 2 * kHalfBytes > budget) return cudaErrorInvalidConfiguration;
+    int64_t grid64 = sm_count;
     if (grid64 > a.row_tiles) grid64 = a.row_tiles;
     const int grid = (int)grid64;
-    const int64_t max_iters = ((a.row_tiles + grid - 1) / grid) * stages_per_rt;
+    const int64_t rts_per_cta = (a.row_tiles + grid - 1) / grid;
+    const bool short_k = a.k_tiles <= kHalfTiles;
+    int tpw = (budget - fixed) / (2 * kHalfBytes) >= 3 ? 2 : 1;
+    if (short_k && rts_per_cta < 2) tpw = 1;
+    const int stage_bytes = tpw * kHalfBytes;
+    int nstages = (int)((budget - fixed) / stage_bytes);
+    if (nstages > kMaxStages / tpw) nstages = kMaxStages / tpw;
+    const int64_t max_iters = short_k ? (rts_per_cta + tpw - 1) / tpw
+                                      : rts_per_cta * ((a.k_tiles + tpw * kHalfTiles - 1) / (tpw * kHalfTiles));
     if (nstages > max_iters) nstages = (int)max_iters;
     if (nstages < 1) nstages = 1;
-    const size_t smem = (size_t)nstages * kStageBytes + fixed;
+    const size_t smem = (size_t)nstages * stage_bytes + fixed;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !g_configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_budget);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_budget);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_budget);
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
         if (e != cudaSuccess) return e;
         g_configured[dev] = 1;
     }
-    switch (a.prologue) {
-        case PRO_RMSNORM: return launch_pdl(gemv_kernel<PRO_RMSNORM>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
-        case PRO_ABSMAX: return launch_pdl(gemv_kernel<PRO_ABSMAX>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
-        default: return launch_pdl(gemv_kernel<PRO_Q8>, dim3(grid), dim3(kThreads), smem, stream, a.pdl, a, nstages, act_stride);
-    }
+    return tpw == 2 ? launch_gemv_t<2>(a, grid, smem, nstages, act_stride, stream)
+                    : launch_gemv_t<1>(a, grid, smem, nstages, act_stride, stream);
 }
 
 cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stride,
