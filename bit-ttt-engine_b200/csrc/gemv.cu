@@ -415,6 +415,49 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             const int qs0 = tok_qsum[0];
             const float sx0 = tok_sx[0];
             float amax1 = 0.f;
+            if (a.epilogue == EPI_SWIGLU) {
+                // silu(gate) * up needs an f64 exponential, a long dependent chain.  Four row tiles
+                // (8 columns each) are therefore finished together, one column per lane, so that the
+                // chain runs once per four row tiles: chunk c = row tiles 4c .. 4c+3 of the CTA,
+                // chunks dealt round-robin to the epilogue warps.
+                const int sub = lane >> 3, col8 = lane & 7;
+                const int n_chunks = (my_rts + 3) / 4;
+                for (int c = epi; c < n_chunks; c += kEpiWarps) {
+                    const int lt0 = 4 * c;
+                    const int lt = lt0 + sub;
+                    const bool valid = lt < my_rts;
+                    const int64_t rtile = blockIdx.x + (int64_t)lt * gridDim.x;
+                    float swg = 0.f, swu = 0.f;
+                    if (valid) { swg = a.sw_tiles[2 * rtile]; swu = a.sw_tiles[2 * rtile + 1]; }
+                    for (int s2 = 0; s2 < 4 && lt0 + s2 < my_rts; ++s2)
+                        if (ok) ok = ptx::mbar_wait_relaxed(&acc_full[(lt0 + s2) % kAccBufs], (unsigned)((lt0 + s2) / kAccBufs) & 1);
+                    int gsum = 0, usum = 0;
+                    if (valid) {
+                        int* buf = accbuf + (lt % kAccBufs) * kAccBufInts;
+                        // rows 0-7 of the tile are gate rows, rows 8-15 the matching up rows
+                        gsum = buf[col8]; usum = buf[col8 + 8];
+                        buf[col8] = 0; buf[col8 + 8] = 0;
+                    }
+                    __threadfence_block();
+                    __syncwarp();
+                    if (lane < 4 && lt0 + lane < my_rts) acc_gen[(lt0 + lane) % kAccBufs] = (unsigned)((lt0 + lane) / kAccBufs) + 1;
+                    const int64_t col = rtile * 8 + col8;
+                    if (valid && col < a.n_out / 2) {
+                        const float y = __fmul_rn(__fmul_rn((float)(gsum - qs0), swg), sx0);
+                        const float uv = __fmul_rn(__fmul_rn((float)(usum - qs0), swu), sx0);
+                        // silu(g) * u, exp in f64 rounded once (layers/swiglu.rs:31-33)
+                        const float act = __fmul_rn(__fdiv_rn(y, __fadd_rn(1.0f, (float)exp(-(double)y))), uv);
+                        reinterpret_cast<float*>(a.out)[col] = act;
+                        amax1 = fmaxf(amax1, fabsf(act));
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax1 = fmaxf(amax1, __shfl_xor_sync(0xffffffffu, amax1, o));
+                if (lane == 0) atomicMax(a.absmax_out, __float_as_uint(amax1));
+                if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
+                if (a.dbg && lane == 0) atomicMax(a.dbg + blockIdx.x * 4 + 3, ptx::globaltimer());  // last epilogue warp to finish
+                return;
+            }
             float sw = 0.f;
             if (a.epilogue != EPI_I32 && epi < my_rts) sw = a.sw_tiles[2 * rt + (r >> 3)];
             for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
@@ -438,17 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                     if (lane < 16 && row < a.n_out) reinterpret_cast<int32_t*>(a.out)[row] = accv;
                 } else {
                     const float y = __fmul_rn(__fmul_rn((float)accv, sw), sx0);
-                    if (a.epilogue == EPI_SWIGLU) {
-                        // rows 0-7 of the tile are gate rows, rows 8-15 the matching up rows
-                        const float uv = __shfl_down_sync(0xffffffffu, y, 8);
-                        const int64_t col = rt * 8 + r;
-                        if (lane < 8 && col < a.n_out / 2) {
-                            // silu(g) * u, exp in f64 rounded once (layers/swiglu.rs:31-33)
-                            const float act = __fmul_rn(__fdiv_rn(y, __fadd_rn(1.0f, (float)exp(-(double)y))), uv);
-                            reinterpret_cast<float*>(a.out)[col] = act;
-                            amax1 = fmaxf(amax1, fabsf(act));
-                        }
-                    } else if (lane < 16 && row < a.n_out) {
+                    if (lane < 16 && row < a.n_out) {
                         if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[row] = y;
                         else if (a.epilogue == EPI_F32_ACCUM)
                             reinterpret_cast<float*>(a.out)[row] = __fadd_rn(reinterpret_cast<float*>(a.out)[row], y);
@@ -458,13 +491,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                 sw = sw_next;
                 rt += (int64_t)kEpiWarps * gridDim.x;
             }
-            if (a.epilogue == EPI_SWIGLU) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) amax1 = fmaxf(amax1, __shfl_xor_sync(0xffffffffu, amax1, o));
-                if (lane == 0) atomicMax(a.absmax_out, __float_as_uint(amax1));
-            }
             if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
-            if (a.dbg && lane == 0 && epi == 0) a.dbg[blockIdx.x * 4 + 3] = ptx::globaltimer();
+            if (a.dbg && lane == 0) atomicMax(a.dbg + blockIdx.x * 4 + 3, ptx::globaltimer());  // last epilogue warp to finish
             return;
         }
         for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
@@ -528,7 +556,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             }
         }
         if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
-        if (a.dbg && lane == 0 && epi == 0) a.dbg[blockIdx.x * 4 + 3] = ptx::globaltimer();
+        if (a.dbg && lane == 0) atomicMax(a.dbg + blockIdx.x * 4 + 3, ptx::globaltimer());  // last epilogue warp to finish
         return;
     }
 
