@@ -170,6 +170,44 @@ def run_linear_probe(bt, n, k, m):
     print("linear probe done", float(y.abs().sum()), file=sys.stderr)
 
 
+def run_timeline(bt, model, args, B):
+    """Profiling aid: the kernels of the fused decode step (batch <= 8) write globaltimer stamps per
+    CTA (entry, dependency released, activations staged, last epilogue warp done) while one step is
+    captured; the replayed step is then printed launch by launch, in ns from the first stamp."""
+    import ctypes as C
+    import torch
+    layers = args.layers
+    L = bt.lib()
+    model.seek(args.context)
+    buf = torch.zeros(layers * 5 * 512 * 4, dtype=torch.int64, device="cuda")
+    ids = np.arange(B, dtype=np.int32) + 5
+    _, ids = model.forward_one(ids, want_logits=False)   # eager step: kernel attributes
+    L.bt_debug_timeline.argtypes = [C.c_void_p]
+    L.bt_debug_timeline(C.c_void_p(buf.data_ptr()))
+    _, ids = model.forward_one(ids, want_logits=False)   # captured with the stamp slots
+    L.bt_debug_timeline(None)
+    for _ in range(5):
+        _, ids = model.forward_one(ids, want_logits=False)
+    torch.cuda.synchronize()
+    t = buf.cpu().numpy().reshape(layers * 5, 512, 4)
+    names = ["q|k|v", "attention", "o_proj", "gate|up", "down_proj"]
+    t00 = None
+    for s in range(layers * 5):
+        v = t[s]
+        if s % 5 == 1:  # attention: 8 stamps per CTA (entry, released, ..., partials written, arrived)
+            v8 = v.reshape(256, 8)
+            v = np.stack([v8[:, 0], v8[:, 1], v8[:, 6], v8[:, 7]], 1)
+        used = v[:, 0] > 0
+        if not used.any():
+            continue
+        if t00 is None:
+            t00 = v[used, 0].min()
+        cols = [v[used, i] - t00 for i in range(4)]
+        print(f"block {s // 5} {names[s % 5]:10s} ctas {int(used.sum()):3d}  entry {int(cols[0].min()):7d}..{int(cols[0].max()):7d}"
+              f"  released {int(cols[1].min()):7d}..{int(cols[1].max()):7d}  staged {int(cols[2].min()):7d}..{int(cols[2].max()):7d}"
+              f" (median {int(np.median(cols[2])):7d})  done {int(cols[3].min()):7d}..{int(cols[3].max()):7d}")
+
+
 def run_sweep(bt, device):
     """BASELINE config 5: per point GB/s of packed weights (HBM-bound points) and int8 TOP/s."""
     import ctypes as C
@@ -283,6 +321,9 @@ def main():
     ap.add_argument("--one-step", action="store_true",
                     help="profiling aid: build the model, --seek to the context, run ONE eager decode step "
                          "(every kernel launched outside a graph) and exit without a JSON line")
+    ap.add_argument("--timeline", action="store_true",
+                    help="profiling aid (batch <= 8): per-launch globaltimer stamps of one graph-replayed step, "
+                         "printed per block; use with --layers 2 --seek")
     ap.add_argument("--linear", type=int, nargs=3, metavar=("N", "K", "M"),
                     help="profiling aid: three bt_linear_forward calls on a random [N, K] weight with M tokens, then exit")
     ap.add_argument("--sweep", action="store_true",
@@ -355,6 +396,11 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.timeline:
+        run_timeline(bt, model, args, B)
+        del model
+        return
 
     if args.one_step:
         model.seek(args.context)

@@ -105,13 +105,19 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int split = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int t0 = split * a.span;
+    // The spans follow the sequence's current length, not the capacity the launch was planned
+    // for: every CTA of a (sequence, KV head) gets an equal share (a multiple of 32 positions) of
+    // what the cache holds now.  The position counter is only written by the last kernel of a
+    // decode step, and steps do not overlap, so it may be read before the dependency wait.
+    int span = (((a.pos[blockIdx.x / a.n_kv] + 1) + a.splits - 1) / a.splits + 31) & ~31;
+    if (span > a.span) span = a.span;
+    const int t0 = split * span;
     const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
     const int row16 = hd / 16;  // 16-byte pieces per row
     // The cache rows of earlier positions were written by earlier steps, so they can be fetched
     // before the dependency wait (whatever sits in rows at or beyond the current position is
     // fetched too and never used; the owner of the new position overwrites its copy below).
-    const int raw_rows = max(0, min(min(kTilePos, a.span), a.cache.max_seq - t0));
+    const int raw_rows = max(0, min(min(kTilePos, span), a.cache.max_seq - t0));
     {
         const uint4* ksrc = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + t0) * hd);
         const uint4* vsrc = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + t0) * hd);
@@ -135,7 +141,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 
     const int p = a.pos[b];
     const int t_len = p + 1;
-    const int t1 = min(t_len, t0 + a.span);
+    const int t1 = min(t_len, t0 + span);
     const int64_t qkv_stride = (int64_t)(a.n_heads + 2 * a.n_kv) * hd;
     const float* qkv = a.qkv + b * qkv_stride;
     double* part_base = a.partial + (((int64_t)b * a.n_heads + kvh * nrep) * a.splits + split) * (hd + 2);

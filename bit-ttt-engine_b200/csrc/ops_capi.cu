@@ -28,7 +28,9 @@ void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* 
     // the positions in 2..4 can fill the last wave better; cost model = waves x (tiles of 128
     // positions per CTA + 1 for the fixed work of a CTA).
     const int64_t pairs = batch * n_kv;
-    int64_t want = ((int64_t)sm_count + pairs - 1) / pairs;
+    // fewer pairs than SMs: as many spans as fit in ONE wave (a CTA takes a whole SM), so that
+    // no span has to wait for another CTA to finish before it can even start
+    int64_t want = (int64_t)sm_count / pairs;
     if (want > 64) want = 64;
     if (want < 1) want = 1;
     if (pairs >= sm_count) {
@@ -41,9 +43,9 @@ void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* 
         }
     }
     int64_t sp = (max_seq + want - 1) / want;
-    sp = (sp + 63) / 64 * 64;
-    *span = (int)sp;
-    *splits = (int)((max_seq + sp - 1) / sp);
+    sp = pairs < sm_count ? (sp + 31) / 32 * 32 : (sp + 63) / 64 * 64;
+    *span = (int)sp;  // upper bound: the kernel cuts the current length, not max_seq, into `splits` spans
+    *splits = pairs < sm_count ? (int)want : (int)((max_seq + sp - 1) / sp);
 }
 
 }  // namespace bt
