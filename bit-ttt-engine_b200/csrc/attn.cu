@@ -49,35 +49,45 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
 }
 
 // One CTA = one (sequence, KV head, span of positions), 512 threads.  The span is walked in
-// tiles of 128 positions that sit in shared memory exactly as the cache stores them (u8 rows +
-// one f32 scale per row); the first tile is fetched before the kernel waits for its
-// predecessor.  Converting to f64 is the expensive instruction here (a fraction of the rate of
-// an f64 FMA), so the work is cut such that every cache element is dequantised and widened by
-// exactly one thread, in registers, and used there for all NREP query heads of the KV group:
-//   (1) scores: warp w owns rows 4w .. 4w + 3 (+64), lane e the dims {2e, 2e + 1} + 64 j; the
-//       lane's partial sums for 4 rows x NREP heads are added across the warp by a butterfly;
-//   (2) softmax weights of the tile, one warp per head (running max / sum across tiles);
-//   (3) P.V: thread (pair of dims, group of rows) accumulates its rows for all NREP heads; the
-//       row groups are added once, after the last tile.
+// tiles of 128 positions that sit in shared memory as the cache stores them (u8 rows + one f32
+// scale per row; rows padded by 32 bytes so that rows 4i .. 4i+3 fall into different banks); the
+// first tile is fetched before the kernel waits for its predecessor.  Both contractions run on
+// the f64 tensor-core path (mma.sync.m8n8k4.f64: 256 multiply-adds per warp instruction, the
+// same peak as the f64 FMA pipe but one issue slot instead of eight and no cross-lane sums):
+//   (1) scores: warp w owns positions 8w .. 8w+7 of the tile (rows of A = dequantised K, widened
+//       to f64 by the lane that feeds it), columns of B = the NREP rotated query heads, k = dims;
+//   (2) softmax weights: one (head, row) per thread; tile maxima and sums through shared memory;
+//   (3) P.V: warp = (32 dims, every n-th group of 4 positions); rows of A = heads (weights),
+//       columns of B = dims (one 32-bit load of V feeds four 8-dim blocks), k = positions; the
+//       position groups are added once, after the last tile.
 // Everything between the u8 loads and the final rounding is f64 on exact f32 values
 // ((f32(q) - 128) * s, dequantize_q8, kv_cache.rs:122-128), so the result does not depend
 // (beyond f64 rounding) on how positions are cut into tiles, groups and spans.
 constexpr int kTilePos = 128;  // = cache rows prefetched per CTA
 constexpr int kMaxRep = 8;
 
+constexpr int kRowPad = 32;                 // bytes added to every cache row in shared memory
+constexpr int kMaxRowBytes = 128 + kRowPad;
+constexpr int kPadD = 132;                  // row length (doubles) of the per-head f64 arrays: rows 8 banks apart
+
 struct AttnSmem {
-    alignas(16) double qd[kMaxRep][128];  // rotated queries (exact f32 values, widened)
-    double pw[kMaxRep][kTilePos];
+    alignas(16) double qd[kMaxRep][kPadD];  // rotated queries (exact f32 values, widened)
+    double pw[kMaxRep][kPadD];              // softmax weights of the tile (0 beyond the tile's rows)
     float sc[kMaxRep][kTilePos];
     double m_run[kMaxRep], l_run[kMaxRep], corr[kMaxRep], m_next[kMaxRep];
     double wmax[kMaxRep][4], wsum[kMaxRep][4];  // per warp (32 rows) maxima and sums of the tile
     float knew[128], vnew[128];
-    // cache rows as stored, two tiles: while one is worked on, the next arrives (cp.async)
-    alignas(16) uint8_t kraw[2][kTilePos * 128];
-    alignas(16) uint8_t vraw[2][kTilePos * 128];
+    // cache rows as stored (padded), two tiles: while one is worked on, the next arrives (cp.async)
+    alignas(16) uint8_t kraw[2][kTilePos * kMaxRowBytes];
+    alignas(16) uint8_t vraw[2][kTilePos * kMaxRowBytes];
     alignas(16) float ksr[2][kTilePos], vsr[2][kTilePos];
-    alignas(16) double red[512 * 2 * kMaxRep];  // [row group][head][dim] partial outputs; scratch of the merge
+    alignas(16) double red[16 * kMaxRep * 32];  // [position group][head][dim] partial outputs; scratch of the merge
 };
+
+// D(8x8, f64) += A(8x4, row) * B(4x8, col): lane (g = lane/4, t = lane%4) holds A[g][t], B[t][g], D[g][2t], D[g][2t+1]
+__device__ __forceinline__ void dmma884(double& d0, double& d1, double a, double b) {
+    asm("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};" : "+d"(d0), "+d"(d1) : "d"(a), "d"(b));
+}
 
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(dst_smem)), "l"(src) : "memory");
@@ -91,6 +101,12 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // 2^23 + b, and subtracting 2^23 + 128 is exact.
 __device__ __forceinline__ double dequant_wide(uint32_t bytes, int which, float s) {
     const uint32_t bits = which == 0 ? __byte_perm(bytes, 0x4B000000u, 0x7540) : __byte_perm(bytes, 0x4B000000u, 0x7541);
+    return (double)__fmul_rn(__fsub_rn(__uint_as_float(bits), 8388736.0f), s);
+}
+
+// the same for byte `which` (0..3) of a 32-bit word
+__device__ __forceinline__ double dequant_byte(uint32_t word, int which, float s) {
+    const uint32_t bits = __byte_perm(word, 0x4B000000u, 0x7540 + which);
     return (double)__fmul_rn(__fsub_rn(__uint_as_float(bits), 8388736.0f), s);
 }
 
@@ -114,6 +130,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     const int t0 = split * span;
     const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
     const int row16 = hd / 16;  // 16-byte pieces per row
+    const int rstride = hd + kRowPad;  // row stride of the tiles in shared memory
     // The cache rows of earlier positions were written by earlier steps, so they can be fetched
     // before the dependency wait (whatever sits in rows at or beyond the current position is
     // fetched too and never used; the owner of the new position overwrites its copy below).
@@ -121,8 +138,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     {
         const uint4* ksrc = reinterpret_cast<const uint4*>(a.cache.k_q + (row_base + t0) * hd);
         const uint4* vsrc = reinterpret_cast<const uint4*>(a.cache.v_q + (row_base + t0) * hd);
-        uint4* kdst = reinterpret_cast<uint4*>(sm.kraw[0]);
-        uint4* vdst = reinterpret_cast<uint4*>(sm.vraw[0]);
         const int n16 = raw_rows * row16;
         for (int i0 = tid; i0 < n16; i0 += 2 * kAttnThreads) {
             const int i1 = i0 + kAttnThreads;
@@ -130,8 +145,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
             const uint4 k0 = ksrc[i0], v0 = vsrc[i0];
             uint4 k1 = make_uint4(0u, 0u, 0u, 0u), v1 = k1;
             if (h1) { k1 = ksrc[i1]; v1 = vsrc[i1]; }
-            kdst[i0] = k0; vdst[i0] = v0;
-            if (h1) { kdst[i1] = k1; vdst[i1] = v1; }
+            const int o0 = (i0 / row16) * rstride + (i0 % row16) * 16;
+            *reinterpret_cast<uint4*>(sm.kraw[0] + o0) = k0;
+            *reinterpret_cast<uint4*>(sm.vraw[0] + o0) = v0;
+            if (h1) {
+                const int o1 = (i1 / row16) * rstride + (i1 % row16) * 16;
+                *reinterpret_cast<uint4*>(sm.kraw[0] + o1) = k1;
+                *reinterpret_cast<uint4*>(sm.vraw[0] + o1) = v1;
+            }
         }
         if (tid < raw_rows) sm.ksr[0][tid] = a.cache.k_s[row_base + t0 + tid];
         else if (tid >= 256 && tid - 256 < raw_rows) sm.vsr[0][tid - 256] = a.cache.v_s[row_base + t0 + tid - 256];
@@ -185,21 +206,26 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     if (owner) {
         const bool in_raw = p - t0 < raw_rows;
         if (warp == 0) quant_row_warp(sm.knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p,
-                                      in_raw ? sm.kraw[0] + (p - t0) * hd : nullptr, in_raw ? sm.ksr[0] + (p - t0) : nullptr, lane);
+                                      in_raw ? sm.kraw[0] + (p - t0) * rstride : nullptr, in_raw ? sm.ksr[0] + (p - t0) : nullptr, lane);
         if (warp == 1) quant_row_warp(sm.vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p,
-                                      in_raw ? sm.vraw[0] + (p - t0) * hd : nullptr, in_raw ? sm.vsr[0] + (p - t0) : nullptr, lane);
+                                      in_raw ? sm.vraw[0] + (p - t0) * rstride : nullptr, in_raw ? sm.vsr[0] + (p - t0) : nullptr, lane);
     }
     __syncthreads();  // the block's own global writes are visible to it after the barrier
     STAMP(2);
 
-    // P.V ownership: thread = (pair of dims dp, row group rg); rows rg, rg + n_rg, ... of each tile
-    const int n_dp = hd >> 1;
-    const int n_rg = kAttnThreads / n_dp < kTilePos ? kAttnThreads / n_dp : kTilePos;
-    const int dp = tid % n_dp, rg = tid / n_dp;
-    const bool pv_active = rg < n_rg;
-    double acc[NREP][2];
+    // fragment coordinates of the f64 MMA: g = row of A / column of B, t = k index
+    const int g = lane >> 2, t = lane & 3;
+    // P.V ownership: warp = (group of 32 dims dg, position group pg); the warp handles the
+    // 4-position groups pg, pg + n_pg, ... of every tile for dims 32 dg .. 32 dg + 31: one
+    // 32-bit load of a V row (dims 32 dg + 4 g .. + 3) feeds four MMAs, MMA e holding dim
+    // 32 dg + 4 n + e in column n.  Lane (g, t) ends with head g, n = 2t and 2t + 1.
+    const int n_dg = hd >> 5;
+    const int n_pg = kAttnWarps / n_dg;
+    const int dg = warp % n_dg, pg = warp / n_dg;
+    const bool pv_active = pg < n_pg;
+    double acc[4][2];
 #pragma unroll
-    for (int h = 0; h < NREP; ++h) acc[h][0] = acc[h][1] = 0.0;
+    for (int e = 0; e < 4; ++e) acc[e][0] = acc[e][1] = 0.0;
 
     int cur = 0;  // buffer holding the current tile
     for (int tb = t0; tb < t1; tb += kTilePos) {
@@ -211,8 +237,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
             const uint8_t* ksrc = a.cache.k_q + (row_base + nb) * hd;
             const uint8_t* vsrc = a.cache.v_q + (row_base + nb) * hd;
             for (int i = tid; i < n_next * row16; i += blockDim.x) {
-                cp_async16(sm.kraw[cur ^ 1] + 16 * i, ksrc + 16 * i);
-                cp_async16(sm.vraw[cur ^ 1] + 16 * i, vsrc + 16 * i);
+                const int o = (i / row16) * rstride + (i % row16) * 16;
+                cp_async16(sm.kraw[cur ^ 1] + o, ksrc + 16 * i);
+                cp_async16(sm.vraw[cur ^ 1] + o, vsrc + 16 * i);
             }
             for (int i = tid; i < n_next; i += blockDim.x) {
                 cp_async4(&sm.ksr[cur ^ 1][i], a.cache.k_s + row_base + nb + i);
@@ -224,56 +251,31 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         const float* ksr = sm.ksr[cur];
         const float* vsr = sm.vsr[cur];
         STAMP(3);
-        // (1) scores.  One read of q serves four rows, one dequantised K element all heads; the
-        //     lane's 4 * NREP partial sums are then added across the warp with a halving
-        //     butterfly (each step sends half of the values and keeps the other half), which
-        //     leaves the sum of value number lane >> kScoreShift in every lane.
-        for (int row0 = 4 * warp; row0 < n_here; row0 += 4 * kAttnWarps) {
-            constexpr int kVals = 4 * NREP;
-            double d[kVals];
+        // (1) scores: S[8 positions x NREP heads] = K[8 x hd] . q[hd x NREP], hd / 4 MMAs per
+        //     group of 8 positions.  Lane (g, t) dequantises dims 4i + t of position row0 + g
+        //     (byte t of every 32-bit word of its row) and supplies q[head g][4i + t].  Rows at or
+        //     beyond n_here hold anything; they only reach their own row of S, which is dropped.
+        for (int row0 = 8 * warp; row0 < n_here; row0 += 8 * kAttnWarps) {
+            const uint8_t* krow = kraw + (row0 + g) * rstride;
+            const float ks = ksr[row0 + g];
+            const double* qrow = sm.qd[g < NREP ? g : 0];
+            double s0 = 0.0, s1 = 0.0, u0 = 0.0, u1 = 0.0;  // two chains: even and odd words
+            for (int j = 0; j < row16; ++j) {
+                const uint4 kw = *reinterpret_cast<const uint4*>(krow + 16 * j);
+                const uint32_t w4[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
-            for (int i = 0; i < kVals; ++i) d[i] = 0.0;
-            for (int c = 2 * lane; c < hd; c += 64) {
-                double2 q2[NREP];
-#pragma unroll
-                for (int h = 0; h < NREP; ++h) q2[h] = *reinterpret_cast<const double2*>(&sm.qd[h][c]);
-#pragma unroll
-                for (int rl = 0; rl < 4; ++rl) {
-                    if (row0 + rl < n_here) {  // rows beyond the current length hold anything
-                        const uint32_t kb = *reinterpret_cast<const uint16_t*>(kraw + (row0 + rl) * hd + c);
-                        const float ks = ksr[row0 + rl];
-                        const double k0 = dequant_wide(kb, 0, ks), k1 = dequant_wide(kb, 1, ks);
-#pragma unroll
-                        for (int h = 0; h < NREP; ++h) {
-                            d[rl * NREP + h] = fma(q2[h].x, k0, d[rl * NREP + h]);
-                            d[rl * NREP + h] = fma(q2[h].y, k1, d[rl * NREP + h]);
-                        }
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    const double kv = dequant_byte(w4[e], t, ks);
+                    const double qv = g < NREP ? qrow[16 * j + 4 * e + t] : 0.0;
+                    if (e & 1) dmma884(u0, u1, kv, qv);
+                    else dmma884(s0, s1, kv, qv);
                 }
             }
-            int n = kVals;
-#pragma unroll
-            for (int msk = 16; msk >= 1; msk >>= 1) {
-                if (n > 1) {
-                    n >>= 1;
-                    const bool upper = (lane & msk) != 0;
-#pragma unroll
-                    for (int i = 0; i < kVals / 2; ++i) {
-                        if (i < n) {
-                            const double keep = upper ? d[n + i] : d[i];
-                            const double send = upper ? d[i] : d[n + i];
-                            d[i] = keep + __shfl_xor_sync(0xffffffffu, send, msk);
-                        }
-                    }
-                } else {
-                    d[0] += __shfl_xor_sync(0xffffffffu, d[0], msk);
-                }
+            s0 += u0; s1 += u1;
+            if (row0 + g < n_here) {
+                if (2 * t < NREP) sm.sc[2 * t][row0 + g] = __fmul_rn((float)s0, a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
+                if (2 * t + 1 < NREP) sm.sc[2 * t + 1][row0 + g] = __fmul_rn((float)s1, a.scaling);
             }
-            constexpr int kScoreShift = NREP == 8 ? 0 : NREP == 4 ? 1 : NREP == 2 ? 2 : 3;
-            const int idx = lane >> kScoreShift;
-            const int rl = idx / NREP, h = idx % NREP;
-            if ((lane & ((1 << kScoreShift) - 1)) == 0 && row0 + rl < n_here)
-                sm.sc[h][row0 + rl] = __fmul_rn((float)d[0], a.scaling);  // (q.k) * 1/sqrt(hd), attention.rs:202
         }
         __syncthreads();
         STAMP(4);
@@ -319,19 +321,22 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
             sm.l_run[tid] = fma(sm.l_run[tid], sm.corr[tid], psum);
             sm.m_run[tid] = sm.m_next[tid];
         }
-        // (3) acc[head][dim pair] = acc * corr + sum over this thread's rows of p[head, r] * v[r, dims]
+        // (3) O[NREP heads x 32 dims] = O * corr + P[heads x positions] . V[positions x dims]
         if (pv_active) {
+            const double cr = g < NREP ? sm.corr[g] : 0.0;
 #pragma unroll
-            for (int h = 0; h < NREP; ++h) { const double cr = sm.corr[h]; acc[h][0] *= cr; acc[h][1] *= cr; }
-            for (int r = rg; r < n_here; r += n_rg) {
-                const uint32_t vb = *reinterpret_cast<const uint16_t*>(vraw + r * hd + 2 * dp);
+            for (int e = 0; e < 4; ++e) { acc[e][0] *= cr; acc[e][1] *= cr; }
+            const double* prow = sm.pw[g < NREP ? g : 0];
+            for (int i = pg; 4 * i < n_here; i += n_pg) {
+                const int r = 4 * i + t;  // this lane's position of the group
+                const bool live = r < n_here;  // rows beyond the tile hold anything: they must not reach the sum
+                const uint32_t vw = *reinterpret_cast<const uint32_t*>(vraw + r * rstride + 32 * dg + 4 * g);
                 const float vs = vsr[r];
-                const double v0 = dequant_wide(vb, 0, vs), v1 = dequant_wide(vb, 1, vs);
+                const double pr = (g < NREP && live) ? prow[r] : 0.0;
 #pragma unroll
-                for (int h = 0; h < NREP; ++h) {
-                    const double pr = sm.pw[h][r];
-                    acc[h][0] = fma(pr, v0, acc[h][0]);
-                    acc[h][1] = fma(pr, v1, acc[h][1]);
+                for (int e = 0; e < 4; ++e) {
+                    const double vv = live ? dequant_byte(vw, e, vs) : 0.0;
+                    dmma884(acc[e][0], acc[e][1], pr, vv);
                 }
             }
         }
@@ -341,19 +346,22 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
             cur ^= 1;
         }
     }
-    // add the row groups (fixed order) through shared memory, one (head, dim) per thread
+    // add the position groups (fixed order) through shared memory, one (head, dim) per thread
     {
-        double* red = sm.red;  // [n_rg][NREP][hd]
-        if (pv_active) {
+        double* red = sm.red;  // [n_pg][NREP][hd]
+        if (pv_active && g < NREP) {
 #pragma unroll
-            for (int h = 0; h < NREP; ++h)
-                *reinterpret_cast<double2*>(red + ((int64_t)rg * NREP + h) * hd + 2 * dp) = make_double2(acc[h][0], acc[h][1]);
+            for (int e = 0; e < 4; ++e) {
+                // MMA e, column n = dim 32 dg + 4 n + e; this lane holds n = 2t and 2t + 1
+                red[((int64_t)pg * NREP + g) * hd + 32 * dg + 4 * (2 * t) + e] = acc[e][0];
+                red[((int64_t)pg * NREP + g) * hd + 32 * dg + 4 * (2 * t + 1) + e] = acc[e][1];
+            }
         }
         __syncthreads();
         for (int it = tid; it < NREP * hd; it += blockDim.x) {
             const int h = it / hd, dcol = it % hd;
             double v = 0.0;
-            for (int g2 = 0; g2 < n_rg; ++g2) v += red[((int64_t)g2 * NREP + h) * hd + dcol];
+            for (int g2 = 0; g2 < n_pg; ++g2) v += red[((int64_t)g2 * NREP + h) * hd + dcol];
             double* dst = part_base + (int64_t)h * a.splits * (hd + 2);
             dst[2 + dcol] = v;
             if (dcol == 0) { dst[0] = sm.m_run[h]; dst[1] = sm.l_run[h]; }
@@ -471,7 +479,7 @@ namespace {
 template <int NREP>
 cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
     // the row-group buffer at the end of the shared-memory block scales with the heads per group
-    constexpr size_t kRedDoubles = 512 * 2 * NREP > 2 * kMaxRep * 64 + kMaxRep ? 512 * 2 * NREP : 2 * kMaxRep * 64 + kMaxRep;
+    constexpr size_t kRedDoubles = 512 * NREP > 2 * kMaxRep * 64 + kMaxRep ? 512 * NREP : 2 * kMaxRep * 64 + kMaxRep;  // [n_pg][NREP][hd], n_pg * hd = 512
     constexpr size_t kSmem = offsetof(AttnSmem, red) + kRedDoubles * sizeof(double);
     constexpr size_t kHalfSm = 116 * 1024;
     static bool configured = false;

@@ -25,6 +25,10 @@ def bt():
 SHAPES = [  # (m, n, k)
     (1, 16, 256), (1, 64, 64), (1, 256, 688), (3, 100, 4), (1, 17, 36), (8, 2048, 2048),
     (2, 688, 256), (1, 4096, 4096), (5, 1024, 4096), (7, 48, 14336), (17, 64, 512), (33, 32, 256),
+    # product kernel for up to 8 tokens: 16 KB ring stages (8 tokens of a long K leave no room for
+    # 32 KB ones), an odd number of row tiles per CTA, and more row tiles per CTA than the ring has
+    # slots and than there are accumulate buffers (slots and buffers are reused)
+    (8, 160, 14336), (1, 7120, 4096), (1, 41000, 512), (3, 41000, 512),
 ]
 
 

@@ -58,10 +58,14 @@ def test_ttt_zero_feature_is_safe(bt):
     assert torch.isfinite(z).all() and torch.isfinite(w).all()
 
 
-@pytest.mark.parametrize("n_heads,n_kv,hd,steps", [(4, 2, 64, 9), (32, 8, 128, 5), (8, 1, 32, 70), (4, 4, 64, 3)])
-def test_attention_decode_matches_oracle(bt, oracle, n_heads, n_kv, hd, steps):
+@pytest.mark.parametrize("n_heads,n_kv,hd,steps,batch,max_seq,every", [
+    (4, 2, 64, 9, 2, 128, 1), (32, 8, 128, 5, 2, 128, 1), (8, 1, 32, 70, 2, 128, 1), (4, 4, 64, 3, 2, 128, 1),
+    # one span per (sequence, KV head) pair (80 pairs: two would not fit in one wave): the span grows past
+    # one and two 128-position tiles, so the tile loop, the next-tile copies and the running maximum are used
+    (16, 8, 128, 290, 10, 320, 41), (8, 8, 64, 150, 10, 160, 29)])
+def test_attention_decode_matches_oracle(bt, oracle, n_heads, n_kv, hd, steps, batch, max_seq, every):
     rng = np.random.default_rng(n_heads * 1000 + hd)
-    batch, theta, max_seq = 2, 10000.0, 128
+    theta = 10000.0
     cache = bt.QuantizedKVCache(max_seq, batch, n_kv, hd)
     hist = [dict(kq=[], ks=[], vq=[], vs=[]) for _ in range(batch)]
     qkv_dim = (n_heads + 2 * n_kv) * hd
@@ -78,6 +82,8 @@ def test_attention_decode_matches_oracle(bt, oracle, n_heads, n_kv, hd, steps):
             h = hist[b]
             h["kq"].append(kq); h["ks"].append(ks); h["vq"].append(vq); h["vs"].append(vs)
             t = p + 1
+            if p % every != 0 and p != steps - 1:
+                continue  # long runs: the oracle checks every few steps and the last one
             kall = np.stack(h["kq"], 1); vall = np.stack(h["vq"], 1)
             ksc = np.stack(h["ks"], 1); vsc = np.stack(h["vs"], 1)
             kd = oracle.kv_dequant(kall.reshape(n_kv * t, hd), ksc.reshape(-1)).reshape(n_kv, t, hd)
