@@ -189,6 +189,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         sm.qd[h][half + c] = (double)__fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
     }
     if (tid < nrep) { sm.m_run[tid] = -INFINITY; sm.l_run[tid] = 0.0; }
+    // The MMA fragments have 8 head rows / columns.  The arrays of heads that do not exist are
+    // zero, so those rows and columns contribute exact zeros without any per-lane condition in the
+    // MMA loops.
+    for (int i = tid; i < (kMaxRep - nrep) * kPadD; i += blockDim.x) {
+        sm.qd[nrep + i / kPadD][i % kPadD] = 0.0;
+        sm.pw[nrep + i / kPadD][i % kPadD] = 0.0;
+    }
+    if (tid >= nrep && tid < kMaxRep) sm.corr[tid] = 0.0;
     // the CTA whose span holds position p appends the new key / value first
     const bool owner = (p >= t0 && p < t1);
     if (owner) {
@@ -251,6 +259,17 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         const float* ksr = sm.ksr[cur];
         const float* vsr = sm.vsr[cur];
         STAMP(3);
+        // Rows at or beyond n_here hold anything.  P.V walks whole 4-position groups, so the (at most
+        // three) rows that complete the last group are cleared: value bytes 128 (= 0), scale 0, and
+        // their softmax weights are 0 as well.  (Read after the barriers that follow the scores.)
+        {
+            const int r_end = (n_here + 3) & ~3;
+            for (int i = tid; i < (r_end - n_here) * (hd >> 2); i += blockDim.x) {
+                const int r = n_here + i / (hd >> 2);
+                *reinterpret_cast<uint32_t*>(sm.vraw[cur] + r * rstride + 4 * (i % (hd >> 2))) = 0x80808080u;
+            }
+            if (tid >= n_here && tid < r_end) sm.vsr[cur][tid] = 0.0f;
+        }
         // (1) scores: S[8 positions x NREP heads] = K[8 x hd] . q[hd x NREP], hd / 4 MMAs per
         //     group of 8 positions.  Lane (g, t) dequantises dims 4i + t of position row0 + g
         //     (byte t of every 32-bit word of its row) and supplies q[head g][4i + t].  Rows at or
@@ -258,7 +277,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         for (int row0 = 8 * warp; row0 < n_here; row0 += 8 * kAttnWarps) {
             const uint8_t* krow = kraw + (row0 + g) * rstride;
             const float ks = ksr[row0 + g];
-            const double* qrow = sm.qd[g < NREP ? g : 0];
+            const double* qrow = sm.qd[g];
             double s0 = 0.0, s1 = 0.0, u0 = 0.0, u1 = 0.0;  // two chains: even and odd words
             for (int j = 0; j < row16; ++j) {
                 const uint4 kw = *reinterpret_cast<const uint4*>(krow + 16 * j);
@@ -266,7 +285,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const double kv = dequant_byte(w4[e], t, ks);
-                    const double qv = g < NREP ? qrow[16 * j + 4 * e + t] : 0.0;
+                    const double qv = qrow[16 * j + 4 * e + t];
                     if (e & 1) dmma884(u0, u1, kv, qv);
                     else dmma884(s0, s1, kv, qv);
                 }
@@ -323,21 +342,18 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         }
         // (3) O[NREP heads x 32 dims] = O * corr + P[heads x positions] . V[positions x dims]
         if (pv_active) {
-            const double cr = g < NREP ? sm.corr[g] : 0.0;
+            const double cr = sm.corr[g];
 #pragma unroll
             for (int e = 0; e < 4; ++e) { acc[e][0] *= cr; acc[e][1] *= cr; }
-            const double* prow = sm.pw[g < NREP ? g : 0];
+            const double* prow = sm.pw[g];
+#pragma unroll 4
             for (int i = pg; 4 * i < n_here; i += n_pg) {
                 const int r = 4 * i + t;  // this lane's position of the group
-                const bool live = r < n_here;  // rows beyond the tile hold anything: they must not reach the sum
                 const uint32_t vw = *reinterpret_cast<const uint32_t*>(vraw + r * rstride + 32 * dg + 4 * g);
                 const float vs = vsr[r];
-                const double pr = (g < NREP && live) ? prow[r] : 0.0;
+                const double pr = prow[r];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const double vv = live ? dequant_byte(vw, e, vs) : 0.0;
-                    dmma884(acc[e][0], acc[e][1], pr, vv);
-                }
+                for (int e = 0; e < 4; ++e) dmma884(acc[e][0], acc[e][1], pr, dequant_byte(vw, e, vs));
             }
         }
         if (tb + kTilePos < t1) {
