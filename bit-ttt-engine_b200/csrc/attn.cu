@@ -391,14 +391,20 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 
     // The last CTA of this (sequence, KV head) to get here merges the spans:
     // out = sum_s e^{m_s - m} acc_s / sum_s e^{m_s - m} l_s, rounded to f32 once.
-    __threadfence();
+    // Release / acquire by one thread around the ticket: the barrier orders every thread's stores
+    // of the partial result before thread 0's fence (fences are cumulative), and for the last
+    // arrival thread 0's second fence orders the ticket before the loads that follow the barrier
+    // (which read through L2).
     __syncthreads();
     __shared__ unsigned int arrived;
-    if (tid == 0) arrived = atomicAdd(a.counters + blockIdx.x, 1u);
+    if (tid == 0) {
+        __threadfence();
+        arrived = atomicAdd(a.counters + blockIdx.x, 1u);
+        __threadfence();
+    }
     __syncthreads();
     STAMP(7);
     if (arrived != (unsigned int)a.splits - 1) return;
-    __threadfence();
     if (tid == 0) a.counters[blockIdx.x] = 0;  // ready for the next launch
     const double* group = a.partial + ((int64_t)b * a.n_heads + kvh * nrep) * a.splits * (hd + 2);
     // One batch of independent loads: every span's maximum and sum into shared memory and, at
@@ -408,7 +414,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     constexpr int kMergeBatch = kItems == 1 ? 32 : 16;          // spans whose values are fetched up front
     double* mw = sm.red;          // [nrep][64] maxima, then weights (the tile buffers are free now)
     double* ls = mw + kMaxRep * 64;                          // [nrep][64] sums
-    double* lsum = ls + kMaxRep * 64;                        // [nrep] merged denominators
+    double* lsum = ls + kMaxRep * 64;                        // [nrep] reciprocals of the merged denominators
     for (int i = tid; i < nrep * a.splits; i += blockDim.x) {
         const int h = i / a.splits, s2 = i % a.splits;
         const double* src = group + ((int64_t)h * a.splits + s2) * (hd + 2);
@@ -444,7 +450,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        if (lane == 0) lsum[h] = l;
+        if (lane == 0) lsum[h] = 1.0 / l;  // one division per head; the outputs multiply
     }
     __syncthreads();
 #pragma unroll
@@ -465,7 +471,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
                 if (s2 + 1 < a.splits && mw[h * 64 + s2 + 1] != 0.0)
                     v1 = fma(__ldcg(base + (int64_t)(s2 + 1) * (hd + 2)), mw[h * 64 + s2 + 1], v1);
             }
-            const float o = (float)((v0 + v1) / lsum[h]);
+            const float o = (float)((v0 + v1) * lsum[h]);
             a.out[((int64_t)b * a.n_heads + kvh * nrep + h) * hd + c] = o;
             if (a.absmax_out) {
                 float mx = fabsf(o);
