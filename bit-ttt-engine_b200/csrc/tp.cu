@@ -84,7 +84,8 @@ constexpr unsigned kErrTpTimeout = 0x54505754u;  // 'TPWT'
 // Inbox layout (identical on every rank): for slot s in {0, 1} and source rank r
 //   acc  [s][r][max_batch * hidden] int32
 //   amax [s][r][max_batch] u32 (rows padded to 16 entries)
-//   flag [s][kind][r] u64 epochs (kind 0: amax published, kind 1: acc published)
+//   flag [s][kind][r] u64 epochs (kind 0: amax published)
+//   cflag [s][r][cta] u64 epochs: CTA `cta` of rank r's sum kernel has pushed its slice of acc
 struct TpLayout {
     int size, max_batch, hidden;
     __host__ __device__ size_t acc_elems() const { return (size_t)max_batch * hidden; }
@@ -93,7 +94,10 @@ struct TpLayout {
     __host__ __device__ size_t amax_off(int s, int r) const { return amax_base() + (size_t)(s * size + r) * 16 * 4; }
     __host__ __device__ size_t flag_base() const { return amax_base() + (size_t)2 * size * 16 * 4; }
     __host__ __device__ size_t flag_off(int s, int kind, int r) const { return flag_base() + (size_t)((s * 2 + kind) * size + r) * 8; }
-    __host__ __device__ size_t bytes() const { return flag_base() + (size_t)2 * 2 * size * 8; }
+    // per-CTA epochs of the sum exchange: [s][r][16 CTAs]
+    __host__ __device__ size_t cflag_base() const { return flag_base() + (size_t)2 * 2 * size * 8; }
+    __host__ __device__ size_t cflag_off(int s, int r, int cta) const { return cflag_base() + (size_t)((s * size + r) * 16 + cta) * 8; }
+    __host__ __device__ size_t bytes() const { return cflag_base() + (size_t)2 * size * 16 * 8; }
 };
 
 struct TpView {
@@ -125,6 +129,8 @@ __device__ __forceinline__ bool wait_sources(const TpView& v, int slot, int kind
 __global__ void __launch_bounds__(256) tp_max_exchange_kernel(TpView v, int slot, unsigned int* amax_cell, int batch) {
     __shared__ int ok_s;
     const int tid = threadIdx.x, R = v.lay.size;
+    ptx::pdl_wait();               // the cells belong to the kernel before this one until here
+    ptx::pdl_launch_dependents();  // the product that follows may start fetching its weights during the exchange
     const unsigned long long e = v.epoch[slot] + 1;
     if (tid == 0) ok_s = 1;
     for (int i = tid; i < batch * R; i += blockDim.x) {
@@ -156,8 +162,9 @@ __global__ void __launch_bounds__(256) tp_sum_residual_kernel(TpView v, int slot
                                                               const unsigned int* __restrict__ amax_cell, float sw,
                                                               int batch, int n, float* __restrict__ h) {
     __shared__ int ok_s;
-    __shared__ unsigned int last_s;
     const int tid = threadIdx.x, R = v.lay.size;
+    ptx::pdl_wait();               // acc and the epoch belong to earlier kernels until here
+    ptx::pdl_launch_dependents();
     const unsigned long long e = v.epoch[slot];  // set by the max exchange just before
     const int total4 = batch * n / 4;            // n is a multiple of 16
     const int per_cta = (total4 + gridDim.x - 1) / gridDim.x;
@@ -167,17 +174,18 @@ __global__ void __launch_bounds__(256) tp_sum_residual_kernel(TpView v, int slot
         const int4 val = reinterpret_cast<const int4*>(acc)[i];
         for (int p = 0; p < R; ++p) reinterpret_cast<int4*>(v.inbox[p] + v.lay.acc_off(slot, v.rank))[i] = val;
     }
-    __threadfence_system();
+    // CTA c of every rank owns the same slice: it publishes its own epoch cell at every peer and
+    // waits for the peers' cells of the same slice.  The barrier orders the CTA's pushes before the
+    // fence of the publishing threads (fences are cumulative).
     __syncthreads();
-    if (tid == 0) last_s = atomicAdd(v.done + slot, 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (last_s) {
-        // every CTA of this rank has pushed (and fenced): publish the epoch to all ranks
-        if (tid == 0) v.done[slot] = 0;
+    if (tid < R) {
         __threadfence_system();
-        if (tid < R) st_release_sys(reinterpret_cast<unsigned long long*>(v.inbox[tid] + v.lay.flag_off(slot, 1, v.rank)), e);
+        st_release_sys(reinterpret_cast<unsigned long long*>(v.inbox[tid] + v.lay.cflag_off(slot, v.rank, blockIdx.x)), e);
+        const unsigned long long* f = reinterpret_cast<const unsigned long long*>(v.inbox[v.rank] + v.lay.cflag_off(slot, tid, blockIdx.x));
+        bool got = false;
+        for (unsigned it = 0; it < (1u << 21) && !got; ++it) got = ld_acquire_sys(f) >= e;
+        if (!got) ok_s = 0;
     }
-    if (tid < R && !wait_sources(v, slot, 1, e, tid)) ok_s = 0;
     __syncthreads();
     for (int i = i0 + tid; i < i1; i += blockDim.x) {
         int4 sum = make_int4(0, 0, 0, 0);
@@ -320,8 +328,7 @@ void tp_peer_destroy(void* peer) {
 
 cudaError_t launch_tp_peer_max(void* peer, int slot, unsigned int* amax_cell, int batch, cudaStream_t s) {
     TpPeer* p = reinterpret_cast<TpPeer*>(peer);
-    tp_max_exchange_kernel<<<1, 256, 0, s>>>(p->view, slot, amax_cell, batch);
-    return cudaGetLastError();
+    return launch_pdl(tp_max_exchange_kernel, dim3(1), dim3(256), 0, s, true, p->view, slot, amax_cell, batch);
 }
 
 cudaError_t launch_tp_peer_sum_residual(void* peer, int slot, const int32_t* acc, const unsigned int* amax_cell, float sw,
@@ -330,8 +337,7 @@ cudaError_t launch_tp_peer_sum_residual(void* peer, int slot, const int32_t* acc
     const int total4 = batch * n / 4;
     int grid = (total4 + 1023) / 1024;
     grid = grid < 1 ? 1 : (grid > 16 ? 16 : grid);
-    tp_sum_residual_kernel<<<grid, 256, 0, s>>>(p->view, slot, acc, amax_cell, sw, batch, n, h);
-    return cudaGetLastError();
+    return launch_pdl(tp_sum_residual_kernel, dim3(grid), dim3(256), 0, s, true, p->view, slot, acc, amax_cell, sw, batch, n, h);
 }
 
 cudaError_t launch_tp_residual(const int32_t* acc, const unsigned int* absmax, float sw, int m, int n, float* h,
