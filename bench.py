@@ -490,7 +490,7 @@ def main():
                 "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                 # dram__bytes_read+write per launch, average over the four projections of a block, from the
                 # ncu capture summarised in profiles/gemv_kernel_decode_layer_8b.md (batch 1, one GPU)
-                "traffic": 13.73e6 if (B == 1 and world == 1) else None,
+                "traffic": 13.75e6 if (B == 1 and world == 1) else None,
                 "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
                 "launches_per_step": n_launch}
 

@@ -17,11 +17,6 @@ namespace {
 constexpr int kAttnWarps = 16;
 constexpr int kAttnThreads = kAttnWarps * 32;
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -97,14 +92,8 @@ __device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// (f32(byte) - 128) * s without an integer-to-float conversion: 0x4B0000bb is the float
-// 2^23 + b, and subtracting 2^23 + 128 is exact.
-__device__ __forceinline__ double dequant_wide(uint32_t bytes, int which, float s) {
-    const uint32_t bits = which == 0 ? __byte_perm(bytes, 0x4B000000u, 0x7540) : __byte_perm(bytes, 0x4B000000u, 0x7541);
-    return (double)__fmul_rn(__fsub_rn(__uint_as_float(bits), 8388736.0f), s);
-}
-
-// the same for byte `which` (0..3) of a 32-bit word
+// (f32(byte) - 128) * s without an integer-to-float conversion, for byte `which` (0..3) of a
+// 32-bit word: 0x4B0000bb is the float 2^23 + b, and subtracting 2^23 + 128 is exact.
 __device__ __forceinline__ double dequant_byte(uint32_t word, int which, float s) {
     const uint32_t bits = __byte_perm(word, 0x4B000000u, 0x7540 + which);
     return (double)__fmul_rn(__fsub_rn(__uint_as_float(bits), 8388736.0f), s);

@@ -97,17 +97,6 @@ __device__ __forceinline__ float math_max_f(float v, float* slot, int warp, int 
     for (int w = 0; w < kMathWarps; ++w) r = fmaxf(r, slot[w]);
     return r;
 }
-__device__ __forceinline__ int math_sum_i(int v, int* slot, int warp, int lane) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) slot[warp] = v;
-    ptx::named_bar_sync(1, kMathThreads);
-    int r = 0;
-#pragma unroll
-    for (int w = 0; w < kMathWarps; ++w) r += slot[w];
-    return r;
-}
-
 // Quantise 16 consecutive values (group j of a token) with multiplier inv = 127/max|x|, store them
 // byte-transposed at their place in the activation image, return their sum.
 __device__ __forceinline__ int quant_store_group(const float (&v)[16], float inv, uint8_t* dst_token, int j) {
@@ -584,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // activation image complete, epilogue warps may read the scales
     if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 2] = ptx::globaltimer();
 
-    int acc[4][4];  // written by the first tile of every row tile
+    int acc[4][4] = {};  // rewritten by the first tile of every row tile
     // lanes whose MMA column has no token read the last token's row instead: their columns are
     // never stored, and the loads need no predicate
     const uint8_t* my_acts = acts + (size_t)(g < a.m ? g : a.m - 1) * act_stride + t * 16;
