@@ -156,6 +156,10 @@ cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m,
                                  int64_t out_stride, int epilogue, unsigned int* absmax_out,
                                  unsigned int* err, int sm_count, cudaStream_t stream);
 
+cudaError_t linear_product_q(const LinearDev& lin, const int8_t* q, int64_t q_stride, const int32_t* qsum,
+                             const float* sx, int m, void* out, int64_t out_stride, int epilogue,
+                             unsigned int* absmax_out, unsigned int* err, int sm_count, cudaStream_t stream);
+
 // Tensor-core (tcgen05) product for more than 8 tokens: quantises x [m, k_in] f32 into the
 // residue-split layout `qtc` (gemm_tc_act_bytes(m, k_tiles) bytes), then runs the product of
 // every basis.  sx / qsum: [m] scratch for the per-token scale and sum.

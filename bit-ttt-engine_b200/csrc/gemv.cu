@@ -781,6 +781,34 @@ cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stri
     return cudaSuccess;
 }
 
+// The product on activations that a quantiser kernel has already written (int8 rows, sums and
+// scales in global memory), with the epilogues of the fused decode step.
+cudaError_t linear_product_q(const LinearDev& lin, const int8_t* q, int64_t q_stride, const int32_t* qsum,
+                             const float* sx, int m, void* out, int64_t out_stride, int epilogue,
+                             unsigned int* absmax_out, unsigned int* err, int sm_count, cudaStream_t stream) {
+    if (lin.w.n_bases != 1 || m < 1 || m > 8) return cudaErrorInvalidValue;
+    GemvArgs a = {};
+    a.tiles = lin.w.tiles;
+    a.row_tiles = lin.w.row_tiles;
+    a.k_tiles = lin.w.k_tiles;
+    a.n_out = lin.w.n_out;
+    a.k_in = lin.w.k_in;
+    a.prologue = PRO_Q8;
+    a.q = q;
+    a.q_stride = q_stride;
+    a.qsum = qsum;
+    a.sx = sx;
+    a.absmax_out = absmax_out;
+    a.sw_tiles = lin.scale_tiles;
+    a.m = m;
+    a.out = out;
+    a.out_stride = out_stride;
+    a.epilogue = epilogue;
+    a.err = err;
+    a.pdl = true;
+    return launch_gemv(a, sm_count, stream);
+}
+
 unsigned long long* g_dbg_base = nullptr;
 int g_dbg_slot = 0;
 

@@ -108,6 +108,7 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
     __shared__ double red_d[32];
     __shared__ int red_i[32];
     ptx::pdl_wait();
+    ptx::pdl_launch_dependents();  // a product launched behind this kernel may fetch its weights meanwhile
     const int b = blockIdx.x;
     const float* xr = x + (int64_t)b * x_stride;
     float amax = 0.0f;

@@ -136,12 +136,28 @@ bt_status make_linear(bt_model* m, HostLinear** parts, int n_parts, bt_linear** 
 // kernels and every launch allowed to start early (programmatic dependent launch):
 // per block  [norm1+quant+q|k|v]  [attention]  [combine]  [quant+o_proj+residual]
 //            [norm2+quant+gate|up+SiLU*up]  [quant+down+residual].
+// Three to eight sequences: the fused product would repeat its per-CTA quantisation prologue for
+// every token in every CTA (3 us per token for the 14336 inputs of down_proj), so the rows are
+// quantised once by a kernel of their own (one CTA per row) and the product reads them.
+constexpr int kSplitQuantBatch = 3;
+bt_status quant_then_product(bt_model* m, bt_linear* lin, int pre, const float* x, int64_t x_stride, const float* w,
+                             int k, int batch, void* out, int64_t out_stride, int epilogue, unsigned int* absmax_out,
+                             unsigned int* err, cudaStream_t s) {
+    const int64_t qs = ((int64_t)k + kTileK - 1) / kTileK * kTileK;
+    BT_CUDA_TRY(launch_row_quant(pre, x, x_stride, w, kRmsEps, batch, k, m->q, qs, m->sx, m->qsum, nullptr, s));
+    BT_CUDA_TRY(linear_product_q(lin->dev(), m->q, qs, m->qsum, m->sx, batch, out, out_stride, epilogue, absmax_out, err,
+                                 m->sm_count, s));
+    return BT_OK;
+}
+
 bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
     const bt_model_config& c = m->cfg;
     const int H = c.hidden_dim, I = m->i_l, B = c.max_batch;
     const int att_dim = m->nh_l * m->head_dim;  // this rank's attention output width
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
+    const bool split_quant = m->tp == 1 && c.arch == 1 && batch >= kSplitQuantBatch;
+    bt_status qst;
     BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, true));
     for (int li = 0; li < c.num_layers; ++li) {
         Layer& L = m->layers[(size_t)li];
@@ -154,7 +170,11 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             FusedIn zin{PRO_ABSMAX, m->z, m->d_small, nullptr, 0.f, amax_core};
             BT_CUDA_TRY(linear_product_fused(L.ttt_up->dev(), zin, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
         } else {
-            BT_CUDA_TRY(linear_product_fused(L.qkv->dev(), norm1, batch, m->qkv, m->qkv_dim, EPI_F32, nullptr, err, sm, s));
+            if (split_quant) {
+                if ((qst = quant_then_product(m, L.qkv, PRE_RMSNORM, m->h, H, L.norm1, H, batch, m->qkv, m->qkv_dim, EPI_F32, nullptr, err, s)) != BT_OK) return qst;
+            } else {
+                BT_CUDA_TRY(linear_product_fused(L.qkv->dev(), norm1, batch, m->qkv, m->qkv_dim, EPI_F32, nullptr, err, sm, s));
+            }
             AttnArgs a;
             a.qkv = m->qkv;
             a.cache = L.kv->view;
@@ -186,12 +206,18 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
                 BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
                 if ((st = tp_allreduce_sum_i32(m->comm, m->acc_i32, (size_t)batch * H, s)) != BT_OK) return st;
                 BT_CUDA_TRY(launch_tp_residual(m->acc_i32, amax_core, L.o->scales[0], batch, H, m->h, s, true));
+            } else if (split_quant) {
+                if ((qst = quant_then_product(m, L.o, PRE_NONE, m->att, att_dim, nullptr, att_dim, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, s)) != BT_OK) return qst;
             } else {
                 BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
             }
         }
         FusedIn norm2{PRO_RMSNORM, m->h, H, L.norm2, kRmsEps, nullptr};
-        BT_CUDA_TRY(linear_product_fused(L.gate_up_il->dev(), norm2, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, sm, s));
+        if (split_quant) {
+            if ((qst = quant_then_product(m, L.gate_up_il, PRE_RMSNORM, m->h, H, L.norm2, H, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, s)) != BT_OK) return qst;
+        } else {
+            BT_CUDA_TRY(linear_product_fused(L.gate_up_il->dev(), norm2, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, sm, s));
+        }
         FusedIn din{PRO_ABSMAX, m->act, I, nullptr, 0.f, amax_mlp};
         if (m->tp > 1 && tp_peer_ready(m->peer)) {
             BT_CUDA_TRY(launch_tp_peer_max(m->peer, 1, amax_mlp, batch, s));
@@ -203,6 +229,8 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
             if ((st = tp_allreduce_sum_i32(m->comm, m->acc_i32, (size_t)batch * H, s)) != BT_OK) return st;
             BT_CUDA_TRY(launch_tp_residual(m->acc_i32, amax_mlp, L.down->scales[0], batch, H, m->h, s, true));
+        } else if (split_quant) {
+            if ((qst = quant_then_product(m, L.down, PRE_NONE, m->act, I, nullptr, I, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, s)) != BT_OK) return qst;
         } else {
             BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
         }
@@ -632,7 +660,8 @@ extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
     if (!m) return 0;
     if (batch <= 8) {
         // fused path: per layer 4 products + attention pair or TTT update; embedding, lm_head per 4 tokens, pick
-        const int per_layer = 4 + 1 + (m->tp > 1 ? 2 : 0);  // 4 products + attention or TTT update (+ 2 scale epilogues after the all-reduces)
+        int per_layer = 4 + 1 + (m->tp > 1 ? 2 : 0);  // 4 products + attention or TTT update (+ 2 scale epilogues after the all-reduces)
+        if (m->tp == 1 && m->cfg.arch == 1 && batch >= kSplitQuantBatch) per_layer += 4;  // a quantiser kernel in front of every product
         return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
     }
     // batches above 8: per layer 3 row kernels (norm1, norm2, SiLU*up, quantiser included), the quantiser of the

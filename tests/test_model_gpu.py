@@ -71,6 +71,18 @@ def test_tiny_llama_model_teacher_forced_batch2(bt, oracle):
     assert bt.lib().bt_device_check(0) == 0
 
 
+@pytest.mark.parametrize("batch", [3, 5, 8])
+def test_tiny_llama_model_teacher_forced_batch_3_to_8(bt, oracle, batch):
+    # three to eight sequences: a quantiser kernel in front of every product instead of the fused prologue
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    cfg = syn.TINY_LLAMA_TEST
+    gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 6, 3300 + batch, batch=batch)
+    kq, ks, vq, vs = gpu.kv_cache(1).export(batch - 1, 6)
+    ref_k = np.stack(states[batch - 1].kq[1], 1)
+    assert np.abs(kq.astype(np.int32) - ref_k.astype(np.int32)).max() <= 1
+    assert bt.lib().bt_device_check(0) == 0
+
+
 def test_position_limit(bt):
     syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
     cfg = syn.BitLlamaConfig("llama", 64, 64, 1, 2, 1, 64, max_position_embeddings=3)
