@@ -65,7 +65,7 @@ def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
     bt = importlib.import_module("bit-ttt-engine_b200")
     syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
     from oracle import oracle as orc
-    cfg = syn.BitLlamaConfig("llama", 1000, 256, 2, 8, 4, 512, max_position_embeddings=64)
+    cfg = syn.BitLlamaConfig("llama", 1000, 256, 2, 8, max(4, world), 512, max_position_embeddings=64)  # KV heads: 4, or one per rank
     w = syn.make_weights(cfg, seed=3000)
     model = syn.build_model(w, max_batch=2, device=rank, tp_rank=rank, tp_size=world)
     if use_peer:
