@@ -660,7 +660,9 @@ extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
     if (!m) return 0;
     if (batch <= 8) {
         // fused path: per layer 4 products + attention pair or TTT update; embedding, lm_head per 4 tokens, pick
-        int per_layer = 4 + 1 + (m->tp > 1 ? 2 : 0);  // 4 products + attention or TTT update (+ 2 scale epilogues after the all-reduces)
+        // 4 products + attention or TTT update; tensor parallel: + 2 scale epilogues after the NCCL all-reduces, or
+        // + 2 max-exchange and 2 sum-exchange kernels over peer memory
+        int per_layer = 4 + 1 + (m->tp > 1 ? (tp_peer_ready(m->peer) ? 4 : 2) : 0);
         if (m->tp == 1 && m->cfg.arch == 1 && batch >= kSplitQuantBatch) per_layer += 4;  // a quantiser kernel in front of every product
         return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
     }
