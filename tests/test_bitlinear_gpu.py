@@ -29,6 +29,8 @@ SHAPES = [  # (m, n, k)
     # 32 KB ones), an odd number of row tiles per CTA, and more row tiles per CTA than the ring has
     # slots and than there are accumulate buffers (slots and buffers are reused)
     (8, 160, 14336), (1, 7120, 4096), (1, 41000, 512), (3, 41000, 512),
+    # one rank's slices of the 8B projections under 8-way tensor parallelism
+    (1, 4096, 512), (1, 4096, 1792), (1, 768, 4096), (2, 3584, 4096),
 ]
 
 
