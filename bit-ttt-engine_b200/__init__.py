@@ -53,6 +53,7 @@ def lib() -> C.CDLL:
     L.bt_device_check.argtypes = [i32]
     L.bt_pack_ternary.argtypes = [vp, i64, vp, C.POINTER(f32)]
     L.bt_unpack_ternary.argtypes = [vp, i64, f32, vp]
+    L.bt_convert_l3_to_l2.argtypes = [vp, i64, i64, i32, vp]
     L.bt_linear_create.argtypes = [C.POINTER(vp), vp, i64, i64, i32, vp, i32]
     L.bt_linear_destroy.argtypes = [vp]
     L.bt_linear_dims.argtypes = [vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)]

@@ -123,9 +123,11 @@ struct GemvArgs {
     int epilogue;
     unsigned int* err;
     bool pdl;               // launch with programmatic stream serialisation
-    unsigned long long* dbg; // optional timeline slot: [grid][4] globaltimer stamps (development aid)
 };
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream);
+// Largest token count (<= 8) one launch can take for this many 256-input tiles per row; 0 = the layer's rows are
+// too long for the kernel's shared memory even with one token.
+int gemv_max_tokens(int64_t k_tiles);
 
 // A BitLinear as the kernels see it: tiles of every basis plus one weight scale per
 // (basis, row tile) - fused projections (q|k|v, gate|up) carry a different scale per
@@ -160,7 +162,7 @@ cudaError_t linear_product_q(const LinearDev& lin, const int8_t* q, int64_t q_st
                              const float* sx, int m, void* out, int64_t out_stride, int epilogue,
                              unsigned int* absmax_out, unsigned int* err, int sm_count, cudaStream_t stream);
 
-// Tensor-core (tcgen05) product for more than 8 tokens: quantises x [m, k_in] f32 into the
+// Tensor-core (tcgen05) product for more than 8 tokens: quantises x [m, k_in] (f32 or bf16) into the
 // residue-split layout `qtc` (gemm_tc_act_bytes(m, k_tiles) bytes), then runs the product of
 // every basis.  sx / qsum: [m] scratch for the per-token scale and sum.
 size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles);
@@ -176,10 +178,11 @@ __host__ __device__ inline int64_t gemm_tc_act_offset(int c, int tin, int nt) {
 size_t gemm_tc_part_bytes(int sm_count);
 // kernels one launch_gemm_tc call runs for the products themselves (with scratch given)
 int gemm_tc_kernels(const LinearDev& lin, int64_t m, int sm_count);
-cudaError_t launch_gemm_tc(const LinearDev& lin, const float* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
+cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
                            int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
                            cudaStream_t stream, int32_t* part = nullptr, size_t part_bytes = 0,
-                           bool prequantised = false);  // prequantised: qtc / sx / qsum are already filled (x unused)
+                           bool prequantised = false,     // qtc / sx / qsum are already filled (x unused)
+                           bt_dtype x_dtype = BT_F32);    // element type of x: BT_F32 or BT_BF16
 
 // Launch with the programmatic-stream-serialisation attribute: the kernel may start while
 // its predecessor in the stream is still running and must call griddepcontrol.wait before

@@ -35,9 +35,6 @@ struct bt_kv_cache {
     double inv_freq_theta = 0.0;
     float* rope_cos = nullptr;   // device [max_seq, head_dim/2] for inv_freq_theta
     float* rope_sin = nullptr;
-    unsigned int* counters = nullptr;  // device [batch * n_kv] arrival counters of the attention kernel
-    double* partial = nullptr;   // split-KV scratch
-    int64_t partial_floats = 0;
     int max_heads = 0;
 };
 
@@ -63,6 +60,8 @@ bt_status tp_peer_create(void** out, int rank, int size, int max_batch, int hidd
 bt_status tp_peer_export(void* peer, void* handle64_out);
 bt_status tp_peer_import(void* peer, const void* handles /* [size][64] */);
 bool tp_peer_ready(const void* peer);
+void tp_peer_set_wait(void* peer, unsigned long long ns);
+cudaError_t tp_peer_reset(void* peer);
 void tp_peer_destroy(void* peer);
 cudaError_t launch_tp_peer_max(void* peer, int slot, unsigned int* amax_cell, int batch, cudaStream_t s);
 cudaError_t launch_tp_peer_sum_residual(void* peer, int slot, const int32_t* acc, const unsigned int* amax_cell, float sw,

@@ -64,19 +64,23 @@ struct AttnArgs {
     const int32_t* pos;      // [batch] position of the new token
     const float* rope_cos;   // [max_seq, head_dim/2] f32 tables (RotaryEmbedding::new, attention.rs:15-41)
     const float* rope_sin;
-    unsigned int* counters;  // [batch * n_kv] zero-initialised arrival counters (self-resetting)
     float* out;              // [batch, n_heads*head_dim]
-    double* partial;         // scratch [batch, n_heads, splits, head_dim + 2] (max, sum, acc)
     int batch, n_heads, n_kv, head_dim;
     int sm_count;            // SMs of the device
-    int splits;              // spans per sequence (grid.y)
+    int splits;              // spans per sequence (grid.y) = CTAs of one thread-block cluster
     int span;                // positions per span, multiple of 32
     float scaling;
     unsigned int* absmax_out;  // optional [batch]: running max|out| (bits) via atomicMax
     bool pdl;                  // launch with programmatic stream serialisation
-    unsigned long long* dbg;   // optional: 16 globaltimer stamps of CTA (0,0) (development aid)
 };
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
+// Spans per (sequence, KV head) and positions per span for a cache of max_seq positions; rep = query
+// heads per KV head (selects the kernel instance whose cluster limit applies).
+void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int rep, int* splits, int* span);
+// QuantizedKVCache::append for one token per sequence: k, v [batch, n_kv, head_dim] f32 (already rotated)
+// are quantised into row pos[b] of the cache.
+cudaError_t launch_kv_append(const KvCacheView& cache, const float* k, const float* v, const int32_t* pos, int batch,
+                             int n_kv, int hd, cudaStream_t stream);
 // cos/sin tables for positions 0..max_seq-1: freq = f32(pos) * inv_freq (f32 product), cos/sin
 // evaluated in f64 and rounded to f32.
 cudaError_t launch_rope_tables(const float* inv_freq, int max_seq, int half, float* cos_t, float* sin_t,

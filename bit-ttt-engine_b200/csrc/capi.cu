@@ -148,6 +148,9 @@ extern "C" bt_status bt_linear_create(bt_linear** out, const uint8_t* packed_hos
     if (k_in % 4 != 0)
         return set_error(BT_ERR_ALIGN, "bt_linear_create: in_features %lld is not a multiple of 4", (long long)k_in);
     if (n_bases < 1 || n_bases > 8) return set_error(BT_ERR_ARG, "bt_linear_create: n_bases %d outside 1..8", n_bases);
+    if (gemv_max_tokens((k_in + kTileK - 1) / kTileK) < 1)
+        return set_error(BT_ERR_SHAPE, "bt_linear_create: in_features %lld exceeds what one CTA's shared memory holds "
+                                       "(about 180000)", (long long)k_in);
     if (bt_device_count() <= device || device < 0)
         return set_error(BT_ERR_DEVICE, "bt_linear_create: no CUDA device %d", device);
     DeviceGuard guard(device);
@@ -309,7 +312,7 @@ extern "C" bt_status bt_linear_forward(bt_linear* lin, bt_workspace* ws, const v
     st = plan_workspace(ws, m, lin->w.k_pad(), lin->w.n_out, lin->w.n_bases > 1 && y_dtype == BT_BF16, &p);
     if (st != BT_OK) return st;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (m > 8 && x_dtype == BT_F32 && !(lin->w.n_bases > 1 && y_dtype == BT_BF16) &&
+    if (m > 8 && !(lin->w.n_bases > 1 && y_dtype == BT_BF16) &&
         gemm_tc_act_bytes(m, lin->w.k_tiles) <= (size_t)m * lin->w.k_pad() + 256 * 1024 &&
         gemm_tc_act_bytes(m, lin->w.k_tiles) + 4096 <= ws->bytes) {
         // more than 8 tokens: tensor-core path (tcgen05), activations re-laid residue-split
@@ -321,10 +324,10 @@ extern "C" bt_status bt_linear_forward(bt_linear* lin, bt_workspace* ws, const v
             // what is left of the workspace serves as scratch for k-split products (optional)
             const size_t part_off = align_up(off + align_up((size_t)m * 4, 256) + (size_t)m * 4, 256);
             int32_t* part = part_off < ws->bytes ? reinterpret_cast<int32_t*>(ws->base + part_off) : nullptr;
-            BT_CUDA_TRY(launch_gemm_tc(lin->dev(), reinterpret_cast<const float*>(x_dev), lin->w.k_in, m, qtc, sx, qs, y_dev,
+            BT_CUDA_TRY(launch_gemm_tc(lin->dev(), x_dev, lin->w.k_in, m, qtc, sx, qs, y_dev,
                                        lin->w.n_out, y_dtype == BT_BF16 ? EPI_BF16 : EPI_F32,
                                        device_error_word(lin->device), device_sm_count(lin->device), s, part,
-                                       part ? ws->bytes - part_off : 0));
+                                       part ? ws->bytes - part_off : 0, false, x_dtype));
             return BT_OK;
         }
     }

@@ -32,60 +32,6 @@ constexpr int kUnpBufs = 2;
 constexpr int kTcThreads = 6 * 32;
 constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
 
-// ---- tcgen05 wrappers ---------------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(dst_smem)),
-                 "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ptx::smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
-        "%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, K-major, no swizzle: core matrices are 8 rows x 16 bytes
-// (128 contiguous bytes); lbo = byte distance between core matrices adjacent along K,
-// sbo = byte distance between core matrices adjacent along rows.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
-    return d;                // base offset 0, layout type 0 = no swizzle
-}
-
 // Instruction descriptor for kind::i8: D = s32, A = u8, B = s8, both K-major, M x N tile.
 __device__ __forceinline__ uint32_t instr_desc_i8(int m, int n) {
     uint32_t d = 0;
@@ -148,12 +94,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
         ptx::mbar_fence_init();
     }
     if (warp == 1) {  // one warp allocates (and later frees) the tensor memory
-        tmem_alloc(tmem_slot, kTmemCols);
-        tmem_relinquish();
+        ptx::tmem_alloc(tmem_slot, kTmemCols);
+        ptx::tmem_relinquish();
     }
-    tc_fence_before();
+    ptx::tc_fence_before();
     __syncthreads();
-    tc_fence_after();
+    ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     bool ok = true;
@@ -193,28 +139,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                 const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
                 if (!first_tile) { ok &= ptx::mbar_wait_bounded(acc_empty, acc_par); acc_par ^= 1; }
                 first_tile = false;
-                tc_fence_after();
+                ptx::tc_fence_after();
                 for (int kt = kt0; kt < kt1; ++kt) {
                     ok &= ptx::mbar_wait_bounded(&full[slot], par);        // activation block landed
                     ok &= ptx::mbar_wait_bounded(&unp_full[u], upar);      // weights unpacked
-                    tc_fence_after();
+                    ptx::tc_fence_after();
                     const uint32_t b_addr = ptx::smem_u32(stage_base + (size_t)slot * kStageBytes + kRawBytes);
                     const uint32_t a_addr = ptx::smem_u32(unp_base + (size_t)u * 4 * kATileBytes);
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
 #pragma unroll
                         for (int ks = 0; ks < 2; ++ks) {  // 64 k' per residue = 2 x K32
-                            const uint64_t ad = smem_desc(a_addr + r * kATileBytes + ks * 256, 128, 512);
-                            const uint64_t bd = smem_desc(b_addr + r * (NT * 64) + ks * 256, 128, 512);
-                            umma_i8(tmem_base + r * NT, ad, bd, idesc, (kt > kt0 || ks > 0) ? 1u : 0u);
+                            const uint64_t ad = ptx::smem_desc(a_addr + r * kATileBytes + ks * 256, 128, 512);
+                            const uint64_t bd = ptx::smem_desc(b_addr + r * (NT * 64) + ks * 256, 128, 512);
+                            ptx::umma_i8(tmem_base + r * NT, ad, bd, idesc, (kt > kt0 || ks > 0) ? 1u : 0u);
                         }
                     }
-                    umma_commit(&unp_empty[u]);  // unpacked buffer reusable once these MMAs are done
-                    umma_commit(&empty[slot]);   // and the stage (its activation block)
+                    ptx::umma_commit(&unp_empty[u]);  // unpacked buffer reusable once these MMAs are done
+                    ptx::umma_commit(&empty[slot]);   // and the stage (its activation block)
                     if (++slot == kStages) { slot = 0; par ^= 1; }
                     if (++u == kUnpBufs) { u = 0; upar ^= 1; }
                 }
-                umma_commit(acc_full);
+                ptx::umma_commit(acc_full);
             }
         }
     } else {
@@ -248,7 +194,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                             make_uint4(w.x & mask, w.y & mask, w.z & mask, w.w & mask);
                     }
                 }
-                fence_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+                ptx::fence_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
                 ptx::mbar_arrive(&unp_full[u]);
                 if (++slot == kStages) { slot = 0; par ^= 1; }
                 if (++u == kUnpBufs) { u = 0; first_unp = false; upar ^= 1; }
@@ -256,7 +202,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
             // ---- epilogue of this tile ----
             ok &= ptx::mbar_wait_bounded(acc_full, acc_par);
             acc_par ^= 1;
-            tc_fence_after();
+            ptx::tc_fence_after();
             const int64_t row = (int64_t)rs * kRows + sub * 32 + lane;
             const int64_t rt = row >> 4;
             float sw = 0.f;
@@ -265,11 +211,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
             for (int c0 = 0; c0 < NT; c0 += 32) {
                 uint32_t d0[32], d1[32], d2[32], d3[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + c0;
-                tmem_ld32(taddr + 0 * NT, d0);
-                tmem_ld32(taddr + 1 * NT, d1);
-                tmem_ld32(taddr + 2 * NT, d2);
-                tmem_ld32(taddr + 3 * NT, d3);
-                tmem_ld_wait();
+                ptx::tmem_ld32(taddr + 0 * NT, d0);
+                ptx::tmem_ld32(taddr + 1 * NT, d1);
+                ptx::tmem_ld32(taddr + 2 * NT, d2);
+                ptx::tmem_ld32(taddr + 3 * NT, d3);
+                ptx::tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int token = tb * NT + c0 + j;
@@ -293,20 +239,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                     }
                 }
             }
-            tc_fence_before();
+            ptx::tc_fence_before();
             ptx::mbar_arrive(acc_empty);
         }
     }
     if (!ok) atomicExch(a.err, kErrTcTimeout);
-    tc_fence_before();
+    ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // Per-token absmax int8 quantiser writing the residue-split, core-matrix-ordered layout that
 // gemm_tc_kernel copies in bulk: [token_block][k_tile][residue][token_group][kc][token%8][16].
-template <int NT>
-__global__ void __launch_bounds__(256) act_quant_tc_kernel(const float* __restrict__ x, int64_t x_stride, int k,
+__device__ __forceinline__ float load_act(const float* p) { return *p; }
+__device__ __forceinline__ float load_act(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+template <int NT, typename T>
+__global__ void __launch_bounds__(256) act_quant_tc_kernel(const T* __restrict__ x, int64_t x_stride, int k,
                                                            int k_tiles, int m, int8_t* __restrict__ qtc,
                                                            float* __restrict__ s_out, int32_t* __restrict__ qsum_out) {
     __shared__ float red_f[32];
@@ -315,10 +264,10 @@ __global__ void __launch_bounds__(256) act_quant_tc_kernel(const float* __restri
     const int tb = token / NT, tin = token % NT;
     int8_t* blk = qtc + (int64_t)tb * k_tiles * (4 * NT * 64);
     const bool real = token < m;
-    const float* xr = x + (int64_t)(real ? token : 0) * x_stride;
+    const T* xr = x + (int64_t)(real ? token : 0) * x_stride;
     float amax = 0.0f;
     if (real)
-        for (int c = threadIdx.x; c < k; c += blockDim.x) amax = fmaxf(amax, fabsf(xr[c]));
+        for (int c = threadIdx.x; c < k; c += blockDim.x) amax = fmaxf(amax, fabsf(load_act(xr + c)));
     // block max
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) red_f[threadIdx.x >> 5] = amax;
@@ -330,7 +279,7 @@ __global__ void __launch_bounds__(256) act_quant_tc_kernel(const float* __restri
     const int k_pad = k_tiles * kChunkK;
     for (int c = threadIdx.x; c < k_pad; c += blockDim.x) {
         int qv = 0;
-        if (real && c < k) qv = max(-127, min(127, ptx::round_half_away(__fmul_rn(xr[c], inv))));
+        if (real && c < k) qv = max(-127, min(127, ptx::round_half_away(__fmul_rn(load_act(xr + c), inv))));
         local += qv;
         blk[gemm_tc_act_offset(c, tin, NT)] = (int8_t)qv;
     }
@@ -418,17 +367,23 @@ size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles) {
     return (size_t)((m + nt - 1) / nt * k_tiles * 4 * nt * 64);
 }
 
-cudaError_t launch_gemm_tc(const LinearDev& lin, const float* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
+cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
                            int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
-                           cudaStream_t stream, int32_t* part, size_t part_bytes, bool prequantised) {
+                           cudaStream_t stream, int32_t* part, size_t part_bytes, bool prequantised, bt_dtype x_dtype) {
     if (lin.w.n_bases != 1 && epilogue == EPI_BF16) return cudaErrorInvalidValue;
     const int nt = m <= 64 ? 64 : 128;
     const int padded = (int)((m + nt - 1) / nt * nt);
+    const int k = (int)lin.w.k_in, kts = (int)lin.w.k_tiles;
     if (prequantised) {
-    } else if (nt == 64)
-        act_quant_tc_kernel<64><<<padded, 256, 0, stream>>>(x, x_stride, (int)lin.w.k_in, (int)lin.w.k_tiles, (int)m, qtc, sx, qsum);
-    else
-        act_quant_tc_kernel<128><<<padded, 256, 0, stream>>>(x, x_stride, (int)lin.w.k_in, (int)lin.w.k_tiles, (int)m, qtc, sx, qsum);
+    } else if (x_dtype == BT_BF16) {
+        const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+        if (nt == 64) act_quant_tc_kernel<64><<<padded, 256, 0, stream>>>(xb, x_stride, k, kts, (int)m, qtc, sx, qsum);
+        else act_quant_tc_kernel<128><<<padded, 256, 0, stream>>>(xb, x_stride, k, kts, (int)m, qtc, sx, qsum);
+    } else {
+        const float* xf = reinterpret_cast<const float*>(x);
+        if (nt == 64) act_quant_tc_kernel<64><<<padded, 256, 0, stream>>>(xf, x_stride, k, kts, (int)m, qtc, sx, qsum);
+        else act_quant_tc_kernel<128><<<padded, 256, 0, stream>>>(xf, x_stride, k, kts, (int)m, qtc, sx, qsum);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     for (int b = 0; b < lin.w.n_bases; ++b) {

@@ -26,6 +26,8 @@
 //     first weight stages are already in flight, which removes a kernel boundary per
 //     projection from the decode step; with programmatic dependent launch the weight
 //     prefetch even starts before the previous kernel has finished.
+#include <mutex>
+
 #include "bt_common.cuh"
 #include "bt_ptx.cuh"
 
@@ -317,7 +319,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     const int my_rts = (int)((a.row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
     const int total_iters = short_k ? (my_rts + TPW - 1) / TPW : my_rts * stages_per_rt;
 
-    if (a.dbg && threadIdx.x == 0) a.dbg[blockIdx.x * 4 + 0] = ptx::globaltimer();
     if (threadIdx.x < 8) tok_qsum[threadIdx.x] = 0;
     for (int i = threadIdx.x; i < kAccBufs * kAccBufInts; i += kThreads) accbuf[i] = 0;
     if (threadIdx.x == 0) {
@@ -444,7 +445,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                 for (int o = 16; o > 0; o >>= 1) amax1 = fmaxf(amax1, __shfl_xor_sync(0xffffffffu, amax1, o));
                 if (lane == 0) atomicMax(a.absmax_out, __float_as_uint(amax1));
                 if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
-                if (a.dbg && lane == 0) atomicMax(a.dbg + blockIdx.x * 4 + 3, ptx::globaltimer());  // last epilogue warp to finish
                 return;
             }
             float sw = 0.f;
@@ -481,7 +481,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                 rt += (int64_t)kEpiWarps * gridDim.x;
             }
             if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
-            if (a.dbg && lane == 0) atomicMax(a.dbg + blockIdx.x * 4 + 3, ptx::globaltimer());  // last epilogue warp to finish
             return;
         }
         for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
@@ -545,7 +544,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             }
         }
         if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
-        if (a.dbg && lane == 0) atomicMax(a.dbg + blockIdx.x * 4 + 3, ptx::globaltimer());  // last epilogue warp to finish
         return;
     }
 
@@ -568,10 +566,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
         }
     }
     ptx::pdl_wait();  // activations belong to earlier kernels until here
-    if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 1] = ptx::globaltimer();
     stage_activations<PRO>(a, acts, act_stride, tok_sx, tok_qsum, scratch, tid, warp, lane, k_tiles, w0, x_issued);
     ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // activation image complete, epilogue warps may read the scales
-    if (a.dbg && tid == 0) a.dbg[blockIdx.x * 4 + 2] = ptx::globaltimer();
 
     int acc[4][4] = {};  // rewritten by the first tile of every row tile
     // lanes whose MMA column has no token read the last token's row instead: their columns are
@@ -692,8 +688,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
 }
 
 int g_configured[64] = {0};
+std::mutex g_configured_mu;  // the forward entry points may be called from several host threads
+
+// Fixed shared memory of a launch besides the ring: activation image of m tokens + bookkeeping.
+size_t gemv_fixed_smem(int m, int64_t k_tiles) {
+    return (size_t)m * (size_t)(k_tiles * kTileK + 64) + kAccBytes + kBarBytes + kTokBytes + kScratchBytes;
+}
+constexpr size_t kSmemBudget = 220 * 1024;
 
 }  // namespace
+
+// Largest token count (<= 8) whose activation image fits beside a minimal ring; 0 if even one token does not.
+int gemv_max_tokens(int64_t k_tiles) {
+    for (int m = 8; m >= 1; --m)
+        if (gemv_fixed_smem(m, k_tiles) + 2 * kHalfBytes <= kSmemBudget) return m;
+    return 0;
+}
 
 template <int TPW>
 static cudaError_t launch_gemv_t(const GemvArgs& a, int grid, size_t smem, int nstages, int act_stride, cudaStream_t stream) {
@@ -710,11 +720,11 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     if (a.prologue == PRO_RMSNORM && a.k_in > 16 * 2 * kMathThreads) return cudaErrorInvalidValue;
     if (a.epilogue == EPI_SWIGLU && (!a.absmax_out || a.n_out % 16 != 0)) return cudaErrorInvalidValue;
     const int act_stride = (int)(a.k_tiles * kTileK + 64);
-    const size_t fixed = (size_t)a.m * act_stride + kAccBytes + kBarBytes + kTokBytes + kScratchBytes;
+    const size_t fixed = gemv_fixed_smem(a.m, a.k_tiles);
     // One CTA per SM.  The ring takes what shared memory allows, but never more stages than
     // the CTA has iterations.  Stages of two passes (32 KB) are used whenever at least three of
     // them fit beside the activation image; HBM needs well over 100 KB in flight per SM.
-    const size_t budget = 220 * 1024;
+    const size_t budget = kSmemBudget;
     if (fixed + 2 * kHalfBytes > budget) return cudaErrorInvalidConfiguration;
     int64_t grid64 = sm_count;
     if (grid64 > a.row_tiles) grid64 = a.row_tiles;
@@ -733,15 +743,18 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     const size_t smem = (size_t)nstages * stage_bytes + fixed;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !g_configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
-        if (e != cudaSuccess) return e;
-        g_configured[dev] = 1;
+    {
+        std::lock_guard<std::mutex> lock(g_configured_mu);
+        if (dev >= 0 && dev < 64 && !g_configured[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_Q8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_RMSNORM, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<PRO_ABSMAX, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            if (e != cudaSuccess) return e;
+            g_configured[dev] = 1;
+        }
     }
     return tpw == 2 ? launch_gemv_t<2>(a, grid, smem, nstages, act_stride, stream)
                     : launch_gemv_t<1>(a, grid, smem, nstages, act_stride, stream);
@@ -754,7 +767,10 @@ cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stri
     const int bases = epilogue == EPI_I32 ? 1 : lin.w.n_bases;
     if (epilogue == EPI_BF16 && bases > 1) return cudaErrorInvalidValue;
     const size_t elem = epilogue == EPI_BF16 ? 2 : 4;
-    for (int64_t m0 = 0; m0 < m; m0 += 8) {
+    // tokens per launch: as many (up to 8) as leave room for the ring beside their activation image
+    const int chunk = gemv_max_tokens(lin.w.k_tiles);
+    if (chunk < 1) return cudaErrorInvalidConfiguration;
+    for (int64_t m0 = 0; m0 < m; m0 += chunk) {
         for (int b = 0; b < bases; ++b) {
             GemvArgs a = {};
             a.tiles = lin.w.tiles + (size_t)b * lin.w.basis_stride();
@@ -768,7 +784,7 @@ cudaError_t linear_product(const LinearDev& lin, const int8_t* q, int64_t q_stri
             a.qsum = qsum + m0;
             a.sx = sx ? sx + m0 : nullptr;
             a.sw_tiles = lin.scale_tiles ? lin.scale_tiles + (size_t)b * lin.w.row_tiles * 2 : nullptr;
-            a.m = (int)(m - m0 < 8 ? m - m0 : 8);
+            a.m = (int)(m - m0 < chunk ? m - m0 : chunk);
             a.out = reinterpret_cast<uint8_t*>(out) + (size_t)m0 * out_stride * elem;
             a.out_stride = out_stride;
             a.epilogue = (b > 0 && epilogue == EPI_F32) ? EPI_F32_ACCUM : epilogue;
@@ -809,9 +825,6 @@ cudaError_t linear_product_q(const LinearDev& lin, const int8_t* q, int64_t q_st
     return launch_gemv(a, sm_count, stream);
 }
 
-unsigned long long* g_dbg_base = nullptr;
-int g_dbg_slot = 0;
-
 cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m, void* out,
                                  int64_t out_stride, int epilogue, unsigned int* absmax_out,
                                  unsigned int* err, int sm_count, cudaStream_t stream) {
@@ -835,7 +848,6 @@ cudaError_t linear_product_fused(const LinearDev& lin, const FusedIn& in, int m,
     a.out_stride = out_stride;
     a.epilogue = epilogue;
     a.err = err;
-    a.dbg = g_dbg_base ? g_dbg_base + (size_t)(g_dbg_slot++) * 4 * 512 : nullptr;
     a.pdl = true;
     return launch_gemv(a, sm_count, stream);
 }

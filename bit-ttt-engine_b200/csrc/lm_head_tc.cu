@@ -20,53 +20,6 @@ constexpr int kStages = 4;
 constexpr int kThreads = 6 * 32;
 constexpr unsigned kErrLmTimeout = 0x4c4d4844u;  // 'LMHD'
 
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(dst_smem)),
-                 "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ptx::smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
-        "%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;
-    return d;
-}
 // kind::f16: D = f32, A = B = bf16, K-major, M x N tile
 __device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n) {
     uint32_t d = 0;
@@ -148,10 +101,10 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_tc_kernel(const uint8_t* 
         ptx::mbar_init(acc_empty, 128);
         ptx::mbar_fence_init();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, kCols); tmem_relinquish(); }
-    tc_fence_before();
+    if (warp == 1) { ptx::tmem_alloc(tmem_slot, kCols); ptx::tmem_relinquish(); }
+    ptx::tc_fence_before();
     __syncthreads();
-    tc_fence_after();
+    ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
@@ -175,22 +128,22 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_tc_kernel(const uint8_t* 
             for (int64_t rs = blockIdx.x; rs < row_sets; rs += gridDim.x) {
                 if (!first_tile) { ok &= ptx::mbar_wait_bounded(acc_empty, acc_par); acc_par ^= 1; }
                 first_tile = false;
-                tc_fence_after();
+                ptx::tc_fence_after();
                 for (int kc = 0; kc < chunks; ++kc) {
                     ok &= ptx::mbar_wait_bounded(&full[slot], par);
-                    tc_fence_after();
+                    ptx::tc_fence_after();
                     const uint32_t a_addr = ptx::smem_u32(stage_base + (size_t)slot * (kATile + kBTile));
                     const uint32_t b_addr = a_addr + kATile;
 #pragma unroll
                     for (int ks = 0; ks < kChunk / 16; ++ks) {  // K = 16 bf16 = 2 core matrices per MMA
-                        const uint64_t ad = smem_desc(a_addr + ks * 256, 128, (kChunk / 8) * 128);
-                        const uint64_t bd = smem_desc(b_addr + ks * 256, 128, (kChunk / 8) * 128);
-                        umma_f16(tmem_base, ad, bd, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
+                        const uint64_t ad = ptx::smem_desc(a_addr + ks * 256, 128, (kChunk / 8) * 128);
+                        const uint64_t bd = ptx::smem_desc(b_addr + ks * 256, 128, (kChunk / 8) * 128);
+                        ptx::umma_f16(tmem_base, ad, bd, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
                     }
-                    umma_commit(&empty[slot]);
+                    ptx::umma_commit(&empty[slot]);
                     if (++slot == kStages) { slot = 0; par ^= 1; }
                 }
-                umma_commit(acc_full);
+                ptx::umma_commit(acc_full);
             }
         }
     } else {
@@ -199,15 +152,15 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_tc_kernel(const uint8_t* 
         for (int64_t rs = blockIdx.x; rs < row_sets; rs += gridDim.x) {
             ok &= ptx::mbar_wait_bounded(acc_full, acc_par);
             acc_par ^= 1;
-            tc_fence_after();
+            ptx::tc_fence_after();
             const int64_t v = rs * kRows + sub * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < kTok; c0 += 32) {
                 uint32_t hi[32], lo[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + c0;
-                tmem_ld32(taddr, hi);
-                tmem_ld32(taddr + kTok, lo);
-                tmem_ld_wait();
+                ptx::tmem_ld32(taddr, hi);
+                ptx::tmem_ld32(taddr + kTok, lo);
+                ptx::tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int token = c0 + j;
@@ -215,14 +168,14 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_tc_kernel(const uint8_t* 
                         logits[(int64_t)token * vocab + v] = __fadd_rn(__uint_as_float(hi[j]), __uint_as_float(lo[j]));
                 }
             }
-            tc_fence_before();
+            ptx::tc_fence_before();
             ptx::mbar_arrive(acc_empty);
         }
     }
     if (!ok) atomicExch(err, kErrLmTimeout);
-    tc_fence_before();
+    ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, kCols);
+    if (warp == 1) ptx::tmem_dealloc(tmem_base, kCols);
 }
 
 }  // namespace

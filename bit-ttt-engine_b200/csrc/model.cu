@@ -12,10 +12,7 @@
 using namespace bt;
 
 namespace bt {
-extern unsigned long long* g_dbg_base;
-extern int g_dbg_slot;
 cudaError_t upload_inv_freq(float* dev, int head_dim, double theta);
-void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* splits, int* span);
 
 __global__ void advance_pos_kernel(int32_t* pos, int n) {
     if (threadIdx.x < n) pos[threadIdx.x] += 1;
@@ -88,7 +85,6 @@ struct bt_model {
     float* xn = nullptr;
     float* logits = nullptr;
     int32_t* next = nullptr;
-    double* attn_partial = nullptr;
     float* act = nullptr;            // [max_batch, intermediate] silu(gate)*up
     float* xt = nullptr;             // [max_batch, max(hidden, intermediate)] transformed rows (batches above 8)
     int8_t* qtc = nullptr;           // activations in the tensor-core product's layout (batches above 8)
@@ -101,6 +97,7 @@ struct bt_model {
     int32_t* cand_idx = nullptr;
     int32_t* tokens_pinned = nullptr;
     int32_t* next_pinned = nullptr;
+    unsigned int* err_pinned = nullptr;  // tensor parallel: the device error word as read after a step
     int host_pos = 0;
     int64_t ternary_bytes = 0;
     cudaStream_t stream = nullptr;
@@ -181,16 +178,13 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.pos = m->pos;
             a.rope_cos = m->rope_cos;
             a.rope_sin = m->rope_sin;
-            a.counters = L.kv->counters;
             a.out = m->att;
-            a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim;
             a.sm_count = sm;
-            attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, &a.splits, &a.span);
+            attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = amax_core;
             a.pdl = true;
-            a.dbg = g_dbg_base ? g_dbg_base + (size_t)(g_dbg_slot++) * 4 * 512 : nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
             FusedIn ain{PRO_ABSMAX, m->att, att_dim, nullptr, 0.f, amax_core};
             if (m->tp > 1 && tp_peer_ready(m->peer)) {
@@ -270,16 +264,13 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.pos = m->pos;
             a.rope_cos = m->rope_cos;
             a.rope_sin = m->rope_sin;
-            a.counters = L.kv->counters;
             a.out = m->att;
-            a.partial = m->attn_partial;
             a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim;
             a.sm_count = sm;
-            attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, &a.splits, &a.span);
+            attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = nullptr;
             a.pdl = false;
-            a.dbg = nullptr;
             BT_CUDA_TRY(launch_attn_decode(a, s));
             BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes));
         }
@@ -496,7 +487,6 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
         BT_CUDA_TRY(dev_alloc(&m->rope_sin, (size_t)c.max_position_embeddings * (m->head_dim / 2)));
         BT_CUDA_TRY(launch_rope_tables(m->inv_freq, c.max_position_embeddings, m->head_dim / 2, m->rope_cos, m->rope_sin, 0));
         BT_CUDA_TRY(cudaDeviceSynchronize());
-        BT_CUDA_TRY(dev_alloc(&m->attn_partial, (size_t)B * c.n_heads * 64 * (m->head_dim + 2)));
         if (m->tp > 1) BT_CUDA_TRY(dev_alloc(&m->acc_i32, (size_t)B * H));
     } else {
         BT_CUDA_TRY(dev_alloc(&m->feat, (size_t)B * m->d_small));
@@ -504,6 +494,8 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
     }
     BT_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&m->tokens_pinned), (size_t)B * sizeof(int32_t)));
     BT_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&m->next_pinned), (size_t)B * sizeof(int32_t)));
+    BT_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&m->err_pinned), sizeof(unsigned int)));
+    *m->err_pinned = 0;
     BT_CUDA_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     m->finalized = true;
     return bt_model_reset(m);
@@ -522,10 +514,11 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->attn_partial, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles, m->tc_part};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles, m->tc_part};
     for (void* p : bufs) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
+    if (m->err_pinned) cudaFreeHost(m->err_pinned);
     if (m->stream) cudaStreamDestroy(m->stream);
     if (m->comm) tp_comm_destroy(m->comm);
     if (m->peer) tp_peer_destroy(m->peer);
@@ -542,6 +535,7 @@ extern "C" bt_status bt_model_reset(bt_model* m) {
         if (L.w_state) BT_CUDA_TRY(cudaMemset(L.w_state, 0, (size_t)m->cfg.max_batch * m->d_small * m->d_small * sizeof(float)));
     }
     BT_CUDA_TRY(cudaMemset(m->pos, 0, (size_t)m->cfg.max_batch * sizeof(int32_t)));
+    if (m->peer) BT_CUDA_TRY(tp_peer_reset(m->peer));  // exchange epochs restart; every rank resets between the same steps
     m->host_pos = 0;
     return BT_OK;
 }
@@ -609,7 +603,18 @@ extern "C" bt_status bt_model_forward_one(bt_model* m, const int32_t* tokens_hos
     if (logits_host)
         BT_CUDA_TRY(cudaMemcpyAsync(logits_host, m->logits, (size_t)batch * m->cfg.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, s));
     BT_CUDA_TRY(cudaMemcpyAsync(m->next_pinned, m->next, (size_t)batch * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    unsigned int* err_word = m->tp > 1 ? device_error_word(m->device) : nullptr;
+    if (err_word) BT_CUDA_TRY(cudaMemcpyAsync(m->err_pinned, err_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
     BT_CUDA_TRY(cudaStreamSynchronize(s));
+    if (err_word && *m->err_pinned != 0) {
+        // a peer never arrived at an exchange: the hidden state of this step is not valid
+        const unsigned int tag = *m->err_pinned;
+        BT_CUDA_TRY(cudaMemsetAsync(err_word, 0, sizeof(unsigned int), s));
+        BT_CUDA_TRY(cudaStreamSynchronize(s));
+        *m->err_pinned = 0;
+        return set_error(BT_ERR_TIMEOUT, "bt_model_forward_one: a tensor-parallel exchange timed out (kernel tag 0x%08x); "
+                                         "reset every rank (bt_model_reset) before the next step", tag);
+    }
     if (next_host) memcpy(next_host, m->next_pinned, (size_t)batch * sizeof(int32_t));
     return BT_OK;
 }
@@ -692,10 +697,6 @@ extern "C" bt_status bt_model_seek(bt_model* m, int pos) {
     return BT_OK;
 }
 
-// Development aid: fused product launches enqueued after this call stamp their timeline
-// (entry / after dependency wait / after activation staging / end) into buf[slot][cta][4].
-extern "C" void bt_debug_timeline(unsigned long long* buf) { bt::g_dbg_base = buf; bt::g_dbg_slot = 0; }
-
 extern "C" bt_status bt_tp_unique_id(uint8_t* id128_out) {
     if (!id128_out) return set_error(BT_ERR_ARG, "bt_tp_unique_id: null pointer");
     return tp_unique_id(id128_out);
@@ -733,6 +734,35 @@ extern "C" bt_status bt_model_tp_peer_import(bt_model* m, const uint8_t* handles
         g = nullptr;
     }
     return tp_peer_import(m->peer, handles);
+}
+
+namespace {
+void drop_graphs(bt_model* m) {
+    for (auto& g : m->graphs) {
+        if (g && g != reinterpret_cast<cudaGraphExec_t>(uintptr_t(1))) cudaGraphExecDestroy(g);
+        g = nullptr;
+    }
+}
+}  // namespace
+
+extern "C" bt_status bt_model_tp_set_timeout(bt_model* m, int milliseconds) {
+    if (!m || !m->finalized || !m->peer) return set_error(BT_ERR_ARG, "bt_model_tp_set_timeout: no peer-memory exchange on this model");
+    if (milliseconds < 1) return set_error(BT_ERR_ARG, "bt_model_tp_set_timeout: %d ms", milliseconds);
+    DeviceGuard guard(m->device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    drop_graphs(m);  // the limit travels as a kernel argument of the captured launches
+    tp_peer_set_wait(m->peer, (unsigned long long)milliseconds * 1000000ull);
+    return BT_OK;
+}
+
+extern "C" bt_status bt_model_tp_destroy(bt_model* m) {
+    if (!m) return BT_OK;
+    DeviceGuard guard(m->device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    drop_graphs(m);
+    if (m->peer) { tp_peer_destroy(m->peer); m->peer = nullptr; }
+    if (m->comm) { tp_comm_destroy(m->comm); m->comm = nullptr; }
+    return BT_OK;
 }
 
 extern "C" bt_status bt_model_tp_init(bt_model* m, const uint8_t* id128) {

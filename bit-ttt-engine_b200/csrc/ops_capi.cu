@@ -20,34 +20,6 @@ cudaError_t upload_inv_freq(float* dev, int head_dim, double theta) {
     return cudaMemcpy(dev, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice);
 }
 
-// Cuts the positions of a sequence into fixed spans so that batch * n_kv * splits CTAs
-// roughly fill the GPU: span is a multiple of 64 (one tile), at most 64 spans.
-void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int* splits, int* span) {
-    // One CTA per (sequence, KV head, span).  Fewer pairs than SMs: cut the positions so that
-    // every SM gets a span.  More pairs than SMs: the CTAs run in waves of sm_count, and cutting
-    // the positions in 2..4 can fill the last wave better; cost model = waves x (tiles of 128
-    // positions per CTA + 1 for the fixed work of a CTA).
-    const int64_t pairs = batch * n_kv;
-    // fewer pairs than SMs: as many spans as fit in ONE wave (a CTA takes a whole SM), so that
-    // no span has to wait for another CTA to finish before it can even start
-    int64_t want = (int64_t)sm_count / pairs;
-    if (want > 64) want = 64;
-    if (want < 1) want = 1;
-    if (pairs >= sm_count) {
-        int64_t best_cost = -1;
-        for (int64_t s = 1; s <= 4; ++s) {
-            const int64_t sp = ((max_seq + s - 1) / s + 63) / 64 * 64;
-            const int64_t waves = (pairs * s + sm_count - 1) / sm_count;
-            const int64_t cost = waves * ((sp + 127) / 128 + 1);
-            if (best_cost < 0 || cost < best_cost) { best_cost = cost; want = s; }
-        }
-    }
-    int64_t sp = (max_seq + want - 1) / want;
-    sp = pairs < sm_count ? (sp + 31) / 32 * 32 : (sp + 63) / 64 * 64;
-    *span = (int)sp;  // upper bound: the kernel cuts the current length, not max_seq, into `splits` spans
-    *splits = pairs < sm_count ? (int)want : (int)((max_seq + sp - 1) / sp);
-}
-
 }  // namespace bt
 
 extern "C" bt_status bt_ttt_update(float* w_state_dev, const float* feat_dev, int64_t batch, int64_t t_len,
@@ -84,20 +56,14 @@ extern "C" bt_status bt_kv_create(bt_kv_cache** out, int64_t batch, int64_t n_kv
     c->device = device;
     c->batch = batch; c->n_kv = n_kv_heads; c->head_dim = head_dim; c->max_seq = max_seq_len;
     const size_t rows = (size_t)batch * n_kv_heads * max_seq_len;
-    const int sm = device_sm_count(device);
     c->max_heads = (int)n_kv_heads * 8;
-    (void)sm;
-    c->partial_floats = (int64_t)batch * c->max_heads * 64 * (head_dim + 2);  // at most 64 spans
     cudaError_t e = cudaMalloc(&c->view.k_q, rows * head_dim);
     if (e == cudaSuccess) e = cudaMalloc(&c->view.v_q, rows * head_dim);
     if (e == cudaSuccess) e = cudaMalloc(&c->view.k_s, rows * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&c->view.v_s, rows * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&c->inv_freq, (size_t)head_dim / 2 * sizeof(float));
-    if (e == cudaSuccess) e = cudaMalloc(&c->partial, (size_t)c->partial_floats * sizeof(double));
     if (e == cudaSuccess) e = cudaMalloc(&c->rope_cos, (size_t)max_seq_len * (head_dim / 2) * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&c->rope_sin, (size_t)max_seq_len * (head_dim / 2) * sizeof(float));
-    if (e == cudaSuccess) e = cudaMalloc(&c->counters, (size_t)batch * n_kv_heads * sizeof(unsigned int));
-    if (e == cudaSuccess) e = cudaMemset(c->counters, 0, (size_t)batch * n_kv_heads * sizeof(unsigned int));
     c->view.max_seq = (int)max_seq_len;
     if (e != cudaSuccess) {
         bt_kv_destroy(c);
@@ -115,7 +81,6 @@ extern "C" bt_status bt_kv_reset(bt_kv_cache* c) {
     BT_CUDA_TRY(cudaMemset(c->view.v_q, 128, rows * c->head_dim));
     BT_CUDA_TRY(cudaMemset(c->view.k_s, 0, rows * sizeof(float)));
     BT_CUDA_TRY(cudaMemset(c->view.v_s, 0, rows * sizeof(float)));
-    BT_CUDA_TRY(cudaMemset(c->counters, 0, (size_t)c->batch * c->n_kv * sizeof(unsigned int)));
     return BT_OK;
 }
 
@@ -123,7 +88,7 @@ extern "C" bt_status bt_kv_destroy(bt_kv_cache* c) {
     if (!c) return BT_OK;
     DeviceGuard guard(c->device);
     cudaFree(c->view.k_q); cudaFree(c->view.v_q); cudaFree(c->view.k_s); cudaFree(c->view.v_s);
-    cudaFree(c->inv_freq); cudaFree(c->partial); cudaFree(c->rope_cos); cudaFree(c->rope_sin); cudaFree(c->counters);
+    cudaFree(c->inv_freq); cudaFree(c->rope_cos); cudaFree(c->rope_sin);
     delete c;
     return BT_OK;
 }
@@ -143,6 +108,35 @@ extern "C" bt_status bt_kv_export(bt_kv_cache* c, int64_t b, int64_t t_len, uint
         if (k_s_host) BT_CUDA_TRY(cudaMemcpy(k_s_host + o, c->view.k_s + row0, (size_t)t_len * sizeof(float), cudaMemcpyDeviceToHost));
         if (v_s_host) BT_CUDA_TRY(cudaMemcpy(v_s_host + o, c->view.v_s + row0, (size_t)t_len * sizeof(float), cudaMemcpyDeviceToHost));
     }
+    return BT_OK;
+}
+
+extern "C" bt_status bt_kv_import(bt_kv_cache* c, int64_t b, int64_t t_len, const uint8_t* k_q_host, const float* k_s_host,
+                                  const uint8_t* v_q_host, const float* v_s_host) {
+    if (!c) return set_error(BT_ERR_ARG, "bt_kv_import: null handle");
+    if (b < 0 || b >= c->batch || t_len < 0 || t_len > c->max_seq)
+        return set_error(BT_ERR_SHAPE, "bt_kv_import: sequence %lld / length %lld out of range", (long long)b, (long long)t_len);
+    DeviceGuard guard(c->device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    for (int64_t h = 0; h < c->n_kv; ++h) {
+        const size_t row0 = ((size_t)b * c->n_kv + h) * c->max_seq;
+        const size_t o = (size_t)h * t_len;
+        if (k_q_host) BT_CUDA_TRY(cudaMemcpy(c->view.k_q + row0 * c->head_dim, k_q_host + o * c->head_dim, (size_t)t_len * c->head_dim, cudaMemcpyHostToDevice));
+        if (v_q_host) BT_CUDA_TRY(cudaMemcpy(c->view.v_q + row0 * c->head_dim, v_q_host + o * c->head_dim, (size_t)t_len * c->head_dim, cudaMemcpyHostToDevice));
+        if (k_s_host) BT_CUDA_TRY(cudaMemcpy(c->view.k_s + row0, k_s_host + o, (size_t)t_len * sizeof(float), cudaMemcpyHostToDevice));
+        if (v_s_host) BT_CUDA_TRY(cudaMemcpy(c->view.v_s + row0, v_s_host + o, (size_t)t_len * sizeof(float), cudaMemcpyHostToDevice));
+    }
+    return BT_OK;
+}
+
+extern "C" bt_status bt_kv_append(bt_kv_cache* c, const float* k_dev, const float* v_dev, const int32_t* pos_dev,
+                                  int64_t batch, void* stream) {
+    if (!c || !k_dev || !v_dev || !pos_dev) return set_error(BT_ERR_ARG, "bt_kv_append: null pointer");
+    if (batch < 1 || batch > c->batch) return set_error(BT_ERR_SHAPE, "bt_kv_append: batch %lld exceeds the cache's %lld", (long long)batch, (long long)c->batch);
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return set_error(BT_ERR_DEVICE, "cannot select device %d", c->device);
+    BT_CUDA_TRY(launch_kv_append(c->view, k_dev, v_dev, pos_dev, (int)batch, (int)c->n_kv, (int)c->head_dim,
+                                 reinterpret_cast<cudaStream_t>(stream)));
     return BT_OK;
 }
 
@@ -168,16 +162,13 @@ extern "C" bt_status bt_attn_decode(bt_kv_cache* c, const float* qkv_dev, const 
     a.pos = pos_dev;
     a.rope_cos = c->rope_cos;
     a.rope_sin = c->rope_sin;
-    a.counters = c->counters;
     a.out = out_dev;
-    a.partial = c->partial;
     a.batch = (int)batch; a.n_heads = (int)n_heads; a.n_kv = (int)c->n_kv; a.head_dim = (int)c->head_dim;
     a.sm_count = device_sm_count(c->device);
-    attn_plan(batch, c->n_kv, c->max_seq, a.sm_count, &a.splits, &a.span);
+    attn_plan(batch, c->n_kv, c->max_seq, a.sm_count, (int)rep, &a.splits, &a.span);
     a.scaling = (float)(1.0 / sqrt((double)c->head_dim));  // layers/attention.rs:114
     a.absmax_out = nullptr;
     a.pdl = false;
-    a.dbg = nullptr;
     BT_CUDA_TRY(launch_attn_decode(a, reinterpret_cast<cudaStream_t>(stream)));
     return BT_OK;
 }

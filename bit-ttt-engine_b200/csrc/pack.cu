@@ -91,3 +91,31 @@ extern "C" bt_status bt_unpack_ternary(const uint8_t* packed, int64_t n_elem, fl
     }
     return BT_OK;
 }
+
+// Legacy one-byte-per-weight layout [n_out, k_in/4, n_bases, 4] (int8 values -1 / 0 / +1 stored as
+// bytes 255 / 0 / 1; pack_interleaved_blocks, tools/conversion/convert_adaptive.py:43-83, read by
+// adaptive_gemm_n3_kernel_f32, kernels/adaptive_bit_op.cu:74-161) -> the 2-bit checkpoint layout
+// [n_out, k_in/4, n_bases] that bt_linear_create takes.  Any other byte value is an error.
+extern "C" bt_status bt_convert_l3_to_l2(const int8_t* l3_host, int64_t n_out, int64_t k_in, int n_bases,
+                                         uint8_t* l2_out_host) {
+    if (!l3_host || !l2_out_host) return bt::set_error(BT_ERR_ARG, "bt_convert_l3_to_l2: null pointer");
+    if (n_out <= 0 || k_in <= 0 || n_bases < 1 || n_bases > 8)
+        return bt::set_error(BT_ERR_SHAPE, "bt_convert_l3_to_l2: bad shape [%lld, %lld] x %d bases", (long long)n_out,
+                             (long long)k_in, n_bases);
+    if (k_in % 4 != 0) return bt::set_error(BT_ERR_ALIGN, "bt_convert_l3_to_l2: in_features %lld is not a multiple of 4", (long long)k_in);
+    const int64_t blocks = n_out * (k_in / 4);
+    for (int64_t blk = 0; blk < blocks; ++blk) {
+        for (int b = 0; b < n_bases; ++b) {
+            const int8_t* src = l3_host + (blk * n_bases + b) * 4;
+            unsigned byte = 0;
+            for (int r = 0; r < 4; ++r) {
+                const int v = src[r];
+                if (v < -1 || v > 1)
+                    return bt::set_error(BT_ERR_ARG, "bt_convert_l3_to_l2: weight value %d at block %lld is not ternary", v, (long long)blk);
+                byte |= (v > 0 ? 1u : (v < 0 ? 2u : 0u)) << (2 * r);
+            }
+            l2_out_host[blk * n_bases + b] = (uint8_t)byte;
+        }
+    }
+    return BT_OK;
+}

@@ -105,6 +105,7 @@ struct TpView {
     int rank;
     uint8_t* inbox[kTpMaxRanks];       // every rank's inbox as mapped into this process (own included)
     unsigned long long* epoch;         // local, [2 slots]: exchanges done on the slot
+    unsigned long long wait_ns;        // how long a kernel waits for its peers before it gives up
     unsigned int* done;                // local, [2 slots]: CTAs of the running sum kernel that have pushed
     unsigned int* err;
 };
@@ -117,12 +118,24 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-// waits until every source rank has published epoch e on (slot, kind) of this rank's inbox
+// Waits until the cell holds epoch e or later.  The wait is bounded in time (globaltimer, the
+// limit is set from the host) and is skipped altogether once any kernel has recorded an error on
+// this device: after one rank has gone missing the rest of the step drains quickly instead of
+// paying the limit at every exchange.
+__device__ __forceinline__ bool wait_epoch(const TpView& v, const unsigned long long* f, unsigned long long e) {
+    if (ld_acquire_sys(f) >= e) return true;
+    if (*reinterpret_cast<volatile unsigned int*>(v.err) != 0u) return false;
+    const unsigned long long t0 = ptx::globaltimer();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (ld_acquire_sys(f) >= e) return true;
+        if (ptx::globaltimer() - t0 > v.wait_ns) return false;
+    }
+}
+// waits until source rank `src` has published epoch e on (slot, kind) of this rank's inbox
 __device__ __forceinline__ bool wait_sources(const TpView& v, int slot, int kind, unsigned long long e, int src) {
-    const unsigned long long* f = reinterpret_cast<const unsigned long long*>(v.inbox[v.rank] + v.lay.flag_off(slot, kind, src));
-    for (unsigned i = 0; i < (1u << 21); ++i)
-        if (ld_acquire_sys(f) >= e) return true;
-    return false;
+    return wait_epoch(v, reinterpret_cast<const unsigned long long*>(v.inbox[v.rank] + v.lay.flag_off(slot, kind, src)), e);
 }
 
 // all-reduce(max) of the per-token max|x| cells: one CTA
@@ -182,11 +195,15 @@ __global__ void __launch_bounds__(256) tp_sum_residual_kernel(TpView v, int slot
         __threadfence_system();
         st_release_sys(reinterpret_cast<unsigned long long*>(v.inbox[tid] + v.lay.cflag_off(slot, v.rank, blockIdx.x)), e);
         const unsigned long long* f = reinterpret_cast<const unsigned long long*>(v.inbox[v.rank] + v.lay.cflag_off(slot, tid, blockIdx.x));
-        bool got = false;
-        for (unsigned it = 0; it < (1u << 21) && !got; ++it) got = ld_acquire_sys(f) >= e;
-        if (!got) ok_s = 0;
+        if (!wait_epoch(v, f, e)) ok_s = 0;
     }
     __syncthreads();
+    if (!ok_s) {
+        // a peer never arrived: its cells are stale, so h is left as it was (the step's result is
+        // invalid either way; the host sees BT_ERR_TIMEOUT and must reset all ranks)
+        if (tid == 0) atomicExch(v.err, kErrTpTimeout);
+        return;
+    }
     for (int i = i0 + tid; i < i1; i += blockDim.x) {
         int4 sum = make_int4(0, 0, 0, 0);
         for (int r = 0; r < R; ++r) {
@@ -202,7 +219,6 @@ __global__ void __launch_bounds__(256) tp_sum_residual_kernel(TpView v, int slot
         hv.w = __fadd_rn(hv.w, __fmul_rn(__fmul_rn((float)sum.w, sw), sx));
         reinterpret_cast<float4*>(h)[i] = hv;
     }
-    if (tid == 0 && !ok_s) atomicExch(v.err, kErrTpTimeout);
 }
 
 }  // namespace
@@ -268,6 +284,7 @@ bt_status tp_peer_create(void** out, int rank, int size, int max_batch, int hidd
     p->view.lay = TpLayout{size, max_batch, hidden};
     p->view.rank = rank;
     p->view.err = err;
+    p->view.wait_ns = 5000000000ull;  // 5 s: longer than any host-side stall between two ranks' launches
     // plain cudaMalloc memory: IPC handles cannot be taken from pool allocations
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&p->local), p->view.lay.bytes());
     if (e == cudaSuccess) e = cudaMemset(p->local, 0, p->view.lay.bytes());
@@ -311,6 +328,22 @@ bt_status tp_peer_import(void* peer, const void* handles) {
     }
     p->ready = true;
     return BT_OK;
+}
+
+void tp_peer_set_wait(void* peer, unsigned long long ns) {
+    if (peer) reinterpret_cast<TpPeer*>(peer)->view.wait_ns = ns;
+}
+
+// Back to epoch 0: clears the epoch counters and every flag of the local inbox.  All ranks have to
+// do this between the same two steps (the peers' next flags start from 1 again).
+cudaError_t tp_peer_reset(void* peer) {
+    TpPeer* p = reinterpret_cast<TpPeer*>(peer);
+    if (!p) return cudaSuccess;
+    const TpLayout& lay = p->view.lay;
+    cudaError_t e = cudaMemset(p->local + lay.flag_base(), 0, lay.bytes() - lay.flag_base());
+    if (e == cudaSuccess) e = cudaMemset(p->view.epoch, 0, 2 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return e;
 }
 
 bool tp_peer_ready(const void* peer) { return peer && reinterpret_cast<const TpPeer*>(peer)->ready; }

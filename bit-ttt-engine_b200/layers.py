@@ -143,6 +143,19 @@ class BitLinear:
         self._create(packed, scales, n_bases)
         return self
 
+    @classmethod
+    def from_l3(cls, packed_l3: np.ndarray, scales, out_dim: int, in_dim: int, device: int = 0) -> "BitLinear":
+        """packed_l3: the legacy int8 layout [out, in/4, n_bases, 4] of
+        tools/conversion/convert_adaptive.py:43-83 (values -1/0/+1, one byte each); converted to the
+        2-bit layout on the host, then handled like any converted checkpoint."""
+        w = np.ascontiguousarray(packed_l3).view(np.int8)
+        if w.ndim != 4 or w.shape[0] != out_dim or w.shape[1] != in_dim // 4 or w.shape[3] != 4:
+            raise ValueError(f"legacy layout has shape {w.shape}, expected ({out_dim}, {in_dim // 4}, n_bases, 4)")
+        n_bases = w.shape[2]
+        l2 = np.zeros((out_dim, in_dim // 4, n_bases), np.uint8)
+        check(lib().bt_convert_l3_to_l2(w.ctypes.data, out_dim, in_dim, n_bases, l2.ctypes.data))
+        return cls.from_packed(l2, scales, out_dim, in_dim, device)
+
     def _create(self, packed, scales, n_bases):
         scales = np.ascontiguousarray(scales, np.float32)
         packed = np.ascontiguousarray(packed, np.uint8)

@@ -33,6 +33,8 @@ def _bind():
     L.bt_kv_reset.argtypes = [vp]
     L.bt_kv_destroy.argtypes = [vp]
     L.bt_kv_export.argtypes = [vp, i64, i64, vp, vp, vp, vp]
+    L.bt_kv_import.argtypes = [vp, i64, i64, vp, vp, vp, vp]
+    L.bt_kv_append.argtypes = [vp, vp, vp, vp, i64, vp]
     L.bt_attn_decode.argtypes = [vp, vp, vp, i64, i64, C.c_double, vp, vp]
     L.bt_linear_create_fused.argtypes = [C.POINTER(vp), C.POINTER(vp), C.POINTER(i64), vp, i32, i64, i32]
     L.bt_model_create.argtypes = [C.POINTER(vp), C.POINTER(_CModelConfig), i32]
@@ -59,6 +61,8 @@ def _bind():
     L.bt_model_seek.argtypes = [vp, i32]
     L.bt_model_tp_peer_export.argtypes = [vp, C.c_char_p]
     L.bt_model_tp_peer_import.argtypes = [vp, C.c_char_p]
+    L.bt_model_tp_set_timeout.argtypes = [vp, i32]
+    L.bt_model_tp_destroy.argtypes = [vp]
     L.bt_model_enqueue_products.argtypes = [vp, i32, vp, C.POINTER(i32)]
     L.bt_model_launches_per_step.argtypes = [vp, i32]
     L._model_bound = True
@@ -104,6 +108,21 @@ class QuantizedKVCache:
         check(self._L.bt_kv_export(self._h, b, t_len, kq.ctypes.data, ks.ctypes.data, vq.ctypes.data,
                                    vs.ctypes.data))
         return kq, ks, vq, vs
+
+    def load(self, b: int, kq, ks, vq, vs):
+        """Restores rows [0, t_len) of sequence b from arrays shaped like export()'s."""
+        kq = np.ascontiguousarray(kq, np.uint8)
+        vq = np.ascontiguousarray(vq, np.uint8)
+        ks = np.ascontiguousarray(ks, np.float32)
+        vs = np.ascontiguousarray(vs, np.float32)
+        t_len = kq.shape[1]
+        check(self._L.bt_kv_import(self._h, b, t_len, kq.ctypes.data, ks.ctypes.data, vq.ctypes.data, vs.ctypes.data))
+
+    def append(self, k, v, pos):
+        """QuantizedKVCache::append (layers/kv_cache.rs:50-92): k, v CUDA f32 [batch, n_kv, head_dim]
+        (k already rotated), pos CUDA int32 [batch]."""
+        k, v = k.contiguous(), v.contiguous()
+        check(self._L.bt_kv_append(self._h, _ptr(k), _ptr(v), _ptr(pos), k.shape[0], _stream_ptr(k.device.index)))
 
     def __del__(self):
         try:
@@ -185,6 +204,13 @@ class BitLlama:
         if len(blob) != 64 * self.tp_size:
             raise ValueError("tp_peer_init expects one 64-byte handle per rank")
         check(self._L.bt_model_tp_peer_import(self._h, blob))
+
+    def tp_set_timeout(self, milliseconds: int) -> None:
+        """How long an exchange kernel waits for its peers before the step fails with BT_ERR_TIMEOUT."""
+        check(self._L.bt_model_tp_set_timeout(self._h, milliseconds))
+
+    def tp_destroy(self) -> None:
+        check(self._L.bt_model_tp_destroy(self._h))
 
     def tp_peer_disable(self) -> None:
         """Back to the NCCL exchange (every rank must call it)."""

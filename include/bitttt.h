@@ -56,6 +56,14 @@ bt_status bt_pack_ternary(const float* w_host, int64_t n_elem, uint8_t* out_host
 /* PackedTensor::unpack, RE/kernels/packing.rs:108-133. */
 bt_status bt_unpack_ternary(const uint8_t* packed_host, int64_t n_elem, float scale, float* out_host);
 
+/* Reader for the legacy one-byte-per-weight layout of tools/conversion/convert_adaptive.py:43-83
+ * ([n_out, k_in/4, n_bases, 4] int8, the input of adaptive_gemm_n3_kernel_f32,
+ * RE/kernels/adaptive_bit_op.cu:74-161): rewrites it as the 2-bit layout [n_out, k_in/4, n_bases]
+ * (n_out * k_in/4 * n_bases bytes) that bt_linear_create accepts, so that such a checkpoint streams
+ * 2 bits per weight and basis instead of 8.  Values other than -1 / 0 / +1 give BT_ERR_ARG. */
+bt_status bt_convert_l3_to_l2(const int8_t* l3_host, int64_t n_out, int64_t k_in, int n_bases,
+                              uint8_t* l2_out_host);
+
 /* ---- BitLinear ---------------------------------------------------------------------- */
 
 typedef struct bt_linear bt_linear;
@@ -145,7 +153,9 @@ bt_status bt_act_quant(const void* x_dev, bt_dtype x_dtype, int64_t m, int64_t k
  *  - Nothing in the array needs to start at zero: each call rewrites every byte it later
  *    reads (the quantiser zero-fills the padding up to k_pad).
  *  - The first call on a device looks up the array's device address
- *    (cudaGetSymbolAddress); make that first call outside of any stream capture.
+ *    (cudaGetSymbolAddress) and, like the first call of any forward entry point, sets the
+ *    product kernel's shared-memory attribute (cudaFuncSetAttribute); neither allocates, but
+ *    make that first call outside of any stream capture.
  * Same arithmetic, arguments and errors as bt_linear_forward otherwise. */
 bt_status bt_linear_forward_noalloc(bt_linear* lin, const void* x_dev, int64_t m, int64_t x_k,
                                     bt_dtype x_dtype, void* y_dev, bt_dtype y_dtype, void* stream);
@@ -187,6 +197,20 @@ bt_status bt_kv_destroy(bt_kv_cache* cache);
  * u8, k_s/v_s [n_kv, t_len] f32 (any may be NULL).  Synchronous; for tests and state I/O. */
 bt_status bt_kv_export(bt_kv_cache* cache, int64_t b, int64_t t_len, uint8_t* k_q_host,
                        float* k_s_host, uint8_t* v_q_host, float* v_s_host);
+
+/* The inverse of bt_kv_export: writes position range [0, t_len) of sequence b from host arrays of the
+ * same shapes (any may be NULL).  With bt_kv_export it carries a cache across processes, next to the
+ * TTT states of Llama::save_memory / load_memory (RE/model/llama.rs:575-611); bt_model_seek then
+ * continues decoding at t_len.  Synchronous. */
+bt_status bt_kv_import(bt_kv_cache* cache, int64_t b, int64_t t_len, const uint8_t* k_q_host,
+                       const float* k_s_host, const uint8_t* v_q_host, const float* v_s_host);
+/* QuantizedKVCache::append (RE/layers/kv_cache.rs:50-92) on its own, one new token per sequence:
+ * k_dev, v_dev [batch, n_kv_heads, head_dim] f32 (keys already rotated, as the caller at
+ * RE/layers/attention.rs:180-196 passes them) are quantised (RE/layers/kv_cache.rs:95-119) into row
+ * pos_dev[b] of sequence b.  Rows with pos outside [0, max_seq_len) are skipped.  Unlike the reference
+ * it does not return the dequantised cache: bt_attn_decode reads the cache in place. */
+bt_status bt_kv_append(bt_kv_cache* cache, const float* k_dev, const float* v_dev, const int32_t* pos_dev,
+                       int64_t batch, void* stream);
 
 /* The attention core of BitAttention::forward for one new token per sequence
  * (RE/layers/attention.rs:166-217 with seq_len == 1): RoPE at pos[b] on q and k
@@ -258,11 +282,21 @@ bt_status bt_model_tp_init(bt_model* m, const uint8_t* id128);
  * exchange the handles by any transport, and each calls bt_model_tp_peer_import with all
  * tp_size handles in rank order (64 bytes each; its own entry is ignored).  One process per
  * GPU, all on one node with peer access.  Results are bit-identical to the NCCL path and to
- * tp_size = 1.  A rank that never arrives makes the others' bounded waits run out: the step
- * completes with garbage and bt_device_check reports BT_ERR_TIMEOUT.  bt_model_tp_peer_import with
- * handles = NULL drops the inbox and returns the model to the NCCL path (all ranks must do the same). */
+ * tp_size = 1.  A rank that never arrives makes the others' waits run out (they are bounded in time,
+ * 5 s unless bt_model_tp_set_timeout says otherwise): the exchange leaves the hidden state as it was,
+ * the remaining exchanges of the step no longer wait, bt_model_forward_one returns BT_ERR_TIMEOUT
+ * (callers of bt_model_step_dev see it through bt_device_check at their next synchronisation), and
+ * decoding continues only after every rank has called bt_model_reset, which also restarts the exchange
+ * epochs.  bt_model_tp_peer_import with handles = NULL drops the inbox and returns the model to the
+ * NCCL path (all ranks must do the same). */
 bt_status bt_model_tp_peer_export(bt_model* m, uint8_t* handle64_out);
 bt_status bt_model_tp_peer_import(bt_model* m, const uint8_t* handles);
+/* How long an exchange kernel waits for its peers (milliseconds, >= 1).  Drops the captured step graphs. */
+bt_status bt_model_tp_set_timeout(bt_model* m, int milliseconds);
+/* Leaves tensor parallelism: closes the peer mappings and destroys the communicator (collective in the
+ * sense that every rank should do it before any rank's inbox memory goes away).  bt_model_destroy does
+ * the same implicitly. */
+bt_status bt_model_tp_destroy(bt_model* m);
 bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
                               int64_t n_out, int64_t k_in, float scale);
 bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int layer, const float* data_host,

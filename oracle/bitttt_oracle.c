@@ -11,8 +11,12 @@
  *     known-answer tests of crates/rust_engine/src/kernels/packing.rs:156-261 and by
  *     fixtures generated from the reference's Python converter
  *     (tools/conversion/convert_llama_v2.py:28-72,111-151).
- *   - BitLinear forward, TTT, Q8 KV cache, RoPE, attention, RMSNorm, SwiGLU: the
- *     reference holds no value test for them and cannot be compiled here (no Rust
+ *   - the ternary product (oracle_bitlinear_f32 / _i32 and the multi-basis sum) is
+ *     pinned against the reference's own CUDA kernels (kernels/bit_op.cu:4-45,
+ *     kernels/adaptive_bit_op.cu:74-161), compiled unchanged from the reference's
+ *     source files by `make ref` into oracle/_ref/ and run in the GPU tests.
+ *   - TTT, Q8 KV cache, RoPE, attention, RMSNorm, SwiGLU: the reference holds no
+ *     value test for them and its Rust host code cannot be compiled here (no Rust
  *     toolchain), so for these functions PARITY IS UNPINNED: they follow the cited
  *     lines operation by operation, nothing more.
  *
@@ -22,10 +26,9 @@
  * Reductions and transcendentals: the reference evaluates sums (RMSNorm mean, L2 norm,
  * matmul rows, softmax) and exp/cos/sin in f32 through candle ops whose evaluation order
  * and libm are not visible in its tree.  Here they are accumulated / evaluated in f64 and
- * rounded to f32 once, which is within one f32 ulp of any f32 evaluation order and - more
- * to the point - reproducible: the CUDA kernels do the same, so every value that feeds an
- * int8 quantiser (a discontinuous step) is the same on both sides.  Pointwise f32
- * operations keep the reference's order.  Built with -ffp-contract=off.
+ * rounded to f32 once: the correctly rounded value, within one f32 ulp of any f32
+ * evaluation order and independent of how a checked implementation orders its sums.
+ * Pointwise f32 operations keep the reference's order.  Built with -ffp-contract=off.
  */
 #include <math.h>
 #include <stdint.h>

@@ -10,9 +10,12 @@ Two things live here:
   that strings the C functions together in the reference's order.
 
 Parity pin status is stated in the header of ``bitttt_oracle.c``: packing is pinned by
-the reference's known-answer tests and converter-generated fixtures; every other
-function is "parity unpinned" (no reference value test exists, and the reference cannot
-be compiled in this environment).
+the reference's known-answer tests and converter-generated fixtures; the ternary product
+(``bitlinear_f32`` / ``bitlinear_i32``, and the multi-basis sum) is pinned against the
+reference's own two CUDA kernels, compiled unchanged into ``oracle/_ref/libref_kernels.so``
+(``ref_lib()``; they need a GPU to run, so that check lives in the GPU tests); every other
+function is "parity unpinned" (no reference value test exists, and the reference's Rust
+host code cannot be compiled in this environment).
 
 Only tests, the smoke check and the benchmark's CPU-baseline leg may import this module.
 """
@@ -27,7 +30,9 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "libbitttt_oracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libref_kernels.so")
 _LIB = None
+_REF_LIB = None
 
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
@@ -43,6 +48,59 @@ def build(force: bool = False) -> str:
     if force or stale:
         subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
     return _SO
+
+
+def build_ref(reference_dir: str) -> str:
+    """Compile the reference's own CUDA kernels (kernels/bit_op.cu, kernels/adaptive_bit_op.cu)
+    from `reference_dir`, where they lie, into oracle/_ref/libref_kernels.so."""
+    subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE={reference_dir}"], check=True, capture_output=True)
+    return _REF_SO
+
+
+def ref_lib():
+    """ctypes handle on the reference-built kernels, or None when they were not built."""
+    global _REF_LIB
+    if _REF_LIB is None and os.path.exists(_REF_SO):
+        L = C.CDLL(_REF_SO)
+        L.ref_bit_linear_forward.argtypes = [_f32p, _u8p, _f32p, C.c_float, C.c_int, C.c_int, C.c_int]
+        L.ref_adaptive_gemm_n3.argtypes = [_f32p, _i8p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
+        _REF_LIB = L
+    return _REF_LIB
+
+
+def ref_bit_linear_forward(x, packed, n, scale):
+    """The reference's bit_linear_forward kernel (kernels/bit_op.cu:4-45) run on the current
+    CUDA device: x f32 [M, K], packed L1 bytes [N, K/4] -> y f32 [M, N]."""
+    x = _f32(x)
+    m, k = x.shape
+    y = np.zeros((m, n), dtype=np.float32)
+    rc = ref_lib().ref_bit_linear_forward(x, np.ascontiguousarray(packed, np.uint8).reshape(-1), y, scale, m, k, n)
+    if rc != 0:
+        raise RuntimeError(f"reference kernel launch failed: cudaError {rc}")
+    return y
+
+
+def pack_l3(bases):
+    """pack_interleaved_blocks of tools/conversion/convert_adaptive.py:43-83: bases int8
+    [B, N, K] with values -1/0/+1 -> bytes [N, K/4, B, 4] (one byte per weight)."""
+    bases = np.ascontiguousarray(bases, np.int8)
+    b, n, k = bases.shape
+    return np.ascontiguousarray(bases.reshape(b, n, k // 4, 4).transpose(1, 2, 0, 3))
+
+
+def ref_adaptive_gemm_n3(x, packed_l3, scales):
+    """The reference's adaptive_gemm_n3_kernel_f32 (kernels/adaptive_bit_op.cu:74-161) run on the
+    current CUDA device: x f32 [M, K], packed_l3 int8 [N, K/4, 3, 4], 3 scales -> y f32 [M, N]."""
+    x = _f32(x)
+    m, k = x.shape
+    w = np.ascontiguousarray(packed_l3).view(np.int8)
+    n = w.shape[0]
+    assert w.shape == (n, k // 4, 3, 4)
+    y = np.zeros((m, n), dtype=np.float32)
+    rc = ref_lib().ref_adaptive_gemm_n3(x, w.reshape(-1), _f32(scales), y, m, k, n)
+    if rc != 0:
+        raise RuntimeError(f"reference kernel launch failed: cudaError {rc}")
+    return y
 
 
 def lib():

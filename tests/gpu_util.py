@@ -18,3 +18,30 @@ def ternary_packed(rng, n, k, p_code3=0.0):
         codes = np.where(rng.random((n, k)) < p_code3, 3, codes).astype(np.uint8)
     c = codes.reshape(n, k // 4, 4)
     return (c[..., 0] | (c[..., 1] << 2) | (c[..., 2] << 4) | (c[..., 3] << 6)).astype(np.uint8)
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def seed_kv_caches(gpu, states, cfg, t0, rng):
+    """Fills positions [0, t0) of every layer's Q8 KV cache with seeded random rows - the same
+    bytes and scales on the GPU (bt_kv_import) and in the oracle's per-sequence states - and
+    declares t0 positions consumed, so that the next decode step attends over a long context
+    without t0 steps of prefill.  Scales are drawn around the magnitude real rows have."""
+    n_kv, hd = cfg.n_kv_heads, cfg.hidden_dim // cfg.n_heads
+    for li in range(cfg.num_layers):
+        cache = gpu.kv_cache(li)
+        for b, st in enumerate(states):
+            kq = rng.integers(0, 256, size=(n_kv, t0, hd), dtype=np.uint8)
+            vq = rng.integers(0, 256, size=(n_kv, t0, hd), dtype=np.uint8)
+            ks = rng.uniform(0.005, 0.03, size=(n_kv, t0)).astype(np.float32)
+            vs = rng.uniform(0.005, 0.03, size=(n_kv, t0)).astype(np.float32)
+            cache.load(b, kq, ks, vq, vs)
+            st.kq[li] = [np.ascontiguousarray(kq[:, t]) for t in range(t0)]
+            st.vq[li] = [np.ascontiguousarray(vq[:, t]) for t in range(t0)]
+            st.ks[li] = [np.ascontiguousarray(ks[:, t]) for t in range(t0)]
+            st.vs[li] = [np.ascontiguousarray(vs[:, t]) for t in range(t0)]
+    for st in states:
+        st.pos = t0
+    gpu.seek(t0)

@@ -111,3 +111,81 @@ def test_kv_cache_reset_and_ones(bt):
     cache.reset()
     kq, ks, vq, vs = cache.export(0, 1)
     assert (kq == 128).all() and (ks == 0).all()
+
+
+def test_kv_append_standalone_and_import_export(bt, oracle):
+    # QuantizedKVCache::append on its own (layers/kv_cache.rs:50-92): stored bytes and scales equal
+    # the oracle's quantize_q8; export -> import into a second cache -> same attention output
+    rng = np.random.default_rng(123)
+    batch, n_kv, hd, n_heads, steps = 3, 2, 64, 8, 5
+    cache = bt.QuantizedKVCache(16, batch, n_kv, hd)
+    ks_all, vs_all = [], []
+    for p in range(steps):
+        k = rng.normal(0, 1, (batch, n_kv, hd)).astype(np.float32)
+        v = rng.normal(0, 1, (batch, n_kv, hd)).astype(np.float32)
+        if p == 2:
+            v[1] = 0  # an all-zero row: scale 0, bytes 128
+        pos = torch.full((batch,), p, dtype=torch.int32, device="cuda")
+        cache.append(torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), pos)
+        ks_all.append(k); vs_all.append(v)
+    for b in range(batch):
+        kq, ks, vq, vs = cache.export(b, steps)
+        for p in range(steps):
+            q0, s0 = oracle.kv_quant(ks_all[p][b])
+            assert np.array_equal(kq[:, p], q0) and np.array_equal(ks[:, p], s0)
+            q1, s1 = oracle.kv_quant(vs_all[p][b])
+            assert np.array_equal(vq[:, p], q1) and np.array_equal(vs[:, p], s1)
+    kq, ks, vq, vs = cache.export(1, steps)
+    assert (vq[:, 2] == 128).all() and (vs[:, 2] == 0).all()
+    # a second cache restored from the exported rows attends identically
+    other = bt.QuantizedKVCache(16, batch, n_kv, hd)
+    for b in range(batch):
+        other.load(b, *cache.export(b, steps))
+    qkv = torch.from_numpy(rng.normal(0, 1, (batch, (n_heads + 2 * n_kv) * hd)).astype(np.float32)).cuda()
+    pos = torch.full((batch,), steps, dtype=torch.int32, device="cuda")
+    a = bt.attn_decode(cache, qkv, pos, n_heads, 10000.0)
+    b2 = bt.attn_decode(other, qkv, pos, n_heads, 10000.0)
+    assert torch.equal(a, b2)
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd,t0,batch", [(32, 8, 128, 2040, 1), (32, 4, 64, 700, 1), (8, 8, 96, 300, 2),
+                                                         (32, 8, 128, 1500, 24)])
+def test_attention_long_context_many_spans(bt, oracle, n_heads, n_kv, hd, t0, batch):
+    # a long seeded context: with one sequence the positions are cut over a whole cluster of spans
+    # (16 x 128 at 2048), with 24 sequences x 8 KV heads every CTA walks many tiles of its own
+    rng = np.random.default_rng(t0 + hd)
+    max_seq = t0 + 16
+    cache = bt.QuantizedKVCache(max_seq, batch, n_kv, hd)
+    seeds = []
+    for b in range(batch):
+        kq = rng.integers(0, 256, size=(n_kv, t0, hd), dtype=np.uint8)
+        vq = rng.integers(0, 256, size=(n_kv, t0, hd), dtype=np.uint8)
+        ks = rng.uniform(0.005, 0.03, size=(n_kv, t0)).astype(np.float32)
+        vs = rng.uniform(0.005, 0.03, size=(n_kv, t0)).astype(np.float32)
+        cache.load(b, kq, ks, vq, vs)
+        seeds.append([kq, ks, vq, vs])
+    theta = 500000.0
+    qkv_dim = (n_heads + 2 * n_kv) * hd
+    for step in range(10):
+        p = t0 + step
+        qkv = rng.normal(0, 1, (batch, qkv_dim)).astype(np.float32)
+        pos = torch.full((batch,), p, dtype=torch.int32, device="cuda")
+        out = bt.attn_decode(cache, torch.from_numpy(qkv).cuda(), pos, n_heads, theta).cpu().numpy()
+        for b in range(batch):
+            q = oracle.rope(qkv[b, :n_heads * hd].reshape(n_heads, hd), p, theta)
+            k = oracle.rope(qkv[b, n_heads * hd:(n_heads + n_kv) * hd].reshape(n_kv, hd), p, theta)
+            v = qkv[b, (n_heads + n_kv) * hd:].reshape(n_kv, hd)
+            kq1, ks1 = oracle.kv_quant(k)
+            vq1, vs1 = oracle.kv_quant(v)
+            s = seeds[b]
+            s[0] = np.concatenate([s[0], kq1[:, None]], 1); s[1] = np.concatenate([s[1], ks1[:, None]], 1)
+            s[2] = np.concatenate([s[2], vq1[:, None]], 1); s[3] = np.concatenate([s[3], vs1[:, None]], 1)
+            if batch > 4 and b % 5 != 0:
+                continue  # the oracle checks every fifth sequence of the large batch
+            t = p + 1
+            kd = oracle.kv_dequant(s[0].reshape(n_kv * t, hd), s[1].reshape(-1)).reshape(n_kv, t, hd)
+            vd = oracle.kv_dequant(s[2].reshape(n_kv * t, hd), s[3].reshape(-1)).reshape(n_kv, t, hd)
+            ref = oracle.attn_decode(q, kd, vd).reshape(-1)
+            assert rel_err(out[b], ref) <= REL_TOL, (step, b, rel_err(out[b], ref))
+            assert rel_err(out[b], ref) <= 2e-5, (step, b, rel_err(out[b], ref))  # expected accuracy of the f32 path
+    assert bt.lib().bt_device_check(0) == 0

@@ -41,3 +41,15 @@ def test_tp2_model_matches_oracle_and_ranks_agree(use_peer):
         worst, same0 = res[0].split()
         assert float(worst) <= 1e-3 and same0 == "1"
         assert res[1].split()[1] == "1"
+
+
+@pytest.mark.gpu
+def test_peer_exchange_wait_runs_out_without_a_fault():
+    # failure detection without a GPU fault: the missing rank is made on the host (it never launches)
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(tp_common.gpu_timeout_worker, args=(2, _free_port(), d), nprocs=2, join=True)
+        res = _results(d, 2)
+        assert res[0] == "status -6 clean 1 usable 1 fast 1", res[0]  # BT_ERR_TIMEOUT
+        assert res[1] == "idle"

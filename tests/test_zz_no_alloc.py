@@ -6,7 +6,8 @@ bt_linear_forward: outputs are caller-owned and the scratch for the quantised ac
 a fixed array inside the library.  The test drives it through the C ABI twice in a row with
 different inputs (the array keeps the previous call's contents) and checks each result
 against bt_linear_forward, which must agree bit for bit (the stated tolerance for f32
-outputs is 1e-3 relative), and checks that oversize requests are refused.
+outputs is 1e-3 relative), and against the CPU oracle; it checks that the calls leave the
+device's free memory untouched, that several bases work, and that oversize requests are refused.
 
 This file sorts last on purpose: a run that stops at the first failure has then already
 executed every other test.
@@ -24,7 +25,7 @@ pytestmark = pytest.mark.gpu
 REL_TOL = 1e-3
 
 
-def test_noalloc_matches_forward_two_calls_in_a_row():
+def test_noalloc_matches_forward_two_calls_in_a_row(oracle):
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
     bt = load_bt()
@@ -45,12 +46,45 @@ def test_noalloc_matches_forward_two_calls_in_a_row():
         e, g = expect.cpu().numpy(), got.cpu().numpy()
         assert np.abs(g - e).max() <= REL_TOL * np.abs(e).max()
         assert np.array_equal(g, e)
+        ref = oracle.bitlinear_q(x.cpu().numpy(), packed, [0.016], n)  # and the CPU oracle
+        assert np.abs(g - ref).max() <= REL_TOL * np.abs(ref).max()
+        assert np.array_equal(g, ref)
     # bf16 in and out through the Python mirror
     xb = torch.from_numpy(rng.normal(0, 1, (2, k)).astype(np.float32)).cuda().bfloat16()
     out = torch.empty((2, n), dtype=torch.bfloat16, device="cuda")
     lin.forward_noalloc(xb, out)
     assert torch.equal(out, lin.forward(xb))
     assert L.bt_device_check(0) == bt.BT_OK
+
+
+def test_noalloc_allocates_nothing_and_handles_several_bases(oracle):
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    bt = load_bt()
+    L = bt.lib()
+    rng = np.random.default_rng(79)
+    n, k, nb = 96, 320, 2
+    bases = rng.integers(-1, 2, size=(nb, n, k)).astype(np.int8)
+    packed = oracle.pack_l2(bases)
+    scales = np.array([0.02, 0.005], np.float32)
+    lin = bt.BitLinear.from_packed(packed, scales, n, k)
+    x = torch.from_numpy(rng.normal(0, 1, (5, k)).astype(np.float32)).cuda()
+    out = torch.empty((5, n), device="cuda")
+    lin.forward_noalloc(x, out)  # first call: symbol lookup and kernel attributes
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(4):
+        lin.forward_noalloc(x, out)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "bt_linear_forward_noalloc changed the device's free memory"
+    ref = oracle.bitlinear_q(x.cpu().numpy(), packed, scales, n, n_bases=nb)
+    assert np.array_equal(out.cpu().numpy(), ref)
+    # several bases with a bf16 output would need an f32 staging buffer: refused, nothing launched
+    outb = torch.empty((5, n), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(bt.BitTTTError) as ei:
+        lin.forward_noalloc(x, outb)
+    assert ei.value.status == bt.BT_ERR_ARG
 
 
 def test_noalloc_rejects_oversize_requests():

@@ -94,3 +94,49 @@ def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
     open(os.path.join(result_dir, f"rank{rank}.txt"), "w").write(f"{worst} {int(same)}")
     del model
     dist.destroy_process_group()
+
+
+def gpu_timeout_worker(rank, world, port, result_dir):
+    """A rank that never joins: both ranks of a 2-way tensor-parallel model live on GPU 0 and
+    exchange their inbox handles, but only rank 0 ever runs a step.  Its exchange kernels wait for
+    flags that rank 1 never writes; the wait is bounded, so the step must come back with
+    BT_ERR_TIMEOUT (no fault, no hang) and the device must stay usable.  Rank 1 launches nothing
+    while rank 0 runs, so no two kernels ever wait on one another on the one GPU."""
+    import time
+    import torch
+    dist = _init(rank, world, port, "gloo")
+    torch.cuda.set_device(0)
+    bt = importlib.import_module("bit-ttt-engine_b200")
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    from oracle import oracle as orc
+    cfg = syn.BitLlamaConfig("llama", 1000, 256, 2, 8, 4, 512, max_position_embeddings=64)
+    w = syn.make_weights(cfg, seed=3000)
+    model = syn.build_model(w, max_batch=2, device=0, tp_rank=rank, tp_size=world)
+    handles = [None] * world
+    dist.all_gather_object(handles, model.tp_peer_handle())
+    model.tp_peer_init(handles)
+    result = "idle"
+    if rank == 0:
+        model.tp_set_timeout(50)
+        t0 = time.perf_counter()
+        try:
+            model.forward_one(np.array([3, 4], np.int32))
+            result = "no error"
+        except bt.BitTTTError as exc:
+            result = f"status {exc.status}"
+        elapsed = time.perf_counter() - t0
+        # the error was consumed by the failing call; the device answers and computes correctly
+        clean = bt.lib().bt_device_check(0) == bt.BT_OK
+        rng = np.random.default_rng(1)
+        wd = rng.normal(0, 0.02, (64, 128)).astype(np.float32)
+        x = rng.normal(0, 1, (2, 128)).astype(np.float32)
+        lin = bt.BitLinear.load(128, 64, wd, device=0)
+        lin.precompute_packed()
+        y = lin.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+        p, s = orc.pack_l1(wd)
+        usable = bool(np.array_equal(y, orc.bitlinear_q(x, p, [s], 64)))
+        result += f" clean {int(clean)} usable {int(usable)} fast {int(elapsed < 20.0)}"
+    dist.barrier()  # rank 1 stays alive (its inbox mapped) until rank 0 is done
+    open(os.path.join(result_dir, f"rank{rank}.txt"), "w").write(result)
+    del model
+    dist.destroy_process_group()
