@@ -424,19 +424,37 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
     // Every CTA of the cluster finishes the output columns rank, rank + S, ... from the partials of all spans.
     cluster_sync_all();  // partials of every span written and visible cluster-wide
     {
-        const uint32_t S = (uint32_t)a.splits, rank = cluster_ctarank();
+        // The output columns are dealt evenly to the CTAs of the cluster.  All remote loads of a thread are
+        // issued before the first use (fixed trip counts, predicated), so that their latencies overlap.
+        const int S = a.splits, rank = (int)cluster_ctarank();
+        const int total = NREP * hd;
+        const int per_cta = (total + S - 1) / S;
         float amax = 0.0f;
-        for (int it = (int)rank * kAttnThreads + tid; it < NREP * hd; it += (int)S * kAttnThreads) {
+        for (int i = tid; i < per_cta; i += kAttnThreads) {
+            const int it = rank * per_cta + i;
+            if (it >= total) break;
             const int h = it / hd;
+            float ms[kMaxCluster], ls[kMaxCluster], os[kMaxCluster];
+#pragma unroll
+            for (int s2 = 0; s2 < kMaxCluster; ++s2) {
+                ms[s2] = -INFINITY; ls[s2] = 0.0f; os[s2] = 0.0f;
+                if (s2 < S) {
+                    ms[s2] = ld_cluster_f32(&sm.ml[0][h], (uint32_t)s2);
+                    ls[s2] = ld_cluster_f32(&sm.ml[1][h], (uint32_t)s2);
+                    os[s2] = ld_cluster_f32(&sm.opart[it], (uint32_t)s2);
+                }
+            }
             float m = -INFINITY;
-            for (uint32_t s2 = 0; s2 < S; ++s2) m = fmaxf(m, ld_cluster_f32(&sm.ml[0][h], s2));
+#pragma unroll
+            for (int s2 = 0; s2 < kMaxCluster; ++s2) m = fmaxf(m, ms[s2]);
             float num = 0.0f, den = 0.0f;
-            for (uint32_t s2 = 0; s2 < S; ++s2) {
-                const float ms = ld_cluster_f32(&sm.ml[0][h], s2);
-                if (ms == -INFINITY) continue;  // a span without positions weighs nothing (and its output is undefined)
-                const float w = expf(__fsub_rn(ms, m));
-                den = fmaf(ld_cluster_f32(&sm.ml[1][h], s2), w, den);
-                num = fmaf(ld_cluster_f32(&sm.opart[it], s2), w, num);
+#pragma unroll
+            for (int s2 = 0; s2 < kMaxCluster; ++s2) {
+                // a span without positions (maximum -inf) weighs nothing; what its output cells hold is undefined
+                const bool live = ms[s2] != -INFINITY;
+                const float w = live ? expf(__fsub_rn(ms[s2], m)) : 0.0f;
+                den = fmaf(ls[s2], w, den);
+                num = fmaf(live ? os[s2] : 0.0f, w, num);
             }
             const float o = __fdiv_rn(num, den);
             a.out[((int64_t)b * a.n_heads + kvh * NREP + h) * hd + (it % hd)] = o;
@@ -486,41 +504,49 @@ constexpr size_t kSmemBytes = sizeof(AttnSmem);
 constexpr size_t kHalfSm = 116 * 1024;
 static_assert(kSmemBytes <= 110 * 1024, "two CTAs of the attention kernel must fit one SM");
 
+// How many clusters of each size can be resident at once (a CTA then takes a whole SM): a cluster's CTAs
+// must sit in one GPC, so large clusters leave SMs unused, and a GPC with fewer SMs than the cluster
+// has CTAs holds none.  Filled once per kernel instance from cudaOccupancyMaxActiveClusters.
+struct ClusterTable {
+    bool ready = false;
+    int active[kMaxCluster + 1] = {0};  // active[s] = resident clusters of s CTAs (0: size unusable)
+};
+
 template <int NREP>
-cudaError_t configure_rep(int* max_cluster_out) {
-    static int max_cluster = 0;  // per process; every device of a process is the same GPU model
-    if (max_cluster == 0) {
+cudaError_t configure_rep(const ClusterTable** out) {
+    static ClusterTable table;  // per process; every device of a process is the same GPU model
+    if (!table.ready) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHalfSm);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(attn_decode_kernel<NREP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        int best = 8;
-        if (e == cudaSuccess) {
-            // clusters of 16 need 16 free SMs inside one GPC: ask the runtime whether one can be resident
+        const bool big = cudaFuncSetAttribute(attn_decode_kernel<NREP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        for (int s = 1; s <= kMaxCluster; ++s) {
+            if (s > 8 && !big) break;
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(1, kMaxCluster, 1);
+            cfg.gridDim = dim3(1, s, 1);
             cfg.blockDim = dim3(kAttnThreads);
             cfg.dynamicSmemBytes = kHalfSm;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
-            attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = kMaxCluster; attr[0].val.clusterDim.z = 1;
+            attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = (unsigned)s; attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<NREP>, &cfg) == cudaSuccess && n >= 1) best = kMaxCluster;
+            if (cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<NREP>, &cfg) == cudaSuccess) table.active[s] = n;
         }
-        cudaGetLastError();  // a refused attribute or query only lowers the cluster size
-        max_cluster = best;
+        cudaGetLastError();  // a refused attribute or query only rules a cluster size out
+        if (table.active[1] < 1) table.active[1] = 1;
+        table.ready = true;
     }
-    *max_cluster_out = max_cluster;
+    *out = &table;
     return cudaSuccess;
 }
 
 template <int NREP>
 cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
-    int max_cluster = 0;
-    cudaError_t e = configure_rep<NREP>(&max_cluster);
+    const ClusterTable* table = nullptr;
+    cudaError_t e = configure_rep<NREP>(&table);
     if (e != cudaSuccess) return e;
-    if (a.splits < 1 || a.splits > max_cluster) return cudaErrorInvalidValue;
+    if (a.splits < 1 || a.splits > kMaxCluster || table->active[a.splits] < 1) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.batch * a.n_kv, a.splits);
     cfg.blockDim = dim3(kAttnThreads);
@@ -538,39 +564,44 @@ cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
     return cudaLaunchKernelEx(&cfg, attn_decode_kernel<NREP>, a);
 }
 
-int attn_max_cluster(int rep) {
-    int mc = 8;
-    cudaError_t e = cudaSuccess;
+const ClusterTable* attn_cluster_table(int rep) {
+    const ClusterTable* t = nullptr;
+    cudaError_t e = cudaErrorInvalidValue;
     switch (rep) {
-        case 1: e = configure_rep<1>(&mc); break;
-        case 2: e = configure_rep<2>(&mc); break;
-        case 4: e = configure_rep<4>(&mc); break;
-        case 8: e = configure_rep<8>(&mc); break;
+        case 1: e = configure_rep<1>(&t); break;
+        case 2: e = configure_rep<2>(&t); break;
+        case 4: e = configure_rep<4>(&t); break;
+        case 8: e = configure_rep<8>(&t); break;
         default: break;
     }
-    return e == cudaSuccess ? mc : 8;
+    return e == cudaSuccess ? t : nullptr;
 }
 
 }  // namespace
 
 // Cuts the positions of a sequence into spans, one CTA each; the spans of a (sequence, KV head) pair
-// form one thread-block cluster.  Fewer pairs than SMs: as many spans as fit in one wave (a CTA then
-// takes a whole SM), up to the largest cluster the device schedules.  More pairs than SMs: two CTAs
-// share an SM and the CTAs run in waves; cutting the positions in 2..4 can fill the last wave better
-// (cost model = waves x (tiles of 128 positions per CTA + 1 for the fixed work of a CTA)).
+// form one thread-block cluster.  Fewer pairs than SMs: the largest cluster size, up to SMs / pairs, of
+// which as many clusters as there are pairs can be resident at once (one wave, a CTA per SM).  More
+// pairs than SMs: two CTAs share an SM and the CTAs run in waves; cutting the positions in 2..4 can fill
+// the last wave better (cost model = waves x (tiles of 128 positions per CTA + 1 for the fixed work of a CTA)).
 void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int rep, int* splits, int* span) {
     const int64_t pairs = batch * n_kv;
-    const int max_cluster = attn_max_cluster(rep);
-    int64_t want = (int64_t)sm_count / pairs;
-    if (want > max_cluster) want = max_cluster;
-    if (want < 1) want = 1;
+    const ClusterTable* table = attn_cluster_table(rep);
+    int64_t want = 1;
     if (pairs >= sm_count) {
         int64_t best_cost = -1;
         for (int64_t s = 1; s <= 4; ++s) {
+            if (table && table->active[s] < 1) continue;
             const int64_t sp = ((max_seq + s - 1) / s + 31) / 32 * 32;
             const int64_t waves = (pairs * s + 2 * sm_count - 1) / (2 * sm_count);
             const int64_t cost = waves * ((sp + kTilePos - 1) / kTilePos + 1);
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; want = s; }
+        }
+    } else {
+        const int64_t cap = (int64_t)sm_count / pairs < kMaxCluster ? (int64_t)sm_count / pairs : kMaxCluster;
+        for (int64_t s = cap; s >= 1; --s) {
+            const int act = table ? table->active[s] : (s <= 8 ? sm_count / (int)s : 0);
+            if (act >= pairs) { want = s; break; }
         }
     }
     const int64_t sp = ((max_seq + want - 1) / want + 31) / 32 * 32;

@@ -97,6 +97,7 @@ struct bt_model {
     int32_t* cand_idx = nullptr;
     int32_t* tokens_pinned = nullptr;
     int32_t* next_pinned = nullptr;
+    float* trace = nullptr;          // inspection aid: per-layer intermediate tensors of a step (caller's device buffer)
     unsigned int* err_pinned = nullptr;  // tensor parallel: the device error word as read after a step
     int host_pos = 0;
     int64_t ternary_bytes = 0;
@@ -147,6 +148,33 @@ bt_status quant_then_product(bt_model* m, bt_linear* lin, int pre, const float* 
     return BT_OK;
 }
 
+// Trace layout: [layer][h_in | qkv | att | h_mid | act | h_out], every part [max_batch, width] f32.
+// arch ttt: the "qkv" part holds the down-projected features and "att" the TTT prediction z.
+enum TraceSlot { TR_H_IN = 0, TR_QKV, TR_ATT, TR_H_MID, TR_ACT, TR_H_OUT, TR_SLOTS };
+void trace_widths(const bt_model* m, int64_t (&w)[TR_SLOTS]) {
+    const int64_t H = m->cfg.hidden_dim;
+    w[TR_H_IN] = H;
+    w[TR_QKV] = m->cfg.arch == 1 ? m->qkv_dim : m->d_small;
+    w[TR_ATT] = m->cfg.arch == 1 ? (int64_t)m->nh_l * m->head_dim : m->d_small;
+    w[TR_H_MID] = H;
+    w[TR_ACT] = m->i_l;
+    w[TR_H_OUT] = H;
+}
+int64_t trace_layer_floats(const bt_model* m) {
+    int64_t w[TR_SLOTS], n = 0;
+    trace_widths(m, w);
+    for (int i = 0; i < TR_SLOTS; ++i) n += w[i] * m->cfg.max_batch;
+    return n;
+}
+cudaError_t trace_copy(const bt_model* m, int layer, int slot, const float* src, int batch, cudaStream_t s) {
+    if (!m->trace) return cudaSuccess;
+    int64_t w[TR_SLOTS], off = 0;
+    trace_widths(m, w);
+    for (int i = 0; i < slot; ++i) off += w[i] * m->cfg.max_batch;
+    float* dst = m->trace + (int64_t)layer * trace_layer_floats(m) + off;
+    return cudaMemcpyAsync(dst, src, (size_t)batch * w[slot] * sizeof(float), cudaMemcpyDeviceToDevice, s);
+}
+
 bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
     const bt_model_config& c = m->cfg;
     const int H = c.hidden_dim, I = m->i_l, B = c.max_batch;
@@ -161,9 +189,12 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
         unsigned int* amax_core = m->absmax + ((size_t)li * 2 + 0) * B;
         unsigned int* amax_mlp = m->absmax + ((size_t)li * 2 + 1) * B;
         FusedIn norm1{PRO_RMSNORM, m->h, H, L.norm1, kRmsEps, nullptr};
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_IN, m->h, batch, s));
         if (c.arch == 0) {
             BT_CUDA_TRY(linear_product_fused(L.ttt_down->dev(), norm1, batch, m->feat, m->d_small, EPI_F32, nullptr, err, sm, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->feat, batch, s));
             BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s, amax_core, true));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->z, batch, s));
             FusedIn zin{PRO_ABSMAX, m->z, m->d_small, nullptr, 0.f, amax_core};
             BT_CUDA_TRY(linear_product_fused(L.ttt_up->dev(), zin, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
         } else {
@@ -185,7 +216,9 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = amax_core;
             a.pdl = true;
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->qkv, batch, s));
             BT_CUDA_TRY(launch_attn_decode(a, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->att, batch, s));
             FusedIn ain{PRO_ABSMAX, m->att, att_dim, nullptr, 0.f, amax_core};
             if (m->tp > 1 && tp_peer_ready(m->peer)) {
                 // row-parallel over NVLink peer memory: max of the quantisation scale, then the integer
@@ -207,12 +240,14 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             }
         }
         FusedIn norm2{PRO_RMSNORM, m->h, H, L.norm2, kRmsEps, nullptr};
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->h, batch, s));
         if (split_quant) {
             if ((qst = quant_then_product(m, L.gate_up_il, PRE_RMSNORM, m->h, H, L.norm2, H, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, s)) != BT_OK) return qst;
         } else {
             BT_CUDA_TRY(linear_product_fused(L.gate_up_il->dev(), norm2, batch, m->act, I, EPI_SWIGLU, amax_mlp, err, sm, s));
         }
         FusedIn din{PRO_ABSMAX, m->act, I, nullptr, 0.f, amax_mlp};
+        BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
         if (m->tp > 1 && tp_peer_ready(m->peer)) {
             BT_CUDA_TRY(launch_tp_peer_max(m->peer, 1, amax_mlp, batch, s));
             BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->acc_i32, H, EPI_I32, nullptr, err, sm, s));
@@ -228,6 +263,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
         } else {
             BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->h, H, EPI_F32_ACCUM, nullptr, err, sm, s));
         }
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
     }
     int n_cand = 0;
     BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
@@ -249,11 +285,14 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
         Layer& L = m->layers[(size_t)li];
         // x_norm = norm1(x)  (model/block.rs:98)
         //   (the row kernels write the int8 activations straight in the tensor-core product's layout)
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_IN, m->h, batch, s));
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm1, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
         if (c.arch == 0) {
             // TTTLayer::forward_update (layers/ttt.rs:48-74)
             BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->feat, m->d_small, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->feat, batch, s));
             BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->z, batch, s));
             BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), m->z, m->d_small, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes));
         } else {
             // BitAttention::forward (layers/attention.rs:149-225), seq_len 1
@@ -271,14 +310,19 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = nullptr;
             a.pdl = false;
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->qkv, batch, s));
             BT_CUDA_TRY(launch_attn_decode(a, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->att, batch, s));
             BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes));
         }
         // x = x + mlp(norm2(x))  (model/block.rs:119-131, layers/swiglu.rs:29-35)
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->h, batch, s));
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
         BT_CUDA_TRY(launch_gemm_tc(L.gate_up->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
-        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_i));
+        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, m->trace ? m->act : nullptr, s, m->qtc, kt_i));
+        BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
         BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
     }
     // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
     if (m->lm_tiles) {
@@ -552,7 +596,11 @@ bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
     static_assert(sizeof(m->graphs) / sizeof(m->graphs[0]) == 65, "graph table");
     cudaGraphExec_t& exec = m->graphs[batch];
     const uintptr_t marker = 1;  // "ran eagerly once" sentinel stored in the table
-    if (exec == nullptr) {
+    if (m->trace) {
+        // inspection: launch by launch with the copies into the trace buffer in between (never captured)
+        bt_status st = batch <= 8 ? enqueue_step_fused(m, batch, s) : enqueue_step(m, batch, s);
+        if (st != BT_OK) return st;
+    } else if (exec == nullptr) {
         bt_status st = batch <= 8 ? enqueue_step_fused(m, batch, s) : enqueue_step(m, batch, s);
         if (st != BT_OK) return st;
         exec = reinterpret_cast<cudaGraphExec_t>(marker);
@@ -630,26 +678,54 @@ extern "C" bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer) {
     if (!m || layer < 0 || layer >= (int)m->layers.size()) return nullptr;
     return m->layers[(size_t)layer].kv;
 }
+extern "C" int64_t bt_model_trace_floats(const bt_model* m) {
+    return (m && m->finalized) ? trace_layer_floats(m) * m->cfg.num_layers : 0;
+}
+extern "C" bt_status bt_model_set_trace(bt_model* m, float* trace_dev) {
+    if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_set_trace: model not finalized");
+    DeviceGuard guard(m->device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    m->trace = trace_dev;
+    return BT_OK;
+}
 extern "C" int64_t bt_model_ternary_bytes(const bt_model* m) { return m ? m->ternary_bytes : 0; }
 
-extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, void* stream, int* n_launches) {
+extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, int as_in_step, void* stream, int* n_launches) {
     if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_enqueue_products: model not finalized");
     if (batch < 1 || batch > m->cfg.max_batch) return set_error(BT_ERR_SHAPE, "batch %d outside 1..%d", batch, m->cfg.max_batch);
     DeviceGuard guard(m->device);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     unsigned int* err = device_error_word(m->device);
+    const bt_model_config& c = m->cfg;
     const int groups = (batch + 7) / 8;
     int launches = 0;
+    const bool fused = as_in_step && batch < kSplitQuantBatch && c.arch == 1 && m->tp == 1;
     // outputs go to the gate/up buffer (the largest activation buffer), never to h
-    for (auto& L : m->layers) {
-        bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up,
+    for (size_t li = 0; li < m->layers.size(); ++li) {
+        Layer& L = m->layers[li];
+        if (fused) {
+            // the launches of enqueue_step_fused, prologues and epilogues included, on whatever the
+            // activation buffers hold; the SwiGLU epilogue's absmax goes to a cell nobody reads
+            unsigned int* amax = m->absmax + (li * 2) * (size_t)c.max_batch;
+            FusedIn norm1{PRO_RMSNORM, m->h, c.hidden_dim, L.norm1, kRmsEps, nullptr};
+            BT_CUDA_TRY(linear_product_fused(L.qkv->dev(), norm1, batch, m->gu, m->qkv_dim, EPI_F32, nullptr, err, m->sm_count, s));
+            FusedIn ain{PRO_ABSMAX, m->att, m->nh_l * m->head_dim, nullptr, 0.f, amax};
+            BT_CUDA_TRY(linear_product_fused(L.o->dev(), ain, batch, m->gu, c.hidden_dim, EPI_F32_ACCUM, nullptr, err, m->sm_count, s));
+            FusedIn norm2{PRO_RMSNORM, m->h, c.hidden_dim, L.norm2, kRmsEps, nullptr};
+            BT_CUDA_TRY(linear_product_fused(L.gate_up_il->dev(), norm2, batch, m->gu, m->i_l, EPI_SWIGLU, amax, err, m->sm_count, s));
+            FusedIn din{PRO_ABSMAX, m->act, m->i_l, nullptr, 0.f, amax};
+            BT_CUDA_TRY(linear_product_fused(L.down->dev(), din, batch, m->gu, c.hidden_dim, EPI_F32_ACCUM, nullptr, err, m->sm_count, s));
+            launches += 4;
+            continue;
+        }
+        bt_linear* seq[4] = {c.arch == 1 ? L.qkv : L.ttt_down, c.arch == 1 ? L.o : L.ttt_up,
                              (batch <= 8 || !L.gate_up) ? L.gate_up_il : L.gate_up, L.down};
         for (bt_linear* lin : seq) {
             if (batch > 8) {
                 // tensor-core product on whatever the transformed-row buffer holds (quantiser included)
                 BT_CUDA_TRY(launch_gemm_tc(lin->dev(), m->xt, lin->w.k_in, batch, m->qtc, m->sx, m->qsum, m->gu,
                                            lin->w.n_out, EPI_F32, err, m->sm_count, s, m->tc_part, m->tc_part_bytes));
-                launches += 2;
+                launches += 1 + gemm_tc_kernels(lin->dev(), batch, m->sm_count);
             } else {
                 BT_CUDA_TRY(linear_product(lin->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, lin->w.n_out,
                                            EPI_F32, err, m->sm_count, s));

@@ -54,6 +54,9 @@ def _bind():
     L.bt_model_ttt_state.argtypes = [vp, i32]
     L.bt_model_kv_cache.restype = vp
     L.bt_model_kv_cache.argtypes = [vp, i32]
+    L.bt_model_trace_floats.restype = i64
+    L.bt_model_trace_floats.argtypes = [vp]
+    L.bt_model_set_trace.argtypes = [vp, vp]
     L.bt_model_ternary_bytes.restype = i64
     L.bt_model_ternary_bytes.argtypes = [vp]
     L.bt_tp_unique_id.argtypes = [vp]
@@ -63,7 +66,7 @@ def _bind():
     L.bt_model_tp_peer_import.argtypes = [vp, C.c_char_p]
     L.bt_model_tp_set_timeout.argtypes = [vp, i32]
     L.bt_model_tp_destroy.argtypes = [vp]
-    L.bt_model_enqueue_products.argtypes = [vp, i32, vp, C.POINTER(i32)]
+    L.bt_model_enqueue_products.argtypes = [vp, i32, i32, vp, C.POINTER(i32)]
     L.bt_model_launches_per_step.argtypes = [vp, i32]
     L._model_bound = True
     return L
@@ -108,6 +111,12 @@ class QuantizedKVCache:
         check(self._L.bt_kv_export(self._h, b, t_len, kq.ctypes.data, ks.ctypes.data, vq.ctypes.data,
                                    vs.ctypes.data))
         return kq, ks, vq, vs
+
+    def export_rows(self, pos: int, batch: int):
+        """The rows at position `pos` of sequences 0..batch-1: (kq [batch, n_kv, hd] u8, ks [batch, n_kv],
+        vq, vs)."""
+        parts = [self.export(b, pos + 1) for b in range(batch)]
+        return tuple(np.stack([p[i][:, pos] for p in parts], 0) for i in range(4))
 
     def load(self, b: int, kq, ks, vq, vs):
         """Restores rows [0, t_len) of sequence b from arrays shaped like export()'s."""
@@ -246,10 +255,45 @@ class BitLlama:
         check(self._L.bt_model_step_dev(self._h, _ptr(tokens_dev), tokens_dev.numel(),
                                         _stream_ptr(tokens_dev.device.index)))
 
-    def enqueue_products(self, batch: int) -> int:
-        """Measurement aid: only the ternary-product launches of one step (state untouched)."""
+    def set_trace(self, on: bool = True) -> None:
+        """Keep the per-layer intermediate tensors of the following steps (see read_trace)."""
+        torch = _torch()
+        if on:
+            n = self._L.bt_model_trace_floats(self._h)
+            self._trace = torch.zeros(n, dtype=torch.float32, device=f"cuda:{self.device}")
+            check(self._L.bt_model_set_trace(self._h, _ptr(self._trace)))
+        else:
+            check(self._L.bt_model_set_trace(self._h, None))  # the buffer stays readable (read_trace)
+
+    def read_trace(self, batch: int):
+        """The last traced step: a list over layers of dicts h_in, qkv, att, h_mid, act, h_out
+        (numpy [batch, width]; arch ttt: qkv = down-projected features, att = TTT prediction)."""
+        torch = _torch()
+        torch.cuda.synchronize(self.device)
+        c, tp = self.cfg, max(self.tp_size, 1)
+        H, B = c.hidden_dim, self.max_batch
+        if c.arch == "ttt":
+            wq = wa = H // 4
+        else:
+            hd = H // c.n_heads
+            wq, wa = (c.n_heads // tp + 2 * (c.n_kv_heads // tp)) * hd, (c.n_heads // tp) * hd
+        widths = [("h_in", H), ("qkv", wq), ("att", wa), ("h_mid", H), ("act", c.intermediate_dim // tp), ("h_out", H)]
+        flat = self._trace.cpu().numpy()
+        per_layer = sum(w for _, w in widths) * B
+        out = []
+        for li in range(c.num_layers):
+            off, d = li * per_layer, {}
+            for name, w in widths:
+                d[name] = flat[off:off + B * w].reshape(B, w)[:batch].copy()
+                off += B * w
+            out.append(d)
+        return out
+
+    def enqueue_products(self, batch: int, as_in_step: bool = False) -> int:
+        """Measurement aid: only the ternary-product launches of one step (state untouched);
+        as_in_step: with the quantiser prologues and fused epilogues the step itself uses."""
         n = C.c_int(0)
-        check(self._L.bt_model_enqueue_products(self._h, batch, _stream_ptr(self.device), C.byref(n)))
+        check(self._L.bt_model_enqueue_products(self._h, batch, int(as_in_step), _stream_ptr(self.device), C.byref(n)))
         return n.value
 
     def launches_per_step(self, batch: int) -> int:

@@ -327,13 +327,27 @@ bt_status bt_model_seek(bt_model* m, int pos);
  * arch llama); KV cache of one layer (NULL for arch ttt). */
 float* bt_model_ttt_state(bt_model* m, int layer);
 bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer);
+/* Inspection aid: the tensors between the calls of BitLlamaBlock::forward (RE/model/block.rs:87-134).
+ * While a trace buffer is set, every step runs launch by launch (no graph replay) and copies, per layer,
+ *   h_in [max_batch, hidden] | q|k|v [max_batch, (n_heads + 2 n_kv) head_dim] | attention output
+ *   [max_batch, hidden] | h after the attention residual | silu(gate)*up [max_batch, intermediate] |
+ *   h after the MLP residual
+ * into trace_dev ([num_layers] blocks of that layout, bt_model_trace_floats floats in all; arch ttt: the
+ * down-projected features and the TTT prediction, d_small wide, take the places of q|k|v and the attention
+ * output; tensor-parallel models record their local slices).  The kernels and their arguments are the ones
+ * of the normal step.  trace_dev = NULL switches it off.  Synchronises the device. */
+int64_t bt_model_trace_floats(const bt_model* m);
+bt_status bt_model_set_trace(bt_model* m, float* trace_dev);
 /* Ternary-weight bytes streamed by one decode step (sum over all BitLinear tiles). */
 int64_t bt_model_ternary_bytes(const bt_model* m);
 /* Measurement aid (no counterpart in the reference): enqueues only the ternary-product
  * launches of one decode step, in step order, on whatever the activation buffers hold,
- * writing to scratch outputs; model state is not touched.  *n_launches receives the number
- * of kernel launches enqueued. */
-bt_status bt_model_enqueue_products(bt_model* m, int batch, void* stream, int* n_launches);
+ * writing to scratch outputs; model state is not touched.  as_in_step = 0: the plain product
+ * on already quantised activations; as_in_step = 1: the launches exactly as the step issues
+ * them (for one or two sequences: RMSNorm / absmax quantisation prologues and the SwiGLU and
+ * accumulate epilogues inside the product kernel).  *n_launches receives the number of kernel
+ * launches enqueued. */
+bt_status bt_model_enqueue_products(bt_model* m, int batch, int as_in_step, void* stream, int* n_launches);
 /* Kernel launches of one decode step at this batch size. */
 int bt_model_launches_per_step(const bt_model* m, int batch);
 

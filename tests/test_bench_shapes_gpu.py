@@ -3,13 +3,14 @@
 a hidden size above 4096, the 128256-row lm_head and the tensor-core product at 512 and 4096
 tokens.  Models are cut to one or two layers and (mostly) a small vocabulary so that the CPU
 oracle finishes in seconds; the caches are seeded with a long random context so that decode
-attention runs over many spans, as it does in the benchmark at context 2048."""
+attention runs over many spans, as it does in the benchmark at context 2048.  Decode steps are
+checked stage by stage (see gpu_util.staged_decode_step for why, and for the tolerances)."""
 import importlib
 
 import numpy as np
 import pytest
 
-from gpu_util import load_bt, rel_err, seed_kv_caches, ternary_packed
+from gpu_util import load_bt, rel_err, seed_kv_caches, staged_decode_step, ternary_packed
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -29,33 +30,17 @@ def syn():
     return importlib.import_module("bit-ttt-engine_b200.synthetic")
 
 
-def teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, t0, n_steps, seed):
-    """Seeds `t0` positions of context, then decodes `n_steps` teacher-forced tokens on the GPU
-    model and in the oracle; returns the worst relative logit error."""
+def teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, t0, n_steps, seed, act_tol=0.0):
+    """Seeds `t0` positions of context, then decodes `n_steps` teacher-forced tokens, every step checked
+    stage by stage against the oracle (gpu_util.staged_decode_step)."""
     gpu.reset_kv_cache()
     states = [ref.new_state() for _ in range(batch)]
     rng = np.random.default_rng(seed)
     seed_kv_caches(gpu, states, cfg, t0, rng)
     tokens = rng.integers(0, cfg.vocab_size, size=(n_steps, batch))
-    worst = 0.0
     for t in range(n_steps):
-        logits, nxt = gpu.forward_one(tokens[t])
-        for b in range(batch):
-            ref_logits = ref.forward_one(int(tokens[t, b]), states[b])
-            worst = max(worst, rel_err(logits[b], ref_logits))
-            assert worst <= REL_TOL, (batch, t, b, worst)
-            assert logits[b, nxt[b]] == logits[b].max()
+        staged_decode_step(oracle, ref, gpu, cfg, tokens[t], states, act_tol)
     assert gpu.current_pos == t0 + n_steps
-    # the rows appended during these steps: values exact, keys within one step of the 8-bit grid
-    # (the rotation can land a key on a rounding tie)
-    li = cfg.num_layers - 1
-    kq, ks, vq, vs = gpu.kv_cache(li).export(batch - 1, t0 + n_steps)
-    st = states[batch - 1]
-    ref_k = np.stack(st.kq[li][t0:], 1).astype(np.int32)
-    ref_v = np.stack(st.vq[li][t0:], 1).astype(np.int32)
-    assert np.abs(kq[:, t0:].astype(np.int32) - ref_k).max() <= 1
-    assert np.abs(vq[:, t0:].astype(np.int32) - ref_v).max() <= 1
-    return worst
 
 
 @pytest.fixture(scope="module")
@@ -71,8 +56,7 @@ def test_llama8b_block_shape_long_context(bt, oracle, syn, llama8b_two_layers, b
     # batch 1 crosses position 2048 (t0 = 2040): the benchmark's attention configuration, 16 spans
     # of 128 positions and then a 17th position group; batches above 8 run the tensor-core products
     cfg, gpu, ref = llama8b_two_layers
-    worst = teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 2040 if batch == 1 else 2046, steps, 77 + batch)
-    assert worst <= REL_TOL
+    teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 2040 if batch == 1 else 2046, steps, 77 + batch)
     assert bt.lib().bt_device_check(0) == 0
 
 
@@ -83,8 +67,7 @@ def test_tinyllama_block_shape(bt, oracle, syn, batch, steps):
     w = syn.make_weights(cfg, seed=5200, from_latent=False)
     gpu = syn.build_model(w, max_batch=batch)
     ref = oracle.model_from_weights(w)
-    worst = teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 509, steps, 99 + batch)
-    assert worst <= REL_TOL
+    teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 509, steps, 99 + batch)
     assert bt.lib().bt_device_check(0) == 0
 
 
@@ -95,8 +78,7 @@ def test_hidden_above_4096(bt, oracle, syn):
     gpu = syn.build_model(w, max_batch=2)
     ref = oracle.model_from_weights(w)
     for batch in (1, 2):
-        worst = teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 5, 4, 5 + batch)
-        assert worst <= REL_TOL
+        teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 5, 4, 5 + batch)
     assert bt.lib().bt_device_check(0) == 0
 
 
@@ -112,8 +94,7 @@ def test_lm_head_full_vocabulary(bt, oracle, syn):
     gpu = syn.build_model(w, max_batch=12)
     ref = oracle.model_from_weights(w)
     for batch in (1, 12):
-        worst = teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 3, 2, 40 + batch)
-        assert worst <= REL_TOL
+        teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, 3, 2, 40 + batch)
     assert bt.lib().bt_device_check(0) == 0
 
 

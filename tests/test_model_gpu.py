@@ -5,7 +5,7 @@ import importlib
 import numpy as np
 import pytest
 
-from gpu_util import load_bt
+from gpu_util import load_bt, staged_decode_step
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -61,13 +61,35 @@ def test_tiny_ttt_model_teacher_forced(bt, oracle):
     assert not np.array_equal(l0, l1)
 
 
+def run_staged(bt, oracle, cfg, n_tokens, seed, batch):
+    """Teacher-forced decode of an arch-llama model from an empty cache, every step checked stage by
+    stage against the oracle (attention is not bit-reproducible in f32, see gpu_util.staged_decode_step)."""
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    w = syn.make_weights(cfg, seed=seed)
+    gpu = syn.build_model(w, max_batch=batch)
+    ref = oracle.model_from_weights(w)
+    states = [ref.new_state() for _ in range(batch)]
+    tokens = np.random.default_rng(7).integers(0, cfg.vocab_size, size=(n_tokens, batch))
+    for t in range(n_tokens):
+        staged_decode_step(oracle, ref, gpu, cfg, tokens[t], states)
+    assert gpu.current_pos == n_tokens
+    return gpu, ref, states
+
+
 def test_tiny_llama_model_teacher_forced_batch2(bt, oracle):
     syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
     cfg = syn.TINY_LLAMA_TEST  # 2 layers, hidden 256, 8 q heads / 2 kv heads, head_dim 32
-    gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 10, 3000, batch=2)
-    kq, ks, vq, vs = gpu.kv_cache(1).export(1, 10)
-    ref_k = np.stack(states[1].kq[1], 1)
-    assert np.abs(kq.astype(np.int32) - ref_k.astype(np.int32)).max() <= 1
+    gpu, ref, states = run_staged(bt, oracle, cfg, 10, 3000, batch=2)
+    # free-running comparison, for the record: the two pipelines may part by quantisation noise
+    free = [ref.new_state() for _ in range(2)]
+    gpu.reset_kv_cache()
+    tokens = np.random.default_rng(8).integers(0, cfg.vocab_size, size=(6, 2))
+    worst = 0.0
+    for t in range(6):
+        logits, _ = gpu.forward_one(tokens[t])
+        for b in range(2):
+            worst = max(worst, rel_err(logits[b], ref.forward_one(int(tokens[t, b]), free[b])))
+    assert worst <= 5e-2, worst
     assert bt.lib().bt_device_check(0) == 0
 
 
@@ -75,11 +97,7 @@ def test_tiny_llama_model_teacher_forced_batch2(bt, oracle):
 def test_tiny_llama_model_teacher_forced_batch_3_to_8(bt, oracle, batch):
     # three to eight sequences: a quantiser kernel in front of every product instead of the fused prologue
     syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
-    cfg = syn.TINY_LLAMA_TEST
-    gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 6, 3300 + batch, batch=batch)
-    kq, ks, vq, vs = gpu.kv_cache(1).export(batch - 1, 6)
-    ref_k = np.stack(states[batch - 1].kq[1], 1)
-    assert np.abs(kq.astype(np.int32) - ref_k.astype(np.int32)).max() <= 1
+    run_staged(bt, oracle, syn.TINY_LLAMA_TEST, 6, 3300 + batch, batch=batch)
     assert bt.lib().bt_device_check(0) == 0
 
 
@@ -97,7 +115,8 @@ def test_position_limit(bt):
 def test_models_batch_12_use_tensor_core_product(bt, oracle):
     # more than 8 sequences: projections run on the tcgen05 kernel, row transforms separately
     syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
-    for cfg, seed in ((syn.TINY_LLAMA_TEST, 3100), (syn.BitLlamaConfig("ttt", 500, 256, 2, 4, 4, 688, inner_lr=0.01), 3200)):
-        gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 4, seed, batch=12)
-        assert worst <= REL_TOL
+    run_staged(bt, oracle, syn.TINY_LLAMA_TEST, 4, 3100, batch=12)
+    cfg = syn.BitLlamaConfig("ttt", 500, 256, 2, 4, 4, 688, inner_lr=0.01)  # no attention: bit-reproducible end to end
+    gpu, ref, states, worst = run_teacher_forced(bt, oracle, cfg, 4, 3200, batch=12)
+    assert worst <= REL_TOL
     assert bt.lib().bt_device_check(0) == 0
