@@ -1,25 +1,32 @@
 #!/usr/bin/env python
 """Benchmark: ternary Llama-3-8B-shaped decode, tokens/s, plus the BitLinear GEMV roofline.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--sweep]
 
-One "step" is one decode step (one new token for each of the B sequences) of a random-init
-ternary model with the Llama-3-8B shape: 32 layers, hidden 4096, MLP 14336, 32 query / 8 KV
-heads, vocab 128256, 2-bit packed BitLinear weights, dense bf16 lm_head, Q8 KV cache.  The
-cache is first filled token by token (the reference CLI's prefill, model/llama.rs:495-498)
-so that the timed steps run at the stated context length.
+One "step" is one decode step (one new token per sequence) of a random-init ternary model with
+the Llama-3-8B shape: 32 layers, hidden 4096, MLP 14336, 32 query / 8 KV heads, vocab 128256,
+2-bit packed BitLinear weights, dense bf16 lm_head, Q8 KV cache.  The cache is first filled
+token by token (the reference CLI's prefill, model/llama.rs:495-498) so that the timed steps
+run at the stated context length.  Before anything is timed, the first decode step of the
+model is compared with the CPU oracle.
 
-Printed: ONE JSON line (rank 0).  `value` is device-timed (CUDA events, tokens fed back on
-the device, graph replay); `e2e` goes through bt_model_forward_one with host token ids in
-and host next-token ids out every step; `roofline` is the ternary GEMV alone (algorithmic
-bytes per launch / average launch time, measured in this run); `cpu_baseline` is the CPU
-oracle timed on this host on a bounded sample.
+Printed: ONE JSON line (rank 0).  The top-level keys are batch 1: `value` is device-timed
+(CUDA events, tokens fed back on the device, graph replay; median of 5 timed regions of K
+steps each, every region starting again at the stated context), `e2e` goes through
+bt_model_forward_one with host token ids in and host next-token ids out every step,
+`e2e_with_logits` also copies the logits out as the reference's loop does (model/llama.rs:507).
+`roofline` is the ternary product: `frac` from the launches exactly as the step issues them
+(quantiser prologues and fused epilogues included), `frac_isolated` from the plain product on
+quantised activations; algorithmic bytes per launch / average launch time, measured here.
+`batch64` holds the same measurements at batch 64 (the metric names both batch sizes), with
+the share of the step spent in decode attention.  `cpu_baseline` is the CPU oracle timed on
+this host on a bounded sample.
 
 With --gpus N > 1 (torchrun, one rank per GPU) the model is tensor-parallel over the N GPUs:
 q|k|v and gate|up split by rows, o_proj and down_proj by input columns with an
 all-reduce(max) of the activation absmax and an all-reduce(sum) of the int32 accumulators
-(NCCL over NVLink), lm_head replicated.  All ranks decode the SAME B sequences, so the total
-work is fixed and the scaling is strong.
+(NVLink), lm_head replicated.  All ranks decode the SAME sequences, so the total work is fixed
+and the scaling is strong.
 """
 from __future__ import annotations
 
@@ -40,6 +47,7 @@ if ROOT not in sys.path:
 
 METRIC = "ternary 8B decode tok/s (b=1,64); BitLinear GEMV GB/s vs 8 TB/s HBM"
 UNIT = "tokens/s"
+REGIONS = 5  # timed regions per measurement; the median is reported
 
 
 def measured_peaks():
@@ -47,8 +55,8 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -99,21 +107,42 @@ class ClockSampler:
 # workload
 # ---------------------------------------------------------------------------------------
 
-def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0, layers=32, vocab=128256):
+def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0):
     """Random-init Llama-3-8B-shaped ternary model.  Layer 0's host arrays are reused for
     every layer (each layer still owns its own device copy, so HBM traffic is real); the
     embedding and lm_head are one N(0, 0.02) block tiled over the vocabulary."""
-    cfg = syn.BitLlamaConfig("llama", vocab, 4096, layers, 32, 8, 14336, rope_theta=500000.0,
-                             max_position_embeddings=max_pos)
+    cfg = syn.LLAMA3_8B
+    cfg = syn.BitLlamaConfig(cfg.arch, cfg.vocab_size, cfg.hidden_dim, cfg.num_layers, cfg.n_heads, cfg.n_kv_heads,
+                             cfg.intermediate_dim, rope_theta=cfg.rope_theta, max_position_embeddings=max_pos)
     rng = np.random.default_rng(seed)
-    block = rng.normal(0, 0.02, (min(8016, vocab), cfg.hidden_dim)).astype(np.float32)
-    table = np.tile(block, ((vocab + block.shape[0] - 1) // block.shape[0], 1))[:vocab]
+    block = syn._bf16_round(rng.normal(0, 0.02, (8016, cfg.hidden_dim)).astype(np.float32))
+    table = np.tile(block, ((cfg.vocab_size + block.shape[0] - 1) // block.shape[0], 1))[:cfg.vocab_size]
     w = syn.SyntheticWeights(cfg, table, table, np.ones(cfg.hidden_dim, np.float32))
     layer = {"norm1": np.ones(cfg.hidden_dim, np.float32), "norm2": np.ones(cfg.hidden_dim, np.float32)}
     for kind, (n, k) in syn.linear_shapes(cfg).items():
         layer[kind] = (syn._ternary_codes(rng, n, k), 0.016, n, k)
     w.layers = [layer] * cfg.num_layers
     return cfg, w, syn.build_model(w, max_batch=batch, device=device, tp_rank=tp_rank, tp_size=tp_size)
+
+
+def verify_first_step(model, weights, batch):
+    """The benchmarked model's own first decode step (empty cache) against the CPU oracle, stage by stage
+    through all layers (oracle/staged.py): q|k|v, the residual sums and silu(gate)*up bit for bit, attention
+    and the 128256-row head to f32 accumulation accuracy.  Sequences 0 and batch-1 are checked; a mismatch
+    raises.  Leaves the cache empty."""
+    from oracle import oracle as orc
+    from oracle.staged import staged_decode_step
+    cfg = weights.cfg
+    tokens = np.random.default_rng(3).integers(0, cfg.vocab_size, size=batch).astype(np.int32)
+    ref = orc.model_from_weights(weights)
+    states = [ref.new_state() for _ in range(batch)]
+    model.reset_kv_cache()
+    try:
+        staged_decode_step(orc, ref, model, cfg, tokens, states, seqs=sorted({0, batch - 1}))
+    except AssertionError as exc:
+        raise SystemExit(f"bench.py: the first decode step differs from the oracle: {exc}")
+    model.reset_kv_cache()
+    return "all stages of 32 layers match (BitLinear stages bit-exact, attention <= 2e-5, logits <= 2e-5)"
 
 
 def cpu_decode_baseline(cfg, syn, budget_s=20.0):
@@ -157,62 +186,12 @@ def cpu_decode_baseline(cfg, syn, budget_s=20.0):
     }
 
 
-def run_linear_probe(bt, n, k, m):
-    """Three forwards of one BitLinear (profiling aid for the product kernels)."""
-    import torch
-    rng = np.random.default_rng(0)
-    lin = bt.BitLinear.from_packed(rng.integers(0, 256, size=(n, k // 4), dtype=np.uint8), [0.016], n, k)
-    x = torch.randn(m, k, device="cuda")
-    ws = bt.Workspace(0, 768 << 20)
-    for _ in range(3):
-        y = lin.forward(x, workspace=ws)
-    torch.cuda.synchronize()
-    print("linear probe done", float(y.abs().sum()), file=sys.stderr)
-
-
-def run_timeline(bt, model, args, B):
-    """Profiling aid: the kernels of the fused decode step (batch <= 8) write globaltimer stamps per
-    CTA (entry, dependency released, activations staged, last epilogue warp done) while one step is
-    captured; the replayed step is then printed launch by launch, in ns from the first stamp."""
-    import ctypes as C
-    import torch
-    layers = args.layers
-    L = bt.lib()
-    model.seek(args.context)
-    buf = torch.zeros(layers * 5 * 512 * 4, dtype=torch.int64, device="cuda")
-    ids = np.arange(B, dtype=np.int32) + 5
-    _, ids = model.forward_one(ids, want_logits=False)   # eager step: kernel attributes
-    L.bt_debug_timeline.argtypes = [C.c_void_p]
-    L.bt_debug_timeline(C.c_void_p(buf.data_ptr()))
-    _, ids = model.forward_one(ids, want_logits=False)   # captured with the stamp slots
-    L.bt_debug_timeline(None)
-    for _ in range(5):
-        _, ids = model.forward_one(ids, want_logits=False)
-    torch.cuda.synchronize()
-    t = buf.cpu().numpy().reshape(layers * 5, 512, 4)
-    names = ["q|k|v", "attention", "o_proj", "gate|up", "down_proj"]
-    t00 = None
-    for s in range(layers * 5):
-        v = t[s]
-        if s % 5 == 1:  # attention: 8 stamps per CTA (entry, released, ..., partials written, arrived)
-            v8 = v.reshape(256, 8)
-            v = np.stack([v8[:, 0], v8[:, 1], v8[:, 6], v8[:, 7]], 1)
-        used = v[:, 0] > 0
-        if not used.any():
-            continue
-        if t00 is None:
-            t00 = v[used, 0].min()
-        cols = [v[used, i] - t00 for i in range(4)]
-        print(f"block {s // 5} {names[s % 5]:10s} ctas {int(used.sum()):3d}  entry {int(cols[0].min()):7d}..{int(cols[0].max()):7d}"
-              f"  released {int(cols[1].min()):7d}..{int(cols[1].max()):7d}  staged {int(cols[2].min()):7d}..{int(cols[2].max()):7d}"
-              f" (median {int(np.median(cols[2])):7d})  done {int(cols[3].min()):7d}..{int(cols[3].max()):7d}")
-
-
 def run_sweep(bt, device):
-    """BASELINE config 5: per point GB/s of packed weights (HBM-bound points) and int8 TOP/s."""
+    """BitLinear shape sweep, bf16 activations in and out: per point GB/s of algorithmic bytes
+    (packed weights + bf16 activations + bf16 outputs) and int8 TOP/s, plus the TTT update."""
     import ctypes as C
     import torch
-    peak, peak_kind = measured_peaks()
+    peak, bf16_tf, peak_kind = measured_peaks()
     L = bt.lib()
     rng = np.random.default_rng(0)
     for (k, n) in [(4096, 4096), (4096, 14336), (14336, 4096), (4096, 128256)]:
@@ -222,16 +201,16 @@ def run_sweep(bt, device):
         lins = [bt.BitLinear.from_packed(packed, [0.016], n, k, device=device) for _ in range(copies)]
         ws = bt.Workspace(device, 768 << 20)
         for m in (1, 8, 64, 512, 4096):
-            if m * n * 4 > 3 << 30:
+            if m * n * 2 > 3 << 30:
                 continue
-            x = torch.randn(m, k, device="cuda")
-            y = torch.empty(m, n, device="cuda")
+            x = torch.randn(m, k, device="cuda").bfloat16()
+            y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
 
             def run():
                 st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
                 for lin in lins:
-                    bt.check(L.bt_linear_forward(lin._h, ws._h, C.c_void_p(x.data_ptr()), m, k, 0,
-                                                 C.c_void_p(y.data_ptr()), 0, st))
+                    bt.check(L.bt_linear_forward(lin._h, ws._h, C.c_void_p(x.data_ptr()), m, k, bt.BT_BF16,
+                                                 C.c_void_p(y.data_ptr()), bt.BT_BF16, st))
             run()  # eager once: kernel attributes are set outside the capture
             torch.cuda.synchronize()
             # one pass over all copies as a CUDA graph, so that small points measure the device and
@@ -250,11 +229,14 @@ def run_sweep(bt, device):
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
             byts = n * k / 4 + 2 * m * k + 2 * m * n
-            print(json.dumps({"sweep": "bitlinear", "K": k, "N": n, "M": m, "us": us,
-                              "kernel": "gemv (mma.sync)" if m <= 8 else "gemm_tc (tcgen05)",
+            tops = 2.0 * m * n * k / us / 1e6
+            print(json.dumps({"sweep": "bitlinear", "K": k, "N": n, "M": m, "us": us, "dtype": "bf16 in / bf16 out",
+                              "kernel": "gemv_kernel (mma.sync)" if m <= 8 else "gemm_tc_kernel (tcgen05)",
                               "GBps": byts / us / 1e3, "hbm_frac": byts / us / 1e3 / peak, "peak_kind": peak_kind,
-                              "int8_TOPs": 2.0 * m * n * k / us / 1e6,
-                              "note": "quantiser kernel included; graph-replayed; weights rotate through copies larger than L2"}),
+                              "int8_TOPs": tops,
+                              "int8_frac_of_2x_bf16_peak": tops / (2 * bf16_tf) if bf16_tf else None,
+                              "note": "quantiser kernel included; graph-replayed; weights rotate through copies larger than L2; "
+                                      "int8 peak taken as twice the measured bf16 GEMM rate (derived, not measured)"}),
                   flush=True)
         del lins
     # TTT fast-weight update: S independent 64x64 states, mini-batch 16
@@ -307,34 +289,185 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------
+# measurements on a built model
+# ---------------------------------------------------------------------------------------
+
+class Timer:
+    def __init__(self, torch, dist, world, dev):
+        self.torch, self.dist, self.world, self.dev = torch, dist, world, dev
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        t = self.torch.tensor([v], dtype=self.torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def fill_context(model, cfg, B, context, rng, dev, torch):
+    """Token-by-token prefill of `context` positions, ids fed from a device array."""
+    model.reset_kv_cache()
+    prompt = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=(context, B)).astype(np.int32)).to(dev)
+    for t in range(context):
+        model.step_dev(prompt[t])
+    torch.cuda.synchronize()
+
+
+def time_decode(model, cfg, B, K, W, context, tm, rng):
+    """Median over REGIONS timed regions of K graph-replayed steps, every region starting at `context`."""
+    torch = tm.torch
+    tok = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(tm.dev)
+    ms_all = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for region in range(REGIONS):
+        model.seek(context)
+        model.step_dev(tok)
+        nxt = model.next_dev()
+        for _ in range(W if region == 0 else 1):
+            model.step_dev(nxt[:B])
+        tm.barrier()
+        e0.record()
+        for _ in range(K):
+            model.step_dev(nxt[:B])  # copies the ids device-to-device, then replays the step graph
+        e1.record()
+        tm.barrier()
+        ms_all.append(tm.max_over_ranks(e0.elapsed_time(e1)))
+    return float(np.median(ms_all)), ms_all
+
+
+def time_e2e(model, cfg, B, K, context, tm, rng, want_logits):
+    torch = tm.torch
+    vals = []
+    for region in range(3):
+        model.seek(context)
+        ids = rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)
+        for _ in range(3):
+            _, ids = model.forward_one(ids, want_logits=want_logits)
+        tm.barrier()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            _, ids = model.forward_one(ids, want_logits=want_logits)
+        torch.cuda.synchronize()
+        vals.append(tm.max_over_ranks(time.perf_counter() - t0))
+    return B * K / float(np.median(vals))
+
+
+def time_products(model, B, as_in_step, torch):
+    """Average duration of one ternary-product launch of a decode step, replayed alone as a graph."""
+    n_launch = model.enqueue_products(B, as_in_step)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            model.enqueue_products(B, as_in_step)
+    reps = 10
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps, n_launch  # microseconds per step's worth of products
+
+
+def time_attention(bt, cfg, B, context, torch, tp=1):
+    """Decode attention alone, through bt_attn_decode on caches of the model's shape: microseconds
+    per layer call at `context` positions (8 caches in rotation, graph-replayed)."""
+    hd = cfg.hidden_dim // cfg.n_heads
+    nh, nkv = cfg.n_heads // tp, cfg.n_kv_heads // tp
+    layers = 8 if B <= 8 else 4
+    caches = [bt.QuantizedKVCache(context + 64, B, nkv, hd) for _ in range(layers)]
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda")
+    pos = torch.full((B,), context, dtype=torch.int32, device="cuda")
+    for c in caches:
+        bt.attn_decode(c, qkv, pos, nh, cfg.rope_theta)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for c in caches:
+            bt.attn_decode(c, qkv, pos, nh, cfg.rope_theta)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (10 * layers)
+    byts = 2 * nkv * (context + 1) * (hd + 4) * B
+    return us, byts
+
+
+def product_bytes(cfg, syn, model, B):
+    """Algorithmic bytes of the ternary products of one step: packed weights once + int8 activations in + f32 out."""
+    shapes = syn.linear_shapes(cfg)
+    act = 0
+    for kinds in ([syn.W_Q, syn.W_K, syn.W_V], [syn.W_O], [syn.W_GATE, syn.W_UP], [syn.W_DOWN]):
+        n = sum(shapes[k][0] for k in kinds)
+        kk = shapes[kinds[0]][1]
+        act += B * kk + 4 * B * n
+    return model.ternary_bytes + act * cfg.num_layers
+
+
+def measure_batch(bt, syn, model, cfg, B, K, W, context, tm, rng, world, peak, peak_kind):
+    torch = tm.torch
+    ms, ms_all = time_decode(model, cfg, B, K, W, context, tm, rng)
+    e2e = time_e2e(model, cfg, B, K, context, tm, rng, want_logits=False)
+    e2e_logits = time_e2e(model, cfg, B, max(8, K // 4), context, tm, rng, want_logits=True)
+    us_step_plain, n_plain = time_products(model, B, False, torch)
+    us_step_fused, n_fused = time_products(model, B, True, torch)
+    byts = product_bytes(cfg, syn, model, B) / max(world, 1) if world > 1 else product_bytes(cfg, syn, model, B)
+    us_attn, attn_bytes = time_attention(bt, cfg, B, context, torch, tp=world)
+    kernel = "gemv_kernel (ternary BitLinear product, mma.sync int8)" if B <= 8 else \
+             "gemm_tc_kernel (ternary BitLinear product, tcgen05 int8) + its quantiser"
+    roofline = {
+        "bound": "hbm", "kernel": kernel, "unit": "GB/s", "peak": peak, "peak_kind": peak_kind,
+        "achieved": byts / us_step_fused / 1e3, "frac": byts / us_step_fused / 1e3 / peak,
+        "achieved_isolated": byts / us_step_plain / 1e3, "frac_isolated": byts / us_step_plain / 1e3 / peak,
+        "bytes_per_launch": byts / 128, "us_per_launch": us_step_fused / 128,
+        "launches_per_step": n_fused, "product_us_per_step": us_step_fused,
+        "traffic": None,
+        "note": "frac: the four products of every block launched exactly as the decode step launches them "
+                "(quantiser prologues / kernels and fused epilogues included), replayed alone; frac_isolated: the plain "
+                "product on already quantised activations; bytes = packed weights once + int8 activations + f32 outputs",
+    }
+    return {
+        "value": B * K / (ms * 1e-3), "ms_per_step": ms / K, "ms_regions": [m / K for m in ms_all],
+        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "e2e_with_logits": {"value": e2e_logits, "unit": UNIT, "h2d_bytes_per_step": 4 * B,
+                            "d2h_bytes_per_step": 4 * B + 4 * B * cfg.vocab_size},
+        "roofline": roofline,
+        "attention": {"us_per_layer": us_attn, "share_of_step": cfg.num_layers * us_attn / (ms / K * 1e3),
+                      "GBps": attn_bytes / us_attn / 1e3, "hbm_frac": attn_bytes / us_attn / 1e3 / peak,
+                      "note": "bt_attn_decode alone on caches of the model's shape at this context"},
+        "gpu_launches": model.launches_per_step(B) * K,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--context", type=int, default=2048, help="tokens in the KV cache before the timed steps")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--layers", type=int, default=32, help="profiling aid: fewer layers of the same shape")
-    ap.add_argument("--vocab", type=int, default=128256, help="profiling aid: smaller vocabulary")
-    ap.add_argument("--one-step", action="store_true",
-                    help="profiling aid: build the model, --seek to the context, run ONE eager decode step "
-                         "(every kernel launched outside a graph) and exit without a JSON line")
-    ap.add_argument("--timeline", action="store_true",
-                    help="profiling aid (batch <= 8): per-launch globaltimer stamps of one graph-replayed step, "
-                         "printed per block; use with --layers 2 --seek")
-    ap.add_argument("--linear", type=int, nargs=3, metavar=("N", "K", "M"),
-                    help="profiling aid: three bt_linear_forward calls on a random [N, K] weight with M tokens, then exit")
+    ap.add_argument("--no-batch64", action="store_true", help="skip the batch-64 half of the metric")
     ap.add_argument("--sweep", action="store_true",
                     help="BitLinear shape sweep (K,N in {4096x4096, 4096x14336, 14336x4096, 4096x128256}, "
-                         "M in {1, 8, 64, 512, 4096}) plus the TTT update: one JSON line per point")
+                         "M in {1, 8, 64, 512, 4096}, bf16 activations) plus the TTT update: one JSON line per point")
     ap.add_argument("--tp-nccl", action="store_true",
                     help="with --gpus N > 1: keep the tensor-parallel exchanges on NCCL instead of the "
                          "library's peer-memory kernels")
-    ap.add_argument("--seek", action="store_true",
-                    help="profiling aid: skip the token-by-token prefill and declare the (zero-filled) "
-                         "cache to hold --context positions")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -354,18 +487,16 @@ def main():
     bt = importlib.import_module("bit-ttt-engine_b200")
     bt.lib()
     syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
-
-    B, K, W = args.batch, args.steps, max(args.warmup, 3)
-    max_pos = args.context + W + 2 * K + 16
-    if args.linear:
-        run_linear_probe(bt, *args.linear)
-        return
     if args.sweep:
         run_sweep(bt, local_rank)
         return
-    cfg, weights, model = build_8b(bt, syn, B, max_pos, tp_rank=rank, tp_size=world, device=local_rank,
-                                   layers=args.layers, vocab=args.vocab)
-    del weights
+
+    K, W = args.steps, max(args.warmup, 3)
+    with_b64 = not args.no_batch64 and world == 1
+    B_max = 64 if with_b64 else 1
+    K64 = max(8, K // 4)
+    max_pos = args.context + max(W + K, 8 + K64) + 16
+    cfg, weights, model = build_8b(bt, syn, B_max, max_pos, tp_rank=rank, tp_size=world, device=local_rank)
     if world > 1:
         uid = [bt.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
@@ -390,124 +521,51 @@ def main():
                 except Exception:  # noqa: BLE001
                     pass
     dev = torch.device(f"cuda:{local_rank}")
+    tm = Timer(torch, dist, world, dev)
     rng = np.random.default_rng(11)  # every rank feeds the same ids
+    peak, _, peak_kind = measured_peaks()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    # ---- the benchmarked model's own first step against the oracle, before anything is timed ----
+    verified = {"batch1": verify_first_step(model, weights, 1)} if world == 1 else {}
+    if with_b64:
+        verified["batch64"] = verify_first_step(model, weights, 64)
+    del weights
 
-    if args.timeline:
-        run_timeline(bt, model, args, B)
-        del model
-        return
-
-    if args.one_step:
-        model.seek(args.context)
-        _, ids = model.forward_one(np.arange(B, dtype=np.int32) + 5, want_logits=False)
-        torch.cuda.synchronize()
-        print("one eager step done, next ids", ids[:4].tolist(), file=sys.stderr)
-        del model
-        return
-
-    # prefill token by token, tokens fed from the host like the reference CLI
-    tok = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(dev)
-    prompt = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=(args.context, B)).astype(np.int32)).to(dev)
-    if args.seek:
-        model.seek(args.context)
-    else:
-        for t in range(args.context):
-            model.step_dev(prompt[t])
-    for _ in range(W):
-        model.step_dev(tok)
-        tok = model.next_dev()[:B].clone()
-    barrier()
-
-    # ---- device-timed decode: K steps, greedy ids fed back on the device --------------------
+    # ---- batch 1 ---------------------------------------------------------------------------
+    fill_context(model, cfg, 1, args.context, rng, dev, torch)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    nxt = model.next_dev()
-    barrier()
-    e0.record()
-    for _ in range(K):
-        model.step_dev(nxt[:B])  # copies the ids device-to-device, then replays the step graph
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    b1 = measure_batch(bt, syn, model, cfg, 1, K, W, args.context, tm, rng, world, peak, peak_kind)
     clocks = sampler.stop()
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    value = B * K / (ms_max * 1e-3)
 
-    # ---- end to end: host ids in, host ids out, every step ---------------------------------
-    ids = rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)
-    for _ in range(3):
-        _, ids = model.forward_one(ids, want_logits=False)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        _, ids = model.forward_one(ids, want_logits=False)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = B * K / float(t.item())
-
-    # ---- roofline of the dominant kernel: the ternary GEMV launches of a step, alone -------
-    peak, peak_kind = measured_peaks()
-    n_launch = model.enqueue_products(B)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(g, stream=side):
-            model.enqueue_products(B)
-    reps = 10
-    g.replay()
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(reps):
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    us_per_launch = e0.elapsed_time(e1) * 1e3 / (reps * n_launch)
-    groups = (B + 7) // 8
-    # algorithmic bytes: packed weights once per launch + int8 activations in + f32 out
-    shapes = syn.linear_shapes(cfg)
-    act_bytes = 0
-    for kinds in ([syn.W_Q, syn.W_K, syn.W_V], [syn.W_O], [syn.W_GATE, syn.W_UP], [syn.W_DOWN]):
-        n = sum(shapes[k][0] for k in kinds)
-        kk = shapes[kinds[0]][1]
-        act_bytes += B * kk + 4 * B * n
-    bytes_per_step = model.ternary_bytes * groups + act_bytes * cfg.num_layers
-    bytes_per_launch = bytes_per_step / n_launch
-    achieved = bytes_per_launch / us_per_launch / 1e3  # GB/s
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel (ternary BitLinear product)", "achieved": achieved,
-                "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                # dram__bytes_read+write per launch, average over the four projections of a block, from the
-                # ncu capture summarised in profiles/gemv_kernel_decode_layer_8b.md (batch 1, one GPU)
-                "traffic": 13.75e6 if (B == 1 and world == 1) else None,
-                "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
-                "launches_per_step": n_launch}
+    # ---- batch 64 --------------------------------------------------------------------------
+    b64 = None
+    if with_b64:
+        fill_context(model, cfg, 64, args.context, rng, dev, torch)
+        b64 = measure_batch(bt, syn, model, cfg, 64, K64, W, args.context, tm, rng, world, peak, peak_kind)
+        b64["steps"] = K64
+        b64["unit"] = UNIT
 
     if rank == 0:
         cpu = None if args.no_cpu_baseline else cpu_decode_baseline(cfg, syn)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "metric": METRIC, "value": b1["value"], "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": b1["ms_per_step"], "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None,
             "dtype": "int8 x ternary -> int32 (f32 epilogue, bf16 lm_head)", "data": "synthetic",
-            "config": {"workload": f"Llama-3-8B-shaped ternary decode, batch {B}, context {args.context}+",
-                       "batch": B, "context": args.context, "parallelism": (f"tp{world} ({'NCCL' if args.tp_nccl else 'peer-memory'} exchange)") if world > 1 else "single GPU",
+            "config": {"workload": f"Llama-3-8B-shaped ternary decode, batch 1 (top level) and batch 64 (`batch64`), context {args.context}+",
+                       "batch": 1, "context": args.context,
+                       "parallelism": (f"tp{world} ({'NCCL' if args.tp_nccl else 'peer-memory'} exchange)") if world > 1 else "single GPU",
+                       "timing": f"median of {REGIONS} regions of {K} steps, each region restarted at the stated context",
                        "l2": "inputs larger than L2: 1.74 GB of ternary tiles + 1.05 GB lm_head per step"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
-            "gpu_launches": model.launches_per_step(B) * K,
-            "roofline": roofline, "clocks": clocks,
+            "ms_regions": b1["ms_regions"],
+            "e2e": b1["e2e"], "e2e_with_logits": b1["e2e_with_logits"],
+            "gpu_launches": b1["gpu_launches"],
+            "roofline": b1["roofline"], "attention": b1["attention"], "clocks": clocks,
+            "verified_against_oracle": verified,
         }
+        if b64 is not None:
+            line["batch64"] = b64
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)

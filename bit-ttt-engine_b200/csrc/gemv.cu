@@ -406,10 +406,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             const float sx0 = tok_sx[0];
             float amax1 = 0.f;
             if (a.epilogue == EPI_SWIGLU) {
-                // silu(gate) * up needs an f64 exponential, a long dependent chain.  Four row tiles
-                // (8 columns each) are therefore finished together, one column per lane, so that the
-                // chain runs once per four row tiles: chunk c = row tiles 4c .. 4c+3 of the CTA,
-                // chunks dealt round-robin to the epilogue warps.
+                // silu(gate) * up has an exponential and a division, a dependent chain.  Four row tiles
+                // (8 columns each) are finished together, one column per lane, so that the chain runs
+                // once per four row tiles: chunk c = row tiles 4c .. 4c+3 of the CTA, chunks dealt
+                // round-robin to the epilogue warps.
                 const int sub = lane >> 3, col8 = lane & 7;
                 const int n_chunks = (my_rts + 3) / 4;
                 for (int c = epi; c < n_chunks; c += kEpiWarps) {
@@ -435,8 +435,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                     if (valid && col < a.n_out / 2) {
                         const float y = __fmul_rn(__fmul_rn((float)(gsum - qs0), swg), sx0);
                         const float uv = __fmul_rn(__fmul_rn((float)(usum - qs0), swu), sx0);
-                        // silu(g) * u, exp in f64 rounded once (layers/swiglu.rs:31-33)
-                        const float act = __fmul_rn(__fdiv_rn(y, __fadd_rn(1.0f, (float)exp(-(double)y))), uv);
+                        // silu(g) * u  (layers/swiglu.rs:31-33), f32 throughout like the reference
+                        const float act = __fmul_rn(__fdiv_rn(y, __fadd_rn(1.0f, expf(-y))), uv);
                         reinterpret_cast<float*>(a.out)[col] = act;
                         amax1 = fmaxf(amax1, fabsf(act));
                     }
@@ -505,8 +505,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                     if (token < a.m && col < a.n_out / 2) {
                         const float gv = __fmul_rn(__fmul_rn((float)(sum[e] - qs[e]), sw[0]), sx[e]);
                         const float uv = __fmul_rn(__fmul_rn((float)(sum[2 + e] - qs[e]), sw[1]), sx[e]);
-                        // silu(g) * u, exp in f64 rounded once (layers/swiglu.rs:31-33)
-                        const float act = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, (float)exp(-(double)gv))), uv);
+                        // silu(g) * u  (layers/swiglu.rs:31-33), f32 throughout like the reference
+                        const float act = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
                         reinterpret_cast<float*>(a.out)[(int64_t)token * a.out_stride + col] = act;
                         run_max[e] = fmaxf(run_max[e], fabsf(act));
                     }

@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
     } else if (PRE == PRE_SWIGLU) {
         for (int c = threadIdx.x; c < k; c += blockDim.x) {
             const float g = xr[c], u = xr[k + c];
-            const float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, (float)exp(-(double)g))), u);
+            const float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
             row[c] = v;
             amax = fmaxf(amax, fabsf(v));
         }

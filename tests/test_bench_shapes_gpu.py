@@ -30,7 +30,7 @@ def syn():
     return importlib.import_module("bit-ttt-engine_b200.synthetic")
 
 
-def teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, t0, n_steps, seed, act_tol=0.0):
+def teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, t0, n_steps, seed):
     """Seeds `t0` positions of context, then decodes `n_steps` teacher-forced tokens, every step checked
     stage by stage against the oracle (gpu_util.staged_decode_step)."""
     gpu.reset_kv_cache()
@@ -39,7 +39,7 @@ def teacher_forced_from_context(oracle, syn, gpu, ref, cfg, batch, t0, n_steps, 
     seed_kv_caches(gpu, states, cfg, t0, rng)
     tokens = rng.integers(0, cfg.vocab_size, size=(n_steps, batch))
     for t in range(n_steps):
-        staged_decode_step(oracle, ref, gpu, cfg, tokens[t], states, act_tol)
+        staged_decode_step(oracle, ref, gpu, cfg, tokens[t], states)
     assert gpu.current_pos == t0 + n_steps
 
 

@@ -38,9 +38,10 @@ def test_tp2_model_matches_oracle_and_ranks_agree(use_peer):
     with tempfile.TemporaryDirectory() as d:
         mp.spawn(tp_common.gpu_model_worker, args=(2, _free_port(), d, 8, use_peer), nprocs=2, join=True)
         res = _results(d, 2)
-        worst, same0 = res[0].split()
-        assert float(worst) <= 1e-3 and same0 == "1"
-        assert res[1].split()[1] == "1"
+        for r in res:
+            worst, same, staged_ok = r.split()
+            assert float(worst) <= 1e-3, r     # dense head on the rank's own final hidden state
+            assert same == "1" and staged_ok == "1", r
 
 
 @pytest.mark.gpu

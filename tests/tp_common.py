@@ -56,9 +56,11 @@ def cpu_row_parallel_worker(rank, world, port, result_dir):
 
 
 def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
-    """Tensor-parallel decode of a small llama-shaped model on `world` GPUs; rank 0 checks the
-    logits against the single-process oracle, every rank checks them against rank 0's.
-    use_peer: exchange over NVLink peer memory (CUDA IPC inboxes) instead of NCCL."""
+    """Tensor-parallel decode of a small llama-shaped model on `world` GPUs, checked stage by stage:
+    every rank's q|k|v and silu(gate)*up slices against the oracle's slices, and the two row-parallel
+    projections (o_proj, down_proj: absmax exchange + integer sum over the ranks) bit for bit against
+    the oracle's unsharded projection of the gathered slices.  Every rank must hold the same hidden
+    state and logits bit for bit.  use_peer: exchange over NVLink peer memory instead of NCCL."""
     import torch
     dist = _init(rank, world, port, "gloo")
     torch.cuda.set_device(rank)
@@ -77,21 +79,53 @@ def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
         dist.broadcast_object_list(uid, src=0)
         model.tp_init(uid[0])
     ref = orc.model_from_weights(w)
-    states = [ref.new_state(), ref.new_state()]
+    hd, nh, nkv, inter = cfg.hidden_dim // cfg.n_heads, cfg.n_heads, cfg.n_kv_heads, cfg.intermediate_dim
+    nh_l, nkv_l, i_l = nh // world, nkv // world, inter // world
     tokens = np.random.default_rng(7).integers(0, cfg.vocab_size, size=(n_tokens, 2))
-    worst, same = 0.0, True
+    worst, same, ok = 0.0, True, True
+    model.set_trace(True)
     for t in range(n_tokens):
         logits, nxt = model.forward_one(tokens[t])
         mine = torch.from_numpy(logits.copy())
         theirs = mine.clone()
         dist.broadcast(theirs, src=0)
         same = same and bool(torch.equal(mine, theirs))
-        if rank == 0:
-            for b in range(2):
-                r = ref.forward_one(int(tokens[t, b]), states[b])
-                worst = max(worst, float(np.abs(logits[b] - r).max() / np.abs(r).max()))
+        tr = model.read_trace(2)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [{k: v for k, v in layer.items() if k in ("att", "act")} for layer in tr])
+        for b in range(2):
+            for li in range(cfg.num_layers):
+                L, lt = ref.layers[li], tr[li]
+                h_in = lt["h_in"][b:b + 1]
+                xn = orc.rmsnorm(h_in, L.norm1, ref.cfg.rms_eps)
+                q, k, v = L.q(xn)[0], L.k(xn)[0], L.v(xn)[0]
+                mine_qkv = np.concatenate([q[rank * nh_l * hd:(rank + 1) * nh_l * hd], k[rank * nkv_l * hd:(rank + 1) * nkv_l * hd],
+                                           v[rank * nkv_l * hd:(rank + 1) * nkv_l * hd]])
+                ok = ok and bool(np.array_equal(lt["qkv"][b], mine_qkv))
+                att_full = np.concatenate([gathered[r][li]["att"][b] for r in range(world)])[None, :]
+                ok = ok and bool(np.array_equal(lt["h_mid"][b:b + 1], h_in + L.o(att_full)))
+                xn2 = orc.rmsnorm(lt["h_mid"][b:b + 1], L.norm2, ref.cfg.rms_eps)
+                act_ref = orc.silu_mul(L.gate(xn2), L.up(xn2))[0]
+                mine_act = act_ref[rank * i_l:(rank + 1) * i_l]
+                ok = ok and float(np.abs(lt["act"][b] - mine_act).max()) <= 1e-6 * float(np.abs(mine_act).max())
+                act_full = np.concatenate([gathered[r][li]["act"][b] for r in range(world)])[None, :]
+                ok = ok and bool(np.array_equal(lt["h_out"][b:b + 1], lt["h_mid"][b:b + 1] + L.down(act_full)))
+            hn = orc.rmsnorm(tr[-1]["h_out"][b:b + 1], ref.norm_f, ref.cfg.rms_eps)
+            r = orc.dense_linear(hn, ref.lm_head)[0]
+            worst = max(worst, float(np.abs(logits[b] - r).max() / np.abs(r).max()))
+    model.set_trace(False)
+    # the captured path (CUDA graph with the exchanges inside) gives the same bits as the traced one
+    model.reset_kv_cache()
+    for t in range(3):
+        logits_g, _ = model.forward_one(tokens[t])
+    model.reset_kv_cache()
+    model.set_trace(True)
+    for t in range(3):
+        logits_t, _ = model.forward_one(tokens[t])
+    model.set_trace(False)
+    ok = ok and bool(np.array_equal(logits_g, logits_t))
     bt.check(bt.lib().bt_device_check(rank))
-    open(os.path.join(result_dir, f"rank{rank}.txt"), "w").write(f"{worst} {int(same)}")
+    open(os.path.join(result_dir, f"rank{rank}.txt"), "w").write(f"{worst} {int(same)} {int(ok)}")
     del model
     dist.destroy_process_group()
 
