@@ -38,7 +38,6 @@ constexpr int kMaxHd = 128;
 constexpr int kRowPad = 16;     // bytes added to a cache row in shared memory (row stride = 16 mod 32: 4-byte
                                 // fragment loads of 8 consecutive rows fall into different banks)
 constexpr int kMaxRowBytes = kMaxHd + kRowPad;
-constexpr int kPieceRows = 3 * kMaxRep;  // (piece, head) rows / columns of the MMA operands
 constexpr int kQpStride = kMaxHd + 8;    // bf16 elements per row of the query pieces
 constexpr int kSrStride = kTilePos + 4;  // floats per row of the raw scores
 constexpr int kPwStride = kTilePos + 8;  // bf16 elements per row of the P.V weights
@@ -76,20 +75,26 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
     }
 }
 
-struct AttnSmem {
-    // cache rows as stored (u8, rows padded), two tiles: while one is worked on, the next arrives
+// G = query vectors that share the K/V rows of a CTA: the NREP heads of a KV group (decode) times the
+// QB query positions of a block (prefill).  "Row" below = piece * G + query vector.
+template <int G>
+struct AttnSmemT {
+    static constexpr int kRows = 3 * G;
+    static constexpr int kRows16 = (kRows + 15) / 16 * 16;
+    // cache rows as stored (u8, rows padded), two tiles: while one is worked on, the next arrives;
+    // after the last tile both arrays serve as scratch of the warp reduction
     alignas(16) uint8_t kraw[2][kTilePos * kMaxRowBytes];
-    alignas(16) uint8_t vraw[2][kTilePos * kMaxRowBytes];  // after the last tile: scratch of the warp reduction
+    alignas(16) uint8_t vraw[2][kTilePos * kMaxRowBytes];
     alignas(16) float ksr[2][kTilePos];
     alignas(16) float vsr[2][kTilePos];
-    alignas(16) __nv_bfloat16 qp[kPieceRows][kQpStride];   // rotated queries, row = piece * NREP + head
-    alignas(16) float sraw[kPieceRows][kSrStride];         // per-piece dot products of the tile
-    alignas(16) __nv_bfloat16 pw[32][kPwStride];           // pieces of p * v_scale, row = piece * NREP + head
-    alignas(16) float opart[kMaxRep * kMaxHd];             // this span's unnormalised output [head][dim] (read by the cluster)
-    float ml[2][kMaxRep];                                  // this span's running maximum / denominator (read by the cluster)
-    float corr[kMaxRep];
-    float wmax[kMaxRep][4];
-    float wsum[kMaxRep][4];
+    alignas(16) __nv_bfloat16 qp[kRows][kQpStride];        // rotated queries
+    alignas(16) float sraw[kRows][kSrStride];              // per-piece dot products of the tile
+    alignas(16) __nv_bfloat16 pw[kRows16][kPwStride];      // pieces of p * v_scale
+    alignas(16) float opart[G * kMaxHd];                   // this span's unnormalised output [query vector][dim] (read by the cluster)
+    float ml[2][G];                                        // this span's running maximum / denominator (read by the cluster)
+    float corr[G];
+    float wmax[G][4];
+    float wsum[G][4];
     float knew[kMaxHd], vnew[kMaxHd];
 };
 
@@ -145,11 +150,17 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t ran
     return v;
 }
 
-template <int NREP>
-__global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a) {
+// QB = 1: decode, one new token per sequence; blockIdx.y = span of positions, the spans of a (sequence, KV
+// head) form a cluster.  QB > 1: prefill, a.q_rows new tokens per sequence whose K/V rows are already in the
+// cache; blockIdx.y = block of QB consecutive query positions, which sees the keys up to its own position
+// (causal rule of layers/attention.rs:249-262: key j is visible to query i when j <= i + past).
+template <int NREP, int QB>
+__global__ void __launch_bounds__(kAttnThreads, QB == 1 ? 2 : 1) attn_kernel(AttnArgs a) {
+    constexpr int G = NREP * QB;
+    using Smem = AttnSmemT<G>;
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
-    constexpr int kRowsUsed = 3 * NREP;            // (piece, head) rows
+    Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+    constexpr int kRowsUsed = 3 * G;               // (piece, query vector) rows
     constexpr int NB = (kRowsUsed + 7) / 8;        // 8-column blocks of the score MMAs
     constexpr int MB = (kRowsUsed + 15) / 16;      // 16-row blocks of the P.V MMAs
     const int hd = a.head_dim, half = hd >> 1;
@@ -157,16 +168,19 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
     const int split = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    // The spans follow the sequence's current length, not the capacity the launch was planned
+    // Decode: the spans follow the sequence's current length, not the capacity the launch was planned
     // for: every CTA of a (sequence, KV head) gets an equal share (a multiple of 32 positions) of
     // what the cache holds now.  The position counter is only written by the last kernel of a
     // decode step, and steps do not overlap, so it may be read before the dependency wait.
+    // Prefill: p is the position of the sequence's first new token; the block of queries q0 .. q0 + QB - 1
+    // walks the keys 0 .. p + q0 + QB - 1.
     const int p = a.pos[b];
-    const int t_len = p + 1;
+    const int q0 = QB == 1 ? 0 : split * QB;
+    const int t_len = QB == 1 ? p + 1 : min(p + q0 + QB, p + a.q_rows);
     int span = ((t_len + a.splits - 1) / a.splits + 31) & ~31;
     if (span > a.span) span = a.span;
-    const int t0 = split * span;
-    const int t1 = min(t_len, t0 + span);
+    const int t0 = QB == 1 ? split * span : 0;
+    const int t1 = QB == 1 ? min(t_len, t0 + span) : t_len;
     const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
     const int row16 = hd >> 4;            // 16-byte pieces per row
     const int rstride = hd + kRowPad;     // row stride of the tiles in shared memory
@@ -189,30 +203,33 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
     // requested before the dependency wait (the row of the current position is fetched too, with
     // whatever it holds; its owner overwrites the copy below).
     const int n_first = max(0, min(kTilePos, t1 - t0));
-    fetch_tile(0, t0, n_first);
-    // (piece, head) rows of the P.V weights beyond the ones in use stay zero
-    for (int i = tid; i < (32 - kRowsUsed) * kPwStride; i += kAttnThreads)
+    if (QB == 1) fetch_tile(0, t0, n_first);  // (prefill: the new rows come from the kernel just before)
+    // (piece, query vector) rows of the P.V weights beyond the ones in use stay zero
+    for (int i = tid; i < (Smem::kRows16 - kRowsUsed) * kPwStride; i += kAttnThreads)
         sm.pw[kRowsUsed + i / kPwStride][i % kPwStride] = __float2bfloat16_rn(0.0f);
     ptx::pdl_wait();
+    if (QB > 1) fetch_tile(0, t0, n_first);
 
     const int64_t qkv_stride = (int64_t)(a.n_heads + 2 * a.n_kv) * hd;
-    const float* qkv = a.qkv + b * qkv_stride;
+    const float* qkv = a.qkv + (int64_t)b * a.q_rows * qkv_stride;  // first new token of the sequence
     const bool empty = t0 >= t_len;
-    const bool owner = (p >= t0 && p < t1);
+    const bool owner = QB == 1 && (p >= t0 && p < t1);
     if (!empty) {
         const float* cos_p = a.rope_cos + (int64_t)p * half;
         const float* sin_p = a.rope_sin + (int64_t)p * half;
-        // rotate the query heads of this KV group, [x1*cos - x2*sin, x1*sin + x2*cos] (attention.rs:79-83),
-        // and cut every value into its three bf16 pieces
-        for (int i = tid; i < NREP * half; i += kAttnThreads) {
-            const int h = i / half, c = i % half;
-            const float cs = cos_p[c], sn = sin_p[c];
-            const float* qh = qkv + (int64_t)(kvh * NREP + h) * hd;
+        // rotate the query vectors of this CTA, [x1*cos - x2*sin, x1*sin + x2*cos] (attention.rs:79-83),
+        // and cut every value into its three bf16 pieces.  Query vector v = (position q0 + v / NREP, head
+        // v % NREP); a block that reaches beyond the last new token repeats the last one (never stored).
+        for (int i = tid; i < G * half; i += kAttnThreads) {
+            const int v = i / half, c = i % half;
+            const int h = v % NREP, qi = min(q0 + v / NREP, a.q_rows - 1);
+            const float cs = a.rope_cos[(int64_t)(p + qi) * half + c], sn = a.rope_sin[(int64_t)(p + qi) * half + c];
+            const float* qh = qkv + (int64_t)qi * qkv_stride + (int64_t)(kvh * NREP + h) * hd;
             const float x1 = qh[c], x2 = qh[half + c];
             const float r1 = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
             const float r2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
-            split3(r1, sm.qp[h][c], sm.qp[NREP + h][c], sm.qp[2 * NREP + h][c]);
-            split3(r2, sm.qp[h][half + c], sm.qp[NREP + h][half + c], sm.qp[2 * NREP + h][half + c]);
+            split3(r1, sm.qp[v][c], sm.qp[G + v][c], sm.qp[2 * G + v][c]);
+            split3(r2, sm.qp[v][half + c], sm.qp[G + v][half + c], sm.qp[2 * G + v][half + c]);
         }
         // the CTA whose span holds position p appends the new key / value first
         if (owner) {
@@ -227,7 +244,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
             for (int c = tid; c < hd; c += kAttnThreads) sm.vnew[c] = vh[c];
         }
     }
-    if (tid < NREP) {
+    if (tid < G) {
         sm.ml[0][tid] = -INFINITY;  // a span without positions keeps these: weight 0 in the merge
         sm.ml[1][tid] = 0.0f;
     }
@@ -310,41 +327,43 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
             __syncthreads();
             // (2) softmax weights of the tile, one (head, position) per thread and round; a warp covers
             //     32 positions of one head.  score = ((q.k_int) * k_scale) * 1/sqrt(hd)  (attention.rs:202)
-            constexpr int kSoftItems = (NREP * kTilePos + kAttnThreads - 1) / kAttnThreads;
+            constexpr int kSoftItems = (G * kTilePos + kAttnThreads - 1) / kAttnThreads;
             float sv[kSoftItems];
 #pragma unroll
             for (int e = 0; e < kSoftItems; ++e) {
                 const int it = tid + e * kAttnThreads;
                 const int h = it / kTilePos, r = it % kTilePos;
                 float s = -INFINITY;
-                if (h < NREP && r < n_here) {
-                    const float dot = __fadd_rn(__fadd_rn(sm.sraw[h][r], sm.sraw[NREP + h][r]), sm.sraw[2 * NREP + h][r]);
+                // prefill: query vector h sits at position p + q0 + h / NREP and sees the keys up to there
+                const bool seen = QB == 1 || tb + r <= p + q0 + h / NREP;
+                if (h < G && r < n_here && seen) {
+                    const float dot = __fadd_rn(__fadd_rn(sm.sraw[h][r], sm.sraw[G + h][r]), sm.sraw[2 * G + h][r]);
                     s = __fmul_rn(__fmul_rn(dot, sm.ksr[cur][r]), a.scaling);
                 }
                 sv[e] = s;
                 const float wm = warp_max(s);
-                if (lane == 0 && h < NREP) sm.wmax[h][(it >> 5) & 3] = wm;
+                if (lane == 0 && h < G) sm.wmax[h][(it >> 5) & 3] = wm;
             }
             __syncthreads();
 #pragma unroll
             for (int e = 0; e < kSoftItems; ++e) {
                 const int it = tid + e * kAttnThreads;
                 const int h = it / kTilePos, r = it % kTilePos;
-                if (h < NREP) {  // warp-uniform
+                if (h < G) {  // warp-uniform
                     const float m_old = sm.ml[0][h];
                     const float m_new = fmaxf(fmaxf(m_old, fmaxf(sm.wmax[h][0], sm.wmax[h][1])), fmaxf(sm.wmax[h][2], sm.wmax[h][3]));
-                    const bool live = r < n_here;
+                    const bool live = sv[e] != -INFINITY;  // inside the tile and visible to this query
                     const float pe = live ? expf(__fsub_rn(sv[e], m_new)) : 0.0f;
                     // weight of the value row: p * v_scale (the value bytes enter the MMA as integers)
                     const float wv = live ? __fmul_rn(pe, sm.vsr[cur][r]) : 0.0f;
-                    split3(wv, sm.pw[h][r], sm.pw[NREP + h][r], sm.pw[2 * NREP + h][r]);
+                    split3(wv, sm.pw[h][r], sm.pw[G + h][r], sm.pw[2 * G + h][r]);
                     const float ws = warp_sum(pe);
                     if (lane == 0) sm.wsum[h][(it >> 5) & 3] = ws;
                     if (r == 0) sm.corr[h] = expf(__fsub_rn(m_old, m_new));  // exp(-inf) = 0 on the first tile
                 }
             }
             __syncthreads();
-            if (tid < NREP) {  // running sum and maximum (nobody reads them before the next barrier)
+            if (tid < G) {  // running sum and maximum (nobody reads them before the next barrier)
                 const float m_old = sm.ml[0][tid];
                 const float m_new = fmaxf(fmaxf(m_old, fmaxf(sm.wmax[tid][0], sm.wmax[tid][1])), fmaxf(sm.wmax[tid][2], sm.wmax[tid][3]));
                 const float psum = __fadd_rn(__fadd_rn(__fadd_rn(sm.wsum[tid][0], sm.wsum[tid][1]), sm.wsum[tid][2]), sm.wsum[tid][3]);
@@ -356,8 +375,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
                     const int r0 = mb * 16 + g, r1 = r0 + 8;
-                    const float c0 = r0 < kRowsUsed ? sm.corr[r0 % NREP] : 0.0f;
-                    const float c1 = r1 < kRowsUsed ? sm.corr[r1 % NREP] : 0.0f;
+                    const float c0 = r0 < kRowsUsed ? sm.corr[r0 % G] : 0.0f;
+                    const float c1 = r1 < kRowsUsed ? sm.corr[r1 % G] : 0.0f;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) { acc[mb][e][0] *= c0; acc[mb][e][1] *= c0; acc[mb][e][2] *= c1; acc[mb][e][3] *= c1; }
                 }
@@ -391,7 +410,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
             cur ^= 1;
         }
         // add the position groups and the three pieces through shared memory (the value tiles are free now)
-        float* red = reinterpret_cast<float*>(sm.vraw);  // [n_pq][rows][hd]
+        float* red = reinterpret_cast<float*>(sm.kraw);  // [n_pq][rows][hd], over the key and value tiles
+        static_assert(sizeof(sm.kraw) + sizeof(sm.vraw) >= (size_t)kRowsUsed * 256 * sizeof(float) &&
+                      offsetof(Smem, vraw) == offsetof(Smem, kraw) + sizeof(sm.kraw), "reduction scratch");
         if (pv_active) {
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
@@ -406,12 +427,12 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
             }
         }
         __syncthreads();
-        for (int it = tid; it < NREP * hd; it += kAttnThreads) {
+        for (int it = tid; it < G * hd; it += kAttnThreads) {
             const int h = it / hd, dcol = it % hd;
             float v = 0.0f;
             for (int g2 = 0; g2 < n_pq; ++g2) {
                 const float* rr = red + (size_t)g2 * kRowsUsed * hd + dcol;
-                v = __fadd_rn(v, __fadd_rn(__fadd_rn(rr[h * hd], rr[(NREP + h) * hd]), rr[(2 * NREP + h) * hd]));
+                v = __fadd_rn(v, __fadd_rn(__fadd_rn(rr[h * hd], rr[(G + h) * hd]), rr[(2 * G + h) * hd]));
             }
             sm.opart[it] = v;
         }
@@ -427,7 +448,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
         // The output columns are dealt evenly to the CTAs of the cluster.  All remote loads of a thread are
         // issued before the first use (fixed trip counts, predicated), so that their latencies overlap.
         const int S = a.splits, rank = (int)cluster_ctarank();
-        const int total = NREP * hd;
+        const int total = G * hd;
         const int per_cta = (total + S - 1) / S;
         float amax = 0.0f;
         for (int i = tid; i < per_cta; i += kAttnThreads) {
@@ -457,7 +478,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(AttnArgs a
                 num = fmaf(live ? os[s2] : 0.0f, w, num);
             }
             const float o = __fdiv_rn(num, den);
-            a.out[((int64_t)b * a.n_heads + kvh * NREP + h) * hd + (it % hd)] = o;
+            const int qi = q0 + h / NREP;  // new token of the sequence this query vector belongs to (decode: 0)
+            if (qi < a.q_rows) a.out[(((int64_t)b * a.q_rows + qi) * a.n_heads + kvh * NREP + h % NREP) * hd + (it % hd)] = o;
             amax = fmaxf(amax, fabsf(o));
         }
         if (a.absmax_out) {
@@ -500,9 +522,44 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, int max_se
     }
 }
 
-constexpr size_t kSmemBytes = sizeof(AttnSmem);
+// K/V rows of a prefill: for every new token i of every sequence, RoPE on the key at position pos[b] + i
+// (layers/attention.rs:180-182) and Q8 append of key and value (layers/kv_cache.rs:50-119) into row
+// pos[b] + i of the cache.  One warp per (sequence, token, KV head, k|v); qkv rows are [b][i].
+__global__ void __launch_bounds__(128) kv_append_rows_kernel(KvCacheView cache, const float* __restrict__ qkv,
+                                                             const int32_t* __restrict__ pos,
+                                                             const float* __restrict__ rope_cos,
+                                                             const float* __restrict__ rope_sin, int batch, int q_rows,
+                                                             int n_heads, int n_kv, int hd) {
+    __shared__ float rowbuf[4][kMaxHd];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 4 + warp;  // ((b * q_rows + i) * n_kv + kvh) * 2 + which
+    if (item >= (int64_t)batch * q_rows * n_kv * 2) return;
+    const int which = (int)(item & 1), kvh = (int)((item >> 1) % n_kv);
+    const int64_t row = (item >> 1) / n_kv;  // b * q_rows + i
+    const int b = (int)(row / q_rows), i = (int)(row % q_rows);
+    const int p = pos[b] + i;
+    if (p < 0 || p >= cache.max_seq) return;
+    const int half = hd >> 1;
+    const float* src = qkv + row * (int64_t)(n_heads + 2 * n_kv) * hd + (int64_t)(n_heads + (which ? n_kv : 0) + kvh) * hd;
+    if (which) {
+        for (int c = lane; c < hd; c += 32) rowbuf[warp][c] = src[c];
+    } else {
+        for (int c = lane; c < half; c += 32) {
+            const float cs = rope_cos[(int64_t)p * half + c], sn = rope_sin[(int64_t)p * half + c];
+            const float x1 = src[c], x2 = src[half + c];
+            rowbuf[warp][c] = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+            rowbuf[warp][half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
+        }
+    }
+    __syncwarp();
+    const int64_t r = ((int64_t)b * n_kv + kvh) * cache.max_seq + p;
+    quant_row_warp(rowbuf[warp], hd, (which ? cache.v_q : cache.k_q) + r * hd, (which ? cache.v_s : cache.k_s) + r, nullptr,
+                   nullptr, lane);
+}
+
 constexpr size_t kHalfSm = 116 * 1024;
-static_assert(kSmemBytes <= 110 * 1024, "two CTAs of the attention kernel must fit one SM");
+static_assert(sizeof(AttnSmemT<kMaxRep>) <= 110 * 1024, "two CTAs of the decode kernel must fit one SM");
+constexpr int kPrefillVectors = 16;  // query vectors per CTA of the prefill kernel: 16 / NREP positions x NREP heads
 
 // How many clusters of each size can be resident at once (a CTA then takes a whole SM): a cluster's CTAs
 // must sit in one GPC, so large clusters leave SMs unused, and a GPC with fewer SMs than the cluster
@@ -516,9 +573,12 @@ template <int NREP>
 cudaError_t configure_rep(const ClusterTable** out) {
     static ClusterTable table;  // per process; every device of a process is the same GPU model
     if (!table.ready) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHalfSm);
+        cudaError_t e = cudaFuncSetAttribute(attn_kernel<NREP, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHalfSm);
         if (e != cudaSuccess) return e;
-        const bool big = cudaFuncSetAttribute(attn_decode_kernel<NREP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        e = cudaFuncSetAttribute(attn_kernel<NREP, kPrefillVectors / NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)sizeof(AttnSmemT<kPrefillVectors>));
+        if (e != cudaSuccess) return e;
+        const bool big = cudaFuncSetAttribute(attn_kernel<NREP, 1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         for (int s = 1; s <= kMaxCluster; ++s) {
             if (s > 8 && !big) break;
             cudaLaunchConfig_t cfg = {};
@@ -531,7 +591,7 @@ cudaError_t configure_rep(const ClusterTable** out) {
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<NREP>, &cfg) == cudaSuccess) table.active[s] = n;
+            if (cudaOccupancyMaxActiveClusters(&n, attn_kernel<NREP, 1>, &cfg) == cudaSuccess) table.active[s] = n;
         }
         cudaGetLastError();  // a refused attribute or query only rules a cluster size out
         if (table.active[1] < 1) table.active[1] = 1;
@@ -546,22 +606,33 @@ cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
     const ClusterTable* table = nullptr;
     cudaError_t e = configure_rep<NREP>(&table);
     if (e != cudaSuccess) return e;
-    if (a.splits < 1 || a.splits > kMaxCluster || table->active[a.splits] < 1) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.batch * a.n_kv, a.splits);
     cfg.blockDim = dim3(kAttnThreads);
-    // When the whole grid fits one CTA per SM, ask for more than half of an SM's shared
-    // memory: the block scheduler then cannot pair two CTAs on one SM while others idle.
-    cfg.dynamicSmemBytes = ((int64_t)a.batch * a.n_kv * a.splits <= a.sm_count) ? kHalfSm : kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = (unsigned)a.splits; attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
+    if (a.q_rows > 1) {
+        // prefill: one CTA per block of query positions, no cluster, ordinary stream order
+        constexpr int QB = kPrefillVectors / NREP;
+        if (a.splits != 1) return cudaErrorInvalidValue;
+        cfg.gridDim = dim3(a.batch * a.n_kv, (a.q_rows + QB - 1) / QB);
+        cfg.dynamicSmemBytes = sizeof(AttnSmemT<kPrefillVectors>);
+        attr[0].val.clusterDim.y = 1;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, attn_kernel<NREP, QB>, a);
+    }
+    if (a.splits < 1 || a.splits > kMaxCluster || table->active[a.splits] < 1) return cudaErrorInvalidValue;
+    cfg.gridDim = dim3(a.batch * a.n_kv, a.splits);
+    // When the whole grid fits one CTA per SM, ask for more than half of an SM's shared
+    // memory: the block scheduler then cannot pair two CTAs on one SM while others idle.
+    cfg.dynamicSmemBytes = ((int64_t)a.batch * a.n_kv * a.splits <= a.sm_count) ? kHalfSm : sizeof(AttnSmemT<NREP>);
+    attr[0].val.clusterDim.y = (unsigned)a.splits;
     cfg.numAttrs = a.pdl ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<NREP>, a);
+    return cudaLaunchKernelEx(&cfg, attn_kernel<NREP, 1>, a);
 }
 
 const ClusterTable* attn_cluster_table(int rep) {
@@ -612,7 +683,7 @@ void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int r
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
     const int rep = a.n_kv > 0 ? a.n_heads / a.n_kv : 0;
     if (a.head_dim % 32 != 0 || a.head_dim > kMaxHd || a.n_heads % a.n_kv != 0 || rep < 1 || rep > kMaxRep ||
-        a.span % 32 != 0 || (int64_t)a.span * a.splits < a.cache.max_seq)
+        a.span % 32 != 0 || (int64_t)a.span * a.splits < a.cache.max_seq || a.q_rows < 1)
         return cudaErrorInvalidValue;
     switch (rep) {
         case 1: return launch_attn_rep<1>(a, stream);
@@ -627,6 +698,15 @@ cudaError_t launch_kv_append(const KvCacheView& cache, const float* k, const flo
                              int n_kv, int hd, cudaStream_t stream) {
     const int rows = batch * n_kv * 2;
     kv_append_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(cache, k, v, pos, batch, n_kv, hd);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_kv_append_rows(const KvCacheView& cache, const float* qkv, const int32_t* pos, const float* rope_cos,
+                                  const float* rope_sin, int batch, int q_rows, int n_heads, int n_kv, int hd,
+                                  cudaStream_t stream) {
+    const int64_t items = (int64_t)batch * q_rows * n_kv * 2;
+    kv_append_rows_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(cache, qkv, pos, rope_cos, rope_sin, batch, q_rows,
+                                                                            n_heads, n_kv, hd);
     return cudaGetLastError();
 }
 

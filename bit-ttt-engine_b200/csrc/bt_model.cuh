@@ -13,7 +13,7 @@ cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int 
                          int n_clear = 0, bool pdl = false);
 
 // Row transform (none | RMSNorm | silu(gate)*up) + per-token absmax int8 quantisation.
-// x: [batch, x_stride] f32 (PRE_SWIGLU: gate at [0,k), up at [k,2k)); q rows of q_stride
+// x: [batch, x_stride] f32 (PRE_SWIGLU: gate and up interleaved in groups of 8 rows, 2k values); q rows of q_stride
 // bytes (multiple of 4, zero-filled beyond k; q may be null); v_out optional [batch, k]
 // transformed row; qtc optional: the same int8 values in the tensor-core product's activation
 // layout (k_tiles = padded k / 256), so that launch_gemm_tc can skip its own quantiser.
@@ -66,6 +66,8 @@ struct AttnArgs {
     const float* rope_sin;
     float* out;              // [batch, n_heads*head_dim]
     int batch, n_heads, n_kv, head_dim;
+    int q_rows;              // new tokens per sequence: 1 = decode; more = prefill (their K/V rows already appended,
+                             // qkv / out rows ordered [sequence][token], pos[b] = position of the first new token)
     int sm_count;            // SMs of the device
     int splits;              // spans per sequence (grid.y) = CTAs of one thread-block cluster
     int span;                // positions per span, multiple of 32
@@ -77,6 +79,11 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
 // Spans per (sequence, KV head) and positions per span for a cache of max_seq positions; rep = query
 // heads per KV head (selects the kernel instance whose cluster limit applies).
 void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int rep, int* splits, int* span);
+// Prefill: RoPE + Q8 append of the keys and values of q_rows new tokens per sequence (qkv rows [b][i]) at
+// positions pos[b] + i.
+cudaError_t launch_kv_append_rows(const KvCacheView& cache, const float* qkv, const int32_t* pos, const float* rope_cos,
+                                  const float* rope_sin, int batch, int q_rows, int n_heads, int n_kv, int hd,
+                                  cudaStream_t stream);
 // QuantizedKVCache::append for one token per sequence: k, v [batch, n_kv, head_dim] f32 (already rotated)
 // are quantised into row pos[b] of the cache.
 cudaError_t launch_kv_append(const KvCacheView& cache, const float* k, const float* v, const int32_t* pos, int batch,

@@ -92,7 +92,8 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const __nv_bflo
 // memory so that global memory is read once.
 //   PRE_NONE   : v = x
 //   PRE_RMSNORM: v = (x / sqrt(mean(x^2) + eps)) * w        (layers/rms_norm.rs:40-55)
-//   PRE_SWIGLU : v = silu(gate) * up, x = [gate | up]        (layers/swiglu.rs:31-33)
+//   PRE_SWIGLU : v = silu(gate) * up, x = gate and up interleaved in groups of 8 (the row order of the fused
+//                gate|up projection: x[16 j + r] = gate[8 j + r], x[16 j + 8 + r] = up[8 j + r])  (layers/swiglu.rs:31-33)
 // then s = max|v|/127, q = clamp(round(v * (127/max|v|))), sum_k q.  `v_out` (optional) receives v.
 // ---------------------------------------------------------------------------------------
 template <int PRE>
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
         }
     } else if (PRE == PRE_SWIGLU) {
         for (int c = threadIdx.x; c < k; c += blockDim.x) {
-            const float g = xr[c], u = xr[k + c];
+            const float g = xr[16 * (c >> 3) + (c & 7)], u = xr[16 * (c >> 3) + 8 + (c & 7)];
             const float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
             row[c] = v;
             amax = fmaxf(amax, fabsf(v));

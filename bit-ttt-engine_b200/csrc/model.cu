@@ -11,6 +11,10 @@
 
 using namespace bt;
 
+__global__ void set_pos_kernel(int32_t* pos, int n, int value) {
+    if (threadIdx.x < n) pos[threadIdx.x] = value;
+}
+
 namespace bt {
 cudaError_t upload_inv_freq(float* dev, int head_dim, double theta);
 
@@ -38,8 +42,7 @@ struct Layer {
     HostLinear host[9];
     bt_linear* qkv = nullptr;
     bt_linear* o = nullptr;
-    bt_linear* gate_up = nullptr;      // [gate; up] stacked (batches above 8)
-    bt_linear* gate_up_il = nullptr;   // gate/up interleaved by 8 rows (fused SwiGLU epilogue)
+    bt_linear* gate_up_il = nullptr;   // gate/up interleaved by 8 rows (fused SwiGLU epilogue; SwiGLU row kernel)
     bt_linear* down = nullptr;
     bt_linear* ttt_down = nullptr;
     bt_linear* ttt_up = nullptr;
@@ -98,6 +101,22 @@ struct bt_model {
     int32_t* tokens_pinned = nullptr;
     int32_t* next_pinned = nullptr;
     float* trace = nullptr;          // inspection aid: per-layer intermediate tensors of a step (caller's device buffer)
+    int trace_rows = 0;              // rows per tensor the trace buffer was sized for
+    // prefill scratch (allocated at the first bt_model_prefill, for pf_rows = sequences x tokens of a chunk)
+    int pf_rows = 0;
+    int32_t* pf_tokens = nullptr;
+    float* pf_h = nullptr;
+    float* pf_qkv = nullptr;
+    float* pf_att = nullptr;
+    float* pf_gu = nullptr;
+    float* pf_act = nullptr;         // silu(gate)*up rows, only while a trace is recorded
+    int pf_act_rows = 0;
+    int8_t* pf_qtc = nullptr;
+    float* pf_sx = nullptr;
+    int32_t* pf_qsum = nullptr;
+    int32_t* pf_part = nullptr;
+    size_t pf_part_bytes = 0;
+    std::vector<int32_t> pf_host;
     unsigned int* err_pinned = nullptr;  // tensor parallel: the device error word as read after a step
     int host_pos = 0;
     int64_t ternary_bytes = 0;
@@ -160,19 +179,20 @@ void trace_widths(const bt_model* m, int64_t (&w)[TR_SLOTS]) {
     w[TR_ACT] = m->i_l;
     w[TR_H_OUT] = H;
 }
-int64_t trace_layer_floats(const bt_model* m) {
+int64_t trace_layer_floats(const bt_model* m, int rows) {
     int64_t w[TR_SLOTS], n = 0;
     trace_widths(m, w);
-    for (int i = 0; i < TR_SLOTS; ++i) n += w[i] * m->cfg.max_batch;
+    for (int i = 0; i < TR_SLOTS; ++i) n += w[i] * rows;
     return n;
 }
-cudaError_t trace_copy(const bt_model* m, int layer, int slot, const float* src, int batch, cudaStream_t s) {
+cudaError_t trace_copy(const bt_model* m, int layer, int slot, const float* src, int rows, cudaStream_t s) {
     if (!m->trace) return cudaSuccess;
+    if (rows > m->trace_rows) return cudaErrorInvalidValue;
     int64_t w[TR_SLOTS], off = 0;
     trace_widths(m, w);
-    for (int i = 0; i < slot; ++i) off += w[i] * m->cfg.max_batch;
-    float* dst = m->trace + (int64_t)layer * trace_layer_floats(m) + off;
-    return cudaMemcpyAsync(dst, src, (size_t)batch * w[slot] * sizeof(float), cudaMemcpyDeviceToDevice, s);
+    for (int i = 0; i < slot; ++i) off += w[i] * m->trace_rows;
+    float* dst = m->trace + (int64_t)layer * trace_layer_floats(m, m->trace_rows) + off;
+    return cudaMemcpyAsync(dst, src, (size_t)rows * w[slot] * sizeof(float), cudaMemcpyDeviceToDevice, s);
 }
 
 bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
@@ -210,7 +230,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
             a.rope_cos = m->rope_cos;
             a.rope_sin = m->rope_sin;
             a.out = m->att;
-            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim;
+            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim; a.q_rows = 1;
             a.sm_count = sm;
             attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
@@ -304,7 +324,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.rope_cos = m->rope_cos;
             a.rope_sin = m->rope_sin;
             a.out = m->att;
-            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim;
+            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim; a.q_rows = 1;
             a.sm_count = sm;
             attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
@@ -318,7 +338,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
         // x = x + mlp(norm2(x))  (model/block.rs:119-131, layers/swiglu.rs:29-35)
         BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->h, batch, s));
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
-        BT_CUDA_TRY(launch_gemm_tc(L.gate_up->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+        BT_CUDA_TRY(launch_gemm_tc(L.gate_up_il->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
         BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, m->trace ? m->act : nullptr, s, m->qtc, kt_i));
         BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
         BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes, true));
@@ -484,12 +504,7 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
         if ((st = create_gate_up(&L.gate_up_il, gu[0]->packed.data(), gu[1]->packed.data(), gu[0]->n_out, gu[0]->k_in,
                                  gu[0]->scale, gu[1]->scale, m->device)) != BT_OK) return st;
         m->ternary_bytes += L.gate_up_il->w.basis_stride();
-        if (B > 8) {
-            if ((st = make_linear(m, gu, 2, &L.gate_up)) != BT_OK) return st;
-            m->ternary_bytes -= L.gate_up->w.basis_stride();  // alternative copy, not streamed in the same step
-        } else {
-            for (HostLinear* hl : gu) { hl->packed.clear(); hl->packed.shrink_to_fit(); }
-        }
+        for (HostLinear* hl : gu) { hl->packed.clear(); hl->packed.shrink_to_fit(); }
         HostLinear* dn[1] = {&L.host[BT_W_DOWN]};
         if ((st = make_linear(m, dn, 1, &L.down)) != BT_OK) return st;
     }
@@ -552,7 +567,7 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
     for (auto& g : m->graphs)
         if (g && g != reinterpret_cast<cudaGraphExec_t>(uintptr_t(1))) cudaGraphExecDestroy(g);  // 1 = "ran eagerly once" sentinel
     for (auto& L : m->layers) {
-        bt_linear_destroy(L.qkv); bt_linear_destroy(L.o); bt_linear_destroy(L.gate_up); bt_linear_destroy(L.gate_up_il); bt_linear_destroy(L.down);
+        bt_linear_destroy(L.qkv); bt_linear_destroy(L.o); bt_linear_destroy(L.gate_up_il); bt_linear_destroy(L.down);
         bt_linear_destroy(L.ttt_down); bt_linear_destroy(L.ttt_up);
         bt_kv_destroy(L.kv);
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
@@ -560,6 +575,8 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
                     m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles, m->tc_part};
     for (void* p : bufs) cudaFree(p);
+    for (void* p : {(void*)m->pf_tokens, (void*)m->pf_h, (void*)m->pf_qkv, (void*)m->pf_att, (void*)m->pf_gu, (void*)m->pf_qtc,
+                    (void*)m->pf_sx, (void*)m->pf_qsum, (void*)m->pf_part, (void*)m->pf_act}) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
     if (m->err_pinned) cudaFreeHost(m->err_pinned);
@@ -667,6 +684,163 @@ extern "C" bt_status bt_model_forward_one(bt_model* m, const int32_t* tokens_hos
     return BT_OK;
 }
 
+
+namespace {
+
+constexpr int kPrefillRowsMax = 2048;  // rows (sequences x tokens) one prefill chunk works on
+
+bt_status prefill_buffers(bt_model* m, int rows) {
+    if (rows <= m->pf_rows) return BT_OK;
+    const bt_model_config& c = m->cfg;
+    const int64_t H = c.hidden_dim, I = m->i_l;
+    const int64_t qw = c.arch == 1 ? m->qkv_dim : m->d_small;  // q|k|v, or the TTT features and predictions (two slots)
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    for (void* p : {(void*)m->pf_tokens, (void*)m->pf_h, (void*)m->pf_qkv, (void*)m->pf_att, (void*)m->pf_gu, (void*)m->pf_qtc,
+                    (void*)m->pf_sx, (void*)m->pf_qsum, (void*)m->pf_part}) cudaFree(p);
+    m->pf_rows = 0;
+    const int64_t kmax = H > I ? H : I;
+    BT_CUDA_TRY(dev_alloc(&m->pf_tokens, (size_t)rows));
+    BT_CUDA_TRY(dev_alloc(&m->pf_h, (size_t)rows * H));
+    BT_CUDA_TRY(dev_alloc(&m->pf_qkv, (size_t)rows * qw));
+    BT_CUDA_TRY(dev_alloc(&m->pf_att, (size_t)rows * H));
+    BT_CUDA_TRY(dev_alloc(&m->pf_gu, (size_t)rows * 2 * I));
+    BT_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&m->pf_qtc), gemm_tc_act_bytes(rows, (kmax + kTileK - 1) / kTileK)));
+    BT_CUDA_TRY(dev_alloc(&m->pf_sx, (size_t)rows));
+    BT_CUDA_TRY(dev_alloc(&m->pf_qsum, (size_t)rows));
+    m->pf_part_bytes = gemm_tc_part_bytes(m->sm_count);
+    BT_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&m->pf_part), m->pf_part_bytes));
+    m->pf_rows = rows;
+    return BT_OK;
+}
+
+// One chunk of a prefill: n new tokens for each of `batch` sequences (rows ordered [sequence][token]), all
+// sequences at position `past`.  Every projection runs on the tensor-core product over all rows at once; K/V
+// rows are appended for the whole chunk, then every token attends causally over the cache
+// (model/block.rs:87-134 applied to a [batch, n, hidden] input, cache semantics of model/llama.rs:495-498).
+bt_status enqueue_prefill_chunk(bt_model* m, int batch, int n, int past, int ttt_chunk, cudaStream_t s) {
+    const bt_model_config& c = m->cfg;
+    const int H = c.hidden_dim, I = m->i_l, M = batch * n;
+    unsigned int* err = device_error_word(m->device);
+    const int sm = m->sm_count;
+    const int kt_h = (H + kTileK - 1) / kTileK, kt_i = (I + kTileK - 1) / kTileK;
+    BT_CUDA_TRY(launch_embed(m->pf_tokens, m->embed, M, H, c.vocab_size, m->pf_h, s, nullptr, 0, false));
+    for (int li = 0; li < c.num_layers; ++li) {
+        Layer& L = m->layers[(size_t)li];
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_IN, m->pf_h, M, s));
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->pf_h, H, L.norm1, kRmsEps, M, H, nullptr, 0, m->pf_sx, m->pf_qsum, nullptr, s, m->pf_qtc, kt_h));
+        if (c.arch == 0) {
+            // TTTLayer::forward_chunkwise (layers/ttt.rs:80-119); ttt_chunk = 1 is the token-by-token update
+            float* feat = m->pf_qkv;
+            float* z = m->pf_att;
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, feat, m->d_small, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, feat, M, s));
+            BT_CUDA_TRY(launch_ttt_chunk(L.w_state, feat, batch, n, m->d_small, c.inner_lr, ttt_chunk, z, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, z, M, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+        } else {
+            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_qkv, m->qkv_dim, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->pf_qkv, M, s));
+            BT_CUDA_TRY(launch_kv_append_rows(L.kv->view, m->pf_qkv, m->pos, m->rope_cos, m->rope_sin, batch, n, m->nh_l, m->nkv_l, m->head_dim, s));
+            AttnArgs a;
+            a.qkv = m->pf_qkv;
+            a.cache = L.kv->view;
+            a.pos = m->pos;
+            a.rope_cos = m->rope_cos;
+            a.rope_sin = m->rope_sin;
+            a.out = m->pf_att;
+            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim; a.q_rows = n;
+            a.sm_count = sm;
+            a.splits = 1;
+            a.span = (c.max_position_embeddings + 31) / 32 * 32;
+            a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
+            a.absmax_out = nullptr;
+            a.pdl = false;
+            if (n == 1) attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
+            BT_CUDA_TRY(launch_attn_decode(a, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->pf_att, M, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+        }
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->pf_h, M, s));
+        BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->pf_h, H, L.norm2, kRmsEps, M, H, nullptr, 0, m->pf_sx, m->pf_qsum, nullptr, s, m->pf_qtc, kt_h));
+        BT_CUDA_TRY(launch_gemm_tc(L.gate_up_il->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, 2 * I, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->pf_gu, 2 * I, nullptr, 0.f, M, I, nullptr, 0, m->pf_sx, m->pf_qsum,
+                                     m->trace ? m->pf_act : nullptr, s, m->pf_qtc, kt_i));
+        if (m->trace) BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->pf_act, M, s));
+        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->pf_h, M, s));
+    }
+    (void)past;
+    return BT_OK;
+}
+
+}  // namespace
+
+extern "C" bt_status bt_model_prefill(bt_model* m, const int32_t* tokens_host, int batch, int n_tokens, int ttt_chunk,
+                                      float* logits_host, int32_t* next_host) {
+    if (!m || !m->finalized || !tokens_host) return set_error(BT_ERR_ARG, "bt_model_prefill: null pointer or model not finalized");
+    if (batch < 1 || batch > m->cfg.max_batch) return set_error(BT_ERR_SHAPE, "bt_model_prefill: batch %d outside 1..%d", batch, m->cfg.max_batch);
+    if (n_tokens < 1) return set_error(BT_ERR_SHAPE, "bt_model_prefill: no tokens");
+    if (m->tp > 1) return set_error(BT_ERR_ARG, "bt_model_prefill: tensor-parallel models prefill token by token (bt_model_forward_one)");
+    if (ttt_chunk < 1 || ttt_chunk > 64) return set_error(BT_ERR_ARG, "bt_model_prefill: ttt_chunk %d outside 1..64", ttt_chunk);
+    const bt_model_config& c = m->cfg;
+    if (c.arch == 1 && m->host_pos + n_tokens > c.max_position_embeddings)
+        return set_error(BT_ERR_SHAPE, "position %d reaches max_position_embeddings %d", m->host_pos + n_tokens, c.max_position_embeddings);
+    DeviceGuard guard(m->device);
+    cudaStream_t s = m->stream;
+    // tokens per sequence and chunk: as many as keep sequences x tokens within the scratch (a TTT chunk is never cut)
+    int per = kPrefillRowsMax / batch;
+    if (per < 1) per = 1;
+    if (per > n_tokens) per = n_tokens;
+    if (c.arch == 0 && per < n_tokens && per > ttt_chunk) per -= per % ttt_chunk;
+    if (m->trace && (int64_t)batch * per > m->trace_rows) per = m->trace_rows / batch;
+    if (per < 1) return set_error(BT_ERR_NOMEM, "bt_model_prefill: the trace buffer holds fewer rows than sequences");
+    bt_status st = prefill_buffers(m, batch * per);
+    if (st != BT_OK) return st;
+    if (m->trace && m->pf_act_rows < batch * per) {
+        BT_CUDA_TRY(cudaDeviceSynchronize());
+        cudaFree(m->pf_act);
+        m->pf_act = nullptr;
+        BT_CUDA_TRY(dev_alloc(&m->pf_act, (size_t)batch * per * m->i_l));
+        m->pf_act_rows = batch * per;
+    }
+    const int H = c.hidden_dim, past0 = m->host_pos;
+    int last_n = 0;
+    for (int c0 = 0; c0 < n_tokens; c0 += per) {
+        const int n = n_tokens - c0 < per ? n_tokens - c0 : per;
+        m->pf_host.resize((size_t)batch * n);
+        for (int b = 0; b < batch; ++b)
+            for (int i = 0; i < n; ++i) m->pf_host[(size_t)b * n + i] = tokens_host[(size_t)b * n_tokens + c0 + i];
+        BT_CUDA_TRY(cudaMemcpyAsync(m->pf_tokens, m->pf_host.data(), (size_t)batch * n * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+        set_pos_kernel<<<1, 64, 0, s>>>(m->pos, c.max_batch, past0 + c0);
+        BT_CUDA_TRY(cudaGetLastError());
+        if ((st = enqueue_prefill_chunk(m, batch, n, past0 + c0, ttt_chunk, s)) != BT_OK) return st;
+        BT_CUDA_TRY(cudaStreamSynchronize(s));  // pf_host is reused by the next chunk
+        last_n = n;
+    }
+    // logits of the last token of every sequence: its hidden state moves into the decode buffers
+    BT_CUDA_TRY(cudaMemcpy2DAsync(m->h, (size_t)H * sizeof(float), m->pf_h + (size_t)(last_n - 1) * H, (size_t)last_n * H * sizeof(float),
+                                  (size_t)H * sizeof(float), (size_t)batch, cudaMemcpyDeviceToDevice, s));
+    if (m->lm_tiles && batch > 8) {
+        BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
+                                      device_error_word(m->device), m->sm_count, s));
+        BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
+    } else {
+        int n_cand = 0;
+        BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
+                                         m->cand_val, m->cand_idx, &n_cand, m->sm_count, s, false));
+        BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, 0, s, false));
+    }
+    set_pos_kernel<<<1, 64, 0, s>>>(m->pos, c.max_batch, past0 + n_tokens);
+    BT_CUDA_TRY(cudaGetLastError());
+    m->host_pos = past0 + n_tokens;
+    if (logits_host)
+        BT_CUDA_TRY(cudaMemcpyAsync(logits_host, m->logits, (size_t)batch * c.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, s));
+    BT_CUDA_TRY(cudaMemcpyAsync(m->next_pinned, m->next, (size_t)batch * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    BT_CUDA_TRY(cudaStreamSynchronize(s));
+    if (next_host) memcpy(next_host, m->next_pinned, (size_t)batch * sizeof(int32_t));
+    return BT_OK;
+}
+
 extern "C" const float* bt_model_logits(bt_model* m) { return m ? m->logits : nullptr; }
 extern "C" const int32_t* bt_model_next(bt_model* m) { return m ? m->next : nullptr; }
 extern "C" int bt_model_pos(const bt_model* m) { return m ? m->host_pos : -1; }
@@ -678,14 +852,16 @@ extern "C" bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer) {
     if (!m || layer < 0 || layer >= (int)m->layers.size()) return nullptr;
     return m->layers[(size_t)layer].kv;
 }
-extern "C" int64_t bt_model_trace_floats(const bt_model* m) {
-    return (m && m->finalized) ? trace_layer_floats(m) * m->cfg.num_layers : 0;
+extern "C" int64_t bt_model_trace_floats(const bt_model* m, int rows) {
+    return (m && m->finalized && rows > 0) ? trace_layer_floats(m, rows) * m->cfg.num_layers : 0;
 }
-extern "C" bt_status bt_model_set_trace(bt_model* m, float* trace_dev) {
+extern "C" bt_status bt_model_set_trace(bt_model* m, float* trace_dev, int rows) {
     if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_set_trace: model not finalized");
+    if (trace_dev && rows < m->cfg.max_batch) return set_error(BT_ERR_ARG, "bt_model_set_trace: rows %d below max_batch %d", rows, m->cfg.max_batch);
     DeviceGuard guard(m->device);
     BT_CUDA_TRY(cudaDeviceSynchronize());
     m->trace = trace_dev;
+    m->trace_rows = trace_dev ? rows : 0;
     return BT_OK;
 }
 extern "C" int64_t bt_model_ternary_bytes(const bt_model* m) { return m ? m->ternary_bytes : 0; }
@@ -719,7 +895,7 @@ extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, int as_in
             continue;
         }
         bt_linear* seq[4] = {c.arch == 1 ? L.qkv : L.ttt_down, c.arch == 1 ? L.o : L.ttt_up,
-                             (batch <= 8 || !L.gate_up) ? L.gate_up_il : L.gate_up, L.down};
+                             L.gate_up_il, L.down};
         for (bt_linear* lin : seq) {
             if (batch > 8) {
                 // tensor-core product on whatever the transformed-row buffer holds (quantiser included)
@@ -751,15 +927,12 @@ extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
     // attention / TTT output, 4 tensor-core products (+ a finishing kernel each where k is split), attention
     // or TTT update; embedding, lm_head (tensor-core: prepare + product; else per 8 tokens), pick
     const Layer& L = m->layers[0];
-    const bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up, L.gate_up, L.down};
+    const bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up, L.gate_up_il, L.down};
     int per_layer = 3 + 1 + 1;
     for (const bt_linear* lin : seq) per_layer += gemm_tc_kernels(lin->dev(), batch, m->sm_count);
     return m->cfg.num_layers * per_layer + 1 + (m->lm_tiles ? 2 + 2 : (batch + 7) / 8 + 1);
 }
 
-__global__ void set_pos_kernel(int32_t* pos, int n, int value) {
-    if (threadIdx.x < n) pos[threadIdx.x] = value;
-}
 
 extern "C" bt_status bt_model_seek(bt_model* m, int pos) {
     if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_seek: model not finalized");

@@ -163,7 +163,7 @@ extern "C" bt_status bt_attn_decode(bt_kv_cache* c, const float* qkv_dev, const 
     a.rope_cos = c->rope_cos;
     a.rope_sin = c->rope_sin;
     a.out = out_dev;
-    a.batch = (int)batch; a.n_heads = (int)n_heads; a.n_kv = (int)c->n_kv; a.head_dim = (int)c->head_dim;
+    a.batch = (int)batch; a.n_heads = (int)n_heads; a.n_kv = (int)c->n_kv; a.head_dim = (int)c->head_dim; a.q_rows = 1;
     a.sm_count = device_sm_count(c->device);
     attn_plan(batch, c->n_kv, c->max_seq, a.sm_count, (int)rep, &a.splits, &a.span);
     a.scaling = (float)(1.0 / sqrt((double)c->head_dim));  // layers/attention.rs:114

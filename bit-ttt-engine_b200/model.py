@@ -55,8 +55,9 @@ def _bind():
     L.bt_model_kv_cache.restype = vp
     L.bt_model_kv_cache.argtypes = [vp, i32]
     L.bt_model_trace_floats.restype = i64
-    L.bt_model_trace_floats.argtypes = [vp]
-    L.bt_model_set_trace.argtypes = [vp, vp]
+    L.bt_model_trace_floats.argtypes = [vp, i32]
+    L.bt_model_set_trace.argtypes = [vp, vp, i32]
+    L.bt_model_prefill.argtypes = [vp, vp, i32, i32, i32, vp, vp]
     L.bt_model_ternary_bytes.restype = i64
     L.bt_model_ternary_bytes.argtypes = [vp]
     L.bt_tp_unique_id.argtypes = [vp]
@@ -250,20 +251,35 @@ class BitLlama:
                                            logits.ctypes.data if want_logits else None, nxt.ctypes.data))
         return logits, nxt
 
+    def prefill(self, tokens, ttt_chunk: int = 1, want_logits: bool = True):
+        """tokens: host ints [batch, n_tokens].  Batched prefill, equivalent to n_tokens forward_one calls
+        (model/llama.rs:495-498); returns (logits of the last token np [batch, vocab] or None, next ids)."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        if tokens.ndim == 1:
+            tokens = tokens[None, :]
+        b, n = tokens.shape
+        logits = np.empty((b, self.cfg.vocab_size), np.float32) if want_logits else None
+        nxt = np.empty(b, np.int32)
+        check(self._L.bt_model_prefill(self._h, tokens.ctypes.data, b, n, ttt_chunk,
+                                       logits.ctypes.data if want_logits else None, nxt.ctypes.data))
+        return logits, nxt
+
     def step_dev(self, tokens_dev):
         """Device-resident step on torch's current stream; results stay on the device."""
         check(self._L.bt_model_step_dev(self._h, _ptr(tokens_dev), tokens_dev.numel(),
                                         _stream_ptr(tokens_dev.device.index)))
 
-    def set_trace(self, on: bool = True) -> None:
-        """Keep the per-layer intermediate tensors of the following steps (see read_trace)."""
+    def set_trace(self, on: bool = True, rows: int = 0) -> None:
+        """Keep the per-layer intermediate tensors of the following steps (see read_trace).
+        rows: rows per tensor (default max_batch; a prefill needs sequences x tokens)."""
         torch = _torch()
         if on:
-            n = self._L.bt_model_trace_floats(self._h)
+            self._trace_rows = max(rows, self.max_batch)
+            n = self._L.bt_model_trace_floats(self._h, self._trace_rows)
             self._trace = torch.zeros(n, dtype=torch.float32, device=f"cuda:{self.device}")
-            check(self._L.bt_model_set_trace(self._h, _ptr(self._trace)))
+            check(self._L.bt_model_set_trace(self._h, _ptr(self._trace), self._trace_rows))
         else:
-            check(self._L.bt_model_set_trace(self._h, None))  # the buffer stays readable (read_trace)
+            check(self._L.bt_model_set_trace(self._h, None, 0))  # the buffer stays readable (read_trace)
 
     def read_trace(self, batch: int):
         """The last traced step: a list over layers of dicts h_in, qkv, att, h_mid, act, h_out
@@ -271,7 +287,7 @@ class BitLlama:
         torch = _torch()
         torch.cuda.synchronize(self.device)
         c, tp = self.cfg, max(self.tp_size, 1)
-        H, B = c.hidden_dim, self.max_batch
+        H, B = c.hidden_dim, self._trace_rows
         if c.arch == "ttt":
             wq = wa = H // 4
         else:

@@ -327,17 +327,32 @@ bt_status bt_model_seek(bt_model* m, int pos);
  * arch llama); KV cache of one layer (NULL for arch ttt). */
 float* bt_model_ttt_state(bt_model* m, int layer);
 bt_kv_cache* bt_model_kv_cache(bt_model* m, int layer);
+/* Batched prefill: n_tokens new tokens for each of `batch` sequences (tokens_host [batch][n_tokens]), all
+ * sequences at the current position.  Equivalent to n_tokens calls of bt_model_forward_one - the reference
+ * CLI's prefill loop, RE/model/llama.rs:495-498: the Q8 caches end up holding the new positions and every
+ * token attends over the dequantised cache up to itself (causal rule of RE/layers/attention.rs:249-262) - but
+ * every projection runs once over all rows on the tensor-core product, K/V rows are appended in one pass and
+ * attention walks blocks of query positions.  arch ttt: the fast-weight state takes one gradient step per
+ * ttt_chunk tokens (TTTLayer::forward_chunkwise, RE/layers/ttt.rs:80-119, as BitLlama::forward_chunkwise
+ * applies it, RE/model/llama.rs:275-312); ttt_chunk = 1 is the token-by-token update of forward_one.
+ * logits_host [batch, vocab] (optional) and next_host [batch] (optional) are those of the LAST token.
+ * Long inputs are worked off in chunks of at most 2048 rows (sequences x tokens).  Synchronous.
+ * Not available on tensor-parallel models (BT_ERR_ARG). */
+bt_status bt_model_prefill(bt_model* m, const int32_t* tokens_host, int batch, int n_tokens, int ttt_chunk,
+                           float* logits_host, int32_t* next_host);
+
 /* Inspection aid: the tensors between the calls of BitLlamaBlock::forward (RE/model/block.rs:87-134).
- * While a trace buffer is set, every step runs launch by launch (no graph replay) and copies, per layer,
- *   h_in [max_batch, hidden] | q|k|v [max_batch, (n_heads + 2 n_kv) head_dim] | attention output
- *   [max_batch, hidden] | h after the attention residual | silu(gate)*up [max_batch, intermediate] |
- *   h after the MLP residual
- * into trace_dev ([num_layers] blocks of that layout, bt_model_trace_floats floats in all; arch ttt: the
- * down-projected features and the TTT prediction, d_small wide, take the places of q|k|v and the attention
- * output; tensor-parallel models record their local slices).  The kernels and their arguments are the ones
- * of the normal step.  trace_dev = NULL switches it off.  Synchronises the device. */
-int64_t bt_model_trace_floats(const bt_model* m);
-bt_status bt_model_set_trace(bt_model* m, float* trace_dev);
+ * While a trace buffer is set, every decode step runs launch by launch (no graph replay) and copies, per layer,
+ *   h_in [rows, hidden] | q|k|v [rows, (n_heads + 2 n_kv) head_dim] | attention output [rows, hidden] |
+ *   h after the attention residual | silu(gate)*up [rows, intermediate] | h after the MLP residual
+ * into trace_dev ([num_layers] blocks of that layout, every tensor with room for `rows` rows,
+ * bt_model_trace_floats(m, rows) floats in all; arch ttt: the down-projected features and the TTT prediction,
+ * d_small wide, take the places of q|k|v and the attention output; tensor-parallel models record their local
+ * slices).  A decode step fills `batch` rows; bt_model_prefill fills sequences x tokens rows, ordered
+ * [sequence][token], and cuts its chunks to fit `rows`.  rows >= max_batch.  The kernels and their
+ * arguments are the ones of the normal step.  trace_dev = NULL switches it off.  Synchronises the device. */
+int64_t bt_model_trace_floats(const bt_model* m, int rows);
+bt_status bt_model_set_trace(bt_model* m, float* trace_dev, int rows);
 /* Ternary-weight bytes streamed by one decode step (sum over all BitLinear tiles). */
 int64_t bt_model_ternary_bytes(const bt_model* m);
 /* Measurement aid (no counterpart in the reference): enqueues only the ternary-product

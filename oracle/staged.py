@@ -102,3 +102,86 @@ def staged_decode_step(oracle, ref, gpu, cfg, tokens, states, act_tol=ACT_TOL, s
         assert logits[b, nxt[b]] == logits[b].max()
         st.pos += 1
     return logits, nxt
+
+
+def staged_prefill(oracle, ref, gpu, cfg, tokens, states, ttt_chunk=1, act_tol=ACT_TOL):
+    """A batched prefill (bt_model_prefill) of tokens [batch, n] checked stage by stage like
+    staged_decode_step: every row of every projection bit for bit on the GPU's own stage inputs, every
+    token's causal attention over the GPU's cache rows, the appended K/V rows, the TTT predictions,
+    and the logits of the last token.  The prefill runs twice from the same state, untraced and traced,
+    and both must give the same bits.  Advances `states`.  Returns (logits, next ids)."""
+    tokens = np.ascontiguousarray(tokens, np.int32)
+    batch, n = tokens.shape
+    pos = gpu.current_pos
+    is_ttt = cfg.arch == "ttt"
+    saved = [gpu.ttt_state(li).clone() for li in range(cfg.num_layers)] if is_ttt else None
+    logits, nxt = gpu.prefill(tokens, ttt_chunk)
+    gpu.seek(pos)
+    if is_ttt:
+        for li in range(cfg.num_layers):
+            gpu.ttt_state(li).copy_(saved[li])
+    gpu.set_trace(True, rows=batch * n)
+    logits_t, nxt_t = gpu.prefill(tokens, ttt_chunk)
+    gpu.set_trace(False)
+    assert np.array_equal(logits, logits_t) and np.array_equal(nxt, nxt_t), "traced and normal prefill differ"
+    assert gpu.current_pos == pos + n
+    tr = gpu.read_trace(batch * n)
+    hd, nh, nkv = cfg.hidden_dim // cfg.n_heads, cfg.n_heads, cfg.n_kv_heads
+    for b in range(batch):
+        st = states[b]
+        assert st.pos == pos
+        rows = slice(b * n, (b + 1) * n)
+        for li in range(cfg.num_layers):
+            L, t = ref.layers[li], tr[li]
+            h_in = t["h_in"][rows]
+            if li == 0:
+                assert np.array_equal(h_in, ref.embed[tokens[b]]), "embedding rows"
+            else:
+                assert np.array_equal(h_in, tr[li - 1]["h_out"][rows])
+            xn = oracle.rmsnorm(h_in, L.norm1, ref.cfg.rms_eps)
+            if is_ttt:
+                assert np.array_equal(t["qkv"][rows], L.ttt_down(xn)), ("ttt down projection", li, b)
+                z_ref = oracle.ttt_chunk(st.w[li], t["qkv"][rows], ref.cfg.inner_lr, ttt_chunk)  # advances the oracle's state
+                assert rel_err(t["att"][rows], z_ref) <= TTT_TOL, ("ttt predictions", li, b, rel_err(t["att"][rows], z_ref))
+                assert np.array_equal(t["h_mid"][rows], h_in + L.ttt_up(t["att"][rows])), ("ttt up projection + residual", li, b)
+            else:
+                qkv_ref = np.concatenate([L.q(xn), L.k(xn), L.v(xn)], axis=1)
+                assert np.array_equal(t["qkv"][rows], qkv_ref), ("q|k|v", li, b, rel_err(t["qkv"][rows], qkv_ref))
+                kq_all, ks_all, vq_all, vs_all = gpu.kv_cache(li).export(b, pos + n)
+                assert len(st.kq[li]) == pos
+                for i in range(n):
+                    qkv = t["qkv"][b * n + i]
+                    k = oracle.rope(qkv[nh * hd:(nh + nkv) * hd].reshape(nkv, hd), pos + i, cfg.rope_theta)
+                    v = qkv[(nh + nkv) * hd:].reshape(nkv, hd)
+                    kq_ref, ks_ref = oracle.kv_quant(k)
+                    vq_ref, vs_ref = oracle.kv_quant(v)
+                    kq, ks, vq, vs = kq_all[:, pos + i], ks_all[:, pos + i], vq_all[:, pos + i], vs_all[:, pos + i]
+                    assert np.array_equal(vq, vq_ref) and np.array_equal(vs, vs_ref), ("appended V row", li, b, i)
+                    assert np.abs(kq.astype(np.int32) - kq_ref.astype(np.int32)).max() <= 1, ("appended K row", li, b, i)
+                    assert rel_err(ks, ks_ref) <= 1e-6
+                    st.kq[li].append(kq.copy()); st.ks[li].append(ks.copy()); st.vq[li].append(vq.copy()); st.vs[li].append(vs.copy())
+                tl = pos + n
+                kd = oracle.kv_dequant(np.ascontiguousarray(kq_all).reshape(nkv * tl, hd), np.ascontiguousarray(ks_all).reshape(-1)).reshape(nkv, tl, hd)
+                vd = oracle.kv_dequant(np.ascontiguousarray(vq_all).reshape(nkv * tl, hd), np.ascontiguousarray(vs_all).reshape(-1)).reshape(nkv, tl, hd)
+                for i in range(n):
+                    q = oracle.rope(t["qkv"][b * n + i][:nh * hd].reshape(nh, hd), pos + i, cfg.rope_theta)
+                    seen = pos + i + 1  # causal: the keys up to the token's own position
+                    att_ref = oracle.attn_decode(q, np.ascontiguousarray(kd[:, :seen]), np.ascontiguousarray(vd[:, :seen])).reshape(-1)
+                    e = rel_err(t["att"][b * n + i], att_ref)
+                    assert e <= ATT_TOL, ("prefill attention", li, b, i, e)
+                h_mid_ref = h_in + L.o(t["att"][rows])
+                assert np.array_equal(t["h_mid"][rows], h_mid_ref), ("o_proj + residual", li, b, rel_err(t["h_mid"][rows], h_mid_ref))
+            xn2 = oracle.rmsnorm(t["h_mid"][rows], L.norm2, ref.cfg.rms_eps)
+            act_ref = oracle.silu_mul(L.gate(xn2), L.up(xn2))
+            e = rel_err(t["act"][rows], act_ref)
+            assert e <= act_tol, ("silu(gate)*up", li, b, e)
+            h_out_ref = t["h_mid"][rows] + L.down(t["act"][rows])
+            assert np.array_equal(t["h_out"][rows], h_out_ref), ("down_proj + residual", li, b, rel_err(t["h_out"][rows], h_out_ref))
+        last = b * n + n - 1
+        hn = oracle.rmsnorm(tr[-1]["h_out"][last:last + 1], ref.norm_f, ref.cfg.rms_eps)
+        logits_ref = oracle.dense_linear(hn, ref.lm_head)[0]
+        e = rel_err(logits[b], logits_ref)
+        assert e <= LOGIT_TOL, ("lm_head", b, e)
+        assert logits[b, nxt[b]] == logits[b].max()
+        st.pos += n
+    return logits, nxt
