@@ -6,8 +6,8 @@
 One "step" is one decode step (one new token per sequence) of a random-init ternary model with
 the Llama-3-8B shape: 32 layers, hidden 4096, MLP 14336, 32 query / 8 KV heads, vocab 128256,
 2-bit packed BitLinear weights, dense bf16 lm_head, Q8 KV cache.  The cache is first filled
-token by token (the reference CLI's prefill, model/llama.rs:495-498) so that the timed steps
-run at the stated context length.  Before anything is timed, the first decode step of the
+by the batched prefill (the semantics of the reference CLI's prefill loop, model/llama.rs:495-498;
+its rate is reported as `prefill`) so that the timed steps run at the stated context length.  Before anything is timed, the first decode step of the
 model is compared with the CPU oracle.
 
 Printed: ONE JSON line (rank 0).  The top-level keys are batch 1: `value` is device-timed
@@ -309,13 +309,30 @@ class Timer:
         return float(t.item())
 
 
-def fill_context(model, cfg, B, context, rng, dev, torch):
-    """Token-by-token prefill of `context` positions, ids fed from a device array."""
+def fill_context(model, cfg, B, context, rng, tm):
+    """Fills the caches with `context` positions per sequence through the batched prefill (bt_model_prefill:
+    host ids in, caches filled, logits of the last token out) and reports its rate."""
+    model.reset_kv_cache()
+    prompt = rng.integers(0, cfg.vocab_size, size=(B, context)).astype(np.int32)
+    model.prefill(prompt[:, :64], want_logits=False)  # first call: scratch allocation and kernel attributes
+    model.reset_kv_cache()
+    tm.barrier()
+    t0 = time.perf_counter()
+    model.prefill(prompt, want_logits=False)
+    seconds = tm.max_over_ranks(time.perf_counter() - t0)
+    return {"tokens": B * context, "batch": B, "tokens_per_sequence": context, "seconds": seconds,
+            "tokens_per_s": B * context / seconds,
+            "note": "bt_model_prefill end to end (host ids in, synchronous): int8 tensor-core products, causal Q8 attention"}
+
+
+def fill_tokenwise(model, cfg, B, context, rng, dev, torch):
+    """Token-by-token prefill (tensor-parallel models): ids fed from a device array."""
     model.reset_kv_cache()
     prompt = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=(context, B)).astype(np.int32)).to(dev)
     for t in range(context):
         model.step_dev(prompt[t])
     torch.cuda.synchronize()
+    return None
 
 
 def time_decode(model, cfg, B, K, W, context, tm, rng):
@@ -532,7 +549,7 @@ def main():
     del weights
 
     # ---- batch 1 ---------------------------------------------------------------------------
-    fill_context(model, cfg, 1, args.context, rng, dev, torch)
+    prefill1 = fill_context(model, cfg, 1, args.context, rng, tm) if world == 1 else fill_tokenwise(model, cfg, 1, args.context, rng, dev, torch)
     sampler = ClockSampler(local_rank)
     sampler.start()
     b1 = measure_batch(bt, syn, model, cfg, 1, K, W, args.context, tm, rng, world, peak, peak_kind)
@@ -541,10 +558,11 @@ def main():
     # ---- batch 64 --------------------------------------------------------------------------
     b64 = None
     if with_b64:
-        fill_context(model, cfg, 64, args.context, rng, dev, torch)
+        prefill64 = fill_context(model, cfg, 64, args.context, rng, tm)
         b64 = measure_batch(bt, syn, model, cfg, 64, K64, W, args.context, tm, rng, world, peak, peak_kind)
         b64["steps"] = K64
         b64["unit"] = UNIT
+        b64["prefill"] = prefill64
 
     if rank == 0:
         cpu = None if args.no_cpu_baseline else cpu_decode_baseline(cfg, syn)
@@ -564,6 +582,8 @@ def main():
             "roofline": b1["roofline"], "attention": b1["attention"], "clocks": clocks,
             "verified_against_oracle": verified,
         }
+        if prefill1 is not None:
+            line["prefill"] = prefill1
         if b64 is not None:
             line["batch64"] = b64
         if cpu is not None:
