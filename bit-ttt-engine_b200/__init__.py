@@ -19,7 +19,7 @@ from . import build as _build
 BT_OK = 0
 BT_ERR_SHAPE, BT_ERR_ALIGN, BT_ERR_DEVICE, BT_ERR_CUDA = -1, -2, -3, -4
 BT_ERR_NCCL, BT_ERR_TIMEOUT, BT_ERR_NOMEM, BT_ERR_ARG = -5, -6, -7, -8
-BT_F32, BT_BF16, BT_I8, BT_I32 = 0, 1, 2, 3
+BT_F32, BT_BF16, BT_I8, BT_I32, BT_F16 = 0, 1, 2, 3, 4
 
 _LIB = None
 

@@ -43,7 +43,8 @@ namespace bt {
 // rows followed by the 8 matching up rows, so that the product's epilogue sees gate[j] and
 // up[j] in the same thread and can emit silu(gate)*up directly (EPI_SWIGLU).
 bt_status create_gate_up(bt_linear** out, const uint8_t* gate_packed_host, const uint8_t* up_packed_host,
-                         int64_t rows, int64_t k_in, float gate_scale, float up_scale, int device);
+                         int64_t rows, int64_t k_in, int n_bases, const float* gate_scales, const float* up_scales,
+                         int device);
 }  // namespace bt
 
 namespace bt {

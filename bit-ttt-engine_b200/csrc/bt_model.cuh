@@ -10,7 +10,7 @@ enum RowPre : int { PRE_NONE = 0, PRE_RMSNORM = 1, PRE_SWIGLU = 2 };
 // Also clears `n_clear` words at `clear` (the per-step absmax cells).
 cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int batch, int hidden,
                          int vocab, float* h, cudaStream_t stream, unsigned int* clear = nullptr,
-                         int n_clear = 0, bool pdl = false);
+                         int n_clear = 0, bool pdl = false, bool f16 = false);  // f16: the table holds IEEE halves, not bf16
 
 // Row transform (none | RMSNorm | silu(gate)*up) + per-token absmax int8 quantisation.
 // x: [batch, x_stride] f32 (PRE_SWIGLU: gate and up interleaved in groups of 8 rows, 2k values); q rows of q_stride
@@ -21,8 +21,8 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
                              int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
                              float* v_out, cudaStream_t stream, int8_t* qtc = nullptr, int k_tiles = 0);
 
-cudaError_t launch_lm_head(const __nv_bfloat16* w, const float* x, int batch, int hidden, int64_t vocab,
-                           float* logits, int sm_count, cudaStream_t stream);
+// h[i] += y[i], i < n
+cudaError_t launch_residual_add(float* h, const float* y, int64_t n, cudaStream_t stream);
 
 cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream);
 
@@ -30,7 +30,8 @@ cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* ou
 // logits[b, :] = lm_head . rmsnorm(h[b, :]); cand_val/cand_idx [batch, *n_cand].
 cudaError_t launch_lm_head_fused(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
                                  int batch, int hidden, int64_t vocab, float* logits, float* cand_val,
-                                 int32_t* cand_idx, int* n_cand, int sm_count, cudaStream_t stream, bool pdl);
+                                 int32_t* cand_idx, int* n_cand, int sm_count, cudaStream_t stream, bool pdl,
+                                 bool f16 = false);  // f16: w holds IEEE halves, not bf16
 // Reduces the candidates to the greedy pick per token and advances the positions.
 cudaError_t launch_pick(const float* cand_val, const int32_t* cand_idx, int n_cand, int batch, int32_t* out,
                         int32_t* pos, int n_pos, cudaStream_t stream, bool pdl);
@@ -42,7 +43,7 @@ size_t lm_head_tc_act_bytes(int hidden);
 cudaError_t launch_lm_retile(const __nv_bfloat16* w, int64_t vocab, int hidden, void* tiles, cudaStream_t stream);
 cudaError_t launch_lm_head_tc(const void* wtiles, const float* h, const float* norm_w, float eps, int batch, int hidden,
                               int64_t vocab, void* btiles, float* logits, unsigned int* err, int sm_count,
-                              cudaStream_t stream);
+                              cudaStream_t stream, bool w_f16 = false);  // w_f16: the weight tiles hold IEEE halves
 
 // Q8 KV cache of one layer: u8 data [batch, n_kv, max_seq, head_dim] and f32 scales
 // [batch, n_kv, max_seq] for K and V (layers/kv_cache.rs:14-24).

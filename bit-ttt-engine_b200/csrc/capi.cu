@@ -518,12 +518,12 @@ extern "C" bt_status bt_linear_forward_noalloc(bt_linear* lin, const void* x_dev
 
 namespace bt {
 
-bt_status create_gate_up(bt_linear** out, const uint8_t* gate, const uint8_t* up, int64_t rows, int64_t k_in,
-                         float gate_scale, float up_scale, int device) {
-    if (!out || !gate || !up) return set_error(BT_ERR_ARG, "create_gate_up: null pointer");
+bt_status create_gate_up(bt_linear** out, const uint8_t* gate, const uint8_t* up, int64_t rows, int64_t k_in, int n_bases,
+                         const float* gate_scales, const float* up_scales, int device) {
+    if (!out || !gate || !up || !gate_scales || !up_scales) return set_error(BT_ERR_ARG, "create_gate_up: null pointer");
     if (rows <= 0 || rows % 8 != 0 || k_in <= 0 || k_in % 4 != 0)
         return set_error(BT_ERR_ALIGN, "create_gate_up: rows must be a multiple of 8 and in_features of 4");
-    const size_t row_bytes = (size_t)(k_in / 4);
+    const size_t row_bytes = (size_t)(k_in / 4) * (size_t)n_bases;  // a row of the [rows, k_in/4, n_bases] layout
     uint8_t* cat = new (std::nothrow) uint8_t[(size_t)rows * 2 * row_bytes];
     if (!cat) return set_error(BT_ERR_NOMEM, "host allocation failed");
     for (int64_t t = 0; t < rows / 8; ++t) {
@@ -531,14 +531,14 @@ bt_status create_gate_up(bt_linear** out, const uint8_t* gate, const uint8_t* up
         memcpy(cat + (size_t)(16 * t + 8) * row_bytes, up + (size_t)(8 * t) * row_bytes, 8 * row_bytes);
     }
     bt_linear* lin = nullptr;
-    const float one_scale[1] = {gate_scale};
-    bt_status st = bt_linear_create(&lin, cat, rows * 2, k_in, 1, one_scale, device);
+    bt_status st = bt_linear_create(&lin, cat, rows * 2, k_in, n_bases, gate_scales, device);
     delete[] cat;
     if (st != BT_OK) return st;
-    const size_t cnt = (size_t)lin->w.row_tiles * 2;
+    const size_t per_basis = (size_t)lin->w.row_tiles * 2, cnt = per_basis * (size_t)n_bases;
     float* host = new (std::nothrow) float[cnt];
     if (!host) { bt_linear_destroy(lin); return set_error(BT_ERR_NOMEM, "host allocation failed"); }
-    for (size_t i = 0; i < cnt; ++i) host[i] = (i & 1) ? up_scale : gate_scale;
+    for (int b = 0; b < n_bases; ++b)
+        for (size_t i = 0; i < per_basis; ++i) host[(size_t)b * per_basis + i] = (i & 1) ? up_scales[b] : gate_scales[b];
     DeviceGuard guard(device);
     cudaError_t e = cudaMemcpy(lin->scale_tiles, host, cnt * sizeof(float), cudaMemcpyHostToDevice);
     delete[] host;

@@ -75,7 +75,7 @@ __device__ __forceinline__ int block_sum_i(int v, int* red) {
 // ---------------------------------------------------------------------------------------
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
                              int hidden, int vocab, float* __restrict__ h, unsigned int* __restrict__ clear,
-                             int n_clear) {
+                             int n_clear, bool f16) {
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
     const int b = blockIdx.x;
@@ -84,7 +84,12 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const __nv_bflo
     int tok = tokens[b];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
     const __nv_bfloat16* row = table + (int64_t)tok * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) h[(int64_t)b * hidden + c] = __bfloat162float(row[c]);
+    if (f16) {  // the table holds IEEE half values (a converted checkpoint's dtype)
+        const __half* hrow = reinterpret_cast<const __half*>(row);
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) h[(int64_t)b * hidden + c] = __half2float(hrow[c]);
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) h[(int64_t)b * hidden + c] = __bfloat162float(row[c]);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -182,61 +187,6 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// dense lm_head: logits[b, v] = sum_c W[v, c] * x[b, c], W bf16 row-major, x f32.
-// (candle_nn::Linear without bias, model/llama.rs:23,266; the converter keeps lm_head in
-// 16-bit, tools/conversion/convert_llama_v2.py:265-268.)  HBM-bound on W: one warp per
-// output row, 16-byte loads, x in shared memory, f32 accumulation.
-// ---------------------------------------------------------------------------------------
-template <int B>
-__global__ void __launch_bounds__(256) lm_head_kernel(const __nv_bfloat16* __restrict__ w,
-                                                      const float* __restrict__ x, int hidden,
-                                                      int64_t v_begin, int64_t v_end,
-                                                      float* __restrict__ logits, int64_t logits_stride) {
-    extern __shared__ float xs[];  // [B][hidden]
-    ptx::pdl_wait();
-    for (int i = threadIdx.x; i < B * hidden; i += blockDim.x) xs[i] = x[i];
-    __syncthreads();
-    const int lane = threadIdx.x & 31;
-    const int64_t warp_global = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t v = v_begin + warp_global; v < v_end; v += warps_total) {
-        const uint4* wr = reinterpret_cast<const uint4*>(w + v * hidden);
-        float acc[B];
-#pragma unroll
-        for (int b = 0; b < B; ++b) acc[b] = 0.0f;
-#pragma unroll 4
-        for (int c8 = lane; c8 < hidden / 8; c8 += 32) {
-            const uint4 pk = wr[c8];
-            const uint32_t u[4] = {pk.x, pk.y, pk.z, pk.w};
-            float wf[8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                wf[2 * j] = __uint_as_float(u[j] << 16);
-                wf[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-            }
-#pragma unroll
-            for (int b = 0; b < B; ++b) {
-                const float4 x0 = *reinterpret_cast<const float4*>(xs + b * hidden + c8 * 8);
-                const float4 x1 = *reinterpret_cast<const float4*>(xs + b * hidden + c8 * 8 + 4);
-                acc[b] = fmaf(wf[0], x0.x, acc[b]);
-                acc[b] = fmaf(wf[1], x0.y, acc[b]);
-                acc[b] = fmaf(wf[2], x0.z, acc[b]);
-                acc[b] = fmaf(wf[3], x0.w, acc[b]);
-                acc[b] = fmaf(wf[4], x1.x, acc[b]);
-                acc[b] = fmaf(wf[5], x1.y, acc[b]);
-                acc[b] = fmaf(wf[6], x1.z, acc[b]);
-                acc[b] = fmaf(wf[7], x1.w, acc[b]);
-            }
-        }
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-            const float r = warp_sum(acc[b]);
-            if (lane == 0) logits[(int64_t)b * logits_stride + v] = r;
-        }
-    }
-}
-
 // Greedy pick: the LAST index among equal maxima, as Iterator::max_by does in the
 // reference's sampler (model/llama.rs:510-515).  One CTA per token.
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t stride,
@@ -274,10 +224,24 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 }
 
 
-// lm_head with the final RMSNorm folded in (every CTA normalises the hidden vector itself,
-// sum of squares in f64) and a running arg-max per CTA, so that the greedy pick does not
-// need a pass over all logits.  Ties keep the larger index (model/llama.rs:510-515).
-template <int B>
+// Two packed 16-bit weights -> f32: bf16 by shifting into the high half, IEEE half by conversion.
+template <bool F16>
+__device__ __forceinline__ void unpack16(uint32_t u, float& lo, float& hi) {
+    if (F16) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
+        lo = f.x; hi = f.y;
+    } else {
+        lo = __uint_as_float(u << 16);
+        hi = __uint_as_float(u & 0xffff0000u);
+    }
+}
+
+// Dense lm_head (candle_nn::Linear without bias, model/llama.rs:23,266; the converter keeps it in 16 bits,
+// tools/conversion/convert_llama_v2.py:265-268) with the final RMSNorm folded in (every CTA normalises the
+// hidden vector itself, sum of squares in f64) and a running arg-max per CTA, so that the greedy pick does
+// not need a pass over all logits.  Ties keep the larger index (model/llama.rs:510-515).  HBM-bound on W:
+// one warp per output row, 16-byte loads, x in shared memory, f32 accumulation.
+template <int B, bool F16>
 __global__ void __launch_bounds__(256) lm_head_fused_kernel(const __nv_bfloat16* __restrict__ w,
                                                             const float* __restrict__ h,
                                                             const float* __restrict__ norm_w, float eps,
@@ -322,10 +286,7 @@ __global__ void __launch_bounds__(256) lm_head_fused_kernel(const __nv_bfloat16*
             const uint32_t u[4] = {pk.x, pk.y, pk.z, pk.w};
             float wf[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                wf[2 * j] = __uint_as_float(u[j] << 16);
-                wf[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-            }
+            for (int j = 0; j < 4; ++j) unpack16<F16>(u[j], wf[2 * j], wf[2 * j + 1]);
 #pragma unroll
             for (int b = 0; b < B; ++b) {
                 const float4 x0 = *reinterpret_cast<const float4*>(xs + b * hidden + c8 * 8);
@@ -400,15 +361,27 @@ __global__ void __launch_bounds__(256) pick_kernel(const float* __restrict__ can
     if (b == 0 && threadIdx.x < n_pos) pos[threadIdx.x] += 1;  // BitLlama::current_pos += 1, model/llama.rs:269
 }
 
+// h += y over n floats (the residual add after a projection whose bases were summed into y first)
+__global__ void __launch_bounds__(256) residual_add_kernel(float* __restrict__ h, const float* __restrict__ y, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        h[i] = __fadd_rn(h[i], y[i]);
+}
+
 }  // namespace
+
+cudaError_t launch_residual_add(float* h, const float* y, int64_t n, cudaStream_t stream) {
+    const int64_t blocks = (n + 255) / 256;
+    residual_add_kernel<<<(unsigned)(blocks < 1184 ? blocks : 1184), 256, 0, stream>>>(h, y, n);
+    return cudaGetLastError();
+}
 
 // ---------------------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------------------
 cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int batch, int hidden,
-                         int vocab, float* h, cudaStream_t stream, unsigned int* clear, int n_clear, bool pdl) {
+                         int vocab, float* h, cudaStream_t stream, unsigned int* clear, int n_clear, bool pdl, bool f16) {
     return launch_pdl(embed_kernel, dim3(batch), dim3(256), 0, stream, pdl, tokens, table, hidden, vocab, h, clear,
-                      n_clear);
+                      n_clear, f16);
 }
 
 cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
@@ -434,41 +407,6 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
     return cudaGetLastError();
 }
 
-template <int B>
-static cudaError_t launch_lm_head_b(const __nv_bfloat16* w, const float* x, int hidden, int64_t vocab,
-                                    float* logits, int64_t stride, int sm_count, cudaStream_t stream) {
-    const size_t smem = (size_t)B * hidden * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(lm_head_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        configured = true;
-    }
-    if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
-    int per_sm = (int)((200 * 1024) / (smem + 1024));
-    per_sm = per_sm > 4 ? 4 : (per_sm < 1 ? 1 : per_sm);
-    lm_head_kernel<B><<<sm_count * per_sm, 256, smem, stream>>>(w, x, hidden, 0, vocab, logits, stride);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_lm_head(const __nv_bfloat16* w, const float* x, int batch, int hidden, int64_t vocab,
-                           float* logits, int sm_count, cudaStream_t stream) {
-    if (hidden % 8 != 0) return cudaErrorInvalidValue;
-    for (int b0 = 0; b0 < batch; b0 += 4) {
-        const int bc = batch - b0 < 4 ? batch - b0 : 4;
-        const float* xb = x + (int64_t)b0 * hidden;
-        float* lb = logits + (int64_t)b0 * vocab;
-        cudaError_t e;
-        switch (bc) {
-            case 1: e = launch_lm_head_b<1>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
-            case 2: e = launch_lm_head_b<2>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
-            case 3: e = launch_lm_head_b<3>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
-            default: e = launch_lm_head_b<4>(w, xb, hidden, vocab, lb, vocab, sm_count, stream); break;
-        }
-        if (e != cudaSuccess) return e;
-    }
-    return cudaSuccess;
-}
-
 cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream) {
     argmax_kernel<<<batch, 1024, 0, stream>>>(logits, vocab, vocab, out);
     return cudaGetLastError();
@@ -476,24 +414,31 @@ cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* ou
 
 int lm_head_max_candidates(int sm_count) { return sm_count * 4; }
 
-template <int B>
-static cudaError_t launch_lm_head_fused_b(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
-                                          int hidden, int64_t vocab, float* logits, float* cand_val,
-                                          int32_t* cand_idx, int grid, cudaStream_t stream, bool pdl) {
+template <int B, bool F16>
+static cudaError_t launch_lm_head_fused_bt(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
+                                           int hidden, int64_t vocab, float* logits, float* cand_val,
+                                           int32_t* cand_idx, int grid, cudaStream_t stream, bool pdl) {
     const size_t smem = (size_t)B * hidden * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(lm_head_fused_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(lm_head_fused_kernel<B, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         configured = true;
     }
     if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
-    return launch_pdl(lm_head_fused_kernel<B>, dim3(grid), dim3(256), smem, stream, pdl, w, h, norm_w, eps, hidden,
+    return launch_pdl(lm_head_fused_kernel<B, F16>, dim3(grid), dim3(256), smem, stream, pdl, w, h, norm_w, eps, hidden,
                       vocab, logits, cand_val, cand_idx);
+}
+template <int B>
+static cudaError_t launch_lm_head_fused_b(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
+                                          int hidden, int64_t vocab, float* logits, float* cand_val,
+                                          int32_t* cand_idx, int grid, cudaStream_t stream, bool pdl, bool f16) {
+    return f16 ? launch_lm_head_fused_bt<B, true>(w, h, norm_w, eps, hidden, vocab, logits, cand_val, cand_idx, grid, stream, pdl)
+               : launch_lm_head_fused_bt<B, false>(w, h, norm_w, eps, hidden, vocab, logits, cand_val, cand_idx, grid, stream, pdl);
 }
 
 cudaError_t launch_lm_head_fused(const __nv_bfloat16* w, const float* h, const float* norm_w, float eps,
                                  int batch, int hidden, int64_t vocab, float* logits, float* cand_val,
-                                 int32_t* cand_idx, int* n_cand, int sm_count, cudaStream_t stream, bool pdl) {
+                                 int32_t* cand_idx, int* n_cand, int sm_count, cudaStream_t stream, bool pdl, bool f16) {
     if (hidden % 8 != 0 || batch < 1) return cudaErrorInvalidValue;
     // one grid size for every group of tokens, so that the candidate rows share a stride
     const int per_pass = batch > 4 ? 8 : 4;  // tokens per pass over the weights
@@ -510,14 +455,14 @@ cudaError_t launch_lm_head_fused(const __nv_bfloat16* w, const float* h, const f
         int32_t* ci = cand_idx + (size_t)b0 * grid;
         cudaError_t e;
         switch (bc) {
-            case 1: e = launch_lm_head_fused_b<1>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            case 2: e = launch_lm_head_fused_b<2>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            case 3: e = launch_lm_head_fused_b<3>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            case 4: e = launch_lm_head_fused_b<4>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            case 5: e = launch_lm_head_fused_b<5>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            case 6: e = launch_lm_head_fused_b<6>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            case 7: e = launch_lm_head_fused_b<7>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
-            default: e = launch_lm_head_fused_b<8>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl); break;
+            case 1: e = launch_lm_head_fused_b<1>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
+            case 2: e = launch_lm_head_fused_b<2>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
+            case 3: e = launch_lm_head_fused_b<3>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
+            case 4: e = launch_lm_head_fused_b<4>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
+            case 5: e = launch_lm_head_fused_b<5>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
+            case 6: e = launch_lm_head_fused_b<6>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
+            case 7: e = launch_lm_head_fused_b<7>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
+            default: e = launch_lm_head_fused_b<8>(w, hb, norm_w, eps, hidden, vocab, lb, cv, ci, grid, stream, pdl, f16); break;
         }
         if (e != cudaSuccess) return e;
     }

@@ -20,12 +20,13 @@ constexpr int kStages = 4;
 constexpr int kThreads = 6 * 32;
 constexpr unsigned kErrLmTimeout = 0x4c4d4844u;  // 'LMHD'
 
-// kind::f16: D = f32, A = B = bf16, K-major, M x N tile
-__device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n) {
+// kind::f16: D = f32, A (the weights) and B (the activation pieces) both bf16 or both IEEE half - the two
+// operand formats of one instruction must be the same 16-bit type - K-major, M x N tile
+__device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n, bool f16) {
     uint32_t d = 0;
     d |= 1u << 4;                    // accumulator format: f32
-    d |= 1u << 7;                    // A format: bf16
-    d |= 1u << 10;                   // B format: bf16
+    d |= (f16 ? 0u : 1u) << 7;       // A format: 0 = f16, 1 = bf16
+    d |= (f16 ? 0u : 1u) << 10;      // B format
     d |= (uint32_t)(n >> 3) << 17;
     d |= (uint32_t)(m >> 4) << 24;
     return d;
@@ -55,8 +56,10 @@ __global__ void lm_retile_kernel(const __nv_bfloat16* __restrict__ w, int64_t vo
 }
 
 // RMSNorm of up to 64 tokens, split into bf16 hi | lo, laid out as the B tiles of every k-chunk
+// f16: the pieces are IEEE halves (hi + lo = 11 + 11 significand bits; a lo piece below 6e-5 is subnormal and
+// keeps an absolute accuracy of 2^-25) to match weights stored as halves; otherwise bf16 (8 + 8 bits).
 __global__ void __launch_bounds__(256) lm_prep_kernel(const float* __restrict__ h, const float* __restrict__ norm_w,
-                                                      float eps, int hidden, int m, uint8_t* __restrict__ btiles) {
+                                                      float eps, int hidden, int m, uint8_t* __restrict__ btiles, bool f16) {
     __shared__ double red[32];
     const int token = blockIdx.x;  // 0..63
     const bool real = token < m;
@@ -72,18 +75,25 @@ __global__ void __launch_bounds__(256) lm_prep_kernel(const float* __restrict__ 
     const float denom = sqrtf(__fadd_rn((float)(ss / (double)hidden), eps));
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float v = real ? __fmul_rn(__fdiv_rn(hr[c], denom), norm_w[c]) : 0.0f;
-        const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-        const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
         uint8_t* tile = btiles + (int64_t)(c / kChunk) * kBTile;
-        *reinterpret_cast<__nv_bfloat16*>(tile + tile_off(token, c % kChunk, kChunk)) = hi;
-        *reinterpret_cast<__nv_bfloat16*>(tile + tile_off(kTok + token, c % kChunk, kChunk)) = lo;
+        if (f16) {
+            const __half hi = __float2half_rn(v);
+            const __half lo = __float2half_rn(v - __half2float(hi));
+            *reinterpret_cast<__half*>(tile + tile_off(token, c % kChunk, kChunk)) = hi;
+            *reinterpret_cast<__half*>(tile + tile_off(kTok + token, c % kChunk, kChunk)) = lo;
+        } else {
+            const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+            const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+            *reinterpret_cast<__nv_bfloat16*>(tile + tile_off(token, c % kChunk, kChunk)) = hi;
+            *reinterpret_cast<__nv_bfloat16*>(tile + tile_off(kTok + token, c % kChunk, kChunk)) = lo;
+        }
     }
 }
 
 __global__ void __launch_bounds__(kThreads, 1) lm_head_tc_kernel(const uint8_t* __restrict__ wtiles,
                                                                  const uint8_t* __restrict__ btiles, int64_t vocab,
                                                                  int hidden, int m, float* __restrict__ logits,
-                                                                 unsigned int* err) {
+                                                                 unsigned int* err, bool w_f16) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stage_base = smem;  // kStages x (A tile | B tile)
     uint64_t* full = reinterpret_cast<uint64_t*>(stage_base + (size_t)kStages * (kATile + kBTile));
@@ -123,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 1) lm_head_tc_kernel(const uint8_t* 
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = instr_desc_bf16(kRows, kCols);
+            const uint32_t idesc = instr_desc_bf16(kRows, kCols, w_f16);
             int slot = 0; uint32_t par = 0, acc_par = 0; bool first_tile = true;
             for (int64_t rs = blockIdx.x; rs < row_sets; rs += gridDim.x) {
                 if (!first_tile) { ok &= ptx::mbar_wait_bounded(acc_empty, acc_par); acc_par ^= 1; }
@@ -194,7 +204,7 @@ cudaError_t launch_lm_retile(const __nv_bfloat16* w, int64_t vocab, int hidden, 
 // logits for up to 64 tokens per pass; h: [batch, hidden] residual stream (RMSNorm applied here)
 cudaError_t launch_lm_head_tc(const void* wtiles, const float* h, const float* norm_w, float eps, int batch, int hidden,
                               int64_t vocab, void* btiles, float* logits, unsigned int* err, int sm_count,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, bool w_f16) {
     if (hidden % kChunk != 0) return cudaErrorInvalidValue;
     const size_t smem = (size_t)kStages * (kATile + kBTile) + 256;
     static bool configured = false;
@@ -208,10 +218,10 @@ cudaError_t launch_lm_head_tc(const void* wtiles, const float* h, const float* n
     for (int b0 = 0; b0 < batch; b0 += kTok) {
         const int bc = batch - b0 < kTok ? batch - b0 : kTok;
         lm_prep_kernel<<<kTok, 256, 0, stream>>>(h + (size_t)b0 * hidden, norm_w, eps, hidden, bc,
-                                                 reinterpret_cast<uint8_t*>(btiles));
+                                                 reinterpret_cast<uint8_t*>(btiles), w_f16);
         lm_head_tc_kernel<<<grid, kThreads, smem, stream>>>(reinterpret_cast<const uint8_t*>(wtiles),
                                                            reinterpret_cast<const uint8_t*>(btiles), vocab, hidden, bc,
-                                                           logits + (size_t)b0 * vocab, err);
+                                                           logits + (size_t)b0 * vocab, err, w_f16);
     }
     return cudaGetLastError();
 }

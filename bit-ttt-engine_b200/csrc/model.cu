@@ -21,9 +21,12 @@ cudaError_t upload_inv_freq(float* dev, int head_dim, double theta);
 __global__ void advance_pos_kernel(int32_t* pos, int n) {
     if (threadIdx.x < n) pos[threadIdx.x] += 1;
 }
-__global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t n) {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-        out[i] = __float2bfloat16_rn(in[i]);
+// f32 -> the 16-bit storage type of the dense tables: bf16, or IEEE half (same 2 bytes per element)
+__global__ void f32_to_16bit_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t n, bool f16) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        if (f16) reinterpret_cast<__half*>(out)[i] = __float2half_rn(in[i]);
+        else out[i] = __float2bfloat16_rn(in[i]);
+    }
 }
 }  // namespace bt
 
@@ -32,9 +35,10 @@ namespace {
 constexpr float kRmsEps = 1e-5f;  // model/block.rs:10, model/llama.rs:13
 
 struct HostLinear {
-    std::vector<uint8_t> packed;
+    std::vector<uint8_t> packed;  // [n_out, k_in/4, n_bases]
     int64_t n_out = 0, k_in = 0;
-    float scale = 0.f;
+    int n_bases = 1;
+    float scales[8] = {0};
     bool set = false;
 };
 
@@ -65,9 +69,11 @@ struct bt_model {
     void* peer = nullptr;            // peer-memory exchange (CUDA IPC inboxes) when the ranks have set it up
     int32_t* acc_i32 = nullptr;      // [max_batch, hidden] accumulators of a row-parallel projection
     bool finalized = false;
+    bool multi_basis = false;        // a projection has several bases: the step runs quantiser and product kernels separately
     std::vector<Layer> layers;
-    __nv_bfloat16* embed = nullptr;
+    __nv_bfloat16* embed = nullptr;   // 16-bit storage: bf16, or IEEE half when embed_f16
     __nv_bfloat16* lm_head = nullptr;
+    bool embed_f16 = false, head_f16 = false;
     float* norm_f = nullptr;
     float* inv_freq = nullptr;
     float* rope_cos = nullptr;   // [max_pos, head_dim/2]
@@ -129,22 +135,46 @@ namespace {
 template <typename T>
 cudaError_t dev_alloc(T** p, size_t count) { return cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)); }
 
+// One BitLinear from 1..3 projections that share their input, stacked along the output rows; every part in the
+// checkpoint layout [rows, k_in/4, n_bases] with its own scale per basis (the parts agree on n_bases).
 bt_status make_linear(bt_model* m, HostLinear** parts, int n_parts, bt_linear** out) {
-    const uint8_t* ptrs[3];
-    int64_t rows[3];
-    float scales[3];
+    int64_t rows_total = 0;
     for (int i = 0; i < n_parts; ++i) {
         if (!parts[i]->set) return set_error(BT_ERR_ARG, "bt_model_finalize: a projection weight was never set");
         if (parts[i]->k_in != parts[0]->k_in) return set_error(BT_ERR_SHAPE, "bt_model_finalize: fused projections disagree on in_features");
-        ptrs[i] = parts[i]->packed.data();
-        rows[i] = parts[i]->n_out;
-        scales[i] = parts[i]->scale;
+        if (parts[i]->n_bases != parts[0]->n_bases) return set_error(BT_ERR_SHAPE, "bt_model_finalize: fused projections disagree on the number of bases");
+        if (n_parts > 1 && parts[i]->n_out % kTileRows != 0)
+            return set_error(BT_ERR_ALIGN, "bt_model_finalize: a fused projection has %lld rows (need a multiple of 16)", (long long)parts[i]->n_out);
+        rows_total += parts[i]->n_out;
     }
+    const int nb = parts[0]->n_bases;
+    const size_t row_bytes = (size_t)(parts[0]->k_in / 4) * nb;
     bt_status st;
-    if (n_parts == 1) st = bt_linear_create(out, ptrs[0], rows[0], parts[0]->k_in, 1, scales, m->device);
-    else st = bt_linear_create_fused(out, ptrs, rows, scales, n_parts, parts[0]->k_in, m->device);
+    if (n_parts == 1) {
+        st = bt_linear_create(out, parts[0]->packed.data(), rows_total, parts[0]->k_in, nb, parts[0]->scales, m->device);
+    } else {
+        std::vector<uint8_t> cat((size_t)rows_total * row_bytes);
+        size_t off = 0;
+        for (int i = 0; i < n_parts; ++i) {
+            memcpy(cat.data() + off, parts[i]->packed.data(), (size_t)parts[i]->n_out * row_bytes);
+            off += (size_t)parts[i]->n_out * row_bytes;
+        }
+        st = bt_linear_create(out, cat.data(), rows_total, parts[0]->k_in, nb, parts[0]->scales, m->device);
+        if (st == BT_OK) {
+            // one weight scale per (basis, half row tile): every part brings its own
+            const int64_t rt2 = (*out)->w.row_tiles * 2;
+            std::vector<float> host((size_t)nb * rt2);
+            for (int b = 0; b < nb; ++b) {
+                int64_t r = 0;
+                for (int i = 0; i < n_parts; ++i)
+                    for (int64_t k = 0; k < parts[i]->n_out / kTileRows * 2; ++k) host[(size_t)b * rt2 + r++] = parts[i]->scales[b];
+            }
+            cudaError_t e = cudaMemcpy((*out)->scale_tiles, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "bt_model_finalize: %s", cudaGetErrorString(e));
+        }
+    }
     if (st != BT_OK) return st;
-    m->ternary_bytes += (*out)->w.basis_stride();
+    m->ternary_bytes += (*out)->w.basis_stride() * nb;
     for (int i = 0; i < n_parts; ++i) { parts[i]->packed.clear(); parts[i]->packed.shrink_to_fit(); }
     return BT_OK;
 }
@@ -203,7 +233,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
     const int sm = m->sm_count;
     const bool split_quant = m->tp == 1 && c.arch == 1 && batch >= kSplitQuantBatch;
     bt_status qst;
-    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, true));
+    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, true, m->embed_f16));
     for (int li = 0; li < c.num_layers; ++li) {
         Layer& L = m->layers[(size_t)li];
         unsigned int* amax_core = m->absmax + ((size_t)li * 2 + 0) * B;
@@ -287,7 +317,7 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
     }
     int n_cand = 0;
     BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
-                                     m->cand_val, m->cand_idx, &n_cand, sm, s, true));
+                                     m->cand_val, m->cand_idx, &n_cand, sm, s, true, m->head_f16));
     BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, true));
     return BT_OK;
 }
@@ -300,7 +330,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
     const int kt_h = (H + kTileK - 1) / kTileK, kt_i = (I + kTileK - 1) / kTileK;
-    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, false));
+    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, false, m->embed_f16));
     for (int li = 0; li < c.num_layers; ++li) {
         Layer& L = m->layers[(size_t)li];
         // x_norm = norm1(x)  (model/block.rs:98)
@@ -347,7 +377,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
     if (m->lm_tiles) {
         BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
-                                      err, sm, s));
+                                      err, sm, s, m->head_f16));
         BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
         advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, B);
         BT_CUDA_TRY(cudaGetLastError());
@@ -355,7 +385,93 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     }
     int n_cand = 0;
     BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
-                                     m->cand_val, m->cand_idx, &n_cand, sm, s, false));
+                                     m->cand_val, m->cand_idx, &n_cand, sm, s, false, m->head_f16));
+    BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, false));
+    return BT_OK;
+}
+
+// One decode step with every stage as its own kernel: row transform + quantiser, then the product of every
+// basis (streaming kernel up to 8 sequences, tensor-core kernel above), the bases summed in basis order before
+// the residual is added (AdaptiveBitLinear: y = x . (sum_b scale_b T_b)^T, layers/adaptive_linear.rs:86-161).
+// Used for models with several bases per projection; any batch size.
+bt_status enqueue_step_generic(bt_model* m, int batch, cudaStream_t s) {
+    const bt_model_config& c = m->cfg;
+    const int H = c.hidden_dim, I = m->i_l, B = c.max_batch;
+    unsigned int* err = device_error_word(m->device);
+    const int sm = m->sm_count;
+    const bool tc = batch > 8;
+    auto quant = [&](int pre, const float* x, int64_t x_stride, const float* w, int k, float* v_out) -> bt_status {
+        const int64_t qs = ((int64_t)k + kTileK - 1) / kTileK * kTileK;
+        BT_CUDA_TRY(launch_row_quant(pre, x, x_stride, w, kRmsEps, batch, k, tc ? nullptr : m->q, tc ? 0 : qs, m->sx, m->qsum, v_out, s,
+                                     tc ? m->qtc : nullptr, (int)(qs / kTileK)));
+        return BT_OK;
+    };
+    auto product = [&](bt_linear* lin, float* out, int64_t out_stride) -> bt_status {
+        const int64_t qs = lin->w.k_pad();
+        if (tc)
+            BT_CUDA_TRY(launch_gemm_tc(lin->dev(), nullptr, lin->w.k_in, batch, m->qtc, m->sx, m->qsum, out, out_stride, EPI_F32, err, sm, s,
+                                       m->tc_part, m->tc_part_bytes, true));
+        else
+            BT_CUDA_TRY(linear_product(lin->dev(), m->q, qs, m->qsum, m->sx, batch, out, out_stride, EPI_F32, err, sm, s));
+        return BT_OK;
+    };
+    bt_status st;
+    float* tmp = m->xn;  // [max_batch, hidden]
+    BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, false, m->embed_f16));
+    for (int li = 0; li < c.num_layers; ++li) {
+        Layer& L = m->layers[(size_t)li];
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_IN, m->h, batch, s));
+        if ((st = quant(PRE_RMSNORM, m->h, H, L.norm1, H, nullptr)) != BT_OK) return st;
+        if (c.arch == 0) {
+            if ((st = product(L.ttt_down, m->feat, m->d_small)) != BT_OK) return st;
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->feat, batch, s));
+            BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->z, batch, s));
+            if ((st = quant(PRE_NONE, m->z, m->d_small, nullptr, m->d_small, nullptr)) != BT_OK) return st;
+            if ((st = product(L.ttt_up, tmp, H)) != BT_OK) return st;
+        } else {
+            if ((st = product(L.qkv, m->qkv, m->qkv_dim)) != BT_OK) return st;
+            BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->qkv, batch, s));
+            AttnArgs a;
+            a.qkv = m->qkv;
+            a.cache = L.kv->view;
+            a.pos = m->pos;
+            a.rope_cos = m->rope_cos;
+            a.rope_sin = m->rope_sin;
+            a.out = m->att;
+            a.batch = batch; a.n_heads = m->nh_l; a.n_kv = m->nkv_l; a.head_dim = m->head_dim; a.q_rows = 1;
+            a.sm_count = sm;
+            attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
+            a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
+            a.absmax_out = nullptr;
+            a.pdl = false;
+            BT_CUDA_TRY(launch_attn_decode(a, s));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->att, batch, s));
+            const int att_dim = m->nh_l * m->head_dim;
+            if ((st = quant(PRE_NONE, m->att, att_dim, nullptr, att_dim, nullptr)) != BT_OK) return st;
+            if ((st = product(L.o, tmp, H)) != BT_OK) return st;
+        }
+        BT_CUDA_TRY(launch_residual_add(m->h, tmp, (int64_t)batch * H, s));
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->h, batch, s));
+        if ((st = quant(PRE_RMSNORM, m->h, H, L.norm2, H, nullptr)) != BT_OK) return st;
+        if ((st = product(L.gate_up_il, m->gu, 2 * I)) != BT_OK) return st;
+        if ((st = quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, I, m->act)) != BT_OK) return st;
+        BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
+        if ((st = product(L.down, tmp, H)) != BT_OK) return st;
+        BT_CUDA_TRY(launch_residual_add(m->h, tmp, (int64_t)batch * H, s));
+        BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
+    }
+    if (m->lm_tiles && tc) {
+        BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
+                                      err, sm, s, m->head_f16));
+        BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
+        advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, B);
+        BT_CUDA_TRY(cudaGetLastError());
+        return BT_OK;
+    }
+    int n_cand = 0;
+    BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
+                                     m->cand_val, m->cand_idx, &n_cand, sm, s, false, m->head_f16));
     BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, false));
     return BT_OK;
 }
@@ -412,12 +528,14 @@ extern "C" bt_status bt_model_create(bt_model** out, const bt_model_config* cfg,
     return BT_OK;
 }
 
-extern "C" bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
-                                         int64_t n_out, int64_t k_in, float scale) {
-    if (!m || !packed_host) return set_error(BT_ERR_ARG, "bt_model_set_linear: null pointer");
+extern "C" bt_status bt_model_set_linear_bases(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
+                                               int64_t n_out, int64_t k_in, int n_bases, const float* scales_host) {
+    if (!m || !packed_host || !scales_host) return set_error(BT_ERR_ARG, "bt_model_set_linear: null pointer");
     if (m->finalized) return set_error(BT_ERR_ARG, "bt_model_set_linear: model already finalized");
     if (layer < 0 || layer >= m->cfg.num_layers || (int)kind < 0 || (int)kind > 8)
         return set_error(BT_ERR_ARG, "bt_model_set_linear: layer %d / kind %d out of range", layer, (int)kind);
+    if (n_bases < 1 || n_bases > 8) return set_error(BT_ERR_ARG, "bt_model_set_linear: n_bases %d outside 1..8", n_bases);
+    if (n_bases > 1 && m->tp > 1) return set_error(BT_ERR_ARG, "bt_model_set_linear: tensor-parallel models take one basis per projection");
     const bt_model_config& c = m->cfg;
     const int64_t H = c.hidden_dim, I = m->i_l, hd = m->head_dim, d = m->d_small;
     int64_t en = 0, ek = 0;
@@ -434,19 +552,34 @@ extern "C" bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind 
         return set_error(BT_ERR_SHAPE, "bt_model_set_linear: weight [%lld, %lld] given, [%lld, %lld] expected",
                          (long long)n_out, (long long)k_in, (long long)en, (long long)ek);
     HostLinear& hl = m->layers[(size_t)layer].host[(int)kind];
-    hl.packed.assign(packed_host, packed_host + (size_t)n_out * (size_t)(k_in / 4));
-    hl.n_out = n_out; hl.k_in = k_in; hl.scale = scale; hl.set = true;
+    hl.packed.assign(packed_host, packed_host + (size_t)n_out * (size_t)(k_in / 4) * (size_t)n_bases);
+    hl.n_out = n_out; hl.k_in = k_in; hl.n_bases = n_bases; hl.set = true;
+    for (int b = 0; b < n_bases; ++b) hl.scales[b] = scales_host[b];
+    if (n_bases > 1) m->multi_basis = true;
     return BT_OK;
 }
 
+extern "C" bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
+                                         int64_t n_out, int64_t k_in, float scale) {
+    return bt_model_set_linear_bases(m, layer, kind, packed_host, n_out, k_in, 1, &scale);
+}
+
 extern "C" bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int layer, const float* data, int64_t n_elem) {
+    return bt_model_set_tensor_typed(m, kind, layer, data, n_elem, BT_BF16);
+}
+
+extern "C" bt_status bt_model_set_tensor_typed(bt_model* m, bt_tensor_kind kind, int layer, const float* data, int64_t n_elem,
+                                               bt_dtype storage) {
     if (!m || !data) return set_error(BT_ERR_ARG, "bt_model_set_tensor: null pointer");
+    if (storage != BT_BF16 && storage != BT_F16) return set_error(BT_ERR_ARG, "bt_model_set_tensor: storage must be BT_BF16 or BT_F16");
+    if (m->finalized) return set_error(BT_ERR_ARG, "bt_model_set_tensor: model already finalized");
     const bt_model_config& c = m->cfg;
     DeviceGuard guard(m->device);
     const int64_t H = c.hidden_dim, VH = (int64_t)c.vocab_size * H;
     if (kind == BT_T_EMBED || kind == BT_T_LM_HEAD) {
         if (n_elem != VH) return set_error(BT_ERR_SHAPE, "bt_model_set_tensor: %lld elements given, %lld expected", (long long)n_elem, (long long)VH);
         __nv_bfloat16** dst = kind == BT_T_EMBED ? &m->embed : &m->lm_head;
+        (kind == BT_T_EMBED ? m->embed_f16 : m->head_f16) = storage == BT_F16;
         if (!*dst) BT_CUDA_TRY(dev_alloc(dst, (size_t)VH));
         // staged through a bounded f32 buffer, converted on the device
         const int64_t chunk = 16 << 20;
@@ -456,7 +589,7 @@ extern "C" bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int l
             const int64_t n = VH - off < chunk ? VH - off : chunk;
             cudaError_t e = cudaMemcpy(tmp, data + off, (size_t)n * sizeof(float), cudaMemcpyHostToDevice);
             if (e == cudaSuccess) {
-                f32_to_bf16_kernel<<<1184, 256>>>(tmp, *dst + off, n);
+                f32_to_16bit_kernel<<<1184, 256>>>(tmp, *dst + off, n, storage == BT_F16);
                 e = cudaDeviceSynchronize();
             }
             if (e != cudaSuccess) { cudaFree(tmp); return set_error(BT_ERR_CUDA, "bt_model_set_tensor: %s", cudaGetErrorString(e)); }
@@ -501,9 +634,10 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
         }
         HostLinear* gu[2] = {&L.host[BT_W_GATE], &L.host[BT_W_UP]};
         if (!gu[0]->set || !gu[1]->set) return set_error(BT_ERR_ARG, "bt_model_finalize: a projection weight was never set");
+        if (gu[0]->n_bases != gu[1]->n_bases) return set_error(BT_ERR_SHAPE, "bt_model_finalize: gate and up projections disagree on the number of bases");
         if ((st = create_gate_up(&L.gate_up_il, gu[0]->packed.data(), gu[1]->packed.data(), gu[0]->n_out, gu[0]->k_in,
-                                 gu[0]->scale, gu[1]->scale, m->device)) != BT_OK) return st;
-        m->ternary_bytes += L.gate_up_il->w.basis_stride();
+                                 gu[0]->n_bases, gu[0]->scales, gu[1]->scales, m->device)) != BT_OK) return st;
+        m->ternary_bytes += L.gate_up_il->w.basis_stride() * gu[0]->n_bases;
         for (HostLinear* hl : gu) { hl->packed.clear(); hl->packed.shrink_to_fit(); }
         HostLinear* dn[1] = {&L.host[BT_W_DOWN]};
         if ((st = make_linear(m, dn, 1, &L.down)) != BT_OK) return st;
@@ -597,11 +731,17 @@ extern "C" bt_status bt_model_reset(bt_model* m) {
     }
     BT_CUDA_TRY(cudaMemset(m->pos, 0, (size_t)m->cfg.max_batch * sizeof(int32_t)));
     if (m->peer) BT_CUDA_TRY(tp_peer_reset(m->peer));  // exchange epochs restart; every rank resets between the same steps
+    BT_CUDA_TRY(cudaDeviceSynchronize());  // the clears are done before a step on another stream can start
     m->host_pos = 0;
     return BT_OK;
 }
 
 namespace {
+
+bt_status enqueue_any(bt_model* m, int batch, cudaStream_t s) {
+    if (m->multi_basis) return enqueue_step_generic(m, batch, s);
+    return batch <= 8 ? enqueue_step_fused(m, batch, s) : enqueue_step(m, batch, s);
+}
 
 bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
     if (m->tp > 1 && !m->comm && !tp_peer_ready(m->peer))
@@ -615,10 +755,10 @@ bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
     const uintptr_t marker = 1;  // "ran eagerly once" sentinel stored in the table
     if (m->trace) {
         // inspection: launch by launch with the copies into the trace buffer in between (never captured)
-        bt_status st = batch <= 8 ? enqueue_step_fused(m, batch, s) : enqueue_step(m, batch, s);
+        bt_status st = enqueue_any(m, batch, s);
         if (st != BT_OK) return st;
     } else if (exec == nullptr) {
-        bt_status st = batch <= 8 ? enqueue_step_fused(m, batch, s) : enqueue_step(m, batch, s);
+        bt_status st = enqueue_any(m, batch, s);
         if (st != BT_OK) return st;
         exec = reinterpret_cast<cudaGraphExec_t>(marker);
     } else if (exec == reinterpret_cast<cudaGraphExec_t>(marker)) {
@@ -627,7 +767,7 @@ bt_status run_step(bt_model* m, int batch, cudaStream_t s) {
         // launched on the caller's
         cudaStream_t cs = m->stream;
         BT_CUDA_TRY(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
-        bt_status st = batch <= 8 ? enqueue_step_fused(m, batch, cs) : enqueue_step(m, batch, cs);
+        bt_status st = enqueue_any(m, batch, cs);
         cudaError_t e = cudaStreamEndCapture(cs, &graph);
         if (st != BT_OK) { if (graph) cudaGraphDestroy(graph); return st; }
         if (e != cudaSuccess) return set_error(BT_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
@@ -723,7 +863,7 @@ bt_status enqueue_prefill_chunk(bt_model* m, int batch, int n, int past, int ttt
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
     const int kt_h = (H + kTileK - 1) / kTileK, kt_i = (I + kTileK - 1) / kTileK;
-    BT_CUDA_TRY(launch_embed(m->pf_tokens, m->embed, M, H, c.vocab_size, m->pf_h, s, nullptr, 0, false));
+    BT_CUDA_TRY(launch_embed(m->pf_tokens, m->embed, M, H, c.vocab_size, m->pf_h, s, nullptr, 0, false, m->embed_f16));
     for (int li = 0; li < c.num_layers; ++li) {
         Layer& L = m->layers[(size_t)li];
         BT_CUDA_TRY(trace_copy(m, li, TR_H_IN, m->pf_h, M, s));
@@ -736,7 +876,12 @@ bt_status enqueue_prefill_chunk(bt_model* m, int batch, int n, int past, int ttt
             BT_CUDA_TRY(trace_copy(m, li, TR_QKV, feat, M, s));
             BT_CUDA_TRY(launch_ttt_chunk(L.w_state, feat, batch, n, m->d_small, c.inner_lr, ttt_chunk, z, s));
             BT_CUDA_TRY(trace_copy(m, li, TR_ATT, z, M, s));
-            BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+            if (m->multi_basis) {  // the bases are summed first, then the residual is added (the order the layer defines)
+                BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, H, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes));
+                BT_CUDA_TRY(launch_residual_add(m->pf_h, m->pf_gu, (int64_t)M * H, s));
+            } else {
+                BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+            }
         } else {
             BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_qkv, m->qkv_dim, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
             BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->pf_qkv, M, s));
@@ -758,7 +903,12 @@ bt_status enqueue_prefill_chunk(bt_model* m, int batch, int n, int past, int ttt
             if (n == 1) attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
             BT_CUDA_TRY(launch_attn_decode(a, s));
             BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->pf_att, M, s));
-            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+            if (m->multi_basis) {
+                BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, H, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes));
+                BT_CUDA_TRY(launch_residual_add(m->pf_h, m->pf_gu, (int64_t)M * H, s));
+            } else {
+                BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+            }
         }
         BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->pf_h, M, s));
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->pf_h, H, L.norm2, kRmsEps, M, H, nullptr, 0, m->pf_sx, m->pf_qsum, nullptr, s, m->pf_qtc, kt_h));
@@ -766,7 +916,12 @@ bt_status enqueue_prefill_chunk(bt_model* m, int batch, int n, int past, int ttt
         BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->pf_gu, 2 * I, nullptr, 0.f, M, I, nullptr, 0, m->pf_sx, m->pf_qsum,
                                      m->trace ? m->pf_act : nullptr, s, m->pf_qtc, kt_i));
         if (m->trace) BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->pf_act, M, s));
-        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+        if (m->multi_basis) {
+            BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_att, H, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+            BT_CUDA_TRY(launch_residual_add(m->pf_h, m->pf_att, (int64_t)M * H, s));
+        } else {
+            BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+        }
         BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->pf_h, M, s));
     }
     (void)past;
@@ -822,12 +977,12 @@ extern "C" bt_status bt_model_prefill(bt_model* m, const int32_t* tokens_host, i
                                   (size_t)H * sizeof(float), (size_t)batch, cudaMemcpyDeviceToDevice, s));
     if (m->lm_tiles && batch > 8) {
         BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
-                                      device_error_word(m->device), m->sm_count, s));
+                                      device_error_word(m->device), m->sm_count, s, m->head_f16));
         BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
     } else {
         int n_cand = 0;
         BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
-                                         m->cand_val, m->cand_idx, &n_cand, m->sm_count, s, false));
+                                         m->cand_val, m->cand_idx, &n_cand, m->sm_count, s, false, m->head_f16));
         BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, 0, s, false));
     }
     set_pos_kernel<<<1, 64, 0, s>>>(m->pos, c.max_batch, past0 + n_tokens);

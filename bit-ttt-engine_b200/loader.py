@@ -143,8 +143,11 @@ def _first(tensors: dict, names, what: str):
 
 
 def _linear(tensors: dict, prefix: str, n_out: int, k_in: int):
-    """(packed [n_out, k_in/4] u8, scale) for one projection: BitLinear::load first, then the
-    converted format (layers/adaptive_linear.rs:42-84)."""
+    """(packed, scale(s)) for one projection: BitLinear::load first (dense weight, packed here), then
+    the converted format (layers/adaptive_linear.rs:42-84): `weight_packed` [n_out, k_in/4, n_bases] with
+    `scales` [n_bases] - one basis comes back as [n_out, k_in/4] with a float scale, several as the 3-d
+    array with an array of scales - or the legacy one-byte-per-weight layout [n_out, k_in/4, n_bases, 4]
+    (tools/conversion/convert_adaptive.py:43-83), rewritten to 2 bits per weight."""
     if prefix + ".weight" in tensors:
         dense = _f32(tensors[prefix + ".weight"])
         if dense.shape != (n_out, k_in):
@@ -159,25 +162,34 @@ def _linear(tensors: dict, prefix: str, n_out: int, k_in: int):
         packed = np.asarray(packed).astype(np.uint8)
     if not 1 <= scales.size <= 8:
         raise CheckpointError(f"{prefix}.scales has {scales.size} entries, the format allows 1..8")
+    if packed.ndim == 4:  # legacy layout: one signed byte per weight, 4 weights per block
+        if packed.shape != (n_out, k_in // 4, scales.size, 4):
+            raise CheckpointError(f"{prefix}.weight_packed has shape {packed.shape}, expected {(n_out, k_in // 4, scales.size, 4)}")
+        from . import check, lib
+        l3 = np.ascontiguousarray(packed).view(np.int8)
+        packed = np.zeros((n_out, k_in // 4, scales.size), np.uint8)
+        check(lib().bt_convert_l3_to_l2(l3.ctypes.data, n_out, k_in, scales.size, packed.ctypes.data))
     if packed.shape != (n_out, k_in // 4, scales.size):
         raise CheckpointError(f"{prefix}.weight_packed has shape {packed.shape}, expected {(n_out, k_in // 4, scales.size)}")
-    if scales.size != 1:
-        raise CheckpointError(f"{prefix}: {scales.size} bases - the model-level entry points take one basis per "
-                              "projection (BitLinear.from_packed runs multi-basis projections on their own)")
-    return np.ascontiguousarray(packed[:, :, 0]), float(scales[0])
+    if scales.size == 1:
+        return np.ascontiguousarray(packed[:, :, 0]), float(scales[0])
+    return np.ascontiguousarray(packed), scales
 
 
 def weights_from_tensors(tensors: dict, cfg: BitLlamaConfig) -> SyntheticWeights:
     """Name resolution of BitLlama::load (model/llama.rs:84-141) and BitLlamaBlock::load
     (model/block.rs:33-64) over a name -> array mapping."""
     V, H = cfg.vocab_size, cfg.hidden_dim
-    embed = _f32(_first(tensors, ["model.embed_tokens.weight", "embed.weight"], "embedding"))
-    head = _f32(_first(tensors, ["lm_head.weight"], "lm_head"))
+    embed_raw = _first(tensors, ["model.embed_tokens.weight", "embed.weight"], "embedding")
+    head_raw = _first(tensors, ["lm_head.weight"], "lm_head")
+    embed, head = _f32(embed_raw), _f32(head_raw)
     norm_f = _f32(_first(tensors, ["model.norm.weight", "norm_f.weight"], "final norm"))
     for name, arr, shape in (("embedding", embed, (V, H)), ("lm_head", head, (V, H)), ("final norm", norm_f, (H,))):
         if arr.shape != shape:
             raise CheckpointError(f"checkpoint: {name} has shape {arr.shape}, expected {shape}")
     w = SyntheticWeights(cfg, embed, head, norm_f)
+    # the converter stores embedding and head as IEEE halves; the device tables then keep exactly those values
+    w.dense_f16 = np.asarray(embed_raw).dtype == np.float16 and np.asarray(head_raw).dtype == np.float16
     names = {W_Q: "self_attn.q_proj", W_K: "self_attn.k_proj", W_V: "self_attn.v_proj", W_O: "self_attn.o_proj",
              W_GATE: "mlp.gate_proj", W_UP: "mlp.up_proj", W_DOWN: "mlp.down_proj",
              W_TTT_DOWN: "ttt.down", W_TTT_UP: "ttt.up"}
@@ -236,8 +248,9 @@ def save_checkpoint(directory: str, w: SyntheticWeights, hf_names: bool = True, 
         for kind, val in layer.items():
             if isinstance(kind, int):
                 packed, scale, n, k = val
-                t[f"{p}.{names[kind]}.weight_packed"] = np.ascontiguousarray(packed, np.uint8).reshape(n, k // 4, 1)
-                t[f"{p}.{names[kind]}.scales"] = np.array([scale], np.float32)
+                scales = np.atleast_1d(np.asarray(scale, np.float32))
+                t[f"{p}.{names[kind]}.weight_packed"] = np.ascontiguousarray(packed, np.uint8).reshape(n, k // 4, scales.size)
+                t[f"{p}.{names[kind]}.scales"] = scales
     t["model.norm.weight" if hf_names else "norm_f.weight"] = w.norm_f.astype(dense_dtype)
     t["lm_head.weight"] = w.lm_head.astype(dense_dtype)
     write_safetensors(os.path.join(directory, "model.safetensors"), t)

@@ -39,7 +39,9 @@ def _bind():
     L.bt_linear_create_fused.argtypes = [C.POINTER(vp), C.POINTER(vp), C.POINTER(i64), vp, i32, i64, i32]
     L.bt_model_create.argtypes = [C.POINTER(vp), C.POINTER(_CModelConfig), i32]
     L.bt_model_set_linear.argtypes = [vp, i32, i32, vp, i64, i64, C.c_float]
+    L.bt_model_set_linear_bases.argtypes = [vp, i32, i32, vp, i64, i64, i32, vp]
     L.bt_model_set_tensor.argtypes = [vp, i32, i32, vp, i64]
+    L.bt_model_set_tensor_typed.argtypes = [vp, i32, i32, vp, i64, i32]
     L.bt_model_finalize.argtypes = [vp]
     L.bt_model_destroy.argtypes = [vp]
     L.bt_model_reset.argtypes = [vp]
@@ -185,13 +187,21 @@ class BitLlama:
         self._h = C.c_void_p()
         check(self._L.bt_model_create(C.byref(self._h), C.byref(cc), device))
 
-    def set_linear(self, layer: int, kind: int, packed: np.ndarray, scale: float, n_out: int, k_in: int):
+    def set_linear(self, layer: int, kind: int, packed: np.ndarray, scale, n_out: int, k_in: int):
+        """packed [n_out, k_in/4] with one scale, or [n_out, k_in/4, n_bases] with n_bases scales."""
         packed = np.ascontiguousarray(packed, np.uint8)
-        check(self._L.bt_model_set_linear(self._h, layer, kind, packed.ctypes.data, n_out, k_in, scale))
+        scales = np.ascontiguousarray(np.atleast_1d(np.asarray(scale, np.float32)))
+        n_bases = packed.shape[2] if packed.ndim == 3 else 1
+        if scales.size != n_bases:
+            raise ValueError(f"{scales.size} scales for {n_bases} bases")
+        check(self._L.bt_model_set_linear_bases(self._h, layer, kind, packed.ctypes.data, n_out, k_in, n_bases,
+                                                scales.ctypes.data))
 
-    def set_tensor(self, kind: int, data: np.ndarray, layer: int = 0):
+    def set_tensor(self, kind: int, data: np.ndarray, layer: int = 0, f16: bool = False):
+        """f16: keep the embedding / lm_head as IEEE halves on the device (a converted checkpoint's dtype)
+        instead of bf16."""
         data = np.ascontiguousarray(data, np.float32)
-        check(self._L.bt_model_set_tensor(self._h, kind, layer, data.ctypes.data, data.size))
+        check(self._L.bt_model_set_tensor_typed(self._h, kind, layer, data.ctypes.data, data.size, 4 if f16 else 1))
 
     def finalize(self):
         check(self._L.bt_model_finalize(self._h))

@@ -28,6 +28,7 @@ class SyntheticWeights:
     lm_head: np.ndarray
     norm_f: np.ndarray
     layers: list = field(default_factory=list)  # dicts: norm1, norm2, kind -> (packed, scale, n, k)
+    dense_f16: bool = False  # embedding and lm_head hold IEEE-half values (a converted checkpoint): keep them so
 
 
 def _bf16_round(a: np.ndarray) -> np.ndarray:
@@ -56,10 +57,19 @@ def linear_shapes(cfg: BitLlamaConfig):
     return shapes
 
 
+def _multi_basis_codes(rng, n, k, n_bases):
+    """Random ternary bases in the converted layout [n, k/4, n_bases] with decreasing scales, the shape a
+    greedy residual decomposition produces (tools/conversion/convert_llama_v2.py:28-72)."""
+    planes = [_ternary_codes(rng, n, k) for _ in range(n_bases)]
+    scales = np.array([0.016 / (2.6 ** b) for b in range(n_bases)], np.float32)
+    return np.ascontiguousarray(np.stack(planes, axis=2)), scales
+
+
 def make_weights(cfg: BitLlamaConfig, seed: int = 2000, from_latent: bool = True,
-                 share_layers: bool = False) -> SyntheticWeights:
+                 share_layers: bool = False, n_bases: int = 1) -> SyntheticWeights:
     """from_latent: draw N(0, 0.02) dense weights and run PackedTensor::pack on them (small
     models); otherwise draw the ternary codes uniformly (p = 1/3) with scale 0.016.
+    n_bases > 1: every projection gets that many random ternary bases (converted-checkpoint layout).
     share_layers: reuse layer 0's host arrays for every layer (the device copies stay
     distinct) - keeps host-side generation of multi-GB models short."""
     rng = np.random.default_rng(seed)
@@ -74,13 +84,15 @@ def make_weights(cfg: BitLlamaConfig, seed: int = 2000, from_latent: bool = True
             continue
         layer = {"norm1": np.ones(H, np.float32), "norm2": np.ones(H, np.float32)}
         for kind, (n, k) in linear_shapes(cfg).items():
-            if from_latent:
+            if n_bases > 1:
+                packed, scale = _multi_basis_codes(rng, n, k, n_bases)
+            elif from_latent:
                 dense = rng.normal(0, 0.02, (n, k)).astype(np.float32)
                 packed, scale = pack_ternary(dense)
                 packed = packed.reshape(n, k // 4)
             else:
                 packed, scale = _ternary_codes(rng, n, k), 0.016
-            layer[kind] = (packed, float(scale), n, k)
+            layer[kind] = (packed, scale if n_bases > 1 else float(scale), n, k)
         w.layers.append(layer)
     return w
 
@@ -92,7 +104,7 @@ def shard_weights(w: SyntheticWeights, rank: int, size: int) -> SyntheticWeights
         return w
     cfg = w.cfg
     hd = cfg.hidden_dim // cfg.n_heads
-    out = SyntheticWeights(cfg, w.embed, w.lm_head, w.norm_f)
+    out = SyntheticWeights(cfg, w.embed, w.lm_head, w.norm_f, dense_f16=w.dense_f16)
     cache = {}
     for layer in w.layers:
         if id(layer) in cache:
@@ -103,6 +115,8 @@ def shard_weights(w: SyntheticWeights, rank: int, size: int) -> SyntheticWeights
             if not isinstance(kind, int):
                 continue
             packed, scale, n, k = val
+            if np.ndim(packed) == 3:
+                raise ValueError("tensor parallelism takes one basis per projection")
             packed = np.ascontiguousarray(packed).reshape(n, k // 4)
             if kind in (W_Q, W_K, W_V, W_GATE, W_UP):      # split output rows
                 rows = n // size
@@ -123,8 +137,8 @@ def build_model(w: SyntheticWeights, max_batch: int = 1, device: int = 0, tp_ran
                 tp_size: int = 1) -> BitLlama:
     w = shard_weights(w, tp_rank, tp_size)
     m = BitLlama(w.cfg, max_batch=max_batch, device=device, tp_rank=tp_rank, tp_size=tp_size)
-    m.set_tensor(T_EMBED, w.embed)
-    m.set_tensor(T_LM_HEAD, w.lm_head)
+    m.set_tensor(T_EMBED, w.embed, f16=w.dense_f16)
+    m.set_tensor(T_LM_HEAD, w.lm_head, f16=w.dense_f16)
     m.set_tensor(T_NORM_F, w.norm_f)
     for li, layer in enumerate(w.layers):
         m.set_tensor(T_NORM1, layer["norm1"], li)

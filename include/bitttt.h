@@ -35,7 +35,7 @@ enum {
     BT_ERR_ARG = -8      /* null pointer, unsupported dtype or option */
 };
 
-typedef enum { BT_F32 = 0, BT_BF16 = 1, BT_I8 = 2, BT_I32 = 3 } bt_dtype;
+typedef enum { BT_F32 = 0, BT_BF16 = 1, BT_I8 = 2, BT_I32 = 3, BT_F16 = 4 } bt_dtype;
 
 /* Message of the calling thread's last failed call ("" if none). */
 const char* bt_last_error(void);
@@ -299,8 +299,24 @@ bt_status bt_model_tp_set_timeout(bt_model* m, int milliseconds);
 bt_status bt_model_tp_destroy(bt_model* m);
 bt_status bt_model_set_linear(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
                               int64_t n_out, int64_t k_in, float scale);
+/* The same for a projection with several bases, as the converter writes them by default (NumBases = 3,
+ * tools/conversion/convert_llama_v2.py:169): packed_host [n_out, k_in/4, n_bases], scales_host [n_bases]
+ * (AdaptiveBitLinear::load, RE/layers/adaptive_linear.rs:40-129; the reference rebuilds a dense f32 matrix from
+ * them, this library streams every basis as 2-bit tiles and adds the per-basis products in basis order).
+ * q, k, v of a layer must agree on n_bases, and so must gate and up.  A model with any multi-basis projection
+ * runs its decode step with the quantiser and product kernels launched separately.  One basis only on
+ * tensor-parallel models. */
+bt_status bt_model_set_linear_bases(bt_model* m, int layer, bt_weight_kind kind, const uint8_t* packed_host,
+                                    int64_t n_out, int64_t k_in, int n_bases, const float* scales_host);
 bt_status bt_model_set_tensor(bt_model* m, bt_tensor_kind kind, int layer, const float* data_host,
                               int64_t n_elem);
+/* The same with the 16-bit storage type of the embedding and the lm_head chosen by the caller: BT_BF16 (what
+ * bt_model_set_tensor uses) or BT_F16.  A converted checkpoint stores these tensors as IEEE halves
+ * (tools/conversion/convert_llama_v2.py:262-283) and the reference widens them to f32 unchanged
+ * (RE/model/llama.rs:414-415): with BT_F16 the device tables hold exactly those values at the same 2 bytes per
+ * element, whereas bf16 would round them to 8 significand bits.  Norm weights are kept in f32 either way. */
+bt_status bt_model_set_tensor_typed(bt_model* m, bt_tensor_kind kind, int layer, const float* data_host,
+                                    int64_t n_elem, bt_dtype storage);
 bt_status bt_model_finalize(bt_model* m);
 bt_status bt_model_destroy(bt_model* m);
 /* reset_kv_cache + fresh zero TTT states (RE/model/llama.rs:179-188,161-170). */

@@ -484,8 +484,10 @@ def model_from_weights(w, quantised: bool = True) -> Model:
         if kind not in layer:
             return None
         packed, scale, n, k = layer[kind]
-        return Linear(np.ascontiguousarray(packed).reshape(n, k // 4), np.array([scale], np.float32), n, k,
-                      quantised)
+        packed = np.ascontiguousarray(packed)
+        if packed.ndim == 3:  # converted layout, several bases
+            return Linear(packed, np.asarray(scale, np.float32).reshape(-1), n, k, quantised)
+        return Linear(packed.reshape(n, k // 4), np.array([scale], np.float32), n, k, quantised)
 
     layers = []
     for layer in w.layers:

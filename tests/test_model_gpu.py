@@ -98,3 +98,19 @@ def test_models_batch_12_use_tensor_core_product(bt, oracle):
     run_staged(bt, oracle, syn.TINY_LLAMA_TEST, 4, 3100, batch=12)
     run_staged(bt, oracle, syn.BitLlamaConfig("ttt", 500, 256, 2, 4, 4, 688, inner_lr=0.01), 4, 3200, batch=12)
     assert bt.lib().bt_device_check(0) == 0
+
+
+@pytest.mark.parametrize("arch,batch", [("llama", 1), ("llama", 6), ("llama", 12), ("ttt", 2), ("ttt", 10)])
+def test_models_with_several_bases_per_projection(bt, oracle, arch, batch):
+    # the converter's default is three bases per projection: q|k|v and gate|up are fused per basis, every
+    # projection adds its per-basis products in basis order before the residual
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    cfg = syn.TINY_LLAMA_TEST if arch == "llama" else syn.BitLlamaConfig("ttt", 500, 256, 2, 4, 4, 688, inner_lr=0.01)
+    w = syn.make_weights(cfg, seed=3400 + batch, n_bases=3)
+    gpu = syn.build_model(w, max_batch=batch)
+    ref = oracle.model_from_weights(w)
+    states = [ref.new_state() for _ in range(batch)]
+    tokens = np.random.default_rng(batch).integers(0, cfg.vocab_size, size=(4, batch))
+    for t in range(4):
+        staged_decode_step(oracle, ref, gpu, cfg, tokens[t], states)
+    assert bt.lib().bt_device_check(0) == 0
