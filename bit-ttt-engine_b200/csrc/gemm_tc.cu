@@ -4,18 +4,22 @@
 // kernels/cuda.rs:21-47) at batch and prefill sizes, where the reference runs a dense f32 GEMM
 // on a host-unpacked weight.
 //
-// Roles inside one CTA (1 per SM, persistent over output tiles of 128 weight rows x NT tokens):
+// Roles inside one CTA (1 per SM, persistent over work units of 128 weight rows x NT tokens x a k range):
 //   warp 0     producer: 1-D bulk copies of the packed weight tiles (8 x 1 KB per 256-input
 //              chunk) and of the chunk's int8 activation block into a shared-memory ring;
-//   warp 1     MMA issuer (one thread): tcgen05.mma.kind::i8, A = weights (u8), B = activations
-//              (s8), both K-major without swizzle, accumulators in TMEM;
-//   warps 2-5  unpack: one AND per 16-byte register isolates field r of every byte as an
-//              unsigned multiple of 4^r and one 16-byte store puts it into the A tile of
-//              residue r, so the four field positions become four independent products
-//              with four TMEM accumulators (shifted back in the epilogue); the same warps
-//              read TMEM (tcgen05.ld) and store the outputs at the end of a tile.
+//   warp 1     MMA issuer (one thread): tcgen05.mma.kind::i8 with the A operand (weights, u8) in
+//              TENSOR MEMORY and the B operand (activations, s8) in shared memory, K-major without
+//              swizzle; accumulators in tensor memory, two sets, so that the MMAs of the next unit
+//              run while the previous one is drained;
+//   warps 2-5  unpack: a thread owns one weight row (= one TMEM lane).  It loads the row's 64 packed
+//              bytes of the chunk, isolates field r of every byte with a shift and an AND
+//              (values 0, 1, 2 = ternary + 1) and writes the four residue planes with tcgen05.st
+//              straight into tensor memory: the unpacked weights never pass through shared memory,
+//              whose bandwidth the B operand and the ring need;
+//   warps 6-9  epilogue: tcgen05.ld of a finished accumulator set, - sum_k q (the +1 offset), scales, store.
 // A 2-bit field at position r of a byte multiplies the activations k = r (mod 4), hence the
-// activations are stored residue-split: B_r[m, k'] = q[m, 4k' + r].
+// activations are stored residue-split: B_r[m, k'] = q[m, 4k' + r]; the four residue products of a
+// chunk accumulate into the same accumulator.
 #include "bt_common.cuh"
 #include "bt_ptx.cuh"
 
@@ -23,13 +27,13 @@ namespace bt {
 
 namespace {
 
-constexpr int kRows = 128;               // weight rows per tile = UMMA M
+constexpr int kRows = 128;               // weight rows per tile = UMMA M = TMEM lanes
 constexpr int kChunkK = 256;             // inputs per k-chunk (one weight tile column)
 constexpr int kRawBytes = 8 * kTileBytes;  // packed weights of a chunk: 8 row tiles x 1 KB
-constexpr int kATileBytes = kRows * 64;  // unpacked A of one residue: 128 rows x 64 k'
-constexpr int kStages = 3;
-constexpr int kUnpBufs = 2;
-constexpr int kTcThreads = 6 * 32;
+constexpr int kStages = 5;
+constexpr int kABufs = 2;                // unpacked-A buffers in tensor memory
+constexpr int kAChunkCols = 64;          // TMEM columns of one unpacked chunk: 4 residues x 64 bytes / 4
+constexpr int kTcThreads = 10 * 32;
 constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
 
 // Instruction descriptor for kind::i8: D = s32, A = u8, B = s8, both K-major, M x N tile.
@@ -66,17 +70,18 @@ template <int NT>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
     constexpr int kBBytes = 4 * NT * 64;                 // activation block of a chunk (4 residues)
     constexpr int kStageBytes = kRawBytes + kBBytes;
-    constexpr uint32_t kTmemCols = 4 * NT;               // four accumulators of NT columns
+    constexpr uint32_t kAccCols = 2 * NT;                // two accumulator sets of NT columns
+    constexpr uint32_t kTmemCols = (kAccCols + kABufs * kAChunkCols) <= 256 ? 256 : 512;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stage_base = smem;                                           // kStages x (raw | B)
-    uint8_t* unp_base = stage_base + (size_t)kStages * kStageBytes;       // kUnpBufs x 4 x A tile
-    uint64_t* full = reinterpret_cast<uint64_t*>(unp_base + (size_t)kUnpBufs * 4 * kATileBytes);
-    uint64_t* empty = full + kStages;
-    uint64_t* unp_full = empty + kStages;
-    uint64_t* unp_empty = unp_full + kUnpBufs;
-    uint64_t* acc_full = unp_empty + kUnpBufs;
-    uint64_t* acc_empty = acc_full + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* full = reinterpret_cast<uint64_t*>(stage_base + (size_t)kStages * kStageBytes);
+    uint64_t* empty = full + kStages;     // a stage is free again: the MMAs that read its B block are done (1 arrival)
+                                          // and the four unpack warps have read its weights (4 arrivals)
+    uint64_t* a_full = empty + kStages;   // unpacked chunk in tensor memory (4 arrivals, one per unpack warp)
+    uint64_t* a_empty = a_full + kABufs;  // the MMAs that read it are done
+    uint64_t* acc_full = a_empty + kABufs;
+    uint64_t* acc_empty = acc_full + 2;   // 4 arrivals, one per epilogue warp
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = (int)a.k_tiles;
@@ -84,13 +89,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
     const int tok_blocks = (a.m + NT - 1) / NT;
     const int k_splits = a.k_splits;
     const int cps = (k_tiles + k_splits - 1) / k_splits;  // chunks per split (the host makes every split non-empty)
-    const int n_tiles = row_sets * tok_blocks * k_splits;  // work units: (row set, token block, k split)
+    const int n_units = row_sets * tok_blocks * k_splits;  // work units: (row set, token block, k split)
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1); }
-        for (int u = 0; u < kUnpBufs; ++u) { ptx::mbar_init(&unp_full[u], 128); ptx::mbar_init(&unp_empty[u], 1); }
-        ptx::mbar_init(acc_full, 1);
-        ptx::mbar_init(acc_empty, 128);
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 5); }
+        for (int u = 0; u < kABufs; ++u) { ptx::mbar_init(&a_full[u], 4); ptx::mbar_init(&a_empty[u], 1); }
+        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], 4); }
         ptx::mbar_fence_init();
     }
     if (warp == 1) {  // one warp allocates (and later frees) the tensor memory
@@ -101,20 +105,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t a_col0 = kAccCols;  // the unpacked-A buffers follow the accumulators
 
     bool ok = true;
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            int slot = 0;
-            uint32_t par = 1;
-            bool first = true;
-            for (int unit = blockIdx.x; unit < n_tiles; unit += gridDim.x) {
+            int g = 0;  // chunks issued so far
+            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
                 const int split = unit % k_splits, tile = unit / k_splits;
                 const int rs = tile % row_sets, tb = tile / row_sets;
                 const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
-                for (int kt = kt0; kt < kt1; ++kt) {
-                    if (!first) ok &= ptx::mbar_wait_bounded(&empty[slot], par);
+                for (int kt = kt0; kt < kt1; ++kt, ++g) {
+                    const int slot = g % kStages, use = g / kStages;
+                    if (use > 0) ok &= ptx::mbar_wait_bounded(&empty[slot], (uint32_t)((use - 1) & 1));
                     uint8_t* st = stage_base + (size_t)slot * kStageBytes;
                     const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
                     ptx::mbar_arrive_expect_tx(&full[slot], (uint32_t)(rts * kTileBytes + kBBytes));
@@ -123,7 +127,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                                       a.tiles + (((int64_t)rs * 8 + r8) * k_tiles + kt) * kTileBytes, kTileBytes,
                                       &full[slot]);
                     ptx::bulk_g2s(st + kRawBytes, a.qtc + ((int64_t)tb * k_tiles + kt) * kBBytes, kBBytes, &full[slot]);
-                    if (++slot == kStages) { slot = 0; first = false; par ^= 1; }
                 }
             }
         }
@@ -131,77 +134,92 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = instr_desc_i8(kRows, NT);
-            int slot = 0, u = 0;
-            uint32_t par = 0, upar = 0, acc_par = 0;
-            bool first_tile = true;
-            for (int unit = blockIdx.x; unit < n_tiles; unit += gridDim.x) {
+            int g = 0, tl = 0;
+            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tl) {
                 const int split = unit % k_splits;
                 const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
-                if (!first_tile) { ok &= ptx::mbar_wait_bounded(acc_empty, acc_par); acc_par ^= 1; }
-                first_tile = false;
+                const int sel = tl & 1, acc_use = tl >> 1;
+                if (acc_use > 0) ok &= ptx::mbar_wait_bounded(&acc_empty[sel], (uint32_t)((acc_use - 1) & 1));
                 ptx::tc_fence_after();
-                for (int kt = kt0; kt < kt1; ++kt) {
-                    ok &= ptx::mbar_wait_bounded(&full[slot], par);        // activation block landed
-                    ok &= ptx::mbar_wait_bounded(&unp_full[u], upar);      // weights unpacked
+                const uint32_t d_tmem = tmem_base + (uint32_t)sel * NT;
+                for (int kt = kt0; kt < kt1; ++kt, ++g) {
+                    const int slot = g % kStages, u = g % kABufs;
+                    ok &= ptx::mbar_wait_bounded(&full[slot], (uint32_t)((g / kStages) & 1));   // activation block landed
+                    ok &= ptx::mbar_wait_bounded(&a_full[u], (uint32_t)((g / kABufs) & 1));     // weights unpacked into tensor memory
                     ptx::tc_fence_after();
                     const uint32_t b_addr = ptx::smem_u32(stage_base + (size_t)slot * kStageBytes + kRawBytes);
-                    const uint32_t a_addr = ptx::smem_u32(unp_base + (size_t)u * 4 * kATileBytes);
+                    const uint32_t a_tmem = tmem_base + a_col0 + (uint32_t)u * kAChunkCols;
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
 #pragma unroll
-                        for (int ks = 0; ks < 2; ++ks) {  // 64 k' per residue = 2 x K32
-                            const uint64_t ad = ptx::smem_desc(a_addr + r * kATileBytes + ks * 256, 128, 512);
+                        for (int ks = 0; ks < 2; ++ks) {  // 64 k' per residue = 2 x K32 = 2 x 8 TMEM columns
                             const uint64_t bd = ptx::smem_desc(b_addr + r * (NT * 64) + ks * 256, 128, 512);
-                            ptx::umma_i8(tmem_base + r * NT, ad, bd, idesc, (kt > kt0 || ks > 0) ? 1u : 0u);
+                            ptx::umma_i8_ts(d_tmem, a_tmem + r * 16 + ks * 8, bd, idesc, (kt > kt0 || r > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
-                    ptx::umma_commit(&unp_empty[u]);  // unpacked buffer reusable once these MMAs are done
-                    ptx::umma_commit(&empty[slot]);   // and the stage (its activation block)
-                    if (++slot == kStages) { slot = 0; par ^= 1; }
-                    if (++u == kUnpBufs) { u = 0; upar ^= 1; }
+                    ptx::umma_commit(&a_empty[u]);   // unpacked buffer reusable once these MMAs are done
+                    ptx::umma_commit(&empty[slot]);  // and the stage's activation block
                 }
-                ptx::umma_commit(acc_full);
+                ptx::umma_commit(&acc_full[sel]);
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- unpack warps (4 warps = 128 threads, one weight row = one TMEM lane each) ----
+        const int sub = warp & 3;                      // the TMEM lanes 32 sub .. 32 sub + 31 belong to this warp
+        const int row = sub * 32 + lane;               // row inside the 128-row tile
+        // this thread's row: row tile r8 = row/16, half = (row%16)/8, g = row%8; its 64 packed bytes of a chunk
+        // are the four 16-byte pieces t = 0..3 at ((half*32 + g*4 + t) * 16) of the row tile
+        const int r8 = row >> 4, half = (row >> 3) & 1, g8 = row & 7;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + a_col0;
+        int g = 0;
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+            const int split = unit % k_splits, tile = unit / k_splits;
+            const int rs = tile % row_sets;
+            const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
+            const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
+            for (int kt = kt0; kt < kt1; ++kt, ++g) {
+                const int slot = g % kStages, u = g % kABufs, a_use = g / kABufs;
+                ok &= ptx::mbar_wait_bounded(&full[slot], (uint32_t)((g / kStages) & 1));
+                const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g8 * 64;
+                uint4 w[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    w[t] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // weight 0 (rows beyond the matrix)
+                    if (r8 < rts) w[t] = *reinterpret_cast<const uint4*>(raw + t * 16);
+                }
+                if (a_use > 0) ok &= ptx::mbar_wait_bounded(&a_empty[u], (uint32_t)((a_use - 1) & 1));
+                ptx::tc_fence_after();
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    // residue r of the row: piece t holds the inputs 64 t .. 64 t + 63, i.e. k' = 16 t .. 16 t + 15
+                    uint32_t v[16];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        v[4 * t + 0] = (w[t].x >> (2 * r)) & 0x03030303u;
+                        v[4 * t + 1] = (w[t].y >> (2 * r)) & 0x03030303u;
+                        v[4 * t + 2] = (w[t].z >> (2 * r)) & 0x03030303u;
+                        v[4 * t + 3] = (w[t].w >> (2 * r)) & 0x03030303u;
+                    }
+                    ptx::tmem_st16(lane_addr + (uint32_t)u * kAChunkCols + r * 16, v);
+                }
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&a_full[u]);
+                    ptx::mbar_arrive(&empty[slot]);  // this warp has read its weights of the stage
+                }
             }
         }
     } else {
-        // ---------------- unpack + epilogue warps (4 warps = 128 threads, one weight row each) ----
-        const int tid = threadIdx.x - 64;              // 0..127 = row inside the tile
-        const int sub = warp & 3;                      // TMEM sub-partition this warp may read
-        int slot = 0, u = 0;
-        uint32_t par = 0, upar = 1, acc_par = 0;
-        bool first_unp = true;
-        for (int unit = blockIdx.x; unit < n_tiles; unit += gridDim.x) {
+        // ---------------- epilogue warps (4 warps, TMEM lanes by warp % 4) ----------------
+        const int sub = warp & 3;
+        int tl = 0;
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tl) {
             const int split = unit % k_splits, tile = unit / k_splits;
             const int rs = tile % row_sets, tb = tile / row_sets;
-            const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
-            const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
-            for (int kt = kt0; kt < kt1; ++kt) {
-                ok &= ptx::mbar_wait_bounded(&full[slot], par);
-                if (!first_unp) ok &= ptx::mbar_wait_bounded(&unp_empty[u], upar);
-                // this thread's row: row tile r8 = tid/16, half = (tid%16)/8, g = tid%8; its 64 packed
-                // bytes are the four 16-byte chunks t = 0..3 at ((half*32 + g*4 + t) * 16)
-                const int r8 = tid >> 4, half = (tid >> 3) & 1, g = tid & 7;
-                const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g * 64;
-                uint8_t* dst = unp_base + (size_t)u * 4 * kATileBytes + (tid >> 3) * 512 + (tid & 7) * 16;
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    uint4 w = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // weight 0
-                    if (r8 < rts) w = *reinterpret_cast<const uint4*>(raw + t * 16);
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const uint32_t mask = 0x03030303u << (2 * r);
-                        *reinterpret_cast<uint4*>(dst + r * kATileBytes + t * 128) =
-                            make_uint4(w.x & mask, w.y & mask, w.z & mask, w.w & mask);
-                    }
-                }
-                ptx::fence_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
-                ptx::mbar_arrive(&unp_full[u]);
-                if (++slot == kStages) { slot = 0; par ^= 1; }
-                if (++u == kUnpBufs) { u = 0; first_unp = false; upar ^= 1; }
-            }
-            // ---- epilogue of this tile ----
-            ok &= ptx::mbar_wait_bounded(acc_full, acc_par);
-            acc_par ^= 1;
+            const int sel = tl & 1;
+            ok &= ptx::mbar_wait_bounded(&acc_full[sel], (uint32_t)((tl >> 1) & 1));
             ptx::tc_fence_after();
             const int64_t row = (int64_t)rs * kRows + sub * 32 + lane;
             const int64_t rt = row >> 4;
@@ -209,23 +227,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
             if (a.epilogue != EPI_I32 && rt < a.row_tiles) sw = a.sw_tiles[2 * rt + ((row >> 3) & 1)];
 #pragma unroll 1
             for (int c0 = 0; c0 < NT; c0 += 32) {
-                uint32_t d0[32], d1[32], d2[32], d3[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + c0;
-                ptx::tmem_ld32(taddr + 0 * NT, d0);
-                ptx::tmem_ld32(taddr + 1 * NT, d1);
-                ptx::tmem_ld32(taddr + 2 * NT, d2);
-                ptx::tmem_ld32(taddr + 3 * NT, d3);
+                uint32_t d[32];
+                ptx::tmem_ld32(tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)sel * NT + c0, d);
                 ptx::tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int token = tb * NT + c0 + j;
                     if (token < a.m && row < a.n_out) {
-                        const int folded = (int)d0[j] + ((int)d1[j] >> 2) + ((int)d2[j] >> 4) + ((int)d3[j] >> 6);
                         if (k_splits > 1) {
-                            a.part[((int64_t)split * a.m + token) * a.n_out + row] = folded;
+                            a.part[((int64_t)split * a.m + token) * a.n_out + row] = (int)d[j];
                             continue;
                         }
-                        const int accv = folded - a.qsum[token];
+                        const int accv = (int)d[j] - a.qsum[token];
                         const int64_t o = (int64_t)token * a.out_stride + row;
                         if (a.epilogue == EPI_I32) {
                             reinterpret_cast<int32_t*>(a.out)[o] = accv;
@@ -240,7 +253,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(acc_empty);
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&acc_empty[sel]);
         }
     }
     if (!ok) atomicExch(a.err, kErrTcTimeout);
@@ -326,7 +340,7 @@ __global__ void __launch_bounds__(256) tc_finish_kernel(TcArgs a) {
 template <int NT>
 cudaError_t launch_nt(TcArgs a, int sm_count, int32_t* part, size_t part_bytes, cudaStream_t stream) {
     constexpr int kBBytes = 4 * NT * 64;
-    const size_t smem = (size_t)kStages * (kRawBytes + kBBytes) + (size_t)kUnpBufs * 4 * kATileBytes + 256;
+    const size_t smem = (size_t)kStages * (kRawBytes + kBBytes) + 256;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
