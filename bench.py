@@ -107,12 +107,12 @@ class ClockSampler:
 # workload
 # ---------------------------------------------------------------------------------------
 
-def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0):
+def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0, num_layers=None):
     """Random-init Llama-3-8B-shaped ternary model.  Layer 0's host arrays are reused for
     every layer (each layer still owns its own device copy, so HBM traffic is real); the
     embedding and lm_head are one N(0, 0.02) block tiled over the vocabulary."""
     cfg = syn.LLAMA3_8B
-    cfg = syn.BitLlamaConfig(cfg.arch, cfg.vocab_size, cfg.hidden_dim, cfg.num_layers, cfg.n_heads, cfg.n_kv_heads,
+    cfg = syn.BitLlamaConfig(cfg.arch, cfg.vocab_size, cfg.hidden_dim, num_layers or cfg.num_layers, cfg.n_heads, cfg.n_kv_heads,
                              cfg.intermediate_dim, rope_theta=cfg.rope_theta, max_position_embeddings=max_pos)
     rng = np.random.default_rng(seed)
     block = syn._bf16_round(rng.normal(0, 0.02, (8016, cfg.hidden_dim)).astype(np.float32))
@@ -482,6 +482,10 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="BitLinear shape sweep (K,N in {4096x4096, 4096x14336, 14336x4096, 4096x128256}, "
                          "M in {1, 8, 64, 512, 4096}, bf16 activations) plus the TTT update: one JSON line per point")
+    ap.add_argument("--profile-case", type=int, default=0, metavar="BATCH",
+                    help="small case for a profiler, not a benchmark: --layers blocks of the 8B shape, BATCH sequences, "
+                         "the context filled by the batched prefill, then 3 decode steps; prints a line marked profile_case")
+    ap.add_argument("--layers", type=int, default=2, help="blocks of the --profile-case model")
     ap.add_argument("--tp-nccl", action="store_true",
                     help="with --gpus N > 1: keep the tensor-parallel exchanges on NCCL instead of the "
                          "library's peer-memory kernels")
@@ -506,6 +510,20 @@ def main():
     syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
     if args.sweep:
         run_sweep(bt, local_rank)
+        return
+
+    if args.profile_case:
+        B = args.profile_case
+        cfg, _, model = build_8b(bt, syn, B, args.context + 64, device=local_rank, num_layers=args.layers)
+        rng = np.random.default_rng(11)
+        model.prefill(rng.integers(0, cfg.vocab_size, size=(B, args.context)).astype(np.int32), want_logits=False)
+        tok = torch.from_numpy(rng.integers(0, cfg.vocab_size, size=B).astype(np.int32)).to(f"cuda:{local_rank}")
+        for _ in range(3):
+            model.step_dev(tok)
+            tok = model.next_dev()[:B].clone()
+        torch.cuda.synchronize()
+        bt.check(bt.lib().bt_device_check(local_rank))
+        print(json.dumps({"profile_case": True, "batch": B, "layers": args.layers, "context": args.context, "decode_steps": 3}))
         return
 
     K, W = args.steps, max(args.warmup, 3)

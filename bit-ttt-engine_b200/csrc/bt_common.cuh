@@ -173,15 +173,13 @@ __host__ __device__ inline int64_t gemm_tc_act_offset(int c, int tin, int nt) {
     const int kt = c >> 8, r = c & 3, kp = (c & 255) >> 2;
     return (int64_t)kt * (4 * nt * 64) + (int64_t)r * (nt * 64) + (tin >> 3) * 512 + (kp >> 4) * 128 + (tin & 7) * 16 + (kp & 15);
 }
-// part / part_bytes: optional int32 scratch; when a product has fewer output tiles than the GPU
-// has SMs, its k range is cut across CTAs and the pieces are added from there
-// (gemm_tc_part_bytes(sm_count) is always enough).
-size_t gemm_tc_part_bytes(int sm_count);
-// kernels one launch_gemm_tc call runs for the products themselves (with scratch given)
+// When a product has fewer output tiles than the GPU has SMs, its k range is cut across the CTAs
+// of a thread-block cluster, whose int32 partial sums are added through distributed shared memory.
+// kernels one launch_gemm_tc call runs for the products themselves
 int gemm_tc_kernels(const LinearDev& lin, int64_t m, int sm_count);
 cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
                            int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
-                           cudaStream_t stream, int32_t* part = nullptr, size_t part_bytes = 0,
+                           cudaStream_t stream,
                            bool prequantised = false,     // qtc / sx / qsum are already filled (x unused)
                            bt_dtype x_dtype = BT_F32);    // element type of x: BT_F32 or BT_BF16
 

@@ -321,13 +321,9 @@ extern "C" bt_status bt_linear_forward(bt_linear* lin, bt_workspace* ws, const v
         if (off + (size_t)m * 8 + 512 <= ws->bytes) {
             float* sx = reinterpret_cast<float*>(ws->base + off);
             int32_t* qs = reinterpret_cast<int32_t*>(ws->base + off + align_up((size_t)m * 4, 256));
-            // what is left of the workspace serves as scratch for k-split products (optional)
-            const size_t part_off = align_up(off + align_up((size_t)m * 4, 256) + (size_t)m * 4, 256);
-            int32_t* part = part_off < ws->bytes ? reinterpret_cast<int32_t*>(ws->base + part_off) : nullptr;
             BT_CUDA_TRY(launch_gemm_tc(lin->dev(), x_dev, lin->w.k_in, m, qtc, sx, qs, y_dev,
                                        lin->w.n_out, y_dtype == BT_BF16 ? EPI_BF16 : EPI_F32,
-                                       device_error_word(lin->device), device_sm_count(lin->device), s, part,
-                                       part ? ws->bytes - part_off : 0, false, x_dtype));
+                                       device_error_word(lin->device), device_sm_count(lin->device), s, false, x_dtype));
             return BT_OK;
         }
     }

@@ -11,15 +11,22 @@
 //              TENSOR MEMORY and the B operand (activations, s8) in shared memory, K-major without
 //              swizzle; accumulators in tensor memory, two sets, so that the MMAs of the next unit
 //              run while the previous one is drained;
-//   warps 2-5  unpack: a thread owns one weight row (= one TMEM lane).  It loads the row's 64 packed
-//              bytes of the chunk, isolates field r of every byte with a shift and an AND
-//              (values 0, 1, 2 = ternary + 1) and writes the four residue planes with tcgen05.st
+//   warps 2-9  unpack: two threads own one weight row (= one TMEM lane), half of its bytes each.  A thread
+//              loads its 32 packed bytes of the chunk, isolates field r of every byte with a shift and
+//              an AND (values 0, 1, 2 = ternary + 1) and writes the four residue planes with tcgen05.st
 //              straight into tensor memory: the unpacked weights never pass through shared memory,
 //              whose bandwidth the B operand and the ring need;
-//   warps 6-9  epilogue: tcgen05.ld of a finished accumulator set, - sum_k q (the +1 offset), scales, store.
+//   warps 10-13 epilogue: tcgen05.ld of a finished accumulator set, - sum_k q (the +1 offset), scales, store.
+// With few output tiles the k range of a tile is cut over the CTAs of a thread-block cluster; their int32
+// partial sums reach the cluster's first CTA through distributed shared memory, and that CTA alone stores.
+// Every launch carries the programmatic-dependent-launch attribute: the producer requests the first weight
+// tiles (which no kernel writes) before it waits for the kernel in front.
 // A 2-bit field at position r of a byte multiplies the activations k = r (mod 4), hence the
 // activations are stored residue-split: B_r[m, k'] = q[m, 4k' + r]; the four residue products of a
 // chunk accumulate into the same accumulator.
+#include <cstdint>
+#include <mutex>
+
 #include "bt_common.cuh"
 #include "bt_ptx.cuh"
 
@@ -33,7 +40,8 @@ constexpr int kRawBytes = 8 * kTileBytes;  // packed weights of a chunk: 8 row t
 constexpr int kStages = 5;
 constexpr int kABufs = 2;                // unpacked-A buffers in tensor memory
 constexpr int kAChunkCols = 64;          // TMEM columns of one unpacked chunk: 4 residues x 64 bytes / 4
-constexpr int kTcThreads = 10 * 32;
+constexpr int tc_threads(int unpack_warps) { return (2 + unpack_warps + 4) * 32; }
+constexpr int kMaxSplit = 8;             // CTAs of one cluster that share a tile along k
 constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
 
 // Instruction descriptor for kind::i8: D = s32, A = u8, B = s8, both K-major, M x N tile.
@@ -59,42 +67,50 @@ struct TcArgs {
     int64_t out_stride;
     int epilogue;              // EPI_I32 / EPI_F32 / EPI_F32_ACCUM / EPI_BF16
     unsigned int* err;
-    // With few output tiles (small N and M) the k range of a tile is cut into k_splits pieces
-    // that different CTAs work on; each piece leaves its raw int32 sums in part[split][token][row]
-    // and tc_finish_kernel adds them (integers: the result does not depend on the cut).
-    int k_splits;
-    int32_t* part;
 };
 
-template <int NT>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
+// UW unpack warps: 4 (a thread unpacks a whole row of the chunk) or 8 (two threads share a row)
+// S: CTAs of a cluster that share a tile along k (1: no cluster work at all)
+template <int NT, int UW, int S>
+__global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
+    static_assert(S == 1 || (NT == 64 && (S == 2 || S == 4 || S == 8)), "k split: 64 tokens, 2 / 4 / 8 CTAs");
+    constexpr int kUnpackWarps = UW, kEpiWarp0 = 2 + UW;
+    constexpr int PT = 16 / UW;                          // 16-byte pieces of a row's 64 packed bytes per unpack thread
     constexpr int kBBytes = 4 * NT * 64;                 // activation block of a chunk (4 residues)
     constexpr int kStageBytes = kRawBytes + kBBytes;
+    constexpr int kPartBytes = S > 1 ? kRows * NT * 4 : 0;  // this CTA's partial sums of a tile, read by the whole cluster
     constexpr uint32_t kAccCols = 2 * NT;                // two accumulator sets of NT columns
     constexpr uint32_t kTmemCols = (kAccCols + kABufs * kAChunkCols) <= 256 ? 256 : 512;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stage_base = smem;                                           // kStages x (raw | B)
-    uint64_t* full = reinterpret_cast<uint64_t*>(stage_base + (size_t)kStages * kStageBytes);
+    int32_t* pbuf = reinterpret_cast<int32_t*>(stage_base + (size_t)kStages * kStageBytes);  // [NT / 4][128 rows][4]
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(pbuf) + kPartBytes);
     uint64_t* empty = full + kStages;     // a stage is free again: the MMAs that read its B block are done (1 arrival)
-                                          // and the four unpack warps have read its weights (4 arrivals)
-    uint64_t* a_full = empty + kStages;   // unpacked chunk in tensor memory (4 arrivals, one per unpack warp)
+                                          // and the unpack warps have read its weights (kUnpackWarps arrivals)
+    uint64_t* a_full = empty + kStages;   // unpacked chunk in tensor memory (one arrival per unpack warp)
     uint64_t* a_empty = a_full + kABufs;  // the MMAs that read it are done
     uint64_t* acc_full = a_empty + kABufs;
     uint64_t* acc_empty = acc_full + 2;   // 4 arrivals, one per epilogue warp
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* red_full = acc_empty + 2;   // every CTA of the cluster has parked its partial sums of the tile (4 S arrivals)
+    uint64_t* red_free = red_full + 1;    // every CTA of the cluster has read this CTA's partial sums (4 S arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_free + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = (int)a.k_tiles;
     const int row_sets = (int)((a.row_tiles + 7) / 8);
     const int tok_blocks = (a.m + NT - 1) / NT;
-    const int k_splits = a.k_splits;
-    const int cps = (k_tiles + k_splits - 1) / k_splits;  // chunks per split (the host makes every split non-empty)
-    const int n_units = row_sets * tok_blocks * k_splits;  // work units: (row set, token block, k split)
+    const int rank = S > 1 ? (int)ptx::cluster_ctarank() : 0;
+    const int cid = blockIdx.x / S, n_clusters = gridDim.x / S;
+    const int cps = (k_tiles + S - 1) / S;                 // chunks per split (the host makes every split non-empty)
+    const int kt0 = rank * cps, kt1 = min(k_tiles, kt0 + cps);
+    const int n_tiles = row_sets * tok_blocks;             // this CTA works on the tiles cid, cid + n_clusters, ...
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 5); }
-        for (int u = 0; u < kABufs; ++u) { ptx::mbar_init(&a_full[u], 4); ptx::mbar_init(&a_empty[u], 1); }
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1 + kUnpackWarps); }
+        for (int u = 0; u < kABufs; ++u) { ptx::mbar_init(&a_full[u], kUnpackWarps); ptx::mbar_init(&a_empty[u], 1); }
         for (int s = 0; s < 2; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], 4); }
+        ptx::mbar_init(red_full, 4 * S);
+        ptx::mbar_init(red_free, 4 * S);
         ptx::mbar_fence_init();
     }
     if (warp == 1) {  // one warp allocates (and later frees) the tensor memory
@@ -104,6 +120,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
+    if (S > 1) {  // the peers' barriers exist before anybody arrives on them
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t a_col0 = kAccCols;  // the unpacked-A buffers follow the accumulators
 
@@ -111,33 +130,41 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            int g = 0;  // chunks issued so far
-            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
-                const int split = unit % k_splits, tile = unit / k_splits;
+            // The weights do not depend on earlier kernels: the first stages' weight tiles are requested before the
+            // dependency wait, their activation blocks (written by the quantiser just before) after it.
+            auto issue = [&](int tile, int kt, int slot, bool raw_part, bool b_part) {
                 const int rs = tile % row_sets, tb = tile / row_sets;
-                const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
-                for (int kt = kt0; kt < kt1; ++kt, ++g) {
-                    const int slot = g % kStages, use = g / kStages;
-                    if (use > 0) ok &= ptx::mbar_wait_bounded(&empty[slot], (uint32_t)((use - 1) & 1));
-                    uint8_t* st = stage_base + (size_t)slot * kStageBytes;
-                    const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
+                uint8_t* st = stage_base + (size_t)slot * kStageBytes;
+                const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
+                if (raw_part) {
                     ptx::mbar_arrive_expect_tx(&full[slot], (uint32_t)(rts * kTileBytes + kBBytes));
                     for (int r8 = 0; r8 < rts; ++r8)
-                        ptx::bulk_g2s(st + r8 * kTileBytes,
-                                      a.tiles + (((int64_t)rs * 8 + r8) * k_tiles + kt) * kTileBytes, kTileBytes,
+                        ptx::bulk_g2s(st + r8 * kTileBytes, a.tiles + (((int64_t)rs * 8 + r8) * k_tiles + kt) * kTileBytes, kTileBytes,
                                       &full[slot]);
-                    ptx::bulk_g2s(st + kRawBytes, a.qtc + ((int64_t)tb * k_tiles + kt) * kBBytes, kBBytes, &full[slot]);
+                }
+                if (b_part) ptx::bulk_g2s(st + kRawBytes, a.qtc + ((int64_t)tb * k_tiles + kt) * kBBytes, kBBytes, &full[slot]);
+            };
+            int g = 0;
+            for (int tile = cid; tile < n_tiles && g < kStages; tile += n_clusters)
+                for (int kt = kt0; kt < kt1 && g < kStages; ++kt, ++g) issue(tile, kt, g, true, false);
+            ptx::pdl_wait();
+            g = 0;
+            for (int tile = cid; tile < n_tiles; tile += n_clusters) {
+                for (int kt = kt0; kt < kt1; ++kt, ++g) {
+                    const int slot = g % kStages, use = g / kStages;
+                    if (use == 0) { issue(tile, kt, slot, false, true); continue; }
+                    ok &= ptx::mbar_wait_bounded(&empty[slot], (uint32_t)((use - 1) & 1));
+                    issue(tile, kt, slot, true, true);
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
+            ptx::pdl_wait();  // nothing to do before the first activation block exists; keeps the bounded waits short
             const uint32_t idesc = instr_desc_i8(kRows, NT);
             int g = 0, tl = 0;
-            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tl) {
-                const int split = unit % k_splits;
-                const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
+            for (int tile = cid; tile < n_tiles; tile += n_clusters, ++tl) {
                 const int sel = tl & 1, acc_use = tl >> 1;
                 if (acc_use > 0) ok &= ptx::mbar_wait_bounded(&acc_empty[sel], (uint32_t)((acc_use - 1) & 1));
                 ptx::tc_fence_after();
@@ -162,28 +189,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                 }
                 ptx::umma_commit(&acc_full[sel]);
             }
+            // every MMA of this CTA is issued: the kernel behind may start (it waits for this one's results itself)
+            ptx::pdl_launch_dependents();
         }
-    } else if (warp < 6) {
-        // ---------------- unpack warps (4 warps = 128 threads, one weight row = one TMEM lane each) ----
+    } else if (warp < kEpiWarp0) {
+        // ---------------- unpack warps: a thread owns half of one weight row (= one TMEM lane) ----
         const int sub = warp & 3;                      // the TMEM lanes 32 sub .. 32 sub + 31 belong to this warp
+        const int hsel = (warp - 2) >> 2;              // which part of the row's 64 bytes: pieces t = PT hsel .. PT hsel + PT - 1
         const int row = sub * 32 + lane;               // row inside the 128-row tile
-        // this thread's row: row tile r8 = row/16, half = (row%16)/8, g = row%8; its 64 packed bytes of a chunk
-        // are the four 16-byte pieces t = 0..3 at ((half*32 + g*4 + t) * 16) of the row tile
+        // the row: row tile r8 = row/16, half = (row%16)/8, g = row%8; its 64 packed bytes of a chunk are the four
+        // 16-byte pieces t = 0..3 at ((half*32 + g*4 + t) * 16) of the row tile
         const int r8 = row >> 4, half = (row >> 3) & 1, g8 = row & 7;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + a_col0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + a_col0 + 4 * PT * hsel;
+        ptx::pdl_wait();
         int g = 0;
-        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
-            const int split = unit % k_splits, tile = unit / k_splits;
+        for (int tile = cid; tile < n_tiles; tile += n_clusters) {
             const int rs = tile % row_sets;
             const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
-            const int kt0 = split * cps, kt1 = min(k_tiles, kt0 + cps);
             for (int kt = kt0; kt < kt1; ++kt, ++g) {
                 const int slot = g % kStages, u = g % kABufs, a_use = g / kABufs;
                 ok &= ptx::mbar_wait_bounded(&full[slot], (uint32_t)((g / kStages) & 1));
-                const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g8 * 64;
-                uint4 w[4];
+                const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g8 * 64 + hsel * (16 * PT);
+                uint4 w[PT];
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
+                for (int t = 0; t < PT; ++t) {
                     w[t] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // weight 0 (rows beyond the matrix)
                     if (r8 < rts) w[t] = *reinterpret_cast<const uint4*>(raw + t * 16);
                 }
@@ -191,16 +220,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
                 ptx::tc_fence_after();
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
-                    // residue r of the row: piece t holds the inputs 64 t .. 64 t + 63, i.e. k' = 16 t .. 16 t + 15
-                    uint32_t v[16];
+                    // residue r: piece t holds the inputs 64 t .. 64 t + 63, i.e. k' = 16 t .. 16 t + 15 = columns 4 t .. 4 t + 3
+                    uint32_t v[4 * PT];
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
+                    for (int t = 0; t < PT; ++t) {
                         v[4 * t + 0] = (w[t].x >> (2 * r)) & 0x03030303u;
                         v[4 * t + 1] = (w[t].y >> (2 * r)) & 0x03030303u;
                         v[4 * t + 2] = (w[t].z >> (2 * r)) & 0x03030303u;
                         v[4 * t + 3] = (w[t].w >> (2 * r)) & 0x03030303u;
                     }
-                    ptx::tmem_st16(lane_addr + (uint32_t)u * kAChunkCols + r * 16, v);
+                    if constexpr (PT == 4) ptx::tmem_st16(lane_addr + (uint32_t)u * kAChunkCols + r * 16, v);
+                    else ptx::tmem_st8(lane_addr + (uint32_t)u * kAChunkCols + r * 16, v);
                 }
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
@@ -214,53 +244,107 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(TcArgs a) {
     } else {
         // ---------------- epilogue warps (4 warps, TMEM lanes by warp % 4) ----------------
         const int sub = warp & 3;
+        const int lrow = sub * 32 + lane;  // row inside the tile
+        ptx::pdl_wait();  // the output (and what EPI_F32_ACCUM adds to) belongs to earlier kernels until here
+        auto store = [&](int token, int64_t row, float sw, uint32_t acc) {
+            if (token < a.m && row < a.n_out) {
+                const int accv = (int)acc - a.qsum[token];
+                const int64_t o = (int64_t)token * a.out_stride + row;
+                if (a.epilogue == EPI_I32) {
+                    reinterpret_cast<int32_t*>(a.out)[o] = accv;
+                } else {
+                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), a.sx[token]);
+                    if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
+                    else if (a.epilogue == EPI_F32_ACCUM)
+                        reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
+                    else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
+                }
+            }
+        };
         int tl = 0;
-        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tl) {
-            const int split = unit % k_splits, tile = unit / k_splits;
+        for (int tile = cid; tile < n_tiles; tile += n_clusters, ++tl) {
             const int rs = tile % row_sets, tb = tile / row_sets;
             const int sel = tl & 1;
             ok &= ptx::mbar_wait_bounded(&acc_full[sel], (uint32_t)((tl >> 1) & 1));
             ptx::tc_fence_after();
-            const int64_t row = (int64_t)rs * kRows + sub * 32 + lane;
+            const int64_t row = (int64_t)rs * kRows + lrow;
             const int64_t rt = row >> 4;
             float sw = 0.f;
             if (a.epilogue != EPI_I32 && rt < a.row_tiles) sw = a.sw_tiles[2 * rt + ((row >> 3) & 1)];
+            const uint32_t acc_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)sel * NT;
+            if constexpr (S == 1) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 32) {
-                uint32_t d[32];
-                ptx::tmem_ld32(tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)sel * NT + c0, d);
-                ptx::tmem_ld_wait();
+                for (int c0 = 0; c0 < NT; c0 += 32) {
+                    uint32_t d[32];
+                    ptx::tmem_ld32(acc_addr + c0, d);
+                    ptx::tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int token = tb * NT + c0 + j;
-                    if (token < a.m && row < a.n_out) {
-                        if (k_splits > 1) {
-                            a.part[((int64_t)split * a.m + token) * a.n_out + row] = (int)d[j];
-                            continue;
-                        }
-                        const int accv = (int)d[j] - a.qsum[token];
-                        const int64_t o = (int64_t)token * a.out_stride + row;
-                        if (a.epilogue == EPI_I32) {
-                            reinterpret_cast<int32_t*>(a.out)[o] = accv;
-                        } else {
-                            const float y = __fmul_rn(__fmul_rn((float)accv, sw), a.sx[token]);
-                            if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
-                            else if (a.epilogue == EPI_F32_ACCUM)
-                                reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
-                            else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
-                        }
+                    for (int j = 0; j < 32; ++j) store(tb * NT + c0 + j, row, sw, d[j]);
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&acc_empty[sel]);
+            } else {
+                // Reduce-scatter over the cluster: every CTA parks its partial sums of the whole tile in its own
+                // shared memory ([token / 4][row][token % 4], 16 bytes per thread and step), then adds up and stores
+                // the NT / S tokens that are its share, reading all S copies through distributed shared memory.
+                if (tl > 0) ok &= ptx::mbar_wait_cluster_bounded(red_free, (uint32_t)((tl - 1) & 1));  // everybody has read the previous tile
+#pragma unroll 1
+                for (int c0 = 0; c0 < NT; c0 += 32) {
+                    uint32_t d[32];
+                    ptx::tmem_ld32(acc_addr + c0, d);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(pbuf + ((size_t)(c0 / 4 + q) * kRows + lrow) * 4) =
+                            make_uint4(d[4 * q], d[4 * q + 1], d[4 * q + 2], d[4 * q + 3]);
+                }
+                ptx::tc_fence_before();
+                ptx::fence_cluster();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&acc_empty[sel]);  // the accumulator set is free for the tile after next
+#pragma unroll
+                    for (int pr = 0; pr < S; ++pr) ptx::mbar_arrive_remote(ptx::map_to_rank(red_full, (uint32_t)pr));
+                }
+                ok &= ptx::mbar_wait_cluster_bounded(red_full, (uint32_t)(tl & 1));  // all S copies are complete
+                ptx::fence_cluster();
+                constexpr int kGroups = NT / 4 / S;  // groups of 4 tokens that this CTA finishes
+                uint4 part[kGroups][S];
+#pragma unroll
+                for (int q = 0; q < kGroups; ++q)
+#pragma unroll
+                    for (int pr = 0; pr < S; ++pr)
+                        part[q][pr] = ptx::ld_dsmem_v4(
+                            ptx::map_to_rank(pbuf + ((size_t)(rank * kGroups + q) * kRows + lrow) * 4, (uint32_t)pr));
+#pragma unroll
+                for (int q = 0; q < kGroups; ++q) {
+                    uint4 s = part[q][0];
+#pragma unroll
+                    for (int pr = 1; pr < S; ++pr) {
+                        s.x += part[q][pr].x; s.y += part[q][pr].y; s.z += part[q][pr].z; s.w += part[q][pr].w;
                     }
+                    const int token = tb * NT + (rank * kGroups + q) * 4;
+                    store(token, row, sw, s.x);
+                    store(token + 1, row, sw, s.y);
+                    store(token + 2, row, sw, s.z);
+                    store(token + 3, row, sw, s.w);
+                }
+                __syncwarp();
+                if (lane == 0) {
+#pragma unroll
+                    for (int pr = 0; pr < S; ++pr) ptx::mbar_arrive_remote(ptx::map_to_rank(red_free, (uint32_t)pr));
                 }
             }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&acc_empty[sel]);
         }
     }
     if (!ok) atomicExch(a.err, kErrTcTimeout);
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if (S > 1) {  // nobody leaves while a peer may still read its shared memory or arrive on its barriers
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
 }
 
 // Per-token absmax int8 quantiser writing the residue-split, core-matrix-ordered layout that
@@ -274,6 +358,8 @@ __global__ void __launch_bounds__(256) act_quant_tc_kernel(const T* __restrict__
                                                            float* __restrict__ s_out, int32_t* __restrict__ qsum_out) {
     __shared__ float red_f[32];
     __shared__ int red_i[32];
+    ptx::pdl_wait();               // x belongs to earlier kernels until here
+    ptx::pdl_launch_dependents();  // the product behind this kernel may fetch its weights meanwhile
     const int token = blockIdx.x;  // grid covers the padded token count
     const int tb = token / NT, tin = token % NT;
     int8_t* blk = qtc + (int64_t)tb * k_tiles * (4 * NT * 64);
@@ -308,72 +394,104 @@ __global__ void __launch_bounds__(256) act_quant_tc_kernel(const T* __restrict__
     }
 }
 
-// Fewer tiles than half the SMs: cut k so that one wave of CTAs covers the product.
-int tc_k_splits(int n_tiles, int64_t k_tiles, int sm_count) {
-    if (n_tiles * 2 > sm_count || k_tiles < 4) return 1;
-    int want = sm_count / n_tiles;
-    if (want > k_tiles / 2) want = (int)(k_tiles / 2);
-    const int cps = (int)((k_tiles + want - 1) / want);
-    return (int)((k_tiles + cps - 1) / cps);
-}
+constexpr int kUnpackWarps = 4;
 
-// Adds the k-split pieces of a product and applies the epilogue: one thread per (token, row).
-__global__ void __launch_bounds__(256) tc_finish_kernel(TcArgs a) {
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (int64_t)a.m * a.n_out) return;
-    const int token = (int)(idx / a.n_out);
-    const int64_t row = idx % a.n_out;
-    int accv = -a.qsum[token];
-    for (int s2 = 0; s2 < a.k_splits; ++s2) accv += a.part[((int64_t)s2 * a.m + token) * a.n_out + row];
-    const int64_t o = (int64_t)token * a.out_stride + row;
-    if (a.epilogue == EPI_I32) {
-        reinterpret_cast<int32_t*>(a.out)[o] = accv;
-        return;
-    }
-    const float sw = a.sw_tiles[2 * (row >> 4) + ((row >> 3) & 1)];
-    const float y = __fmul_rn(__fmul_rn((float)accv, sw), a.sx[token]);
-    if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
-    else if (a.epilogue == EPI_F32_ACCUM) reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
-    else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
-}
+// One kernel variant (token tile NT, S CTAs per cluster): its shared memory and how many clusters fit on the GPU
+// at once (a cluster lives inside one GPC, so this is not SMs / S), asked of the runtime once.
+struct TcVariant {
+    size_t smem = 0;
+    int max_clusters = 0;
+    cudaError_t status = cudaErrorNotReady;
+};
 
-template <int NT>
-cudaError_t launch_nt(TcArgs a, int sm_count, int32_t* part, size_t part_bytes, cudaStream_t stream) {
+template <int NT, int S>
+const TcVariant& tc_variant(int sm_count) {
+    static TcVariant v;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (v.status != cudaErrorNotReady) return v;
     constexpr int kBBytes = 4 * NT * 64;
-    const size_t smem = (size_t)kStages * (kRawBytes + kBBytes) + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
+    v.smem = (size_t)kStages * (kRawBytes + kBBytes) + (S > 1 ? kRows * NT * 4 : 0) + 256;
+    auto* kernel = gemm_tc_kernel<NT, kUnpackWarps, S>;
+    v.status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)v.smem);
+    if (v.status != cudaSuccess) return v;
+    if (S == 1) { v.max_clusters = sm_count; return v; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sm_count / S * S));
+    cfg.blockDim = dim3(tc_threads(kUnpackWarps));
+    cfg.dynamicSmemBytes = v.smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)S; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        n = 0;  // this cluster size cannot be used
     }
+    v.max_clusters = n;
+    return v;
+}
+
+template <int NT, int S>
+cudaError_t launch_variant(TcArgs a, int n_tiles, int sm_count, cudaStream_t stream) {
+    const TcVariant& v = tc_variant<NT, S>(sm_count);
+    if (v.status != cudaSuccess) return v.status;
+    const int n_clusters = v.max_clusters < n_tiles ? v.max_clusters : n_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n_clusters * S));
+    cfg.blockDim = dim3(tc_threads(kUnpackWarps));
+    cfg.dynamicSmemBytes = v.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)S; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = S > 1 ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<NT, kUnpackWarps, S>, a);
+}
+
+// Chunk steps on the busiest CTA when a tile's k range is cut over `s` CTAs (one step charged for the exchange of
+// partial sums); a huge number when the cut is not possible.
+int64_t tc_split_cost(int s, int max_clusters, int n_tiles, int64_t k_tiles) {
+    if (max_clusters < 1) return INT64_MAX;
+    const int64_t cps = (k_tiles + s - 1) / s;
+    if (s > 1 && (k_tiles < 2 * s || cps * (s - 1) >= k_tiles)) return INT64_MAX;  // a CTA would be left without chunks
+    const int nc = max_clusters < n_tiles ? max_clusters : n_tiles;
+    return (int64_t)((n_tiles + nc - 1) / nc) * (cps + (s > 1 ? 1 : 0));
+}
+
+cudaError_t launch_product(TcArgs a, int nt, int sm_count, cudaStream_t stream) {
     const int row_sets = (int)((a.row_tiles + 7) / 8);
-    const int n_tiles = row_sets * ((a.m + NT - 1) / NT);
-    int splits = part ? tc_k_splits(n_tiles, a.k_tiles, sm_count) : 1;
-    if ((size_t)splits * a.m * a.n_out * sizeof(int32_t) > part_bytes) splits = 1;
-    a.k_splits = splits;
-    a.part = splits > 1 ? part : nullptr;
-    const int units = n_tiles * splits;
-    const int grid = units < sm_count ? units : sm_count;
-    gemm_tc_kernel<NT><<<grid, kTcThreads, smem, stream>>>(a);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess || splits == 1) return e;
-    const int64_t total = (int64_t)a.m * a.n_out;
-    tc_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
-    return cudaGetLastError();
+    const int n_tiles = row_sets * ((a.m + nt - 1) / nt);
+    if (nt == 128) return launch_variant<128, 1>(a, n_tiles, sm_count, stream);
+    // 64 tokens at most: with few output tiles, cut k over a cluster so that one wave of CTAs covers the product
+    int best = 1;
+    int64_t best_cost = tc_split_cost(1, sm_count, n_tiles, a.k_tiles);
+    if (n_tiles * 2 <= sm_count) {
+        const int64_t c2 = tc_split_cost(2, tc_variant<64, 2>(sm_count).max_clusters, n_tiles, a.k_tiles);
+        const int64_t c4 = tc_split_cost(4, tc_variant<64, 4>(sm_count).max_clusters, n_tiles, a.k_tiles);
+        const int64_t c8 = tc_split_cost(8, tc_variant<64, 8>(sm_count).max_clusters, n_tiles, a.k_tiles);
+        if (c2 < best_cost) { best = 2; best_cost = c2; }
+        if (c4 < best_cost) { best = 4; best_cost = c4; }
+        if (c8 < best_cost) { best = 8; best_cost = c8; }
+    }
+    switch (best) {
+        case 2: return launch_variant<64, 2>(a, n_tiles, sm_count, stream);
+        case 4: return launch_variant<64, 4>(a, n_tiles, sm_count, stream);
+        case 8: return launch_variant<64, 8>(a, n_tiles, sm_count, stream);
+        default: return launch_variant<64, 1>(a, n_tiles, sm_count, stream);
+    }
 }
 
 }  // namespace
 
-size_t gemm_tc_part_bytes(int sm_count) {
-    // pieces <= SMs / tiles and tokens x rows <= tiles x 128 x 128, hence pieces x tokens x rows <= SMs x 128 x 128
-    return (size_t)sm_count * kRows * 128 * sizeof(int32_t);
-}
-
 int gemm_tc_kernels(const LinearDev& lin, int64_t m, int sm_count) {
-    const int nt = m <= 64 ? 64 : 128;
-    const int n_tiles = (int)((lin.w.row_tiles + 7) / 8) * (int)((m + nt - 1) / nt);
-    return lin.w.n_bases * (tc_k_splits(n_tiles, lin.w.k_tiles, sm_count) > 1 ? 2 : 1);
+    (void)m; (void)sm_count;
+    return lin.w.n_bases;  // one launch per basis; a k split is reduced inside the launch
 }
 
 size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles) {
@@ -383,22 +501,22 @@ size_t gemm_tc_act_bytes(int64_t m, int64_t k_tiles) {
 
 cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride, int64_t m, int8_t* qtc, float* sx,
                            int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
-                           cudaStream_t stream, int32_t* part, size_t part_bytes, bool prequantised, bt_dtype x_dtype) {
+                           cudaStream_t stream, bool prequantised, bt_dtype x_dtype) {
     if (lin.w.n_bases != 1 && epilogue == EPI_BF16) return cudaErrorInvalidValue;
     const int nt = m <= 64 ? 64 : 128;
     const int padded = (int)((m + nt - 1) / nt * nt);
     const int k = (int)lin.w.k_in, kts = (int)lin.w.k_tiles;
+    cudaError_t e = cudaSuccess;
     if (prequantised) {
     } else if (x_dtype == BT_BF16) {
         const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-        if (nt == 64) act_quant_tc_kernel<64><<<padded, 256, 0, stream>>>(xb, x_stride, k, kts, (int)m, qtc, sx, qsum);
-        else act_quant_tc_kernel<128><<<padded, 256, 0, stream>>>(xb, x_stride, k, kts, (int)m, qtc, sx, qsum);
+        e = nt == 64 ? launch_pdl(act_quant_tc_kernel<64, __nv_bfloat16>, dim3(padded), dim3(256), 0, stream, true, xb, x_stride, k, kts, (int)m, qtc, sx, qsum)
+                     : launch_pdl(act_quant_tc_kernel<128, __nv_bfloat16>, dim3(padded), dim3(256), 0, stream, true, xb, x_stride, k, kts, (int)m, qtc, sx, qsum);
     } else {
         const float* xf = reinterpret_cast<const float*>(x);
-        if (nt == 64) act_quant_tc_kernel<64><<<padded, 256, 0, stream>>>(xf, x_stride, k, kts, (int)m, qtc, sx, qsum);
-        else act_quant_tc_kernel<128><<<padded, 256, 0, stream>>>(xf, x_stride, k, kts, (int)m, qtc, sx, qsum);
+        e = nt == 64 ? launch_pdl(act_quant_tc_kernel<64, float>, dim3(padded), dim3(256), 0, stream, true, xf, x_stride, k, kts, (int)m, qtc, sx, qsum)
+                     : launch_pdl(act_quant_tc_kernel<128, float>, dim3(padded), dim3(256), 0, stream, true, xf, x_stride, k, kts, (int)m, qtc, sx, qsum);
     }
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     for (int b = 0; b < lin.w.n_bases; ++b) {
         TcArgs a = {};
@@ -415,7 +533,7 @@ cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride
         a.out_stride = out_stride;
         a.epilogue = (b > 0 && epilogue == EPI_F32) ? EPI_F32_ACCUM : epilogue;
         a.err = err;
-        e = nt == 64 ? launch_nt<64>(a, sm_count, part, part_bytes, stream) : launch_nt<128>(a, sm_count, part, part_bytes, stream);
+        e = launch_product(a, nt, sm_count, stream);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;

@@ -398,13 +398,14 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
         configured = true;
     }
     if (smem > 160 * 1024) return cudaErrorInvalidConfiguration;
+    // an ordinary launch (starting early behind a tensor-core product measured slower inside the decode step); the
+    // kernel still releases its own dependent at once, so that the product behind it can fetch weights meanwhile
+    const dim3 grid((unsigned)batch), block((unsigned)threads);
     if (pre == PRE_RMSNORM)
-        row_quant_kernel<PRE_RMSNORM><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
-    else if (pre == PRE_SWIGLU)
-        row_quant_kernel<PRE_SWIGLU><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
-    else
-        row_quant_kernel<PRE_NONE><<<batch, threads, smem, stream>>>(x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
-    return cudaGetLastError();
+        return launch_pdl(row_quant_kernel<PRE_RMSNORM>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
+    if (pre == PRE_SWIGLU)
+        return launch_pdl(row_quant_kernel<PRE_SWIGLU>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
+    return launch_pdl(row_quant_kernel<PRE_NONE>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
 }
 
 cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream) {

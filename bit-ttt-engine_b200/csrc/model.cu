@@ -97,8 +97,6 @@ struct bt_model {
     float* act = nullptr;            // [max_batch, intermediate] silu(gate)*up
     float* xt = nullptr;             // [max_batch, max(hidden, intermediate)] transformed rows (batches above 8)
     int8_t* qtc = nullptr;           // activations in the tensor-core product's layout (batches above 8)
-    int32_t* tc_part = nullptr;      // k-split pieces of the tensor-core product
-    size_t tc_part_bytes = 0;
     void* lm_tiles = nullptr;        // lm_head in tensor-core tile order (batches above 8, hidden % 64 == 0)
     void* lm_btiles = nullptr;       // normalised hidden states as bf16 hi|lo tiles
     unsigned int* absmax = nullptr;  // [num_layers][2][max_batch] max|x| cells of the fused path
@@ -120,8 +118,6 @@ struct bt_model {
     int8_t* pf_qtc = nullptr;
     float* pf_sx = nullptr;
     int32_t* pf_qsum = nullptr;
-    int32_t* pf_part = nullptr;
-    size_t pf_part_bytes = 0;
     std::vector<int32_t> pf_host;
     unsigned int* err_pinned = nullptr;  // tensor parallel: the device error word as read after a step
     int host_pos = 0;
@@ -339,14 +335,14 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm1, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
         if (c.arch == 0) {
             // TTTLayer::forward_update (layers/ttt.rs:48-74)
-            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->feat, m->d_small, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->feat, m->d_small, EPI_F32, err, sm, s, true));
             BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->feat, batch, s));
             BT_CUDA_TRY(launch_ttt_step(L.w_state, m->feat, batch, m->d_small, c.inner_lr, m->z, s));
             BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->z, batch, s));
-            BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), m->z, m->d_small, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), m->z, m->d_small, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
         } else {
             // BitAttention::forward (layers/attention.rs:149-225), seq_len 1
-            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->qkv, m->qkv_dim, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->qkv, m->qkv_dim, EPI_F32, err, sm, s, true));
             AttnArgs a;
             a.qkv = m->qkv;
             a.cache = L.kv->view;
@@ -359,19 +355,19 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
             a.absmax_out = nullptr;
-            a.pdl = false;
+            a.pdl = true;
             BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->qkv, batch, s));
             BT_CUDA_TRY(launch_attn_decode(a, s));
             BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->att, batch, s));
-            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes));
+            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
         }
         // x = x + mlp(norm2(x))  (model/block.rs:119-131, layers/swiglu.rs:29-35)
         BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->h, batch, s));
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
-        BT_CUDA_TRY(launch_gemm_tc(L.gate_up_il->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+        BT_CUDA_TRY(launch_gemm_tc(L.gate_up_il->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s, true));
         BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, m->trace ? m->act : nullptr, s, m->qtc, kt_i));
         BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
-        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, m->tc_part, m->tc_part_bytes, true));
+        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, true));
         BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
     }
     // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
@@ -409,8 +405,7 @@ bt_status enqueue_step_generic(bt_model* m, int batch, cudaStream_t s) {
     auto product = [&](bt_linear* lin, float* out, int64_t out_stride) -> bt_status {
         const int64_t qs = lin->w.k_pad();
         if (tc)
-            BT_CUDA_TRY(launch_gemm_tc(lin->dev(), nullptr, lin->w.k_in, batch, m->qtc, m->sx, m->qsum, out, out_stride, EPI_F32, err, sm, s,
-                                       m->tc_part, m->tc_part_bytes, true));
+            BT_CUDA_TRY(launch_gemm_tc(lin->dev(), nullptr, lin->w.k_in, batch, m->qtc, m->sx, m->qsum, out, out_stride, EPI_F32, err, sm, s, true));
         else
             BT_CUDA_TRY(linear_product(lin->dev(), m->q, qs, m->qsum, m->sx, batch, out, out_stride, EPI_F32, err, sm, s));
         return BT_OK;
@@ -656,8 +651,6 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
     if (B > 8) {
         BT_CUDA_TRY(dev_alloc(&m->xt, (size_t)B * (H > I ? H : I)));
         BT_CUDA_TRY(dev_alloc(&m->qtc, gemm_tc_act_bytes(B, (kmax + kTileK - 1) / kTileK)));
-        m->tc_part_bytes = gemm_tc_part_bytes(m->sm_count);
-        BT_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&m->tc_part), m->tc_part_bytes));
         if (H % 64 == 0) {
             BT_CUDA_TRY(cudaMalloc(&m->lm_tiles, lm_head_tc_weight_bytes(c.vocab_size, H)));
             BT_CUDA_TRY(cudaMalloc(&m->lm_btiles, lm_head_tc_act_bytes(H)));
@@ -707,10 +700,10 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles, m->tc_part};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles};
     for (void* p : bufs) cudaFree(p);
     for (void* p : {(void*)m->pf_tokens, (void*)m->pf_h, (void*)m->pf_qkv, (void*)m->pf_att, (void*)m->pf_gu, (void*)m->pf_qtc,
-                    (void*)m->pf_sx, (void*)m->pf_qsum, (void*)m->pf_part, (void*)m->pf_act}) cudaFree(p);
+                    (void*)m->pf_sx, (void*)m->pf_qsum, (void*)m->pf_act}) cudaFree(p);
     if (m->tokens_pinned) cudaFreeHost(m->tokens_pinned);
     if (m->next_pinned) cudaFreeHost(m->next_pinned);
     if (m->err_pinned) cudaFreeHost(m->err_pinned);
@@ -836,7 +829,7 @@ bt_status prefill_buffers(bt_model* m, int rows) {
     const int64_t qw = c.arch == 1 ? m->qkv_dim : m->d_small;  // q|k|v, or the TTT features and predictions (two slots)
     BT_CUDA_TRY(cudaDeviceSynchronize());
     for (void* p : {(void*)m->pf_tokens, (void*)m->pf_h, (void*)m->pf_qkv, (void*)m->pf_att, (void*)m->pf_gu, (void*)m->pf_qtc,
-                    (void*)m->pf_sx, (void*)m->pf_qsum, (void*)m->pf_part}) cudaFree(p);
+                    (void*)m->pf_sx, (void*)m->pf_qsum}) cudaFree(p);
     m->pf_rows = 0;
     const int64_t kmax = H > I ? H : I;
     BT_CUDA_TRY(dev_alloc(&m->pf_tokens, (size_t)rows));
@@ -847,8 +840,6 @@ bt_status prefill_buffers(bt_model* m, int rows) {
     BT_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&m->pf_qtc), gemm_tc_act_bytes(rows, (kmax + kTileK - 1) / kTileK)));
     BT_CUDA_TRY(dev_alloc(&m->pf_sx, (size_t)rows));
     BT_CUDA_TRY(dev_alloc(&m->pf_qsum, (size_t)rows));
-    m->pf_part_bytes = gemm_tc_part_bytes(m->sm_count);
-    BT_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&m->pf_part), m->pf_part_bytes));
     m->pf_rows = rows;
     return BT_OK;
 }
@@ -872,18 +863,18 @@ bt_status enqueue_prefill_chunk(bt_model* m, int batch, int n, int past, int ttt
             // TTTLayer::forward_chunkwise (layers/ttt.rs:80-119); ttt_chunk = 1 is the token-by-token update
             float* feat = m->pf_qkv;
             float* z = m->pf_att;
-            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, feat, m->d_small, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+            BT_CUDA_TRY(launch_gemm_tc(L.ttt_down->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, feat, m->d_small, EPI_F32, err, sm, s, true));
             BT_CUDA_TRY(trace_copy(m, li, TR_QKV, feat, M, s));
             BT_CUDA_TRY(launch_ttt_chunk(L.w_state, feat, batch, n, m->d_small, c.inner_lr, ttt_chunk, z, s));
             BT_CUDA_TRY(trace_copy(m, li, TR_ATT, z, M, s));
             if (m->multi_basis) {  // the bases are summed first, then the residual is added (the order the layer defines)
-                BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, H, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes));
+                BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, H, EPI_F32, err, sm, s));
                 BT_CUDA_TRY(launch_residual_add(m->pf_h, m->pf_gu, (int64_t)M * H, s));
             } else {
-                BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+                BT_CUDA_TRY(launch_gemm_tc(L.ttt_up->dev(), z, m->d_small, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s));
             }
         } else {
-            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_qkv, m->qkv_dim, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+            BT_CUDA_TRY(launch_gemm_tc(L.qkv->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_qkv, m->qkv_dim, EPI_F32, err, sm, s, true));
             BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->pf_qkv, M, s));
             BT_CUDA_TRY(launch_kv_append_rows(L.kv->view, m->pf_qkv, m->pos, m->rope_cos, m->rope_sin, batch, n, m->nh_l, m->nkv_l, m->head_dim, s));
             AttnArgs a;
@@ -904,23 +895,23 @@ bt_status enqueue_prefill_chunk(bt_model* m, int batch, int n, int past, int ttt
             BT_CUDA_TRY(launch_attn_decode(a, s));
             BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->pf_att, M, s));
             if (m->multi_basis) {
-                BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, H, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes));
+                BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, H, EPI_F32, err, sm, s));
                 BT_CUDA_TRY(launch_residual_add(m->pf_h, m->pf_gu, (int64_t)M * H, s));
             } else {
-                BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes));
+                BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->pf_att, m->nh_l * m->head_dim, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s));
             }
         }
         BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->pf_h, M, s));
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->pf_h, H, L.norm2, kRmsEps, M, H, nullptr, 0, m->pf_sx, m->pf_qsum, nullptr, s, m->pf_qtc, kt_h));
-        BT_CUDA_TRY(launch_gemm_tc(L.gate_up_il->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, 2 * I, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+        BT_CUDA_TRY(launch_gemm_tc(L.gate_up_il->dev(), nullptr, H, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_gu, 2 * I, EPI_F32, err, sm, s, true));
         BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->pf_gu, 2 * I, nullptr, 0.f, M, I, nullptr, 0, m->pf_sx, m->pf_qsum,
                                      m->trace ? m->pf_act : nullptr, s, m->pf_qtc, kt_i));
         if (m->trace) BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->pf_act, M, s));
         if (m->multi_basis) {
-            BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_att, H, EPI_F32, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+            BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_att, H, EPI_F32, err, sm, s, true));
             BT_CUDA_TRY(launch_residual_add(m->pf_h, m->pf_att, (int64_t)M * H, s));
         } else {
-            BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, m->pf_part, m->pf_part_bytes, true));
+            BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, M, m->pf_qtc, m->pf_sx, m->pf_qsum, m->pf_h, H, EPI_F32_ACCUM, err, sm, s, true));
         }
         BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->pf_h, M, s));
     }
@@ -1055,7 +1046,7 @@ extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, int as_in
             if (batch > 8) {
                 // tensor-core product on whatever the transformed-row buffer holds (quantiser included)
                 BT_CUDA_TRY(launch_gemm_tc(lin->dev(), m->xt, lin->w.k_in, batch, m->qtc, m->sx, m->qsum, m->gu,
-                                           lin->w.n_out, EPI_F32, err, m->sm_count, s, m->tc_part, m->tc_part_bytes));
+                                           lin->w.n_out, EPI_F32, err, m->sm_count, s));
                 launches += 1 + gemm_tc_kernels(lin->dev(), batch, m->sm_count);
             } else {
                 BT_CUDA_TRY(linear_product(lin->dev(), m->q, m->q_stride, m->qsum, m->sx, batch, m->gu, lin->w.n_out,
