@@ -246,17 +246,23 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
         const int sub = warp & 3;
         const int lrow = sub * 32 + lane;  // row inside the tile
         ptx::pdl_wait();  // the output (and what EPI_F32_ACCUM adds to) belongs to earlier kernels until here
-        auto store = [&](int token, int64_t row, float sw, uint32_t acc) {
+        // The old value of an accumulated output is fetched apart from its update, so that a thread's loads are all
+        // in flight before the first store (a store followed by a load of the same array would serialise them);
+        // the per-token terms come through the read-only path for the same reason.
+        const bool accum = a.epilogue == EPI_F32_ACCUM;
+        auto load_old = [&](int token, int64_t row) -> float {
+            return (accum && token < a.m && row < a.n_out) ? reinterpret_cast<const float*>(a.out)[(int64_t)token * a.out_stride + row] : 0.0f;
+        };
+        auto store = [&](int token, int64_t row, float sw, uint32_t acc, float old) {
             if (token < a.m && row < a.n_out) {
-                const int accv = (int)acc - a.qsum[token];
+                const int accv = (int)acc - __ldg(a.qsum + token);
                 const int64_t o = (int64_t)token * a.out_stride + row;
                 if (a.epilogue == EPI_I32) {
                     reinterpret_cast<int32_t*>(a.out)[o] = accv;
                 } else {
-                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), a.sx[token]);
+                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), __ldg(a.sx + token));
                     if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
-                    else if (a.epilogue == EPI_F32_ACCUM)
-                        reinterpret_cast<float*>(a.out)[o] = __fadd_rn(reinterpret_cast<float*>(a.out)[o], y);
+                    else if (accum) reinterpret_cast<float*>(a.out)[o] = __fadd_rn(old, y);
                     else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
                 }
             }
@@ -270,16 +276,30 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
             const int64_t row = (int64_t)rs * kRows + lrow;
             const int64_t rt = row >> 4;
             float sw = 0.f;
-            if (a.epilogue != EPI_I32 && rt < a.row_tiles) sw = a.sw_tiles[2 * rt + ((row >> 3) & 1)];
+            if (a.epilogue != EPI_I32 && rt < a.row_tiles) sw = __ldg(a.sw_tiles + 2 * rt + ((row >> 3) & 1));
             const uint32_t acc_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)sel * NT;
             if constexpr (S == 1) {
+                if (accum) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < NT; c0 += 32) {
-                    uint32_t d[32];
-                    ptx::tmem_ld32(acc_addr + c0, d);
-                    ptx::tmem_ld_wait();
+                    for (int c0 = 0; c0 < NT; c0 += 16) {
+                        uint32_t d[16];
+                        float old[16];
+                        ptx::tmem_ld16(acc_addr + c0, d);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) store(tb * NT + c0 + j, row, sw, d[j]);
+                        for (int j = 0; j < 16; ++j) old[j] = load_old(tb * NT + c0 + j, row);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) store(tb * NT + c0 + j, row, sw, d[j], old[j]);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < NT; c0 += 32) {
+                        uint32_t d[32];
+                        ptx::tmem_ld32(acc_addr + c0, d);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) store(tb * NT + c0 + j, row, sw, d[j], 0.0f);
+                    }
                 }
                 ptx::tc_fence_before();
                 __syncwarp();
@@ -310,25 +330,34 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
                 ok &= ptx::mbar_wait_cluster_bounded(red_full, (uint32_t)(tl & 1));  // all S copies are complete
                 ptx::fence_cluster();
                 constexpr int kGroups = NT / 4 / S;  // groups of 4 tokens that this CTA finishes
-                uint4 part[kGroups][S];
+                constexpr int kBatch = 8 / S;        // groups per round: 8 remote 16-byte loads in flight
+#pragma unroll 1
+                for (int q0 = 0; q0 < kGroups; q0 += kBatch) {
+                    float old[kBatch][4];
+                    uint4 part[kBatch][S];
 #pragma unroll
-                for (int q = 0; q < kGroups; ++q)
+                    for (int q = 0; q < kBatch; ++q)
 #pragma unroll
-                    for (int pr = 0; pr < S; ++pr)
-                        part[q][pr] = ptx::ld_dsmem_v4(
-                            ptx::map_to_rank(pbuf + ((size_t)(rank * kGroups + q) * kRows + lrow) * 4, (uint32_t)pr));
+                        for (int pr = 0; pr < S; ++pr)
+                            part[q][pr] = ptx::ld_dsmem_v4(
+                                ptx::map_to_rank(pbuf + ((size_t)(rank * kGroups + q0 + q) * kRows + lrow) * 4, (uint32_t)pr));
 #pragma unroll
-                for (int q = 0; q < kGroups; ++q) {
-                    uint4 s = part[q][0];
+                    for (int q = 0; q < kBatch; ++q)
 #pragma unroll
-                    for (int pr = 1; pr < S; ++pr) {
-                        s.x += part[q][pr].x; s.y += part[q][pr].y; s.z += part[q][pr].z; s.w += part[q][pr].w;
+                        for (int e = 0; e < 4; ++e) old[q][e] = load_old(tb * NT + (rank * kGroups + q0 + q) * 4 + e, row);
+#pragma unroll
+                    for (int q = 0; q < kBatch; ++q) {
+                        uint4 s = part[q][0];
+#pragma unroll
+                        for (int pr = 1; pr < S; ++pr) {
+                            s.x += part[q][pr].x; s.y += part[q][pr].y; s.z += part[q][pr].z; s.w += part[q][pr].w;
+                        }
+                        const int token = tb * NT + (rank * kGroups + q0 + q) * 4;
+                        store(token, row, sw, s.x, old[q][0]);
+                        store(token + 1, row, sw, s.y, old[q][1]);
+                        store(token + 2, row, sw, s.z, old[q][2]);
+                        store(token + 3, row, sw, s.w, old[q][3]);
                     }
-                    const int token = tb * NT + (rank * kGroups + q) * 4;
-                    store(token, row, sw, s.x);
-                    store(token + 1, row, sw, s.y);
-                    store(token + 2, row, sw, s.z);
-                    store(token + 3, row, sw, s.w);
                 }
                 __syncwarp();
                 if (lane == 0) {
