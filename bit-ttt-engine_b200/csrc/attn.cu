@@ -6,15 +6,29 @@
 // re-materialised in f32 (the reference dequantises the whole cache every step,
 // layers/kv_cache.rs:84-92).  HBM-bound on the cache bytes: 2*n_kv*T*(hd+4) per sequence.
 //
-// Arithmetic.  Both contractions run on the tensor cores (mma.sync.m16n8k16, bf16 operands,
-// f32 accumulators) with operands that are exact:
-//   * a cache byte b stands for the integer b - 128 in [-128, 127], which bf16 holds exactly;
-//     the row scale (one f32 per cached row) is applied to the f32 result;
-//   * an f32 factor (a rotated query value, a softmax weight times the value-row scale) is cut
-//     into three bf16 pieces hi + mid + lo = x (8 + 8 + 8 significand bits), which ride as
-//     extra columns (scores) or rows (P.V) of the same MMA and are added in f32 afterwards.
-// Every product is therefore exact and only the f32 accumulation rounds: the result is within
-// about 1e-6 relative of the f32 value of layers/attention.rs:202-217.  Softmax runs in f32.
+// Arithmetic.  Both contractions are INTEGER products on the tensor cores
+// (mma.sync.m16n8k32, 8-bit operands, int32 accumulators), so the cache bytes enter the MMA as
+// they lie in memory, without any conversion:
+//   * a cache byte b (unsigned) stands for b - 128; the "- 128" is taken out afterwards with the
+//     sum of the other operand (for the scores a constant per query, for P.V a column of ones
+//     that rides in the same MMAs);
+//   * an f32 factor is turned into fixed point relative to a power-of-two bound and cut into
+//     four 8-bit digits, which ride as extra columns (scores) or rows (P.V) of the same MMA:
+//     a rotated query value q = S * Q / 2^27 with S = the power of two >= max|q| of its vector and
+//     |Q| <= 2^27 (four signed 7-bit digits); a weight p * v_scale = B * U / 2^32 with B = the power
+//     of two above the largest value-row scale of the chunk and U < 2^32 (four unsigned bytes).
+// The digit sums are put together in 64-bit integers and rounded to f32 once, so a score is the
+// correctly rounded product of the key bytes with a query that is exact to 2^-28 of its vector's
+// largest component, and the weights are exact to 2^-33 of the chunk's bound.  Softmax runs in f32.
+// The result is within about 1e-6 relative of the f32 value of layers/attention.rs:202-217.
+//
+// Order of work.  The positions of a CTA are taken in chunks of up to kChunk positions.  Phase A of a
+// chunk streams its KEY tiles (128 positions each) and leaves the f32 scores in shared memory; the
+// chunk's maximum then fixes the softmax reference and the weight bound; phase B streams the VALUE
+// tiles, turns the scores into weight digits tile by tile and accumulates P.V in int32 over the whole
+// chunk.  Only at the end of a chunk do the accumulators become f32 and meet the running output
+// (rescaled by exp(m_old - m_new) as usual).  Key and value tiles flow through one ring of three
+// buffers, fetched two tiles ahead with cp.async.
 //
 // Work split.  One CTA = one (sequence, KV head, span of positions); the spans of one
 // (sequence, KV head) form a thread-block cluster, and the partial results (running maximum,
@@ -35,12 +49,12 @@ constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kTilePos = 128;   // cache rows per tile
 constexpr int kMaxRep = 8;      // query heads per KV head
 constexpr int kMaxHd = 128;
-constexpr int kRowPad = 16;     // bytes added to a cache row in shared memory (row stride = 16 mod 32: 4-byte
-                                // fragment loads of 8 consecutive rows fall into different banks)
+constexpr int kRowPad = 32;     // bytes added to a cache row in shared memory: row stride = 32 mod 128, so the 8-byte
+                                // fragment loads of 4 consecutive rows and the 4-byte loads of rows r, r+1, r+2, r+3
+                                // fall into different banks
 constexpr int kMaxRowBytes = kMaxHd + kRowPad;
-constexpr int kQpStride = kMaxHd + 8;    // bf16 elements per row of the query pieces
-constexpr int kSrStride = kTilePos + 4;  // floats per row of the raw scores
-constexpr int kPwStride = kTilePos + 8;  // bf16 elements per row of the P.V weights
+constexpr int kStages = 3;      // tile buffers of the ring
+constexpr int kWStride = kTilePos + 16;  // bytes per row of the weight digits
 constexpr int kMaxCluster = 16;
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -53,12 +67,17 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+__device__ __forceinline__ long long shfl_xor_ll(long long v, int mask) {
+    const int lo = __shfl_xor_sync(0xffffffffu, (int)(v & 0xffffffffll), mask);
+    const int hi = __shfl_xor_sync(0xffffffffu, (int)(v >> 32), mask);
+    return ((long long)hi << 32) | (unsigned int)lo;
+}
 
 // Quantise one head vector held in shared memory (hd values) by one warp:
 // s = max|x| / 127, q = u8(round(x / s) + 128)  (quantize_q8, layers/kv_cache.rs:95-119; an all-zero
-// row gives s = 0, q = 128).  q_copy / s_copy: optional second destination (a prefetched copy of the row).
+// row gives s = 0, q = 128).  q_copy: optional second destination (a prefetched copy of the row).
 __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* q_out, float* s_out, uint8_t* q_copy,
-                                               float* s_copy, int lane) {
+                                               int lane) {
     float amax = 0.0f;
     for (int c = lane; c < hd; c += 32) amax = fmaxf(amax, fabsf(v[c]));
     amax = warp_max(amax);
@@ -69,40 +88,47 @@ __device__ __forceinline__ void quant_row_warp(const float* v, int hd, uint8_t* 
         q_out[c] = (uint8_t)r;
         if (q_copy) q_copy[c] = (uint8_t)r;
     }
-    if (lane == 0) {
-        *s_out = s;
-        if (s_copy) *s_copy = s;
-    }
+    if (lane == 0) *s_out = s;
 }
 
 // G = query vectors that share the K/V rows of a CTA: the NREP heads of a KV group (decode) times the
-// QB query positions of a block (prefill).  "Row" below = piece * G + query vector.
+// QB query positions of a block (prefill).  Score column / weight row 4 v + j = digit j of query vector v.
 template <int G>
 struct AttnSmemT {
-    static constexpr int kRows = 3 * G;
-    static constexpr int kRows16 = (kRows + 15) / 16 * 16;
-    // cache rows as stored (u8, rows padded), two tiles: while one is worked on, the next arrives;
-    // after the last tile both arrays serve as scratch of the warp reduction
-    alignas(16) uint8_t kraw[2][kTilePos * kMaxRowBytes];
-    alignas(16) uint8_t vraw[2][kTilePos * kMaxRowBytes];
-    alignas(16) float ksr[2][kTilePos];
-    alignas(16) float vsr[2][kTilePos];
-    alignas(16) __nv_bfloat16 qp[kRows][kQpStride];        // rotated queries
-    alignas(16) float sraw[kRows][kSrStride];              // per-piece dot products of the tile
-    alignas(16) __nv_bfloat16 pw[kRows16][kPwStride];      // pieces of p * v_scale
-    alignas(16) float opart[G * kMaxHd];                   // this span's unnormalised output [query vector][dim] (read by the cluster)
-    float ml[2][G];                                        // this span's running maximum / denominator (read by the cluster)
+    static constexpr int kChunk = G <= 4 ? 1024 : 512;     // positions whose scores are held at once
+    static constexpr int kCols = 4 * G;
+    static constexpr int kCols8 = (kCols + 7) / 8 * 8;
+    static constexpr int kRows16 = (kCols + 15) / 16 * 16;
+    alignas(16) uint8_t ring[kStages][kTilePos * kMaxRowBytes];  // key / value tiles as stored (u8), rows padded
+    alignas(16) float sbuf[G][kChunk];                      // scores of the chunk (before the chunk: the rotated queries)
+    alignas(16) float sc[kStages][kTilePos];                // row scales that came with a key tile
+    alignas(16) float vsc[kChunk];                          // value-row scales of the chunk
+    alignas(16) int8_t qdig[kCols8][kMaxRowBytes];          // query digits, [column][dim]
+    alignas(16) uint8_t wdig[2][kRows16][kWStride];         // weight digits of a tile, [row][position slot], two tiles
+    alignas(16) float opart[G * kMaxHd];                    // this span's unnormalised output [query vector][dim] (read by the cluster)
+    alignas(16) float part[2 * G * kMaxHd];                 // a chunk's P.V result per position group, [group][vector][dim], before it meets opart
+    long long icorr[G];                                     // 128 * sum_d Q[v][d]: the "- 128" of the key bytes
+    float qscale[G];                                        // S / 2^27 of a query vector
+    float ml[2][G];                                         // this span's running maximum / denominator (read by the cluster)
     float corr[G];
-    float wmax[G][4];
-    float wsum[G][4];
+    float wmax[kAttnWarps][G];
+    float wsum[kAttnWarps][(G + 1) / 2];
+    float wvmax[kAttnWarps];
+    float wup, wdown;                                       // weight scale of the chunk: 2^32 / B and B / 2^32
     float knew[kMaxHd], vnew[kMaxHd];
 };
 
-// D(16x8, f32) += A(16x16, bf16, row) * B(16x8, bf16, col)
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+// D(16x8, s32) += A(16x32, u8, row) * B(32x8, s8 or u8, col)
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
@@ -112,24 +138,19 @@ __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
 __device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_u32(dst_smem)), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// all but the newest `N` groups of this thread are complete
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// f32(byte `which` of word) - 128 without an integer-to-float conversion: 0x4B0000bb is the float
-// 2^23 + b, and subtracting 2^23 + 128 is exact.
-__device__ __forceinline__ float byte_minus_128(uint32_t word, int which) {
-    return __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540 + which)), 8388736.0f);
-}
-// two integers in [-128, 127] as a bf16 pair (exact), `lo` in the low half
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&p);
-}
-// x = hi + mid + lo with three bf16 terms (the residuals are exact f32 differences)
-__device__ __forceinline__ void split3(float x, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
-    hi = __float2bfloat16_rn(x);
-    const float r1 = __fsub_rn(x, __bfloat162float(hi));
-    mid = __float2bfloat16_rn(r1);
-    lo = __float2bfloat16_rn(__fsub_rn(r1, __bfloat162float(mid)));
+// bytes e of the words v0..v3 as one word (v0.e, v1.e, v2.e, v3.e), e = 0..3: a 4 x 4 byte transpose
+__device__ __forceinline__ void transpose4(uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3, uint32_t (&r)[4]) {
+    const uint32_t lo01 = __byte_perm(v0, v1, 0x5140), hi01 = __byte_perm(v0, v1, 0x7362);
+    const uint32_t lo23 = __byte_perm(v2, v3, 0x5140), hi23 = __byte_perm(v2, v3, 0x7362);
+    r[0] = __byte_perm(lo01, lo23, 0x5410);
+    r[1] = __byte_perm(lo01, lo23, 0x7632);
+    r[2] = __byte_perm(hi01, hi23, 0x5410);
+    r[3] = __byte_perm(hi01, hi23, 0x7632);
 }
 
 // ---- thread-block cluster primitives -----------------------------------------------------
@@ -155,14 +176,15 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t ran
 // cache; blockIdx.y = block of QB consecutive query positions, which sees the keys up to its own position
 // (causal rule of layers/attention.rs:249-262: key j is visible to query i when j <= i + past).
 template <int NREP, int QB>
-__global__ void __launch_bounds__(kAttnThreads, QB == 1 ? 2 : 1) attn_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_kernel(AttnArgs a) {
     constexpr int G = NREP * QB;
     using Smem = AttnSmemT<G>;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
-    constexpr int kRowsUsed = 3 * G;               // (piece, query vector) rows
-    constexpr int NB = (kRowsUsed + 7) / 8;        // 8-column blocks of the score MMAs
-    constexpr int MB = (kRowsUsed + 15) / 16;      // 16-row blocks of the P.V MMAs
+    constexpr int kChunk = Smem::kChunk;
+    constexpr int NB = Smem::kCols8 / 8;           // 8-column blocks of the score MMAs (two query vectors each)
+    constexpr int MB = Smem::kRows16 / 16;         // 16-row blocks of the P.V MMAs (four query vectors each)
+    constexpr int kRounds = (G * kTilePos + kAttnThreads - 1) / kAttnThreads;  // (vector, position) items per thread and tile
     const int hd = a.head_dim, half = hd >> 1;
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int split = blockIdx.y;
@@ -182,54 +204,75 @@ __global__ void __launch_bounds__(kAttnThreads, QB == 1 ? 2 : 1) attn_kernel(Att
     const int t0 = QB == 1 ? split * span : 0;
     const int t1 = QB == 1 ? min(t_len, t0 + span) : t_len;
     const int64_t row_base = ((int64_t)b * a.n_kv + kvh) * a.cache.max_seq;
-    const int row16 = hd >> 4;            // 16-byte pieces per row
-    const int rstride = hd + kRowPad;     // row stride of the tiles in shared memory
+    const int row16 = hd >> 4;                            // 16-byte pieces per row
+    const int l16 = hd == 128 ? 3 : (hd == 64 ? 2 : (hd == 32 ? 1 : -1));  // their log2 when a power of two
+    const int rstride = hd + kRowPad;                    // row stride of the tiles in shared memory
 
-    // cache rows [r0, r0 + n) of this (sequence, KV head) -> tile buffer `buf` (asynchronous copies)
-    auto fetch_tile = [&](int buf, int r0, int n) {
-        const uint8_t* ksrc = a.cache.k_q + (row_base + r0) * hd;
-        const uint8_t* vsrc = a.cache.v_q + (row_base + r0) * hd;
-        for (int i = tid; i < n * row16; i += kAttnThreads) {
-            const int o = (i / row16) * rstride + (i % row16) * 16;
-            cp_async16(sm.kraw[buf] + o, ksrc + 16 * i);
-            cp_async16(sm.vraw[buf] + o, vsrc + 16 * i);
-        }
-        for (int i = tid; i < n; i += kAttnThreads) {
-            cp_async4(&sm.ksr[buf][i], a.cache.k_s + row_base + r0 + i);
-            cp_async4(&sm.vsr[buf][i], a.cache.v_s + row_base + r0 + i);
+    // The tiles of this CTA in the order they are worked on: per chunk its key tiles, then its value tiles.
+    // `Cursor` names one of them; the fetches run two tiles ahead of the work.
+    struct Cursor { int chunk0; int phase; int tile; };  // first position of the chunk, 0 = keys / 1 = values, tile in chunk
+    auto chunk_tiles = [&](int chunk0) { return (min(kChunk, t1 - chunk0) + kTilePos - 1) / kTilePos; };
+    auto advance = [&](Cursor& c) {
+        if (++c.tile >= chunk_tiles(c.chunk0)) {
+            c.tile = 0;
+            if (++c.phase == 2) { c.phase = 0; c.chunk0 += kChunk; }
         }
     };
-    // The cache rows of earlier positions were written by earlier steps, so the first tile can be
-    // requested before the dependency wait (the row of the current position is fetched too, with
-    // whatever it holds; its owner overwrites the copy below).
-    const int n_first = max(0, min(kTilePos, t1 - t0));
-    if (QB == 1) fetch_tile(0, t0, n_first);  // (prefill: the new rows come from the kernel just before)
-    // (piece, query vector) rows of the P.V weights beyond the ones in use stay zero
-    for (int i = tid; i < (Smem::kRows16 - kRowsUsed) * kPwStride; i += kAttnThreads)
-        sm.pw[kRowsUsed + i / kPwStride][i % kPwStride] = __float2bfloat16_rn(0.0f);
+    // rows of the tile `c` -> ring buffer `stage` (asynchronous copies); a key tile brings its row scales along
+    auto fetch = [&](const Cursor& c, int stage) {
+        if (c.chunk0 < t1) {
+            const int r0 = c.chunk0 + c.tile * kTilePos;
+            const int n = min(kTilePos, t1 - r0);
+            const uint8_t* src = (c.phase ? a.cache.v_q : a.cache.k_q) + (row_base + r0) * hd;
+            uint8_t* dst = sm.ring[stage];
+            if (l16 >= 0) {
+                for (int i = tid; i < (n << l16); i += kAttnThreads)
+                    cp_async16(dst + (i >> l16) * rstride + ((i & ((1 << l16) - 1)) << 4), src + 16 * i);
+            } else {
+                for (int i = tid; i < n * row16; i += kAttnThreads)
+                    cp_async16(dst + (i / row16) * rstride + (i % row16) * 16, src + 16 * i);
+            }
+            if (c.phase == 0 && tid < n) cp_async4(&sm.sc[stage][tid], a.cache.k_s + row_base + r0 + tid);
+        }
+        cp_async_commit();  // one group per tile, also when there is nothing left to fetch
+    };
+
+    Cursor fc = {t0, 0, 0};
+    const bool empty = t0 >= t_len;
+    // The cache rows of earlier positions were written by earlier steps, so the first tile can be requested
+    // before the dependency wait; the row of the current position is fetched too, with whatever it holds, and its
+    // owner overwrites the copy below.
+    if (QB == 1 && !empty) {
+        fetch(fc, 0);
+        advance(fc);
+    }
+    // weight rows and query columns beyond the ones in use stay zero
+    for (int i = tid; i < (int)(sizeof(sm.wdig) / 4); i += kAttnThreads) reinterpret_cast<uint32_t*>(sm.wdig)[i] = 0u;
+    for (int i = tid; i < (int)(sizeof(sm.qdig) / 4); i += kAttnThreads) reinterpret_cast<uint32_t*>(sm.qdig)[i] = 0u;
+    for (int i = tid; i < G * kMaxHd; i += kAttnThreads) sm.opart[i] = 0.0f;
     ptx::pdl_wait();
-    if (QB > 1) fetch_tile(0, t0, n_first);
+    if (QB > 1 && !empty) {  // prefill: the new rows come from the kernel just before
+        fetch(fc, 0);
+        advance(fc);
+    }
 
     const int64_t qkv_stride = (int64_t)(a.n_heads + 2 * a.n_kv) * hd;
     const float* qkv = a.qkv + (int64_t)b * a.q_rows * qkv_stride;  // first new token of the sequence
-    const bool empty = t0 >= t_len;
     const bool owner = QB == 1 && (p >= t0 && p < t1);
     if (!empty) {
         const float* cos_p = a.rope_cos + (int64_t)p * half;
         const float* sin_p = a.rope_sin + (int64_t)p * half;
-        // rotate the query vectors of this CTA, [x1*cos - x2*sin, x1*sin + x2*cos] (attention.rs:79-83),
-        // and cut every value into its three bf16 pieces.  Query vector v = (position q0 + v / NREP, head
-        // v % NREP); a block that reaches beyond the last new token repeats the last one (never stored).
+        // rotate the query vectors of this CTA, [x1*cos - x2*sin, x1*sin + x2*cos] (attention.rs:79-83), into the
+        // score buffer (free until the first chunk).  Query vector v = (position q0 + v / NREP, head v % NREP); a
+        // block that reaches beyond the last new token repeats the last one (never stored).
         for (int i = tid; i < G * half; i += kAttnThreads) {
             const int v = i / half, c = i % half;
             const int h = v % NREP, qi = min(q0 + v / NREP, a.q_rows - 1);
             const float cs = a.rope_cos[(int64_t)(p + qi) * half + c], sn = a.rope_sin[(int64_t)(p + qi) * half + c];
             const float* qh = qkv + (int64_t)qi * qkv_stride + (int64_t)(kvh * NREP + h) * hd;
             const float x1 = qh[c], x2 = qh[half + c];
-            const float r1 = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
-            const float r2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
-            split3(r1, sm.qp[v][c], sm.qp[G + v][c], sm.qp[2 * G + v][c]);
-            split3(r2, sm.qp[v][half + c], sm.qp[G + v][half + c], sm.qp[2 * G + v][half + c]);
+            sm.sbuf[v][c] = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+            sm.sbuf[v][half + c] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, cs));
         }
         // the CTA whose span holds position p appends the new key / value first
         if (owner) {
@@ -248,193 +291,275 @@ __global__ void __launch_bounds__(kAttnThreads, QB == 1 ? 2 : 1) attn_kernel(Att
         sm.ml[0][tid] = -INFINITY;  // a span without positions keeps these: weight 0 in the merge
         sm.ml[1][tid] = 0.0f;
     }
-    cp_async_wait_all();
+    cp_async_wait<0>();
     __syncthreads();  // first tile landed; rotated q / k / v visible
+    if (!empty) {
+        // Query digits, one warp per vector in turn: S = power of two >= max|q|, Q = round(q / S * 2^27),
+        // Q = ((d0 * 128 + d1) * 128 + d2) * 128 + d3 with digits in [-64, 64].
+        for (int v = warp; v < G; v += kAttnWarps) {
+            float amax = 0.0f;
+            for (int c = lane; c < hd; c += 32) amax = fmaxf(amax, fabsf(sm.sbuf[v][c]));
+            amax = warp_max(amax);
+            int ex = 0;
+            if (amax > 0.0f) (void)frexpf(amax, &ex);   // amax = m * 2^ex, m in [0.5, 1)
+            const float up = ldexpf(1.0f, 27 - ex);
+            long long qsum = 0;
+            for (int c = lane; c < hd; c += 32) {
+                int Q = __float2int_rn(__fmul_rn(sm.sbuf[v][c], up));
+                qsum += Q;
+                const int d3 = ((Q + 64) & 127) - 64; Q = (Q - d3) >> 7;
+                const int d2 = ((Q + 64) & 127) - 64; Q = (Q - d2) >> 7;
+                const int d1 = ((Q + 64) & 127) - 64; Q = (Q - d1) >> 7;
+                sm.qdig[4 * v + 0][c] = (int8_t)Q;
+                sm.qdig[4 * v + 1][c] = (int8_t)d1;
+                sm.qdig[4 * v + 2][c] = (int8_t)d2;
+                sm.qdig[4 * v + 3][c] = (int8_t)d3;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) qsum += shfl_xor_ll(qsum, o);
+            if (lane == 0) {
+                sm.icorr[v] = 128ll * qsum;
+                sm.qscale[v] = ldexpf(1.0f, ex - 27);
+            }
+        }
+    }
     if (owner) {
-        const bool in_first = p - t0 < n_first;
-        if (warp == 0) quant_row_warp(sm.knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p,
-                                      in_first ? sm.kraw[0] + (p - t0) * rstride : nullptr, in_first ? sm.ksr[0] + (p - t0) : nullptr, lane);
-        if (warp == 1) quant_row_warp(sm.vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p,
-                                      in_first ? sm.vraw[0] + (p - t0) * rstride : nullptr, in_first ? sm.vsr[0] + (p - t0) : nullptr, lane);
+        const bool in_first = p - t0 < kTilePos;
+        if (warp == 6) quant_row_warp(sm.knew, hd, a.cache.k_q + (row_base + p) * hd, a.cache.k_s + row_base + p,
+                                      in_first ? sm.ring[0] + (p - t0) * rstride : nullptr, lane);
+        if (warp == 7) quant_row_warp(sm.vnew, hd, a.cache.v_q + (row_base + p) * hd, a.cache.v_s + row_base + p, nullptr, lane);
     }
     __syncthreads();  // the block's own global writes are visible to its later copies after the barrier
+    if (owner && p - t0 < kTilePos && tid == 0) sm.sc[0][p - t0] = a.cache.k_s[row_base + p];  // the prefetched copy was stale
+    if (!empty) {
+        fetch(fc, 1);  // second tile
+        advance(fc);
+    }
 
-    // P.V ownership: warp = (group of 32 dims dg, position group pq); the warp handles the 16-position
-    // steps pq, pq + n_pq, ... of every tile for dims 32 dg .. 32 dg + 31.  One 32-bit load of a V row
-    // (dims 32 dg + 4 g .. + 3) feeds four MMAs, MMA e holding dim 32 dg + 4 n + e in column n.
+    // P.V ownership: warp = (group of 32 dims dg, position group pq); the warp handles the 32-position steps
+    // pq, pq + n_pq, ... of every tile for dims 32 dg .. 32 dg + 31.  Four 32-bit loads of V rows (dims
+    // 32 dg + 4 g .. + 3 of four positions) are transposed into the B fragments of four MMAs, MMA e holding
+    // dim 32 dg + 4 n + e in column n.
     const int n_dg = hd >> 5;
     const int n_pq = kAttnWarps / n_dg;
     const int dg = warp % n_dg, pq = warp / n_dg;
-    const bool pv_active = pq < n_pq;
-    float acc[MB][4][4];
-#pragma unroll
-    for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[mb][e][j] = 0.0f;
+    int acc[MB][4][4], ones[MB][4];
+    float psum[kRounds], mx[NB];
 
     if (!empty) {
-        int cur = 0;
-        for (int tb = t0; tb < t1; tb += kTilePos) {
-            const int n_here = min(kTilePos, t1 - tb);
-            if (tb + kTilePos < t1)  // long span: the next tile's rows go into the other buffer meanwhile
-                fetch_tile(cur ^ 1, tb + kTilePos, min(kTilePos, t1 - tb - kTilePos));
-            const uint8_t* kraw = sm.kraw[cur];
-            const uint8_t* vraw = sm.vraw[cur];
-            // (1) per-piece dot products S[16 positions x (piece, head)] = K[16 x hd] . q[hd x (piece, head)]:
-            //     warp w owns positions 16 w .. 16 w + 15.  Lane (g, t) supplies dims 16 j + 4 t .. + 3 of
-            //     rows g and g + 8 in step j (the order of the dims inside a step is free as long as q
-            //     follows it).  Rows at or beyond n_here hold anything; they only reach their own row of
-            //     S, which the softmax ignores.
-            if (16 * warp < n_here) {
-                float c[NB][4];
+        int n = 0;  // tiles done so far: tile n sits in ring[n % kStages]
+        for (int chunk0 = t0; chunk0 < t1; chunk0 += kChunk) {
+            const int clen = min(kChunk, t1 - chunk0);
+            const int ctiles = (clen + kTilePos - 1) / kTilePos;
 #pragma unroll
-                for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.0f;
-                const uint8_t* krow0 = kraw + (16 * warp + g) * rstride + 4 * t;
-                const uint8_t* krow1 = krow0 + 8 * rstride;
-                for (int j = 0; j < row16; ++j) {
-                    const uint32_t w0 = *reinterpret_cast<const uint32_t*>(krow0 + 16 * j);
-                    const uint32_t w1 = *reinterpret_cast<const uint32_t*>(krow1 + 16 * j);
-                    const uint32_t a0 = pack_bf16(byte_minus_128(w0, 0), byte_minus_128(w0, 1));
-                    const uint32_t a2 = pack_bf16(byte_minus_128(w0, 2), byte_minus_128(w0, 3));
-                    const uint32_t a1 = pack_bf16(byte_minus_128(w1, 0), byte_minus_128(w1, 1));
-                    const uint32_t a3 = pack_bf16(byte_minus_128(w1, 2), byte_minus_128(w1, 3));
+            for (int nb = 0; nb < NB; ++nb) mx[nb] = -INFINITY;
+            // the chunk's value-row scales, needed between the phases: requested now, used then
+            float vs_reg[kChunk / kAttnThreads];
+#pragma unroll
+            for (int i = 0; i < kChunk / kAttnThreads; ++i)
+                vs_reg[i] = tid + i * kAttnThreads < clen ? a.cache.v_s[row_base + chunk0 + tid + i * kAttnThreads] : 0.0f;
+            // ---- phase A: scores of the chunk.  Warp w owns positions 16 w .. 16 w + 15 of a tile; per 32-dim
+            //      step lane (g, t) supplies bytes 32 j + 8 t .. + 7 of rows g and g + 8 (the order of the dims
+            //      inside a step is free as long as the query digits follow it). -------------------------------
+            for (int ti = 0; ti < ctiles; ++ti, ++n) {
+                cp_async_wait<1>();
+                __syncthreads();  // tile n landed and visible; everybody is done with tile n - 1
+                fetch(fc, (n + 2) % kStages);
+                advance(fc);
+                const int n_here = min(kTilePos, clen - ti * kTilePos);
+                if (16 * warp < n_here) {
+                    const uint8_t* kraw = sm.ring[n % kStages];
+                    int c[NB][4];
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0;
+                    const uint8_t* krow0 = kraw + (16 * warp + g) * rstride + 8 * t;
+                    const uint8_t* krow1 = krow0 + 8 * rstride;
+                    for (int j = 0; j < (hd >> 5); ++j) {
+                        const uint2 w0 = *reinterpret_cast<const uint2*>(krow0 + 32 * j);
+                        const uint2 w1 = *reinterpret_cast<const uint2*>(krow1 + 32 * j);
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            const uint2 q8 = *reinterpret_cast<const uint2*>(&sm.qdig[nb * 8 + g][32 * j + 8 * t]);
+                            mma_u8s8(c[nb], w0.x, w1.x, w0.y, w1.y, q8.x, q8.y);
+                        }
+                    }
+                    // Lane t holds columns 2t, 2t + 1 of block nb: digits (0, 1) (t even) or (2, 3) (t odd) of query
+                    // vector 2 nb + t / 2, for rows g and g + 8.  The lane pair swaps halves: the even lane finishes
+                    // row g, the odd lane row g + 8.
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) {
-                        const int col = nb * 8 + g;  // (piece, head) column this lane feeds
-                        uint32_t b0 = 0u, b1 = 0u;
-                        if (col < kRowsUsed) {
-                            const uint2 q4 = *reinterpret_cast<const uint2*>(&sm.qp[col][16 * j + 4 * t]);
-                            b0 = q4.x; b1 = q4.y;
+                        const int v = 2 * nb + (t >> 1);
+                        const bool odd = t & 1;
+                        // even: own = c0 * 2^21 + c1 * 2^14 (row g), send the same of row g + 8;
+                        // odd : own = c2 * 2^7 + c3 (row g + 8), send the same of row g
+                        const long long own = odd ? (long long)(c[nb][2] * 128 + c[nb][3])
+                                                  : (long long)c[nb][0] * 2097152ll + (long long)c[nb][1] * 16384ll;
+                        const long long send = odd ? (long long)(c[nb][0] * 128 + c[nb][1])
+                                                   : (long long)c[nb][2] * 2097152ll + (long long)c[nb][3] * 16384ll;
+                        const long long got = shfl_xor_ll(send, 1);
+                        if (v < G) {
+                            const int r = 16 * warp + g + (odd ? 8 : 0);
+                            // prefill: query vector v sits at position p + q0 + v / NREP and sees the keys up to there
+                            const bool seen = QB == 1 || chunk0 + ti * kTilePos + r <= p + q0 + v / NREP;
+                            float s = -INFINITY;
+                            if (r < n_here && seen) {
+                                const float dot = __fmul_rn(__ll2float_rn(own + got - sm.icorr[v]), sm.qscale[v]);
+                                s = __fmul_rn(__fmul_rn(dot, sm.sc[n % kStages][r]), a.scaling);  // (attention.rs:202)
+                            }
+                            sm.sbuf[v][ti * kTilePos + r] = s;
+                            mx[nb] = fmaxf(mx[nb], s);
                         }
-                        mma_bf16(c[nb], a0, a1, a2, a3, b0, b1);
-                    }
-                }
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb) {
-                    const int col = nb * 8 + 2 * t;
-                    if (col < kRowsUsed) {
-                        sm.sraw[col][16 * warp + g] = c[nb][0];
-                        sm.sraw[col][16 * warp + g + 8] = c[nb][2];
-                    }
-                    if (col + 1 < kRowsUsed) {
-                        sm.sraw[col + 1][16 * warp + g] = c[nb][1];
-                        sm.sraw[col + 1][16 * warp + g + 8] = c[nb][3];
                     }
                 }
             }
-            __syncthreads();
-            // (2) softmax weights of the tile, one (head, position) per thread and round; a warp covers
-            //     32 positions of one head.  score = ((q.k_int) * k_scale) * 1/sqrt(hd)  (attention.rs:202)
-            constexpr int kSoftItems = (G * kTilePos + kAttnThreads - 1) / kAttnThreads;
-            float sv[kSoftItems];
+            // ---- between the phases: the chunk's maximum per query vector, the bound of the weights ----
 #pragma unroll
-            for (int e = 0; e < kSoftItems; ++e) {
-                const int it = tid + e * kAttnThreads;
-                const int h = it / kTilePos, r = it % kTilePos;
-                float s = -INFINITY;
-                // prefill: query vector h sits at position p + q0 + h / NREP and sees the keys up to there
-                const bool seen = QB == 1 || tb + r <= p + q0 + h / NREP;
-                if (h < G && r < n_here && seen) {
-                    const float dot = __fadd_rn(__fadd_rn(sm.sraw[h][r], sm.sraw[G + h][r]), sm.sraw[2 * G + h][r]);
-                    s = __fmul_rn(__fmul_rn(dot, sm.ksr[cur][r]), a.scaling);
+            for (int nb = 0; nb < NB; ++nb) {
+                float m = mx[nb];
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+                if (g == 0 && (t & 1) == 0 && 2 * nb + (t >> 1) < G) sm.wmax[warp][2 * nb + (t >> 1)] = m;
+            }
+            {
+                float vm = 0.0f;
+#pragma unroll
+                for (int i = 0; i < kChunk / kAttnThreads; ++i) {
+                    sm.vsc[tid + i * kAttnThreads] = vs_reg[i];
+                    vm = fmaxf(vm, vs_reg[i]);
                 }
-                sv[e] = s;
-                const float wm = warp_max(s);
-                if (lane == 0 && h < G) sm.wmax[h][(it >> 5) & 3] = wm;
+                vm = warp_max(vm);
+                if (lane == 0) sm.wvmax[warp] = vm;
             }
             __syncthreads();
-#pragma unroll
-            for (int e = 0; e < kSoftItems; ++e) {
-                const int it = tid + e * kAttnThreads;
-                const int h = it / kTilePos, r = it % kTilePos;
-                if (h < G) {  // warp-uniform
-                    const float m_old = sm.ml[0][h];
-                    const float m_new = fmaxf(fmaxf(m_old, fmaxf(sm.wmax[h][0], sm.wmax[h][1])), fmaxf(sm.wmax[h][2], sm.wmax[h][3]));
-                    const bool live = sv[e] != -INFINITY;  // inside the tile and visible to this query
-                    const float pe = live ? expf(__fsub_rn(sv[e], m_new)) : 0.0f;
-                    // weight of the value row: p * v_scale (the value bytes enter the MMA as integers)
-                    const float wv = live ? __fmul_rn(pe, sm.vsr[cur][r]) : 0.0f;
-                    split3(wv, sm.pw[h][r], sm.pw[G + h][r], sm.pw[2 * G + h][r]);
-                    const float ws = warp_sum(pe);
-                    if (lane == 0) sm.wsum[h][(it >> 5) & 3] = ws;
-                    if (r == 0) sm.corr[h] = expf(__fsub_rn(m_old, m_new));  // exp(-inf) = 0 on the first tile
-                }
-            }
-            __syncthreads();
-            if (tid < G) {  // running sum and maximum (nobody reads them before the next barrier)
+            if (tid < G) {
                 const float m_old = sm.ml[0][tid];
-                const float m_new = fmaxf(fmaxf(m_old, fmaxf(sm.wmax[tid][0], sm.wmax[tid][1])), fmaxf(sm.wmax[tid][2], sm.wmax[tid][3]));
-                const float psum = __fadd_rn(__fadd_rn(__fadd_rn(sm.wsum[tid][0], sm.wsum[tid][1]), sm.wsum[tid][2]), sm.wsum[tid][3]);
-                sm.ml[1][tid] = fmaf(sm.ml[1][tid], sm.corr[tid], psum);
+                float m_new = m_old;
+#pragma unroll
+                for (int w = 0; w < kAttnWarps; ++w) m_new = fmaxf(m_new, sm.wmax[w][tid]);
+                // nothing visible so far (prefill blocks whose first chunk lies ahead never happen; kept for safety)
+                sm.corr[tid] = m_new == -INFINITY ? 1.0f : expf(__fsub_rn(m_old, m_new));  // exp(-inf) = 0 on the first chunk
                 sm.ml[0][tid] = m_new;
             }
-            // (3) O[(piece, head) x 32 dims] = O * corr + W[(piece, head) x positions] . V[positions x dims]
-            if (pv_active) {
+            if (tid == 32) {
+                float vm = 0.0f;
 #pragma unroll
-                for (int mb = 0; mb < MB; ++mb) {
-                    const int r0 = mb * 16 + g, r1 = r0 + 8;
-                    const float c0 = r0 < kRowsUsed ? sm.corr[r0 % G] : 0.0f;
-                    const float c1 = r1 < kRowsUsed ? sm.corr[r1 % G] : 0.0f;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) { acc[mb][e][0] *= c0; acc[mb][e][1] *= c0; acc[mb][e][2] *= c1; acc[mb][e][3] *= c1; }
-                }
-                const uint8_t* vcol = vraw + 32 * dg + 4 * g;
-                for (int i = pq; 16 * i < n_here; i += n_pq) {
-                    const int pos0 = 16 * i + 2 * t;  // this lane's positions of the step: pos0, +1, +8, +9
-                    const uint32_t v0 = *reinterpret_cast<const uint32_t*>(vcol + (pos0) * rstride);
-                    const uint32_t v1 = *reinterpret_cast<const uint32_t*>(vcol + (pos0 + 1) * rstride);
-                    const uint32_t v8 = *reinterpret_cast<const uint32_t*>(vcol + (pos0 + 8) * rstride);
-                    const uint32_t v9 = *reinterpret_cast<const uint32_t*>(vcol + (pos0 + 9) * rstride);
-                    uint32_t pa[MB][4];
-#pragma unroll
-                    for (int mb = 0; mb < MB; ++mb) {
-                        const int r0 = mb * 16 + g, r1 = r0 + 8;
-                        pa[mb][0] = *reinterpret_cast<const uint32_t*>(&sm.pw[r0][pos0]);
-                        pa[mb][1] = *reinterpret_cast<const uint32_t*>(&sm.pw[r1][pos0]);
-                        pa[mb][2] = *reinterpret_cast<const uint32_t*>(&sm.pw[r0][pos0 + 8]);
-                        pa[mb][3] = *reinterpret_cast<const uint32_t*>(&sm.pw[r1][pos0 + 8]);
-                    }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t b0 = pack_bf16(byte_minus_128(v0, e), byte_minus_128(v1, e));
-                        const uint32_t b1 = pack_bf16(byte_minus_128(v8, e), byte_minus_128(v9, e));
-#pragma unroll
-                        for (int mb = 0; mb < MB; ++mb) mma_bf16(acc[mb][e], pa[mb][0], pa[mb][1], pa[mb][2], pa[mb][3], b0, b1);
-                    }
-                }
+                for (int w = 0; w < kAttnWarps; ++w) vm = fmaxf(vm, sm.wvmax[w]);
+                int ex = 0;
+                if (vm > 0.0f) (void)frexpf(vm, &ex);  // every weight p * v_scale <= vm < 2^ex
+                sm.wup = ldexpf(1.0f, 32 - ex);
+                sm.wdown = ldexpf(1.0f, ex - 32);
             }
-            if (tb + kTilePos < t1) cp_async_wait_all();
-            __syncthreads();  // next tile complete and visible; this tile's buffers free again
-            cur ^= 1;
-        }
-        // add the position groups and the three pieces through shared memory (the value tiles are free now)
-        float* red = reinterpret_cast<float*>(sm.kraw);  // [n_pq][rows][hd], over the key and value tiles
-        static_assert(sizeof(sm.kraw) + sizeof(sm.vraw) >= (size_t)kRowsUsed * 256 * sizeof(float) &&
-                      offsetof(Smem, vraw) == offsetof(Smem, kraw) + sizeof(sm.kraw), "reduction scratch");
-        if (pv_active) {
+            __syncthreads();
+            // ---- phase B: weights and P.V of the chunk ---------------------------------------------------------
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
-                const int r0 = mb * 16 + g, r1 = r0 + 8;
+                ones[mb][0] = ones[mb][1] = ones[mb][2] = ones[mb][3] = 0;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    // MMA e, column n = dim 32 dg + 4 n + e; this lane holds n = 2t and 2t + 1
-                    const int d0 = 32 * dg + 4 * (2 * t) + e, d1 = d0 + 4;
-                    if (r0 < kRowsUsed) { red[(pq * kRowsUsed + r0) * hd + d0] = acc[mb][e][0]; red[(pq * kRowsUsed + r0) * hd + d1] = acc[mb][e][1]; }
-                    if (r1 < kRowsUsed) { red[(pq * kRowsUsed + r1) * hd + d0] = acc[mb][e][2]; red[(pq * kRowsUsed + r1) * hd + d1] = acc[mb][e][3]; }
+                for (int e = 0; e < 4; ++e) acc[mb][e][0] = acc[mb][e][1] = acc[mb][e][2] = acc[mb][e][3] = 0;
+            }
+#pragma unroll
+            for (int e = 0; e < kRounds; ++e) psum[e] = 0.0f;
+            const float wup = sm.wup;
+            for (int ti = 0; ti < ctiles; ++ti, ++n) {
+                const int n_here = min(kTilePos, clen - ti * kTilePos);
+                uint8_t (*wd)[kWStride] = sm.wdig[ti & 1];
+                // weight digits of the tile: one (query vector, position) per thread and round, a warp covers 32
+                // positions of one vector.  Position r = 16 q + 4 i + t' goes to slot 16 q + 4 t' + i: the four
+                // positions that one lane feeds into an MMA lie in one word, and so do the rows it reads from V.
+#pragma unroll
+                for (int e = 0; e < kRounds; ++e) {
+                    const int it = tid + e * kAttnThreads;
+                    const int v = it / kTilePos, r = it % kTilePos;
+                    if (v < G) {  // warp-uniform
+                        const float s = r < n_here ? sm.sbuf[v][ti * kTilePos + r] : -INFINITY;
+                        const float pe = s != -INFINITY ? expf(__fsub_rn(s, sm.ml[0][v])) : 0.0f;
+                        psum[e] += pe;
+                        // weight of the value row: p * v_scale (the value bytes enter the MMA as integers)
+                        const uint32_t u = pe > 0.0f ? __float2uint_rn(__fmul_rn(__fmul_rn(pe, sm.vsc[ti * kTilePos + r]), wup)) : 0u;
+                        const int slot = (r & ~15) | ((r & 3) << 2) | ((r >> 2) & 3);
+                        wd[4 * v + 0][slot] = (uint8_t)(u >> 24);
+                        wd[4 * v + 1][slot] = (uint8_t)(u >> 16);
+                        wd[4 * v + 2][slot] = (uint8_t)(u >> 8);
+                        wd[4 * v + 3][slot] = (uint8_t)u;
+                    }
+                }
+                cp_async_wait<1>();
+                __syncthreads();  // tile n landed, its weight digits complete; everybody is done with tile n - 1
+                fetch(fc, (n + 2) % kStages);
+                advance(fc);
+                const uint8_t* vcol = sm.ring[n % kStages] + 32 * dg + 4 * g;
+                for (int ks = pq; 32 * ks < n_here; ks += n_pq) {
+                    uint32_t b0[4], b1[4];
+                    {
+                        const uint8_t* vp = vcol + (32 * ks + t) * rstride;
+                        transpose4(*reinterpret_cast<const uint32_t*>(vp), *reinterpret_cast<const uint32_t*>(vp + 4 * rstride),
+                                   *reinterpret_cast<const uint32_t*>(vp + 8 * rstride), *reinterpret_cast<const uint32_t*>(vp + 12 * rstride), b0);
+                        vp += 16 * rstride;
+                        transpose4(*reinterpret_cast<const uint32_t*>(vp), *reinterpret_cast<const uint32_t*>(vp + 4 * rstride),
+                                   *reinterpret_cast<const uint32_t*>(vp + 8 * rstride), *reinterpret_cast<const uint32_t*>(vp + 12 * rstride), b1);
+                    }
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb) {
+                        const uint8_t* w0 = &wd[16 * mb + g][32 * ks + 4 * t];
+                        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(w0);
+                        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(w0 + 8 * kWStride);
+                        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(w0 + 16);
+                        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(w0 + 8 * kWStride + 16);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) mma_u8u8(acc[mb][e], a0, a1, a2, a3, b0[e], b1[e]);
+                        mma_u8u8(ones[mb], a0, a1, a2, a3, 0x01010101u, 0x01010101u);  // sum of the digits: the "- 128" of the value bytes
+                    }
                 }
             }
-        }
-        __syncthreads();
-        for (int it = tid; it < G * hd; it += kAttnThreads) {
-            const int h = it / hd, dcol = it % hd;
-            float v = 0.0f;
-            for (int g2 = 0; g2 < n_pq; ++g2) {
-                const float* rr = red + (size_t)g2 * kRowsUsed * hd + dcol;
-                v = __fadd_rn(v, __fadd_rn(__fadd_rn(rr[h * hd], rr[(G + h) * hd]), rr[(2 * G + h) * hd]));
+            // ---- end of the chunk: digits together, "- 128" out, to f32, into the running output ----
+            // Row 16 mb + g (+ 8) = digit g % 4 of query vector 4 mb + g / 4 (+ 2); the four digits of a vector sit in
+            // four lanes that differ in bits 2 and 3 of the lane number.
+            {
+                const float wdown = sm.wdown;
+                const long long weight = 1ll << (8 * (3 - (g & 3)));
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow) {
+                        const int v = 4 * mb + 2 * hrow + (g >> 2);
+                        const int one = ones[mb][2 * hrow];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                            for (int cc = 0; cc < 2; ++cc) {
+                                long long x = (long long)(acc[mb][e][2 * hrow + cc] - 128 * one) * weight;
+                                x += shfl_xor_ll(x, 4);
+                                x += shfl_xor_ll(x, 8);
+                                // MMA e, column n = dim 32 dg + 4 n + e; this lane holds n = 2t and 2t + 1
+                                if ((g & 3) == 0 && v < G)
+                                    sm.part[(pq * G + v) * hd + 32 * dg + 4 * (2 * t + cc) + e] = __fmul_rn(__ll2float_rn(x), wdown);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < kRounds; ++e) {
+                    const float ws = warp_sum(psum[e]);
+                    if (lane == 0 && e < (G + 1) / 2) sm.wsum[warp][e] = ws;
+                }
             }
-            sm.opart[it] = v;
+            __syncthreads();
+            for (int it = tid; it < G * hd; it += kAttnThreads) {
+                const int v = it / hd;
+                float add = sm.part[it];
+                for (int g2 = 1; g2 < n_pq; ++g2) add = __fadd_rn(add, sm.part[g2 * G * hd + it]);
+                sm.opart[it] = fmaf(sm.opart[it], sm.corr[v], add);
+            }
+            if (tid < G) {
+                // round e of warp w covered query vector (32 w + 256 e) / 128 = w / 4 + 2 e
+                float ps = 0.0f;
+                for (int w = 0; w < kAttnWarps; ++w)
+                    if ((w >> 2) == (tid & 1)) ps = __fadd_rn(ps, sm.wsum[w][tid >> 1]);
+                sm.ml[1][tid] = fmaf(sm.ml[1][tid], sm.corr[tid], ps);
+            }
+            __syncthreads();
         }
     }
     // only now may the next kernel's CTAs move in: earlier they would take the registers and
@@ -471,7 +596,7 @@ __global__ void __launch_bounds__(kAttnThreads, QB == 1 ? 2 : 1) attn_kernel(Att
             float num = 0.0f, den = 0.0f;
 #pragma unroll
             for (int s2 = 0; s2 < kMaxCluster; ++s2) {
-                // a span without positions (maximum -inf) weighs nothing; what its output cells hold is undefined
+                // a span without positions (maximum -inf) weighs nothing
                 const bool live = ms[s2] != -INFINITY;
                 const float w = live ? expf(__fsub_rn(ms[s2], m)) : 0.0f;
                 den = fmaf(ls[s2], w, den);
@@ -507,8 +632,7 @@ __global__ void __launch_bounds__(128) kv_append_kernel(KvCacheView cache, const
     for (int c = lane; c < hd; c += 32) rowbuf[warp][c] = src[c];
     __syncwarp();
     const int64_t r = ((int64_t)b * n_kv + kvh) * cache.max_seq + p;
-    quant_row_warp(rowbuf[warp], hd, (which ? cache.v_q : cache.k_q) + r * hd, (which ? cache.v_s : cache.k_s) + r, nullptr,
-                   nullptr, lane);
+    quant_row_warp(rowbuf[warp], hd, (which ? cache.v_q : cache.k_q) + r * hd, (which ? cache.v_s : cache.k_s) + r, nullptr, lane);
 }
 
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, int max_seq, int half,
@@ -553,12 +677,12 @@ __global__ void __launch_bounds__(128) kv_append_rows_kernel(KvCacheView cache, 
     }
     __syncwarp();
     const int64_t r = ((int64_t)b * n_kv + kvh) * cache.max_seq + p;
-    quant_row_warp(rowbuf[warp], hd, (which ? cache.v_q : cache.k_q) + r * hd, (which ? cache.v_s : cache.k_s) + r, nullptr,
-                   nullptr, lane);
+    quant_row_warp(rowbuf[warp], hd, (which ? cache.v_q : cache.k_q) + r * hd, (which ? cache.v_s : cache.k_s) + r, nullptr, lane);
 }
 
 constexpr size_t kHalfSm = 116 * 1024;
-static_assert(sizeof(AttnSmemT<kMaxRep>) <= 110 * 1024, "two CTAs of the decode kernel must fit one SM");
+static_assert(sizeof(AttnSmemT<4>) <= 112 * 1024, "two CTAs of the decode kernel (up to 4 query heads per KV head) must fit one SM");
+static_assert(sizeof(AttnSmemT<kMaxRep>) <= kHalfSm, "decode kernel: shared memory");
 constexpr int kPrefillVectors = 16;  // query vectors per CTA of the prefill kernel: 16 / NREP positions x NREP heads
 
 // How many clusters of each size can be resident at once (a CTA then takes a whole SM): a cluster's CTAs
