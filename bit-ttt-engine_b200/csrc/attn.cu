@@ -17,10 +17,11 @@
 //     a rotated query value q = S * Q / 2^27 with S = the power of two >= max|q| of its vector and
 //     |Q| <= 2^27 (four signed 7-bit digits); a weight p * v_scale = B * U / 2^32 with B = the power
 //     of two above the largest value-row scale of the chunk and U < 2^32 (four unsigned bytes).
-// The digit sums are put together in 64-bit integers and rounded to f32 once, so a score is the
-// correctly rounded product of the key bytes with a query that is exact to 2^-28 of its vector's
-// largest component, and the weights are exact to 2^-33 of the chunk's bound.  Softmax runs in f32.
-// The result is within about 1e-6 relative of the f32 value of layers/attention.rs:202-217.
+// Every digit product is an exact integer.  The four digit sums of a score are joined in f32 (three
+// roundings, no cancellation: each digit weighs 1/128 of the one before), those of an output value in a
+// 64-bit integer that is rounded to f32 once.  A query is exact to 2^-28 of its vector's largest
+// component, a weight to 2^-33 of the chunk's bound.  Softmax runs in f32.  The result is within about
+// 1e-6 relative of the f32 value of layers/attention.rs:202-217.
 //
 // Order of work.  The positions of a CTA are taken in chunks of up to kChunk positions.  Phase A of a
 // chunk streams its KEY tiles (128 positions each) and leaves the f32 scores in shared memory; the
@@ -36,6 +37,8 @@
 // cluster barrier every CTA of the cluster finishes a slice of the output columns, reading the
 // partials of all spans with ld.shared::cluster.  No global scratch, no second launch.
 #include <stddef.h>
+
+#include <mutex>
 
 #include "bt_model.cuh"
 #include "bt_ptx.cuh"
@@ -107,12 +110,12 @@ struct AttnSmemT {
     alignas(16) uint8_t wdig[2][kRows16][kWStride];         // weight digits of a tile, [row][position slot], two tiles
     alignas(16) float opart[G * kMaxHd];                    // this span's unnormalised output [query vector][dim] (read by the cluster)
     alignas(16) float part[2 * G * kMaxHd];                 // a chunk's P.V result per position group, [group][vector][dim], before it meets opart
-    long long icorr[G];                                     // 128 * sum_d Q[v][d]: the "- 128" of the key bytes
+    int dcorr[kCols8];                                      // 128 * sum_d digit[column][d]: the "- 128" of the key bytes
     float qscale[G];                                        // S / 2^27 of a query vector
     float ml[2][G];                                         // this span's running maximum / denominator (read by the cluster)
     float corr[G];
     float wmax[kAttnWarps][G];
-    float wsum[kAttnWarps][(G + 1) / 2];
+    float wsum[kAttnWarps][(G + 7) / 8];
     float wvmax[kAttnWarps];
     float wup, wdown;                                       // weight scale of the chunk: 2^32 / B and B / 2^32
     float knew[kMaxHd], vnew[kMaxHd];
@@ -175,7 +178,8 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t ran
 // head) form a cluster.  QB > 1: prefill, a.q_rows new tokens per sequence whose K/V rows are already in the
 // cache; blockIdx.y = block of QB consecutive query positions, which sees the keys up to its own position
 // (causal rule of layers/attention.rs:249-262: key j is visible to query i when j <= i + past).
-template <int NREP, int QB>
+// HD: head_dim fixed at compile time (128, 64), or 0 = any multiple of 32 up to 128 read from the arguments.
+template <int NREP, int QB, int HD>
 __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_kernel(AttnArgs a) {
     constexpr int G = NREP * QB;
     using Smem = AttnSmemT<G>;
@@ -184,8 +188,8 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
     constexpr int kChunk = Smem::kChunk;
     constexpr int NB = Smem::kCols8 / 8;           // 8-column blocks of the score MMAs (two query vectors each)
     constexpr int MB = Smem::kRows16 / 16;         // 16-row blocks of the P.V MMAs (four query vectors each)
-    constexpr int kRounds = (G * kTilePos + kAttnThreads - 1) / kAttnThreads;  // (vector, position) items per thread and tile
-    const int hd = a.head_dim, half = hd >> 1;
+    constexpr int kRounds = (G + kAttnWarps - 1) / kAttnWarps;  // weight rounds per tile: a warp turns one query vector's 128 scores into digits
+    const int hd = HD > 0 ? HD : a.head_dim, half = hd >> 1;
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int split = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -249,6 +253,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
     // weight rows and query columns beyond the ones in use stay zero
     for (int i = tid; i < (int)(sizeof(sm.wdig) / 4); i += kAttnThreads) reinterpret_cast<uint32_t*>(sm.wdig)[i] = 0u;
     for (int i = tid; i < (int)(sizeof(sm.qdig) / 4); i += kAttnThreads) reinterpret_cast<uint32_t*>(sm.qdig)[i] = 0u;
+    if (tid < Smem::kCols8) sm.dcorr[tid] = 0;
     for (int i = tid; i < G * kMaxHd; i += kAttnThreads) sm.opart[i] = 0.0f;
     ptx::pdl_wait();
     if (QB > 1 && !empty) {  // prefill: the new rows come from the kernel just before
@@ -303,10 +308,9 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
             int ex = 0;
             if (amax > 0.0f) (void)frexpf(amax, &ex);   // amax = m * 2^ex, m in [0.5, 1)
             const float up = ldexpf(1.0f, 27 - ex);
-            long long qsum = 0;
+            int dsum[4] = {0, 0, 0, 0};
             for (int c = lane; c < hd; c += 32) {
                 int Q = __float2int_rn(__fmul_rn(sm.sbuf[v][c], up));
-                qsum += Q;
                 const int d3 = ((Q + 64) & 127) - 64; Q = (Q - d3) >> 7;
                 const int d2 = ((Q + 64) & 127) - 64; Q = (Q - d2) >> 7;
                 const int d1 = ((Q + 64) & 127) - 64; Q = (Q - d1) >> 7;
@@ -314,13 +318,15 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 sm.qdig[4 * v + 1][c] = (int8_t)d1;
                 sm.qdig[4 * v + 2][c] = (int8_t)d2;
                 sm.qdig[4 * v + 3][c] = (int8_t)d3;
+                dsum[0] += Q; dsum[1] += d1; dsum[2] += d2; dsum[3] += d3;
             }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) qsum += shfl_xor_ll(qsum, o);
-            if (lane == 0) {
-                sm.icorr[v] = 128ll * qsum;
-                sm.qscale[v] = ldexpf(1.0f, ex - 27);
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) dsum[j] += __shfl_xor_sync(0xffffffffu, dsum[j], o);
+                if (lane == 0) sm.dcorr[4 * v + j] = 128 * dsum[j];
             }
+            if (lane == 0) sm.qscale[v] = ldexpf(1.0f, ex - 27);
         }
     }
     if (owner) {
@@ -345,8 +351,16 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
     const int dg = warp % n_dg, pq = warp / n_dg;
     int acc[MB][4][4], ones[MB][4];
     float psum[kRounds], mx[NB];
+    int dc[NB][2];  // the "- 128" terms of this lane's two columns of every block
+    float qs[NB];   // and the scale of the query vector they belong to
 
     if (!empty) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            dc[nb][0] = sm.dcorr[8 * nb + 2 * t];
+            dc[nb][1] = sm.dcorr[8 * nb + 2 * t + 1];
+            qs[nb] = 2 * nb + (t >> 1) < G ? sm.qscale[2 * nb + (t >> 1)] : 0.0f;
+        }
         int n = 0;  // tiles done so far: tile n sits in ring[n % kStages]
         for (int chunk0 = t0; chunk0 < t1; chunk0 += kChunk) {
             const int clen = min(kChunk, t1 - chunk0);
@@ -354,6 +368,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) mx[nb] = -INFINITY;
             // the chunk's value-row scales, needed between the phases: requested now, used then
+            // (thread -> positions tid, tid + 256, ...; they go to shared memory in the slot order of the weights)
             float vs_reg[kChunk / kAttnThreads];
 #pragma unroll
             for (int i = 0; i < kChunk / kAttnThreads; ++i)
@@ -374,39 +389,41 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                     for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0;
                     const uint8_t* krow0 = kraw + (16 * warp + g) * rstride + 8 * t;
                     const uint8_t* krow1 = krow0 + 8 * rstride;
-                    for (int j = 0; j < (hd >> 5); ++j) {
-                        const uint2 w0 = *reinterpret_cast<const uint2*>(krow0 + 32 * j);
-                        const uint2 w1 = *reinterpret_cast<const uint2*>(krow1 + 32 * j);
 #pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) {
-                            const uint2 q8 = *reinterpret_cast<const uint2*>(&sm.qdig[nb * 8 + g][32 * j + 8 * t]);
-                            mma_u8s8(c[nb], w0.x, w1.x, w0.y, w1.y, q8.x, q8.y);
+                    for (int j = 0; j < kMaxHd / 32; ++j) {
+                        if (32 * j < hd) {
+                            const uint2 w0 = *reinterpret_cast<const uint2*>(krow0 + 32 * j);
+                            const uint2 w1 = *reinterpret_cast<const uint2*>(krow1 + 32 * j);
+#pragma unroll
+                            for (int nb = 0; nb < NB; ++nb) {
+                                const uint2 q8 = *reinterpret_cast<const uint2*>(&sm.qdig[nb * 8 + g][32 * j + 8 * t]);
+                                mma_u8s8(c[nb], w0.x, w1.x, w0.y, w1.y, q8.x, q8.y);
+                            }
                         }
                     }
                     // Lane t holds columns 2t, 2t + 1 of block nb: digits (0, 1) (t even) or (2, 3) (t odd) of query
-                    // vector 2 nb + t / 2, for rows g and g + 8.  The lane pair swaps halves: the even lane finishes
-                    // row g, the odd lane row g + 8.
+                    // vector 2 nb + t / 2, for rows g and g + 8.  Each lane joins its two digits, the lane pair swaps
+                    // halves: the even lane finishes row g, the odd lane row g + 8.  Scores go to shared memory in the
+                    // slot order of the weights (position 16 q + 4 i + t' -> slot 16 q + 4 t' + i).
+                    const bool odd = t & 1;
+                    const int r = 16 * warp + g + (odd ? 8 : 0);
+                    const int slot = ti * kTilePos + 16 * warp + 4 * (g & 3) + (g >> 2) + (odd ? 2 : 0);
+                    const float ksr = r < n_here ? sm.sc[n % kStages][r] : 0.0f;
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) {
                         const int v = 2 * nb + (t >> 1);
-                        const bool odd = t & 1;
-                        // even: own = c0 * 2^21 + c1 * 2^14 (row g), send the same of row g + 8;
-                        // odd : own = c2 * 2^7 + c3 (row g + 8), send the same of row g
-                        const long long own = odd ? (long long)(c[nb][2] * 128 + c[nb][3])
-                                                  : (long long)c[nb][0] * 2097152ll + (long long)c[nb][1] * 16384ll;
-                        const long long send = odd ? (long long)(c[nb][0] * 128 + c[nb][1])
-                                                   : (long long)c[nb][2] * 2097152ll + (long long)c[nb][3] * 16384ll;
-                        const long long got = shfl_xor_ll(send, 1);
+                        const float x_lo = fmaf((float)(c[nb][0] - dc[nb][0]), 128.0f, (float)(c[nb][1] - dc[nb][1]));  // row g
+                        const float x_hi = fmaf((float)(c[nb][2] - dc[nb][0]), 128.0f, (float)(c[nb][3] - dc[nb][1]));  // row g + 8
+                        const float got = __shfl_xor_sync(0xffffffffu, odd ? x_lo : x_hi, 1);
                         if (v < G) {
-                            const int r = 16 * warp + g + (odd ? 8 : 0);
                             // prefill: query vector v sits at position p + q0 + v / NREP and sees the keys up to there
                             const bool seen = QB == 1 || chunk0 + ti * kTilePos + r <= p + q0 + v / NREP;
                             float s = -INFINITY;
                             if (r < n_here && seen) {
-                                const float dot = __fmul_rn(__ll2float_rn(own + got - sm.icorr[v]), sm.qscale[v]);
-                                s = __fmul_rn(__fmul_rn(dot, sm.sc[n % kStages][r]), a.scaling);  // (attention.rs:202)
+                                const float dot = __fmul_rn(odd ? fmaf(got, 16384.0f, x_hi) : fmaf(x_lo, 16384.0f, got), qs[nb]);
+                                s = __fmul_rn(__fmul_rn(dot, ksr), a.scaling);  // (attention.rs:202)
                             }
-                            sm.sbuf[v][ti * kTilePos + r] = s;
+                            sm.sbuf[v][slot] = s;
                             mx[nb] = fmaxf(mx[nb], s);
                         }
                     }
@@ -426,7 +443,8 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 float vm = 0.0f;
 #pragma unroll
                 for (int i = 0; i < kChunk / kAttnThreads; ++i) {
-                    sm.vsc[tid + i * kAttnThreads] = vs_reg[i];
+                    const int r = tid + i * kAttnThreads;  // position in the chunk -> slot: bits 0-1 and 2-3 swapped
+                    sm.vsc[(r & ~15) | ((r & 3) << 2) | ((r >> 2) & 3)] = vs_reg[i];
                     vm = fmaxf(vm, vs_reg[i]);
                 }
                 vm = warp_max(vm);
@@ -465,24 +483,30 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
             for (int ti = 0; ti < ctiles; ++ti, ++n) {
                 const int n_here = min(kTilePos, clen - ti * kTilePos);
                 uint8_t (*wd)[kWStride] = sm.wdig[ti & 1];
-                // weight digits of the tile: one (query vector, position) per thread and round, a warp covers 32
-                // positions of one vector.  Position r = 16 q + 4 i + t' goes to slot 16 q + 4 t' + i: the four
-                // positions that one lane feeds into an MMA lie in one word, and so do the rows it reads from V.
+                // weight digits of the tile: a warp takes one query vector per round, lane L the slots 4 L .. 4 L + 3 =
+                // positions 16 (L / 4) + 4 i + L % 4, i = 0..3: the four positions that one lane feeds into an MMA
+                // lie in one word, and so do the rows it reads from V.
 #pragma unroll
                 for (int e = 0; e < kRounds; ++e) {
-                    const int it = tid + e * kAttnThreads;
-                    const int v = it / kTilePos, r = it % kTilePos;
+                    const int v = warp + e * kAttnWarps;
                     if (v < G) {  // warp-uniform
-                        const float s = r < n_here ? sm.sbuf[v][ti * kTilePos + r] : -INFINITY;
-                        const float pe = s != -INFINITY ? expf(__fsub_rn(s, sm.ml[0][v])) : 0.0f;
-                        psum[e] += pe;
-                        // weight of the value row: p * v_scale (the value bytes enter the MMA as integers)
-                        const uint32_t u = pe > 0.0f ? __float2uint_rn(__fmul_rn(__fmul_rn(pe, sm.vsc[ti * kTilePos + r]), wup)) : 0u;
-                        const int slot = (r & ~15) | ((r & 3) << 2) | ((r >> 2) & 3);
-                        wd[4 * v + 0][slot] = (uint8_t)(u >> 24);
-                        wd[4 * v + 1][slot] = (uint8_t)(u >> 16);
-                        wd[4 * v + 2][slot] = (uint8_t)(u >> 8);
-                        wd[4 * v + 3][slot] = (uint8_t)u;
+                        const float4 s4 = *reinterpret_cast<const float4*>(&sm.sbuf[v][ti * kTilePos + 4 * lane]);
+                        const float4 v4 = *reinterpret_cast<const float4*>(&sm.vsc[ti * kTilePos + 4 * lane]);
+                        const float m_new = sm.ml[0][v];
+                        const int r0 = 16 * (lane >> 2) + (lane & 3);
+                        const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+                        uint32_t u[4], dig[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const bool live = r0 + 4 * i < n_here && sv[i] != -INFINITY;  // (beyond the tile the buffer holds anything)
+                            const float pe = live ? expf(__fsub_rn(sv[i], m_new)) : 0.0f;
+                            psum[e] += pe;
+                            // weight of the value row: p * v_scale (the value bytes enter the MMA as integers)
+                            u[i] = live ? __float2uint_rn(__fmul_rn(__fmul_rn(pe, vv[i]), wup)) : 0u;
+                        }
+                        transpose4(u[0], u[1], u[2], u[3], dig);  // dig[e] = byte e of the four weights; digit j = byte 3 - j
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint32_t*>(&wd[4 * v + j][4 * lane]) = dig[3 - j];
                     }
                 }
                 cp_async_wait<1>();
@@ -490,7 +514,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 fetch(fc, (n + 2) % kStages);
                 advance(fc);
                 const uint8_t* vcol = sm.ring[n % kStages] + 32 * dg + 4 * g;
-                for (int ks = pq; 32 * ks < n_here; ks += n_pq) {
+                for (int ks = pq; 32 * ks < n_here; ks += n_pq) {  // (head_dim 128: steps pq and pq + 2)
                     uint32_t b0[4], b1[4];
                     {
                         const uint8_t* vp = vcol + (32 * ks + t) * rstride;
@@ -542,7 +566,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
 #pragma unroll
                 for (int e = 0; e < kRounds; ++e) {
                     const float ws = warp_sum(psum[e]);
-                    if (lane == 0 && e < (G + 1) / 2) sm.wsum[warp][e] = ws;
+                    if (lane == 0) sm.wsum[warp][e] = ws;  // query vector warp + 8 e
                 }
             }
             __syncthreads();
@@ -552,13 +576,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 for (int g2 = 1; g2 < n_pq; ++g2) add = __fadd_rn(add, sm.part[g2 * G * hd + it]);
                 sm.opart[it] = fmaf(sm.opart[it], sm.corr[v], add);
             }
-            if (tid < G) {
-                // round e of warp w covered query vector (32 w + 256 e) / 128 = w / 4 + 2 e
-                float ps = 0.0f;
-                for (int w = 0; w < kAttnWarps; ++w)
-                    if ((w >> 2) == (tid & 1)) ps = __fadd_rn(ps, sm.wsum[w][tid >> 1]);
-                sm.ml[1][tid] = fmaf(sm.ml[1][tid], sm.corr[tid], ps);
-            }
+            if (tid < G) sm.ml[1][tid] = fmaf(sm.ml[1][tid], sm.corr[tid], sm.wsum[tid % kAttnWarps][tid / kAttnWarps]);
             __syncthreads();
         }
     }
@@ -693,16 +711,19 @@ struct ClusterTable {
     int active[kMaxCluster + 1] = {0};  // active[s] = resident clusters of s CTAs (0: size unusable)
 };
 
-template <int NREP>
+template <int NREP, int HD>
 cudaError_t configure_rep(const ClusterTable** out) {
     static ClusterTable table;  // per process; every device of a process is the same GPU model
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
     if (!table.ready) {
-        cudaError_t e = cudaFuncSetAttribute(attn_kernel<NREP, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHalfSm);
+        auto* decode = attn_kernel<NREP, 1, HD>;
+        auto* prefill = attn_kernel<NREP, kPrefillVectors / NREP, HD>;
+        cudaError_t e = cudaFuncSetAttribute(decode, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHalfSm);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(attn_kernel<NREP, kPrefillVectors / NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)sizeof(AttnSmemT<kPrefillVectors>));
+        e = cudaFuncSetAttribute(prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnSmemT<kPrefillVectors>));
         if (e != cudaSuccess) return e;
-        const bool big = cudaFuncSetAttribute(attn_kernel<NREP, 1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        const bool big = cudaFuncSetAttribute(decode, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         for (int s = 1; s <= kMaxCluster; ++s) {
             if (s > 8 && !big) break;
             cudaLaunchConfig_t cfg = {};
@@ -715,7 +736,7 @@ cudaError_t configure_rep(const ClusterTable** out) {
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, attn_kernel<NREP, 1>, &cfg) == cudaSuccess) table.active[s] = n;
+            if (cudaOccupancyMaxActiveClusters(&n, decode, &cfg) == cudaSuccess) table.active[s] = n;
         }
         cudaGetLastError();  // a refused attribute or query only rules a cluster size out
         if (table.active[1] < 1) table.active[1] = 1;
@@ -725,10 +746,10 @@ cudaError_t configure_rep(const ClusterTable** out) {
     return cudaSuccess;
 }
 
-template <int NREP>
+template <int NREP, int HD>
 cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
     const ClusterTable* table = nullptr;
-    cudaError_t e = configure_rep<NREP>(&table);
+    cudaError_t e = configure_rep<NREP, HD>(&table);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kAttnThreads);
@@ -747,7 +768,7 @@ cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
         cfg.dynamicSmemBytes = sizeof(AttnSmemT<kPrefillVectors>);
         attr[0].val.clusterDim.y = 1;
         cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, attn_kernel<NREP, QB>, a);
+        return cudaLaunchKernelEx(&cfg, attn_kernel<NREP, QB, HD>, a);
     }
     if (a.splits < 1 || a.splits > kMaxCluster || table->active[a.splits] < 1) return cudaErrorInvalidValue;
     cfg.gridDim = dim3(a.batch * a.n_kv, a.splits);
@@ -756,17 +777,25 @@ cudaError_t launch_attn_rep(const AttnArgs& a, cudaStream_t stream) {
     cfg.dynamicSmemBytes = ((int64_t)a.batch * a.n_kv * a.splits <= a.sm_count) ? kHalfSm : sizeof(AttnSmemT<NREP>);
     attr[0].val.clusterDim.y = (unsigned)a.splits;
     cfg.numAttrs = a.pdl ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, attn_kernel<NREP, 1>, a);
+    return cudaLaunchKernelEx(&cfg, attn_kernel<NREP, 1, HD>, a);
 }
 
+template <int NREP>
+cudaError_t launch_attn_hd(const AttnArgs& a, cudaStream_t stream) {
+    if (a.head_dim == 128) return launch_attn_rep<NREP, 128>(a, stream);
+    if (a.head_dim == 64) return launch_attn_rep<NREP, 64>(a, stream);
+    return launch_attn_rep<NREP, 0>(a, stream);
+}
+
+// The cluster limits do not depend on the head size (the query asks for a whole SM per CTA): one table per `rep`.
 const ClusterTable* attn_cluster_table(int rep) {
     const ClusterTable* t = nullptr;
     cudaError_t e = cudaErrorInvalidValue;
     switch (rep) {
-        case 1: e = configure_rep<1>(&t); break;
-        case 2: e = configure_rep<2>(&t); break;
-        case 4: e = configure_rep<4>(&t); break;
-        case 8: e = configure_rep<8>(&t); break;
+        case 1: e = configure_rep<1, 128>(&t); break;
+        case 2: e = configure_rep<2, 128>(&t); break;
+        case 4: e = configure_rep<4, 128>(&t); break;
+        case 8: e = configure_rep<8, 128>(&t); break;
         default: break;
     }
     return e == cudaSuccess ? t : nullptr;
@@ -810,10 +839,10 @@ cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream) {
         a.span % 32 != 0 || (int64_t)a.span * a.splits < a.cache.max_seq || a.q_rows < 1)
         return cudaErrorInvalidValue;
     switch (rep) {
-        case 1: return launch_attn_rep<1>(a, stream);
-        case 2: return launch_attn_rep<2>(a, stream);
-        case 4: return launch_attn_rep<4>(a, stream);
-        case 8: return launch_attn_rep<8>(a, stream);
+        case 1: return launch_attn_hd<1>(a, stream);
+        case 2: return launch_attn_hd<2>(a, stream);
+        case 4: return launch_attn_hd<4>(a, stream);
+        case 8: return launch_attn_hd<8>(a, stream);
         default: return cudaErrorInvalidValue;
     }
 }
