@@ -28,6 +28,7 @@
 #include <mutex>
 
 #include "bt_common.cuh"
+#include "bt_model.cuh"
 #include "bt_ptx.cuh"
 
 namespace bt {
@@ -542,9 +543,10 @@ cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride
         e = nt == 64 ? launch_pdl(act_quant_tc_kernel<64, __nv_bfloat16>, dim3(padded), dim3(256), 0, stream, true, xb, x_stride, k, kts, (int)m, qtc, sx, qsum)
                      : launch_pdl(act_quant_tc_kernel<128, __nv_bfloat16>, dim3(padded), dim3(256), 0, stream, true, xb, x_stride, k, kts, (int)m, qtc, sx, qsum);
     } else {
-        const float* xf = reinterpret_cast<const float*>(x);
-        e = nt == 64 ? launch_pdl(act_quant_tc_kernel<64, float>, dim3(padded), dim3(256), 0, stream, true, xf, x_stride, k, kts, (int)m, qtc, sx, qsum)
-                     : launch_pdl(act_quant_tc_kernel<128, float>, dim3(padded), dim3(256), 0, stream, true, xf, x_stride, k, kts, (int)m, qtc, sx, qsum);
+        // f32 rows: the row kernel of the decode step (identity transform); rows of a partly filled token block
+        // keep whatever they held, their output columns are never stored
+        e = launch_row_quant(PRE_NONE, reinterpret_cast<const float*>(x), x_stride, nullptr, 0.0f, (int)m, k, nullptr, 0, sx, qsum,
+                             nullptr, stream, qtc, kts);
     }
     if (e != cudaSuccess) return e;
     for (int b = 0; b < lin.w.n_bases; ++b) {

@@ -101,15 +101,25 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const __nv_bflo
 //                gate|up projection: x[16 j + r] = gate[8 j + r], x[16 j + 8 + r] = up[8 j + r])  (layers/swiglu.rs:31-33)
 // then s = max|v|/127, q = clamp(round(v * (127/max|v|))), sum_k q.  `v_out` (optional) receives v.
 // ---------------------------------------------------------------------------------------
+// Four consecutive floats; `vec` = the address is 16-byte aligned (uniform over the block).
+__device__ __forceinline__ float4 load4(const float* p, bool vec) {
+    if (vec) return *reinterpret_cast<const float4*>(p);
+    return make_float4(p[0], p[1], p[2], p[3]);
+}
+
+// k must be a multiple of 4 (the packed weight layouts require it anyway).  A thread works on groups of four
+// consecutive values; in the tensor-core layout these are the four residues of one k' (see gemm_tc_act_offset),
+// which are first laid out in shared memory in the order of that layout's 16-byte pieces and then copied out a
+// piece per thread.
 template <int PRE>
-__global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict__ x, int64_t x_stride,
-                                                        const float* __restrict__ w, float eps, int k,
-                                                        int8_t* __restrict__ q, int64_t q_stride,
-                                                        float* __restrict__ s_out,
-                                                        int32_t* __restrict__ qsum_out,
-                                                        float* __restrict__ v_out, int8_t* __restrict__ qtc,
-                                                        int tc_nt, int k_tiles) {
-    extern __shared__ float row[];
+__global__ void __launch_bounds__(1024) row_quant_kernel(const float* __restrict__ x, int64_t x_stride,
+                                                         const float* __restrict__ w, float eps, int k,
+                                                         int8_t* __restrict__ q, int64_t q_stride,
+                                                         float* __restrict__ s_out,
+                                                         int32_t* __restrict__ qsum_out,
+                                                         float* __restrict__ v_out, int8_t* __restrict__ qtc,
+                                                         int tc_nt, int k_tiles) {
+    extern __shared__ __align__(16) float row[];  // k floats, then k_tiles * 256 staged bytes (tensor-core layout only)
     __shared__ float red_f[32];
     __shared__ double red_d[32];
     __shared__ int red_i[32];
@@ -117,70 +127,92 @@ __global__ void __launch_bounds__(512) row_quant_kernel(const float* __restrict_
     ptx::pdl_launch_dependents();  // a product launched behind this kernel may fetch its weights meanwhile
     const int b = blockIdx.x;
     const float* xr = x + (int64_t)b * x_stride;
+    const bool xvec = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
+    const bool wvec = PRE == PRE_RMSNORM && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+    const int groups = k >> 2;
     float amax = 0.0f;
     if (PRE == PRE_RMSNORM) {
         // sum of squares in f64, rounded once: reproducible against the CPU restatement
         double ss = 0.0;
-        for (int c = threadIdx.x; c < k; c += blockDim.x) {
-            const float v = xr[c];
-            row[c] = v;
-            ss = fma((double)v, (double)v, ss);
+        for (int gi = threadIdx.x; gi < groups; gi += blockDim.x) {
+            const float4 v = load4(xr + 4 * gi, xvec);
+            *reinterpret_cast<float4*>(row + 4 * gi) = v;
+            ss = fma((double)v.x, (double)v.x, ss);
+            ss = fma((double)v.y, (double)v.y, ss);
+            ss = fma((double)v.z, (double)v.z, ss);
+            ss = fma((double)v.w, (double)v.w, ss);
         }
         ss = block_sum_d(ss, red_d);
         const float denom = sqrtf(__fadd_rn((float)(ss / (double)k), eps));
-        for (int c = threadIdx.x; c < k; c += blockDim.x) {
-            const float v = __fmul_rn(__fdiv_rn(row[c], denom), w[c]);
-            row[c] = v;
-            amax = fmaxf(amax, fabsf(v));
+        for (int gi = threadIdx.x; gi < groups; gi += blockDim.x) {
+            float4 v = *reinterpret_cast<const float4*>(row + 4 * gi);  // written by this same thread
+            const float4 ww = load4(w + 4 * gi, wvec);
+            v.x = __fmul_rn(__fdiv_rn(v.x, denom), ww.x);
+            v.y = __fmul_rn(__fdiv_rn(v.y, denom), ww.y);
+            v.z = __fmul_rn(__fdiv_rn(v.z, denom), ww.z);
+            v.w = __fmul_rn(__fdiv_rn(v.w, denom), ww.w);
+            *reinterpret_cast<float4*>(row + 4 * gi) = v;
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
     } else if (PRE == PRE_SWIGLU) {
-        for (int c = threadIdx.x; c < k; c += blockDim.x) {
-            const float g = xr[16 * (c >> 3) + (c & 7)], u = xr[16 * (c >> 3) + 8 + (c & 7)];
-            const float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
-            row[c] = v;
-            amax = fmaxf(amax, fabsf(v));
+        for (int gi = threadIdx.x; gi < groups; gi += blockDim.x) {
+            const int c = 4 * gi;  // outputs c .. c + 3: gate at x[16 (c / 8) + c % 8 ..], up 8 further
+            const float4 g4 = load4(xr + 16 * (c >> 3) + (c & 7), xvec), u4 = load4(xr + 16 * (c >> 3) + 8 + (c & 7), xvec);
+            float4 v;
+            v.x = __fmul_rn(__fdiv_rn(g4.x, __fadd_rn(1.0f, expf(-g4.x))), u4.x);
+            v.y = __fmul_rn(__fdiv_rn(g4.y, __fadd_rn(1.0f, expf(-g4.y))), u4.y);
+            v.z = __fmul_rn(__fdiv_rn(g4.z, __fadd_rn(1.0f, expf(-g4.z))), u4.z);
+            v.w = __fmul_rn(__fdiv_rn(g4.w, __fadd_rn(1.0f, expf(-g4.w))), u4.w);
+            *reinterpret_cast<float4*>(row + 4 * gi) = v;
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
     } else {
-        for (int c = threadIdx.x; c < k; c += blockDim.x) {
-            const float v = xr[c];
-            row[c] = v;
-            amax = fmaxf(amax, fabsf(v));
+        for (int gi = threadIdx.x; gi < groups; gi += blockDim.x) {
+            const float4 v = load4(xr + 4 * gi, xvec);
+            *reinterpret_cast<float4*>(row + 4 * gi) = v;
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
     }
-    amax = block_max(amax, red_f);  // also orders the row[] writes before the reads below
+    amax = block_max(amax, red_f);
     const float s = __fdiv_rn(amax, 127.0f);
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     int local = 0;
-    if (qtc) {
-        // straight into the tensor-core product's activation layout (gemm_tc_act_offset)
-        const int tb = b / tc_nt, tin = b % tc_nt;
-        int8_t* blk = qtc + (int64_t)tb * k_tiles * (4 * tc_nt * 64);
-        for (int c = threadIdx.x; c < k_tiles * kTileK; c += blockDim.x) {
-            int v = 0;
-            if (c < k && amax > 0.0f) v = max(-127, min(127, ptx::round_half_away(__fmul_rn(row[c], inv))));
-            local += v;
-            blk[gemm_tc_act_offset(c, tin, tc_nt)] = (int8_t)v;
+    uint8_t* stage = reinterpret_cast<uint8_t*>(row + k);
+    int8_t* qr = q ? q + (int64_t)b * q_stride : nullptr;
+    const int groups_pad = qtc ? k_tiles * (kTileK / 4) : (int)(q_stride >> 2);
+    for (int gi = threadIdx.x; gi < groups_pad; gi += blockDim.x) {
+        int v[4] = {0, 0, 0, 0};
+        if (gi < groups && amax > 0.0f) {
+            const float4 f = *reinterpret_cast<const float4*>(row + 4 * gi);  // this thread's own values again
+            v[0] = max(-127, min(127, ptx::round_half_away(__fmul_rn(f.x, inv))));
+            v[1] = max(-127, min(127, ptx::round_half_away(__fmul_rn(f.y, inv))));
+            v[2] = max(-127, min(127, ptx::round_half_away(__fmul_rn(f.z, inv))));
+            v[3] = max(-127, min(127, ptx::round_half_away(__fmul_rn(f.w, inv))));
         }
-    }
-    int8_t* qr = q + (int64_t)b * q_stride;
-    for (int c = threadIdx.x * 4; q && c < q_stride; c += blockDim.x * 4) {
-        uint32_t packed = 0;
+        local += v[0] + v[1] + v[2] + v[3];
+        if (qtc) {
+            // residue r of k' = gi % 64 in k-tile gi / 64: staged at [k-tile][residue][k']
+            const int kt = gi >> 6, kp = gi & 63;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int v = 0;
-            if (c + j < k && amax > 0.0f) {
-                float r = roundf(__fmul_rn(row[c + j], inv));
-                r = fminf(fmaxf(r, -127.0f), 127.0f);
-                v = (int)r;
-            }
-            local += v;
-            packed |= (uint32_t)(v & 0xff) << (8 * j);
+            for (int r = 0; r < 4; ++r) stage[(kt * 4 + r) * 64 + kp] = (uint8_t)v[r];
         }
-        *reinterpret_cast<uint32_t*>(qr + c) = packed;
+        if (qr)
+            *reinterpret_cast<uint32_t*>(qr + 4 * gi) = (uint32_t)(v[0] & 0xff) | ((uint32_t)(v[1] & 0xff) << 8) |
+                                                        ((uint32_t)(v[2] & 0xff) << 16) | ((uint32_t)(v[3] & 0xff) << 24);
     }
     if (v_out)
-        for (int c = threadIdx.x; c < k; c += blockDim.x) v_out[(int64_t)b * k + c] = row[c];
-    const int total = block_sum_i(local, red_i);
+        for (int gi = threadIdx.x; gi < groups; gi += blockDim.x)
+            *reinterpret_cast<float4*>(v_out + (int64_t)b * k + 4 * gi) = *reinterpret_cast<const float4*>(row + 4 * gi);
+    const int total = block_sum_i(local, red_i);  // (its barriers also complete the staged bytes)
+    if (qtc) {
+        // 16-byte pieces [k-tile][residue][k' / 16] -> their places in the token block (gemm_tc_act_offset)
+        const int tb = b / tc_nt, tin = b % tc_nt;
+        int8_t* blk = qtc + (int64_t)tb * k_tiles * (4 * tc_nt * 64) + (tin >> 3) * 512 + (tin & 7) * 16;
+        for (int pid = threadIdx.x; pid < k_tiles * 16; pid += blockDim.x) {
+            const int kc = pid & 3, kr = pid >> 2;  // kr = k-tile * 4 + residue
+            *reinterpret_cast<uint4*>(blk + (int64_t)kr * (tc_nt * 64) + kc * 128) = *reinterpret_cast<const uint4*>(stage + pid * 16);
+        }
+    }
     if (threadIdx.x == 0) {
         s_out[b] = s;
         qsum_out[b] = total;
@@ -388,16 +420,17 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
                              int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
                              float* v_out, cudaStream_t stream, int8_t* qtc, int k_tiles) {
     const int tc_nt = batch <= 64 ? 64 : 128;
-    const size_t smem = (size_t)k * sizeof(float);
-    const int threads = k >= 4096 ? 512 : 256;
+    if (k % 4 != 0 || (q && q_stride % 4 != 0)) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)k * sizeof(float) + (qtc ? (size_t)k_tiles * kTileK : 0);
+    const int threads = k >= 4096 ? 1024 : (k >= 2048 ? 512 : 256);
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(row_quant_kernel<PRE_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        cudaFuncSetAttribute(row_quant_kernel<PRE_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        cudaFuncSetAttribute(row_quant_kernel<PRE_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(row_quant_kernel<PRE_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(row_quant_kernel<PRE_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(row_quant_kernel<PRE_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         configured = true;
     }
-    if (smem > 160 * 1024) return cudaErrorInvalidConfiguration;
+    if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
     // an ordinary launch (starting early behind a tensor-core product measured slower inside the decode step); the
     // kernel still releases its own dependent at once, so that the product behind it can fetch weights meanwhile
     const dim3 grid((unsigned)batch), block((unsigned)threads);
