@@ -452,7 +452,9 @@ def measure_batch(bt, syn, model, cfg, B, K, W, context, tm, rng, world, peak, p
         "achieved_isolated": byts / us_step_plain / 1e3, "frac_isolated": byts / us_step_plain / 1e3 / peak,
         "bytes_per_launch": byts / 128, "us_per_launch": us_step_fused / 128,
         "launches_per_step": n_fused, "product_us_per_step": us_step_fused,
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum per product launch, mean over the four launches of a block,
+        # from one ncu capture of a two-block case of the same shape (read here, not measured by this run)
+        "traffic": (13750912.0 if B <= 8 else 14637952.0) if world == 1 and B in (1, 64) else None,
         "note": "frac: the four products of every block launched exactly as the decode step launches them "
                 "(quantiser prologues / kernels and fused epilogues included), replayed alone; frac_isolated: the plain "
                 "product on already quantised activations; bytes = packed weights once + int8 activations + f32 outputs",
