@@ -401,7 +401,7 @@ def time_attention(bt, cfg, B, context, torch, tp=1):
     hd = cfg.hidden_dim // cfg.n_heads
     nh, nkv = cfg.n_heads // tp, cfg.n_kv_heads // tp
     layers = 8 if B <= 8 else 4
-    caches = [bt.QuantizedKVCache(context + 64, B, nkv, hd) for _ in range(layers)]
+    caches = [bt.QuantizedKVCache(context + 64, B, nkv, hd, device=torch.cuda.current_device()) for _ in range(layers)]
     qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda")
     pos = torch.full((B,), context, dtype=torch.int32, device="cuda")
     for c in caches:

@@ -713,17 +713,24 @@ struct ClusterTable {
 
 template <int NREP, int HD>
 cudaError_t configure_rep(const ClusterTable** out) {
-    static ClusterTable table;  // per process; every device of a process is the same GPU model
+    static ClusterTable table;        // per process; every device of a process is the same GPU model
+    static PerDeviceOnce attributes;  // shared-memory limits and the cluster-size permission: per device
+    static bool big = false;
+    auto* decode = attn_kernel<NREP, 1, HD>;
+    auto* prefill = attn_kernel<NREP, kPrefillVectors / NREP, HD>;
+    cudaError_t e = attributes.run([decode, prefill] {
+        cudaError_t e2 = cudaFuncSetAttribute(decode, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHalfSm);
+        if (e2 == cudaSuccess)
+            e2 = cudaFuncSetAttribute(prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnSmemT<kPrefillVectors>));
+        if (e2 != cudaSuccess) return e2;
+        big = cudaFuncSetAttribute(decode, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        (void)cudaGetLastError();  // a refused permission only rules the large cluster sizes out
+        return cudaSuccess;
+    });
+    if (e != cudaSuccess) return e;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     if (!table.ready) {
-        auto* decode = attn_kernel<NREP, 1, HD>;
-        auto* prefill = attn_kernel<NREP, kPrefillVectors / NREP, HD>;
-        cudaError_t e = cudaFuncSetAttribute(decode, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHalfSm);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnSmemT<kPrefillVectors>));
-        if (e != cudaSuccess) return e;
-        const bool big = cudaFuncSetAttribute(decode, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         for (int s = 1; s <= kMaxCluster; ++s) {
             if (s > 8 && !big) break;
             cudaLaunchConfig_t cfg = {};
@@ -738,7 +745,7 @@ cudaError_t configure_rep(const ClusterTable** out) {
             int n = 0;
             if (cudaOccupancyMaxActiveClusters(&n, decode, &cfg) == cudaSuccess) table.active[s] = n;
         }
-        cudaGetLastError();  // a refused attribute or query only rules a cluster size out
+        cudaGetLastError();  // a refused query only rules a cluster size out
         if (table.active[1] < 1) table.active[1] = 1;
         table.ready = true;
     }

@@ -8,6 +8,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/bitttt.h"
 
 namespace bt {
@@ -182,6 +184,24 @@ cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride
                            cudaStream_t stream,
                            bool prequantised = false,     // qtc / sx / qsum are already filled (x unused)
                            bt_dtype x_dtype = BT_F32);    // element type of x: BT_F32 or BT_BF16
+
+// Kernel attributes (dynamic shared-memory limit, cluster sizes) belong to a device, not to the process: `run(f)`
+// calls f() once per device (the current one), under a lock, and remembers success.
+struct PerDeviceOnce {
+    std::mutex mu;
+    bool done[64] = {};
+    template <typename F>
+    cudaError_t run(F f) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+        e = f();
+        if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+        return e;
+    }
+};
 
 // Launch with the programmatic-stream-serialisation attribute: the kernel may start while
 // its predecessor in the stream is still running and must call griddepcontrol.wait before

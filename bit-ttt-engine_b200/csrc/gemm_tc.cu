@@ -436,15 +436,17 @@ struct TcVariant {
 
 template <int NT, int S>
 const TcVariant& tc_variant(int sm_count) {
-    static TcVariant v;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    if (v.status != cudaErrorNotReady) return v;
+    static TcVariant v;              // cluster limit: once per process (every device of a process is the same GPU model)
+    static PerDeviceOnce attributes;  // the kernel's shared-memory limit: once per device
     constexpr int kBBytes = 4 * NT * 64;
     v.smem = (size_t)kStages * (kRawBytes + kBBytes) + (S > 1 ? kRows * NT * 4 : 0) + 256;
     auto* kernel = gemm_tc_kernel<NT, kUnpackWarps, S>;
-    v.status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)v.smem);
+    const size_t smem = v.smem;
+    v.status = attributes.run([kernel, smem] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
     if (v.status != cudaSuccess) return v;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (v.max_clusters != 0) return v;
     if (S == 1) { v.max_clusters = sm_count; return v; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(sm_count / S * S));
@@ -458,7 +460,7 @@ const TcVariant& tc_variant(int sm_count) {
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
         (void)cudaGetLastError();
-        n = 0;  // this cluster size cannot be used
+        n = -1;  // this cluster size cannot be used
     }
     v.max_clusters = n;
     return v;
@@ -487,7 +489,7 @@ cudaError_t launch_variant(TcArgs a, int n_tiles, int sm_count, cudaStream_t str
 // Chunk steps on the busiest CTA when a tile's k range is cut over `s` CTAs (one step charged for the exchange of
 // partial sums); a huge number when the cut is not possible.
 int64_t tc_split_cost(int s, int max_clusters, int n_tiles, int64_t k_tiles) {
-    if (max_clusters < 1) return INT64_MAX;
+    if (max_clusters < 1) return INT64_MAX;  // (-1: the cluster size is unusable)
     const int64_t cps = (k_tiles + s - 1) / s;
     if (s > 1 && (k_tiles < 2 * s || cps * (s - 1) >= k_tiles)) return INT64_MAX;  // a CTA would be left without chunks
     const int nc = max_clusters < n_tiles ? max_clusters : n_tiles;

@@ -423,13 +423,14 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
     if (k % 4 != 0 || (q && q_stride % 4 != 0)) return cudaErrorInvalidValue;
     const size_t smem = (size_t)k * sizeof(float) + (qtc ? (size_t)k_tiles * kTileK : 0);
     const int threads = k >= 4096 ? 1024 : (k >= 2048 ? 512 : 256);
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(row_quant_kernel<PRE_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(row_quant_kernel<PRE_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(row_quant_kernel<PRE_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    cudaError_t ce = once.run([] {
+        cudaError_t e = cudaFuncSetAttribute(row_quant_kernel<PRE_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(row_quant_kernel<PRE_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(row_quant_kernel<PRE_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        return e;
+    });
+    if (ce != cudaSuccess) return ce;
     if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
     // an ordinary launch (starting early behind a tensor-core product measured slower inside the decode step); the
     // kernel still releases its own dependent at once, so that the product behind it can fetch weights meanwhile
@@ -453,11 +454,9 @@ static cudaError_t launch_lm_head_fused_bt(const __nv_bfloat16* w, const float* 
                                            int hidden, int64_t vocab, float* logits, float* cand_val,
                                            int32_t* cand_idx, int grid, cudaStream_t stream, bool pdl) {
     const size_t smem = (size_t)B * hidden * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(lm_head_fused_kernel<B, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    cudaError_t ce = once.run([] { return cudaFuncSetAttribute(lm_head_fused_kernel<B, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
+    if (ce != cudaSuccess) return ce;
     if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
     return launch_pdl(lm_head_fused_kernel<B, F16>, dim3(grid), dim3(256), smem, stream, pdl, w, h, norm_w, eps, hidden,
                       vocab, logits, cand_val, cand_idx);

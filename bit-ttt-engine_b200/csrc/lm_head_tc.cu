@@ -207,12 +207,9 @@ cudaError_t launch_lm_head_tc(const void* wtiles, const float* h, const float* n
                               cudaStream_t stream, bool w_f16) {
     if (hidden % kChunk != 0) return cudaErrorInvalidValue;
     const size_t smem = (size_t)kStages * (kATile + kBTile) + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(lm_head_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    cudaError_t ce = once.run([smem] { return cudaFuncSetAttribute(lm_head_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
+    if (ce != cudaSuccess) return ce;
     const int64_t row_sets = (vocab + kRows - 1) / kRows;
     const int grid = (int)(row_sets < sm_count ? row_sets : sm_count);
     for (int b0 = 0; b0 < batch; b0 += kTok) {

@@ -723,9 +723,18 @@ extern "C" bt_status bt_model_reset(bt_model* m) {
         if (L.w_state) BT_CUDA_TRY(cudaMemset(L.w_state, 0, (size_t)m->cfg.max_batch * m->d_small * m->d_small * sizeof(float)));
     }
     BT_CUDA_TRY(cudaMemset(m->pos, 0, (size_t)m->cfg.max_batch * sizeof(int32_t)));
-    if (m->peer) BT_CUDA_TRY(tp_peer_reset(m->peer));  // exchange epochs restart; every rank resets between the same steps
     BT_CUDA_TRY(cudaDeviceSynchronize());  // the clears are done before a step on another stream can start
     m->host_pos = 0;
+    return BT_OK;
+}
+
+// After a timed-out exchange the ranks' epoch counters no longer agree.  Every rank calls this while no rank has a
+// step in flight (host barrier before) and starts its next step only when all ranks are through (host barrier after).
+extern "C" bt_status bt_model_tp_resync(bt_model* m) {
+    if (!m || !m->finalized) return set_error(BT_ERR_ARG, "bt_model_tp_resync: model not finalized");
+    DeviceGuard guard(m->device);
+    BT_CUDA_TRY(cudaDeviceSynchronize());
+    if (m->peer) BT_CUDA_TRY(tp_peer_reset(m->peer));
     return BT_OK;
 }
 

@@ -69,6 +69,7 @@ def _bind():
     L.bt_model_tp_peer_import.argtypes = [vp, C.c_char_p]
     L.bt_model_tp_set_timeout.argtypes = [vp, i32]
     L.bt_model_tp_destroy.argtypes = [vp]
+    L.bt_model_tp_resync.argtypes = [vp]
     L.bt_model_enqueue_products.argtypes = [vp, i32, i32, vp, C.POINTER(i32)]
     L.bt_model_launches_per_step.argtypes = [vp, i32]
     L._model_bound = True
@@ -228,6 +229,10 @@ class BitLlama:
     def tp_set_timeout(self, milliseconds: int) -> None:
         """How long an exchange kernel waits for its peers before the step fails with BT_ERR_TIMEOUT."""
         check(self._L.bt_model_tp_set_timeout(self._h, milliseconds))
+
+    def tp_resync(self) -> None:
+        """After a timed-out exchange: every rank, with a host barrier before and after."""
+        check(self._L.bt_model_tp_resync(self._h))
 
     def tp_destroy(self) -> None:
         check(self._L.bt_model_tp_destroy(self._h))

@@ -286,13 +286,17 @@ bt_status bt_model_tp_init(bt_model* m, const uint8_t* id128);
  * 5 s unless bt_model_tp_set_timeout says otherwise): the exchange leaves the hidden state as it was,
  * the remaining exchanges of the step no longer wait, bt_model_forward_one returns BT_ERR_TIMEOUT
  * (callers of bt_model_step_dev see it through bt_device_check at their next synchronisation), and
- * decoding continues only after every rank has called bt_model_reset, which also restarts the exchange
- * epochs.  bt_model_tp_peer_import with handles = NULL drops the inbox and returns the model to the
+ * decoding continues only after every rank has called bt_model_reset and bt_model_tp_resync (which
+ * restarts the exchange epochs) with a host-side barrier before and after the latter, so that no rank
+ * clears flags a faster rank has already written for the next step.  bt_model_tp_peer_import with handles = NULL drops the inbox and returns the model to the
  * NCCL path (all ranks must do the same). */
 bt_status bt_model_tp_peer_export(bt_model* m, uint8_t* handle64_out);
 bt_status bt_model_tp_peer_import(bt_model* m, const uint8_t* handles);
 /* How long an exchange kernel waits for its peers (milliseconds, >= 1).  Drops the captured step graphs. */
 bt_status bt_model_tp_set_timeout(bt_model* m, int milliseconds);
+/* Restarts the exchange epochs and clears this rank's inbox flags after a timeout; see above for the barriers
+ * the host has to put around it.  Not needed in normal operation (bt_model_reset leaves the epochs alone). */
+bt_status bt_model_tp_resync(bt_model* m);
 /* Leaves tensor parallelism: closes the peer mappings and destroys the communicator (collective in the
  * sense that every rank should do it before any rank's inbox memory goes away).  bt_model_destroy does
  * the same implicitly. */

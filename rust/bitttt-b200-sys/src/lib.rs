@@ -113,6 +113,7 @@ pub mod ffi {
         pub fn bt_model_tp_peer_import(m: *mut bt_model, handles: *const u8) -> bt_status;
         pub fn bt_model_tp_set_timeout(m: *mut bt_model, milliseconds: c_int) -> bt_status;
         pub fn bt_model_tp_destroy(m: *mut bt_model) -> bt_status;
+        pub fn bt_model_tp_resync(m: *mut bt_model) -> bt_status;
         pub fn bt_model_set_linear(m: *mut bt_model, layer: c_int, kind: bt_weight_kind, packed_host: *const u8, n_out: i64,
                                    k_in: i64, scale: c_float) -> bt_status;
         pub fn bt_model_set_linear_bases(m: *mut bt_model, layer: c_int, kind: bt_weight_kind, packed_host: *const u8, n_out: i64,
