@@ -107,11 +107,11 @@ class ClockSampler:
 # workload
 # ---------------------------------------------------------------------------------------
 
-def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0, num_layers=None):
-    """Random-init Llama-3-8B-shaped ternary model.  Layer 0's host arrays are reused for
-    every layer (each layer still owns its own device copy, so HBM traffic is real); the
-    embedding and lm_head are one N(0, 0.02) block tiled over the vocabulary."""
-    cfg = syn.LLAMA3_8B
+def build_8b(bt, syn, batch, max_pos, seed=4000, tp_rank=0, tp_size=1, device=0, num_layers=None, shape="8b"):
+    """Random-init ternary model of the Llama-3-8B shape (or, shape="tinyllama", the TinyLlama-1.1B shape).
+    Layer 0's host arrays are reused for every layer (each layer still owns its own device copy, so HBM
+    traffic is real); the embedding and lm_head are one N(0, 0.02) block tiled over the vocabulary."""
+    cfg = syn.LLAMA3_8B if shape == "8b" else syn.TINYLLAMA_1B
     cfg = syn.BitLlamaConfig(cfg.arch, cfg.vocab_size, cfg.hidden_dim, num_layers or cfg.num_layers, cfg.n_heads, cfg.n_kv_heads,
                              cfg.intermediate_dim, rope_theta=cfg.rope_theta, max_position_embeddings=max_pos)
     rng = np.random.default_rng(seed)
@@ -450,11 +450,11 @@ def measure_batch(bt, syn, model, cfg, B, K, W, context, tm, rng, world, peak, p
         "bound": "hbm", "kernel": kernel, "unit": "GB/s", "peak": peak, "peak_kind": peak_kind,
         "achieved": byts / us_step_fused / 1e3, "frac": byts / us_step_fused / 1e3 / peak,
         "achieved_isolated": byts / us_step_plain / 1e3, "frac_isolated": byts / us_step_plain / 1e3 / peak,
-        "bytes_per_launch": byts / 128, "us_per_launch": us_step_fused / 128,
+        "bytes_per_launch": byts / (4 * cfg.num_layers), "us_per_launch": us_step_fused / (4 * cfg.num_layers),
         "launches_per_step": n_fused, "product_us_per_step": us_step_fused,
         # dram__bytes_read.sum + dram__bytes_write.sum per product launch, mean over the four launches of a block,
         # from one ncu capture of a two-block case of the same shape (read here, not measured by this run)
-        "traffic": (13750912.0 if B <= 8 else 14637952.0) if world == 1 and B in (1, 64) else None,
+        "traffic": (13750912.0 if B <= 8 else 14637952.0) if world == 1 and B in (1, 64) and cfg.hidden_dim == 4096 else None,
         "note": "frac: the four products of every block launched exactly as the decode step launches them "
                 "(quantiser prologues / kernels and fused epilogues included), replayed alone; frac_isolated: the plain "
                 "product on already quantised activations; bytes = packed weights once + int8 activations + f32 outputs",
@@ -488,6 +488,9 @@ def main():
                     help="small case for a profiler, not a benchmark: --layers blocks of the 8B shape, BATCH sequences, "
                          "the context filled by the batched prefill, then 3 decode steps; prints a line marked profile_case")
     ap.add_argument("--layers", type=int, default=2, help="blocks of the --profile-case model")
+    ap.add_argument("--shape", default="8b", choices=["8b", "tinyllama"],
+                    help="8b: the metric's workload (batch 1 and 64); tinyllama: the TinyLlama-1.1B shape at batch 1 and 16 "
+                         "(same measurements, a second reported configuration; use --context 512 for its stated prefill)")
     ap.add_argument("--tp-nccl", action="store_true",
                     help="with --gpus N > 1: keep the tensor-parallel exchanges on NCCL instead of the "
                          "library's peer-memory kernels")
@@ -529,11 +532,12 @@ def main():
         return
 
     K, W = args.steps, max(args.warmup, 3)
-    with_b64 = not args.no_batch64 and world == 1
-    B_max = 64 if with_b64 else 1
+    with_b64 = not args.no_batch64
+    B2 = 64 if args.shape == "8b" else 16  # the second batch size of the configuration
+    B_max = B2 if with_b64 else 1
     K64 = max(8, K // 4)
     max_pos = args.context + max(W + K, 8 + K64) + 16
-    cfg, weights, model = build_8b(bt, syn, B_max, max_pos, tp_rank=rank, tp_size=world, device=local_rank)
+    cfg, weights, model = build_8b(bt, syn, B_max, max_pos, tp_rank=rank, tp_size=world, device=local_rank, shape=args.shape)
     if world > 1:
         uid = [bt.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
@@ -564,8 +568,8 @@ def main():
 
     # ---- the benchmarked model's own first step against the oracle, before anything is timed ----
     verified = {"batch1": verify_first_step(model, weights, 1)} if world == 1 else {}
-    if with_b64:
-        verified["batch64"] = verify_first_step(model, weights, 64)
+    if with_b64 and world == 1:
+        verified[f"batch{B2}"] = verify_first_step(model, weights, B2)
     del weights
 
     # ---- batch 1 ---------------------------------------------------------------------------
@@ -578,11 +582,12 @@ def main():
     # ---- batch 64 --------------------------------------------------------------------------
     b64 = None
     if with_b64:
-        prefill64 = fill_context(model, cfg, 64, args.context, rng, tm)
-        b64 = measure_batch(bt, syn, model, cfg, 64, K64, W, args.context, tm, rng, world, peak, peak_kind)
+        prefill64 = fill_context(model, cfg, B2, args.context, rng, tm) if world == 1 else fill_tokenwise(model, cfg, B2, args.context, rng, dev, torch)
+        b64 = measure_batch(bt, syn, model, cfg, B2, K64, W, args.context, tm, rng, world, peak, peak_kind)
         b64["steps"] = K64
         b64["unit"] = UNIT
-        b64["prefill"] = prefill64
+        if prefill64 is not None:
+            b64["prefill"] = prefill64
 
     if rank == 0:
         cpu = None if args.no_cpu_baseline else cpu_decode_baseline(cfg, syn)
@@ -591,11 +596,11 @@ def main():
             "ms_per_step": b1["ms_per_step"], "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None,
             "dtype": "int8 x ternary -> int32 (f32 epilogue, bf16 lm_head)", "data": "synthetic",
-            "config": {"workload": f"Llama-3-8B-shaped ternary decode, batch 1 (top level) and batch 64 (`batch64`), context {args.context}+",
+            "config": {"workload": f"{'Llama-3-8B' if args.shape == '8b' else 'TinyLlama-1.1B'}-shaped ternary decode, batch 1 (top level) and batch {B2} (`batch{B2}`), context {args.context}+",
                        "batch": 1, "context": args.context,
                        "parallelism": (f"tp{world} ({'NCCL' if args.tp_nccl else 'peer-memory'} exchange)") if world > 1 else "single GPU",
                        "timing": f"median of {REGIONS} regions of {K} steps, each region restarted at the stated context",
-                       "l2": "inputs larger than L2: 1.74 GB of ternary tiles + 1.05 GB lm_head per step"},
+                       "l2": f"inputs larger than L2: {model.ternary_bytes / 1e9:.2f} GB of ternary tiles + {2 * cfg.vocab_size * cfg.hidden_dim / 1e9:.2f} GB lm_head per step"},
             "ms_regions": b1["ms_regions"],
             "e2e": b1["e2e"], "e2e_with_logits": b1["e2e_with_logits"],
             "gpu_launches": b1["gpu_launches"],
@@ -605,7 +610,7 @@ def main():
         if prefill1 is not None:
             line["prefill"] = prefill1
         if b64 is not None:
-            line["batch64"] = b64
+            line[f"batch{B2}"] = b64
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)

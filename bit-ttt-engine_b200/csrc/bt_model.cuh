@@ -19,7 +19,8 @@ cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int 
 // layout (k_tiles = padded k / 256), so that launch_gemm_tc can skip its own quantiser.
 cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
                              int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
-                             float* v_out, cudaStream_t stream, int8_t* qtc = nullptr, int k_tiles = 0);
+                             float* v_out, cudaStream_t stream, int8_t* qtc = nullptr, int k_tiles = 0,
+                             const unsigned int* amax_in = nullptr, unsigned int* amax_out = nullptr);
 
 // h[i] += y[i], i < n
 cudaError_t launch_residual_add(float* h, const float* y, int64_t n, cudaStream_t stream);

@@ -118,7 +118,12 @@ __global__ void __launch_bounds__(1024) row_quant_kernel(const float* __restrict
                                                          float* __restrict__ s_out,
                                                          int32_t* __restrict__ qsum_out,
                                                          float* __restrict__ v_out, int8_t* __restrict__ qtc,
-                                                         int tc_nt, int k_tiles) {
+                                                         int tc_nt, int k_tiles,
+                                                         const unsigned int* __restrict__ amax_in,
+                                                         unsigned int* __restrict__ amax_out) {
+    // amax_in : [rows] bit patterns of max|v| to quantise with (a maximum agreed over several GPUs) instead of
+    //           this row's own.  amax_out: values-only mode, the row's v goes to v_out and its max|v| (bits) to
+    //           amax_out[row]; nothing is quantised.
     extern __shared__ __align__(16) float row[];  // k floats, then k_tiles * 256 staged bytes (tensor-core layout only)
     __shared__ float red_f[32];
     __shared__ double red_d[32];
@@ -174,6 +179,13 @@ __global__ void __launch_bounds__(1024) row_quant_kernel(const float* __restrict
         }
     }
     amax = block_max(amax, red_f);
+    if (amax_out) {
+        for (int gi = threadIdx.x; gi < groups; gi += blockDim.x)
+            *reinterpret_cast<float4*>(v_out + (int64_t)b * k + 4 * gi) = *reinterpret_cast<const float4*>(row + 4 * gi);
+        if (threadIdx.x == 0) amax_out[b] = __float_as_uint(amax);
+        return;
+    }
+    if (amax_in) amax = __uint_as_float(amax_in[b]);
     const float s = __fdiv_rn(amax, 127.0f);
     const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     int local = 0;
@@ -418,8 +430,10 @@ cudaError_t launch_embed(const int32_t* tokens, const __nv_bfloat16* table, int 
 
 cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const float* w, float eps,
                              int batch, int k, int8_t* q, int64_t q_stride, float* s, int32_t* qsum,
-                             float* v_out, cudaStream_t stream, int8_t* qtc, int k_tiles) {
+                             float* v_out, cudaStream_t stream, int8_t* qtc, int k_tiles,
+                             const unsigned int* amax_in, unsigned int* amax_out) {
     const int tc_nt = batch <= 64 ? 64 : 128;
+    if (amax_out && !v_out) return cudaErrorInvalidValue;
     if (k % 4 != 0 || (q && q_stride % 4 != 0)) return cudaErrorInvalidValue;
     const size_t smem = (size_t)k * sizeof(float) + (qtc ? (size_t)k_tiles * kTileK : 0);
     const int threads = k >= 4096 ? 1024 : (k >= 2048 ? 512 : 256);
@@ -436,10 +450,10 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
     // kernel still releases its own dependent at once, so that the product behind it can fetch weights meanwhile
     const dim3 grid((unsigned)batch), block((unsigned)threads);
     if (pre == PRE_RMSNORM)
-        return launch_pdl(row_quant_kernel<PRE_RMSNORM>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
+        return launch_pdl(row_quant_kernel<PRE_RMSNORM>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles, amax_in, amax_out);
     if (pre == PRE_SWIGLU)
-        return launch_pdl(row_quant_kernel<PRE_SWIGLU>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
-    return launch_pdl(row_quant_kernel<PRE_NONE>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles);
+        return launch_pdl(row_quant_kernel<PRE_SWIGLU>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles, amax_in, amax_out);
+    return launch_pdl(row_quant_kernel<PRE_NONE>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles, amax_in, amax_out);
 }
 
 cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream) {

@@ -326,9 +326,28 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
     unsigned int* err = device_error_word(m->device);
     const int sm = m->sm_count;
     const int kt_h = (H + kTileK - 1) / kTileK, kt_i = (I + kTileK - 1) / kTileK;
+    const int att_dim = m->nh_l * m->head_dim;
+    const int kt_att = (att_dim + kTileK - 1) / kTileK;
+    // Tensor parallelism at these batch sizes: q|k|v and gate|up hold this rank's rows, o_proj and down_proj this
+    // rank's input columns.  Their input is quantised with the maximum over all ranks (all-reduce max of the
+    // per-token absmax), their int32 accumulators are summed over the ranks (all-reduce sum) before the scale
+    // epilogue: the hidden state stays bit-identical to one GPU.  Both collectives go through NCCL here.
+    const bool tp = m->tp > 1;
+    if (tp && !m->comm) return set_error(BT_ERR_NCCL, "tensor-parallel steps of more than 8 sequences need bt_model_tp_init (NCCL)");
+    auto row_parallel = [&](bt_linear* lin, const float* x, int k, int k_tiles, unsigned int* amax) -> bt_status {
+        bt_status st = tp_allreduce_max_f32(m->comm, reinterpret_cast<float*>(amax), (size_t)batch, s);
+        if (st != BT_OK) return st;
+        BT_CUDA_TRY(launch_row_quant(PRE_NONE, x, k, nullptr, 0.f, batch, k, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, k_tiles, amax));
+        BT_CUDA_TRY(launch_gemm_tc(lin->dev(), nullptr, k, batch, m->qtc, m->sx, m->qsum, m->acc_i32, H, EPI_I32, err, sm, s, true));
+        if ((st = tp_allreduce_sum_i32(m->comm, m->acc_i32, (size_t)batch * H, s)) != BT_OK) return st;
+        BT_CUDA_TRY(launch_tp_residual(m->acc_i32, amax, lin->scales[0], batch, H, m->h, s, false));
+        return BT_OK;
+    };
     BT_CUDA_TRY(launch_embed(m->tokens, m->embed, batch, H, c.vocab_size, m->h, s, m->absmax, c.num_layers * 2 * B, false, m->embed_f16));
     for (int li = 0; li < c.num_layers; ++li) {
         Layer& L = m->layers[(size_t)li];
+        unsigned int* amax_core = m->absmax + ((size_t)li * 2 + 0) * B;
+        unsigned int* amax_mlp = m->absmax + ((size_t)li * 2 + 1) * B;
         // x_norm = norm1(x)  (model/block.rs:98)
         //   (the row kernels write the int8 activations straight in the tensor-core product's layout)
         BT_CUDA_TRY(trace_copy(m, li, TR_H_IN, m->h, batch, s));
@@ -354,20 +373,33 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
             a.sm_count = sm;
             attn_plan(batch, m->nkv_l, c.max_position_embeddings, sm, m->nh_l / m->nkv_l, &a.splits, &a.span);
             a.scaling = (float)(1.0 / sqrt((double)m->head_dim));
-            a.absmax_out = nullptr;
+            a.absmax_out = tp ? amax_core : nullptr;
             a.pdl = true;
             BT_CUDA_TRY(trace_copy(m, li, TR_QKV, m->qkv, batch, s));
             BT_CUDA_TRY(launch_attn_decode(a, s));
             BT_CUDA_TRY(trace_copy(m, li, TR_ATT, m->att, batch, s));
-            BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, m->nh_l * m->head_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
+            if (tp) {
+                bt_status st = row_parallel(L.o, m->att, att_dim, kt_att, amax_core);
+                if (st != BT_OK) return st;
+            } else {
+                BT_CUDA_TRY(launch_gemm_tc(L.o->dev(), m->att, att_dim, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s));
+            }
         }
         // x = x + mlp(norm2(x))  (model/block.rs:119-131, layers/swiglu.rs:29-35)
         BT_CUDA_TRY(trace_copy(m, li, TR_H_MID, m->h, batch, s));
         BT_CUDA_TRY(launch_row_quant(PRE_RMSNORM, m->h, H, L.norm2, kRmsEps, batch, H, nullptr, 0, m->sx, m->qsum, nullptr, s, m->qtc, kt_h));
         BT_CUDA_TRY(launch_gemm_tc(L.gate_up_il->dev(), nullptr, H, batch, m->qtc, m->sx, m->qsum, m->gu, 2 * I, EPI_F32, err, sm, s, true));
-        BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, m->trace ? m->act : nullptr, s, m->qtc, kt_i));
-        BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
-        BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, true));
+        if (tp) {
+            // silu(gate) * up of this rank's columns and their maximum, then the row-parallel product
+            BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, m->act, s, nullptr, 0, nullptr, amax_mlp));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
+            bt_status st = row_parallel(L.down, m->act, I, kt_i, amax_mlp);
+            if (st != BT_OK) return st;
+        } else {
+            BT_CUDA_TRY(launch_row_quant(PRE_SWIGLU, m->gu, 2 * I, nullptr, 0.f, batch, I, nullptr, 0, m->sx, m->qsum, m->trace ? m->act : nullptr, s, m->qtc, kt_i));
+            BT_CUDA_TRY(trace_copy(m, li, TR_ACT, m->act, batch, s));
+            BT_CUDA_TRY(launch_gemm_tc(L.down->dev(), nullptr, I, batch, m->qtc, m->sx, m->qsum, m->h, H, EPI_F32_ACCUM, err, sm, s, true));
+        }
         BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
     }
     // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
@@ -502,10 +534,10 @@ extern "C" bt_status bt_model_create(bt_model** out, const bt_model_config* cfg,
     if (tp > 1) {
         if (c.arch != 1) { delete m; return set_error(BT_ERR_ARG, "bt_model_create: tensor parallelism needs arch llama"); }
         if (c.tp_rank < 0 || c.tp_rank >= tp || c.n_kv_heads % tp != 0 || c.n_heads % tp != 0 ||
-            c.intermediate_dim % (16 * tp) != 0 || c.max_batch > 8) {
+            c.intermediate_dim % (16 * tp) != 0) {
             delete m;
             return set_error(BT_ERR_SHAPE, "bt_model_create: tp_size %d must divide n_kv_heads, n_heads and intermediate_dim/16 "
-                                           "(rank in range, max_batch <= 8)", tp);
+                                           "(rank in range)", tp);
         }
     }
     m->cfg = c;
@@ -1111,7 +1143,8 @@ extern "C" bt_status bt_model_tp_peer_export(bt_model* m, uint8_t* handle64_out)
     if (m->tp <= 1) return set_error(BT_ERR_ARG, "bt_model_tp_peer_export: the model is not tensor-parallel");
     DeviceGuard guard(m->device);
     if (!m->peer) {
-        bt_status st = tp_peer_create(&m->peer, m->cfg.tp_rank, m->tp, m->cfg.max_batch, m->cfg.hidden_dim, device_error_word(m->device));
+        bt_status st = tp_peer_create(&m->peer, m->cfg.tp_rank, m->tp, m->cfg.max_batch < 8 ? m->cfg.max_batch : 8,  // steps of up to 8 sequences use it
+                                      m->cfg.hidden_dim, device_error_word(m->device));
         if (st != BT_OK) return st;
     }
     return tp_peer_export(m->peer, handle64_out);

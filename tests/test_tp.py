@@ -45,6 +45,21 @@ def test_tp2_model_matches_oracle_and_ranks_agree(use_peer):
 
 
 @pytest.mark.gpu
+def test_tp2_model_more_than_8_sequences():
+    # the tensor-core decode step under tensor parallelism (12 sequences): same stage-wise checks
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(tp_common.gpu_model_worker, args=(2, _free_port(), d, 4, False, 12), nprocs=2, join=True)
+        for r in _results(d, 2):
+            worst, same, staged_ok = r.split()
+            assert float(worst) <= 1e-3, r
+            assert same == "1" and staged_ok == "1", r
+
+
+@pytest.mark.gpu
 def test_peer_exchange_wait_runs_out_without_a_fault():
     # failure detection without a GPU fault: the missing rank is made on the host (it never launches)
     if not torch.cuda.is_available():

@@ -55,12 +55,13 @@ def cpu_row_parallel_worker(rank, world, port, result_dir):
     dist.destroy_process_group()
 
 
-def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
+def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False, batch=2):
     """Tensor-parallel decode of a small llama-shaped model on `world` GPUs, checked stage by stage:
     every rank's q|k|v and silu(gate)*up slices against the oracle's slices, and the two row-parallel
     projections (o_proj, down_proj: absmax exchange + integer sum over the ranks) bit for bit against
     the oracle's unsharded projection of the gathered slices.  Every rank must hold the same hidden
-    state and logits bit for bit.  use_peer: exchange over NVLink peer memory instead of NCCL."""
+    state and logits bit for bit.  use_peer: exchange over NVLink peer memory instead of NCCL.
+    batch > 8 takes the tensor-core step (row quantiser + tcgen05 products, collectives over NCCL)."""
     import torch
     dist = _init(rank, world, port, "gloo")
     torch.cuda.set_device(rank)
@@ -69,7 +70,7 @@ def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
     from oracle import oracle as orc
     cfg = syn.BitLlamaConfig("llama", 1000, 256, 2, 8, max(4, world), 512, max_position_embeddings=64)  # KV heads: 4, or one per rank
     w = syn.make_weights(cfg, seed=3000)
-    model = syn.build_model(w, max_batch=2, device=rank, tp_rank=rank, tp_size=world)
+    model = syn.build_model(w, max_batch=batch, device=rank, tp_rank=rank, tp_size=world)
     if use_peer:
         handles = [None] * world
         dist.all_gather_object(handles, model.tp_peer_handle())
@@ -81,7 +82,7 @@ def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
     ref = orc.model_from_weights(w)
     hd, nh, nkv, inter = cfg.hidden_dim // cfg.n_heads, cfg.n_heads, cfg.n_kv_heads, cfg.intermediate_dim
     nh_l, nkv_l, i_l = nh // world, nkv // world, inter // world
-    tokens = np.random.default_rng(7).integers(0, cfg.vocab_size, size=(n_tokens, 2))
+    tokens = np.random.default_rng(7).integers(0, cfg.vocab_size, size=(n_tokens, batch))
     worst, same, ok = 0.0, True, True
     model.set_trace(True)
     for t in range(n_tokens):
@@ -90,10 +91,10 @@ def gpu_model_worker(rank, world, port, result_dir, n_tokens, use_peer=False):
         theirs = mine.clone()
         dist.broadcast(theirs, src=0)
         same = same and bool(torch.equal(mine, theirs))
-        tr = model.read_trace(2)
+        tr = model.read_trace(batch)
         gathered = [None] * world
         dist.all_gather_object(gathered, [{k: v for k, v in layer.items() if k in ("att", "act")} for layer in tr])
-        for b in range(2):
+        for b in range(batch):
             for li in range(cfg.num_layers):
                 L, lt = ref.layers[li], tr[li]
                 h_in = lt["h_in"][b:b + 1]
