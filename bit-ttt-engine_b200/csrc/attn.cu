@@ -39,6 +39,7 @@
 #include <stddef.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "bt_model.cuh"
 #include "bt_ptx.cuh"
@@ -229,7 +230,16 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
             const int n = min(kTilePos, t1 - r0);
             const uint8_t* src = (c.phase ? a.cache.v_q : a.cache.k_q) + (row_base + r0) * hd;
             uint8_t* dst = sm.ring[stage];
-            if (l16 >= 0) {
+            if constexpr (HD > 0) {
+                // thread -> (row tid / P16 + k RP, 16-byte piece tid % P16): all offsets are compile-time constants
+                constexpr int P16 = HD / 16, RP = kAttnThreads / P16, NP = kTilePos / RP;
+                const int rr = tid / P16;
+                const uint8_t* s0 = src + 16 * tid;
+                uint8_t* d0 = dst + rr * (HD + kRowPad) + (tid % P16) * 16;
+#pragma unroll
+                for (int k = 0; k < NP; ++k)
+                    if (rr + k * RP < n) cp_async16(d0 + k * RP * (HD + kRowPad), s0 + k * RP * HD);
+            } else if (l16 >= 0) {
                 for (int i = tid; i < (n << l16); i += kAttnThreads)
                     cp_async16(dst + (i >> l16) * rstride + ((i & ((1 << l16) - 1)) << 4), src + 16 * i);
             } else {
@@ -382,7 +392,10 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 fetch(fc, (n + 2) % kStages);
                 advance(fc);
                 const int n_here = min(kTilePos, clen - ti * kTilePos);
-                if (16 * warp < n_here) {
+                // FULL: a whole tile that every query may see (decode; all but the last tile of a span)
+                auto score_tile = [&](auto full_tag) {
+                    constexpr bool FULL = decltype(full_tag)::value;
+                    if (!FULL && 16 * warp >= n_here) return;
                     const uint8_t* kraw = sm.ring[n % kStages];
                     int c[NB][4];
 #pragma unroll
@@ -408,18 +421,18 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                     const bool odd = t & 1;
                     const int r = 16 * warp + g + (odd ? 8 : 0);
                     const int slot = ti * kTilePos + 16 * warp + 4 * (g & 3) + (g >> 2) + (odd ? 2 : 0);
-                    const float ksr = r < n_here ? sm.sc[n % kStages][r] : 0.0f;
+                    const float ksr = (FULL || r < n_here) ? sm.sc[n % kStages][r] : 0.0f;
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) {
                         const int v = 2 * nb + (t >> 1);
                         const float x_lo = fmaf((float)(c[nb][0] - dc[nb][0]), 128.0f, (float)(c[nb][1] - dc[nb][1]));  // row g
                         const float x_hi = fmaf((float)(c[nb][2] - dc[nb][0]), 128.0f, (float)(c[nb][3] - dc[nb][1]));  // row g + 8
                         const float got = __shfl_xor_sync(0xffffffffu, odd ? x_lo : x_hi, 1);
-                        if (v < G) {
-                            // prefill: query vector v sits at position p + q0 + v / NREP and sees the keys up to there
-                            const bool seen = QB == 1 || chunk0 + ti * kTilePos + r <= p + q0 + v / NREP;
+                        if (G % 2 == 0 || v < G) {
                             float s = -INFINITY;
-                            if (r < n_here && seen) {
+                            // prefill: query vector v sits at position p + q0 + v / NREP and sees the keys up to there
+                            const bool seen = FULL || (r < n_here && (QB == 1 || chunk0 + ti * kTilePos + r <= p + q0 + v / NREP));
+                            if (seen) {
                                 const float dot = __fmul_rn(odd ? fmaf(got, 16384.0f, x_hi) : fmaf(x_lo, 16384.0f, got), qs[nb]);
                                 s = __fmul_rn(__fmul_rn(dot, ksr), a.scaling);  // (attention.rs:202)
                             }
@@ -427,7 +440,10 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                             mx[nb] = fmaxf(mx[nb], s);
                         }
                     }
-                }
+                };
+                // (prefill: the last new token's position bounds what the block's first query may see)
+                if (n_here == kTilePos && (QB == 1 || chunk0 + ti * kTilePos + kTilePos - 1 <= p + q0)) score_tile(std::true_type{});
+                else score_tile(std::false_type{});
             }
             // ---- between the phases: the chunk's maximum per query vector, the bound of the weights ----
 #pragma unroll
@@ -486,6 +502,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 // weight digits of the tile: a warp takes one query vector per round, lane L the slots 4 L .. 4 L + 3 =
                 // positions 16 (L / 4) + 4 i + L % 4, i = 0..3: the four positions that one lane feeds into an MMA
                 // lie in one word, and so do the rows it reads from V.
+                const bool full_tile = n_here == kTilePos && (QB == 1 || chunk0 + ti * kTilePos + kTilePos - 1 <= p + q0);
 #pragma unroll
                 for (int e = 0; e < kRounds; ++e) {
                     const int v = warp + e * kAttnWarps;
@@ -498,7 +515,8 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                         uint32_t u[4], dig[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const bool live = r0 + 4 * i < n_here && sv[i] != -INFINITY;  // (beyond the tile the buffer holds anything)
+                            // (beyond the tile the buffer holds anything; a masked score is -inf and gives exp = 0)
+                            const bool live = full_tile || (r0 + 4 * i < n_here && sv[i] != -INFINITY);
                             const float pe = live ? expf(__fsub_rn(sv[i], m_new)) : 0.0f;
                             psum[e] += pe;
                             // weight of the value row: p * v_scale (the value bytes enter the MMA as integers)
@@ -514,7 +532,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 fetch(fc, (n + 2) % kStages);
                 advance(fc);
                 const uint8_t* vcol = sm.ring[n % kStages] + 32 * dg + 4 * g;
-                for (int ks = pq; 32 * ks < n_here; ks += n_pq) {  // (head_dim 128: steps pq and pq + 2)
+                auto pv_step = [&](int ks) {
                     uint32_t b0[4], b1[4];
                     {
                         const uint8_t* vp = vcol + (32 * ks + t) * rstride;
@@ -535,6 +553,12 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                         for (int e = 0; e < 4; ++e) mma_u8u8(acc[mb][e], a0, a1, a2, a3, b0[e], b1[e]);
                         mma_u8u8(ones[mb], a0, a1, a2, a3, 0x01010101u, 0x01010101u);  // sum of the digits: the "- 128" of the value bytes
                     }
+                };
+                if (HD == 128 && n_here == kTilePos) {  // two fixed steps per warp
+                    pv_step(pq);
+                    pv_step(pq + 2);
+                } else {
+                    for (int ks = pq; 32 * ks < n_here; ks += n_pq) pv_step(ks);
                 }
             }
             // ---- end of the chunk: digits together, "- 128" out, to f32, into the running output ----
