@@ -142,7 +142,7 @@ def verify_first_step(model, weights, batch):
     except AssertionError as exc:
         raise SystemExit(f"bench.py: the first decode step differs from the oracle: {exc}")
     model.reset_kv_cache()
-    return "all stages of 32 layers match (BitLinear stages bit-exact, attention <= 2e-5, logits <= 2e-5)"
+    return f"all stages of {cfg.num_layers} layers match (BitLinear stages bit-exact, attention <= 2e-5, logits <= 2e-5)"
 
 
 def cpu_decode_baseline(cfg, syn, budget_s=20.0):

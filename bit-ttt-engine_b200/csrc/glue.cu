@@ -241,9 +241,37 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     const float* row = logits + (int64_t)blockIdx.x * stride;
     float best = -INFINITY;
     int idx = -1;
-    for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
-        const float v = row[c];
-        if (v >= best || idx < 0) { best = v; idx = c; }
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // four consecutive values per load, four loads in flight per thread; within a thread the indices rise,
+        // so ">=" keeps the last of equal maxima
+        const int groups = vocab >> 2;
+        for (int g0 = threadIdx.x; g0 < groups; g0 += 4 * blockDim.x) {
+            float4 f[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int gi = g0 + u * blockDim.x;
+                f[u] = gi < groups ? *reinterpret_cast<const float4*>(row + 4 * gi) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = 4 * (g0 + u * blockDim.x);
+                if (c < 4 * groups) {
+                    if (f[u].x >= best || idx < 0) { best = f[u].x; idx = c; }
+                    if (f[u].y >= best) { best = f[u].y; idx = c + 1; }
+                    if (f[u].z >= best) { best = f[u].z; idx = c + 2; }
+                    if (f[u].w >= best) { best = f[u].w; idx = c + 3; }
+                }
+            }
+        }
+        for (int c = 4 * groups + threadIdx.x; c < vocab; c += blockDim.x) {
+            const float v = row[c];
+            if (v >= best || idx < 0) { best = v; idx = c; }
+        }
+    } else {
+        for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
+            const float v = row[c];
+            if (v >= best || idx < 0) { best = v; idx = c; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

@@ -347,17 +347,27 @@ class BitLlama:
 
     def save_memory(self, path: str) -> None:
         """TTT fast-weight states to a safetensors file, tensors `layer_{i}` (Llama::save_memory,
-        model/llama.rs:575-591): `[d, d]` for a single-sequence model, `[batch, d, d]` otherwise."""
+        model/llama.rs:575-591): `[d, d]` for a single-sequence model, `[batch, d, d]` otherwise.
+        Attention blocks (which the reference's file does not cover) add their Q8 cache rows up to the
+        current position as `kv_{i}.k_q / k_s / v_q / v_s` (`[batch, n_kv, T, hd]` u8, `[batch, n_kv, T]` f32)
+        and the position as `kv_position`, so that a conversation can be resumed without a second prefill."""
         from .loader import write_safetensors
         torch = _torch()
         torch.cuda.synchronize(self.device)
         tensors = {}
+        t_len = self.current_pos
         for li in range(self.cfg.num_layers):
             st = self.ttt_state(li)
-            if st is None:
-                continue
-            a = st.cpu().numpy()
-            tensors[f"layer_{li}"] = a[0] if self.max_batch == 1 else a
+            if st is not None:
+                a = st.cpu().numpy()
+                tensors[f"layer_{li}"] = a[0] if self.max_batch == 1 else a
+            kv = self.kv_cache(li)
+            if kv is not None and t_len > 0:
+                rows = [kv.export(b, t_len) for b in range(self.max_batch)]
+                for j, name in enumerate(("k_q", "k_s", "v_q", "v_s")):
+                    tensors[f"kv_{li}.{name}"] = np.stack([r[j] for r in rows])
+        if any(k.startswith("kv_") for k in tensors):
+            tensors["kv_position"] = np.array([t_len], np.int32)
         write_safetensors(path, tensors)
 
     def load_memory(self, path: str) -> None:
@@ -380,6 +390,22 @@ class BitLlama:
             if a.shape != (self.max_batch, d, d):
                 raise CheckpointError(f"{path}: layer_{li} has shape {a.shape}, expected {(d, d)} or {(self.max_batch, d, d)}")
             st.copy_(torch.from_numpy(np.array(a, dtype=np.float32)).to(st.device))
+        if "kv_position" in tensors:
+            t_len = int(np.array(tensors["kv_position"]).reshape(-1)[0])
+            c = self.cfg
+            n_kv, hd = c.n_kv_heads // max(self.tp_size, 1), c.hidden_dim // c.n_heads
+            if not 0 < t_len <= c.max_position_embeddings:
+                raise CheckpointError(f"{path}: kv_position {t_len} outside 1..{c.max_position_embeddings}")
+            for li in range(c.num_layers):
+                kv = self.kv_cache(li)
+                if kv is None or f"kv_{li}.k_q" not in tensors:
+                    continue
+                parts = [np.array(tensors[f"kv_{li}.{name}"]) for name in ("k_q", "k_s", "v_q", "v_s")]
+                if parts[0].shape != (self.max_batch, n_kv, t_len, hd) or parts[1].shape != (self.max_batch, n_kv, t_len):
+                    raise CheckpointError(f"{path}: kv_{li} has shape {parts[0].shape}, expected {(self.max_batch, n_kv, t_len, hd)}")
+                for b in range(self.max_batch):
+                    kv.load(b, parts[0][b], parts[1][b], parts[2][b], parts[3][b])
+            self.seek(t_len)
         torch.cuda.synchronize(self.device)
 
     def kv_cache(self, layer: int):

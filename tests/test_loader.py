@@ -176,6 +176,31 @@ def test_ttt_memory_file_round_trip(mods, tmp_path):
     assert np.array_equal(la, lb)
 
 
+@pytest.mark.gpu
+def test_kv_cache_in_the_memory_file(mods, tmp_path):
+    """Attention blocks: the Q8 cache rows and the position travel in the same file (an addition to the
+    reference's format, which holds TTT states only); a model that loads them continues bit for bit."""
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    loader, syn, _ = mods
+    w = syn.make_weights(syn.TINY_LLAMA_TEST, seed=21)
+    a, b = syn.build_model(w, max_batch=2), syn.build_model(w, max_batch=2)
+    rng = np.random.default_rng(5)
+    for _ in range(9):
+        a.forward_one(rng.integers(0, 1000, size=2).astype(np.int32))
+    path = str(tmp_path / "memory.soul")
+    a.save_memory(path)
+    saved = loader.read_safetensors(path)
+    assert int(saved["kv_position"][0]) == 9 and saved["kv_0.k_q"].shape == (2, 2, 9, 32) and saved["kv_1.v_s"].shape == (2, 2, 9)
+    b.load_memory(path)
+    assert b.current_pos == 9
+    tok = np.array([11, 12], np.int32)
+    la, na = a.forward_one(tok)
+    lb, nb = b.forward_one(tok)
+    assert np.array_equal(la, lb) and np.array_equal(na, nb)
+
+
 def test_reference_converted_checkpoint_is_read(mods, oracle):
     """tests/golden/converted_tiny was written by the reference's own converter (its main(), default
     NumBases = 3; regenerate with tests/golden/make_golden.py): the container parser, the HF tensor names,
