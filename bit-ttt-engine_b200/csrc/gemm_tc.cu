@@ -4,19 +4,19 @@
 // kernels/cuda.rs:21-47) at batch and prefill sizes, where the reference runs a dense f32 GEMM
 // on a host-unpacked weight.
 //
-// Roles inside one CTA (1 per SM, persistent over work units of 128 weight rows x NT tokens x a k range):
+// Roles inside one CTA (1 per SM, persistent over work units of RS x 128 weight rows x NT tokens x a k range;
+// the RS = 1 or 2 row sets of a unit share every activation block):
 //   warp 0     producer: 1-D bulk copies of the packed weight tiles (8 x 1 KB per 256-input
 //              chunk) and of the chunk's int8 activation block into a shared-memory ring;
 //   warp 1     MMA issuer (one thread): tcgen05.mma.kind::i8 with the A operand (weights, u8) in
 //              TENSOR MEMORY and the B operand (activations, s8) in shared memory, K-major without
 //              swizzle; accumulators in tensor memory, two sets, so that the MMAs of the next unit
 //              run while the previous one is drained;
-//   warps 2-9  unpack: two threads own one weight row (= one TMEM lane), half of its bytes each.  A thread
-//              loads its 32 packed bytes of the chunk, isolates field r of every byte with a shift and
-//              an AND (values 0, 1, 2 = ternary + 1) and writes the four residue planes with tcgen05.st
-//              straight into tensor memory: the unpacked weights never pass through shared memory,
-//              whose bandwidth the B operand and the ring need;
-//   warps 10-13 epilogue: tcgen05.ld of a finished accumulator set, - sum_k q (the +1 offset), scales, store.
+//   4 RS unpack warps: a thread owns one weight row (= one TMEM lane) of one row set.  It loads the row's 64
+//              packed bytes of the chunk, isolates field r of every byte with a shift and an AND (values 0, 1, 2 =
+//              ternary + 1) and writes the four residue planes with tcgen05.st straight into tensor memory:
+//              the unpacked weights never pass through shared memory, whose bandwidth the B operand and the ring need;
+//   4 RS epilogue warps: tcgen05.ld of a finished accumulator set, - sum_k q (the +1 offset), scales, store.
 // With few output tiles the k range of a tile is cut over the CTAs of a thread-block cluster; their int32
 // partial sums reach the cluster's first CTA through distributed shared memory, and that CTA alone stores.
 // Every launch carries the programmatic-dependent-launch attribute: the producer requests the first weight
@@ -35,15 +35,24 @@ namespace bt {
 
 namespace {
 
-constexpr int kRows = 128;               // weight rows per tile = UMMA M = TMEM lanes
+constexpr int kRows = 128;               // weight rows per MMA = UMMA M = TMEM lanes
 constexpr int kChunkK = 256;             // inputs per k-chunk (one weight tile column)
-constexpr int kRawBytes = 8 * kTileBytes;  // packed weights of a chunk: 8 row tiles x 1 KB
-constexpr int kStages = 5;
+constexpr int kSetBytes = 8 * kTileBytes;  // packed weights of 128 rows of a chunk: 8 row tiles x 1 KB
 constexpr int kABufs = 2;                // unpacked-A buffers in tensor memory
-constexpr int kAChunkCols = 64;          // TMEM columns of one unpacked chunk: 4 residues x 64 bytes / 4
-constexpr int tc_threads(int unpack_warps) { return (2 + unpack_warps + 4) * 32; }
+constexpr int kAChunkCols = 64;          // TMEM columns of one unpacked 128-row chunk: 4 residues x 64 bytes / 4
 constexpr int kMaxSplit = 8;             // CTAs of one cluster that share a tile along k
 constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
+
+// A tile is RS x 128 weight rows x NT tokens: the RS row sets share every activation block, which is what a CTA
+// pulls most of through L2 (NT x 256 bytes per chunk against RS x 8 KB of packed weights).
+__host__ __device__ constexpr int tc_threads(int rs) { return (2 + 8 * rs) * 32; }  // producer, MMA issuer, 4 RS unpack warps, 4 RS epilogue warps
+__host__ __device__ constexpr int tc_acc_sets(int nt, int rs) { return (2 * rs * nt + kABufs * rs * kAChunkCols <= 512) ? 2 : 1; }
+__host__ __device__ constexpr int tc_stages(int nt, int rs, int s) {
+    // ring depth that fits 227 KB next to the partial-sum buffer of a k split
+    const int stage = rs * kSetBytes + 4 * nt * 64, part = s > 1 ? rs * kRows * nt * 4 : 0;
+    const int n = (225 * 1024 - part) / stage;
+    return n > 5 ? 5 : n;
+}
 
 // Instruction descriptor for kind::i8: D = s32, A = u8, B = s8, both K-major, M x N tile.
 __device__ __forceinline__ uint32_t instr_desc_i8(int m, int n) {
@@ -70,35 +79,41 @@ struct TcArgs {
     unsigned int* err;
 };
 
-// UW unpack warps: 4 (a thread unpacks a whole row of the chunk) or 8 (two threads share a row)
-// S: CTAs of a cluster that share a tile along k (1: no cluster work at all)
-template <int NT, int UW, int S>
-__global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
+// NT: tokens per tile (64 / 128).  RS: 128-row sets per tile (1 / 2).  S: CTAs of a cluster that share a tile
+// along k (1: no cluster work at all).
+template <int NT, int RS, int S>
+__global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     static_assert(S == 1 || (NT == 64 && (S == 2 || S == 4 || S == 8)), "k split: 64 tokens, 2 / 4 / 8 CTAs");
-    constexpr int kUnpackWarps = UW, kEpiWarp0 = 2 + UW;
-    constexpr int PT = 16 / UW;                          // 16-byte pieces of a row's 64 packed bytes per unpack thread
+    constexpr int kUnpackWarps = 4 * RS, kEpiWarps = 4 * RS, kEpiWarp0 = 2 + kUnpackWarps;
+    constexpr int kStages = tc_stages(NT, RS, S);
+    constexpr int kAccSets = tc_acc_sets(NT, RS);
+    constexpr int kRawBytes = RS * kSetBytes;
     constexpr int kBBytes = 4 * NT * 64;                 // activation block of a chunk (4 residues)
     constexpr int kStageBytes = kRawBytes + kBBytes;
-    constexpr int kPartBytes = S > 1 ? kRows * NT * 4 : 0;  // this CTA's partial sums of a tile, read by the whole cluster
-    constexpr uint32_t kAccCols = 2 * NT;                // two accumulator sets of NT columns
-    constexpr uint32_t kTmemCols = (kAccCols + kABufs * kAChunkCols) <= 256 ? 256 : 512;
+    constexpr int kPartBytes = S > 1 ? RS * kRows * NT * 4 : 0;  // this CTA's partial sums of a tile, read by the whole cluster
+    constexpr uint32_t kAccCols = kAccSets * RS * NT;
+    constexpr uint32_t kTmemCols = (kAccCols + kABufs * RS * kAChunkCols) <= 256 ? 256 : 512;
+    static_assert(kAccCols + kABufs * RS * kAChunkCols <= 512, "tensor memory");
+    static_assert(kStages >= 3, "ring");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stage_base = smem;                                           // kStages x (raw | B)
-    int32_t* pbuf = reinterpret_cast<int32_t*>(stage_base + (size_t)kStages * kStageBytes);  // [NT / 4][128 rows][4]
+    int32_t* pbuf = reinterpret_cast<int32_t*>(stage_base + (size_t)kStages * kStageBytes);  // [RS][NT / 4][128 rows][4]
     uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(pbuf) + kPartBytes);
     uint64_t* empty = full + kStages;     // a stage is free again: the MMAs that read its B block are done (1 arrival)
                                           // and the unpack warps have read its weights (kUnpackWarps arrivals)
     uint64_t* a_full = empty + kStages;   // unpacked chunk in tensor memory (one arrival per unpack warp)
     uint64_t* a_empty = a_full + kABufs;  // the MMAs that read it are done
     uint64_t* acc_full = a_empty + kABufs;
-    uint64_t* acc_empty = acc_full + 2;   // 4 arrivals, one per epilogue warp
-    uint64_t* red_full = acc_empty + 2;   // every CTA of the cluster has parked its partial sums of the tile (4 S arrivals)
-    uint64_t* red_free = red_full + 1;    // every CTA of the cluster has read this CTA's partial sums (4 S arrivals)
+    uint64_t* acc_empty = acc_full + 2;   // one arrival per epilogue warp
+    uint64_t* red_full = acc_empty + 2;   // every CTA of the cluster has parked its partial sums of the tile
+    uint64_t* red_free = red_full + 1;    // every CTA of the cluster has read this CTA's partial sums
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_free + 1);
+    int* tok_qsum = reinterpret_cast<int*>(tmem_slot + 2);          // [2][NT] per-token sum of q and scale of the tile being drained
+    float* tok_sx = reinterpret_cast<float*>(tok_qsum + 2 * NT);    // (two copies: the row sets' warps may be one tile apart)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = (int)a.k_tiles;
-    const int row_sets = (int)((a.row_tiles + 7) / 8);
+    const int row_sets = (int)((a.row_tiles + 8 * RS - 1) / (8 * RS));   // tiles along the rows
     const int tok_blocks = (a.m + NT - 1) / NT;
     const int rank = S > 1 ? (int)ptx::cluster_ctarank() : 0;
     const int cid = blockIdx.x / S, n_clusters = gridDim.x / S;
@@ -109,9 +124,9 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1 + kUnpackWarps); }
         for (int u = 0; u < kABufs; ++u) { ptx::mbar_init(&a_full[u], kUnpackWarps); ptx::mbar_init(&a_empty[u], 1); }
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], 4); }
-        ptx::mbar_init(red_full, 4 * S);
-        ptx::mbar_init(red_free, 4 * S);
+        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], kEpiWarps); }
+        ptx::mbar_init(red_full, kEpiWarps * S);
+        ptx::mbar_init(red_free, kEpiWarps * S);
         ptx::mbar_fence_init();
     }
     if (warp == 1) {  // one warp allocates (and later frees) the tensor memory
@@ -125,25 +140,26 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t a_col0 = kAccCols;  // the unpacked-A buffers follow the accumulators
+    const uint32_t a_col0 = kAccCols;  // the unpacked-A buffers follow the accumulators: [buffer][row set][64]
 
     bool ok = true;
     if (warp == 0) {
-        // ---------------- producer ----------------
-        if (lane == 0) {
+        // ---------------- producer (whole warp: lane r8 requests row tile r8 of a chunk, so that the small copies are
+        //                  issued side by side; lane 0 also registers the byte count and requests the activation block) ----
+        {
             // The weights do not depend on earlier kernels: the first stages' weight tiles are requested before the
             // dependency wait, their activation blocks (written by the quantiser just before) after it.
             auto issue = [&](int tile, int kt, int slot, bool raw_part, bool b_part) {
                 const int rs = tile % row_sets, tb = tile / row_sets;
                 uint8_t* st = stage_base + (size_t)slot * kStageBytes;
-                const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
+                const int rts = min(8 * RS, (int)(a.row_tiles - (int64_t)rs * 8 * RS));
                 if (raw_part) {
-                    ptx::mbar_arrive_expect_tx(&full[slot], (uint32_t)(rts * kTileBytes + kBBytes));
-                    for (int r8 = 0; r8 < rts; ++r8)
-                        ptx::bulk_g2s(st + r8 * kTileBytes, a.tiles + (((int64_t)rs * 8 + r8) * k_tiles + kt) * kTileBytes, kTileBytes,
+                    if (lane == 0) ptx::mbar_arrive_expect_tx(&full[slot], (uint32_t)(rts * kTileBytes + kBBytes));
+                    if (lane < rts)
+                        ptx::bulk_g2s(st + lane * kTileBytes, a.tiles + (((int64_t)rs * 8 * RS + lane) * k_tiles + kt) * kTileBytes, kTileBytes,
                                       &full[slot]);
                 }
-                if (b_part) ptx::bulk_g2s(st + kRawBytes, a.qtc + ((int64_t)tb * k_tiles + kt) * kBBytes, kBBytes, &full[slot]);
+                if (b_part && lane == 0) ptx::bulk_g2s(st + kRawBytes, a.qtc + ((int64_t)tb * k_tiles + kt) * kBBytes, kBBytes, &full[slot]);
             };
             int g = 0;
             for (int tile = cid; tile < n_tiles && g < kStages; tile += n_clusters)
@@ -166,23 +182,26 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
             const uint32_t idesc = instr_desc_i8(kRows, NT);
             int g = 0, tl = 0;
             for (int tile = cid; tile < n_tiles; tile += n_clusters, ++tl) {
-                const int sel = tl & 1, acc_use = tl >> 1;
+                const int sel = tl % kAccSets, acc_use = tl / kAccSets;
                 if (acc_use > 0) ok &= ptx::mbar_wait_bounded(&acc_empty[sel], (uint32_t)((acc_use - 1) & 1));
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)sel * NT;
                 for (int kt = kt0; kt < kt1; ++kt, ++g) {
                     const int slot = g % kStages, u = g % kABufs;
                     ok &= ptx::mbar_wait_bounded(&full[slot], (uint32_t)((g / kStages) & 1));   // activation block landed
                     ok &= ptx::mbar_wait_bounded(&a_full[u], (uint32_t)((g / kABufs) & 1));     // weights unpacked into tensor memory
                     ptx::tc_fence_after();
                     const uint32_t b_addr = ptx::smem_u32(stage_base + (size_t)slot * kStageBytes + kRawBytes);
-                    const uint32_t a_tmem = tmem_base + a_col0 + (uint32_t)u * kAChunkCols;
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) {
+                    for (int h = 0; h < RS; ++h) {
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(sel * RS + h) * NT;
+                        const uint32_t a_tmem = tmem_base + a_col0 + (uint32_t)(u * RS + h) * kAChunkCols;
 #pragma unroll
-                        for (int ks = 0; ks < 2; ++ks) {  // 64 k' per residue = 2 x K32 = 2 x 8 TMEM columns
-                            const uint64_t bd = ptx::smem_desc(b_addr + r * (NT * 64) + ks * 256, 128, 512);
-                            ptx::umma_i8_ts(d_tmem, a_tmem + r * 16 + ks * 8, bd, idesc, (kt > kt0 || r > 0 || ks > 0) ? 1u : 0u);
+                        for (int r = 0; r < 4; ++r) {
+#pragma unroll
+                            for (int ks = 0; ks < 2; ++ks) {  // 64 k' per residue = 2 x K32 = 2 x 8 TMEM columns
+                                const uint64_t bd = ptx::smem_desc(b_addr + r * (NT * 64) + ks * 256, 128, 512);
+                                ptx::umma_i8_ts(d_tmem, a_tmem + r * 16 + ks * 8, bd, idesc, (kt > kt0 || r > 0 || ks > 0) ? 1u : 0u);
+                            }
                         }
                     }
                     ptx::umma_commit(&a_empty[u]);   // unpacked buffer reusable once these MMAs are done
@@ -194,26 +213,26 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
             ptx::pdl_launch_dependents();
         }
     } else if (warp < kEpiWarp0) {
-        // ---------------- unpack warps: a thread owns half of one weight row (= one TMEM lane) ----
+        // ---------------- unpack warps: a thread owns one weight row (= one TMEM lane) of one row set ----
         const int sub = warp & 3;                      // the TMEM lanes 32 sub .. 32 sub + 31 belong to this warp
-        const int hsel = (warp - 2) >> 2;              // which part of the row's 64 bytes: pieces t = PT hsel .. PT hsel + PT - 1
-        const int row = sub * 32 + lane;               // row inside the 128-row tile
+        const int h = (warp - 2) >> 2;                 // row set of the tile
+        const int row = sub * 32 + lane;               // row inside the set
         // the row: row tile r8 = row/16, half = (row%16)/8, g = row%8; its 64 packed bytes of a chunk are the four
         // 16-byte pieces t = 0..3 at ((half*32 + g*4 + t) * 16) of the row tile
-        const int r8 = row >> 4, half = (row >> 3) & 1, g8 = row & 7;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + a_col0 + 4 * PT * hsel;
+        const int r8 = h * 8 + (row >> 4), half = (row >> 3) & 1, g8 = row & 7;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + a_col0 + (uint32_t)h * kAChunkCols;
         ptx::pdl_wait();
         int g = 0;
         for (int tile = cid; tile < n_tiles; tile += n_clusters) {
             const int rs = tile % row_sets;
-            const int rts = min(8, (int)(a.row_tiles - (int64_t)rs * 8));
+            const int rts = min(8 * RS, (int)(a.row_tiles - (int64_t)rs * 8 * RS));
             for (int kt = kt0; kt < kt1; ++kt, ++g) {
                 const int slot = g % kStages, u = g % kABufs, a_use = g / kABufs;
                 ok &= ptx::mbar_wait_bounded(&full[slot], (uint32_t)((g / kStages) & 1));
-                const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g8 * 64 + hsel * (16 * PT);
-                uint4 w[PT];
+                const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g8 * 64;
+                uint4 w[4];
 #pragma unroll
-                for (int t = 0; t < PT; ++t) {
+                for (int t = 0; t < 4; ++t) {
                     w[t] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // weight 0 (rows beyond the matrix)
                     if (r8 < rts) w[t] = *reinterpret_cast<const uint4*>(raw + t * 16);
                 }
@@ -222,16 +241,15 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     // residue r: piece t holds the inputs 64 t .. 64 t + 63, i.e. k' = 16 t .. 16 t + 15 = columns 4 t .. 4 t + 3
-                    uint32_t v[4 * PT];
+                    uint32_t v[16];
 #pragma unroll
-                    for (int t = 0; t < PT; ++t) {
+                    for (int t = 0; t < 4; ++t) {
                         v[4 * t + 0] = (w[t].x >> (2 * r)) & 0x03030303u;
                         v[4 * t + 1] = (w[t].y >> (2 * r)) & 0x03030303u;
                         v[4 * t + 2] = (w[t].z >> (2 * r)) & 0x03030303u;
                         v[4 * t + 3] = (w[t].w >> (2 * r)) & 0x03030303u;
                     }
-                    if constexpr (PT == 4) ptx::tmem_st16(lane_addr + (uint32_t)u * kAChunkCols + r * 16, v);
-                    else ptx::tmem_st8(lane_addr + (uint32_t)u * kAChunkCols + r * 16, v);
+                    ptx::tmem_st16(lane_addr + (uint32_t)(u * RS) * kAChunkCols + r * 16, v);
                 }
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
@@ -243,9 +261,11 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
             }
         }
     } else {
-        // ---------------- epilogue warps (4 warps, TMEM lanes by warp % 4) ----------------
+        // ---------------- epilogue warps (4 per row set, TMEM lanes by warp % 4) ----------------
         const int sub = warp & 3;
-        const int lrow = sub * 32 + lane;  // row inside the tile
+        const int h = (warp - kEpiWarp0) >> 2;  // row set of the tile
+        const int lrow = sub * 32 + lane;       // row inside the set
+        int32_t* pb = pbuf + (size_t)h * (kRows * NT);
         ptx::pdl_wait();  // the output (and what EPI_F32_ACCUM adds to) belongs to earlier kernels until here
         // The old value of an accumulated output is fetched apart from its update, so that a thread's loads are all
         // in flight before the first store (a store followed by a load of the same array would serialise them);
@@ -254,14 +274,15 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
         auto load_old = [&](int token, int64_t row) -> float {
             return (accum && token < a.m && row < a.n_out) ? reinterpret_cast<const float*>(a.out)[(int64_t)token * a.out_stride + row] : 0.0f;
         };
-        auto store = [&](int token, int64_t row, float sw, uint32_t acc, float old) {
-            if (token < a.m && row < a.n_out) {
-                const int accv = (int)acc - __ldg(a.qsum + token);
-                const int64_t o = (int64_t)token * a.out_stride + row;
+        // i = token inside the tile; tq / ts = the tile's staged per-token terms
+        auto store = [&](const int* tq, const float* ts, int tb, int i, int n_tok, int64_t row, float sw, uint32_t acc, float old) {
+            if (i < n_tok && row < a.n_out) {
+                const int accv = (int)acc - tq[i];
+                const int64_t o = (int64_t)(tb * NT + i) * a.out_stride + row;
                 if (a.epilogue == EPI_I32) {
                     reinterpret_cast<int32_t*>(a.out)[o] = accv;
                 } else {
-                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), __ldg(a.sx + token));
+                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), ts[i]);
                     if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
                     else if (accum) reinterpret_cast<float*>(a.out)[o] = __fadd_rn(old, y);
                     else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
@@ -271,14 +292,30 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
         int tl = 0;
         for (int tile = cid; tile < n_tiles; tile += n_clusters, ++tl) {
             const int rs = tile % row_sets, tb = tile / row_sets;
-            const int sel = tl & 1;
-            ok &= ptx::mbar_wait_bounded(&acc_full[sel], (uint32_t)((tl >> 1) & 1));
+            const int sel = tl % kAccSets;
+            // the tile's per-token terms, once per row set's four warps into shared memory (named barrier 1 + h)
+            {
+                int* tq = tok_qsum + (tl & 1) * NT;
+                float* ts = tok_sx + (tl & 1) * NT;
+                if (h == 0 || RS == 1) {
+                    for (int i = lrow; i < NT; i += kRows) {
+                        const int token = tb * NT + i;
+                        tq[i] = token < a.m ? __ldg(a.qsum + token) : 0;
+                        ts[i] = (token < a.m && a.epilogue != EPI_I32) ? __ldg(a.sx + token) : 0.0f;
+                    }
+                }
+                ptx::named_bar_sync(1, kEpiWarps * 32);  // all epilogue warps: written before read, read before the tile after next overwrites
+            }
+            ok &= ptx::mbar_wait_bounded(&acc_full[sel], (uint32_t)((tl / kAccSets) & 1));
             ptx::tc_fence_after();
-            const int64_t row = (int64_t)rs * kRows + lrow;
+            const int* tq = tok_qsum + (tl & 1) * NT;
+            const float* ts = tok_sx + (tl & 1) * NT;
+            const int64_t row = ((int64_t)rs * RS + h) * kRows + lrow;
             const int64_t rt = row >> 4;
             float sw = 0.f;
             if (a.epilogue != EPI_I32 && rt < a.row_tiles) sw = __ldg(a.sw_tiles + 2 * rt + ((row >> 3) & 1));
-            const uint32_t acc_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)sel * NT;
+            const uint32_t acc_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(sel * RS + h) * NT;
+            const int n_tok = min(NT, a.m - tb * NT);  // tokens of this tile that exist
             if constexpr (S == 1) {
                 if (accum) {
 #pragma unroll 1
@@ -290,7 +327,7 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
                         for (int j = 0; j < 16; ++j) old[j] = load_old(tb * NT + c0 + j, row);
                         ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) store(tb * NT + c0 + j, row, sw, d[j], old[j]);
+                        for (int j = 0; j < 16; ++j) store(tq, ts, tb, c0 + j, n_tok, row, sw, d[j], old[j]);
                     }
                 } else {
 #pragma unroll 1
@@ -299,7 +336,7 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
                         ptx::tmem_ld32(acc_addr + c0, d);
                         ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) store(tb * NT + c0 + j, row, sw, d[j], 0.0f);
+                        for (int j = 0; j < 32; ++j) store(tq, ts, tb, c0 + j, n_tok, row, sw, d[j], 0.0f);
                     }
                 }
                 ptx::tc_fence_before();
@@ -307,8 +344,8 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
                 if (lane == 0) ptx::mbar_arrive(&acc_empty[sel]);
             } else {
                 // Reduce-scatter over the cluster: every CTA parks its partial sums of the whole tile in its own
-                // shared memory ([token / 4][row][token % 4], 16 bytes per thread and step), then adds up and stores
-                // the NT / S tokens that are its share, reading all S copies through distributed shared memory.
+                // shared memory ([row set][token / 4][row][token % 4], 16 bytes per thread and step), then adds up and
+                // stores the NT / S tokens that are its share, reading all S copies through distributed shared memory.
                 if (tl > 0) ok &= ptx::mbar_wait_cluster_bounded(red_free, (uint32_t)((tl - 1) & 1));  // everybody has read the previous tile
 #pragma unroll 1
                 for (int c0 = 0; c0 < NT; c0 += 32) {
@@ -317,14 +354,14 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int q = 0; q < 8; ++q)
-                        *reinterpret_cast<uint4*>(pbuf + ((size_t)(c0 / 4 + q) * kRows + lrow) * 4) =
+                        *reinterpret_cast<uint4*>(pb + ((size_t)(c0 / 4 + q) * kRows + lrow) * 4) =
                             make_uint4(d[4 * q], d[4 * q + 1], d[4 * q + 2], d[4 * q + 3]);
                 }
                 ptx::tc_fence_before();
                 ptx::fence_cluster();
                 __syncwarp();
                 if (lane == 0) {
-                    ptx::mbar_arrive(&acc_empty[sel]);  // the accumulator set is free for the tile after next
+                    ptx::mbar_arrive(&acc_empty[sel]);  // the accumulator set is free for a later tile
 #pragma unroll
                     for (int pr = 0; pr < S; ++pr) ptx::mbar_arrive_remote(ptx::map_to_rank(red_full, (uint32_t)pr));
                 }
@@ -341,7 +378,7 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
 #pragma unroll
                         for (int pr = 0; pr < S; ++pr)
                             part[q][pr] = ptx::ld_dsmem_v4(
-                                ptx::map_to_rank(pbuf + ((size_t)(rank * kGroups + q0 + q) * kRows + lrow) * 4, (uint32_t)pr));
+                                ptx::map_to_rank(pb + ((size_t)(rank * kGroups + q0 + q) * kRows + lrow) * 4, (uint32_t)pr));
 #pragma unroll
                     for (int q = 0; q < kBatch; ++q)
 #pragma unroll
@@ -353,11 +390,11 @@ __global__ void __launch_bounds__(tc_threads(UW), 1) gemm_tc_kernel(TcArgs a) {
                         for (int pr = 1; pr < S; ++pr) {
                             s.x += part[q][pr].x; s.y += part[q][pr].y; s.z += part[q][pr].z; s.w += part[q][pr].w;
                         }
-                        const int token = tb * NT + (rank * kGroups + q0 + q) * 4;
-                        store(token, row, sw, s.x, old[q][0]);
-                        store(token + 1, row, sw, s.y, old[q][1]);
-                        store(token + 2, row, sw, s.z, old[q][2]);
-                        store(token + 3, row, sw, s.w, old[q][3]);
+                        const int i = (rank * kGroups + q0 + q) * 4;
+                        store(tq, ts, tb, i, n_tok, row, sw, s.x, old[q][0]);
+                        store(tq, ts, tb, i + 1, n_tok, row, sw, s.y, old[q][1]);
+                        store(tq, ts, tb, i + 2, n_tok, row, sw, s.z, old[q][2]);
+                        store(tq, ts, tb, i + 3, n_tok, row, sw, s.w, old[q][3]);
                     }
                 }
                 __syncwarp();
@@ -424,23 +461,20 @@ __global__ void __launch_bounds__(256) act_quant_tc_kernel(const T* __restrict__
     }
 }
 
-constexpr int kUnpackWarps = 4;
-
-// One kernel variant (token tile NT, S CTAs per cluster): its shared memory and how many clusters fit on the GPU
-// at once (a cluster lives inside one GPC, so this is not SMs / S), asked of the runtime once.
+// One kernel variant (token tile NT, RS row sets per tile, S CTAs per cluster): its shared memory and how many
+// clusters fit on the GPU at once (a cluster lives inside one GPC, so this is not SMs / S), asked of the runtime once.
 struct TcVariant {
     size_t smem = 0;
     int max_clusters = 0;
     cudaError_t status = cudaErrorNotReady;
 };
 
-template <int NT, int S>
+template <int NT, int RS, int S>
 const TcVariant& tc_variant(int sm_count) {
     static TcVariant v;              // cluster limit: once per process (every device of a process is the same GPU model)
     static PerDeviceOnce attributes;  // the kernel's shared-memory limit: once per device
-    constexpr int kBBytes = 4 * NT * 64;
-    v.smem = (size_t)kStages * (kRawBytes + kBBytes) + (S > 1 ? kRows * NT * 4 : 0) + 256;
-    auto* kernel = gemm_tc_kernel<NT, kUnpackWarps, S>;
+    v.smem = (size_t)tc_stages(NT, RS, S) * (RS * kSetBytes + 4 * NT * 64) + (S > 1 ? RS * kRows * NT * 4 : 0) + 512 + 16 * NT;
+    auto* kernel = gemm_tc_kernel<NT, RS, S>;
     const size_t smem = v.smem;
     v.status = attributes.run([kernel, smem] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
     if (v.status != cudaSuccess) return v;
@@ -450,7 +484,7 @@ const TcVariant& tc_variant(int sm_count) {
     if (S == 1) { v.max_clusters = sm_count; return v; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(sm_count / S * S));
-    cfg.blockDim = dim3(tc_threads(kUnpackWarps));
+    cfg.blockDim = dim3(tc_threads(RS));
     cfg.dynamicSmemBytes = v.smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -466,14 +500,15 @@ const TcVariant& tc_variant(int sm_count) {
     return v;
 }
 
-template <int NT, int S>
-cudaError_t launch_variant(TcArgs a, int n_tiles, int sm_count, cudaStream_t stream) {
-    const TcVariant& v = tc_variant<NT, S>(sm_count);
+template <int NT, int RS, int S>
+cudaError_t launch_variant(TcArgs a, int sm_count, cudaStream_t stream) {
+    const TcVariant& v = tc_variant<NT, RS, S>(sm_count);
     if (v.status != cudaSuccess) return v.status;
+    const int n_tiles = (int)((a.row_tiles + 8 * RS - 1) / (8 * RS)) * ((a.m + NT - 1) / NT);
     const int n_clusters = v.max_clusters < n_tiles ? v.max_clusters : n_tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(n_clusters * S));
-    cfg.blockDim = dim3(tc_threads(kUnpackWarps));
+    cfg.blockDim = dim3(tc_threads(RS));
     cfg.dynamicSmemBytes = v.smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -483,7 +518,7 @@ cudaError_t launch_variant(TcArgs a, int n_tiles, int sm_count, cudaStream_t str
     attr[1].val.clusterDim.x = (unsigned)S; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = S > 1 ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<NT, kUnpackWarps, S>, a);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<NT, RS, S>, a);
 }
 
 // Chunk steps on the busiest CTA when a tile's k range is cut over `s` CTAs (one step charged for the exchange of
@@ -497,25 +532,31 @@ int64_t tc_split_cost(int s, int max_clusters, int n_tiles, int64_t k_tiles) {
 }
 
 cudaError_t launch_product(TcArgs a, int nt, int sm_count, cudaStream_t stream) {
-    const int row_sets = (int)((a.row_tiles + 7) / 8);
-    const int n_tiles = row_sets * ((a.m + nt - 1) / nt);
-    if (nt == 128) return launch_variant<128, 1>(a, n_tiles, sm_count, stream);
-    // 64 tokens at most: with few output tiles, cut k over a cluster so that one wave of CTAs covers the product
+    const int tok_blocks = (a.m + nt - 1) / nt;
+    const int n_tiles = (int)((a.row_tiles + 7) / 8) * tok_blocks;          // tiles of 128 rows
+    const int n_tiles2 = (int)((a.row_tiles + 15) / 16) * tok_blocks;       // tiles of 256 rows
+    if (nt == 128) {
+        // 256-row tiles halve the activation traffic per weight; 128-row tiles when there is too little work for them
+        return 2 * n_tiles2 >= sm_count ? launch_variant<128, 2, 1>(a, sm_count, stream) : launch_variant<128, 1, 1>(a, sm_count, stream);
+    }
+    // 64 tokens at most.  More 128-row tiles than SMs: 256-row tiles.  Fewer than half: cut k over a cluster so that
+    // one wave of CTAs covers the product.
+    if (n_tiles > sm_count) return launch_variant<64, 2, 1>(a, sm_count, stream);
     int best = 1;
     int64_t best_cost = tc_split_cost(1, sm_count, n_tiles, a.k_tiles);
     if (n_tiles * 2 <= sm_count) {
-        const int64_t c2 = tc_split_cost(2, tc_variant<64, 2>(sm_count).max_clusters, n_tiles, a.k_tiles);
-        const int64_t c4 = tc_split_cost(4, tc_variant<64, 4>(sm_count).max_clusters, n_tiles, a.k_tiles);
-        const int64_t c8 = tc_split_cost(8, tc_variant<64, 8>(sm_count).max_clusters, n_tiles, a.k_tiles);
+        const int64_t c2 = tc_split_cost(2, tc_variant<64, 1, 2>(sm_count).max_clusters, n_tiles, a.k_tiles);
+        const int64_t c4 = tc_split_cost(4, tc_variant<64, 1, 4>(sm_count).max_clusters, n_tiles, a.k_tiles);
+        const int64_t c8 = tc_split_cost(8, tc_variant<64, 1, 8>(sm_count).max_clusters, n_tiles, a.k_tiles);
         if (c2 < best_cost) { best = 2; best_cost = c2; }
         if (c4 < best_cost) { best = 4; best_cost = c4; }
         if (c8 < best_cost) { best = 8; best_cost = c8; }
     }
     switch (best) {
-        case 2: return launch_variant<64, 2>(a, n_tiles, sm_count, stream);
-        case 4: return launch_variant<64, 4>(a, n_tiles, sm_count, stream);
-        case 8: return launch_variant<64, 8>(a, n_tiles, sm_count, stream);
-        default: return launch_variant<64, 1>(a, n_tiles, sm_count, stream);
+        case 2: return launch_variant<64, 1, 2>(a, sm_count, stream);
+        case 4: return launch_variant<64, 1, 4>(a, sm_count, stream);
+        case 8: return launch_variant<64, 1, 8>(a, sm_count, stream);
+        default: return launch_variant<64, 1, 1>(a, sm_count, stream);
     }
 }
 
