@@ -78,6 +78,8 @@ struct AttnArgs {
     bool pdl;                  // launch with programmatic stream serialisation
 };
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t stream);
+cudaError_t launch_row_quant_bf16(const __nv_bfloat16* x, int64_t x_stride, int batch, int k, float* s, int32_t* qsum,
+                                  cudaStream_t stream, int8_t* qtc, int k_tiles);
 // Spans per (sequence, KV head) and positions per span for a cache of max_seq positions; rep = query
 // heads per KV head (selects the kernel instance whose cluster limit applies).
 void attn_plan(int64_t batch, int64_t n_kv, int64_t max_seq, int sm_count, int rep, int* splits, int* span);

@@ -414,53 +414,6 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     }
 }
 
-// Per-token absmax int8 quantiser writing the residue-split, core-matrix-ordered layout that
-// gemm_tc_kernel copies in bulk: [token_block][k_tile][residue][token_group][kc][token%8][16].
-__device__ __forceinline__ float load_act(const float* p) { return *p; }
-__device__ __forceinline__ float load_act(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-
-template <int NT, typename T>
-__global__ void __launch_bounds__(256) act_quant_tc_kernel(const T* __restrict__ x, int64_t x_stride, int k,
-                                                           int k_tiles, int m, int8_t* __restrict__ qtc,
-                                                           float* __restrict__ s_out, int32_t* __restrict__ qsum_out) {
-    __shared__ float red_f[32];
-    __shared__ int red_i[32];
-    ptx::pdl_wait();               // x belongs to earlier kernels until here
-    ptx::pdl_launch_dependents();  // the product behind this kernel may fetch its weights meanwhile
-    const int token = blockIdx.x;  // grid covers the padded token count
-    const int tb = token / NT, tin = token % NT;
-    int8_t* blk = qtc + (int64_t)tb * k_tiles * (4 * NT * 64);
-    const bool real = token < m;
-    const T* xr = x + (int64_t)(real ? token : 0) * x_stride;
-    float amax = 0.0f;
-    if (real)
-        for (int c = threadIdx.x; c < k; c += blockDim.x) amax = fmaxf(amax, fabsf(load_act(xr + c)));
-    // block max
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) red_f[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = 0.0f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) amax = fmaxf(amax, red_f[w]);
-    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    int local = 0;
-    const int k_pad = k_tiles * kChunkK;
-    for (int c = threadIdx.x; c < k_pad; c += blockDim.x) {
-        int qv = 0;
-        if (real && c < k) qv = max(-127, min(127, ptx::round_half_away(__fmul_rn(load_act(xr + c), inv))));
-        local += qv;
-        blk[gemm_tc_act_offset(c, tin, NT)] = (int8_t)qv;
-    }
-    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-    if ((threadIdx.x & 31) == 0) red_i[threadIdx.x >> 5] = local;
-    __syncthreads();
-    if (threadIdx.x == 0 && real) {
-        int tot = 0;
-        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red_i[w];
-        s_out[token] = __fdiv_rn(amax, 127.0f);
-        qsum_out[token] = tot;
-    }
-}
-
 // One kernel variant (token tile NT, RS row sets per tile, S CTAs per cluster): its shared memory and how many
 // clusters fit on the GPU at once (a cluster lives inside one GPC, so this is not SMs / S), asked of the runtime once.
 struct TcVariant {
@@ -577,14 +530,11 @@ cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride
                            cudaStream_t stream, bool prequantised, bt_dtype x_dtype) {
     if (lin.w.n_bases != 1 && epilogue == EPI_BF16) return cudaErrorInvalidValue;
     const int nt = m <= 64 ? 64 : 128;
-    const int padded = (int)((m + nt - 1) / nt * nt);
     const int k = (int)lin.w.k_in, kts = (int)lin.w.k_tiles;
     cudaError_t e = cudaSuccess;
     if (prequantised) {
     } else if (x_dtype == BT_BF16) {
-        const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-        e = nt == 64 ? launch_pdl(act_quant_tc_kernel<64, __nv_bfloat16>, dim3(padded), dim3(256), 0, stream, true, xb, x_stride, k, kts, (int)m, qtc, sx, qsum)
-                     : launch_pdl(act_quant_tc_kernel<128, __nv_bfloat16>, dim3(padded), dim3(256), 0, stream, true, xb, x_stride, k, kts, (int)m, qtc, sx, qsum);
+        e = launch_row_quant_bf16(reinterpret_cast<const __nv_bfloat16*>(x), x_stride, (int)m, k, sx, qsum, stream, qtc, kts);
     } else {
         // f32 rows: the row kernel of the decode step (identity transform); rows of a partly filled token block
         // keep whatever they held, their output columns are never stored

@@ -106,13 +106,22 @@ __device__ __forceinline__ float4 load4(const float* p, bool vec) {
     if (vec) return *reinterpret_cast<const float4*>(p);
     return make_float4(p[0], p[1], p[2], p[3]);
 }
+// The same from bf16 values (`vec` = 16-byte aligned row start; a group of four is then 8-byte aligned).
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p, bool vec) {
+    if (vec) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                           __uint_as_float(u.y & 0xffff0000u));
+    }
+    return make_float4(__bfloat162float(p[0]), __bfloat162float(p[1]), __bfloat162float(p[2]), __bfloat162float(p[3]));
+}
 
 // k must be a multiple of 4 (the packed weight layouts require it anyway).  A thread works on groups of four
 // consecutive values; in the tensor-core layout these are the four residues of one k' (see gemm_tc_act_offset),
 // which are first laid out in shared memory in the order of that layout's 16-byte pieces and then copied out a
 // piece per thread.
-template <int PRE>
-__global__ void __launch_bounds__(1024) row_quant_kernel(const float* __restrict__ x, int64_t x_stride,
+template <int PRE, typename T = float>
+__global__ void __launch_bounds__(1024) row_quant_kernel(const T* __restrict__ x, int64_t x_stride,
                                                          const float* __restrict__ w, float eps, int k,
                                                          int8_t* __restrict__ q, int64_t q_stride,
                                                          float* __restrict__ s_out,
@@ -131,7 +140,7 @@ __global__ void __launch_bounds__(1024) row_quant_kernel(const float* __restrict
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();  // a product launched behind this kernel may fetch its weights meanwhile
     const int b = blockIdx.x;
-    const float* xr = x + (int64_t)b * x_stride;
+    const T* xr = x + (int64_t)b * x_stride;
     const bool xvec = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
     const bool wvec = PRE == PRE_RMSNORM && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     const int groups = k >> 2;
@@ -482,6 +491,22 @@ cudaError_t launch_row_quant(int pre, const float* x, int64_t x_stride, const fl
     if (pre == PRE_SWIGLU)
         return launch_pdl(row_quant_kernel<PRE_SWIGLU>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles, amax_in, amax_out);
     return launch_pdl(row_quant_kernel<PRE_NONE>, grid, block, smem, stream, false, x, x_stride, w, eps, k, q, q_stride, s, qsum, v_out, qtc, tc_nt, k_tiles, amax_in, amax_out);
+}
+
+// Identity transform + quantiser on bf16 rows, into the tensor-core product's layout.
+cudaError_t launch_row_quant_bf16(const __nv_bfloat16* x, int64_t x_stride, int batch, int k, float* s, int32_t* qsum,
+                                  cudaStream_t stream, int8_t* qtc, int k_tiles) {
+    const int tc_nt = batch <= 64 ? 64 : 128;
+    if (k % 4 != 0 || !qtc) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)k * sizeof(float) + (size_t)k_tiles * kTileK;
+    const int threads = k >= 4096 ? 1024 : (k >= 2048 ? 512 : 256);
+    static PerDeviceOnce once;
+    cudaError_t ce = once.run([] { return cudaFuncSetAttribute(row_quant_kernel<PRE_NONE, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
+    if (ce != cudaSuccess) return ce;
+    if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+    return launch_pdl(row_quant_kernel<PRE_NONE, __nv_bfloat16>, dim3((unsigned)batch), dim3((unsigned)threads), smem, stream, false, x, x_stride,
+                      (const float*)nullptr, 0.0f, k, (int8_t*)nullptr, (int64_t)0, s, qsum, (float*)nullptr, qtc, tc_nt, k_tiles,
+                      (const unsigned int*)nullptr, (unsigned int*)nullptr);
 }
 
 cudaError_t launch_argmax(const float* logits, int batch, int vocab, int32_t* out, cudaStream_t stream) {
