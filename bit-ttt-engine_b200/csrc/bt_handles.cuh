@@ -54,6 +54,9 @@ bt_status tp_comm_init(void** comm, const void* id128, int rank, int size);
 void tp_comm_destroy(void* comm);
 bt_status tp_allreduce_max_f32(void* comm, float* buf, size_t count, cudaStream_t s);
 bt_status tp_allreduce_sum_i32(void* comm, int32_t* buf, size_t count, cudaStream_t s);
+bool tp_allgather_available();
+bt_status tp_allgather_f32(void* comm, float* buf, size_t count, int rank, cudaStream_t s);
+cudaError_t launch_tp_logits_rows(const float* parts, int tp, int batch, int64_t vl, int64_t vocab, float* full, cudaStream_t s);
 cudaError_t launch_tp_residual(const int32_t* acc, const unsigned int* absmax, float sw, int m, int n, float* h,
                                cudaStream_t s, bool pdl);
 // exchange over NVLink peer memory (CUDA IPC between the ranks' processes) instead of NCCL

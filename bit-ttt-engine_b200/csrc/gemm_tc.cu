@@ -36,11 +36,9 @@ namespace bt {
 namespace {
 
 constexpr int kRows = 128;               // weight rows per MMA = UMMA M = TMEM lanes
-constexpr int kChunkK = 256;             // inputs per k-chunk (one weight tile column)
 constexpr int kSetBytes = 8 * kTileBytes;  // packed weights of 128 rows of a chunk: 8 row tiles x 1 KB
 constexpr int kABufs = 2;                // unpacked-A buffers in tensor memory
 constexpr int kAChunkCols = 64;          // TMEM columns of one unpacked 128-row chunk: 4 residues x 64 bytes / 4
-constexpr int kMaxSplit = 8;             // CTAs of one cluster that share a tile along k
 constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
 
 // A tile is RS x 128 weight rows x NT tokens: the RS row sets share every activation block, which is what a CTA

@@ -99,6 +99,8 @@ struct bt_model {
     int8_t* qtc = nullptr;           // activations in the tensor-core product's layout (batches above 8)
     void* lm_tiles = nullptr;        // lm_head in tensor-core tile order (batches above 8, hidden % 64 == 0)
     void* lm_btiles = nullptr;       // normalised hidden states as bf16 hi|lo tiles
+    float* lm_gather = nullptr;      // tensor parallelism: the ranks' vocabulary slices of the logits, [tp][batch][vl]
+    int64_t vl = 0;                  // rows of the head per rank (multiple of 128)
     unsigned int* absmax = nullptr;  // [num_layers][2][max_batch] max|x| cells of the fused path
     float* cand_val = nullptr;
     int32_t* cand_idx = nullptr;
@@ -221,6 +223,8 @@ cudaError_t trace_copy(const bt_model* m, int layer, int slot, const float* src,
     return cudaMemcpyAsync(dst, src, (size_t)rows * w[slot] * sizeof(float), cudaMemcpyDeviceToDevice, s);
 }
 
+bt_status enqueue_head(bt_model* m, int batch, cudaStream_t s, bool fused_launches);
+
 bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
     const bt_model_config& c = m->cfg;
     const int H = c.hidden_dim, I = m->i_l, B = c.max_batch;
@@ -311,10 +315,52 @@ bt_status enqueue_step_fused(bt_model* m, int batch, cudaStream_t s) {
         }
         BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
     }
+    return enqueue_head(m, batch, s, true);
+}
+
+// logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance.  Under tensor parallelism with
+// an NCCL communicator every rank computes the vocabulary rows rank * vl .. (the weights stay replicated in memory,
+// the reading and the arithmetic are split), the slices are all-gathered and every rank picks from the full row.
+bt_status enqueue_head(bt_model* m, int batch, cudaStream_t s, bool fused_launches) {
+    const bt_model_config& c = m->cfg;
+    const int H = c.hidden_dim, B = c.max_batch;
+    unsigned int* err = device_error_word(m->device);
+    const int sm = m->sm_count;
+    const bool tc = m->lm_tiles && batch > 8;
+    if (m->tp > 1 && m->comm && m->lm_gather) {
+        const int64_t v0 = (int64_t)c.tp_rank * m->vl;
+        const int64_t n_loc = c.vocab_size - v0 < m->vl ? c.vocab_size - v0 : m->vl;
+        float* mine = m->lm_gather + (size_t)c.tp_rank * batch * m->vl;
+        if (n_loc > 0) {
+            if (tc) {
+                const uint8_t* tiles = reinterpret_cast<const uint8_t*>(m->lm_tiles) + lm_head_tc_weight_bytes(v0, H);
+                BT_CUDA_TRY(launch_lm_head_tc(tiles, m->h, m->norm_f, kRmsEps, batch, H, n_loc, m->lm_btiles, mine, err, sm, s, m->head_f16));
+            } else {
+                int n_cand = 0;
+                BT_CUDA_TRY(launch_lm_head_fused(m->lm_head + (size_t)v0 * H, m->h, m->norm_f, kRmsEps, batch, H, n_loc, mine,
+                                                 m->cand_val, m->cand_idx, &n_cand, sm, s, fused_launches, m->head_f16));
+            }
+        }
+        bt_status st = tp_allgather_f32(m->comm, m->lm_gather, (size_t)batch * m->vl, c.tp_rank, s);
+        if (st != BT_OK) return st;
+        BT_CUDA_TRY(launch_tp_logits_rows(m->lm_gather, m->tp, batch, m->vl, c.vocab_size, m->logits, s));
+        BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
+        advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, B);
+        BT_CUDA_TRY(cudaGetLastError());
+        return BT_OK;
+    }
+    if (tc) {
+        BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
+                                      err, sm, s, m->head_f16));
+        BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
+        advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, B);
+        BT_CUDA_TRY(cudaGetLastError());
+        return BT_OK;
+    }
     int n_cand = 0;
     BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
-                                     m->cand_val, m->cand_idx, &n_cand, sm, s, true, m->head_f16));
-    BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, true));
+                                     m->cand_val, m->cand_idx, &n_cand, sm, s, fused_launches, m->head_f16));
+    BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, fused_launches));
     return BT_OK;
 }
 
@@ -402,20 +448,7 @@ bt_status enqueue_step(bt_model* m, int batch, cudaStream_t s) {
         }
         BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
     }
-    // logits = lm_head(norm(h))  (model/llama.rs:256-266), greedy pick, position advance
-    if (m->lm_tiles) {
-        BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
-                                      err, sm, s, m->head_f16));
-        BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
-        advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, B);
-        BT_CUDA_TRY(cudaGetLastError());
-        return BT_OK;
-    }
-    int n_cand = 0;
-    BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
-                                     m->cand_val, m->cand_idx, &n_cand, sm, s, false, m->head_f16));
-    BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, false));
-    return BT_OK;
+    return enqueue_head(m, batch, s, false);
 }
 
 // One decode step with every stage as its own kernel: row transform + quantiser, then the product of every
@@ -488,19 +521,7 @@ bt_status enqueue_step_generic(bt_model* m, int batch, cudaStream_t s) {
         BT_CUDA_TRY(launch_residual_add(m->h, tmp, (int64_t)batch * H, s));
         BT_CUDA_TRY(trace_copy(m, li, TR_H_OUT, m->h, batch, s));
     }
-    if (m->lm_tiles && tc) {
-        BT_CUDA_TRY(launch_lm_head_tc(m->lm_tiles, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->lm_btiles, m->logits,
-                                      err, sm, s, m->head_f16));
-        BT_CUDA_TRY(launch_argmax(m->logits, batch, c.vocab_size, m->next, s));
-        advance_pos_kernel<<<1, 64, 0, s>>>(m->pos, B);
-        BT_CUDA_TRY(cudaGetLastError());
-        return BT_OK;
-    }
-    int n_cand = 0;
-    BT_CUDA_TRY(launch_lm_head_fused(m->lm_head, m->h, m->norm_f, kRmsEps, batch, H, c.vocab_size, m->logits,
-                                     m->cand_val, m->cand_idx, &n_cand, sm, s, false, m->head_f16));
-    BT_CUDA_TRY(launch_pick(m->cand_val, m->cand_idx, n_cand, batch, m->next, m->pos, B, s, false));
-    return BT_OK;
+    return enqueue_head(m, batch, s, false);
 }
 
 }  // namespace
@@ -706,6 +727,10 @@ extern "C" bt_status bt_model_finalize(bt_model* m) {
         BT_CUDA_TRY(launch_rope_tables(m->inv_freq, c.max_position_embeddings, m->head_dim / 2, m->rope_cos, m->rope_sin, 0));
         BT_CUDA_TRY(cudaDeviceSynchronize());
         if (m->tp > 1) BT_CUDA_TRY(dev_alloc(&m->acc_i32, (size_t)B * H));
+        if (m->tp > 1 && tp_allgather_available()) {
+            m->vl = ((c.vocab_size + m->tp - 1) / m->tp + 127) / 128 * 128;
+            BT_CUDA_TRY(dev_alloc(&m->lm_gather, (size_t)m->tp * B * m->vl));
+        }
     } else {
         BT_CUDA_TRY(dev_alloc(&m->feat, (size_t)B * m->d_small));
         BT_CUDA_TRY(dev_alloc(&m->z, (size_t)B * m->d_small));
@@ -732,7 +757,7 @@ extern "C" bt_status bt_model_destroy(bt_model* m) {
         cudaFree(L.norm1); cudaFree(L.norm2); cudaFree(L.w_state);
     }
     void* bufs[] = {m->embed, m->lm_head, m->norm_f, m->inv_freq, m->tokens, m->pos, m->h, m->q, m->sx, m->qsum,
-                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles};
+                    m->qkv, m->att, m->gu, m->feat, m->z, m->xn, m->logits, m->next, m->act, m->absmax, m->cand_val, m->cand_idx, m->rope_cos, m->rope_sin, m->acc_i32, m->xt, m->qtc, m->lm_tiles, m->lm_btiles, m->lm_gather};
     for (void* p : bufs) cudaFree(p);
     for (void* p : {(void*)m->pf_tokens, (void*)m->pf_h, (void*)m->pf_qkv, (void*)m->pf_att, (void*)m->pf_gu, (void*)m->pf_qtc,
                     (void*)m->pf_sx, (void*)m->pf_qsum, (void*)m->pf_act}) cudaFree(p);

@@ -37,6 +37,7 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;  // optional
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     bool ok = false;
 };
@@ -56,6 +57,7 @@ NcclApi* nccl_api() {
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(h, "ncclAllReduce"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
     api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GetErrorString;
     return api.ok ? &api : nullptr;
 }
@@ -263,6 +265,37 @@ bt_status tp_allreduce_sum_i32(void* comm, int32_t* buf, size_t count, cudaStrea
     ncclResult_t r = api->AllReduce(buf, buf, count, ncclInt32, ncclSum, reinterpret_cast<ncclComm_t>(comm), s);
     if (r != ncclSuccess) return set_error(BT_ERR_NCCL, "ncclAllReduce(sum): %s", api->GetErrorString(r));
     return BT_OK;
+}
+
+bool tp_allgather_available() {
+    NcclApi* api = nccl_api();
+    return api && api->AllGather;
+}
+
+// In-place all-gather of `count` floats per rank: rank r's part lies at buf + r * count on every rank.
+bt_status tp_allgather_f32(void* comm, float* buf, size_t count, int rank, cudaStream_t s) {
+    NcclApi* api = nccl_api();
+    if (!api || !api->AllGather) return set_error(BT_ERR_NCCL, "ncclAllGather is not available");
+    ncclResult_t r = api->AllGather(buf + (size_t)rank * count, buf, count, ncclFloat32, reinterpret_cast<ncclComm_t>(comm), s);
+    if (r != ncclSuccess) return set_error(BT_ERR_NCCL, "ncclAllGather: %s", api->GetErrorString(r));
+    return BT_OK;
+}
+
+// full[b][r * vl + j] = parts[r][b][j]: the vocabulary slices of the ranks (rank r computed rows r * vl .. of the
+// head, n_r = min(vl, vocab - r * vl) of them, stored [batch][n_r] at parts + r * batch * vl) side by side.
+__global__ void tp_logits_rows_kernel(const float* __restrict__ parts, int tp, int batch, int64_t vl, int64_t vocab,
+                                      float* __restrict__ full) {
+    const int b = blockIdx.y;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < vocab; v += (int64_t)gridDim.x * blockDim.x) {
+        const int r = (int)(v / vl);
+        const int64_t n_r = vocab - r * vl < vl ? vocab - r * vl : vl;
+        full[(int64_t)b * vocab + v] = parts[((int64_t)r * batch) * vl + (int64_t)b * n_r + (v - r * vl)];
+    }
+}
+
+cudaError_t launch_tp_logits_rows(const float* parts, int tp, int batch, int64_t vl, int64_t vocab, float* full, cudaStream_t s) {
+    tp_logits_rows_kernel<<<dim3(148, batch), 256, 0, s>>>(parts, tp, batch, vl, vocab, full);
+    return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------------------
