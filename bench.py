@@ -239,6 +239,7 @@ def run_sweep(bt, device):
                                       "int8 peak taken as twice the measured bf16 GEMM rate (derived, not measured)"}),
                   flush=True)
         del lins
+    run_cpu_cases(bt, device)
     # TTT fast-weight update: S independent 64x64 states, mini-batch 16
     for s_cnt in (4, 64, 1024, 8192):
         w = torch.zeros(s_cnt, 64, 64, device="cuda")
@@ -261,6 +262,94 @@ def run_sweep(bt, device):
         print(json.dumps({"sweep": "ttt_update", "states": s_cnt, "d": 64, "chunk": 16, "us": us,
                           "updates_per_s": s_cnt / us * 1e6, "GBps": byts / us / 1e3, "hbm_frac": byts / us / 1e3 / peak}),
               flush=True)
+
+
+def run_cpu_cases(bt, device):
+    """The two configurations the reference can run on a CPU, GPU library beside the CPU port on this host:
+    (1) one BitLinear forward, 2048 x 2048 ternary weights, 8 tokens of f32 activations (plus the reference
+    micro-benchmark's own shape, 8192 x 8192 with one token, bin/bench_cpu_kernel.rs:15-17), 10 warm-ups and
+    100 iterations as in bin/bench_cpu_kernel.rs:54-69; (2) the tiny TTT model (4 blocks, hidden 256, MLP 688,
+    vocabulary 32000): prompt of 32 ids, then 128 greedy steps at batch 1."""
+    import ctypes as C
+    import torch
+    from oracle import oracle as orc
+    syn = importlib.import_module("bit-ttt-engine_b200.synthetic")
+    L = bt.lib()
+    for (n, k, m) in [(2048, 2048, 8), (8192, 8192, 1)]:
+        rng = np.random.default_rng(1234)
+        wt = rng.integers(-1, 2, size=(n, k)).astype(np.float32) * 0.016
+        packed, scale = orc.pack_l1(wt)
+        x = np.random.default_rng(1235).normal(0, 1, (m, k)).astype(np.float32)
+        for _ in range(10):
+            y_cpu = orc.bitlinear_f32(x, packed, n, scale)
+        t0 = time.perf_counter()
+        for _ in range(100):
+            y_cpu = orc.bitlinear_f32(x, packed, n, scale)
+        cpu_us = (time.perf_counter() - t0) / 100 * 1e6
+        y_q = orc.bitlinear_q(x, packed, [scale], n)  # the quantised pipeline the library implements
+        lin = bt.BitLinear.from_packed(packed.reshape(n, k // 4), [scale], n, k, device=device)
+        ws = bt.Workspace(device, 64 << 20)
+        xd = torch.from_numpy(x).cuda()
+        yd = torch.empty(m, n, device="cuda")
+
+        def run():
+            bt.check(L.bt_linear_forward(lin._h, ws._h, C.c_void_p(xd.data_ptr()), m, k, bt.BT_F32, C.c_void_p(yd.data_ptr()),
+                                         bt.BT_F32, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        run()
+        torch.cuda.synchronize()
+        exact = bool(np.array_equal(yd.cpu().numpy(), y_q))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                run()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        gpu_us = e0.elapsed_time(e1) * 1e3 / 100
+        byts = m * k * 4 + n * k / 4 + m * n * 4  # bin/bench_cpu_kernel.rs:87-91
+        print(json.dumps({"sweep": "cpu_case_bitlinear", "N": n, "K": k, "M": m, "gpu_us": gpu_us, "cpu_us": cpu_us,
+                          "cpu_threads": int(orc.lib().oracle_num_threads()), "cpu_GBps": byts / cpu_us / 1e3,
+                          "gpu_GBps": byts / gpu_us / 1e3, "gpu_equals_quantised_oracle_bit_for_bit": exact,
+                          "max_rel_diff_quantised_vs_f32_reference": float(np.abs(y_q - y_cpu).max() / np.abs(y_cpu).max()),
+                          "note": "cpu = restated BitLinearCpu::forward, f32 activations; gpu = quantiser + product, weights in L2 "
+                                  "(one small matrix replayed)"}), flush=True)
+    cfg = syn.TINY_TTT
+    w = syn.make_weights(cfg, seed=2000)
+    model = syn.build_model(w, max_batch=1, device=device)
+    ref = orc.model_from_weights(w)
+    prompt = np.random.default_rng(7).integers(0, cfg.vocab_size, size=32).astype(np.int32)
+
+    def gpu_run():
+        model.reset_kv_cache()
+        for t in prompt:
+            _, nxt = model.forward_one(np.array([t], np.int32), want_logits=False)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(128):
+            _, nxt = model.forward_one(nxt, want_logits=False)
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0
+    gpu_run()
+    gpu_s = min(gpu_run() for _ in range(3))
+    st = ref.new_state()
+    for t in prompt:
+        logits = ref.forward_one(int(t), st)
+    t0 = time.perf_counter()
+    tok = int(np.flatnonzero(logits == logits.max())[-1])
+    for _ in range(128):
+        logits = ref.forward_one(tok, st)
+        tok = int(np.flatnonzero(logits == logits.max())[-1])
+    cpu_s = time.perf_counter() - t0
+    print(json.dumps({"sweep": "cpu_case_tiny_ttt_decode", "decode_steps": 128, "prompt": 32,
+                      "gpu_tokens_per_s": 128 / gpu_s, "cpu_tokens_per_s": 128 / cpu_s,
+                      "cpu_threads": int(orc.lib().oracle_num_threads()),
+                      "note": "gpu: bt_model_forward_one end to end (host id in, host id out, CUDA graph per step); cpu: the oracle "
+                              "model (quantised pipeline) on the host cores"}), flush=True)
 
 
 def run_reference_arm(args, rank):
