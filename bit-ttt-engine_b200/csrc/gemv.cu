@@ -387,6 +387,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
         // lt % kAccBufs; the epilogue warp reads the finished sums, clears the buffer and
         // publishes the buffer's generation so that the math warps may use it again. ----------
         const int epi = warp - kEpilogueWarp0;
+        // single token, accumulated output: the old value of this warp's first row tile is fetched now, while the
+        // math warps still build the activation image (it costs an L2 round trip that would otherwise end the kernel)
+        float old_first = 0.f;
+        if (a.m == 1 && a.epilogue == EPI_F32_ACCUM && epi < my_rts) {
+            const int64_t row0 = (blockIdx.x + (int64_t)epi * gridDim.x) * kTileRows + (lane & 15);
+            if (row0 < a.n_out) old_first = reinterpret_cast<const float*>(a.out)[row0];
+        }
         ptx::named_bar_sync(2, kMathThreads + 32 * kEpiWarps);  // tok_sx / tok_qsum are ready
         const int t = lane & 3, g = lane >> 2;
         int qs[2] = {0, 0};
@@ -449,11 +456,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
             }
             float sw = 0.f;
             if (a.epilogue != EPI_I32 && epi < my_rts) sw = a.sw_tiles[2 * rt + (r >> 3)];
+            float old = old_first;
             for (int lt = epi; lt < my_rts; lt += kEpiWarps) {
-                // the next row tile's scale comes from global memory: fetch it a round early
-                float sw_next = 0.f;
-                if (a.epilogue != EPI_I32 && lt + kEpiWarps < my_rts)
-                    sw_next = a.sw_tiles[2 * (rt + (int64_t)kEpiWarps * gridDim.x) + (r >> 3)];
+                // the next row tile's scale (and old output) come from global memory: fetch them a round early
+                float sw_next = 0.f, old_next = 0.f;
+                if (a.epilogue != EPI_I32 && lt + kEpiWarps < my_rts) {
+                    const int64_t rt_next = rt + (int64_t)kEpiWarps * gridDim.x;
+                    sw_next = a.sw_tiles[2 * rt_next + (r >> 3)];
+                    if (a.epilogue == EPI_F32_ACCUM && rt_next * kTileRows + r < a.n_out)
+                        old_next = reinterpret_cast<const float*>(a.out)[rt_next * kTileRows + r];
+                }
                 const int b = lt % kAccBufs;
                 const unsigned use = (unsigned)(lt / kAccBufs);
                 if (ok) ok = ptx::mbar_wait_relaxed(&acc_full[b], use & 1);
@@ -473,11 +485,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
                     if (lane < 16 && row < a.n_out) {
                         if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[row] = y;
                         else if (a.epilogue == EPI_F32_ACCUM)
-                            reinterpret_cast<float*>(a.out)[row] = __fadd_rn(reinterpret_cast<float*>(a.out)[row], y);
+                            reinterpret_cast<float*>(a.out)[row] = __fadd_rn(old, y);
                         else reinterpret_cast<__nv_bfloat16*>(a.out)[row] = __float2bfloat16_rn(y);
                     }
                 }
                 sw = sw_next;
+                old = old_next;
                 rt += (int64_t)kEpiWarps * gridDim.x;
             }
             if (!ok && lane == 0) atomicExch(a.err, kErrGemvTimeout);
