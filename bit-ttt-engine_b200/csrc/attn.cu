@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
     constexpr int NB = Smem::kCols8 / 8;           // 8-column blocks of the score MMAs (two query vectors each)
     constexpr int MB = Smem::kRows16 / 16;         // 16-row blocks of the P.V MMAs (four query vectors each)
     constexpr int kRounds = (G + kAttnWarps - 1) / kAttnWarps;  // weight rounds per tile: a warp turns one query vector's 128 scores into digits
+    constexpr bool kSplitDigits = 2 * G <= kAttnWarps;          // few vectors: two warps share one
     const int hd = HD > 0 ? HD : a.head_dim, half = hd >> 1;
     const int b = blockIdx.x / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int split = blockIdx.y;
@@ -503,6 +504,34 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 // positions 16 (L / 4) + 4 i + L % 4, i = 0..3: the four positions that one lane feeds into an MMA
                 // lie in one word, and so do the rows it reads from V.
                 const bool full_tile = n_here == kTilePos && (QB == 1 || chunk0 + ti * kTilePos + kTilePos - 1 <= p + q0);
+                if constexpr (kSplitDigits) {
+                    // two warps per query vector (all eight warps busy for four vectors): warp = (vector, half of the
+                    // tile's 32 words), lane = (word L % 16, pair of positions L / 16); the lane pair L, L ^ 16 swaps
+                    // its weights so that each lane can write two of the word's four digit rows
+                    const int v = warp >> 1;
+                    if (v < G) {  // warp-uniform
+                        const int wi = 16 * (warp & 1) + (lane & 15), sub = lane >> 4;
+                        const float2 s2 = *reinterpret_cast<const float2*>(&sm.sbuf[v][ti * kTilePos + 4 * wi + 2 * sub]);
+                        const float2 v2 = *reinterpret_cast<const float2*>(&sm.vsc[ti * kTilePos + 4 * wi + 2 * sub]);
+                        const float m_new = sm.ml[0][v];
+                        const int r0 = 16 * (wi >> 2) + (wi & 3) + 8 * sub;  // positions r0 and r0 + 4
+                        const float sv[2] = {s2.x, s2.y}, vv[2] = {v2.x, v2.y};
+                        uint32_t u[2];
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const bool live = full_tile || (r0 + 4 * i < n_here && sv[i] != -INFINITY);
+                            const float pe = live ? expf(__fsub_rn(sv[i], m_new)) : 0.0f;
+                            psum[0] += pe;
+                            u[i] = live ? __float2uint_rn(__fmul_rn(__fmul_rn(pe, vv[i]), wup)) : 0u;
+                        }
+                        const uint32_t o0 = __shfl_xor_sync(0xffffffffu, u[0], 16), o1 = __shfl_xor_sync(0xffffffffu, u[1], 16);
+                        uint32_t dig[4];
+                        if (sub == 0) transpose4(u[0], u[1], o0, o1, dig); else transpose4(o0, o1, u[0], u[1], dig);
+                        // digit j = byte 3 - j: this lane writes digits 2 sub and 2 sub + 1
+                        *reinterpret_cast<uint32_t*>(&wd[4 * v + 2 * sub][4 * wi]) = sub == 0 ? dig[3] : dig[1];
+                        *reinterpret_cast<uint32_t*>(&wd[4 * v + 2 * sub + 1][4 * wi]) = sub == 0 ? dig[2] : dig[0];
+                    }
+                } else {
 #pragma unroll
                 for (int e = 0; e < kRounds; ++e) {
                     const int v = warp + e * kAttnWarps;
@@ -526,6 +555,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
 #pragma unroll
                         for (int j = 0; j < 4; ++j) *reinterpret_cast<uint32_t*>(&wd[4 * v + j][4 * lane]) = dig[3 - j];
                     }
+                }
                 }
                 cp_async_wait<1>();
                 __syncthreads();  // tile n landed, its weight digits complete; everybody is done with tile n - 1
@@ -590,7 +620,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
 #pragma unroll
                 for (int e = 0; e < kRounds; ++e) {
                     const float ws = warp_sum(psum[e]);
-                    if (lane == 0) sm.wsum[warp][e] = ws;  // query vector warp + 8 e
+                    if (lane == 0) sm.wsum[warp][e] = ws;  // query vector warp + 8 e (two warps per vector: warp / 2)
                 }
             }
             __syncthreads();
@@ -600,7 +630,10 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 for (int g2 = 1; g2 < n_pq; ++g2) add = __fadd_rn(add, sm.part[g2 * G * hd + it]);
                 sm.opart[it] = fmaf(sm.opart[it], sm.corr[v], add);
             }
-            if (tid < G) sm.ml[1][tid] = fmaf(sm.ml[1][tid], sm.corr[tid], sm.wsum[tid % kAttnWarps][tid / kAttnWarps]);
+            if (tid < G) {
+                const float ps = kSplitDigits ? __fadd_rn(sm.wsum[2 * tid][0], sm.wsum[2 * tid + 1][0]) : sm.wsum[tid % kAttnWarps][tid / kAttnWarps];
+                sm.ml[1][tid] = fmaf(sm.ml[1][tid], sm.corr[tid], ps);
+            }
             __syncthreads();
         }
     }
