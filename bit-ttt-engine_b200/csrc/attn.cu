@@ -216,12 +216,12 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
 
     // The tiles of this CTA in the order they are worked on: per chunk its key tiles, then its value tiles.
     // `Cursor` names one of them; the fetches run two tiles ahead of the work.
-    struct Cursor { int chunk0; int phase; int tile; };  // first position of the chunk, 0 = keys / 1 = values, tile in chunk
+    struct Cursor { int chunk0; int phase; int tile; int tiles; };  // first position of the chunk, 0 = keys / 1 = values, tile in chunk, tiles of the chunk
     auto chunk_tiles = [&](int chunk0) { return (min(kChunk, t1 - chunk0) + kTilePos - 1) / kTilePos; };
     auto advance = [&](Cursor& c) {
-        if (++c.tile >= chunk_tiles(c.chunk0)) {
+        if (++c.tile >= c.tiles) {
             c.tile = 0;
-            if (++c.phase == 2) { c.phase = 0; c.chunk0 += kChunk; }
+            if (++c.phase == 2) { c.phase = 0; c.chunk0 += kChunk; c.tiles = chunk_tiles(c.chunk0); }
         }
     };
     // rows of the tile `c` -> ring buffer `stage` (asynchronous copies); a key tile brings its row scales along
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
         cp_async_commit();  // one group per tile, also when there is nothing left to fetch
     };
 
-    Cursor fc = {t0, 0, 0};
+    Cursor fc = {t0, 0, 0, chunk_tiles(t0)};
     const bool empty = t0 >= t_len;
     // The cache rows of earlier positions were written by earlier steps, so the first tile can be requested
     // before the dependency wait; the row of the current position is fetched too, with whatever it holds, and its
@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
             dc[nb][1] = sm.dcorr[8 * nb + 2 * t + 1];
             qs[nb] = 2 * nb + (t >> 1) < G ? sm.qscale[2 * nb + (t >> 1)] : 0.0f;
         }
-        int n = 0;  // tiles done so far: tile n sits in ring[n % kStages]
+        int cur = 0;  // ring buffer of the tile being worked on (tiles go through the buffers in turn)
         for (int chunk0 = t0; chunk0 < t1; chunk0 += kChunk) {
             const int clen = min(kChunk, t1 - chunk0);
             const int ctiles = (clen + kTilePos - 1) / kTilePos;
@@ -387,17 +387,17 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
             // ---- phase A: scores of the chunk.  Warp w owns positions 16 w .. 16 w + 15 of a tile; per 32-dim
             //      step lane (g, t) supplies bytes 32 j + 8 t .. + 7 of rows g and g + 8 (the order of the dims
             //      inside a step is free as long as the query digits follow it). -------------------------------
-            for (int ti = 0; ti < ctiles; ++ti, ++n) {
+            for (int ti = 0; ti < ctiles; ++ti, cur = cur + 1 == kStages ? 0 : cur + 1) {
                 cp_async_wait<1>();
-                __syncthreads();  // tile n landed and visible; everybody is done with tile n - 1
-                fetch(fc, (n + 2) % kStages);
+                __syncthreads();  // the tile landed and is visible; everybody is done with the tile before
+                fetch(fc, cur >= 1 ? cur - 1 : kStages - 1);  // two tiles ahead = the buffer of the tile before (three buffers)
                 advance(fc);
                 const int n_here = min(kTilePos, clen - ti * kTilePos);
                 // FULL: a whole tile that every query may see (decode; all but the last tile of a span)
                 auto score_tile = [&](auto full_tag) {
                     constexpr bool FULL = decltype(full_tag)::value;
                     if (!FULL && 16 * warp >= n_here) return;
-                    const uint8_t* kraw = sm.ring[n % kStages];
+                    const uint8_t* kraw = sm.ring[cur];
                     int c[NB][4];
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0;
@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                     const bool odd = t & 1;
                     const int r = 16 * warp + g + (odd ? 8 : 0);
                     const int slot = ti * kTilePos + 16 * warp + 4 * (g & 3) + (g >> 2) + (odd ? 2 : 0);
-                    const float ksr = (FULL || r < n_here) ? sm.sc[n % kStages][r] : 0.0f;
+                    const float ksr = (FULL || r < n_here) ? sm.sc[cur][r] : 0.0f;
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) {
                         const int v = 2 * nb + (t >> 1);
@@ -497,7 +497,7 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
 #pragma unroll
             for (int e = 0; e < kRounds; ++e) psum[e] = 0.0f;
             const float wup = sm.wup;
-            for (int ti = 0; ti < ctiles; ++ti, ++n) {
+            for (int ti = 0; ti < ctiles; ++ti, cur = cur + 1 == kStages ? 0 : cur + 1) {
                 const int n_here = min(kTilePos, clen - ti * kTilePos);
                 uint8_t (*wd)[kWStride] = sm.wdig[ti & 1];
                 // weight digits of the tile: a warp takes one query vector per round, lane L the slots 4 L .. 4 L + 3 =
@@ -558,10 +558,10 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
                 }
                 }
                 cp_async_wait<1>();
-                __syncthreads();  // tile n landed, its weight digits complete; everybody is done with tile n - 1
-                fetch(fc, (n + 2) % kStages);
+                __syncthreads();  // the tile landed, its weight digits are complete; everybody is done with the tile before
+                fetch(fc, cur >= 1 ? cur - 1 : kStages - 1);
                 advance(fc);
-                const uint8_t* vcol = sm.ring[n % kStages] + 32 * dg + 4 * g;
+                const uint8_t* vcol = sm.ring[cur] + 32 * dg + 4 * g;
                 auto pv_step = [&](int ks) {
                     uint32_t b0[4], b1[4];
                     {
@@ -756,6 +756,7 @@ __global__ void __launch_bounds__(128) kv_append_rows_kernel(KvCacheView cache, 
 }
 
 constexpr size_t kHalfSm = 116 * 1024;
+static_assert(kStages == 3, "the fetch two tiles ahead reuses the buffer of the tile before");
 static_assert(sizeof(AttnSmemT<4>) <= 112 * 1024, "two CTAs of the decode kernel (up to 4 query heads per KV head) must fit one SM");
 static_assert(sizeof(AttnSmemT<kMaxRep>) <= kHalfSm, "decode kernel: shared memory");
 constexpr int kPrefillVectors = 16;  // query vectors per CTA of the prefill kernel: 16 / NREP positions x NREP heads
