@@ -12,7 +12,8 @@
 //              TENSOR MEMORY and the B operand (activations, s8) in shared memory, K-major without
 //              swizzle; accumulators in tensor memory, two sets, so that the MMAs of the next unit
 //              run while the previous one is drained;
-//   4 RS unpack warps: a thread owns one weight row (= one TMEM lane) of one row set.  It loads the row's 64
+//   8 unpack warps: a thread owns one weight row (= one TMEM lane) of one row set (with one row set, two warps per
+//              lane quarter take the chunks in turn).  It loads the row's 64
 //              packed bytes of the chunk, isolates field r of every byte with a shift and an AND (values 0, 1, 2 =
 //              ternary + 1) and writes the four residue planes with tcgen05.st straight into tensor memory:
 //              the unpacked weights never pass through shared memory, whose bandwidth the B operand and the ring need;
@@ -37,14 +38,14 @@ namespace {
 
 constexpr int kRows = 128;               // weight rows per MMA = UMMA M = TMEM lanes
 constexpr int kSetBytes = 8 * kTileBytes;  // packed weights of 128 rows of a chunk: 8 row tiles x 1 KB
-constexpr int kABufs = 2;                // unpacked-A buffers in tensor memory
 constexpr int kAChunkCols = 64;          // TMEM columns of one unpacked 128-row chunk: 4 residues x 64 bytes / 4
 constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
 
 // A tile is RS x 128 weight rows x NT tokens: the RS row sets share every activation block, which is what a CTA
 // pulls most of through L2 (NT x 256 bytes per chunk against RS x 8 KB of packed weights).
-__host__ __device__ constexpr int tc_threads(int rs) { return (2 + 8 * rs) * 32; }  // producer, MMA issuer, 4 RS unpack warps, 4 RS epilogue warps
-__host__ __device__ constexpr int tc_acc_sets(int nt, int rs) { return (2 * rs * nt + kABufs * rs * kAChunkCols <= 512) ? 2 : 1; }
+__host__ __device__ constexpr int tc_threads(int rs) { return (2 + 8 + 4 * rs) * 32; }  // producer, MMA issuer, 8 unpack warps, 4 RS epilogue warps
+__host__ __device__ constexpr int tc_abufs(int rs) { return rs == 1 ? 4 : 2; }           // unpacked-A buffers in tensor memory
+__host__ __device__ constexpr int tc_acc_sets(int nt, int rs) { return (2 * rs * nt + tc_abufs(rs) * rs * kAChunkCols <= 512) ? 2 : 1; }
 __host__ __device__ constexpr int tc_stages(int nt, int rs, int s) {
     // ring depth that fits 227 KB next to the partial-sum buffer of a k split
     const int stage = rs * kSetBytes + 4 * nt * 64, part = s > 1 ? rs * kRows * nt * 4 : 0;
@@ -82,7 +83,11 @@ struct TcArgs {
 template <int NT, int RS, int S>
 __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     static_assert(S == 1 || (NT == 64 && (S == 2 || S == 4 || S == 8)), "k split: 64 tokens, 2 / 4 / 8 CTAs");
-    constexpr int kUnpackWarps = 4 * RS, kEpiWarps = 4 * RS, kEpiWarp0 = 2 + kUnpackWarps;
+    // Eight unpack warps.  RS = 2: one per (row set, TMEM lane quarter).  RS = 1: two per lane quarter, which take
+    // the chunks in turn (two independent chains of load - unpack - store, four A buffers).
+    constexpr int kUnpackWarps = 8, kEpiWarps = 4 * RS, kEpiWarp0 = 2 + kUnpackWarps;
+    constexpr int kABufs = tc_abufs(RS);
+    constexpr int kReaders = RS == 1 ? 4 : 8;            // unpack warps that read one stage's weights and fill one A buffer
     constexpr int kStages = tc_stages(NT, RS, S);
     constexpr int kAccSets = tc_acc_sets(NT, RS);
     constexpr int kRawBytes = RS * kSetBytes;
@@ -98,7 +103,7 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     int32_t* pbuf = reinterpret_cast<int32_t*>(stage_base + (size_t)kStages * kStageBytes);  // [RS][NT / 4][128 rows][4]
     uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(pbuf) + kPartBytes);
     uint64_t* empty = full + kStages;     // a stage is free again: the MMAs that read its B block are done (1 arrival)
-                                          // and the unpack warps have read its weights (kUnpackWarps arrivals)
+                                          // and the unpack warps that take the chunk have read its weights
     uint64_t* a_full = empty + kStages;   // unpacked chunk in tensor memory (one arrival per unpack warp)
     uint64_t* a_empty = a_full + kABufs;  // the MMAs that read it are done
     uint64_t* acc_full = a_empty + kABufs;
@@ -120,8 +125,8 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     const int n_tiles = row_sets * tok_blocks;             // this CTA works on the tiles cid, cid + n_clusters, ...
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1 + kUnpackWarps); }
-        for (int u = 0; u < kABufs; ++u) { ptx::mbar_init(&a_full[u], kUnpackWarps); ptx::mbar_init(&a_empty[u], 1); }
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1 + kReaders); }
+        for (int u = 0; u < kABufs; ++u) { ptx::mbar_init(&a_full[u], kReaders); ptx::mbar_init(&a_empty[u], 1); }
         for (int s = 0; s < 2; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], kEpiWarps); }
         ptx::mbar_init(red_full, kEpiWarps * S);
         ptx::mbar_init(red_free, kEpiWarps * S);
@@ -213,7 +218,8 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     } else if (warp < kEpiWarp0) {
         // ---------------- unpack warps: a thread owns one weight row (= one TMEM lane) of one row set ----
         const int sub = warp & 3;                      // the TMEM lanes 32 sub .. 32 sub + 31 belong to this warp
-        const int h = (warp - 2) >> 2;                 // row set of the tile
+        const int set = (warp - 2) >> 2;               // RS = 2: row set of the tile; RS = 1: which chunks (even / odd)
+        const int h = RS == 2 ? set : 0;
         const int row = sub * 32 + lane;               // row inside the set
         // the row: row tile r8 = row/16, half = (row%16)/8, g = row%8; its 64 packed bytes of a chunk are the four
         // 16-byte pieces t = 0..3 at ((half*32 + g*4 + t) * 16) of the row tile
@@ -221,12 +227,28 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
         const uint32_t lane_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + a_col0 + (uint32_t)h * kAChunkCols;
         ptx::pdl_wait();
         int g = 0;
+        int pending = -1;  // A buffer whose stores are issued but not yet published
+        // The stores of a chunk are published (wait, fence, arrive) only after the next chunk's weights have been
+        // loaded from shared memory, if those have landed already: the store latency hides behind the loads.
+        auto publish = [&]() {
+            if (pending < 0) return;
+            ptx::tmem_st_wait();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&a_full[pending]);
+            pending = -1;
+        };
         for (int tile = cid; tile < n_tiles; tile += n_clusters) {
             const int rs = tile % row_sets;
             const int rts = min(8 * RS, (int)(a.row_tiles - (int64_t)rs * 8 * RS));
             for (int kt = kt0; kt < kt1; ++kt, ++g) {
+                if (RS == 1 && (g & 1) != set) continue;
                 const int slot = g % kStages, u = g % kABufs, a_use = g / kABufs;
-                ok &= ptx::mbar_wait_bounded(&full[slot], (uint32_t)((g / kStages) & 1));
+                const uint32_t full_parity = (uint32_t)((g / kStages) & 1);
+                if (!__all_sync(0xffffffffu, ptx::mbar_test_wait(&full[slot], full_parity))) {  // (one answer for the whole warp)
+                    publish();  // the next weights are not here yet: do not hold the finished buffer back
+                    ok &= ptx::mbar_wait_bounded(&full[slot], full_parity);
+                }
                 const uint8_t* raw = stage_base + (size_t)slot * kStageBytes + r8 * kTileBytes + half * 512 + g8 * 64;
                 uint4 w[4];
 #pragma unroll
@@ -234,6 +256,7 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                     w[t] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // weight 0 (rows beyond the matrix)
                     if (r8 < rts) w[t] = *reinterpret_cast<const uint4*>(raw + t * 16);
                 }
+                publish();
                 if (a_use > 0) ok &= ptx::mbar_wait_bounded(&a_empty[u], (uint32_t)((a_use - 1) & 1));
                 ptx::tc_fence_after();
 #pragma unroll
@@ -249,15 +272,12 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                     }
                     ptx::tmem_st16(lane_addr + (uint32_t)(u * RS) * kAChunkCols + r * 16, v);
                 }
-                ptx::tmem_st_wait();
-                ptx::tc_fence_before();
+                pending = u;
                 __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive(&a_full[u]);
-                    ptx::mbar_arrive(&empty[slot]);  // this warp has read its weights of the stage
-                }
+                if (lane == 0) ptx::mbar_arrive(&empty[slot]);  // this warp holds the stage's weights in registers
             }
         }
+        publish();
     } else {
         // ---------------- epilogue warps (4 per row set, TMEM lanes by warp % 4) ----------------
         const int sub = warp & 3;
