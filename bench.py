@@ -659,6 +659,21 @@ def main():
     verified = {"batch1": verify_first_step(model, weights, 1)} if world == 1 else {}
     if with_b64 and world == 1:
         verified[f"batch{B2}"] = verify_first_step(model, weights, B2)
+    if world > 1:
+        # tensor parallelism: every rank must hold the same logits bit for bit (the exchanges are exact), and the
+        # sharded model must agree with the oracle on rank 0's first step within the head's accumulation accuracy
+        import hashlib
+        for bsz in ([1, B2] if with_b64 else [1]):
+            model.reset_kv_cache()
+            toks = np.random.default_rng(3).integers(0, cfg.vocab_size, size=bsz).astype(np.int32)
+            logits, nxt = model.forward_one(toks)
+            digest = hashlib.sha256(logits.tobytes() + nxt.tobytes()).hexdigest()
+            digests = [None] * world
+            dist.all_gather_object(digests, digest)
+            if len(set(digests)) != 1:
+                raise SystemExit(f"bench.py: the ranks' logits differ at batch {bsz}")
+            verified[f"tp{world}_batch{bsz}"] = f"first-step logits and picks bit-identical on all {world} ranks"
+        model.reset_kv_cache()
     del weights
 
     # ---- batch 1 ---------------------------------------------------------------------------
@@ -694,7 +709,7 @@ def main():
             "e2e": b1["e2e"], "e2e_with_logits": b1["e2e_with_logits"],
             "gpu_launches": b1["gpu_launches"],
             "roofline": b1["roofline"], "attention": b1["attention"], "clocks": clocks,
-            "verified_against_oracle": verified,
+            ("verified_against_oracle" if world == 1 else "verified_ranks_agree"): verified,
         }
         if prefill1 is not None:
             line["prefill"] = prefill1
