@@ -52,6 +52,25 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// The same with relaxed semantics: no acquire on the waiting thread.  For the thread that issues tcgen05.mma: an
+// acquiring wait costs it about 280 clocks of issue time per call even when the phase is long complete (measured),
+// a relaxed one about 100; the tcgen05.fence::after_thread_sync that follows orders the tensor-core operations, and
+// what they read was written before the arrival the wait observes.
+__device__ __forceinline__ bool mbar_spin_relaxed(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 24)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.relaxed.cta.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // Bounded wait for warps that are off the critical path (a producer waiting for a free slot,
 // an epilogue warp waiting for partial sums): a non-blocking test and a short sleep between
 // tests, so that the waiting warp leaves the shared-memory pipeline to the warps doing work.
@@ -312,6 +331,11 @@ __device__ __forceinline__ uint4 ld_dsmem_v4(uint32_t remote_addr) {
 // to whoever observes the arrival with acquire semantics
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_bar_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
+}
+// Arrival without ordering of its own: after a fence_cluster() that already published this thread's writes (one fence,
+// then one cheap arrival per peer), or where the arrival only says that loads whose values have been used are over.
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t remote_bar_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
 }
 __device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 // bounded wait with cluster-scope acquire (pairs with mbar_arrive_remote)

@@ -190,8 +190,10 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                 ptx::tc_fence_after();
                 for (int kt = kt0; kt < kt1; ++kt, ++g) {
                     const int slot = g % kStages, u = g % kABufs;
-                    ok &= ptx::mbar_wait_bounded(&full[slot], (uint32_t)((g / kStages) & 1));   // activation block landed
-                    ok &= ptx::mbar_wait_bounded(&a_full[u], (uint32_t)((g / kABufs) & 1));     // weights unpacked into tensor memory
+                    // One wait per chunk: the unpack warps arrive on a_full after they have seen full[slot] complete, which
+                    // covers the stage's activation block as well as its weights.  Every instruction between two MMAs
+                    // of this thread costs tensor-pipe time (the queue behind it is short), hence the relaxed wait.
+                    ok &= ptx::mbar_spin_relaxed(&a_full[u], (uint32_t)((g / kABufs) & 1));     // weights unpacked into tensor memory
                     ptx::tc_fence_after();
                     const uint32_t b_addr = ptx::smem_u32(stage_base + (size_t)slot * kStageBytes + kRawBytes);
 #pragma unroll
@@ -293,19 +295,23 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
             return (accum && token < a.m && row < a.n_out) ? reinterpret_cast<const float*>(a.out)[(int64_t)token * a.out_stride + row] : 0.0f;
         };
         // i = token inside the tile; tq / ts = the tile's staged per-token terms
-        auto store = [&](const int* tq, const float* ts, int tb, int i, int n_tok, int64_t row, float sw, uint32_t acc, float old) {
+        // tqi / tsi: the token's sum of q and scale (read from shared memory by the caller, ahead of its stores)
+        auto store_v = [&](int tqi, float tsi, int tb, int i, int n_tok, int64_t row, float sw, uint32_t acc, float old) {
             if (i < n_tok && row < a.n_out) {
-                const int accv = (int)acc - tq[i];
+                const int accv = (int)acc - tqi;
                 const int64_t o = (int64_t)(tb * NT + i) * a.out_stride + row;
                 if (a.epilogue == EPI_I32) {
                     reinterpret_cast<int32_t*>(a.out)[o] = accv;
                 } else {
-                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), ts[i]);
+                    const float y = __fmul_rn(__fmul_rn((float)accv, sw), tsi);
                     if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
                     else if (accum) reinterpret_cast<float*>(a.out)[o] = __fadd_rn(old, y);
                     else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
                 }
             }
+        };
+        auto store = [&](const int* tq, const float* ts, int tb, int i, int n_tok, int64_t row, float sw, uint32_t acc, float old) {
+            store_v(tq[i], ts[i], tb, i, n_tok, row, sw, acc, old);
         };
         int tl = 0;
         for (int tile = cid; tile < n_tiles; tile += n_clusters, ++tl) {
@@ -380,11 +386,11 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                 __syncwarp();
                 if (lane == 0) {
                     ptx::mbar_arrive(&acc_empty[sel]);  // the accumulator set is free for a later tile
+                    // (the fence above has published the parked sums: the arrivals need no release of their own)
 #pragma unroll
-                    for (int pr = 0; pr < S; ++pr) ptx::mbar_arrive_remote(ptx::map_to_rank(red_full, (uint32_t)pr));
+                    for (int pr = 0; pr < S; ++pr) ptx::mbar_arrive_remote_relaxed(ptx::map_to_rank(red_full, (uint32_t)pr));
                 }
                 ok &= ptx::mbar_wait_cluster_bounded(red_full, (uint32_t)(tl & 1));  // all S copies are complete
-                ptx::fence_cluster();
                 constexpr int kGroups = NT / 4 / S;  // groups of 4 tokens that this CTA finishes
                 constexpr int kBatch = 8 / S;        // groups per round: 8 remote 16-byte loads in flight
 #pragma unroll 1
@@ -401,6 +407,16 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                     for (int q = 0; q < kBatch; ++q)
 #pragma unroll
                         for (int e = 0; e < 4; ++e) old[q][e] = load_old(tb * NT + (rank * kGroups + q0 + q) * 4 + e, row);
+                    // the per-token terms too: a shared-memory load between two global stores would wait for the store
+                    int tqv[kBatch][4];
+                    float tsv[kBatch][4];
+#pragma unroll
+                    for (int q = 0; q < kBatch; ++q)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            tqv[q][e] = tq[(rank * kGroups + q0 + q) * 4 + e];
+                            tsv[q][e] = ts[(rank * kGroups + q0 + q) * 4 + e];
+                        }
 #pragma unroll
                     for (int q = 0; q < kBatch; ++q) {
                         uint4 s = part[q][0];
@@ -409,16 +425,17 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                             s.x += part[q][pr].x; s.y += part[q][pr].y; s.z += part[q][pr].z; s.w += part[q][pr].w;
                         }
                         const int i = (rank * kGroups + q0 + q) * 4;
-                        store(tq, ts, tb, i, n_tok, row, sw, s.x, old[q][0]);
-                        store(tq, ts, tb, i + 1, n_tok, row, sw, s.y, old[q][1]);
-                        store(tq, ts, tb, i + 2, n_tok, row, sw, s.z, old[q][2]);
-                        store(tq, ts, tb, i + 3, n_tok, row, sw, s.w, old[q][3]);
+                        store_v(tqv[q][0], tsv[q][0], tb, i, n_tok, row, sw, s.x, old[q][0]);
+                        store_v(tqv[q][1], tsv[q][1], tb, i + 1, n_tok, row, sw, s.y, old[q][1]);
+                        store_v(tqv[q][2], tsv[q][2], tb, i + 2, n_tok, row, sw, s.z, old[q][2]);
+                        store_v(tqv[q][3], tsv[q][3], tb, i + 3, n_tok, row, sw, s.w, old[q][3]);
                     }
                 }
                 __syncwarp();
                 if (lane == 0) {
+                    // the peers' sums have been read and used: nothing of this thread is left to order
 #pragma unroll
-                    for (int pr = 0; pr < S; ++pr) ptx::mbar_arrive_remote(ptx::map_to_rank(red_free, (uint32_t)pr));
+                    for (int pr = 0; pr < S; ++pr) ptx::mbar_arrive_remote_relaxed(ptx::map_to_rank(red_free, (uint32_t)pr));
                 }
             }
         }
