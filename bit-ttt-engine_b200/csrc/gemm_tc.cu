@@ -139,9 +139,10 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
-    if (S > 1) {  // the peers' barriers exist before anybody arrives on them
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
+    // The peers' barriers must exist before anybody arrives on them.  Only the epilogue warps ever touch a peer, so
+    // everybody reports here and only they wait (at the top of their role): the cluster's start-up skew stays off
+    // the path of the first copies and MMAs.
+    if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t a_col0 = kAccCols;  // the unpacked-A buffers follow the accumulators: [buffer][row set][64]
 
@@ -286,6 +287,7 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
         const int h = (warp - kEpiWarp0) >> 2;  // row set of the tile
         const int lrow = sub * 32 + lane;       // row inside the set
         int32_t* pb = pbuf + (size_t)h * (kRows * NT);
+        if (S > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         ptx::pdl_wait();  // the output (and what EPI_F32_ACCUM adds to) belongs to earlier kernels until here
         // The old value of an accumulated output is fetched apart from its update, so that a thread's loads are all
         // in flight before the first store (a store followed by a load of the same array would serialise them);
@@ -444,8 +446,13 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
-    if (S > 1) {  // nobody leaves while a peer may still read its shared memory or arrive on its barriers
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (S > 1) {
+        // Nobody leaves while a peer may still read its shared memory or arrive on its barriers: the last of both is
+        // the peers' arrival on red_free for this CTA's last tile (they read the parked sums before it, and arrived on
+        // red_full before that).  One warp waits for it; the CTA lives as long as that warp.
+        const int my_tiles = cid < n_tiles ? (n_tiles - cid + n_clusters - 1) / n_clusters : 0;
+        if (warp == 2 && my_tiles > 0 && !ptx::mbar_wait_cluster_bounded(red_free, (uint32_t)((my_tiles - 1) & 1)))
+            atomicExch(a.err, kErrTcTimeout);
     }
 }
 
