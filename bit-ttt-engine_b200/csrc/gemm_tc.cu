@@ -27,6 +27,7 @@
 // chunk accumulate into the same accumulator.
 #include <cstdint>
 #include <mutex>
+#include <type_traits>
 
 #include "bt_common.cuh"
 #include "bt_model.cuh"
@@ -43,7 +44,13 @@ constexpr unsigned kErrTcTimeout = 0x54434d4du;  // 'TCMM'
 
 // A tile is RS x 128 weight rows x NT tokens: the RS row sets share every activation block, which is what a CTA
 // pulls most of through L2 (NT x 256 bytes per chunk against RS x 8 KB of packed weights).
-__host__ __device__ constexpr int tc_threads(int rs) { return (2 + 8 + 4 * rs) * 32; }  // producer, MMA issuer, 8 unpack warps, 4 RS epilogue warps
+// Warps: producer, MMA issuer, 8 unpack warps, 4 RS epilogue warps.  With two row sets two idle warps follow the MMA
+// issuer, so that the roles fall on whole warpgroups (4 warps) and can trade registers (setmaxnreg).
+__host__ __device__ constexpr int tc_lead_warps(int rs) { return rs == 2 ? 4 : 2; }
+__host__ __device__ constexpr int tc_threads(int rs) { return (tc_lead_warps(rs) + 8 + 4 * rs) * 32; }
+// Register split of the 128-token, two-row-set kernel: the epilogue warps hold a whole accumulator row (128 values) so
+// that the single accumulator set is free again after four tensor-memory loads instead of after the stores.
+constexpr int kRegsLead = 40, kRegsUnpack = 64, kRegsEpilogue = 152;
 __host__ __device__ constexpr int tc_abufs(int rs) { return rs == 1 ? 4 : 2; }           // unpacked-A buffers in tensor memory
 __host__ __device__ constexpr int tc_acc_sets(int nt, int rs) { return (2 * rs * nt + tc_abufs(rs) * rs * kAChunkCols <= 512) ? 2 : 1; }
 __host__ __device__ constexpr int tc_stages(int nt, int rs, int s) {
@@ -85,7 +92,8 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     static_assert(S == 1 || (NT == 64 && (S == 2 || S == 4 || S == 8)), "k split: 64 tokens, 2 / 4 / 8 CTAs");
     // Eight unpack warps.  RS = 2: one per (row set, TMEM lane quarter).  RS = 1: two per lane quarter, which take
     // the chunks in turn (two independent chains of load - unpack - store, four A buffers).
-    constexpr int kUnpackWarps = 8, kEpiWarps = 4 * RS, kEpiWarp0 = 2 + kUnpackWarps;
+    constexpr int kUnpackWarps = 8, kEpiWarps = 4 * RS, kUnpackWarp0 = tc_lead_warps(RS), kEpiWarp0 = kUnpackWarp0 + kUnpackWarps;
+    constexpr bool kRegSplit = NT == 128 && RS == 2 && S == 1;
     constexpr int kABufs = tc_abufs(RS);
     constexpr int kReaders = RS == 1 ? 4 : 8;            // unpack warps that read one stage's weights and fill one A buffer
     constexpr int kStages = tc_stages(NT, RS, S);
@@ -146,7 +154,11 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t a_col0 = kAccCols;  // the unpacked-A buffers follow the accumulators: [buffer][row set][64]
 
+    // With the register split every warpgroup states its share at the top of its branch (the host has checked that the
+    // shares fit the register file the launch gives the CTA).
     bool ok = true;
+    if (warp < kUnpackWarp0) {
+    if constexpr (kRegSplit) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLead));
     if (warp == 0) {
         // ---------------- producer (whole warp: lane r8 requests row tile r8 of a chunk, so that the small copies are
         //                  issued side by side; lane 0 also registers the byte count and requests the activation block) ----
@@ -218,10 +230,12 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
             // every MMA of this CTA is issued: the kernel behind may start (it waits for this one's results itself)
             ptx::pdl_launch_dependents();
         }
+    }
     } else if (warp < kEpiWarp0) {
+        if constexpr (kRegSplit) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsUnpack));
         // ---------------- unpack warps: a thread owns one weight row (= one TMEM lane) of one row set ----
         const int sub = warp & 3;                      // the TMEM lanes 32 sub .. 32 sub + 31 belong to this warp
-        const int set = (warp - 2) >> 2;               // RS = 2: row set of the tile; RS = 1: which chunks (even / odd)
+        const int set = (warp - kUnpackWarp0) >> 2;               // RS = 2: row set of the tile; RS = 1: which chunks (even / odd)
         const int h = RS == 2 ? set : 0;
         const int row = sub * 32 + lane;               // row inside the set
         // the row: row tile r8 = row/16, half = (row%16)/8, g = row%8; its 64 packed bytes of a chunk are the four
@@ -282,6 +296,7 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
         }
         publish();
     } else {
+        if constexpr (kRegSplit) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
         // ---------------- epilogue warps (4 per row set, TMEM lanes by warp % 4) ----------------
         const int sub = warp & 3;
         const int h = (warp - kEpiWarp0) >> 2;  // row set of the tile
@@ -292,7 +307,12 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
         // The old value of an accumulated output is fetched apart from its update, so that a thread's loads are all
         // in flight before the first store (a store followed by a load of the same array would serialise them);
         // the per-token terms come through the read-only path for the same reason.
-        const bool accum = a.epilogue == EPI_F32_ACCUM;
+        // The epilogue kind is a compile-time constant of everything below (one copy of the role per kind, chosen once):
+        // the unrolled store sequences are long, and a kind switch inside every element made them four times as long -
+        // code that is fetched once per tile and does not stay in the instruction cache.
+        auto epilogue_role = [&](auto kind) {
+        constexpr int EPI = decltype(kind)::value;
+        constexpr bool accum = EPI == EPI_F32_ACCUM;
         auto load_old = [&](int token, int64_t row) -> float {
             return (accum && token < a.m && row < a.n_out) ? reinterpret_cast<const float*>(a.out)[(int64_t)token * a.out_stride + row] : 0.0f;
         };
@@ -302,12 +322,12 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
             if (i < n_tok && row < a.n_out) {
                 const int accv = (int)acc - tqi;
                 const int64_t o = (int64_t)(tb * NT + i) * a.out_stride + row;
-                if (a.epilogue == EPI_I32) {
+                if constexpr (EPI == EPI_I32) {
                     reinterpret_cast<int32_t*>(a.out)[o] = accv;
                 } else {
                     const float y = __fmul_rn(__fmul_rn((float)accv, sw), tsi);
-                    if (a.epilogue == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
-                    else if (accum) reinterpret_cast<float*>(a.out)[o] = __fadd_rn(old, y);
+                    if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(a.out)[o] = y;
+                    else if constexpr (accum) reinterpret_cast<float*>(a.out)[o] = __fadd_rn(old, y);
                     else reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(y);
                 }
             }
@@ -327,7 +347,7 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                     for (int i = lrow; i < NT; i += kRows) {
                         const int token = tb * NT + i;
                         tq[i] = token < a.m ? __ldg(a.qsum + token) : 0;
-                        ts[i] = (token < a.m && a.epilogue != EPI_I32) ? __ldg(a.sx + token) : 0.0f;
+                        ts[i] = (token < a.m && EPI != EPI_I32) ? __ldg(a.sx + token) : 0.0f;
                     }
                 }
                 ptx::named_bar_sync(1, kEpiWarps * 32);  // all epilogue warps: written before read, read before the tile after next overwrites
@@ -339,10 +359,48 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
             const int64_t row = ((int64_t)rs * RS + h) * kRows + lrow;
             const int64_t rt = row >> 4;
             float sw = 0.f;
-            if (a.epilogue != EPI_I32 && rt < a.row_tiles) sw = __ldg(a.sw_tiles + 2 * rt + ((row >> 3) & 1));
+            if (EPI != EPI_I32 && rt < a.row_tiles) sw = __ldg(a.sw_tiles + 2 * rt + ((row >> 3) & 1));
             const uint32_t acc_addr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(sel * RS + h) * NT;
             const int n_tok = min(NT, a.m - tb * NT);  // tokens of this tile that exist
-            if constexpr (S == 1) {
+            bool drained = false;
+            if constexpr (kRegSplit) {
+                // Whole tiles with an f32 output: this thread's whole accumulator row goes to registers and the set is
+                // handed back to the MMA issuer before the first store, so that the next tile's MMAs run under this
+                // tile's stores.  The store code is kept short (one epilogue kind per loop, no per-element bounds):
+                // it is unrolled 128 times and is fetched once per tile.
+                // (one decision per warp: the tensor-memory loads are warp-wide instructions)
+                if ((EPI == EPI_F32 || accum) && n_tok == NT && __all_sync(0xffffffffu, row < a.n_out)) {
+                    drained = true;
+                    uint32_t d[NT];
+#pragma unroll
+                    for (int c0 = 0; c0 < NT; c0 += 32) ptx::tmem_ld32(acc_addr + c0, reinterpret_cast<uint32_t(&)[32]>(d[c0]));
+                    ptx::tmem_ld_wait();
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&acc_empty[sel]);
+                    float* po = reinterpret_cast<float*>(a.out) + (int64_t)(tb * NT) * a.out_stride + row;
+                    const int64_t stride = a.out_stride;
+                    if (accum) {
+#pragma unroll
+                        for (int c0 = 0; c0 < NT; c0 += 16) {
+                            float old[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) old[j] = po[(c0 + j) * stride];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                po[(c0 + j) * stride] =
+                                    __fadd_rn(old[j], __fmul_rn(__fmul_rn((float)((int)d[c0 + j] - tq[c0 + j]), sw), ts[c0 + j]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < NT; ++i)
+                            po[i * stride] = __fmul_rn(__fmul_rn((float)((int)d[i] - tq[i]), sw), ts[i]);
+                    }
+                }
+            }
+            if (drained) {
+                // nothing left to do for this tile
+            } else if constexpr (S == 1) {
                 if (accum) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < NT; c0 += 16) {
@@ -441,6 +499,13 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
                 }
             }
         }
+        };
+        switch (a.epilogue) {
+            case EPI_I32: epilogue_role(std::integral_constant<int, EPI_I32>{}); break;
+            case EPI_F32: epilogue_role(std::integral_constant<int, EPI_F32>{}); break;
+            case EPI_F32_ACCUM: epilogue_role(std::integral_constant<int, EPI_F32_ACCUM>{}); break;
+            default: epilogue_role(std::integral_constant<int, EPI_BF16>{}); break;
+        }
     }
     if (!ok) atomicExch(a.err, kErrTcTimeout);
     ptx::tc_fence_before();
@@ -471,7 +536,18 @@ const TcVariant& tc_variant(int sm_count) {
     v.smem = (size_t)tc_stages(NT, RS, S) * (RS * kSetBytes + 4 * NT * 64) + (S > 1 ? RS * kRows * NT * 4 : 0) + 512 + 16 * NT;
     auto* kernel = gemm_tc_kernel<NT, RS, S>;
     const size_t smem = v.smem;
-    v.status = attributes.run([kernel, smem] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
+    v.status = attributes.run([kernel, smem] {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess && NT == 128 && RS == 2 && S == 1) {
+            // the register shares the warpgroups ask for must fit what the launch gives the CTA, or the asking waits for ever
+            cudaFuncAttributes fa;
+            e = cudaFuncGetAttributes(&fa, kernel);
+            const int have = fa.numRegs * tc_threads(RS);
+            const int want = 128 * kRegsLead + 256 * kRegsUnpack + 256 * kRegsEpilogue;
+            if (e == cudaSuccess && have < want) e = cudaErrorLaunchOutOfResources;
+        }
+        return e;
+    });
     if (v.status != cudaSuccess) return v;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
