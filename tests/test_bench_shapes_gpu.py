@@ -138,3 +138,25 @@ def test_tensor_core_product_bf16_and_multi_basis(bt, oracle):
     assert rel_err(y3, ref3) <= REL_TOL
     assert np.array_equal(y3, ref3)
     assert bt.lib().bt_device_check(0) == 0
+
+
+@pytest.mark.parametrize("m,n,k,nb", [(512, 14336, 1024, 2), (500, 14328, 1024, 1), (500, 14328, 768, 3)])
+def test_tensor_core_product_register_split_paths(bt, oracle, m, n, k, nb):
+    # Tiles of 256 rows x 128 tokens (the kernel whose epilogue warps take a whole accumulator row into registers):
+    # whole tiles with a second basis accumulated onto the first, and ragged edges (a last token block of 116 tokens,
+    # a last warp with rows beyond the matrix), where a warp falls back to the batched epilogue.
+    rng = np.random.default_rng(m + n + k + nb)
+    bases = rng.integers(-1, 2, size=(nb, n, k)).astype(np.int8)
+    packed = oracle.pack_l2(bases)
+    scales = np.array([0.02, 0.007, 0.003][:nb], np.float32)
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    lin = bt.BitLinear.from_packed(packed, scales, n, k)
+    ws = bt.Workspace(0, 768 << 20)
+    y = lin.forward(torch.from_numpy(x).cuda(), workspace=ws).cpu().numpy()
+    rows = np.unique(np.concatenate([rng.integers(0, n, 96), [0, 127, 128, 255, 256, n - 130, n - 9, n - 1]]))
+    toks = np.unique(np.concatenate([rng.integers(0, m, 120), [0, 127, 128, 383, 384, m - 1]]))
+    ref = oracle.bitlinear_q(x[toks], np.ascontiguousarray(packed[rows]), scales, rows.size, n_bases=nb)
+    got = y[np.ix_(toks, rows)]
+    assert rel_err(got, ref) <= REL_TOL
+    assert np.array_equal(got, ref)
+    assert bt.lib().bt_device_check(0) == 0
