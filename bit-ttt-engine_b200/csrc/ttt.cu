@@ -4,8 +4,8 @@
 // W only needs X and its own predictions, so one warp owns one row of one state, keeps it
 // in registers across all chunks of the launch, and the state is read and written exactly
 // once: 2*d*d*4 bytes per state per launch, which is the HBM bound of this kernel.
-// Sums (L2 norm, W row . x, the chunk gradient) are accumulated in f64 and rounded to f32
-// once, so that they do not depend on the order in which lanes add them.
+// The general kernel below accumulates its sums (L2 norm, W row . x, the chunk gradient) in f64 and rounds to f32
+// once; the kernel for the small states the models use (d = 32, 64, 128) keeps f64 for the norm only.
 // The reference issues ~12 tensor ops and two small batched matmuls per token.
 #include "bt_model.cuh"
 #include "bt_ptx.cuh"
@@ -103,13 +103,14 @@ __global__ void __launch_bounds__(kTttWarps * 32) ttt_chunk_kernel(float* __rest
     }
 }
 
-// Small states (d = 32, 64 or 128): LPR = d / 16 lanes share a row of W, each holding 16
-// consecutive columns widened to f64 once per launch, so that the inner loops are plain f64
-// FMAs on registers (a float-to-double conversion costs several FMAs on this part, and the
-// per-row kernel above converts both operands of every product).  A row's dot product is
-// finished with log2(LPR) shuffles, which also leave z - x in every lane of the row for the
-// gradient.  A warp covers 32 / LPR rows; with d <= 64 a CTA of 8 warps covers a whole state,
-// so the chunk is normalised once per state.
+// Small states (d = 32, 64 or 128): LPR = d / 16 lanes share a row of W, each holding 16 consecutive columns in
+// registers, so that the inner loops are plain FMAs on registers.  A row's dot product is finished with log2(LPR)
+// shuffles, which also leave z - x in every lane of the row for the gradient.  A warp covers 32 / LPR rows; with
+// d <= 64 a CTA of 8 warps covers a whole state, so the chunk is normalised once per state.
+// The products W row . x and the chunk gradient are accumulated in f32 like the reference's own matmuls
+// (layers/ttt.rs:58-65), in a fixed order (four partial sums per lane, then the lanes of the row), so a result does
+// not depend on the batch or on the run; only the L2 norm keeps its f64 sum.  f64 FMAs run at half the f32 rate on
+// this part and made the kernel arithmetic-bound at a sixth of the HBM bound.
 template <int LPR>
 __global__ void __launch_bounds__(kTttWarps * 32, 2) ttt_rows_kernel(float* __restrict__ w,
                                                                     const float* __restrict__ feats,
@@ -117,26 +118,26 @@ __global__ void __launch_bounds__(kTttWarps * 32, 2) ttt_rows_kernel(float* __re
                                                                     float* __restrict__ z_out,
                                                                     unsigned int* __restrict__ absmax_out) {
     constexpr int kCols = 16;                 // columns per lane
+    constexpr int kPad = 4;                   // floats between two blocks of 16 columns
     constexpr int kRowsPerWarp = 32 / LPR;
-    // [chunk][d + 2 * LPR] normalised features of the current chunk, widened; every block of 16
-    // columns is shifted by 2 more doubles, so that the LPR lanes of a row, which read different
-    // blocks in the same instruction, hit different banks
-    extern __shared__ __align__(16) double xd[];
-    const int pitch = d + 2 * LPR;
+    // [chunk][d + kPad * LPR] normalised features of the current chunk; every block of 16 columns is shifted by 4 more
+    // floats, so that the LPR lanes of a row, which read different blocks in the same 16-byte load, hit different banks
+    extern __shared__ __align__(16) float xs[];
+    const int pitch = d + kPad * LPR;
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
     const int b = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a = (blockIdx.y * kTttWarps + warp) * kRowsPerWarp + lane / LPR;  // this lane's row of W
-    const int c0 = (lane % LPR) * kCols;                                        // and its first column
+    const int blk = lane % LPR;                                                 // and its block of 16 columns
     const bool active = a < d;
-    float* wrow = w + ((int64_t)b * d + (active ? a : 0)) * d + c0;
-    // the row is requested first and widened only after the first chunk has been staged, so that
-    // its DRAM latency overlaps the feature loads
-    float4 wf[kCols / 4];
+    float* wrow = w + ((int64_t)b * d + (active ? a : 0)) * d + blk * kCols;
+    float wr[kCols];
 #pragma unroll
-    for (int i = 0; i < kCols / 4; ++i) wf[i] = active ? reinterpret_cast<const float4*>(wrow)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    double wr[kCols];
+    for (int i = 0; i < kCols / 4; ++i) {
+        const float4 v = active ? reinterpret_cast<const float4*>(wrow)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        wr[4 * i] = v.x; wr[4 * i + 1] = v.y; wr[4 * i + 2] = v.z; wr[4 * i + 3] = v.w;
+    }
     const float* fb = feats + (int64_t)b * t_len * d;
     float* zb = z_out + (int64_t)b * t_len * d;
     float run_max = 0.0f;
@@ -161,59 +162,50 @@ __global__ void __launch_bounds__(kTttWarps * 32, 2) ttt_rows_kernel(float* __re
             const float nrm = __fadd_rn(sqrtf((float)ss), 1e-6f);
 #pragma unroll
             for (int e = 0; e < kElems; ++e)
-                if (t < len) xd[t * pitch + sub + (kPerTok + 2) * e] = (double)__fdiv_rn(f[e], nrm);
-        }
-        if (start == 0) {
-#pragma unroll
-            for (int i = 0; i < kCols / 4; ++i) {
-                wr[4 * i] = (double)wf[i].x; wr[4 * i + 1] = (double)wf[i].y;
-                wr[4 * i + 2] = (double)wf[i].z; wr[4 * i + 3] = (double)wf[i].w;
-            }
+                if (t < len) xs[t * pitch + sub + (kPerTok + kPad) * e] = __fdiv_rn(f[e], nrm);
         }
         __syncthreads();
-        double g[kCols];
+        float g[kCols];
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) g[i] = 0.0;
+        for (int i = 0; i < kCols; ++i) g[i] = 0.0f;
         for (int t = 0; t < len; ++t) {
-            const double* xt = xd + t * pitch;
-            double x[kCols];
-#pragma unroll
-            for (int i = 0; i < kCols; i += 2) {
-                const double2 v = *reinterpret_cast<const double2*>(xt + c0 + 2 * (lane % LPR) + i);
-                x[i] = v.x;
-                x[i + 1] = v.y;
-            }
-            // prediction with the pre-update row: four partial sums, then the lanes of the row
-            double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+            const float* xt = xs + t * pitch;
+            float x[kCols];
 #pragma unroll
             for (int i = 0; i < kCols; i += 4) {
-                s0 = fma(wr[i], x[i], s0);
-                s1 = fma(wr[i + 1], x[i + 1], s1);
-                s2 = fma(wr[i + 2], x[i + 2], s2);
-                s3 = fma(wr[i + 3], x[i + 3], s3);
+                const float4 v = *reinterpret_cast<const float4*>(xt + blk * (kCols + kPad) + i);
+                x[i] = v.x; x[i + 1] = v.y; x[i + 2] = v.z; x[i + 3] = v.w;
             }
-            double sd = (s0 + s1) + (s2 + s3);
+            // prediction with the pre-update row: four partial sums, then the lanes of the row
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-            for (int o = LPR / 2; o > 0; o >>= 1) sd += __shfl_xor_sync(0xffffffffu, sd, o);
-            const float s = (float)sd;
-            const float xa = active ? (float)xt[a + 2 * (a / kCols)] : 0.0f;
-            if (active && (lane % LPR) == 0) {
+            for (int i = 0; i < kCols; i += 4) {
+                s0 = __fmaf_rn(wr[i], x[i], s0);
+                s1 = __fmaf_rn(wr[i + 1], x[i + 1], s1);
+                s2 = __fmaf_rn(wr[i + 2], x[i + 2], s2);
+                s3 = __fmaf_rn(wr[i + 3], x[i + 3], s3);
+            }
+            float s = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
+            const float xa = active ? xt[a + kPad * (a / kCols)] : 0.0f;
+            if (active && blk == 0) {
                 zb[(int64_t)(start + t) * d + a] = s;
                 run_max = fmaxf(run_max, fabsf(s));
             }
             // rank-1 piece of the chunk gradient
-            const double df = (double)__fsub_rn(s, xa);
+            const float df = __fsub_rn(s, xa);
 #pragma unroll
-            for (int i = 0; i < kCols; ++i) g[i] = fma(df, x[i], g[i]);
+            for (int i = 0; i < kCols; ++i) g[i] = __fmaf_rn(df, x[i], g[i]);
         }
-        // W <- W - lr * G in f32 (layers/ttt.rs:68,111), widened again for the next chunk
+        // W <- W - lr * G (layers/ttt.rs:68,111)
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) wr[i] = (double)__fsub_rn((float)wr[i], __fmul_rn((float)g[i], lr));
+        for (int i = 0; i < kCols; ++i) wr[i] = __fsub_rn(wr[i], __fmul_rn(g[i], lr));
     }
     if (active) {
 #pragma unroll
         for (int i = 0; i < kCols / 4; ++i)
-            reinterpret_cast<float4*>(wrow)[i] = make_float4((float)wr[4 * i], (float)wr[4 * i + 1], (float)wr[4 * i + 2], (float)wr[4 * i + 3]);
+            reinterpret_cast<float4*>(wrow)[i] = make_float4(wr[4 * i], wr[4 * i + 1], wr[4 * i + 2], wr[4 * i + 3]);
     }
     if (absmax_out) {
 #pragma unroll
@@ -225,7 +217,7 @@ __global__ void __launch_bounds__(kTttWarps * 32, 2) ttt_rows_kernel(float* __re
 template <int LPR>
 cudaError_t launch_rows(float* w, const float* feats, int batch, int t_len, int d, float lr, int chunk,
                         float* z_out, cudaStream_t stream, unsigned int* absmax_out, bool pdl) {
-    const size_t smem = (size_t)chunk * (d + 2 * LPR) * sizeof(double);
+    const size_t smem = (size_t)chunk * (d + 4 * LPR) * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(ttt_rows_kernel<LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;

@@ -12,7 +12,7 @@ def rel_err(a, b):
 ATT_TOL = 2e-5      # attention output vs the oracle on identical inputs (f32 accumulation on the GPU)
 LOGIT_TOL = 2e-5    # dense head vs the oracle on identical hidden states
 ACT_TOL = 1e-6      # silu(gate)*up: the GPU's f32 exponential against the oracle's correctly rounded one
-TTT_TOL = 1e-6      # TTT prediction z on identical features and state
+TTT_TOL = 2e-5      # TTT prediction z on identical features and (separately advanced) state: f32 accumulation on the GPU
 
 
 def staged_decode_step(oracle, ref, gpu, cfg, tokens, states, act_tol=ACT_TOL, seqs=None):
