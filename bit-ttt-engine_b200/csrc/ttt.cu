@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kTttWarps * 32) ttt_chunk_kernel(float* __rest
 // not depend on the batch or on the run; only the L2 norm keeps its f64 sum.  f64 FMAs run at half the f32 rate on
 // this part and made the kernel arithmetic-bound at a sixth of the HBM bound.
 template <int LPR>
-__global__ void __launch_bounds__(kTttWarps * 32, 2) ttt_rows_kernel(float* __restrict__ w,
+__global__ void __launch_bounds__(kTttWarps * 32, 3) ttt_rows_kernel(float* __restrict__ w,
                                                                     const float* __restrict__ feats,
                                                                     int t_len, int d, float lr, int chunk,
                                                                     float* __restrict__ z_out,
