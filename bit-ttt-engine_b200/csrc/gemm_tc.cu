@@ -132,12 +132,12 @@ __global__ void __launch_bounds__(tc_threads(RS), 1) gemm_tc_kernel(TcArgs a) {
     const int kt0 = rank * cps, kt1 = min(k_tiles, kt0 + cps);
     const int n_tiles = row_sets * tok_blocks;             // this CTA works on the tiles cid, cid + n_clusters, ...
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1 + kReaders); }
-        for (int u = 0; u < kABufs; ++u) { ptx::mbar_init(&a_full[u], kReaders); ptx::mbar_init(&a_empty[u], 1); }
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], kEpiWarps); }
-        ptx::mbar_init(red_full, kEpiWarps * S);
-        ptx::mbar_init(red_free, kEpiWarps * S);
+    if (warp == 0) {  // the barriers side by side, a lane each (the set-up is on the path of every launch)
+        if (lane < kStages) { ptx::mbar_init(&full[lane], 1); ptx::mbar_init(&empty[lane], 1 + kReaders); }
+        if (lane >= 8 && lane < 8 + kABufs) { ptx::mbar_init(&a_full[lane - 8], kReaders); ptx::mbar_init(&a_empty[lane - 8], 1); }
+        if (lane >= 16 && lane < 18) { ptx::mbar_init(&acc_full[lane - 16], 1); ptx::mbar_init(&acc_empty[lane - 16], kEpiWarps); }
+        if (lane == 24) ptx::mbar_init(red_full, kEpiWarps * S);
+        if (lane == 25) ptx::mbar_init(red_free, kEpiWarps * S);
         ptx::mbar_fence_init();
     }
     if (warp == 1) {  // one warp allocates (and later frees) the tensor memory

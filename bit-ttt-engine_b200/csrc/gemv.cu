@@ -319,21 +319,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     const int my_rts = (int)((a.row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
     const int total_iters = short_k ? (my_rts + TPW - 1) / TPW : my_rts * stages_per_rt;
 
-    if (threadIdx.x < 8) tok_qsum[threadIdx.x] = 0;
-    for (int i = threadIdx.x; i < kAccBufs * kAccBufInts; i += kThreads) accbuf[i] = 0;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < nstages; ++s) {
-            ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&empty[s], kMathWarps);
+    // The barriers are set up side by side, one thread each, in the producer's warp, which then only reports at the
+    // CTA barrier and goes on to request weights: nothing is copied before the barriers exist, and the set-up of a
+    // CTA is on the path of every launch.  The other warps clear the accumulate buffers meanwhile.
+    if (warp != kProducerWarp) {
+        if (threadIdx.x < 8) tok_qsum[threadIdx.x] = 0;
+        const int i0 = threadIdx.x < kProducerWarp * 32 ? threadIdx.x : threadIdx.x - 32;  // the producer's warp left out
+        for (int i = i0; i < kAccBufs * kAccBufInts; i += kThreads - 32) accbuf[i] = 0;
+        ptx::named_bar_sync(0, kThreads);
+    } else {
+        if (lane < nstages) {
+            ptx::mbar_init(&full[lane], 1);
+            ptx::mbar_init(&empty[lane], kMathWarps);
         }
-        for (int b = 0; b < kAccBufs; ++b) {
-            ptx::mbar_init(&acc_full[b], kMathWarps);
-            acc_gen[b] = 0;
+        if (lane >= 16 && lane < 16 + kAccBufs) {
+            ptx::mbar_init(&acc_full[lane - 16], kMathWarps);
+            acc_gen[lane - 16] = 0;
         }
-        ptx::mbar_init(x_issued, kMathWarps);
+        if (lane == 15) ptx::mbar_init(x_issued, kMathWarps);
         ptx::mbar_fence_init();
+        __syncwarp();
+        ptx::named_bar_arrive(0, kThreads);
     }
-    __syncthreads();
 
     if (warp == kProducerWarp) {
         // ---------------- producer: weights do not depend on earlier kernels ----------------
