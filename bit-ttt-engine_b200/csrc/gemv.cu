@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(GemvArgs a, int nstag
     const int k_tiles = (int)a.k_tiles;
     const bool short_k = k_tiles <= kHalfTiles;  // a row tile is one pass
     const int stages_per_rt = (k_tiles + kStageTiles - 1) / kStageTiles;  // long K only
-    const int my_rts = (int)((a.row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+    const int my_rts = ((int)a.row_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // (32-bit: a 64-bit division is slow)
     const int total_iters = short_k ? (my_rts + TPW - 1) / TPW : my_rts * stages_per_rt;
 
     // The barriers are set up side by side, one thread each, in the producer's warp, which then only reports at the
