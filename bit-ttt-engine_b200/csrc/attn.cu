@@ -120,6 +120,12 @@ struct AttnSmemT {
     float wvmax[kAttnWarps];
     float wup, wdown;                                       // weight scale of the chunk: 2^32 / B and B / 2^32
     float knew[kMaxHd], vnew[kMaxHd];
+    // Merge of a cluster's spans: every span pushes its partial output columns (and its maximum / denominator) into
+    // the CTA that finishes those columns, [span][column of the receiver] and [span][max | denominator][vector].
+    // Written by peers only, between the start of the kernel and the cluster barrier; never initialised.
+    static constexpr int kRx = G <= 8 ? G * kMaxHd + 16 : 4;  // (more than 8 vectors: prefill, which has no cluster)
+    alignas(16) float rx_o[kRx];
+    float rx_ml[G <= 8 ? 16 : 1][2][G];
 };
 
 // D(16x8, s32) += A(16x32, u8, row) * B(32x8, s8 or u8, col)
@@ -155,6 +161,13 @@ __device__ __forceinline__ void transpose4(uint32_t v0, uint32_t v1, uint32_t v2
     r[1] = __byte_perm(lo01, lo23, 0x7632);
     r[2] = __byte_perm(hi01, hi23, 0x5410);
     r[3] = __byte_perm(hi01, hi23, 0x7632);
+}
+
+// f32 to the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ void st_cluster_f32(float* local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(ptx::smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 // ---- thread-block cluster primitives -----------------------------------------------------
@@ -642,52 +655,55 @@ __global__ void __launch_bounds__(kAttnThreads, (NREP * QB <= 4) ? 2 : 1) attn_k
     ptx::pdl_launch_dependents();
 
     // Merge of the spans of this (sequence, KV head): out = sum_s e^{m_s - m} o_s / sum_s e^{m_s - m} l_s.
-    // Every CTA of the cluster finishes the output columns rank, rank + S, ... from the partials of all spans.
-    cluster_sync_all();  // partials of every span written and visible cluster-wide
+    // The output columns are dealt evenly to the CTAs of the cluster.  Every span PUSHES its partial columns into the
+    // CTA that finishes them (plain stores into the peer's shared memory), one cluster barrier makes the pushes
+    // visible, and the finishing CTA reads local shared memory only: no remote load on the path and no second
+    // barrier before the CTAs leave (nobody touches a peer after the barrier).
     {
-        // The output columns are dealt evenly to the CTAs of the cluster.  All remote loads of a thread are
-        // issued before the first use (fixed trip counts, predicated), so that their latencies overlap.
-        const int S = a.splits, rank = (int)cluster_ctarank();
+        const int S = a.splits, rank = S > 1 ? (int)cluster_ctarank() : 0;
         const int total = G * hd;
-        const int per_cta = (total + S - 1) / S;
         float amax = 0.0f;
-        for (int i = tid; i < per_cta; i += kAttnThreads) {
-            const int it = rank * per_cta + i;
-            if (it >= total) break;
+        auto emit = [&](int it, float o) {
             const int h = it / hd;
-            float ms[kMaxCluster], ls[kMaxCluster], os[kMaxCluster];
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxCluster; ++s2) {
-                ms[s2] = -INFINITY; ls[s2] = 0.0f; os[s2] = 0.0f;
-                if (s2 < S) {
-                    ms[s2] = ld_cluster_f32(&sm.ml[0][h], (uint32_t)s2);
-                    ls[s2] = ld_cluster_f32(&sm.ml[1][h], (uint32_t)s2);
-                    os[s2] = ld_cluster_f32(&sm.opart[it], (uint32_t)s2);
-                }
-            }
-            float m = -INFINITY;
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxCluster; ++s2) m = fmaxf(m, ms[s2]);
-            float num = 0.0f, den = 0.0f;
-#pragma unroll
-            for (int s2 = 0; s2 < kMaxCluster; ++s2) {
-                // a span without positions (maximum -inf) weighs nothing
-                const bool live = ms[s2] != -INFINITY;
-                const float w = live ? expf(__fsub_rn(ms[s2], m)) : 0.0f;
-                den = fmaf(ls[s2], w, den);
-                num = fmaf(live ? os[s2] : 0.0f, w, num);
-            }
-            const float o = __fdiv_rn(num, den);
             const int qi = q0 + h / NREP;  // new token of the sequence this query vector belongs to (decode: 0)
             if (qi < a.q_rows) a.out[(((int64_t)b * a.q_rows + qi) * a.n_heads + kvh * NREP + h % NREP) * hd + (it % hd)] = o;
             amax = fmaxf(amax, fabsf(o));
+        };
+        if (S == 1) {
+            // one span: its own sums are the result (the weight e^{m - m} is exactly 1)
+            for (int it = tid; it < total; it += kAttnThreads) emit(it, __fdiv_rn(sm.opart[it], sm.ml[1][it / hd]));
+        } else if constexpr (G <= 8) {
+            const int per_cta = (total + S - 1) / S;
+            for (int it = tid; it < total; it += kAttnThreads)
+                st_cluster_f32(&sm.rx_o[rank * per_cta + it % per_cta], (uint32_t)(it / per_cta), sm.opart[it]);
+            for (int i = tid; i < S * 2 * G; i += kAttnThreads) {
+                const int dst = i / (2 * G), j = i % (2 * G);
+                st_cluster_f32(&sm.rx_ml[rank][j / G][j % G], (uint32_t)dst, sm.ml[j / G][j % G]);
+            }
+            cluster_sync_all();  // the pushes of every span are complete and visible
+            for (int i = tid; i < per_cta; i += kAttnThreads) {
+                const int it = rank * per_cta + i;
+                if (it >= total) break;
+                const int h = it / hd;
+                float m = -INFINITY;
+                for (int s2 = 0; s2 < S; ++s2) m = fmaxf(m, sm.rx_ml[s2][0][h]);
+                float num = 0.0f, den = 0.0f;
+                for (int s2 = 0; s2 < S; ++s2) {
+                    // a span without positions (maximum -inf) weighs nothing
+                    const float ms = sm.rx_ml[s2][0][h];
+                    const bool live = ms != -INFINITY;
+                    const float w = live ? expf(__fsub_rn(ms, m)) : 0.0f;
+                    den = fmaf(sm.rx_ml[s2][1][h], w, den);
+                    num = fmaf(live ? sm.rx_o[s2 * per_cta + i] : 0.0f, w, num);
+                }
+                emit(it, __fdiv_rn(num, den));
+            }
         }
         if (a.absmax_out) {
             amax = warp_max(amax);
             if (lane == 0 && amax > 0.0f) atomicMax(a.absmax_out + b, __float_as_uint(amax));
         }
     }
-    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
 }
 
 // Standalone QuantizedKVCache::append (layers/kv_cache.rs:50-92) for one new token per sequence:
