@@ -1127,22 +1127,27 @@ extern "C" bt_status bt_model_enqueue_products(bt_model* m, int batch, int as_in
 
 extern "C" int bt_model_launches_per_step(const bt_model* m, int batch) {
     if (!m) return 0;
+    // kernels of this library only: NCCL's own kernels (all-reduce, all-gather) are not counted
+    const bool split_head = m->tp > 1 && m->comm && m->lm_gather;  // the head's rows cut over the ranks
     if (batch <= 8) {
-        // fused path: per layer 4 products + attention pair or TTT update; embedding, lm_head per 4 tokens, pick
-        // 4 products + attention or TTT update; tensor parallel: + 2 scale epilogues after the NCCL all-reduces, or
-        // + 2 max-exchange and 2 sum-exchange kernels over peer memory
+        // fused path: per layer 4 products + attention or TTT update; tensor parallel: + 2 scale epilogues after the
+        // NCCL all-reduces, or + 2 max-exchange and 2 sum-exchange kernels over peer memory;
+        // embedding, lm_head per 4 tokens, pick (split head: gathered-rows copy, arg-max, position advance instead)
         int per_layer = 4 + 1 + (m->tp > 1 ? (tp_peer_ready(m->peer) ? 4 : 2) : 0);
         if (m->tp == 1 && m->cfg.arch == 1 && batch >= kSplitQuantBatch) per_layer += 4;  // a quantiser kernel in front of every product
-        return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + 1;
+        return m->cfg.num_layers * per_layer + 1 + (batch + 3) / 4 + (split_head ? 3 : 1);
     }
     // batches above 8: per layer 3 row kernels (norm1, norm2, SiLU*up, quantiser included), the quantiser of the
-    // attention / TTT output, 4 tensor-core products (+ a finishing kernel each where k is split), attention
-    // or TTT update; embedding, lm_head (tensor-core: prepare + product; else per 8 tokens), pick
+    // attention / TTT output, 4 tensor-core products, attention or TTT update; tensor parallel: each of the two
+    // row-parallel projections also has its scale-and-residual kernel, and SiLU*up and the quantiser of its result
+    // are two kernels; embedding; lm_head (tensor-core: prepare + product; else per 8 tokens) + pick pair, or with a
+    // split head the gathered-rows copy, arg-max and position advance
     const Layer& L = m->layers[0];
     const bt_linear* seq[4] = {m->cfg.arch == 1 ? L.qkv : L.ttt_down, m->cfg.arch == 1 ? L.o : L.ttt_up, L.gate_up_il, L.down};
-    int per_layer = 3 + 1 + 1;
+    int per_layer = 3 + 1 + 1 + (m->tp > 1 ? 3 : 0);
     for (const bt_linear* lin : seq) per_layer += gemm_tc_kernels(lin->dev(), batch, m->sm_count);
-    return m->cfg.num_layers * per_layer + 1 + (m->lm_tiles ? 2 + 2 : (batch + 7) / 8 + 1);
+    const int head = m->lm_tiles ? 2 : (batch + 7) / 8;
+    return m->cfg.num_layers * per_layer + 1 + head + (split_head ? 3 : (m->lm_tiles ? 2 : 1));
 }
 
 
