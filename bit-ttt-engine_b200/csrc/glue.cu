@@ -37,6 +37,9 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     __syncthreads();
     return r;
 }
+// REUSE = false: `red` is used by this one reduction only in the kernel, the closing barrier (which protects the
+// array against the next use) is left out.
+template <bool REUSE = true>
 __device__ __forceinline__ float block_max(float v, float* red) {
     v = warp_max(v);
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -44,9 +47,10 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     __syncthreads();
     float r = l < nw ? red[l] : 0.0f;
     r = warp_max(r);
-    __syncthreads();
+    if (REUSE) __syncthreads();
     return r;
 }
+template <bool REUSE = true>
 __device__ __forceinline__ double block_sum_d(double v, double* red) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -56,7 +60,7 @@ __device__ __forceinline__ double block_sum_d(double v, double* red) {
     double r = l < nw ? red[l] : 0.0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-    __syncthreads();
+    if (REUSE) __syncthreads();
     return r;
 }
 __device__ __forceinline__ int block_sum_i(int v, int* red) {
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(1024) row_quant_kernel(const T* __restrict__ x
             ss = fma((double)v.z, (double)v.z, ss);
             ss = fma((double)v.w, (double)v.w, ss);
         }
-        ss = block_sum_d(ss, red_d);
+        ss = block_sum_d<false>(ss, red_d);
         const float denom = sqrtf(__fadd_rn((float)(ss / (double)k), eps));
         for (int gi = threadIdx.x; gi < groups; gi += blockDim.x) {
             float4 v = *reinterpret_cast<const float4*>(row + 4 * gi);  // written by this same thread
@@ -187,7 +191,7 @@ __global__ void __launch_bounds__(1024) row_quant_kernel(const T* __restrict__ x
             amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
     }
-    amax = block_max(amax, red_f);
+    amax = block_max<false>(amax, red_f);
     if (amax_out) {
         for (int gi = threadIdx.x; gi < groups; gi += blockDim.x)
             *reinterpret_cast<float4*>(v_out + (int64_t)b * k + 4 * gi) = *reinterpret_cast<const float4*>(row + 4 * gi);
