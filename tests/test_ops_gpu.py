@@ -62,7 +62,10 @@ def test_ttt_zero_feature_is_safe(bt):
     (4, 2, 64, 9, 2, 128, 1), (32, 8, 128, 5, 2, 128, 1), (8, 1, 32, 70, 2, 128, 1), (4, 4, 64, 3, 2, 128, 1),
     # one span per (sequence, KV head) pair (80 pairs: two would not fit in one wave): the span grows past
     # one and two 128-position tiles, so the tile loop, the next-tile copies and the running maximum are used
-    (16, 8, 128, 290, 10, 320, 41), (8, 8, 64, 150, 10, 160, 29)])
+    (16, 8, 128, 290, 10, 320, 41), (8, 8, 64, 150, 10, 160, 29),
+    # one (sequence, KV head) pair, as on a rank of eight-way tensor parallelism: the largest cluster the GPU
+    # offers, most of its spans empty at first, more and more of them pushing partial columns as the context grows
+    (4, 1, 128, 300, 1, 2112, 37)])
 def test_attention_decode_matches_oracle(bt, oracle, n_heads, n_kv, hd, steps, batch, max_seq, every):
     rng = np.random.default_rng(n_heads * 1000 + hd)
     theta = 10000.0
