@@ -647,6 +647,8 @@ cudaError_t launch_gemm_tc(const LinearDev& lin, const void* x, int64_t x_stride
                            int32_t* qsum, void* out, int64_t out_stride, int epilogue, unsigned int* err, int sm_count,
                            cudaStream_t stream, bool prequantised, bt_dtype x_dtype) {
     if (lin.w.n_bases != 1 && epilogue == EPI_BF16) return cudaErrorInvalidValue;
+    if (epilogue != EPI_I32 && epilogue != EPI_F32 && epilogue != EPI_F32_ACCUM && epilogue != EPI_BF16)
+        return cudaErrorInvalidValue;  // (the SiLU*up epilogue exists in the streaming kernel only)
     const int nt = m <= 64 ? 64 : 128;
     const int k = (int)lin.w.k_in, kts = (int)lin.w.k_tiles;
     cudaError_t e = cudaSuccess;
